@@ -1,0 +1,128 @@
+"""In-tree native builds: host runtime (g++) and sm_100a CUDA kernels (nvcc).
+
+The reference builds with CMake against CANN (CMakeLists.txt, ggml/src/ggml-cann/CMakeLists.txt);
+here two shared libraries are produced next to the Python package so that they travel with a
+source snapshot and are loaded with ctypes:
+
+* ``lib/libjib200_runtime.so`` — paged-KV allocator, scheduler, GGUF, tokenizer, samplers, llama.h C API
+* ``lib/libjib200_kernels.so`` — every CUDA kernel, compiled for ``sm_100a`` only
+
+``python -m jittorinfer_b200.build`` builds both; each library is rebuilt only when a source is
+newer than the output.
+"""
+from __future__ import annotations
+
+import glob
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from typing import List
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+RUNTIME_SO = os.path.join(LIBDIR, "libjib200_runtime.so")
+KERNELS_SO = os.path.join(LIBDIR, "libjib200_kernels.so")
+
+NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def _newer(srcs: List[str], out: str) -> bool:
+    if not os.path.exists(out):
+        return True
+    t = os.path.getmtime(out)
+    return any(os.path.getmtime(s) > t for s in srcs)
+
+
+def _run(cmd: List[str], verbose: bool):
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        raise RuntimeError(f"build failed: {' '.join(cmd[:3])} ...")
+    if verbose and r.stdout.strip():
+        print(r.stdout)
+    return r.stdout
+
+
+def nvcc_path() -> str:
+    p = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(p):
+        raise RuntimeError("nvcc not found")
+    return p
+
+
+def build_runtime(force: bool = False, verbose: bool = False) -> str:
+    srcs = sorted(glob.glob(os.path.join(CSRC, "runtime", "*.cpp")))
+    deps = srcs + glob.glob(os.path.join(CSRC, "runtime", "*.h")) + glob.glob(os.path.join(CSRC, "include", "*.h"))
+    os.makedirs(LIBDIR, exist_ok=True)
+    if force or _newer(deps, RUNTIME_SO):
+        objs = []
+        objdir = os.path.join(LIBDIR, "obj")
+        os.makedirs(objdir, exist_ok=True)
+        procs = []
+        for s in srcs:
+            o = os.path.join(objdir, os.path.basename(s) + ".o")
+            objs.append(o)
+            if force or _newer([s] + [d for d in deps if d.endswith(".h")], o):
+                cmd = ["g++", "-std=c++17", "-O2", "-g", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function",
+                       "-I", os.path.join(CSRC, "include"), "-I", os.path.join(CSRC, "runtime"), "-c", s, "-o", o]
+                if verbose:
+                    print(" ".join(cmd), flush=True)
+                procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        for cmd, p in procs:
+            out, _ = p.communicate()
+            if p.returncode != 0:
+                sys.stderr.write(out)
+                raise RuntimeError(f"build failed: {cmd[-3]}")
+        _run(["g++", "-shared", "-o", RUNTIME_SO] + objs + ["-lpthread", "-ldl"], verbose)
+    return RUNTIME_SO
+
+
+def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[str] = ()) -> str:
+    srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
+    hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h"))
+    os.makedirs(LIBDIR, exist_ok=True)
+    if not srcs:
+        raise RuntimeError("no CUDA sources found")
+    if force or _newer(srcs + hdrs, KERNELS_SO):
+        nvcc = nvcc_path()
+        objdir = os.path.join(LIBDIR, "obj")
+        os.makedirs(objdir, exist_ok=True)
+        objs, procs = [], []
+        for s in srcs:
+            o = os.path.join(objdir, os.path.basename(s) + ".o")
+            objs.append(o)
+            if force or _newer([s] + hdrs, o):
+                cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", *NVCC_ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden",
+                       "--expt-relaxed-constexpr", "-Xptxas", "-v", *extra_flags,
+                       "-I", os.path.join(CSRC, "kernels"), "-c", s, "-o", o]
+                if verbose:
+                    print(" ".join(cmd), flush=True)
+                procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        log = []
+        for s, p in procs:
+            out, _ = p.communicate()
+            log.append(f"==== {os.path.basename(s)}\n{out}")
+            if p.returncode != 0:
+                sys.stderr.write(out)
+                raise RuntimeError(f"nvcc failed on {s}")
+        if log:
+            with open(os.path.join(LIBDIR, "ptxas.log"), "w") as f:
+                f.write("\n".join(log))
+        _run([nvcc, "-shared", *NVCC_ARCH, "-o", KERNELS_SO] + objs, verbose)
+    return KERNELS_SO
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    return build_runtime(force, verbose), build_kernels(force, verbose)
+
+
+if __name__ == "__main__":
+    f = "--force" in sys.argv
+    v = "-v" in sys.argv or "--verbose" in sys.argv
+    for p in build_all(f, v):
+        print("built", p)

@@ -1,0 +1,110 @@
+// C ABI over the host runtime (paged KV allocator + scheduler) for the Python engine (ctypes) and
+// the llama.h layer.  Handles are opaque pointers; every array is caller-owned.
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "kv_paged.h"
+#include "scheduler.h"
+
+using namespace jib;
+
+#define JIB_API extern "C" __attribute__((visibility("default")))
+
+struct jib_sched {
+    Scheduler sched;
+    std::vector<StepEvent> events;
+    jib_sched(PagedKv * kv, int n_slots, int n_batch, int n_ctx_slot, int eos, int n_keep, bool cb)
+        : sched(kv, n_slots, n_batch, n_ctx_slot, eos, n_keep, cb) {}
+};
+
+// ---- paged KV -------------------------------------------------------------------------------
+JIB_API PagedKv * jib_kv_create(int n_blocks, int block_size, int max_seqs) { return new PagedKv(n_blocks, block_size, max_seqs); }
+JIB_API void jib_kv_destroy(PagedKv * kv) { delete kv; }
+JIB_API int jib_kv_append(PagedKv * kv, int seq, int n, int32_t * slots) { return kv->append(seq, n, slots) ? 0 : 1; }
+JIB_API int jib_kv_blocks_needed(PagedKv * kv, int seq, int n) { return kv->blocks_needed(seq, n); }
+JIB_API int jib_kv_seq_rm(PagedKv * kv, int seq, int p0, int p1) { return kv->seq_rm(seq, p0, p1) ? 1 : 0; }
+JIB_API int jib_kv_seq_cp(PagedKv * kv, int src, int dst, int p0, int p1) { return kv->seq_cp(src, dst, p0, p1) ? 1 : 0; }
+JIB_API void jib_kv_seq_keep(PagedKv * kv, int seq) { kv->seq_keep(seq); }
+JIB_API void jib_kv_clear(PagedKv * kv) { kv->clear(); }
+JIB_API int jib_kv_seq_len(PagedKv * kv, int seq) { return kv->seq_len(seq); }
+JIB_API int jib_kv_seq_blocks(PagedKv * kv, int seq, int32_t * out, int cap) {
+    const auto & b = kv->seq_blocks(seq);
+    int n = std::min<int>((int) b.size(), cap);
+    if (out) std::memcpy(out, b.data(), n * sizeof(int32_t));
+    return (int) b.size();
+}
+JIB_API int jib_kv_free_blocks(PagedKv * kv) { return kv->free_blocks(); }
+JIB_API int jib_kv_used_blocks(PagedKv * kv) { return kv->used_blocks(); }
+JIB_API int jib_kv_n_blocks(PagedKv * kv) { return kv->n_blocks(); }
+JIB_API int jib_kv_block_size(PagedKv * kv) { return kv->block_size(); }
+JIB_API int jib_kv_refcount(PagedKv * kv, int block) { return kv->refcount(block); }
+JIB_API float jib_kv_fragmentation(PagedKv * kv) { return kv->fragmentation(); }
+JIB_API int jib_kv_check(PagedKv * kv) { return kv->check() ? 1 : 0; }
+// Pops up to cap queued copy-on-write copies.
+JIB_API int jib_kv_take_copies(PagedKv * kv, int32_t * src, int32_t * dst, int cap) {
+    auto & p = kv->pending_copies();
+    int n = std::min<int>((int) p.size(), cap);
+    for (int i = 0; i < n; ++i) { src[i] = p[i].first; dst[i] = p[i].second; }
+    p.erase(p.begin(), p.begin() + n);
+    return n;
+}
+JIB_API int jib_kv_defrag(PagedKv * kv, int max_moves, int32_t * src, int32_t * dst) {
+    auto m = kv->defrag(max_moves);
+    for (size_t i = 0; i < m.size(); ++i) { src[i] = m[i].first; dst[i] = m[i].second; }
+    return (int) m.size();
+}
+
+// ---- scheduler ------------------------------------------------------------------------------
+JIB_API jib_sched * jib_sched_create(PagedKv * kv, int n_slots, int n_batch, int n_ctx_slot, int eos_id, int n_keep,
+                                     int cont_batching) {
+    return new jib_sched(kv, n_slots, n_batch, n_ctx_slot, eos_id, n_keep, cont_batching != 0);
+}
+JIB_API void jib_sched_destroy(jib_sched * s) { delete s; }
+JIB_API void jib_sched_add(jib_sched * s, int64_t req_id, const int32_t * prompt, int n_prompt, int max_new, int ignore_eos) {
+    Request r;
+    r.id = req_id;
+    r.prompt.assign(prompt, prompt + n_prompt);
+    r.max_new = max_new;
+    r.ignore_eos = ignore_eos != 0;
+    s->sched.add_request(r);
+}
+JIB_API int jib_sched_cancel(jib_sched * s, int64_t req_id) { return s->sched.cancel(req_id, &s->events) ? 1 : 0; }
+// info_out: n_tokens, n_seqs, n_out, n_decode_seqs, max_q_len, n_preempted, n_copies
+JIB_API int jib_sched_step(jib_sched * s, StepArrays * arrays, int32_t * info_out) {
+    StepInfo i = s->sched.step(*arrays);
+    info_out[0] = i.n_tokens; info_out[1] = i.n_seqs; info_out[2] = i.n_out; info_out[3] = i.n_decode_seqs;
+    info_out[4] = i.max_q_len; info_out[5] = i.n_preempted; info_out[6] = i.n_copies;
+    return i.n_tokens;
+}
+JIB_API void jib_sched_commit(jib_sched * s, const int32_t * sampled, int n_out) { s->sched.commit(sampled, n_out, &s->events); }
+// Pops queued events; each is 6 x int64: req_id, slot, token, finish, n_prompt, n_decoded.
+JIB_API int jib_sched_take_events(jib_sched * s, int64_t * out, int cap) {
+    int n = std::min<int>((int) s->events.size(), cap);
+    for (int i = 0; i < n; ++i) {
+        const StepEvent & e = s->events[i];
+        int64_t * o = out + 6 * i;
+        o[0] = e.req_id; o[1] = e.slot; o[2] = e.token; o[3] = e.finish; o[4] = e.n_prompt; o[5] = e.n_decoded;
+    }
+    s->events.erase(s->events.begin(), s->events.begin() + n);
+    return n;
+}
+// Request id owning each output row of the last step().
+JIB_API int jib_sched_out_reqs(jib_sched * s, int64_t * out, int cap) {
+    const auto & v = s->sched.last_out_slots();
+    int n = std::min<int>((int) v.size(), cap);
+    for (int i = 0; i < n; ++i) out[i] = s->sched.slots()[v[i]].req_id;
+    return n;
+}
+JIB_API int64_t jib_sched_slot_req(jib_sched * s, int slot) { return s->sched.slots()[slot].req_id; }
+JIB_API int jib_sched_idle(jib_sched * s) { return s->sched.idle() ? 1 : 0; }
+JIB_API int jib_sched_n_waiting(jib_sched * s) { return s->sched.n_waiting(); }
+JIB_API int jib_sched_n_running(jib_sched * s) { return s->sched.n_running(); }
+JIB_API void jib_sched_set_n_batch(jib_sched * s, int n) { s->sched.set_n_batch(n); }
+JIB_API int jib_sched_slot_state(jib_sched * s, int slot) { return s->sched.slots()[slot].state; }
+// stats_out: steps, prompt_tokens, decode_tokens, preemptions, finished, prefix_hits
+JIB_API void jib_sched_stats(jib_sched * s, int64_t * o) {
+    const SchedStats & st = s->sched.stats();
+    o[0] = st.steps; o[1] = st.prompt_tokens; o[2] = st.decode_tokens; o[3] = st.preemptions; o[4] = st.finished; o[5] = st.prefix_hits;
+}

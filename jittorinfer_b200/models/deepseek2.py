@@ -1,0 +1,252 @@
+"""DeepSeek-V2 / V2-Lite module graph over a paged compressed-latent KV cache.
+
+This replaces the reference's per-step ggml graph construction (``llm_build_deepseek2``,
+src/llama-graph-deepseek2.cpp:113-405, with sub-graphs in src/llama-graph-attn.cpp and
+src/llama-graph-ffn.cpp) by a fixed PyTorch module graph whose ops are the sm_100a kernels in
+``jittorinfer_b200.ops``; the engine replays it as CUDA graphs per decode bucket.
+
+Differences from the reference that are deliberate:
+
+* attention always runs in the weight-absorbed MLA form over one latent row ``[c_kv | k_pe]``
+  per token (the reference also keeps a transposed duplicate of ``c_kv``,
+  src/llama-graph-attn.cpp:233-255, and its shipped multi-card server uses per-head K/V);
+* ``attn_q``/``attn_q_a`` and ``attn_kv_a_mqa`` share their input, so they are one GEMM;
+* sequence lengths and block tables replace the O(T*S) host-built mask
+  (src/llama-context.cpp:326-423);
+* the q-LoRA branch is selected by ``q_lora_rank``, not by ``n_layer == 27``.
+
+Under tensor parallelism every rank holds the full residual stream; attention heads, dense/shared
+FFN columns and routed experts are sharded (see ``models.weights.shard_dim``) and the two partial
+sums per layer are combined by ``comm.all_reduce`` (reference: src/llama-graph-deepseek2.cpp:294-297,
+365-368) or by the fused GEMM+all-reduce kernel when the communicator provides one.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from .hparams import DeepSeek2HParams
+from .weights import ShardSpec
+
+
+@dataclass
+class ForwardBatch:
+    """One engine step's inputs (all device tensors, int32 unless noted).
+
+    ``tokens/positions/slot_mapping`` have one entry per query token; tokens of one sequence are
+    contiguous.  Sequence ``b`` owns rows ``q_start[b]:q_start[b+1]`` and, after this step, has
+    ``seq_lens[b]`` cached tokens.  ``slot_mapping[i] < 0`` marks a padding row.
+    ``out_rows`` selects the rows whose logits are wanted.
+    """
+    tokens: torch.Tensor
+    positions: torch.Tensor
+    slot_mapping: torch.Tensor
+    block_tables: torch.Tensor
+    seq_lens: torch.Tensor
+    q_start: torch.Tensor
+    out_rows: torch.Tensor
+    max_q_len: int = 1
+    attn_meta: Optional[object] = None
+
+
+class _Layer:
+    __slots__ = ("attn_norm", "w_qkv_a", "q_a_norm", "w_q_b", "kv_a_norm", "w_uk", "w_uv", "w_o", "ffn_norm",
+                 "w_gate", "w_up", "w_down", "w_router", "router_bias", "w_gate_exps", "w_up_exps", "w_down_exps",
+                 "w_gate_sh", "w_up_sh", "w_down_sh", "is_moe")
+
+    def __init__(self):
+        for s in self.__slots__:
+            setattr(self, s, None)
+
+
+class DeepSeek2Model:
+    def __init__(self, hp: DeepSeek2HParams, weights: Iterable[Tuple[str, torch.Tensor]],
+                 dtype: torch.dtype = torch.bfloat16, device="cpu", spec: ShardSpec = ShardSpec(),
+                 comm=None, max_positions: int = 8192, block_size: int = 64):
+        self.hp = hp
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.spec = spec
+        self.comm = comm
+        self.block_size = block_size
+        if hp.n_head % spec.tp_size:
+            raise ValueError("n_head must be divisible by tp_size")
+        self.n_head_local = hp.n_head // spec.tp_size
+        if spec.expert_parallel:
+            if hp.n_expert % spec.tp_size:
+                raise ValueError("n_expert must be divisible by the expert-parallel size")
+            self.n_expert_local = hp.n_expert // spec.tp_size
+            self.expert_base = spec.tp_rank * self.n_expert_local
+        else:
+            self.n_expert_local = hp.n_expert
+            self.expert_base = 0
+        self.layers: List[_Layer] = [_Layer() for _ in range(hp.n_layer)]
+        self.tok_embd = None
+        self.out_norm = None
+        self.w_out = None
+        self._load(weights)
+        lo, hi = hp.yarn_corr_dims()
+        self.max_positions = max_positions
+        self.rope_table = ops.ref.yarn_table(max_positions, hp.qk_rope_head_dim, hp.rope_freq_base, hp.freq_scale,
+                                             hp.ext_factor, hp.rope_attn, lo, hi, device=self.device)
+
+    # ---- weight intake -------------------------------------------------------------------
+    def _dev(self, t: torch.Tensor, dtype=None) -> torch.Tensor:
+        return t.to(device=self.device, dtype=dtype or self.dtype).contiguous()
+
+    def _load(self, weights: Iterable[Tuple[str, torch.Tensor]]):
+        hp = self.hp
+        H, dn, dv, r = self.n_head_local, hp.qk_nope_head_dim, hp.v_head_dim, hp.kv_lora_rank
+        pend: Dict[str, torch.Tensor] = {}
+        for name, t in weights:
+            if name == "token_embd.weight":
+                self.tok_embd = self._dev(t)
+            elif name == "output_norm.weight":
+                self.out_norm = self._dev(t, torch.float32)
+            elif name == "output.weight":
+                self.w_out = self._dev(t)
+            elif name.startswith("blk."):
+                _, il, base, _ = name.split(".", 3)
+                L = self.layers[int(il)]
+                key = f"{il}.{base}"
+                if base == "attn_norm":
+                    L.attn_norm = self._dev(t, torch.float32)
+                elif base == "ffn_norm":
+                    L.ffn_norm = self._dev(t, torch.float32)
+                elif base == "attn_q_a_norm":
+                    L.q_a_norm = self._dev(t, torch.float32)
+                elif base == "attn_kv_a_norm":
+                    L.kv_a_norm = self._dev(t, torch.float32)
+                elif base in ("attn_q", "attn_q_a", "attn_kv_a_mqa"):
+                    pend[key] = self._dev(t)
+                    qk = f"{il}.attn_q" if hp.is_lite else f"{il}.attn_q_a"
+                    kk = f"{il}.attn_kv_a_mqa"
+                    if qk in pend and kk in pend:
+                        L.w_qkv_a = torch.cat([pend.pop(qk), pend.pop(kk)], dim=0).contiguous()
+                elif base == "attn_q_b":
+                    L.w_q_b = self._dev(t)
+                elif base == "attn_kv_b":
+                    # load-time re-layout into the absorbed factors (reference: wkv_b_post_process,
+                    # src/llama-model.cpp:408-459)
+                    w = self._dev(t).view(H, dn + dv, r)
+                    L.w_uk = w[:, :dn, :].contiguous()          # [H, dn, r]
+                    L.w_uv = w[:, dn:, :].contiguous()          # [H, dv, r]
+                elif base == "attn_output":
+                    L.w_o = self._dev(t)
+                elif base == "ffn_gate":
+                    L.w_gate = self._dev(t)
+                elif base == "ffn_up":
+                    L.w_up = self._dev(t)
+                elif base == "ffn_down":
+                    L.w_down = self._dev(t)
+                elif base == "ffn_gate_inp":
+                    L.w_router = self._dev(t, torch.float32)
+                    L.is_moe = True
+                elif base == "exp_probs_b":
+                    L.router_bias = self._dev(t, torch.float32)
+                elif base == "ffn_gate_exps":
+                    L.w_gate_exps = self._dev(t)
+                elif base == "ffn_up_exps":
+                    L.w_up_exps = self._dev(t)
+                elif base == "ffn_down_exps":
+                    L.w_down_exps = self._dev(t)
+                elif base == "ffn_gate_shexp":
+                    L.w_gate_sh = self._dev(t)
+                elif base == "ffn_up_shexp":
+                    L.w_up_sh = self._dev(t)
+                elif base == "ffn_down_shexp":
+                    L.w_down_sh = self._dev(t)
+                else:
+                    raise KeyError(f"unknown tensor {name}")
+            else:
+                raise KeyError(f"unknown tensor {name}")
+        if self.w_out is None:
+            self.w_out = self.tok_embd
+        for il, L in enumerate(self.layers):
+            need = ["attn_norm", "w_qkv_a", "kv_a_norm", "w_uk", "w_o", "ffn_norm"]
+            need += ["w_router", "w_gate_exps", "w_up_exps", "w_down_exps"] if L.is_moe else ["w_gate", "w_up", "w_down"]
+            missing = [n for n in need if getattr(L, n) is None]
+            if missing:
+                raise ValueError(f"layer {il}: missing tensors {missing}")
+
+    def weight_bytes(self) -> int:
+        n = 0
+        seen = set()
+        for obj in [self] + self.layers:
+            names = obj.__slots__ if hasattr(obj, "__slots__") else ("tok_embd", "out_norm", "w_out")
+            for s in names:
+                t = getattr(obj, s, None)
+                if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    n += t.numel() * t.element_size()
+        return n
+
+    # ---- forward ---------------------------------------------------------------------------
+    def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.comm is not None and self.spec.sharded:
+            return self.comm.all_reduce(x)
+        return x
+
+    def _row_parallel(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        """y = all_reduce(x_shard @ w_shard^T) + residual.  One fused kernel when the communicator has it."""
+        if self.comm is not None and self.spec.sharded:
+            return self.comm.linear_all_reduce(x, w, residual)
+        return ops.linear(x, w, residual=residual)
+
+    def _attention(self, L: _Layer, h: torch.Tensor, batch: ForwardBatch, cache_l: torch.Tensor) -> torch.Tensor:
+        hp = self.hp
+        H, dn, dr, r = self.n_head_local, hp.qk_nope_head_dim, hp.qk_rope_head_dim, hp.kv_lora_rank
+        T = h.shape[0]
+        qkv = ops.linear(h, L.w_qkv_a)
+        nq = qkv.shape[1] - hp.kv_row
+        ckv = qkv[:, nq:]
+        if hp.is_lite:
+            q = qkv[:, :nq]
+        else:
+            qa, _ = ops.rmsnorm(qkv[:, :nq].contiguous(), L.q_a_norm, hp.rms_eps)
+            q = ops.linear(qa, L.w_q_b)
+        q_full = torch.empty(T, H, r + dr, dtype=h.dtype, device=h.device)
+        q_nope = ops.mla_qkv_post(q, ckv, L.kv_a_norm, hp.rms_eps, self.rope_table, batch.positions,
+                                  batch.slot_mapping, cache_l, q_full, H, dn, dr, r)
+        ops.q_absorb(q_nope, L.w_uk, q_full, r)
+        o_lat = ops.mla_attention(q_full, cache_l, batch.block_tables, batch.seq_lens, batch.q_start, hp.kq_scale,
+                                  r, self.block_size, batch.max_q_len, batch.attn_meta)
+        return ops.v_up(o_lat, L.w_uv)
+
+    def _mlp(self, L: _Layer, g: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        hp = self.hp
+        if not L.is_moe:
+            hmid = ops.gateup_silu(g, L.w_gate, L.w_up)
+            return self._row_parallel(hmid, L.w_down, residual)
+        ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
+                                hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid")
+        if self.spec.sharded and not self.spec.expert_parallel:
+            moe = ops.moe_experts(g, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, 0)
+        else:
+            moe = ops.moe_experts(g, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, self.expert_base)
+        if L.w_gate_sh is not None:
+            hs = ops.gateup_silu(g, L.w_gate_sh, L.w_up_sh)
+            part = ops.linear(hs, L.w_down_sh, residual=moe, out_dtype=torch.float32)
+        else:
+            part = moe
+        if self.comm is not None and self.spec.sharded:
+            part = self.comm.all_reduce(part)
+        return (part + residual.float()).to(g.dtype)
+
+    @torch.no_grad()
+    def forward(self, batch: ForwardBatch, kv_cache: torch.Tensor) -> torch.Tensor:
+        """kv_cache [n_layer, n_slots, r+dr].  Returns fp32 logits [len(out_rows), n_vocab]."""
+        hp = self.hp
+        x = ops.embed_gather(self.tok_embd, batch.tokens)
+        for il, L in enumerate(self.layers):
+            h, _ = ops.rmsnorm(x, L.attn_norm, hp.rms_eps)
+            a = self._attention(L, h, batch, kv_cache[il])
+            y = self._row_parallel(a, L.w_o, x)
+            g, _ = ops.rmsnorm(y, L.ffn_norm, hp.rms_eps)
+            x = self._mlp(L, g, y)
+        xo = x[batch.out_rows.long()] if batch.out_rows is not None else x
+        xo, _ = ops.rmsnorm(xo.contiguous(), self.out_norm, hp.rms_eps)
+        return ops.linear(xo, self.w_out, out_dtype=torch.float32)

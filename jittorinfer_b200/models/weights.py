@@ -1,0 +1,208 @@
+"""Tensor table, sharding plan, random initialisation and GGUF load for DeepSeek-V2 weights.
+
+Tensor names and shapes are the GGUF ones the reference creates in ``llama_model::load_tensors``
+(src/llama-model.cpp:744-867; name table src/llama-arch.cpp:903-927).  The per-tensor shard rule
+mirrors the reference's ``llm_split_method`` choices (src/llama-model.cpp:309-322, 761-866):
+
+* by head: ``attn_q`` / ``attn_q_b`` / ``attn_kv_b`` (output rows), ``attn_output`` (input columns)
+* dense FFN and shared experts: gate/up by output rows, down by input columns
+* routed experts: on the expert axis under expert parallelism, else on the ``n_ff_exp`` axis
+* replicated: norms, ``attn_q_a``, ``attn_kv_a_mqa``, router, token embedding, ``output``
+
+A rank only ever materialises its own shard: the GGUF path slices the mmap view, the random path
+generates each tensor from a (seed, tensor-name, outer-index) stream so that every rank's shard is
+bit-identical to the corresponding slice of the single-GPU tensor.
+"""
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass
+from typing import Callable, Dict, Iterator, Optional, Tuple
+
+import torch
+
+from .hparams import DeepSeek2HParams
+
+
+@dataclass(frozen=True)
+class ShardSpec:
+    tp_rank: int = 0
+    tp_size: int = 1
+    expert_parallel: bool = False     # routed experts split on the expert axis over the tp group
+
+    @property
+    def sharded(self) -> bool:
+        return self.tp_size > 1
+
+
+def tensor_table(hp: DeepSeek2HParams) -> Dict[str, Tuple[int, ...]]:
+    """name -> full (unsharded) torch-order shape."""
+    d, H = hp.n_embd, hp.n_head
+    t: Dict[str, Tuple[int, ...]] = {"token_embd.weight": (hp.n_vocab, d)}
+    for il in range(hp.n_layer):
+        p = f"blk.{il}."
+        t[p + "attn_norm.weight"] = (d,)
+        if hp.is_lite:
+            t[p + "attn_q.weight"] = (H * hp.qk_head_dim, d)
+        else:
+            t[p + "attn_q_a.weight"] = (hp.q_lora_rank, d)
+            t[p + "attn_q_a_norm.weight"] = (hp.q_lora_rank,)
+            t[p + "attn_q_b.weight"] = (H * hp.qk_head_dim, hp.q_lora_rank)
+        t[p + "attn_kv_a_mqa.weight"] = (hp.kv_row, d)
+        t[p + "attn_kv_a_norm.weight"] = (hp.kv_lora_rank,)
+        t[p + "attn_kv_b.weight"] = (H * (hp.qk_nope_head_dim + hp.v_head_dim), hp.kv_lora_rank)
+        t[p + "attn_output.weight"] = (d, H * hp.v_head_dim)
+        t[p + "ffn_norm.weight"] = (d,)
+        if il < hp.n_layer_dense_lead:
+            t[p + "ffn_gate.weight"] = (hp.n_ff, d)
+            t[p + "ffn_up.weight"] = (hp.n_ff, d)
+            t[p + "ffn_down.weight"] = (d, hp.n_ff)
+        else:
+            t[p + "ffn_gate_inp.weight"] = (hp.n_expert, d)
+            t[p + "ffn_gate_exps.weight"] = (hp.n_expert, hp.n_ff_exp, d)
+            t[p + "ffn_up_exps.weight"] = (hp.n_expert, hp.n_ff_exp, d)
+            t[p + "ffn_down_exps.weight"] = (hp.n_expert, d, hp.n_ff_exp)
+            if hp.n_expert_shared:
+                fs = hp.n_ff_exp * hp.n_expert_shared
+                t[p + "ffn_gate_shexp.weight"] = (fs, d)
+                t[p + "ffn_up_shexp.weight"] = (fs, d)
+                t[p + "ffn_down_shexp.weight"] = (d, fs)
+    t["output_norm.weight"] = (d,)
+    t["output.weight"] = (hp.n_vocab, d)
+    return t
+
+
+def shard_dim(name: str, spec: ShardSpec) -> Optional[int]:
+    """Torch dim along which ``name`` is split across the TP group (None = replicated)."""
+    if not spec.sharded:
+        return None
+    base = name.split(".")[-2] if name.startswith("blk.") else name
+    if base in ("attn_q", "attn_q_b", "attn_kv_b", "ffn_gate", "ffn_up", "ffn_gate_shexp", "ffn_up_shexp"):
+        return 0
+    if base in ("attn_output", "ffn_down", "ffn_down_shexp"):
+        return 1
+    if base in ("ffn_gate_exps", "ffn_up_exps"):
+        return 0 if spec.expert_parallel else 1
+    if base == "ffn_down_exps":
+        return 0 if spec.expert_parallel else 2
+    return None
+
+
+def local_shape(name: str, shape: Tuple[int, ...], spec: ShardSpec) -> Tuple[int, ...]:
+    dim = shard_dim(name, spec)
+    if dim is None:
+        return shape
+    if shape[dim] % spec.tp_size:
+        raise ValueError(f"{name}: dim {dim} ({shape[dim]}) is not divisible by tp_size {spec.tp_size}")
+    s = list(shape)
+    s[dim] //= spec.tp_size
+    return tuple(s)
+
+
+def _stream_seed(seed: int, name: str, outer: int) -> int:
+    h = hashlib.blake2b(f"{seed}:{name}:{outer}".encode(), digest_size=8).digest()
+    return int.from_bytes(h, "little") & 0x7FFF_FFFF_FFFF_FFFF
+
+
+def random_tensor(name: str, shape: Tuple[int, ...], spec: ShardSpec, seed: int, std: float,
+                  dtype: torch.dtype, device) -> torch.Tensor:
+    """Shard of a N(0, std) tensor (norm gammas: 1 + N(0, std)); identical across shardings.
+
+    Values are drawn on the CPU generator one outer slice at a time (3-D expert tensors: per expert;
+    2-D: whole matrix) so that device and world size never change the numbers.
+    """
+    dim = shard_dim(name, spec)
+    is_norm = name.endswith("_norm.weight")
+    gen = torch.Generator(device="cpu")
+
+    def draw(outer: int, shp) -> torch.Tensor:
+        gen.manual_seed(_stream_seed(seed, name, outer))
+        x = torch.randn(shp, generator=gen, dtype=torch.float32) * std
+        return x + 1.0 if is_norm else x
+
+    if len(shape) == 3:
+        E = shape[0]
+        if dim == 0:
+            step = E // spec.tp_size
+            experts = range(spec.tp_rank * step, (spec.tp_rank + 1) * step)
+        else:
+            experts = range(E)
+        parts = []
+        for e in experts:
+            x = draw(e, shape[1:])
+            if dim in (1, 2):
+                n = shape[dim] // spec.tp_size
+                x = x.narrow(dim - 1, spec.tp_rank * n, n)
+            parts.append(x.to(dtype).to(device))
+        return torch.stack(parts, 0)
+    x = draw(0, shape)
+    if dim is not None:
+        n = shape[dim] // spec.tp_size
+        x = x.narrow(dim, spec.tp_rank * n, n)
+    return x.to(dtype).contiguous().to(device)
+
+
+def fast_random_tensor(name: str, shape: Tuple[int, ...], spec: ShardSpec, seed: int, std: float,
+                       dtype: torch.dtype, device) -> torch.Tensor:
+    """Device-side generation for benchmark-sized models (values depend on the sharding)."""
+    shp = local_shape(name, shape, spec)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(_stream_seed(seed, name, spec.tp_rank if shard_dim(name, spec) is not None else 0))
+    x = torch.empty(shp, dtype=dtype, device=device)
+    x.normal_(0.0, std, generator=gen)
+    if name.endswith("_norm.weight"):
+        x += 1.0
+    return x
+
+
+def iter_random(hp: DeepSeek2HParams, spec: ShardSpec = ShardSpec(), seed: int = 0, std: float = 0.02,
+                dtype: torch.dtype = torch.float32, device="cpu", fast: bool = False
+                ) -> Iterator[Tuple[str, torch.Tensor]]:
+    fn = fast_random_tensor if fast else random_tensor
+    for name, shape in tensor_table(hp).items():
+        yield name, fn(name, shape, spec, seed, std, dtype, device)
+
+
+def random_weights(hp: DeepSeek2HParams, **kw) -> Dict[str, torch.Tensor]:
+    return dict(iter_random(hp, **kw))
+
+
+def write_random_gguf(path: str, hp: DeepSeek2HParams, seed: int = 0, std: float = 0.02,
+                      dtype: torch.dtype = torch.float32, vocab: bool = True) -> None:
+    """Emit a random-init GGUF with the reference's key/tensor layout (and a byte-level toy vocab)."""
+    from ..gguf.io import GGUFWriter
+    w = GGUFWriter(path)
+    w.add_dict(hp.to_gguf_kv())
+    if vocab:
+        from ..utils.toy_vocab import toy_vocab_kv
+        w.add_dict(toy_vocab_kv(hp.n_vocab, hp.bos_id, hp.eos_id))
+    for name, t in iter_random(hp, seed=seed, std=std, dtype=torch.float32):
+        if t.dim() == 1:
+            w.add_tensor(name, t)                      # norms stay f32, as in real checkpoints
+        else:
+            w.add_tensor(name, t.to(dtype))
+    w.write()
+
+
+def iter_gguf(reader, hp: DeepSeek2HParams, spec: ShardSpec = ShardSpec()) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Yield (name, CPU shard view) for every tensor of the model; checks names and shapes."""
+    table = tensor_table(hp)
+    seen = 0
+    for name, shape in table.items():
+        if name not in reader.tensors:
+            if name == "output.weight" and "token_embd.weight" in reader.tensors:
+                yield name, reader.tensor("token_embd.weight")      # tied embeddings
+                continue
+            raise KeyError(f"GGUF is missing tensor {name}")
+        ti = reader.tensors[name]
+        if tuple(ti.shape) != tuple(shape):
+            raise ValueError(f"{name}: GGUF shape {ti.shape} != expected {shape}")
+        dim = shard_dim(name, spec)
+        seen += 1
+        if dim is None:
+            yield name, reader.tensor(name)
+        else:
+            yield name, reader.tensor_slice(name, dim, spec.tp_rank, spec.tp_size)
+    extra = [n for n in reader.tensors if n not in table and not n.endswith("exp_probs_b.bias")]
+    if extra:
+        raise ValueError(f"GGUF has {len(extra)} tensors the model does not use, e.g. {extra[:3]}")

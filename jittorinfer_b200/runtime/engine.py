@@ -1,0 +1,323 @@
+"""The serving engine: scheduler -> packed step inputs -> model forward (CUDA graph or eager) -> sample.
+
+One ``LLMEngine.step()`` is what one ``llama_decode`` + sampling round is in the reference
+(src/llama-execute-decode.cpp:156-344 driven by examples/server/server.cpp:1304-1564).  Differences
+by design:
+
+* the batch description (tokens, positions, slot mapping, block tables, sequence lengths) is written
+  by the native scheduler straight into ONE pinned host buffer and reaches the device with ONE
+  async copy per step — no host-built masks (src/llama-context.cpp:244-518);
+* decode-only batches replay a CUDA graph captured per batch bucket (the analogue of the reference's
+  persistent GE graph, src/llama-context-load-utils.cpp:134-174), with padding rows masked by
+  ``slot_mapping = -1`` / ``seq_len = 0``;
+* greedy sampling stays on the device (argmax kernel in the graph); other requests use a device
+  top-k ("presample", src/llama-execute-decode.cpp:132-154) followed by the host chain.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.deepseek2 import DeepSeek2Model, ForwardBatch
+from ..models.hparams import DeepSeek2HParams
+from .native_rt import PagedKV, Scheduler, StepArrays, i32p
+from .sampling import HostSampler, SamplingParams
+
+
+@dataclass
+class EngineConfig:
+    n_ctx: int = 16384                 # total cached tokens over all sequences (reference: n_ctx cell pool)
+    n_batch: int = 2048                # token budget of one step (chunked prefill)
+    n_parallel: int = 8                # concurrent sequences (slots)
+    n_ctx_slot: Optional[int] = None   # per-sequence limit; default n_ctx / n_parallel as in the reference
+    block_size: int = 64
+    n_keep: int = 0
+    cont_batching: bool = True
+    presample_count: int = 64
+    cuda_graphs: bool = True
+    graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
+    defrag_thold: float = -1.0         # <0 disables automatic defrag
+    defrag_max_moves: int = 256
+
+
+@dataclass
+class RequestState:
+    req_id: int
+    params: SamplingParams
+    sampler: Optional[HostSampler]
+    n_prompt: int
+    output: List[int] = field(default_factory=list)
+    finish_reason: Optional[str] = None
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+
+
+class _StepIO:
+    """Packed int32 step inputs: a pinned host buffer, its device twin and typed views of both."""
+
+    def __init__(self, cap_tokens: int, cap_seqs: int, max_blocks: int, device: torch.device):
+        self.cap_tokens, self.cap_seqs, self.max_blocks = cap_tokens, cap_seqs, max_blocks
+        sizes = [("tokens", cap_tokens), ("positions", cap_tokens), ("slot_mapping", cap_tokens),
+                 ("q_start", cap_seqs + 1), ("seq_lens", cap_seqs), ("out_rows", cap_seqs),
+                 ("block_tables", cap_seqs * max_blocks), ("seq_slots", cap_seqs), ("out_slots", cap_seqs)]
+        off = 0
+        self.off: Dict[str, Tuple[int, int]] = {}
+        for name, n in sizes:
+            self.off[name] = (off, n)
+            off = (off + n + 3) // 4 * 4           # keep every section 16-byte aligned
+        self.total = off
+        # seq_slots / out_slots are host-only: the device copy stops before them
+        self.dev_len = self.off["seq_slots"][0]
+        pin = device.type == "cuda"
+        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
+        self.dev = torch.zeros(self.dev_len, dtype=torch.int32, device=device)
+        self.np = self.host.numpy()
+        self.h = {k: self.np[o:o + n] for k, (o, n) in self.off.items()}
+        self.d = {k: self.dev[o:o + n] for k, (o, n) in self.off.items() if o < self.dev_len}
+        self.arrays = StepArrays()
+        for k in ("tokens", "positions", "slot_mapping", "q_start", "seq_lens", "seq_slots", "block_tables", "out_rows",
+                  "out_slots"):
+            setattr(self.arrays, k, self.h[k].ctypes.data_as(i32p))
+        self.arrays.cap_tokens, self.arrays.cap_seqs, self.arrays.max_blocks_per_seq = cap_tokens, cap_seqs, max_blocks
+
+    def upload(self):
+        self.dev.copy_(self.host[: self.dev_len], non_blocking=True)
+
+    @property
+    def h2d_bytes(self) -> int:
+        return self.dev_len * 4
+
+
+class LLMEngine:
+    def __init__(self, model: DeepSeek2Model, cfg: EngineConfig = EngineConfig()):
+        self.model = model
+        self.cfg = cfg
+        self.hp: DeepSeek2HParams = model.hp
+        self.device = model.device
+        bs = cfg.block_size
+        self.n_ctx_slot = cfg.n_ctx_slot or max(bs, cfg.n_ctx // cfg.n_parallel)
+        self.max_blocks = (self.n_ctx_slot + bs - 1) // bs
+        self.n_blocks = max((cfg.n_ctx + bs - 1) // bs, self.max_blocks)
+        if self.n_ctx_slot > model.max_positions:
+            raise ValueError(f"n_ctx_slot {self.n_ctx_slot} exceeds the model's RoPE table ({model.max_positions})")
+        self.kv = PagedKV(self.n_blocks, bs, cfg.n_parallel)
+        self.sched = Scheduler(self.kv, cfg.n_parallel, cfg.n_batch, self.n_ctx_slot, self.hp.eos_id, cfg.n_keep,
+                               cfg.cont_batching)
+        self.kv_cache = torch.zeros(self.hp.n_layer, self.n_blocks * bs, self.hp.kv_row, dtype=model.dtype,
+                                    device=self.device)
+        cap_tokens = max(cfg.n_batch, max(cfg.graph_buckets))
+        cap_seqs = max(cfg.n_parallel, max(cfg.graph_buckets))
+        self.io = _StepIO(cap_tokens, cap_seqs, self.max_blocks, self.device)
+        self.requests: Dict[int, RequestState] = {}
+        self._next_id = 1
+        self._graphs: Dict[Tuple[int, str], Tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self._use_graphs = cfg.cuda_graphs and self.device.type == "cuda"
+        self._out_host = torch.zeros(cap_seqs * (1 + 2 * max(1, cfg.presample_count)), dtype=torch.int32,
+                                     pin_memory=self.device.type == "cuda")
+        self.stats = {"steps": 0, "graph_steps": 0, "eager_steps": 0, "tokens_in": 0, "tokens_out": 0,
+                      "h2d_bytes": 0, "d2h_bytes": 0, "defrag_moves": 0}
+        self.kernel_launches_last_step = 0
+
+    # ------------------------------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        rid = self._next_id
+        self._next_id += 1
+        st = RequestState(rid, params, None if params.greedy else HostSampler(params), len(prompt), t_submit=time.time())
+        if st.sampler is not None:
+            for t in prompt[-params.repeat_last_n:]:
+                st.sampler.accept(t)
+        self.requests[rid] = st
+        self.sched.add(rid, prompt, params.max_tokens, params.ignore_eos)
+        return rid
+
+    def cancel(self, req_id: int) -> bool:
+        ok = self.sched.cancel(req_id)
+        self._drain_events()
+        return ok
+
+    def has_work(self) -> bool:
+        return not self.sched.idle()
+
+    # ------------------------------------------------------------------------------------------
+    def _batch_views(self, n_tokens: int, n_seqs: int, n_out: int, max_q_len: int) -> ForwardBatch:
+        d = self.io.d
+        return ForwardBatch(tokens=d["tokens"][:n_tokens], positions=d["positions"][:n_tokens],
+                            slot_mapping=d["slot_mapping"][:n_tokens],
+                            block_tables=d["block_tables"].view(self.io.cap_seqs, self.max_blocks)[:n_seqs],
+                            seq_lens=d["seq_lens"][:n_seqs], q_start=d["q_start"][:n_seqs + 1],
+                            out_rows=d["out_rows"][:n_out], max_q_len=max_q_len)
+
+    def _sample_device(self, logits: torch.Tensor, mode: str) -> torch.Tensor:
+        """Returns an int32 tensor: [n] token ids (greedy) or [n, 2k] (k float bit patterns + k ids)."""
+        if mode == "greedy":
+            return ops.argmax(logits)
+        k = min(self.cfg.presample_count, logits.shape[-1])
+        v, i = ops.topk_logits(logits, k)
+        return torch.cat([v.contiguous().view(torch.int32), i], dim=-1)
+
+    def _forward_sample(self, batch: ForwardBatch, mode: str) -> torch.Tensor:
+        logits = self.model.forward(batch, self.kv_cache)
+        return self._sample_device(logits, mode)
+
+    def _graph_for(self, bucket: int, mode: str):
+        key = (bucket, mode)
+        if key in self._graphs:
+            return self._graphs[key]
+        batch = self._batch_views(bucket, bucket, bucket, 1)
+        # warm-up on a side stream (allocations, lazy init), then capture
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._forward_sample(batch, mode)
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = self._forward_sample(batch, mode)
+        self._graphs[key] = (g, out)
+        return self._graphs[key]
+
+    def warmup(self, modes: Iterable[str] = ("greedy",)):
+        """Capture the decode graphs up front (the reference compiles its GE graph at context creation)."""
+        if not self._use_graphs:
+            return
+        h = self.io.h
+        h["slot_mapping"][:] = -1
+        h["seq_lens"][:] = 0
+        h["q_start"][:] = np.arange(len(h["q_start"]))
+        h["out_rows"][:] = np.arange(len(h["out_rows"]))
+        self.io.upload()
+        for b in self.cfg.graph_buckets:
+            if b <= self.io.cap_seqs:
+                for m in modes:
+                    self._graph_for(b, m)
+
+    # ------------------------------------------------------------------------------------------
+    def _maybe_defrag(self):
+        if self.cfg.defrag_thold < 0 or self.kv.fragmentation() <= self.cfg.defrag_thold:
+            return
+        self.defrag(self.cfg.defrag_max_moves)
+
+    def defrag(self, max_moves: int) -> int:
+        src, dst = self.kv.defrag(max_moves)
+        if len(src):
+            self._copy_blocks(src, dst)
+            self.stats["defrag_moves"] += len(src)
+        return len(src)
+
+    def _copy_blocks(self, src: np.ndarray, dst: np.ndarray):
+        s = torch.from_numpy(np.ascontiguousarray(src)).to(self.device)
+        d = torch.from_numpy(np.ascontiguousarray(dst)).to(self.device)
+        ops.kv_block_copy(self.kv_cache, s, d, self.cfg.block_size)
+
+    def _drain_events(self) -> List[Tuple[int, int, Optional[str]]]:
+        out = []
+        for rid, slot, tok, fin, n_prompt, n_dec in self.sched.take_events():
+            st = self.requests.get(rid)
+            if st is None:
+                continue
+            if tok >= 0:
+                st.output.append(tok)
+                if len(st.output) == 1:
+                    st.t_first = time.time()
+            if fin is not None:
+                st.finish_reason = fin
+                st.t_done = time.time()
+            out.append((rid, tok, fin))
+        return out
+
+    @torch.no_grad()
+    def step(self) -> List[Tuple[int, int, Optional[str]]]:
+        """Runs one engine step. Returns [(req_id, new_token, finish_reason_or_None)]."""
+        io = self.io
+        info = self.sched.step(io.arrays)
+        n_tokens, n_seqs, n_out, n_dec, max_q, _, n_copies = (int(x) for x in info[:7])
+        if n_tokens == 0:
+            return self._drain_events()
+        if n_copies:
+            src, dst = self.kv.take_copies()
+            self._copy_blocks(src, dst)
+        states = [self.requests[int(r)] for r in self.sched.out_reqs(n_out)] if n_out else []
+        mode = "greedy" if all(s.sampler is None for s in states) else "topk"
+        use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets)
+        if use_graph:
+            bucket = next(b for b in self.cfg.graph_buckets if b >= n_seqs)
+            h = io.h
+            if bucket > n_seqs:
+                h["tokens"][n_seqs:bucket] = 0
+                h["positions"][n_seqs:bucket] = 0
+                h["slot_mapping"][n_seqs:bucket] = -1
+                h["seq_lens"][n_seqs:bucket] = 0
+                h["q_start"][n_seqs:bucket + 1] = np.arange(n_seqs, bucket + 1)
+                h["out_rows"][n_out:bucket] = np.arange(n_out, bucket)
+                h["block_tables"][n_seqs * self.max_blocks: bucket * self.max_blocks] = 0
+            g, out = self._graph_for(bucket, mode)
+            io.upload()
+            g.replay()
+            self.stats["graph_steps"] += 1
+        else:
+            io.upload()
+            batch = self._batch_views(n_tokens, n_seqs, n_out, max_q)
+            out = self._forward_sample(batch, mode) if n_out else None
+            if n_out == 0:
+                self.model.forward(batch, self.kv_cache)
+            self.stats["eager_steps"] += 1
+        self.stats["steps"] += 1
+        self.stats["tokens_in"] += n_tokens
+        self.stats["h2d_bytes"] += io.h2d_bytes
+        if n_out:
+            flat = out.reshape(-1)
+            n_el = flat.numel()
+            host = self._out_host[:n_el]
+            host.copy_(flat, non_blocking=True)
+            if self.device.type == "cuda":
+                torch.cuda.current_stream(self.device).synchronize()
+            self.stats["d2h_bytes"] += n_el * 4
+            res = host.numpy().reshape(out.shape[0], -1)
+            sampled = np.empty(n_out, dtype=np.int32)
+            if mode == "greedy":
+                sampled[:] = res[:n_out, 0]
+            else:
+                k = res.shape[1] // 2
+                for i, st in enumerate(states):
+                    vals = res[i, :k].view(np.float32)
+                    ids = res[i, k:]
+                    if st.sampler is None:
+                        sampled[i] = ids[int(np.argmax(vals))]
+                    else:
+                        sampled[i] = st.sampler.sample(vals, ids)
+            for i, st in enumerate(states):
+                if st.sampler is not None:
+                    st.sampler.accept(int(sampled[i]))
+            self.sched.commit(sampled, n_out)
+            self.stats["tokens_out"] += n_out
+        else:
+            self.sched.commit(np.empty(0, dtype=np.int32), 0)
+        ev = self._drain_events()
+        self._maybe_defrag()
+        return ev
+
+    # ------------------------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None,
+                 max_new_tokens: Optional[int] = None) -> List[List[int]]:
+        """Blocking helper: run the given prompts to completion, return the generated ids per prompt."""
+        ids = []
+        for p in prompts:
+            sp = params or SamplingParams()
+            if max_new_tokens is not None:
+                sp = SamplingParams(**{**sp.__dict__, "max_tokens": max_new_tokens})
+            ids.append(self.add_request(p, sp))
+        while self.has_work():
+            self.step()
+        outs = [self.requests[i].output for i in ids]
+        for i in ids:
+            self.requests.pop(i, None)
+        return outs

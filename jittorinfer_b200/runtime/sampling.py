@@ -1,0 +1,110 @@
+"""Request-level sampling parameters and the host sampler chain over device top-k candidates.
+
+The reference runs its sampler chain on the host (src/llama-sampling.cpp) over either the full
+logits or, with ``presample_count = k``, over the k candidates a device top-k returned
+(src/llama-execute-decode.cpp:132-154; common/sampling_local.cpp:109-125).  Here greedy requests are
+sampled entirely on the device (argmax kernel inside the CUDA graph); everything else goes through
+the device top-k and then this chain, whose order and defaults follow common/sampling_local.cpp:
+153-209 and common/common_local.h:94-140: penalties -> top_k -> typical -> top_p -> min_p -> xtc ->
+temperature -> logit_bias -> dist.  The native chain in ``libjib200_runtime.so`` implements the same
+stages for the C API; this module is the engine-side implementation.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0          # <= 0: greedy (src/llama-sampling.cpp:246-263)
+    top_k: int = 40
+    top_p: float = 0.95
+    min_p: float = 0.05
+    typical_p: float = 1.0
+    xtc_probability: float = 0.0
+    xtc_threshold: float = 0.1
+    repeat_penalty: float = 1.0
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    repeat_last_n: int = 64
+    logit_bias: Dict[int, float] = field(default_factory=dict)
+    seed: Optional[int] = None
+    max_tokens: int = -1
+    ignore_eos: bool = False
+    stop: List[str] = field(default_factory=list)
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0 and self.repeat_penalty == 1.0 and self.frequency_penalty == 0.0 \
+            and self.presence_penalty == 0.0 and not self.logit_bias
+
+
+class HostSampler:
+    """Per-request sampler state (RNG + token history for the penalties)."""
+
+    def __init__(self, params: SamplingParams):
+        self.p = params
+        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else None))
+        self.history: List[int] = []
+
+    def accept(self, token: int):
+        self.history.append(int(token))
+        if self.p.repeat_last_n > 0 and len(self.history) > self.p.repeat_last_n:
+            del self.history[: len(self.history) - self.p.repeat_last_n]
+
+    def sample(self, values: np.ndarray, ids: np.ndarray) -> int:
+        """values/ids: candidate logits (any order) and their token ids."""
+        p = self.p
+        logit = values.astype(np.float64).copy()
+        ids = ids.astype(np.int64)
+        # penalties (src/llama-sampling.cpp:1284-1316)
+        if self.history and (p.repeat_penalty != 1.0 or p.frequency_penalty or p.presence_penalty):
+            counts: Dict[int, int] = {}
+            for t in self.history:
+                counts[t] = counts.get(t, 0) + 1
+            for i, t in enumerate(ids):
+                c = counts.get(int(t))
+                if c:
+                    logit[i] = logit[i] / p.repeat_penalty if logit[i] > 0 else logit[i] * p.repeat_penalty
+                    logit[i] -= c * p.frequency_penalty + p.presence_penalty
+        for t, b in p.logit_bias.items():
+            hit = np.nonzero(ids == t)[0]
+            if hit.size:
+                logit[hit] += b
+        if p.temperature <= 0.0:
+            return int(ids[int(np.argmax(logit))])
+        order = np.argsort(-logit, kind="stable")
+        logit, ids = logit[order], ids[order]
+        if p.top_k > 0:
+            logit, ids = logit[: p.top_k], ids[: p.top_k]
+
+        def softmax(x):
+            e = np.exp(x - x.max())
+            return e / e.sum()
+
+        if p.typical_p < 1.0:
+            pr = softmax(logit)
+            ent = -(pr * np.log(pr + 1e-30)).sum()
+            dev = np.abs(-np.log(pr + 1e-30) - ent)
+            o = np.argsort(dev, kind="stable")
+            keep = int(np.searchsorted(np.cumsum(pr[o]), p.typical_p) + 1)
+            sel = np.sort(o[: max(1, keep)])
+            logit, ids = logit[sel], ids[sel]
+        if p.top_p < 1.0:
+            pr = softmax(logit)
+            keep = int(np.searchsorted(np.cumsum(pr), p.top_p) + 1)     # smallest prefix with cum >= top_p
+            logit, ids = logit[: max(1, keep)], ids[: max(1, keep)]
+        if p.min_p > 0.0:
+            keep = logit >= logit.max() + math.log(p.min_p)
+            logit, ids = logit[keep], ids[keep]
+        if p.xtc_probability > 0.0 and self.rng.random() < p.xtc_probability:
+            pr = softmax(logit)
+            above = np.nonzero(pr >= p.xtc_threshold)[0]
+            if above.size >= 2:
+                logit, ids = logit[above[-1]:], ids[above[-1]:]
+        pr = softmax(logit / p.temperature)
+        return int(ids[int(self.rng.choice(len(ids), p=pr))])
