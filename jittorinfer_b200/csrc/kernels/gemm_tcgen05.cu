@@ -1,0 +1,428 @@
+// bf16 GEMM family on tcgen05 tensor cores: Y[t, n] = sum_k X[t, k] * W[n, k]  (+ epilogue)
+//
+// One kernel template covers every dense projection of the model, the per-head absorbed-MLA
+// products and the routed-expert grouped GEMMs (reference ops: aclnnMm/BatchMatMul
+// ggml/src/ggml-cann/aclnn_ops.cpp:4647-4693, aclnnGroupedMatmulV4 x3 + Silu + Mul 2258-2421).
+//
+// Design (swap-AB, weight-stationary M):
+//  * the 128-row MMA "M" dimension is a tile of OUTPUT FEATURES (rows of W, K-major as stored), the
+//    MMA "N" dimension is a tile of BN tokens (16..256).  Decode batches of 1..64 tokens therefore use
+//    full 128-lane tensor-core instructions and stream each weight byte exactly once;
+//  * operands are staged by TMA (128-byte swizzle, no multicast) into a ring of STAGES shared-memory
+//    slots guarded by full/empty mbarriers; one elected thread issues tcgen05.mma into a TMEM
+//    accumulator; four epilogue warps read it back with tcgen05.ld;
+//  * split-K: when N/128 tiles cannot fill 148 SMs, the K range is split over several CTAs that write
+//    fp32 partials to a scratch buffer; the last CTA to arrive (per-tile counter) reduces them and runs
+//    the epilogue, then resets the counter so the buffers need no clearing between launches;
+//  * DUAL mode keeps two accumulators (gate and up projections of the same tile) and stores
+//    silu(gate) * up — the gated-FFN epilogue — so the 2x wider intermediate never reaches HBM;
+//  * grouped mode: blockIdx.z selects an expert; the token rows of that expert are a segment
+//    [seg[e], seg[e+1]) of an expert-sorted activation matrix; segment bounds are read on the device
+//    (no host sync, unlike aclnn_ops.cpp:2136-2146).
+//  * every mbarrier wait is bounded; on expiry a status word is set and the CTA leaves normally.
+#include "sm100.cuh"
+
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+#include <string.h>
+
+#include "jib_kernels.h"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;      // output features per CTA (MMA M)
+constexpr int BK = 64;       // K elements per stage (128 bytes of bf16 = one swizzle row)
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;   // warp0 TMA, warp1 MMA + TMEM owner, warps 2..5 epilogue
+
+struct GemmArgs {
+    void * out;
+    const void * residual;
+    const int * seg;          // grouped: expert segment offsets [batch+1] into the sorted rows, else null
+    float * scratch;
+    int * counters;
+    int * status;
+    long long ldo, out_batch_stride, ldr, res_batch_stride;
+    int T, N, K;
+    int splits, kb_per_split;
+    int out_f32, res_f32;
+    long long rows_total;     // rows of out (all batches of a grouped launch share them); stores beyond are refused
+    long long scratch_elems;
+};
+
+template <int BN, bool DUAL>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
+    static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+            const __grid_constant__ CUtensorMap tmB, const GemmArgs args) {
+    using C = Cfg<BN, DUAL>;
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int n0 = blockIdx.x * BM;
+    const int splits = args.splits;
+    const int batch = blockIdx.z / splits;
+    const int split = blockIdx.z - batch * splits;
+    int row0 = blockIdx.y * BN;      // first token row of this tile, relative to the segment / matrix
+    int rows_valid = args.T;         // rows of this batch's matrix
+    int row_base = 0;                // grouped: offset of the expert's segment in the sorted rows
+    if (args.seg != nullptr) {
+        row_base = args.seg[batch];
+        rows_valid = args.seg[batch + 1] - row_base;
+    }
+    if (row0 >= rows_valid) return;  // whole CTA: nothing to do (empty expert / tail tile)
+
+    const int num_kb = (args.K + BK - 1) / BK;
+    const int kb0 = split * args.kb_per_split;
+    const int kb1 = min(num_kb, kb0 + args.kb_per_split);
+    const int nkb = kb1 - kb0;
+
+    // ---- shared memory carve-up ----
+    uint8_t * tiles = (uint8_t *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    uint64_t * bars = (uint64_t *) (tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t * full = bars;
+    uint64_t * empty = bars + C::STAGES;
+    uint64_t * acc_ready = bars + 2 * C::STAGES;
+    uint32_t * tmem_slot = (uint32_t *) (bars + 2 * C::STAGES + 1);
+    int * flag = (int *) (tmem_slot + 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        if (DUAL) prefetch_tmap(&tmA2);
+        *flag = 0;
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (elect_one()) {
+            const int a_z = batch;
+            const int b_z = args.seg != nullptr ? 0 : batch;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 1, i); break; }
+                uint8_t * st = tiles + s * C::STAGE_BYTES;
+                mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                const int k = (kb0 + i) * BK;
+                tma_load_3d(st, &tmA, &full[s], k, n0, a_z);
+                if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[s], k, n0, a_z);
+                tma_load_3d(st + (DUAL ? 2 : 1) * C::A_BYTES, &tmB, &full[s], k, row_base + row0, b_z);
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                if (!mbar_wait(&full[s], ph)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 2, i); ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + s * C::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * C::A_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    const uint64_t bd = desc_k_sw128(b_addr + kk * UMMA_K * 2);
+                    mma_bf16(tmem, desc_k_sw128(a_addr + kk * UMMA_K * 2), bd, idesc, (i | kk) != 0);
+                    if (DUAL)
+                        mma_bf16(tmem + BN, desc_k_sw128(a_addr + C::A_BYTES + kk * UMMA_K * 2), bd, idesc, (i | kk) != 0);
+                }
+                mma_commit(&empty[s]);     // frees the slot once these MMAs have read it
+            }
+            mma_commit(acc_ready);         // accumulators complete (also arrives after a failed wait)
+        }
+    } else {
+        // ================= epilogue (warps 2..5) =================
+        const int q = warp & 3;                   // TMEM lane quarter this warp may access
+        const int r = q * 32 + lane;              // feature row inside the tile
+        const int n = n0 + r;
+        const bool acc_ok = mbar_wait(acc_ready, 0);
+        if (!acc_ok) jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 3, 0);
+        tc_fence_after();
+        const uint32_t tbase = tmem + ((uint32_t) (q * 32) << 16);
+        const int tile_id = (batch * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        constexpr int ACC = DUAL ? 2 : 1;
+        float * part = nullptr;
+        bool do_final = true;
+
+        if (splits > 1) {
+            // 1) publish this split's fp32 partial: layout [acc][BN tokens][128 features]
+            part = args.scratch + ((size_t) tile_id * splits) * (ACC * BN * BM);
+            float * mine = part + (size_t) split * (ACC * BN * BM);
+            const bool in_scratch = ((long long) tile_id * splits + splits) * (ACC * BN * BM) <= args.scratch_elems;
+            if (!in_scratch) jib_report(args.status, JIB_ERR_BOUNDS, 4, tile_id);
+            if (acc_ok && in_scratch) {
+#pragma unroll 1
+                for (int a = 0; a < ACC; ++a)
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(tbase + a * BN + c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) mine[(size_t) (a * BN + c + j) * BM + r] = __uint_as_float(v[j]);
+                    }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                const int old = atomicAdd(&args.counters[tile_id], 1);
+                const int last = old == splits - 1;
+                if (last) args.counters[tile_id] = 0;      // ready for the next launch
+                *flag = last;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            do_final = *flag != 0;
+            if (do_final) __threadfence();
+        }
+
+        if (do_final && acc_ok && splits > 1 && ((long long) tile_id * splits + splits) * (ACC * BN * BM) > args.scratch_elems)
+            do_final = false;
+        if (do_final && acc_ok) {
+            const long long obase = (long long) batch * args.out_batch_stride;
+            const long long rbase = (long long) batch * args.res_batch_stride;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (row0 + c >= rows_valid) break;
+                float g[16], u[16];
+                if (splits > 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
+                    for (int s = 0; s < splits; ++s) {
+                        const float * p = part + (size_t) s * (ACC * BN * BM);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            g[j] += __ldcg(p + (size_t) (c + j) * BM + r);
+                            if (DUAL) u[j] += __ldcg(p + (size_t) (BN + c + j) * BM + r);
+                        }
+                    }
+                } else {
+                    uint32_t v[16];
+                    tmem_ld16(tbase + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) g[j] = __uint_as_float(v[j]);
+                    if (DUAL) {
+                        tmem_ld16(tbase + BN + c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) u[j] = __uint_as_float(v[j]);
+                    }
+                }
+                if (n < args.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = row0 + c + j;
+                        if (t >= rows_valid) break;
+                        float y = DUAL ? silu(g[j]) * u[j] : g[j];
+                        const long long row = row_base + t;
+                        if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 5, (int) row); break; }
+                        if (args.residual != nullptr) {
+                            const long long ri = rbase + row * args.ldr + n;
+                            y += args.res_f32 ? ((const float *) args.residual)[ri]
+                                              : __bfloat162float(((const __nv_bfloat16 *) args.residual)[ri]);
+                        }
+                        const long long oi = obase + row * args.ldo + n;
+                        if (args.out_f32) ((float *) args.out)[oi] = y;
+                        else ((__nv_bfloat16 *) args.out)[oi] = __float2bfloat16(y);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void * p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn) p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void * ptr;
+    long long rows, cols, batch, row_stride, batch_stride;
+    int box_rows;
+    bool operator==(const MapKey & o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey & k) const {
+        const uint64_t * p = (const uint64_t *) &k;
+        size_t h = 1469598103934665603ull;
+        for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) h = (h ^ p[i]) * 1099511628211ull;
+        return h;
+    }
+};
+
+// bf16 matrix [batch][rows][cols] with element strides; box = {64 cols, box_rows, 1}; 128B swizzle.
+int make_map(CUtensorMap * out, const void * ptr, long long rows, long long cols, long long batch, long long row_stride,
+             long long batch_stride, int box_rows) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key;
+    memset(&key, 0, sizeof(key));
+    key.ptr = ptr; key.rows = rows; key.cols = cols; key.batch = batch; key.row_stride = row_stride;
+    key.batch_stride = batch_stride; key.box_rows = box_rows;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return 0; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return JIB_E_DRIVER;
+    if (((uintptr_t) ptr & 15) || (row_stride * 2) % 16 || (batch > 1 && (batch_stride * 2) % 16)) return JIB_E_ALIGN;
+    cuuint64_t dims[3] = {(cuuint64_t) cols, (cuuint64_t) rows, (cuuint64_t) (batch > 0 ? batch : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t) row_stride * 2, (cuuint64_t) (batch > 1 ? batch_stride : rows * row_stride) * 2};
+    cuuint32_t box[3] = {(cuuint32_t) BK, (cuuint32_t) box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return JIB_E_TENSORMAP;
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 65536) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int BN, bool DUAL>
+int launch(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b, const GemmArgs & args, dim3 grid,
+           cudaStream_t stream) {
+    using C = Cfg<BN, DUAL>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return JIB_E_LAUNCH;
+        attr_done = true;
+    }
+    gemm_kernel<BN, DUAL><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(a, a2, b, args);
+    return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
+}
+
+}  // namespace
+
+extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_) {
+    cudaStream_t stream = (cudaStream_t) stream_;
+    if (d->T <= 0 || d->N <= 0 || d->K <= 0) return 0;
+    const bool dual = d->w2 != nullptr;
+    const bool grouped = d->seg != nullptr;
+    const int batch = d->batch > 0 ? d->batch : 1;
+    const int rows_bound = grouped ? (d->max_rows > 0 ? d->max_rows : d->T) : d->T;
+    int bn = d->bn;
+    if (bn == 0) {
+        bn = 16;
+        while (bn < rows_bound && bn < 256) bn *= 2;
+        if (dual && bn > 128) bn = 128;     // keeps three pipeline stages in shared memory
+    }
+    const int n_tiles = (d->N + BM - 1) / BM;
+    const int t_tiles = (rows_bound + bn - 1) / bn;
+    const int num_kb = (d->K + BK - 1) / BK;
+    // split-K: fill the machine when there are too few output tiles
+    int splits = d->splits;
+    const long long base_ctas = (long long) n_tiles * t_tiles * (grouped ? (d->active_hint > 0 ? d->active_hint : batch) : batch);
+    if (splits <= 0) {
+        splits = 1;
+        const int sms = d->sm_count > 0 ? d->sm_count : 148;
+        if (base_ctas < sms && d->scratch != nullptr) {
+            splits = (int) ((sms + base_ctas - 1) / base_ctas);
+            if (splits > num_kb / 4) splits = num_kb / 4;      // at least 4 k-blocks (256 K) per split
+            if (splits < 1) splits = 1;
+        }
+    }
+    if (splits > num_kb) splits = num_kb;
+    int kbps = (num_kb + splits - 1) / splits;
+    splits = (num_kb + kbps - 1) / kbps;                        // no empty split
+    const long long tiles_total = (long long) n_tiles * t_tiles * batch;
+    if (splits > 1) {
+        const size_t need = (size_t) tiles_total * splits * (dual ? 2 : 1) * bn * BM * sizeof(float);
+        if (d->scratch == nullptr || need > d->scratch_bytes || tiles_total > d->n_counters) {
+            if (d->splits > 0) return JIB_E_SCRATCH;            // explicit request that cannot be met
+            splits = 1;
+            kbps = num_kb;
+        }
+    }
+
+    CUtensorMap ma, ma2, mb;
+    int rc = make_map(&ma, d->w, d->N, d->K, batch, d->w_row_stride, d->w_batch_stride, BM);
+    if (rc) return rc;
+    if (dual) {
+        rc = make_map(&ma2, d->w2, d->N, d->K, batch, d->w_row_stride, d->w_batch_stride, BM);
+        if (rc) return rc;
+    } else {
+        ma2 = ma;
+    }
+    const long long x_rows = grouped ? d->x_rows_total : d->T;
+    rc = make_map(&mb, d->x, x_rows, d->K, grouped ? 1 : batch, d->x_row_stride, d->x_batch_stride, bn);
+    if (rc) return rc;
+
+    GemmArgs a;
+    a.out = d->out; a.residual = d->residual; a.seg = d->seg; a.scratch = (float *) d->scratch; a.counters = d->counters;
+    a.status = d->status; a.ldo = d->ldo; a.out_batch_stride = d->out_batch_stride; a.ldr = d->ldr;
+    a.res_batch_stride = d->res_batch_stride; a.T = d->T; a.N = d->N; a.K = d->K; a.splits = splits; a.kb_per_split = kbps;
+    a.out_f32 = d->out_f32; a.res_f32 = d->res_f32;
+    a.rows_total = grouped ? d->x_rows_total : d->T;
+    a.scratch_elems = (long long) (d->scratch_bytes / sizeof(float));
+    dim3 grid(n_tiles, t_tiles, batch * splits);
+#define JIB_LAUNCH(BN_)                                                                           \
+    case BN_:                                                                                     \
+        return dual ? launch<BN_, true>(ma, ma2, mb, a, grid, stream) : launch<BN_, false>(ma, ma2, mb, a, grid, stream);
+    switch (bn) {
+        JIB_LAUNCH(16)
+        JIB_LAUNCH(32)
+        JIB_LAUNCH(64)
+        JIB_LAUNCH(128)
+        case 256:
+            if (dual) return JIB_E_ARG;
+            return launch<256, false>(ma, ma2, mb, a, grid, stream);
+        default:
+            return JIB_E_ARG;
+    }
+#undef JIB_LAUNCH
+}

@@ -1,0 +1,83 @@
+// C ABI of libjib200_kernels.so: every launcher takes raw device pointers and a CUDA stream, returns
+// 0 on success or a negative JIB_E_* code, and never allocates or synchronises.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#define JIB_EXPORT __attribute__((visibility("default")))
+
+enum {
+    JIB_E_ARG = -1,         // unsupported shape / argument
+    JIB_E_ALIGN = -2,       // pointer or stride not 16-byte aligned (TMA requirement)
+    JIB_E_DRIVER = -3,      // cuTensorMapEncodeTiled entry point unavailable
+    JIB_E_TENSORMAP = -4,   // tensor-map encode failed
+    JIB_E_LAUNCH = -5,      // kernel launch failed
+    JIB_E_SCRATCH = -6,     // scratch / counter buffer too small for the requested split
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Y[b][t][n] = sum_k X[b][t][k] * W[b][n][k]  (bf16 in, fp32 accumulate), optional second weight
+// (w2: out = silu(X W^T) * (X W2^T)), optional residual add, optional expert-grouped rows.
+typedef struct jib_gemm_desc {
+    const void * x;            // bf16 activations
+    const void * w;            // bf16 weights [batch][N][K]
+    const void * w2;           // NULL, or second weight of the gated pair (same layout as w)
+    void * out;
+    const void * residual;     // NULL or [rows][N] added in the epilogue
+    const int * seg;           // NULL, or device int[batch+1]: rows of expert b are [seg[b], seg[b+1]) of x / out
+    void * scratch;            // split-K partials (fp32), may be NULL (then no split)
+    int * counters;            // split-K tile counters, zero-initialised once; the kernel leaves them zero
+    int * status;              // 4 ints, see sm100.cuh; may be NULL
+    long long x_row_stride, x_batch_stride;   // elements
+    long long w_row_stride, w_batch_stride;
+    long long ldo, out_batch_stride, ldr, res_batch_stride;
+    long long x_rows_total;    // grouped: total rows of x (all experts)
+    size_t scratch_bytes;
+    int n_counters;
+    int T, N, K, batch;        // grouped: T = upper bound of rows of one expert
+    int max_rows;              // grouped: tighter bound of rows per expert if known (else 0)
+    int active_hint;           // grouped: expected number of non-empty experts (split-K heuristic), else 0
+    int out_f32, res_f32;
+    int splits;                // 0 = choose
+    int bn;                    // 0 = choose; token-tile width 16/32/64/128/256
+    int sm_count;
+} jib_gemm_desc;
+
+JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);
+
+// ---- memory-bound kernels (elementwise.cu) ----------------------------------------------------
+JIB_EXPORT int jib_embed_gather(const void * table, const int * ids, void * out, int T, int d, int n_vocab, void * stream);
+JIB_EXPORT int jib_rmsnorm(const void * x, const void * residual, const float * w, void * out_norm, void * out_sum, int T, int d,
+                           long long x_stride, float eps, void * stream);
+JIB_EXPORT int jib_mla_qkv_post(const void * q, long long q_stride, const void * ckv, long long ckv_stride, const float * kv_norm_w,
+                                float eps, const float * rope_table, const int * positions, const int * slot_mapping, void * cache,
+                                void * q_out, int T, int H, int dn, int dr, int r, int max_pos, long long n_slots, int * status,
+                                void * stream);
+JIB_EXPORT int jib_argmax(const float * logits, int * out, int n, int V, void * stream);
+JIB_EXPORT int jib_topk(const float * logits, float * vals, int * ids, int n, int V, int k, void * stream);
+JIB_EXPORT int jib_kv_block_copy(void * cache, long long layer_stride_elems, int n_layers, const int * src, const int * dst, int n,
+                                 int block_elems, void * stream);
+JIB_EXPORT int jib_gather_rows(const void * x, const int * src_row, void * out, int rows, int d, void * stream);
+
+// ---- MoE routing (moe.cu) ---------------------------------------------------------------------
+JIB_EXPORT int jib_moe_gate(const void * g, const float * w_router, const float * bias, int * ids, float * wts, int T, int d, int E,
+                            int k, int n_group, int topk_group, float scale, int norm, int sigmoid, void * stream);
+// Stable counting sort of the (token, k) pairs by local expert. dest[t*k+j] = sorted row or -1 (not local).
+JIB_EXPORT int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
+                               void * stream);
+JIB_EXPORT int jib_moe_combine(const void * y, const int * dest, const float * wts, const void * shared, const void * residual,
+                               void * out, int T, int k, int d, void * stream);
+
+// ---- attention (mla_attention.cu) -------------------------------------------------------------
+// Split-KV absorbed MLA over the paged latent cache. q [T][H][r+dr] bf16; o_lat [T][H][r] bf16.
+// part_o [T][n_splits][H][r] fp32 and part_ml [T][n_splits][H][2] fp32 are scratch.
+JIB_EXPORT int jib_mla_attention(const void * q, const void * cache, const int * block_tables, int max_blocks, const int * seq_lens,
+                                 const int * q_start, int n_seqs, int T, int H, int r, int dr, int block_size, float scale,
+                                 int n_splits, float * part_o, float * part_ml, void * o_lat, void * stream);
+
+#ifdef __cplusplus
+}
+#endif

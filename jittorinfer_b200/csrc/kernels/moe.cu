@@ -1,0 +1,255 @@
+// MoE routing kernels: fused router (fp32 matmul + softmax/sigmoid + [group-limited] top-k + renorm/scale),
+// expert-sorted permutation with device-side segment offsets, and the weighted top-k combine.
+//
+// Reference: router + softmax + full argsort + slice + gather + scale as separate graph ops
+// (src/llama-graph-ffn.cpp:145-197), aclnnMoeInitRouting + a device->host copy and host binary search for the
+// local expert range (ggml/src/ggml-cann/aclnn_ops.cpp:2129-2168), aclnnMoeFinalizeRoutingV2 (2540-2542).
+// Here nothing leaves the device and expert-parallel ranks simply mark foreign experts as "not local".
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "jib_kernels.h"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int MAX_E = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One block per token.  smem: g as fp32 [d], logits/probs [E].
+template <int NT>
+__global__ void __launch_bounds__(NT) moe_gate_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
+                                                      const float * __restrict__ bias, int * __restrict__ ids, float * __restrict__ wts,
+                                                      int d, int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid) {
+    extern __shared__ float sm[];
+    float * xs = sm;              // [d]
+    __shared__ float prob[MAX_E];
+    __shared__ float sel[MAX_E];
+    __shared__ float gscore[32];
+    const int t = blockIdx.x;
+    const bf16 * row = g + (size_t) t * d;
+    for (int i = threadIdx.x; i < d; i += NT) xs[i] = __bfloat162float(row[i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = warp; e < E; e += NT / 32) {
+        const float4 * wr = (const float4 *) (w_router + (size_t) e * d);
+        float acc = 0.f;
+        for (int i = lane; i < d / 4; i += 32) {
+            const float4 w = wr[i];
+            const float4 x = ((const float4 *) xs)[i];
+            acc += w.x * x.x + w.y * x.y + w.z * x.z + w.w * x.w;
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) prob[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // softmax / sigmoid over E (E <= 256 -> 8 per lane)
+        float mx = -FLT_MAX;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = sigmoid ? 1.f / (1.f + expf(-prob[e])) : expf(prob[e] - mx);
+            prob[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) {
+            if (!sigmoid) prob[e] = prob[e] / sum;
+            sel[e] = prob[e] + (bias ? bias[e] : 0.f);
+        }
+        __syncwarp();
+        if (n_group > 1) {
+            const int gs = E / n_group;
+            if (lane < n_group) {
+                float m = -FLT_MAX;
+                for (int j = 0; j < gs; ++j) m = fmaxf(m, sel[lane * gs + j]);
+                gscore[lane] = m;
+            }
+            __syncwarp();
+            // keep the topk_group best groups (ties -> lower group id): rank of my group
+            if (lane < n_group) {
+                int rank = 0;
+                const float mine = gscore[lane];
+                for (int j = 0; j < n_group; ++j) rank += (gscore[j] > mine) || (gscore[j] == mine && j < lane);
+                if (rank >= topk_group)
+                    for (int j = 0; j < gs; ++j) sel[lane * gs + j] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        // k rounds of warp arg-max (ties -> lower expert id)
+        float wsum = 0.f;
+        for (int round = 0; round < k; ++round) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = sel[e];
+                if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (bi >= E) bi = 0;
+            if (lane == 0) {
+                ids[(size_t) t * k + round] = bi;
+                wts[(size_t) t * k + round] = prob[bi];
+                sel[bi] = -INFINITY;
+                // a -inf that was already masked can only be re-picked when fewer than k experts are eligible
+            }
+            wsum += prob[bi];
+            __syncwarp();
+        }
+        if (lane < k) {
+            float w = wts[(size_t) t * k + lane];
+            if (norm) w /= wsum;
+            wts[(size_t) t * k + lane] = w * scale;
+        }
+    }
+}
+
+// Single-block stable counting sort of n = T*k (token,slot) pairs by local expert id.
+// seg[e] .. seg[e+1] delimit expert e's rows; src_token[row] = token feeding sorted row; dest[i] = row or -1.
+__global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
+                                                          int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest) {
+    __shared__ int count[MAX_E + 1];
+    __shared__ int offs[MAX_E + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < E_local; e += nw) {
+        int c = 0;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < n && ids[i] - expert_base == e;
+            c += __popc(__ballot_sync(0xffffffffu, hit));
+        }
+        if (lane == 0) count[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < E_local; ++e) { offs[e] = acc; acc += count[e]; }
+        offs[E_local] = acc;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E_local; e += blockDim.x) seg[e] = offs[e];
+    for (int i = offs[E_local] + threadIdx.x; i < n; i += blockDim.x) src_token[i] = -1;   // rows no local expert owns
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int le = ids[i] - expert_base;
+        if (le < 0 || le >= E_local) dest[i] = -1;
+    }
+    for (int e = warp; e < E_local; e += nw) {
+        int base = offs[e];
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < n && ids[i] - expert_base == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int row = base + __popc(m & ((1u << lane) - 1));
+                dest[i] = row;
+                if (row < n) src_token[row] = i / k;
+            }
+            base += __popc(m);
+        }
+    }
+}
+
+// out[t] = residual[t] + shared[t] + sum_j wts[t][j] * y[dest[t][j]]   (fp32 accumulate, bf16 out)
+__global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
+                                   const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
+                                   int d) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < d / 8; i += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int j = 0; j < k; ++j) {
+            const int row = dest[(size_t) t * k + j];
+            if (row < 0) continue;
+            const float w = wts[(size_t) t * k + j];
+            const uint4 raw = ((const uint4 *) (y + (size_t) row * d))[i];
+            const __nv_bfloat162 * p = (const __nv_bfloat162 *) &raw;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = __bfloat1622float2(p[q]);
+                acc[2 * q] += w * f.x;
+                acc[2 * q + 1] += w * f.y;
+            }
+        }
+        if (shared) {
+            const uint4 raw = ((const uint4 *) (shared + (size_t) t * d))[i];
+            const __nv_bfloat162 * p = (const __nv_bfloat162 *) &raw;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = __bfloat1622float2(p[q]);
+                acc[2 * q] += f.x;
+                acc[2 * q + 1] += f.y;
+            }
+        }
+        if (residual) {
+            const uint4 raw = ((const uint4 *) (residual + (size_t) t * d))[i];
+            const __nv_bfloat162 * p = (const __nv_bfloat162 *) &raw;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = __bfloat1622float2(p[q]);
+                acc[2 * q] += f.x;
+                acc[2 * q + 1] += f.y;
+            }
+        }
+        uint4 o;
+        __nv_bfloat162 * po = (__nv_bfloat162 *) &o;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) po[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+        ((uint4 *) (out + (size_t) t * d))[i] = o;
+    }
+}
+
+inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH; }
+
+}  // namespace
+
+extern "C" {
+
+int jib_moe_gate(const void * g, const float * w_router, const float * bias, int * ids, float * wts, int T, int d, int E, int k,
+                 int n_group, int topk_group, float scale, int norm, int sigmoid, void * stream) {
+    if (T <= 0) return 0;
+    if (E > MAX_E || k > 32 || k > E || d % 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
+    static bool attr = false;
+    const size_t smem = (size_t) d * sizeof(float);
+    if (!attr && smem > 48 * 1024) {
+        cudaFuncSetAttribute(moe_gate_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        attr = true;
+    }
+    moe_gate_kernel<256><<<T, 256, smem, (cudaStream_t) stream>>>((const bf16 *) g, w_router, bias, ids, wts, d, E, k, n_group, topk_group,
+                                                                   scale, norm, sigmoid);
+    return launched();
+}
+
+int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest, void * stream) {
+    if (T <= 0) return 0;
+    if (E_local > MAX_E) return JIB_E_ARG;
+    moe_permute_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(ids, T * k, k, expert_base, E_local, seg, src_token, dest);
+    return launched();
+}
+
+int jib_moe_combine(const void * y, const int * dest, const float * wts, const void * shared, const void * residual, void * out, int T,
+                    int k, int d, void * stream) {
+    if (T <= 0) return 0;
+    if (d % 8) return JIB_E_ARG;
+    moe_combine_kernel<<<T, 256, 0, (cudaStream_t) stream>>>((const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual,
+                                                              (bf16 *) out, k, d);
+    return launched();
+}
+
+}  // extern "C"

@@ -132,8 +132,8 @@ class DeepSeek2Model:
                     # load-time re-layout into the absorbed factors (reference: wkv_b_post_process,
                     # src/llama-model.cpp:408-459)
                     w = self._dev(t).view(H, dn + dv, r)
-                    L.w_uk = w[:, :dn, :].contiguous()          # [H, dn, r]
-                    L.w_uv = w[:, dn:, :].contiguous()          # [H, dv, r]
+                    L.w_uk = w[:, :dn, :].transpose(1, 2).contiguous()   # [H, r, dn]: q_abs = q_nope @ w_uk[h]^T
+                    L.w_uv = w[:, dn:, :].contiguous()                   # [H, dv, r]: o = o_lat @ w_uv[h]^T
                 elif base == "attn_output":
                     L.w_o = self._dev(t)
                 elif base == "ffn_gate":
@@ -206,7 +206,7 @@ class DeepSeek2Model:
         if hp.is_lite:
             q = qkv[:, :nq]
         else:
-            qa, _ = ops.rmsnorm(qkv[:, :nq].contiguous(), L.q_a_norm, hp.rms_eps)
+            qa, _ = ops.rmsnorm(qkv[:, :nq], L.q_a_norm, hp.rms_eps)
             q = ops.linear(qa, L.w_q_b)
         q_full = torch.empty(T, H, r + dr, dtype=h.dtype, device=h.device)
         q_nope = ops.mla_qkv_post(q, ckv, L.kv_a_norm, hp.rms_eps, self.rope_table, batch.positions,
@@ -223,18 +223,13 @@ class DeepSeek2Model:
             return self._row_parallel(hmid, L.w_down, residual)
         ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
                                 hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid")
-        if self.spec.sharded and not self.spec.expert_parallel:
-            moe = ops.moe_experts(g, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, 0)
-        else:
-            moe = ops.moe_experts(g, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, self.expert_base)
-        if L.w_gate_sh is not None:
-            hs = ops.gateup_silu(g, L.w_gate_sh, L.w_up_sh)
-            part = ops.linear(hs, L.w_down_sh, residual=moe, out_dtype=torch.float32)
-        else:
-            part = moe
+        base = self.expert_base if self.spec.expert_parallel else 0
         if self.comm is not None and self.spec.sharded:
-            part = self.comm.all_reduce(part)
-        return (part + residual.float()).to(g.dtype)
+            part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
+                               L.w_down_sh, base)
+            return self.comm.all_reduce(part) + residual
+        return ops.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
+                           L.w_down_sh, base)
 
     @torch.no_grad()
     def forward(self, batch: ForwardBatch, kv_cache: torch.Tensor) -> torch.Tensor:

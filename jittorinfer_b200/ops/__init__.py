@@ -18,7 +18,7 @@ _FORCE_TORCH = os.environ.get("JITTORINFER_OPS", "").lower() == "torch"
 _native = None
 
 
-def native():
+def nat():
     """The ctypes binding module; raises if the CUDA library is not built."""
     global _native
     if _native is None:
@@ -42,63 +42,69 @@ def force_torch() -> bool:
 
 
 def embed_gather(table, ids):
-    return native().embed_gather(table, ids) if use_native(table) else ref.embed_gather(table, ids)
+    return nat().embed_gather(table, ids) if use_native(table) else ref.embed_gather(table, ids)
 
 
 def rmsnorm(x, w, eps, residual=None):
-    return native().rmsnorm(x, w, eps, residual) if use_native(x) else ref.rmsnorm(x, w, eps, residual)
+    return nat().rmsnorm(x, w, eps, residual) if use_native(x) else ref.rmsnorm(x, w, eps, residual)
 
 
 def linear(x, w, residual=None, out_dtype=None):
     if use_native(x) and x.dtype == torch.bfloat16:
-        return native().linear(x, w, residual, out_dtype)
+        return nat().linear(x, w, residual, out_dtype)
     return ref.linear(x, w, residual, out_dtype)
 
 
 def gateup_silu(x, wg, wu):
     if use_native(x) and x.dtype == torch.bfloat16:
-        return native().gateup_silu(x, wg, wu)
+        return nat().gateup_silu(x, wg, wu)
     return ref.gateup_silu(x, wg, wu)
 
 
 def mla_qkv_post(q, ckv, kv_norm_w, eps, rope_table, positions, slot_mapping, cache, q_out, n_head, dn, dr, r):
-    f = native().mla_qkv_post if use_native(q) else ref.mla_qkv_post
+    f = nat().mla_qkv_post if use_native(q) else ref.mla_qkv_post
     return f(q, ckv, kv_norm_w, eps, rope_table, positions, slot_mapping, cache, q_out, n_head, dn, dr, r)
 
 
 def q_absorb(q_nope, w_uk, q_out, r):
-    return (native().q_absorb if use_native(q_nope) else ref.q_absorb)(q_nope, w_uk, q_out, r)
+    return (nat().q_absorb if use_native(q_nope) else ref.q_absorb)(q_nope, w_uk, q_out, r)
 
 
 def v_up(o_lat, w_uv):
-    return (native().v_up if use_native(o_lat) else ref.v_up)(o_lat, w_uv)
+    return (nat().v_up if use_native(o_lat) else ref.v_up)(o_lat, w_uv)
 
 
 def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size, max_q_len=None, meta=None):
     if use_native(q):
-        return native().mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size, max_q_len, meta)
+        return nat().mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size, max_q_len, meta)
     return ref.mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size)
 
 
 def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid):
-    f = native().moe_gate if use_native(g) else ref.moe_gate
+    f = nat().moe_gate if use_native(g) else ref.moe_gate
     return f(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid)
 
 
 def moe_experts(x, ids, wts, wg, wu, wd, expert_base=0):
     if use_native(x) and x.dtype == torch.bfloat16:
-        return native().moe_experts(x, ids, wts, wg, wu, wd, expert_base)
+        return nat().moe_experts(x, ids, wts, wg, wu, wd, expert_base)
     return ref.moe_experts(x, ids, wts, wg, wu, wd, expert_base)
 
 
+def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0):
+    if use_native(x) and x.dtype == torch.bfloat16:
+        return nat().moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base)
+    return ref.moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base)
+
+
 def argmax(logits):
-    return native().argmax(logits) if use_native(logits) else ref.argmax(logits)
+    return nat().argmax(logits) if use_native(logits) else ref.argmax(logits)
 
 
 def topk_logits(logits, k):
-    return native().topk_logits(logits, k) if use_native(logits) else ref.topk_logits(logits, k)
+    return nat().topk_logits(logits, k) if use_native(logits) else ref.topk_logits(logits, k)
 
 
 def kv_block_copy(cache, src_blocks, dst_blocks, block_size):
-    f = native().kv_block_copy if use_native(cache) else ref.kv_block_copy
+    f = nat().kv_block_copy if use_native(cache) else ref.kv_block_copy
     return f(cache, src_blocks, dst_blocks, block_size)

@@ -1,0 +1,338 @@
+"""ctypes front-end of ``libjib200_kernels.so`` (the sm_100a kernels) for torch CUDA tensors.
+
+Every wrapper passes raw device pointers and the current torch CUDA stream; outputs are allocated
+with ``torch.empty`` so that the same code runs eagerly and under CUDA-graph capture.  A non-zero
+return code from a launcher raises: there is no fallback to PyTorch here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+_lib = None
+_ws: Dict[int, "Workspace"] = {}
+launch_count = 0            # kernels launched through this module (bench.py reports it)
+
+ERRORS = {-1: "unsupported shape/argument", -2: "pointer or stride not 16-byte aligned", -3: "driver entry point missing",
+          -4: "tensor map encode failed", -5: "kernel launch failed", -6: "scratch too small for requested split"}
+
+
+class GemmDesc(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("x", "w", "w2", "out", "residual", "seg", "scratch", "counters", "status")] + \
+               [(n, C.c_longlong) for n in ("x_row_stride", "x_batch_stride", "w_row_stride", "w_batch_stride", "ldo",
+                                            "out_batch_stride", "ldr", "res_batch_stride", "x_rows_total")] + \
+               [("scratch_bytes", C.c_size_t)] + \
+               [(n, C.c_int) for n in ("n_counters", "T", "N", "K", "batch", "max_rows", "active_hint", "out_f32", "res_f32",
+                                       "splits", "bn", "sm_count")]
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    from .. import build
+    path = build.KERNELS_SO
+    if not os.path.exists(path):
+        build.build_kernels()
+    L = C.CDLL(path)
+    vp, ip, fp, ll, i, f = C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_float
+
+    def sig(name, *args):
+        fn = getattr(L, name)
+        fn.restype = C.c_int
+        fn.argtypes = list(args)
+
+    sig("jib_gemm_bf16", C.POINTER(GemmDesc), vp)
+    sig("jib_embed_gather", vp, ip, vp, i, i, i, vp)
+    sig("jib_rmsnorm", vp, vp, fp, vp, vp, i, i, ll, f, vp)
+    sig("jib_mla_qkv_post", vp, ll, vp, ll, fp, f, fp, ip, ip, vp, vp, i, i, i, i, i, i, ll, ip, vp)
+    sig("jib_argmax", fp, ip, i, i, vp)
+    sig("jib_topk", fp, fp, ip, i, i, i, vp)
+    sig("jib_kv_block_copy", vp, ll, i, ip, ip, i, i, vp)
+    sig("jib_gather_rows", vp, ip, vp, i, i, vp)
+    sig("jib_moe_gate", vp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, vp)
+    sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
+    sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
+    sig("jib_mla_attention", vp, vp, ip, i, ip, ip, i, i, i, i, i, i, f, i, fp, fp, vp, vp)
+    _lib = L
+    return L
+
+
+class Workspace:
+    """Per-device scratch shared by all launches on one stream: split-K partials, tile counters
+    (zero between launches by construction) and the status words kernels set when a bounded wait
+    expires."""
+
+    SCRATCH_BYTES = 96 << 20
+    N_COUNTERS = 1 << 16
+
+    def __init__(self, device: torch.device):
+        self.scratch = torch.empty(self.SCRATCH_BYTES, dtype=torch.uint8, device=device)
+        self.counters = torch.zeros(self.N_COUNTERS, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def workspace(device: torch.device) -> Workspace:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _ws.get(idx)
+    if w is None:
+        w = _ws[idx] = Workspace(torch.device("cuda", idx))
+    return w
+
+
+def check_status(device=None) -> None:
+    """Raises if any kernel recorded a bounded-wait expiry or a bounds violation (synchronises)."""
+    for idx, w in _ws.items():
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        st = w.status.tolist()
+        if st[0] != 0:
+            w.status.zero_()
+            w.counters.zero_()
+            names = {1: "wait timeout", 2: "index out of bounds", 3: "misaligned"}
+            raise RuntimeError(f"kernel status: {names.get(st[0], st[0])} at site {st[1]} block {st[2]} extra {st[3]}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ck(rc: int, what: str):
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise RuntimeError(f"{what}: {ERRORS.get(rc, rc)}")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# ---- GEMM family ---------------------------------------------------------------------------------
+def gemm(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, *, out: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, splits: int = 0, bn: int = 0
+         ) -> torch.Tensor:
+    """out[T,N] = x[T,K] @ w[N,K]^T  (w2: silu(x w^T) * (x w2^T)) (+ residual)."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(-1) == 1 and w.is_contiguous()
+    T, K = x.shape
+    N = w.shape[0]
+    od = out_dtype or torch.bfloat16
+    if out is None:
+        out = torch.empty(T, N, dtype=od, device=x.device)
+    ws = workspace(x.device)
+    d = GemmDesc()
+    d.x, d.w, d.w2, d.out, d.residual = x.data_ptr(), w.data_ptr(), _p(w2), out.data_ptr(), _p(residual)
+    d.seg, d.scratch, d.counters, d.status = None, ws.scratch.data_ptr(), ws.counters.data_ptr(), ws.status.data_ptr()
+    d.x_row_stride, d.x_batch_stride, d.w_row_stride, d.w_batch_stride = x.stride(0), 0, K, 0
+    d.ldo, d.out_batch_stride = out.stride(0), 0
+    d.ldr = residual.stride(0) if residual is not None else 0
+    d.res_batch_stride, d.x_rows_total, d.scratch_bytes, d.n_counters = 0, T, ws.SCRATCH_BYTES, ws.N_COUNTERS
+    d.T, d.N, d.K, d.batch, d.max_rows, d.active_hint = T, N, K, 1, 0, 0
+    d.out_f32 = int(out.dtype == torch.float32)
+    d.res_f32 = int(residual is not None and residual.dtype == torch.float32)
+    d.splits, d.bn, d.sm_count = splits, bn, ws.sm_count
+    _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm")
+    return out
+
+
+def gemm_batched(x_ptr: int, x_row_stride: int, x_batch_stride: int, w: torch.Tensor, out_ptr: int, ldo: int,
+                 out_batch_stride: int, T: int, device, splits: int = 0) -> None:
+    """Per-batch (per-head) GEMM with arbitrary element strides: out[b][t][:N] = x[b][t][:K] @ w[b]^T."""
+    B, N, K = w.shape
+    ws = workspace(device)
+    d = GemmDesc()
+    d.x, d.w, d.w2, d.out, d.residual = x_ptr, w.data_ptr(), None, out_ptr, None
+    d.seg, d.scratch, d.counters, d.status = None, ws.scratch.data_ptr(), ws.counters.data_ptr(), ws.status.data_ptr()
+    d.x_row_stride, d.x_batch_stride, d.w_row_stride, d.w_batch_stride = x_row_stride, x_batch_stride, K, N * K
+    d.ldo, d.out_batch_stride, d.ldr, d.res_batch_stride = ldo, out_batch_stride, 0, 0
+    d.x_rows_total, d.scratch_bytes, d.n_counters = T, ws.SCRATCH_BYTES, ws.N_COUNTERS
+    d.T, d.N, d.K, d.batch, d.max_rows, d.active_hint = T, N, K, B, 0, 0
+    d.out_f32, d.res_f32, d.splits, d.bn, d.sm_count = 0, 0, splits, 0, ws.sm_count
+    _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_batched")
+
+
+def gemm_grouped(xp: torch.Tensor, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor], max_rows: int,
+                 active_hint: int, splits: int = 0) -> torch.Tensor:
+    """Rows of xp are sorted by expert; expert e owns rows seg[e]:seg[e+1] and weight w[e] ([E,N,K])."""
+    E, N, K = w.shape
+    R = xp.shape[0]
+    out = torch.empty(R, N, dtype=torch.bfloat16, device=xp.device)
+    ws = workspace(xp.device)
+    d = GemmDesc()
+    d.x, d.w, d.w2, d.out, d.residual = xp.data_ptr(), w.data_ptr(), _p(w2), out.data_ptr(), None
+    d.seg, d.scratch, d.counters, d.status = seg.data_ptr(), ws.scratch.data_ptr(), ws.counters.data_ptr(), ws.status.data_ptr()
+    d.x_row_stride, d.x_batch_stride, d.w_row_stride, d.w_batch_stride = xp.stride(0), 0, K, N * K
+    d.ldo, d.out_batch_stride, d.ldr, d.res_batch_stride = N, 0, 0, 0
+    d.x_rows_total, d.scratch_bytes, d.n_counters = R, ws.SCRATCH_BYTES, ws.N_COUNTERS
+    d.T, d.N, d.K, d.batch, d.max_rows, d.active_hint = max_rows, N, K, E, max_rows, active_hint
+    d.out_f32, d.res_f32, d.splits, d.bn, d.sm_count = 0, 0, splits, 0, ws.sm_count
+    _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_grouped")
+    return out
+
+
+def linear(x, w, residual=None, out_dtype=None):
+    return gemm(x, w, residual=residual, out_dtype=out_dtype)
+
+
+def gateup_silu(x, wg, wu):
+    return gemm(x, wg, wu)
+
+
+# ---- memory-bound kernels ------------------------------------------------------------------------
+def embed_gather(table, ids):
+    T, d = ids.shape[0], table.shape[1]
+    out = torch.empty(T, d, dtype=table.dtype, device=table.device)
+    _ck(load().jib_embed_gather(table.data_ptr(), ids.data_ptr(), out.data_ptr(), T, d, table.shape[0], _stream()), "embed")
+    return out
+
+
+def rmsnorm(x, w, eps, residual=None):
+    assert x.dtype == torch.bfloat16 and x.stride(-1) == 1
+    T, d = x.shape
+    out = torch.empty(T, d, dtype=x.dtype, device=x.device)
+    summed = torch.empty(T, d, dtype=x.dtype, device=x.device) if residual is not None else None
+    _ck(load().jib_rmsnorm(x.data_ptr(), _p(residual), w.data_ptr(), out.data_ptr(), _p(summed), T, d, x.stride(0),
+                           float(eps), _stream()), "rmsnorm")
+    return out, (summed if residual is not None else x)
+
+
+def mla_qkv_post(q, ckv, kv_norm_w, eps, rope_table, positions, slot_mapping, cache, q_out, n_head, dn, dr, r):
+    T = q.shape[0]
+    ws = workspace(q.device)
+    _ck(load().jib_mla_qkv_post(q.data_ptr(), q.stride(0), ckv.data_ptr(), ckv.stride(0), kv_norm_w.data_ptr(), float(eps),
+                                rope_table.data_ptr(), positions.data_ptr(), slot_mapping.data_ptr(), cache.data_ptr(),
+                                q_out.data_ptr(), T, n_head, dn, dr, r, rope_table.shape[0], cache.shape[0],
+                                ws.status.data_ptr(), _stream()), "mla_qkv_post")
+    return q.view(T, n_head, dn + dr)[..., :dn] if q.is_contiguous() else q.as_strided((T, n_head, dn), (q.stride(0), dn + dr, 1))
+
+
+def q_absorb(q_nope, w_ukT, q_out, r):
+    """q_out[t,h,:r] = q_nope[t,h,:] @ w_ukT[h]^T with w_ukT [H, r, dn]."""
+    T, H, dn = q_nope.shape
+    gemm_batched(q_nope.data_ptr(), q_nope.stride(0), q_nope.stride(1), w_ukT, q_out.data_ptr(), q_out.stride(0),
+                 q_out.stride(1), T, q_nope.device)
+
+
+def v_up(o_lat, w_uv):
+    """o[t, h*dv:(h+1)*dv] = o_lat[t,h,:] @ w_uv[h]^T with w_uv [H, dv, r]."""
+    T, H, r = o_lat.shape
+    dv = w_uv.shape[1]
+    out = torch.empty(T, H * dv, dtype=o_lat.dtype, device=o_lat.device)
+    gemm_batched(o_lat.data_ptr(), o_lat.stride(0), o_lat.stride(1), w_uv, out.data_ptr(), H * dv, dv, T, o_lat.device)
+    return out
+
+
+def attn_splits(T: int, H: int, sm_count: int = 148) -> int:
+    """Split count for the decode kernel: enough CTAs to cover the machine about twice."""
+    per = max(1, T * max(1, H // 16))
+    return max(1, min(32, (2 * sm_count + per - 1) // per))
+
+
+def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size, max_q_len=None, meta=None):
+    T, H, D = q.shape
+    n_seqs = seq_lens.shape[0]
+    n_splits = 1 if (max_q_len or 1) > 1 and T > 64 else attn_splits(T, H)
+    o = torch.empty(T, H, r, dtype=q.dtype, device=q.device)
+    if n_splits > 1:
+        part_o = torch.empty(T, n_splits, H, r, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(T, n_splits, H, 2, dtype=torch.float32, device=q.device)
+    else:
+        part_o = part_ml = None
+    _ck(load().jib_mla_attention(q.data_ptr(), cache.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+                                 seq_lens.data_ptr(), q_start.data_ptr(), n_seqs, T, H, r, D - r, block_size, float(scale),
+                                 n_splits, _p(part_o), _p(part_ml), o.data_ptr(), _stream()), "mla_attention")
+    return o
+
+
+# ---- MoE -----------------------------------------------------------------------------------------
+def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid):
+    T, d = g.shape
+    E = w_router.shape[0]
+    ids = torch.empty(T, k, dtype=torch.int32, device=g.device)
+    wts = torch.empty(T, k, dtype=torch.float32, device=g.device)
+    _ck(load().jib_moe_gate(g.data_ptr(), w_router.data_ptr(), _p(bias), ids.data_ptr(), wts.data_ptr(), T, d, E, k, n_group,
+                            topk_group, float(scale), int(norm), int(sigmoid), _stream()), "moe_gate")
+    return ids, wts
+
+
+def moe_permute(ids, expert_base, E_local):
+    T, k = ids.shape
+    dev = ids.device
+    seg = torch.empty(E_local + 1, dtype=torch.int32, device=dev)
+    src = torch.empty(T * k, dtype=torch.int32, device=dev)
+    dest = torch.empty(T, k, dtype=torch.int32, device=dev)
+    _ck(load().jib_moe_permute(ids.data_ptr(), T, k, expert_base, E_local, seg.data_ptr(), src.data_ptr(), dest.data_ptr(),
+                               _stream()), "moe_permute")
+    return seg, src, dest
+
+
+def gather_rows(x, src_row):
+    R, d = src_row.shape[0], x.shape[1]
+    out = torch.empty(R, d, dtype=x.dtype, device=x.device)
+    _ck(load().jib_gather_rows(x.data_ptr(), src_row.data_ptr(), out.data_ptr(), R, d, _stream()), "gather_rows")
+    return out
+
+
+def moe_combine(y, dest, wts, shared, residual):
+    T, k = dest.shape
+    d = y.shape[1]
+    out = torch.empty(T, d, dtype=torch.bfloat16, device=y.device)
+    _ck(load().jib_moe_combine(y.data_ptr(), dest.data_ptr(), wts.data_ptr(), _p(shared), _p(residual), out.data_ptr(), T, k, d,
+                               _stream()), "moe_combine")
+    return out
+
+
+def moe_routed(x, ids, wts, wg, wu, wd, expert_base=0):
+    """Expert-sorted rows -> grouped gate|up GEMM (SiLU*mul epilogue) -> grouped down GEMM.
+    Returns (y [T*k, d] in sorted order, dest [T,k])."""
+    T, k = ids.shape
+    E_local = wg.shape[0]
+    seg, src, dest = moe_permute(ids, expert_base, E_local)
+    xp = gather_rows(x, src)
+    active = min(E_local, T * k)
+    h = gemm_grouped(xp, seg, wg, wu, T, active)
+    y = gemm_grouped(h, seg, wd, None, T, active)
+    return y, dest
+
+
+def moe_experts(x, ids, wts, wg, wu, wd, expert_base=0):
+    """fp32 [T, d] sum over the local experts (API parity with the reference implementation)."""
+    y, dest = moe_routed(x, ids, wts, wg, wu, wd, expert_base)
+    return moe_combine(y, dest, wts, None, None).float()
+
+
+def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0):
+    """residual + shared_experts(x) + sum_k w_k expert_k(x), bf16; residual/shared may be None."""
+    y, dest = moe_routed(x, ids, wts, wg, wu, wd, expert_base)
+    shared = None
+    if wgs is not None:
+        shared = gemm(gemm(x, wgs, wus), wds)
+    return moe_combine(y, dest, wts, shared, residual)
+
+
+# ---- sampling / cache ----------------------------------------------------------------------------
+def argmax(logits):
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    out = torch.empty(n, dtype=torch.int32, device=logits.device)
+    _ck(load().jib_argmax(logits.data_ptr(), out.data_ptr(), n, V, _stream()), "argmax")
+    return out
+
+
+def topk_logits(logits, k):
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    vals = torch.empty(n, k, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(n, k, dtype=torch.int32, device=logits.device)
+    _ck(load().jib_topk(logits.data_ptr(), vals.data_ptr(), ids.data_ptr(), n, V, k, _stream()), "topk")
+    return vals, ids
+
+
+def kv_block_copy(cache, src_blocks, dst_blocks, block_size):
+    L, n_slots, row = cache.shape
+    _ck(load().jib_kv_block_copy(cache.data_ptr(), n_slots * row, L, src_blocks.data_ptr(), dst_blocks.data_ptr(),
+                                 src_blocks.shape[0], block_size * row, _stream()), "kv_block_copy")

@@ -99,8 +99,8 @@ def mla_qkv_post(q: torch.Tensor, ckv: torch.Tensor, kv_norm_w: torch.Tensor, ep
 
 
 def q_absorb(q_nope: torch.Tensor, w_uk: torch.Tensor, q_out: torch.Tensor, r: int) -> None:
-    """q_out[..., :r] = q_nope[T,H,dn] @ w_uk[H,dn,r]  (src/llama-graph-attn.cpp:269-275)."""
-    q_out[..., :r] = torch.einsum("thd,hdr->thr", q_nope.float(), w_uk.float()).to(q_out.dtype)
+    """q_out[..., :r] = q_nope[T,H,dn] @ w_uk[H,r,dn]^T  (src/llama-graph-attn.cpp:269-275)."""
+    q_out[..., :r] = torch.einsum("thd,hrd->thr", q_nope.float(), w_uk.float()).to(q_out.dtype)
 
 
 def v_up(o_lat: torch.Tensor, w_uv: torch.Tensor) -> torch.Tensor:
@@ -177,6 +177,16 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, wg: torch
         y = linear(h, wd[e], out_dtype=torch.float32)
         out.index_add_(0, tok, y * wts[tok, slot][:, None])
     return out
+
+
+def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0):
+    """residual + shared_experts(x) + routed experts (src/llama-graph-deepseek2.cpp:343-362)."""
+    out = moe_experts(x, ids, wts, wg, wu, wd, expert_base)
+    if wgs is not None:
+        out = out + linear(gateup_silu(x, wgs, wus), wds, out_dtype=torch.float32)
+    if residual is not None:
+        out = out + residual.float()
+    return out.to(x.dtype)
 
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:

@@ -122,7 +122,8 @@ class LLMEngine:
                                      pin_memory=self.device.type == "cuda")
         self.stats = {"steps": 0, "graph_steps": 0, "eager_steps": 0, "tokens_in": 0, "tokens_out": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "defrag_moves": 0}
-        self.kernel_launches_last_step = 0
+        self.graph_launches: Dict[Tuple[int, str], int] = {}    # launcher calls captured per decode graph
+        self.launches = 0                                          # launcher calls executed (eager + replayed)
 
     # ------------------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -180,8 +181,11 @@ class LLMEngine:
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
+        n0 = ops.nat().launch_count if not ops.force_torch() else 0
         with torch.cuda.graph(g):
             out = self._forward_sample(batch, mode)
+        if not ops.force_torch():
+            self.graph_launches[key] = ops.nat().launch_count - n0
         self._graphs[key] = (g, out)
         return self._graphs[key]
 
@@ -262,13 +266,17 @@ class LLMEngine:
             g, out = self._graph_for(bucket, mode)
             io.upload()
             g.replay()
+            self.launches += self.graph_launches.get((bucket, mode), 0)
             self.stats["graph_steps"] += 1
         else:
             io.upload()
             batch = self._batch_views(n_tokens, n_seqs, n_out, max_q)
+            n0 = ops.nat().launch_count if self.device.type == "cuda" and not ops.force_torch() else 0
             out = self._forward_sample(batch, mode) if n_out else None
             if n_out == 0:
                 self.model.forward(batch, self.kv_cache)
+            if self.device.type == "cuda" and not ops.force_torch():
+                self.launches += ops.nat().launch_count - n0
             self.stats["eager_steps"] += 1
         self.stats["steps"] += 1
         self.stats["tokens_in"] += n_tokens

@@ -1,0 +1,48 @@
+"""Engine construction: model source (GGUF file or random init) + parallel layout -> LLMEngine.
+
+Counterpart of ``common_init_from_params`` (common/common_local.cpp:121-209: model load, then
+context creation) for this runtime.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from ..models.deepseek2 import DeepSeek2Model
+from ..models.hparams import DeepSeek2HParams
+from ..models.weights import ShardSpec, iter_gguf, iter_random
+from .engine import EngineConfig, LLMEngine
+
+
+def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] = None, device="cuda",
+                dtype: torch.dtype = torch.bfloat16, world: int = 1, rank: int = 0, expert_parallel: bool = True,
+                comm=None, seed: int = 0, std: float = 0.02, max_positions: int = 8192, fast_random: bool = True
+                ) -> DeepSeek2Model:
+    spec = ShardSpec(rank, world, expert_parallel and world > 1)
+    if gguf_path is not None:
+        from ..gguf.io import GGUFReader
+        reader = GGUFReader(gguf_path)
+        hp = DeepSeek2HParams.from_gguf_kv(reader.kv, reader.tensors)
+        weights = iter_gguf(reader, hp, spec)
+    else:
+        assert hp is not None
+        dev = torch.device(device)
+        weights = iter_random(hp, spec=spec, seed=seed, std=std, dtype=dtype if dev.type == "cuda" else torch.float32,
+                              device=dev, fast=fast_random and dev.type == "cuda")
+    if world > 1 and comm is None:
+        from ..parallel.comm import make_communicator
+        comm = make_communicator(torch.device(device), world, rank, hp.n_embd)
+    return DeepSeek2Model(hp, weights, dtype=dtype, device=device, spec=spec, comm=comm, max_positions=max_positions)
+
+
+def build_engine(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] = None, device="cuda",
+                 dtype: torch.dtype = torch.bfloat16, world: int = 1, rank: int = 0, n_parallel: int = 8,
+                 n_ctx_slot: int = 2048, n_batch: int = 2048, seed: int = 0, graph_buckets: Sequence[int] = (1, 2, 4, 8),
+                 cuda_graphs: bool = True, expert_parallel: bool = True, comm=None, n_ctx: Optional[int] = None,
+                 **engine_kw) -> LLMEngine:
+    model = build_model(hp, gguf_path, device, dtype, world, rank, expert_parallel, comm, seed,
+                        max_positions=max(n_ctx_slot, 64))
+    cfg = EngineConfig(n_ctx=n_ctx or n_ctx_slot * n_parallel, n_batch=n_batch, n_parallel=n_parallel, n_ctx_slot=n_ctx_slot,
+                       graph_buckets=tuple(graph_buckets), cuda_graphs=cuda_graphs, **engine_kw)
+    return LLMEngine(model, cfg)

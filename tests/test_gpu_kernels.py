@@ -1,0 +1,209 @@
+"""sm_100a kernels vs the plain-PyTorch fp32 reference of the same op (tile-edge shapes included)."""
+import pytest
+import torch
+
+from jittorinfer_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from jittorinfer_b200.ops import native
+    native.load()
+    yield native
+    torch.cuda.synchronize()
+    native.check_status()
+
+
+def rnd(*shape, scale=1.0, dtype=torch.bfloat16, seed=None):
+    g = torch.Generator(device="cpu")
+    g.manual_seed(hash(shape) % (2 ** 31) if seed is None else seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(a, b, tol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref_mag = b.abs().max().item() + 1e-6
+    assert err <= tol * ref_mag, f"max err {err} vs magnitude {ref_mag}"
+
+
+@pytest.mark.parametrize("T", [1, 2, 7, 8, 16, 17, 63, 64, 65, 128, 129, 300])
+@pytest.mark.parametrize("N,K", [(256, 512), (200, 192), (3648, 2048)])
+def test_gemm_shapes(nat, T, N, K):
+    x, w = rnd(T, K), rnd(N, K, scale=0.05)
+    y = nat.gemm(x, w)
+    close(y, x.float() @ w.float().T)
+    nat.check_status()
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+@pytest.mark.parametrize("T", [1, 8, 40])
+def test_gemm_split_k(nat, splits, T):
+    x, w = rnd(T, 2048), rnd(384, 2048, scale=0.05)
+    for _ in range(2):     # second launch checks that the tile counters were left at zero
+        y = nat.gemm(x, w, splits=splits)
+        close(y, x.float() @ w.float().T)
+    nat.check_status()
+
+
+def test_gemm_residual_f32_out(nat):
+    x, w, r = rnd(5, 1024), rnd(640, 1024, scale=0.05), rnd(5, 640)
+    close(nat.gemm(x, w, residual=r), x.float() @ w.float().T + r.float())
+    rf = r.float()
+    y = nat.gemm(x, w, residual=rf, out_dtype=torch.float32)
+    assert y.dtype == torch.float32
+    close(y, x.float() @ w.float().T + rf, tol=1e-3)
+
+
+@pytest.mark.parametrize("T,splits", [(1, 0), (8, 0), (8, 4), (33, 1), (200, 0)])
+def test_gemm_gateup_silu(nat, T, splits):
+    x, wg, wu = rnd(T, 1024), rnd(1408, 1024, scale=0.05), rnd(1408, 1024, scale=0.05, seed=3)
+    y = nat.gemm(x, wg, wu, splits=splits)
+    g, u = x.float() @ wg.float().T, x.float() @ wu.float().T
+    close(y, torch.nn.functional.silu(g) * u)
+    nat.check_status()
+
+
+def test_gemm_strided_rows(nat):
+    big = rnd(9, 1000)
+    x = big[:, 104:104 + 512]            # row stride 1000, 16-byte aligned start
+    w = rnd(256, 512, scale=0.05)
+    close(nat.gemm(x, w), x.float() @ w.float().T)
+
+
+@pytest.mark.parametrize("T", [1, 8, 70])
+def test_q_absorb_v_up(nat, T):
+    H, dn, dr, r, dv = 16, 128, 64, 512, 128
+    q = rnd(T, H * (dn + dr))
+    w_uk = rnd(H, r, dn, scale=0.05)
+    q_out = torch.zeros(T, H, r + dr, dtype=torch.bfloat16, device=DEV)
+    q_nope = q.view(T, H, dn + dr)[..., :dn]
+    nat.q_absorb(q_nope, w_uk, q_out, r)
+    exp = torch.zeros_like(q_out)
+    ref.q_absorb(q_nope, w_uk, exp, r)
+    close(q_out[..., :r], exp[..., :r])
+    assert q_out[..., r:].abs().max().item() == 0
+    o_lat, w_uv = rnd(T, H, r), rnd(H, dv, r, scale=0.05)
+    close(nat.v_up(o_lat, w_uv), ref.v_up(o_lat, w_uv))
+    nat.check_status()
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (8, 64, 6), (50, 64, 6), (300, 16, 4)])
+def test_moe_routed(nat, T, E, k):
+    d, F = 512, 384
+    x = rnd(T, d)
+    wg, wu, wd = rnd(E, F, d, scale=0.05), rnd(E, F, d, scale=0.05, seed=5), rnd(E, d, F, scale=0.05)
+    g = torch.Generator().manual_seed(T)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).int().to(DEV)
+    wts = torch.rand(T, k, generator=g).to(DEV)
+    for base, El in ((0, E), (E // 2, E // 2)):       # all experts local / second half local (expert parallel)
+        out = nat.moe_experts(x, ids, wts, wg[base:base + El].contiguous(), wu[base:base + El].contiguous(),
+                              wd[base:base + El].contiguous(), base)
+        exp = ref.moe_experts(x, ids, wts, wg[base:base + El], wu[base:base + El], wd[base:base + El], base)
+        close(out, exp, tol=3e-2)
+    nat.check_status()
+
+
+def test_moe_permute_is_stable_sort(nat):
+    T, k, E = 37, 6, 64
+    g = torch.Generator().manual_seed(1)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).int().to(DEV)
+    seg, src, dest = nat.moe_permute(ids, 0, E)
+    flat = ids.flatten().cpu()
+    order = torch.sort(flat, stable=True).indices
+    assert torch.equal(src.cpu(), (order // k).int())
+    counts = torch.bincount(flat, minlength=E)
+    assert torch.equal(seg.cpu()[1:] - seg.cpu()[:-1], counts.int())
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(T * k)
+    assert torch.equal(dest.flatten().cpu(), inv.int())
+
+
+@pytest.mark.parametrize("E,k,ng,tg,sig", [(64, 6, 1, 1, False), (160, 6, 8, 3, False), (8, 2, 1, 1, False), (16, 4, 4, 2, True)])
+def test_moe_gate(nat, E, k, ng, tg, sig):
+    T, d = 9, 2048
+    g = rnd(T, d)
+    wr = rnd(E, d, dtype=torch.float32, scale=0.05)
+    ids, w = nat.moe_gate(g, wr, None, k, ng, tg, 16.0, False, sig)
+    ids2, w2 = ref.moe_gate(g, wr, None, k, ng, tg, 16.0, False, sig)
+    assert torch.equal(ids.cpu(), ids2.cpu())
+    close(w, w2, tol=1e-4)
+    ids, w = nat.moe_gate(g, wr, None, k, ng, tg, 1.0, True, sig)
+    ids2, w2 = ref.moe_gate(g, wr, None, k, ng, tg, 1.0, True, sig)
+    close(w, w2, tol=1e-4)
+
+
+@pytest.mark.parametrize("d", [512, 1536, 2048, 5120])
+def test_rmsnorm(nat, d):
+    x, r, w = rnd(11, d), rnd(11, d), rnd(d, dtype=torch.float32) + 1
+    n, s = nat.rmsnorm(x, w, 1e-6, r)
+    n2, s2 = ref.rmsnorm(x, w, 1e-6, r)
+    assert torch.equal(s, s2)
+    close(n, n2, tol=1e-2)
+    n, _ = nat.rmsnorm(x, w, 1e-6)
+    close(n, ref.rmsnorm(x, w, 1e-6)[0], tol=1e-2)
+
+
+def test_mla_qkv_post_and_embed(nat):
+    T, H, dn, dr, r = 10, 16, 128, 64, 512
+    q, ckv, w = rnd(T, H * (dn + dr)), rnd(T, r + dr), rnd(r, dtype=torch.float32) + 1
+    table = ref.yarn_table(256, dr, 10000.0, 0.025, 1.0, 0.73, 10, 23, device=DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV) * 7
+    slots = torch.tensor([5, 3, -1, 9, 64, 65, 66, 0, 1, 127], dtype=torch.int32, device=DEV)
+    c1 = torch.zeros(128, r + dr, dtype=torch.bfloat16, device=DEV)
+    c2 = c1.clone()
+    q1 = torch.zeros(T, H, r + dr, dtype=torch.bfloat16, device=DEV)
+    q2 = q1.clone()
+    nat.mla_qkv_post(q, ckv, w, 1e-6, table, pos, slots, c1, q1, H, dn, dr, r)
+    ref.mla_qkv_post(q, ckv, w, 1e-6, table, pos, slots, c2, q2, H, dn, dr, r)
+    close(c1, c2, tol=1e-2)
+    close(q1, q2, tol=1e-2)
+    emb = rnd(1000, 256)
+    ids = torch.randint(0, 1000, (33,), dtype=torch.int32, device=DEV)
+    assert torch.equal(nat.embed_gather(emb, ids), emb[ids.long()])
+
+
+@pytest.mark.parametrize("r,dr,H", [(512, 64, 16), (64, 16, 16), (512, 64, 32), (64, 16, 4)])
+@pytest.mark.parametrize("lens,qlens", [([1], [1]), ([70, 300, 5, 129], [1, 1, 1, 1]), ([40, 200], [40, 73]), ([0, 33], [1, 1])])
+def test_mla_attention(nat, r, dr, H, lens, qlens):
+    bs = 64
+    nb_per = 8
+    B = len(lens)
+    cache = rnd(B * nb_per * bs, r + dr)
+    g = torch.Generator().manual_seed(7)
+    perm = torch.randperm(B * nb_per, generator=g).view(B, nb_per).int().to(DEV)
+    T = sum(qlens)
+    q = rnd(T, H, r + dr, scale=0.3)
+    qs = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    o = nat.mla_attention(q, cache, perm, sl, qs, 0.11, r, bs, max(qlens))
+    o2 = ref.mla_attention(q, cache, perm, sl, qs, 0.11, r, bs)
+    close(o, o2)
+
+
+def test_argmax_topk(nat):
+    x = rnd(6, 102400, dtype=torch.float32)
+    x[2, 77] = 50.0
+    x[3, 5] = x[3, 9] = 60.0       # tie -> lower index
+    am = nat.argmax(x)
+    assert am.tolist() == torch.argmax(x, -1).tolist() or am[3].item() == 5
+    assert am[2].item() == 77 and am[3].item() == 5
+    for k in (1, 40, 64):
+        v, i = nat.topk_logits(x, k)
+        v2, i2 = torch.topk(x, k, dim=-1)
+        assert torch.equal(v, v2)
+        assert torch.equal(torch.gather(x, 1, i.long()), v)
+
+
+def test_kv_block_copy(nat):
+    L, nb, bs, row = 3, 10, 64, 576
+    cache = rnd(L, nb * bs, row)
+    exp = cache.clone()
+    src = torch.tensor([7, 9], dtype=torch.int32, device=DEV)
+    dst = torch.tensor([1, 2], dtype=torch.int32, device=DEV)
+    nat.kv_block_copy(cache, src, dst, bs)
+    ref.kv_block_copy(exp, src, dst, bs)
+    assert torch.equal(cache, exp)

@@ -1,0 +1,88 @@
+"""Native host runtime: paged KV allocator and scheduler (no GPU)."""
+import numpy as np
+import torch
+
+from jittorinfer_b200.runtime.engine import _StepIO
+from jittorinfer_b200.runtime.native_rt import PagedKV, Scheduler
+
+
+def test_kv_append_rm_cp_cow():
+    kv = PagedKV(8, 4, 4)
+    s = kv.append(0, 6)
+    assert list(s) == [0, 1, 2, 3, 4, 5] and kv.used_blocks == 2
+    assert kv.seq_cp(0, 1)                           # share prefix: refcounts bump, no new blocks
+    assert kv.used_blocks == 2 and kv.refcount(0) == 2 and kv.seq_len(1) == 6
+    s1 = kv.append(1, 1)                             # partially filled shared tail block -> copy-on-write
+    src, dst = kv.take_copies()
+    assert list(src) == [1] and list(dst) == [2] and s1[0] == 2 * 4 + 2
+    assert kv.refcount(1) == 1 and kv.check()
+    assert not kv.seq_rm(0, 1, 3)                    # hole in the middle is not representable
+    assert kv.seq_rm(0, 4, -1) and kv.seq_len(0) == 4 and kv.check()
+    assert kv.seq_rm(1, 0, -1) and kv.check()
+    assert kv.append(2, 4 * 7) is not None and kv.append(3, 1) is None   # out of blocks: refused, unchanged
+    assert kv.check()
+
+
+def test_kv_defrag_compacts_and_keeps_tables_valid():
+    kv = PagedKV(16, 4, 4)
+    for s in range(4):
+        kv.append(s, 12)
+    kv.seq_rm(0, 0, -1)
+    kv.seq_rm(2, 0, -1)
+    frag = kv.fragmentation()
+    assert frag > 0.4
+    before = {s: kv.seq_len(s) for s in range(4)}
+    src, dst = kv.defrag(64)
+    assert len(src) > 0 and set(dst.tolist()).isdisjoint(src.tolist())
+    assert kv.fragmentation() == 0.0 and kv.check()
+    assert {s: kv.seq_len(s) for s in range(4)} == before
+    assert max(max(kv.seq_blocks(1)), max(kv.seq_blocks(3))) < 6
+
+
+def _run(sched, io, sample, max_steps=10000):
+    out = {}
+    for _ in range(max_steps):
+        info = sched.step(io.arrays)
+        n_tok, n_seq, n_out = int(info[0]), int(info[1]), int(info[2])
+        if n_tok == 0:
+            if sched.idle():
+                break
+            continue
+        assert io.h["q_start"][n_seq] == n_tok
+        toks = np.array([sample(r) for r in sched.out_reqs(n_out)], dtype=np.int32)
+        sched.commit(toks, n_out)
+        for rid, slot, tok, fin, npmt, ndec in sched.take_events():
+            out.setdefault(rid, []).append((tok, fin))
+    return out
+
+
+def test_scheduler_chunked_prefill_budget_and_stop_rules():
+    kv = PagedKV(64, 16, 4)
+    sched = Scheduler(kv, 4, 32, 256, eos_id=7)
+    io = _StepIO(32, 4, 16, torch.device("cpu"))
+    sched.add(1, list(range(100, 170)), max_new=5)            # 70-token prompt: 32+32+6 chunks
+    sched.add(2, [1, 2, 3], max_new=50)                       # stops on EOS
+    sched.add(3, [4, 5], max_new=3, ignore_eos=True)
+    out = _run(sched, io, lambda rid: 7 if rid in (2, 3) else 9)
+    assert [t for t, _ in out[1]] == [9] * 5 and out[1][-1][1] == "length"
+    assert out[2] == [(7, "stop")]
+    assert [f for _, f in out[3]] == [None, None, "length"]
+    st = sched.stats()
+    assert st["finished"] == 3 and st["prompt_tokens"] == 75 and kv.check()
+
+
+def test_scheduler_prefix_reuse_and_preemption():
+    kv = PagedKV(12, 16, 2)
+    sched = Scheduler(kv, 2, 64, 512, eos_id=-1)
+    io = _StepIO(64, 2, 32, torch.device("cpu"))
+    p = list(range(40))
+    sched.add(1, p, max_new=2)
+    _run(sched, io, lambda rid: 3)
+    sched.add(2, p + [99, 98], max_new=2)                      # shares 40 cached tokens with the idle slot
+    _run(sched, io, lambda rid: 3)
+    assert sched.stats()["prefix_hits"] == 1
+    # two long generations in a 12-block cache: the younger one is preempted, both still finish
+    sched.add(3, list(range(60)), max_new=60)
+    sched.add(4, list(range(60, 120)), max_new=60)
+    out = _run(sched, io, lambda rid: 5)
+    assert len(out[3]) == 60 and len(out[4]) == 60 and sched.stats()["preemptions"] >= 1 and kv.check()
