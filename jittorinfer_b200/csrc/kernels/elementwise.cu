@@ -278,10 +278,10 @@ __global__ void kv_block_copy_kernel(bf16 * cache, long long layer_stride, const
     for (int j = threadIdx.x; j < block_elems / 8; j += blockDim.x) d[j] = s[j];
 }
 
-__global__ void gather_rows_kernel(const bf16 * __restrict__ x, const int * __restrict__ src_row, bf16 * __restrict__ out, int d) {
+__global__ void gather_rows_kernel(const bf16 * __restrict__ x, const int * __restrict__ src_row, bf16 * __restrict__ out, int d, int n_src) {
     const int rrow = blockIdx.x;
     const int s = src_row[rrow];
-    if (s < 0) return;
+    if (s < 0 || s >= n_src) return;   // unowned / out-of-range row: leave the destination untouched
     const uint4 * src = (const uint4 *) (x + (size_t) s * d);
     uint4 * dst = (uint4 *) (out + (size_t) rrow * d);
     for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
@@ -351,10 +351,10 @@ int jib_kv_block_copy(void * cache, long long layer_stride_elems, int n_layers, 
     return launched();
 }
 
-int jib_gather_rows(const void * x, const int * src_row, void * out, int rows, int d, void * stream) {
+int jib_gather_rows(const void * x, const int * src_row, void * out, int rows, int d, int n_src, void * stream) {
     if (rows <= 0) return 0;
     if (d % 8) return JIB_E_ARG;
-    gather_rows_kernel<<<rows, 128, 0, (cudaStream_t) stream>>>((const bf16 *) x, src_row, (bf16 *) out, d);
+    gather_rows_kernel<<<rows, 128, 0, (cudaStream_t) stream>>>((const bf16 *) x, src_row, (bf16 *) out, d, n_src);
     return launched();
 }
 

@@ -58,7 +58,10 @@ struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
-    static constexpr int STAGES_RAW = (200 * 1024) / STAGE_BYTES;
+    // Narrow token tiles are bandwidth-bound streams of small CTAs: give each half of the shared memory so
+    // that two CTAs share an SM and one's prologue/epilogue hides behind the other's loads.
+    static constexpr int SMEM_BUDGET = BN <= 32 ? 108 * 1024 : 200 * 1024;
+    static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
@@ -370,8 +373,9 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     if (splits <= 0) {
         splits = 1;
         const int sms = d->sm_count > 0 ? d->sm_count : 148;
-        if (base_ctas < sms && d->scratch != nullptr) {
-            splits = (int) ((sms + base_ctas - 1) / base_ctas);
+        const int slots = sms * (bn <= 32 ? 2 : 1);             // CTAs resident at once (one wave)
+        if (2 * base_ctas <= slots && d->scratch != nullptr) {
+            splits = (int) (slots / base_ctas);
             if (splits > num_kb / 4) splits = num_kb / 4;      // at least 4 k-blocks (256 K) per split
             if (splits < 1) splits = 1;
         }

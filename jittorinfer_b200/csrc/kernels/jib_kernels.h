@@ -60,11 +60,12 @@ JIB_EXPORT int jib_argmax(const float * logits, int * out, int n, int V, void * 
 JIB_EXPORT int jib_topk(const float * logits, float * vals, int * ids, int n, int V, int k, void * stream);
 JIB_EXPORT int jib_kv_block_copy(void * cache, long long layer_stride_elems, int n_layers, const int * src, const int * dst, int n,
                                  int block_elems, void * stream);
-JIB_EXPORT int jib_gather_rows(const void * x, const int * src_row, void * out, int rows, int d, void * stream);
+JIB_EXPORT int jib_gather_rows(const void * x, const int * src_row, void * out, int rows, int d, int n_src, void * stream);
 
 // ---- MoE routing (moe.cu) ---------------------------------------------------------------------
-JIB_EXPORT int jib_moe_gate(const void * g, const float * w_router, const float * bias, int * ids, float * wts, int T, int d, int E,
-                            int k, int n_group, int topk_group, float scale, int norm, int sigmoid, void * stream);
+// logits: fp32 scratch [T][E] (router outputs, kept for inspection)
+JIB_EXPORT int jib_moe_gate(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int T,
+                            int d, int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, void * stream);
 // Stable counting sort of the (token, k) pairs by local expert. dest[t*k+j] = sorted row or -1 (not local).
 JIB_EXPORT int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
                                void * stream);

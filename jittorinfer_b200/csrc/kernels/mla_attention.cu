@@ -172,25 +172,42 @@ __global__ void __launch_bounds__(NT) mla_attn_split_kernel(const bf16 * __restr
 template <int R>
 __global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_ml, int n_splits, int H,
                                         bf16 * __restrict__ o_lat) {
+    // n_splits <= 32: warp 0 turns the (m, l) pairs into normalised weights, then every thread sums its
+    // dims over the splits with independent loads.
+    __shared__ float wsm[32];
     const int t = blockIdx.x, h = blockIdx.y;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(((size_t) t * n_splits + s) * H + h) * 2]);
-    float L = 0.f;
-    if (M > -INFINITY)
-        for (int s = 0; s < n_splits; ++s) {
+    if (threadIdx.x < 32) {
+        const int s = threadIdx.x;
+        float m = -INFINITY, l = 0.f;
+        if (s < n_splits) {
             const size_t pidx = ((size_t) t * n_splits + s) * H + h;
-            const float l = part_ml[pidx * 2 + 1];
-            if (l > 0.f) L += l * __expf(part_ml[pidx * 2] - M);
+            m = part_ml[pidx * 2];
+            l = part_ml[pidx * 2 + 1];
         }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int i = threadIdx.x; i < R; i += blockDim.x) {
-        float acc = 0.f;
-        if (L > 0.f)
-            for (int s = 0; s < n_splits; ++s) {
-                const size_t pidx = ((size_t) t * n_splits + s) * H + h;
-                if (part_ml[pidx * 2 + 1] > 0.f) acc += __expf(part_ml[pidx * 2] - M) * part_o[pidx * R + i];
+        float M = m;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float w = (l > 0.f && M > -INFINITY) ? __expf(m - M) : 0.f;
+        float L = l * w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        wsm[s] = L > 0.f ? w / L : 0.f;
+    }
+    __syncthreads();
+    // float4 per thread, 8 splits unrolled: enough independent loads in flight to cover L2 latency
+    for (int i = threadIdx.x * 4; i < R; i += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int s = 0; s < n_splits; ++s) {
+            const float w = wsm[s];
+            const float4 v = *(const float4 *) (part_o + (((size_t) t * n_splits + s) * H + h) * R + i);
+            if (w > 0.f) {                       // empty splits never wrote part_o
+                acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
             }
-        o_lat[((size_t) t * H + h) * R + i] = __float2bfloat16(acc * inv);
+        }
+        __nv_bfloat162 * po = (__nv_bfloat162 *) (o_lat + ((size_t) t * H + h) * R + i);
+        po[0] = __floats2bfloat162_rn(acc.x, acc.y);
+        po[1] = __floats2bfloat162_rn(acc.z, acc.w);
     }
 }
 

@@ -23,34 +23,73 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// One block per token.  smem: g as fp32 [d], logits/probs [E].
-template <int NT>
-__global__ void __launch_bounds__(NT) moe_gate_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
-                                                      const float * __restrict__ bias, int * __restrict__ ids, float * __restrict__ wts,
-                                                      int d, int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid) {
-    extern __shared__ float sm[];
-    float * xs = sm;              // [d]
+// Router logits in fp32: logits[t][e] = sum_i g[t][i] * w_router[e][i].
+// grid (E, ceil(T/64)), 256 threads: one expert per CTA, the d axis spread over all threads (its router row
+// slice stays in registers), tokens walked in groups of 8 so that every load of a group is independent —
+// the kernel is latency-bound, so memory-level parallelism is what matters.
+constexpr int GATE_TG = 8;
+constexpr int GATE_NT = 256;
+constexpr int GATE_MAXV = 8;      // float4 slices per thread: d <= 8 * 256 * 4 = 8192
+__global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
+                                                                float * __restrict__ logits, int T, int d, int E) {
+    __shared__ float red[GATE_NT / 32][GATE_TG];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x;
+    const int nv = d / 4;
+    const float4 * wr = (const float4 *) (w_router + (size_t) e * d);
+    float4 w[GATE_MAXV];
+#pragma unroll
+    for (int v = 0; v < GATE_MAXV; ++v) {
+        const int i = threadIdx.x + v * GATE_NT;
+        w[v] = i < nv ? wr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int t_end = min(T, (int) (blockIdx.y + 1) * 64);
+    for (int t0 = blockIdx.y * 64; t0 < t_end; t0 += GATE_TG) {
+        float acc[GATE_TG];
+#pragma unroll
+        for (int j = 0; j < GATE_TG; ++j) acc[j] = 0.f;
+#pragma unroll
+        for (int v = 0; v < GATE_MAXV; ++v) {
+            const int i = threadIdx.x + v * GATE_NT;
+            if (i < nv) {
+#pragma unroll
+                for (int j = 0; j < GATE_TG; ++j) {
+                    const int t = min(t0 + j, T - 1);
+                    const uint2 raw = *(const uint2 *) (g + (size_t) t * d + 4 * i);
+                    const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                    const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                    acc[j] += w[v].x * a.x + w[v].y * a.y + w[v].z * b.x + w[v].w * b.y;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < GATE_TG; ++j) {
+            const float s = warp_sum(acc[j]);
+            if (lane == 0) red[warp][j] = s;
+        }
+        __syncthreads();
+        if (threadIdx.x < GATE_TG && t0 + threadIdx.x < t_end) {
+            float s = 0.f;
+#pragma unroll
+            for (int q = 0; q < GATE_NT / 32; ++q) s += red[q][threadIdx.x];
+            logits[(size_t) (t0 + threadIdx.x) * E + e] = s;
+        }
+        __syncthreads();
+    }
+}
+
+// One warp per token: softmax/sigmoid over the logits, optional group-limited masking, k rounds of arg-max.
+__global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__ logits, const float * __restrict__ bias,
+                                                      int * __restrict__ ids, float * __restrict__ wts, int E, int k, int n_group,
+                                                      int topk_group, float scale, int norm, int sigmoid) {
     __shared__ float prob[MAX_E];
     __shared__ float sel[MAX_E];
     __shared__ float gscore[32];
     const int t = blockIdx.x;
-    const bf16 * row = g + (size_t) t * d;
-    for (int i = threadIdx.x; i < d; i += NT) xs[i] = __bfloat162float(row[i]);
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = warp; e < E; e += NT / 32) {
-        const float4 * wr = (const float4 *) (w_router + (size_t) e * d);
-        float acc = 0.f;
-        for (int i = lane; i < d / 4; i += 32) {
-            const float4 w = wr[i];
-            const float4 x = ((const float4 *) xs)[i];
-            acc += w.x * x.x + w.y * x.y + w.z * x.z + w.w * x.w;
-        }
-        acc = warp_sum(acc);
-        if (lane == 0) prob[e] = acc;
-    }
-    __syncthreads();
-    if (warp == 0) {
+    const int lane = threadIdx.x;
+    for (int e = lane; e < E; e += 32) prob[e] = logits[(size_t) t * E + e];
+    __syncwarp();
+    {
         // softmax / sigmoid over E (E <= 256 -> 8 per lane)
         float mx = -FLT_MAX;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
@@ -221,18 +260,13 @@ inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAU
 
 extern "C" {
 
-int jib_moe_gate(const void * g, const float * w_router, const float * bias, int * ids, float * wts, int T, int d, int E, int k,
-                 int n_group, int topk_group, float scale, int norm, int sigmoid, void * stream) {
+int jib_moe_gate(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int T, int d,
+                 int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, void * stream) {
     if (T <= 0) return 0;
-    if (E > MAX_E || k > 32 || k > E || d % 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
-    static bool attr = false;
-    const size_t smem = (size_t) d * sizeof(float);
-    if (!attr && smem > 48 * 1024) {
-        cudaFuncSetAttribute(moe_gate_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        attr = true;
-    }
-    moe_gate_kernel<256><<<T, 256, smem, (cudaStream_t) stream>>>((const bf16 *) g, w_router, bias, ids, wts, d, E, k, n_group, topk_group,
-                                                                   scale, norm, sigmoid);
+    if (E > MAX_E || k > 32 || k > E || d % 4 || d > GATE_MAXV * GATE_NT * 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
+    router_logits_kernel<<<dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream>>>((const bf16 *) g, w_router, logits, T, d, E);
+    if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;
+    moe_gate_kernel<<<T, 32, 0, (cudaStream_t) stream>>>(logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid);
     return launched();
 }
 

@@ -242,6 +242,6 @@ class DeepSeek2Model:
             y = self._row_parallel(a, L.w_o, x)
             g, _ = ops.rmsnorm(y, L.ffn_norm, hp.rms_eps)
             x = self._mlp(L, g, y)
-        xo = x[batch.out_rows.long()] if batch.out_rows is not None else x
-        xo, _ = ops.rmsnorm(xo.contiguous(), self.out_norm, hp.rms_eps)
+        xo = ops.select_rows(x, batch.out_rows) if batch.out_rows is not None else x
+        xo, _ = ops.rmsnorm(xo, self.out_norm, hp.rms_eps)
         return ops.linear(xo, self.w_out, out_dtype=torch.float32)

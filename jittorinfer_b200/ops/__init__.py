@@ -45,6 +45,13 @@ def embed_gather(table, ids):
     return nat().embed_gather(table, ids) if use_native(table) else ref.embed_gather(table, ids)
 
 
+def select_rows(x, rows):
+    """x[rows] (the reference's inp_out_ids row selection, src/llama-graph-deepseek2.cpp:302-308)."""
+    if use_native(x) and x.dtype == torch.bfloat16:
+        return nat().gather_rows(x, rows)
+    return x[rows.long()].contiguous()
+
+
 def rmsnorm(x, w, eps, residual=None):
     return nat().rmsnorm(x, w, eps, residual) if use_native(x) else ref.rmsnorm(x, w, eps, residual)
 

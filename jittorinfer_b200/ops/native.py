@@ -52,8 +52,8 @@ def load():
     sig("jib_argmax", fp, ip, i, i, vp)
     sig("jib_topk", fp, fp, ip, i, i, i, vp)
     sig("jib_kv_block_copy", vp, ll, i, ip, ip, i, i, vp)
-    sig("jib_gather_rows", vp, ip, vp, i, i, vp)
-    sig("jib_moe_gate", vp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, vp)
+    sig("jib_gather_rows", vp, ip, vp, i, i, i, vp)
+    sig("jib_moe_gate", vp, fp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, vp)
     sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
     sig("jib_mla_attention", vp, vp, ip, i, ip, ip, i, i, i, i, i, i, f, i, fp, fp, vp, vp)
@@ -229,7 +229,7 @@ def v_up(o_lat, w_uv):
 def attn_splits(T: int, H: int, sm_count: int = 148) -> int:
     """Split count for the decode kernel: enough CTAs to cover the machine about twice."""
     per = max(1, T * max(1, H // 16))
-    return max(1, min(32, (2 * sm_count + per - 1) // per))
+    return max(1, min(32, sm_count // per))
 
 
 def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size, max_q_len=None, meta=None):
@@ -254,8 +254,9 @@ def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid):
     E = w_router.shape[0]
     ids = torch.empty(T, k, dtype=torch.int32, device=g.device)
     wts = torch.empty(T, k, dtype=torch.float32, device=g.device)
-    _ck(load().jib_moe_gate(g.data_ptr(), w_router.data_ptr(), _p(bias), ids.data_ptr(), wts.data_ptr(), T, d, E, k, n_group,
-                            topk_group, float(scale), int(norm), int(sigmoid), _stream()), "moe_gate")
+    logits = torch.empty(T, E, dtype=torch.float32, device=g.device)
+    _ck(load().jib_moe_gate(g.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, d,
+                            E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), _stream()), "moe_gate")
     return ids, wts
 
 
@@ -273,7 +274,7 @@ def moe_permute(ids, expert_base, E_local):
 def gather_rows(x, src_row):
     R, d = src_row.shape[0], x.shape[1]
     out = torch.empty(R, d, dtype=x.dtype, device=x.device)
-    _ck(load().jib_gather_rows(x.data_ptr(), src_row.data_ptr(), out.data_ptr(), R, d, _stream()), "gather_rows")
+    _ck(load().jib_gather_rows(x.data_ptr(), src_row.data_ptr(), out.data_ptr(), R, d, x.shape[0], _stream()), "gather_rows")
     return out
 
 

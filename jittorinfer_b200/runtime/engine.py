@@ -263,8 +263,8 @@ class LLMEngine:
                 h["q_start"][n_seqs:bucket + 1] = np.arange(n_seqs, bucket + 1)
                 h["out_rows"][n_out:bucket] = np.arange(n_out, bucket)
                 h["block_tables"][n_seqs * self.max_blocks: bucket * self.max_blocks] = 0
+            io.upload()                      # before a first-use capture too: its warm-up runs read these buffers
             g, out = self._graph_for(bucket, mode)
-            io.upload()
             g.replay()
             self.launches += self.graph_launches.get((bucket, mode), 0)
             self.stats["graph_steps"] += 1
