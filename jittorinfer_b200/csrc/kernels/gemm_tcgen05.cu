@@ -430,3 +430,122 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     }
 #undef JIB_LAUNCH
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in jib_noalloc.h).
+//
+// The split-K scratch is this file-scope device array.  In host code its name is only a handle for the
+// runtime, not an address a kernel could use: the device address is obtained once per device with
+// cudaGetSymbolAddress (that device current) and passed to the kernel like any other pointer.
+// Layout: [partials: JIB_NOALLOC_SCRATCH_BYTES][tile counters: JIB_NOALLOC_MAX_TILES ints][status: 4 ints].
+// ---------------------------------------------------------------------------------------------
+#include "jib_noalloc.h"
+
+static __device__ __align__(256) unsigned char jib_noalloc_scratch[JIB_NOALLOC_SCRATCH_BYTES + JIB_NOALLOC_MAX_TILES * sizeof(int) + 256];
+
+namespace {
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char * g_noalloc_base[NOALLOC_MAX_DEVICES] = {nullptr};
+std::mutex g_noalloc_mu;
+
+// Device address of the built-in scratch for the current device; looked up on first use.
+int noalloc_base(unsigned char ** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return JIB_E_ARG;
+    std::lock_guard<std::mutex> g(g_noalloc_mu);
+    if (g_noalloc_base[dev] == nullptr) {
+        void * p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, jib_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) return JIB_E_DRIVER;
+        g_noalloc_base[dev] = (unsigned char *) p;
+    }
+    *out = g_noalloc_base[dev];
+    return 0;
+}
+
+struct NoallocPlan {
+    int bn, n_tiles, num_kb, splits, kbps;
+    size_t need;
+};
+
+NoallocPlan noalloc_plan(int T, int N, int K, int splits) {
+    NoallocPlan p;
+    p.bn = 16;
+    while (p.bn < T && p.bn < 256) p.bn *= 2;
+    p.n_tiles = (N + BM - 1) / BM;
+    p.num_kb = (K + BK - 1) / BK;
+    if (splits <= 0) {                       // same rule as jib_gemm_bf16 for a 148-SM part
+        splits = 1;
+        const int slots = 148 * (p.bn <= 32 ? 2 : 1);
+        if (2 * p.n_tiles <= slots) {
+            splits = slots / p.n_tiles;
+            if (splits > p.num_kb / 4) splits = p.num_kb / 4;
+            if (splits < 1) splits = 1;
+        }
+    }
+    if (splits > p.num_kb) splits = p.num_kb;
+    p.kbps = (p.num_kb + splits - 1) / splits;
+    p.splits = (p.num_kb + p.kbps - 1) / p.kbps;
+    p.need = p.splits > 1 ? (size_t) p.n_tiles * p.splits * p.bn * BM * sizeof(float) : 0;
+    return p;
+}
+
+// Tensor map built straight into caller storage (no cache, no host allocation).
+int encode_plain(CUtensorMap * out, const void * ptr, long long rows, long long cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return JIB_E_DRIVER;
+    if (((uintptr_t) ptr & 15) || (cols * 2) % 16) return JIB_E_ALIGN;
+    cuuint64_t dims[3] = {(cuuint64_t) cols, (cuuint64_t) rows, 1};
+    cuuint64_t strides[2] = {(cuuint64_t) cols * 2, (cuuint64_t) rows * cols * 2};
+    cuuint32_t box[3] = {(cuuint32_t) BK, (cuuint32_t) box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : JIB_E_TENSORMAP;
+}
+
+}  // namespace
+
+extern "C" JIB_EXPORT size_t jib_gemm_bf16_noalloc_need(int T, int N, int K, int splits) {
+    if (T <= 0 || N <= 0 || K <= 0) return 0;
+    return noalloc_plan(T, N, K, splits).need;
+}
+
+extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, void * out, int T, int N, int K, int splits,
+                                                void * stream_) {
+    cudaStream_t stream = (cudaStream_t) stream_;
+    if (T <= 0 || N <= 0 || K <= 0) return 0;
+    if (T > 256 || x == nullptr || w == nullptr || out == nullptr) return JIB_E_ARG;
+    const NoallocPlan p = noalloc_plan(T, N, K, splits);
+    if (p.need > JIB_NOALLOC_SCRATCH_BYTES || p.n_tiles > JIB_NOALLOC_MAX_TILES) return JIB_E_NOALLOC_TOO_LARGE;
+    unsigned char * base = nullptr;
+    int rc = noalloc_base(&base);            // first call on this device: symbol lookup (keep it outside stream capture)
+    if (rc) return rc;
+    int * counters = (int *) (base + JIB_NOALLOC_SCRATCH_BYTES);
+    int * status = counters + JIB_NOALLOC_MAX_TILES;
+    // the array keeps whatever the previous call left: counters (and the status words) must start at zero
+    if (cudaMemsetAsync(counters, 0, (size_t) p.n_tiles * sizeof(int), stream) != cudaSuccess) return JIB_E_LAUNCH;
+    if (cudaMemsetAsync(status, 0, 4 * sizeof(int), stream) != cudaSuccess) return JIB_E_LAUNCH;
+
+    CUtensorMap ma, mb;
+    rc = encode_plain(&ma, w, N, K, BM);
+    if (rc) return rc;
+    rc = encode_plain(&mb, x, T, K, p.bn);
+    if (rc) return rc;
+    GemmArgs a;
+    a.out = out; a.residual = nullptr; a.seg = nullptr; a.scratch = (float *) base; a.counters = counters; a.status = status;
+    a.ldo = N; a.out_batch_stride = 0; a.ldr = 0; a.res_batch_stride = 0; a.T = T; a.N = N; a.K = K; a.splits = p.splits;
+    a.kb_per_split = p.kbps; a.out_f32 = 0; a.res_f32 = 0; a.rows_total = T;
+    a.scratch_elems = (long long) (JIB_NOALLOC_SCRATCH_BYTES / sizeof(float));
+    dim3 grid(p.n_tiles, 1, p.splits);
+    switch (p.bn) {
+        case 16: return launch<16, false>(ma, ma, mb, a, grid, stream);
+        case 32: return launch<32, false>(ma, ma, mb, a, grid, stream);
+        case 64: return launch<64, false>(ma, ma, mb, a, grid, stream);
+        case 128: return launch<128, false>(ma, ma, mb, a, grid, stream);
+        case 256: return launch<256, false>(ma, ma, mb, a, grid, stream);
+        default: return JIB_E_ARG;
+    }
+}
