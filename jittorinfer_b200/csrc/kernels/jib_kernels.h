@@ -79,6 +79,13 @@ JIB_EXPORT int jib_mla_attention(const void * q, const void * cache, const int *
                                  const int * q_start, int n_seqs, int T, int H, int r, int dr, int block_size, float scale,
                                  int n_splits, float * part_o, float * part_ml, void * o_lat, void * stream);
 
+JIB_EXPORT int jib_mla_combine(const float * part_o, const float * part_ml, int n_splits, int T, int H, int r, void * o_lat,
+                               void * stream);
+// tcgen05 flash MLA (mla_flash_tcgen05.cu): r = 512, dr = 64, block size 64 only; qt = query tokens per CTA (1 or 2).
+JIB_EXPORT int jib_mla_flash(const void * q, const void * cache, long long n_slots, const int * block_tables, int max_blocks,
+                             const int * seq_lens, const int * q_start, int n_seqs, int T, int H, float scale, int n_splits, int qt,
+                             float * part_o, float * part_ml, void * o_lat, int * status, void * stream);
+
 #ifdef __cplusplus
 }
 #endif

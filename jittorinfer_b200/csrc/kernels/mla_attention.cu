@@ -246,3 +246,15 @@ extern "C" int jib_mla_attention(const void * q, const void * cache, const int *
 #undef JIB_MLA_CASE
     return JIB_E_ARG;
 }
+
+// Merge of split-KV partials (m, l, o) written by either attention kernel.  r in {512, 64}.
+extern "C" int jib_mla_combine(const float * part_o, const float * part_ml, int n_splits, int T, int H, int r, void * o_lat,
+                               void * stream) {
+    if (T <= 0) return 0;
+    if (n_splits < 1 || n_splits > 32) return JIB_E_ARG;
+    cudaStream_t s = (cudaStream_t) stream;
+    if (r == 512) mla_attn_combine_kernel<512><<<dim3(T, H), 128, 0, s>>>(part_o, part_ml, n_splits, H, (bf16 *) o_lat);
+    else if (r == 64) mla_attn_combine_kernel<64><<<dim3(T, H), 128, 0, s>>>(part_o, part_ml, n_splits, H, (bf16 *) o_lat);
+    else return JIB_E_ARG;
+    return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
+}

@@ -57,6 +57,8 @@ def load():
     sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
     sig("jib_mla_attention", vp, vp, ip, i, ip, ip, i, i, i, i, i, i, f, i, fp, fp, vp, vp)
+    sig("jib_mla_combine", fp, fp, i, i, i, i, vp, vp)
+    sig("jib_mla_flash", vp, vp, ll, ip, i, ip, ip, i, i, i, f, i, i, fp, fp, vp, ip, vp)
     _lib = L
     return L
 
@@ -232,11 +234,30 @@ def attn_splits(T: int, H: int, sm_count: int = 148) -> int:
     return max(1, min(32, sm_count // per))
 
 
+ATTN_IMPL = os.environ.get("JITTORINFER_ATTN", "flash")      # "flash" (tcgen05) | "simt" (CUDA-core kernel)
+
+
 def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size, max_q_len=None, meta=None):
     T, H, D = q.shape
     n_seqs = seq_lens.shape[0]
-    n_splits = 1 if (max_q_len or 1) > 1 and T > 64 else attn_splits(T, H)
+    prefill = (max_q_len or 1) > 1
     o = torch.empty(T, H, r, dtype=q.dtype, device=q.device)
+    if ATTN_IMPL == "flash" and r == 512 and D == 576 and block_size == 64 and cache.shape[0] % 64 == 0:
+        qt = 2 if prefill else 1
+        n_splits = 1 if prefill else attn_splits(T, H)
+        part_o = part_ml = None
+        if n_splits > 1:
+            part_o = torch.empty(T, n_splits, H, r, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(T, n_splits, H, 2, dtype=torch.float32, device=q.device)
+        ws = workspace(q.device)
+        _ck(load().jib_mla_flash(q.data_ptr(), cache.data_ptr(), cache.shape[0], block_tables.data_ptr(), block_tables.stride(0),
+                                 seq_lens.data_ptr(), q_start.data_ptr(), n_seqs, T, H, float(scale), n_splits, qt, _p(part_o),
+                                 _p(part_ml), o.data_ptr(), ws.status.data_ptr(), _stream()), "mla_flash")
+        if n_splits > 1:
+            _ck(load().jib_mla_combine(part_o.data_ptr(), part_ml.data_ptr(), n_splits, T, H, r, o.data_ptr(), _stream()),
+                "mla_combine")
+        return o
+    n_splits = 1 if prefill and T > 64 else attn_splits(T, H)
     if n_splits > 1:
         part_o = torch.empty(T, n_splits, H, r, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(T, n_splits, H, 2, dtype=torch.float32, device=q.device)

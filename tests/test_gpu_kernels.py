@@ -167,10 +167,11 @@ def test_mla_qkv_post_and_embed(nat):
 
 
 @pytest.mark.parametrize("r,dr,H", [(512, 64, 16), (64, 16, 16), (512, 64, 32), (64, 16, 4)])
-@pytest.mark.parametrize("lens,qlens", [([1], [1]), ([70, 300, 5, 129], [1, 1, 1, 1]), ([40, 200], [40, 73]), ([0, 33], [1, 1])])
+@pytest.mark.parametrize("lens,qlens", [([1], [1]), ([70, 300, 5, 129], [1, 1, 1, 1]), ([40, 200], [40, 73]), ([0, 33], [1, 1]),
+                                        ([41, 200, 7], [41, 73, 1]), ([1000, 1500, 129, 64, 1], [1, 1, 1, 1, 1]), ([700], [300])])
 def test_mla_attention(nat, r, dr, H, lens, qlens):
     bs = 64
-    nb_per = 8
+    nb_per = 24
     B = len(lens)
     cache = rnd(B * nb_per * bs, r + dr)
     g = torch.Generator().manual_seed(7)
