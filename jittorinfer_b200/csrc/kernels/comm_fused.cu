@@ -1,0 +1,127 @@
+// Peer-memory collectives over NVLink / NVSwitch issued from inside kernels: no NCCL on these paths.
+//
+// The reference's only device collective is a blocking HcclAllReduce (fp32) after o_proj and after the
+// FFN/MoE block, 120 times per decoded token for DeepSeek-V2 (ggml/src/ggml-cann/aclnn_ops.cpp:522-536;
+// src/llama-graph-deepseek2.cpp:294-297, 365-368).  Here each rank owns a buffer that every peer maps through
+// CUDA IPC ("symmetric" layout: same offsets on every rank) and the reduction is one-shot:
+//   push   every rank stores its fp32 partial rows into slot [my_rank] of every peer's receive buffer,
+//   signal st.release.sys of the step epoch into a per-(site, source, tile) flag on the peer,
+//   wait   ld.acquire.sys spin on the local flags of all sources — bounded; on expiry a status word is set,
+//   reduce sum the slots in rank order (bitwise identical on every rank), add the residual, store bf16.
+// The same push/wait/reduce sequence is the epilogue of the tcgen05 GEMM (gemm_tcgen05.cu, args.ar) so that the
+// transfer of one tile overlaps the MMA work of the others; this file holds the stand-alone all-reduce used
+// after the MoE combine, the epoch kernel and the IPC plumbing.
+//
+// Flags are never reset: they carry the step epoch, a device-side counter bumped once per forward pass, and
+// each collective call site of the model owns its own flag rows.  Receive buffers are double-buffered by the
+// parity of (site + epoch * n_sites): consecutive collectives always use different halves, so a fast rank
+// cannot overwrite data a slow rank is still reducing.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "comm_fused.cuh"
+#include "jib_kernels.h"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__global__ void epoch_bump_kernel(unsigned * epoch) { *epoch += 1; }
+
+// One CTA per (8 rows, 512 features).  x: fp32 or bf16 partial [T][d]; out bf16 [T][d] = sum over ranks + residual.
+template <typename TIn>
+__global__ void __launch_bounds__(128) allreduce_oneshot_kernel(const TIn * __restrict__ x, const bf16 * __restrict__ residual,
+                                                                bf16 * __restrict__ out, int T, int d, JibArCtx ar, int site) {
+    const unsigned epoch = *ar.epoch;
+    const int parity = (site + (int) (epoch % 2u) * (ar.n_sites & 1)) & 1;
+    const int f0 = blockIdx.x * 512, r0 = blockIdx.y * 8;
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    const int f = f0 + threadIdx.x * 4;
+    const int rows = min(8, T - r0);
+    const size_t half = (size_t) ar.world * ar.max_rows * ar.d_max;        // floats per parity half
+    if (f < d) {       // push my partial into slot [rank] of every peer
+        for (int j = 0; j < rows; ++j) {
+            float4 v;
+            if (sizeof(TIn) == 4) {
+                v = *(const float4 *) ((const float *) x + (size_t) (r0 + j) * d + f);
+            } else {
+                const uint2 raw = *(const uint2 *) ((const bf16 *) x + (size_t) (r0 + j) * d + f);
+                const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                v = make_float4(a.x, a.y, b.x, b.y);
+            }
+            const size_t off = (size_t) parity * half + ((size_t) ar.rank * ar.max_rows + (r0 + j)) * ar.d_max + f;
+            for (int p = 0; p < ar.world; ++p) *(float4 *) (ar.recv[p] + off) = v;
+        }
+    }
+    jib_ar_signal_and_wait(ar, site, tile, epoch, 128, (int) threadIdx.x);
+    if (f < d) {       // reduce in rank order
+        for (int j = 0; j < rows; ++j) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < ar.world; ++s) {
+                const float4 v = jib_ld_cg4(ar.recv[ar.rank] + (size_t) parity * half + ((size_t) s * ar.max_rows + (r0 + j)) * ar.d_max + f);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            if (residual) {
+                const uint2 raw = *(const uint2 *) (residual + (size_t) (r0 + j) * d + f);
+                const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+            }
+            uint2 o;
+            *(__nv_bfloat162 *) &o.x = __floats2bfloat162_rn(acc.x, acc.y);
+            *(__nv_bfloat162 *) &o.y = __floats2bfloat162_rn(acc.z, acc.w);
+            *(uint2 *) (out + (size_t) (r0 + j) * d + f) = o;
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---- IPC plumbing (cudaMalloc'd buffers exchanged as 64-byte handles by the Python side) --------------------
+JIB_EXPORT int jib_symm_alloc(size_t bytes, void ** ptr_out, void * handle_out /*64 bytes*/) {
+    void * p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) return JIB_E_LAUNCH;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess) return JIB_E_LAUNCH;
+    if (cudaDeviceSynchronize() != cudaSuccess) return JIB_E_LAUNCH;
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) return JIB_E_DRIVER;
+    memcpy(handle_out, &h, sizeof(h));
+    *ptr_out = p;
+    return 0;
+}
+JIB_EXPORT int jib_symm_open(const void * handle, void ** ptr_out) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void * p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return JIB_E_DRIVER;
+    *ptr_out = p;
+    return 0;
+}
+JIB_EXPORT int jib_symm_close(void * ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : JIB_E_DRIVER; }
+JIB_EXPORT int jib_symm_free(void * ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : JIB_E_DRIVER; }
+
+JIB_EXPORT int jib_ar_epoch_bump(unsigned * epoch, void * stream) {
+    epoch_bump_kernel<<<1, 1, 0, (cudaStream_t) stream>>>(epoch);
+    return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
+}
+
+// Stand-alone one-shot all-reduce of a [T][d] partial (fp32 or bf16) + residual -> bf16.
+JIB_EXPORT int jib_allreduce_oneshot(const void * x, int x_f32, const void * residual, void * out, int T, int d, const JibArCtx * ar,
+                                     int site, void * stream) {
+    if (T <= 0) return 0;
+    if (d % 4 || d > ar->d_max || T > ar->max_rows || site < 0 || site >= ar->n_sites) return JIB_E_ARG;
+    dim3 grid((d + 511) / 512, (T + 7) / 8);
+    if ((int) (grid.x * grid.y) > ar->max_tiles) return JIB_E_ARG;
+    if (x_f32)
+        allreduce_oneshot_kernel<float><<<grid, 128, 0, (cudaStream_t) stream>>>((const float *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
+    else
+        allreduce_oneshot_kernel<bf16><<<grid, 128, 0, (cudaStream_t) stream>>>((const bf16 *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
+    return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
+}
+
+}  // extern "C"

@@ -27,6 +27,7 @@
 #include <vector>
 #include <string.h>
 
+#include "comm_fused.cuh"
 #include "jib_kernels.h"
 
 using namespace sm100;
@@ -51,6 +52,8 @@ struct GemmArgs {
     int out_f32, res_f32;
     long long rows_total;     // rows of out (all batches of a grouped launch share them); stores beyond are refused
     long long scratch_elems;
+    JibArCtx ar;              // peer-memory all-reduce fused into the epilogue (ar_on != 0)
+    int ar_on, ar_site;
 };
 
 template <int BN, bool DUAL>
@@ -213,6 +216,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (do_final && acc_ok) {
             const long long obase = (long long) batch * args.out_batch_stride;
             const long long rbase = (long long) batch * args.res_batch_stride;
+            // fused all-reduce: the tile's fp32 values go to slot [rank] of every peer instead of `out`
+            unsigned ar_epoch = 0;
+            size_t ar_par = 0;
+            if (args.ar_on) {
+                ar_epoch = *args.ar.epoch;
+                const size_t ar_half = (size_t) args.ar.world * args.ar.max_rows * args.ar.d_max;
+                ar_par = (size_t) ((args.ar_site + (int) (ar_epoch % 2u) * (args.ar.n_sites & 1)) & 1) * ar_half;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 if (row0 + c >= rows_valid) break;
@@ -249,6 +260,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         float y = DUAL ? silu(g[j]) * u[j] : g[j];
                         const long long row = row_base + t;
                         if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 5, (int) row); break; }
+                        if (args.ar_on) {
+                            const size_t off = ar_par + ((size_t) args.ar.rank * args.ar.max_rows + row) * args.ar.d_max + n;
+                            for (int p = 0; p < args.ar.world; ++p) args.ar.recv[p][off] = y;
+                            continue;
+                        }
+                        if (args.residual != nullptr) {
+                            const long long ri = rbase + row * args.ldr + n;
+                            y += args.res_f32 ? ((const float *) args.residual)[ri]
+                                              : __bfloat162float(((const __nv_bfloat16 *) args.residual)[ri]);
+                        }
+                        const long long oi = obase + row * args.ldo + n;
+                        if (args.out_f32) ((float *) args.out)[oi] = y;
+                        else ((__nv_bfloat16 *) args.out)[oi] = __float2bfloat16(y);
+                    }
+                }
+            }
+            if (args.ar_on) {
+                // signal every peer, wait (bounded) for every source, then sum the slots in rank order
+                jib_ar_signal_and_wait(args.ar, args.ar_site, tile_id, ar_epoch, 128, (int) threadIdx.x - 64);
+                if (n < args.N) {
+                    const int t_end = min(rows_valid, row0 + BN);
+                    for (int t = row0; t < t_end; ++t) {
+                        const long long row = row_base + t;
+                        float y = 0.f;
+                        for (int s = 0; s < args.ar.world; ++s)
+                            y += __ldcg(args.ar.recv[args.ar.rank] + ar_par + ((size_t) s * args.ar.max_rows + row) * args.ar.d_max + n);
                         if (args.residual != nullptr) {
                             const long long ri = rbase + row * args.ldr + n;
                             y += args.res_f32 ? ((const float *) args.residual)[ri]
@@ -413,6 +450,15 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     a.out_f32 = d->out_f32; a.res_f32 = d->res_f32;
     a.rows_total = grouped ? d->x_rows_total : d->T;
     a.scratch_elems = (long long) (d->scratch_bytes / sizeof(float));
+    a.ar_on = 0; a.ar_site = 0;
+    memset(&a.ar, 0, sizeof(a.ar));
+    if (d->ar != nullptr) {
+        const JibArCtx * ar = (const JibArCtx *) d->ar;
+        if (dual || grouped || batch != 1 || d->N > ar->d_max || d->T > ar->max_rows || n_tiles * t_tiles > ar->max_tiles ||
+            d->ar_site < 0 || d->ar_site >= ar->n_sites)
+            return JIB_E_ARG;
+        a.ar = *ar; a.ar_on = 1; a.ar_site = d->ar_site;
+    }
     dim3 grid(n_tiles, t_tiles, batch * splits);
 #define JIB_LAUNCH(BN_)                                                                           \
     case BN_:                                                                                     \
@@ -539,6 +585,8 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.ldo = N; a.out_batch_stride = 0; a.ldr = 0; a.res_batch_stride = 0; a.T = T; a.N = N; a.K = K; a.splits = p.splits;
     a.kb_per_split = p.kbps; a.out_f32 = 0; a.res_f32 = 0; a.rows_total = T;
     a.scratch_elems = (long long) (JIB_NOALLOC_SCRATCH_BYTES / sizeof(float));
+    a.ar_on = 0; a.ar_site = 0;
+    memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);
     switch (p.bn) {
         case 16: return launch<16, false>(ma, ma, mb, a, grid, stream);

@@ -44,6 +44,8 @@ typedef struct jib_gemm_desc {
     int splits;                // 0 = choose
     int bn;                    // 0 = choose; token-tile width 16/32/64/128/256
     int sm_count;
+    int ar_site;               // fused all-reduce: call-site index (see comm_fused.cu)
+    const void * ar;           // NULL, or a JibArCtx: the epilogue sums the tile over all ranks through peer memory
 } jib_gemm_desc;
 
 JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);

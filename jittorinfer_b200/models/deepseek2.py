@@ -227,7 +227,7 @@ class DeepSeek2Model:
         if self.comm is not None and self.spec.sharded:
             part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                                L.w_down_sh, base)
-            return self.comm.all_reduce(part) + residual
+            return self.comm.all_reduce(part, residual)
         return ops.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                            L.w_down_sh, base)
 
@@ -235,6 +235,8 @@ class DeepSeek2Model:
     def forward(self, batch: ForwardBatch, kv_cache: torch.Tensor) -> torch.Tensor:
         """kv_cache [n_layer, n_slots, r+dr].  Returns fp32 logits [len(out_rows), n_vocab]."""
         hp = self.hp
+        if self.comm is not None:
+            self.comm.begin_step()
         x = ops.embed_gather(self.tok_embd, batch.tokens)
         for il, L in enumerate(self.layers):
             h, _ = ops.rmsnorm(x, L.attn_norm, hp.rms_eps)

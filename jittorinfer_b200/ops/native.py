@@ -26,7 +26,7 @@ class GemmDesc(C.Structure):
                                             "out_batch_stride", "ldr", "res_batch_stride", "x_rows_total")] + \
                [("scratch_bytes", C.c_size_t)] + \
                [(n, C.c_int) for n in ("n_counters", "T", "N", "K", "batch", "max_rows", "active_hint", "out_f32", "res_f32",
-                                       "splits", "bn", "sm_count")]
+                                       "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p)]
 
 
 def load():
@@ -116,8 +116,8 @@ def _p(t: Optional[torch.Tensor]) -> Optional[int]:
 
 # ---- GEMM family ---------------------------------------------------------------------------------
 def gemm(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, *, out: Optional[torch.Tensor] = None,
-         residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, splits: int = 0, bn: int = 0
-         ) -> torch.Tensor:
+         residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, splits: int = 0, bn: int = 0,
+         ar=None, ar_site: int = 0) -> torch.Tensor:
     """out[T,N] = x[T,K] @ w[N,K]^T  (w2: silu(x w^T) * (x w2^T)) (+ residual)."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(-1) == 1 and w.is_contiguous()
     T, K = x.shape
@@ -137,6 +137,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, *,
     d.out_f32 = int(out.dtype == torch.float32)
     d.res_f32 = int(residual is not None and residual.dtype == torch.float32)
     d.splits, d.bn, d.sm_count = splits, bn, ws.sm_count
+    if ar is not None:          # fused one-shot all-reduce over peer memory in the epilogue
+        d.ar, d.ar_site = C.addressof(ar), ar_site
     _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm")
     return out
 

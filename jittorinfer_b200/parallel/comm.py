@@ -1,0 +1,175 @@
+"""Tensor/expert-parallel communicators.
+
+The reference's data plane is one blocking ``HcclAllReduce`` (fp32) after ``o_proj`` and one after
+the FFN/MoE block of every layer (src/llama-graph-deepseek2.cpp:294-297, 365-368;
+ggml/src/ggml-cann/aclnn_ops.cpp:522-536), bootstrapped over MPI
+(src/llama-context-load-utils.cpp:346-434).  Two implementations of the same interface:
+
+* :class:`Communicator` — ``torch.distributed`` all-reduce (NCCL on GPUs, gloo on CPU).  This is
+  the *baseline*, and the path for CPU tests and for batches too large for the one-shot buffers.
+* :class:`FusedCommunicator` — the product path: every rank maps every peer's receive buffer and
+  flag array through CUDA IPC; the row-parallel GEMMs push their tiles to the peers from the tcgen05
+  epilogue and reduce in the same kernel (``jib_gemm_bf16`` with ``ar``), and the MoE partial sum
+  uses the stand-alone one-shot kernel.  ``torch.distributed`` is used once, to exchange the IPC
+  handles.
+
+Both return bitwise identical results on every rank (slots are summed in rank order), which is what
+lets every rank run the same scheduler and sample the same tokens without a control broadcast.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class Communicator:
+    """Baseline: library all-reduce."""
+
+    fused = False
+
+    def __init__(self, world: int, rank: int, group=None):
+        self.world, self.rank, self.group = world, rank, group
+        self.n_collectives = 0
+
+    def begin_step(self) -> None:
+        """Called once at the start of every forward pass."""
+
+    def all_reduce(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """sum over ranks of ``x`` (+ residual); the reduction itself runs in fp32 as in the reference."""
+        self.n_collectives += 1
+        y = x.float()
+        dist.all_reduce(y, group=self.group)
+        if residual is not None:
+            y = y + residual.float()
+        return y.to(residual.dtype if residual is not None else x.dtype)
+
+    def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        """all_reduce(x_shard @ w_shard^T) + residual."""
+        from .. import ops
+        part = ops.linear(x, w, out_dtype=torch.float32)
+        out = self.all_reduce(part, residual)
+        return out if residual is not None else out.to(x.dtype)
+
+    def close(self) -> None:
+        pass
+
+
+class ArCtx(C.Structure):
+    _fields_ = [("recv", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("status", C.c_void_p),
+                ("world", C.c_int), ("rank", C.c_int), ("n_sites", C.c_int), ("max_rows", C.c_int), ("d_max", C.c_int),
+                ("max_tiles", C.c_int)]
+
+
+class FusedCommunicator(Communicator):
+    """One-shot all-reduce over peer memory, fused into the GEMM epilogue where a GEMM produces the partial."""
+
+    fused = True
+    MAX_TILES = 512
+
+    def __init__(self, device: torch.device, world: int, rank: int, d_max: int, n_sites: int, max_rows: int = 256,
+                 group=None):
+        super().__init__(world, rank, group)
+        from ..ops import native
+        self.native = native
+        self.L = native.load()
+        self.device = device
+        self.d_max, self.n_sites, self.max_rows = d_max, n_sites, max_rows
+        vp = C.c_void_p
+        for name, args in (("jib_symm_alloc", [C.c_size_t, C.POINTER(vp), vp]), ("jib_symm_open", [vp, C.POINTER(vp)]),
+                           ("jib_symm_close", [vp]), ("jib_symm_free", [vp]), ("jib_ar_epoch_bump", [vp, vp]),
+                           ("jib_allreduce_oneshot", [vp, C.c_int, vp, vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, vp])):
+            fn = getattr(self.L, name)
+            fn.restype, fn.argtypes = C.c_int, args
+        self._own, self._peers = [], []
+        recv_ptrs = self._exchange(2 * world * max_rows * d_max * 4)
+        flag_ptrs = self._exchange(n_sites * world * self.MAX_TILES * 4)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        ws = native.workspace(device)
+        self.ctx = ArCtx()
+        for i in range(world):
+            self.ctx.recv[i] = recv_ptrs[i]
+            self.ctx.flags[i] = flag_ptrs[i]
+        self.ctx.epoch, self.ctx.status = self.epoch.data_ptr(), ws.status.data_ptr()
+        self.ctx.world, self.ctx.rank, self.ctx.n_sites = world, rank, n_sites
+        self.ctx.max_rows, self.ctx.d_max, self.ctx.max_tiles = max_rows, d_max, self.MAX_TILES
+        self.site = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def _exchange(self, nbytes: int):
+        ptr = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        rc = self.L.jib_symm_alloc(nbytes, C.byref(ptr), handle)
+        if rc:
+            raise RuntimeError(f"symmetric buffer allocation failed ({rc})")
+        self._own.append(ptr.value)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=self.group)
+        ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(ptr.value)
+                continue
+            p = C.c_void_p()
+            buf = (C.c_ubyte * 64).from_buffer_copy(h)
+            rc = self.L.jib_symm_open(buf, C.byref(p))
+            if rc:
+                raise RuntimeError(f"cudaIpcOpenMemHandle for rank {r} failed ({rc})")
+            self._peers.append(p.value)
+            ptrs.append(p.value)
+        return ptrs
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for p in self._peers:
+            self.L.jib_symm_close(p)
+        self._peers = []
+        dist.barrier(group=self.group)
+        for p in self._own:
+            self.L.jib_symm_free(p)
+        self._own = []
+
+    # ---------------------------------------------------------------------------------------------
+    def begin_step(self) -> None:
+        rc = self.L.jib_ar_epoch_bump(self.epoch.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        self.native._ck(rc, "epoch_bump")
+        self.site = 0
+
+    def _next_site(self) -> int:
+        s = self.site
+        self.site += 1
+        if s >= self.n_sites:
+            raise RuntimeError("more collectives in one forward pass than the communicator was sized for")
+        return s
+
+    def all_reduce(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, d = x.shape
+        site = self._next_site()
+        if T > self.max_rows:
+            return super().all_reduce(x, residual)
+        self.n_collectives += 1
+        out = torch.empty(T, d, dtype=torch.bfloat16, device=x.device)
+        rc = self.L.jib_allreduce_oneshot(x.data_ptr(), int(x.dtype == torch.float32),
+                                          None if residual is None else residual.data_ptr(), out.data_ptr(), T, d,
+                                          C.byref(self.ctx), site, torch.cuda.current_stream().cuda_stream)
+        self.native._ck(rc, "allreduce_oneshot")
+        return out
+
+    def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        site = self._next_site()
+        if x.shape[0] > self.max_rows:
+            return Communicator.linear_all_reduce(self, x, w, residual)
+        self.n_collectives += 1
+        return self.native.gemm(x, w, residual=residual, ar=self.ctx, ar_site=site)
+
+
+def make_communicator(device: torch.device, world: int, rank: int, d_model: int, n_layer: int, group=None):
+    impl = os.environ.get("JITTORINFER_COMM", "fused").lower()
+    if device.type != "cuda" or impl == "nccl":
+        return Communicator(world, rank, group)
+    return FusedCommunicator(device, world, rank, d_model, 2 * n_layer, group=group)

@@ -32,7 +32,7 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
                               device=dev, fast=fast_random and dev.type == "cuda")
     if world > 1 and comm is None:
         from ..parallel.comm import make_communicator
-        comm = make_communicator(torch.device(device), world, rank, hp.n_embd)
+        comm = make_communicator(torch.device(device), world, rank, hp.n_embd, hp.n_layer)
     return DeepSeek2Model(hp, weights, dtype=dtype, device=device, spec=spec, comm=comm, max_positions=max_positions)
 
 
