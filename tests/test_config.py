@@ -1,0 +1,39 @@
+"""YAML config: the reference's own files load, ours load, bad values are refused."""
+import glob
+import os
+
+import pytest
+
+from jittorinfer_b200.config import ServerConfig, load_yaml
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shipped_configs_load():
+    files = sorted(glob.glob(os.path.join(ROOT, "configs", "*.yaml")))
+    assert len(files) == 4
+    for f in files:
+        c = load_yaml(f)
+        assert c.model.endswith(".gguf") and c.n_parallel >= 8
+    assert load_yaml(os.path.join(ROOT, "configs", "config_deepseek_v2_ep.yaml")).world_size == 8
+
+
+def test_reference_style_file_and_defaults(tmp_path):
+    p = tmp_path / "ref.yaml"
+    p.write_text("main_gpu: 1\nn_gpu_layers: 99\nsplit_mode: LLAMA_SPLIT_MODE_LAYER\ntensor_split: [0]\nuse_mmap: true\n"
+                 "n_threads: 128\ndefrag_thold: 0.5\nenable_mla: false\nenable_fused_moe: true\noffload_input: true\n"
+                 "enable_ge: true\npresample_count: -1\nenable_cann_flash_attention: true\nn_ctx: 65536\nn_batch: 16\n"
+                 "n_parallel: 16\nmodel: \"/root/data/x-f16.gguf\"\nport: 8084\nn_threads_http: 16\nhostname: \"127.0.0.1\"\n"
+                 "reasoning_format: COMMON_REASONING_FORMAT_DEEPSEEK\n")
+    c = load_yaml(str(p))
+    assert c.port == 8084 and c.n_ctx == 65536 and c.presample_count == -1 and c.cuda_graphs
+    assert "n_threads" in c.ignored and "enable_cann_flash_attention" in c.ignored
+    assert load_yaml(str(tmp_path / "missing.yaml")) == ServerConfig()
+
+
+def test_bad_values_rejected(tmp_path):
+    for body in ("tp_size: 3\n", "split_mode: SIDEWAYS\n", "kv_block_size: 32\n", "tp_size: 4\nep_size: 2\n"):
+        p = tmp_path / "bad.yaml"
+        p.write_text(body)
+        with pytest.raises(ValueError):
+            load_yaml(str(p))
