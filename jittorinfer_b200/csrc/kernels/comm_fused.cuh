@@ -6,7 +6,8 @@
 
 #define JIB_AR_MAX_WORLD 8
 #ifndef JIB_AR_SPIN_LIMIT
-#define JIB_AR_SPIN_LIMIT (1u << 17)      // polls of ~1-2 us each (a peer load plus a short sleep): gives up after ~0.2 s
+#define JIB_AR_SPIN_LIMIT (1u << 20)      // polls of ~1-2 us each (a flag load plus a short sleep): gives up after 1-2 s,
+                                          // enough for host-side skew between ranks (graph capture, first-use loads)
 #endif
 
 struct JibArCtx {

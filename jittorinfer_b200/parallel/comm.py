@@ -54,6 +54,13 @@ class Communicator:
         out = self.all_reduce(part, residual)
         return out if residual is not None else out.to(x.dtype)
 
+    def host_barrier(self) -> None:
+        """Align the ranks on the host (used after one-off slow host work such as CUDA-graph capture)."""
+        if dist.is_initialized() and self.world > 1:
+            if torch.cuda.is_available() and dist.get_backend(self.group) == "nccl":
+                torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+
     def close(self) -> None:
         pass
 

@@ -187,6 +187,9 @@ class LLMEngine:
         if not ops.force_torch():
             self.graph_launches[key] = ops.nat().launch_count - n0
         self._graphs[key] = (g, out)
+        comm = getattr(self.model, "comm", None)
+        if comm is not None and hasattr(comm, "host_barrier"):
+            comm.host_barrier()          # capture time differs per rank; re-align before the first replay
         return self._graphs[key]
 
     def warmup(self, modes: Iterable[str] = ("greedy",)):
