@@ -138,6 +138,12 @@ def main():
     if W + K >= args.gen_len:
         raise SystemExit("steps + warmup must be smaller than --gen-len")
 
+    t_start = time.time()
+
+    def note(msg):
+        if rank == 0:
+            print(f"[bench +{time.time() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
     eng = build_engine(hp, device=dev, world=world, rank=rank, n_parallel=C, n_ctx_slot=total_len + 64,
                        n_batch=2048, seed=0, graph_buckets=tuple(b for b in (1, 2, 4, 8, 16, 32, 64) if b <= max(C, 1)) or (1,))
     g = torch.Generator().manual_seed(1234)
@@ -184,8 +190,11 @@ def main():
             eng.requests.pop(i, None)
         return ms / k_steps, clocks, launches
 
+    note(f"model built: {eng.model.weight_bytes() / 2**30:.1f} GiB of weights on this rank")
     eng.warmup()
+    note("decode graphs captured")
     ms_step, clocks, launches = timed_decode(C, K, W, True)
+    note(f"timed region done: {ms_step:.3f} ms/step")
     value = C * 1000.0 / ms_step
 
     # bare graph replay (no host work between steps): explains how much of a step is device time
@@ -250,8 +259,14 @@ def main():
         if by_conc:
             out["by_concurrency"] = by_conc
         print(json.dumps(out))
+    note("done")
+    sys.stdout.flush()
     if world > 1:
-        dist.destroy_process_group()
+        dist.barrier()
+        torch.cuda.synchronize()
+        # leave without interpreter teardown: destroying captured graphs that hold communicator state after the
+        # process group is gone can block at exit
+        os._exit(0)
     return 0
 
 

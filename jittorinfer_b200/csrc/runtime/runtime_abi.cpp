@@ -108,3 +108,44 @@ JIB_API void jib_sched_stats(jib_sched * s, int64_t * o) {
     const SchedStats & st = s->sched.stats();
     o[0] = st.steps; o[1] = st.prompt_tokens; o[2] = st.decode_tokens; o[3] = st.preemptions; o[4] = st.finished; o[5] = st.prefix_hits;
 }
+
+// ---- tokenizer ------------------------------------------------------------------------------
+#include "tokenizer.h"
+
+JIB_API Tokenizer * jib_tok_create(const char ** tokens, const int32_t * token_lens, const int32_t * types, int n_tokens,
+                                   const char ** merges, const int32_t * merge_lens, int n_merges, int bos, int eos, int eot,
+                                   int add_bos, int add_eos) {
+    std::vector<std::string> toks(n_tokens), mg(n_merges);
+    for (int i = 0; i < n_tokens; ++i) toks[i].assign(tokens[i], token_lens[i]);
+    for (int i = 0; i < n_merges; ++i) mg[i].assign(merges[i], merge_lens[i]);
+    std::vector<int32_t> ty(types ? types : nullptr, types ? types + n_tokens : nullptr);
+    TokenizerConfig cfg;
+    cfg.bos = bos; cfg.eos = eos; cfg.eot = eot; cfg.add_bos = add_bos != 0; cfg.add_eos = add_eos != 0;
+    return new Tokenizer(std::move(toks), std::move(ty), mg, cfg);
+}
+JIB_API void jib_tok_destroy(Tokenizer * t) { delete t; }
+// Returns the token count; writes at most cap ids (call again with a larger buffer if the count exceeds cap).
+JIB_API int jib_tok_encode(Tokenizer * t, const char * text, int len, int add_special, int parse_special, int32_t * out, int cap) {
+    const std::vector<int32_t> ids = t->encode(std::string(text, len), add_special != 0, parse_special != 0);
+    const int n = std::min<int>((int) ids.size(), cap);
+    if (out && n > 0) std::memcpy(out, ids.data(), n * sizeof(int32_t));
+    return (int) ids.size();
+}
+JIB_API int jib_tok_piece(Tokenizer * t, int32_t id, int special, char * buf, int cap) {
+    const std::string s = t->token_to_piece(id, special != 0);
+    const int n = std::min<int>((int) s.size(), cap);
+    if (buf && n > 0) std::memcpy(buf, s.data(), n);
+    return (int) s.size();
+}
+JIB_API int jib_tok_decode(Tokenizer * t, const int32_t * ids, int n_ids, int remove_special, int unparse_special, char * buf, int cap) {
+    const std::string s = t->decode(std::vector<int32_t>(ids, ids + n_ids), remove_special != 0, unparse_special != 0);
+    const int n = std::min<int>((int) s.size(), cap);
+    if (buf && n > 0) std::memcpy(buf, s.data(), n);
+    return (int) s.size();
+}
+JIB_API int jib_tok_is_eog(Tokenizer * t, int32_t id) { return t->is_eog(id) ? 1 : 0; }
+JIB_API int jib_tok_n_tokens(Tokenizer * t) { return t->n_tokens(); }
+JIB_API int jib_tok_bos(Tokenizer * t) { return t->config().bos; }
+JIB_API int jib_tok_eos(Tokenizer * t) { return t->config().eos; }
+JIB_API int jib_tok_eot(Tokenizer * t) { return t->config().eot; }
+JIB_API int jib_utf8_incomplete_tail(const char * s, int len) { return (int) utf8_incomplete_tail(std::string(s, len)); }
