@@ -1,0 +1,85 @@
+"""Builds engine + tokenizer from a YAML config and runs the HTTP server (all ranks call this)."""
+from __future__ import annotations
+
+import argparse
+import logging
+import os
+import sys
+
+log = logging.getLogger("jittorinfer_b200.server")
+
+
+def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
+    import torch
+    from ..models.hparams import DeepSeek2HParams, preset
+    from ..runtime.factory import build_engine
+    from ..tokenizer import Tokenizer
+    from ..utils.toy_vocab import toy_vocab_kv
+    if device is None:
+        device = torch.device("cuda", cfg.main_gpu if world == 1 else rank) if torch.cuda.is_available() else torch.device("cpu")
+    dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    n_ctx_slot = max(cfg.kv_block_size, cfg.n_ctx // cfg.slots)
+    common = dict(device=device, dtype=dtype, world=world, rank=rank, n_parallel=cfg.slots, n_ctx_slot=n_ctx_slot, n_ctx=cfg.n_ctx,
+                  n_batch=cfg.n_batch, cuda_graphs=cfg.cuda_graphs, graph_buckets=tuple(b for b in cfg.cuda_graph_buckets if b <= cfg.slots) or (1,),
+                  expert_parallel=cfg.ep_size > 1, n_keep=cfg.n_keep, cont_batching=cfg.cont_batching, defrag_thold=cfg.defrag_thold,
+                  presample_count=max(1, cfg.presample_count) if cfg.presample_count > 0 else 64)
+    if cfg.random_init:
+        hp = preset(cfg.random_init)
+        eng = build_engine(hp, **common)
+        kv = {k: (v[1] if isinstance(v, tuple) else v) for k, v in toy_vocab_kv(hp.n_vocab, hp.bos_id, hp.eos_id).items()}
+        kv["tokenizer.ggml.bos_token_id"], kv["tokenizer.ggml.eos_token_id"] = hp.bos_id, hp.eos_id
+        tok = Tokenizer.from_gguf_kv(kv)
+        template_src = ""
+    else:
+        from ..gguf.io import GGUFReader
+        reader = GGUFReader(cfg.model)
+        tok = Tokenizer.from_gguf_kv(reader.kv)
+        template_src = reader.kv.get("tokenizer.chat_template", "")
+        reader.close()
+        eng = build_engine(None, gguf_path=cfg.model, **common)
+    return eng, tok, (cfg.chat_template or template_src or "")
+
+
+def main(argv=None, world: int = 1, rank: int = 0, control_group=None) -> int:
+    ap = argparse.ArgumentParser(prog="jittorinfer_b200.server")
+    ap.add_argument("--config", "-c", default=None, help="YAML file with the reference's keys (configs/*.yaml)")
+    ap.add_argument("--port", type=int, default=None)
+    ap.add_argument("--host", default=None)
+    ap.add_argument("--random-init", default=None, help="serve a random-init preset (tiny | lite | v2) instead of a GGUF file")
+    args = ap.parse_args(argv)
+    logging.basicConfig(level=os.environ.get("JITTORINFER_LOG", "INFO"), format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    from ..config import load_yaml
+    from .app import ServerContext, serve
+    from .chat import ChatTemplate
+    cfg = load_yaml(args.config)
+    if args.random_init:
+        cfg.random_init = args.random_init
+    if args.port:
+        cfg.port = args.port
+    if args.host:
+        cfg.hostname = args.host
+    if not cfg.model and not cfg.random_init:
+        print("config has no \"model\" (GGUF path) and no random_init preset", file=sys.stderr)
+        return 2
+    eng, tok, template_src = build_from_config(cfg, world=world, rank=rank)
+    try:
+        template = ChatTemplate(template_src)
+    except Exception as e:        # a template the Jinja subset cannot render: fall back to the built-in one
+        log.warning("chat template rejected (%s): using the built-in deepseek2 template", e)
+        template = ChatTemplate("")
+    eng.warmup()
+    ctx = ServerContext(eng, tok, cfg, template, rank=rank, world=world, control_group=control_group)
+    if rank != 0:
+        ctx.run()                 # worker ranks: follow rank 0's task broadcasts until told to stop
+        return 0
+    httpd = serve(ctx, cfg.hostname, cfg.port, cfg.n_threads_http)
+    log.info("listening on http://%s:%d  (slots=%d, n_ctx_slot=%d, kv blocks=%d)", cfg.hostname, cfg.port, eng.cfg.n_parallel,
+             eng.n_ctx_slot, eng.kv.n_blocks)
+    try:
+        httpd.serve_forever()
+    except KeyboardInterrupt:
+        pass
+    finally:
+        ctx.shutdown()
+        httpd.server_close()
+    return 0

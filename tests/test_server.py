@@ -1,0 +1,94 @@
+"""OpenAI-compatible server end to end on CPU: tiny random model, toy byte-level vocabulary."""
+import json
+import threading
+import urllib.error
+import urllib.request
+
+import pytest
+import torch
+
+from jittorinfer_b200.config import ServerConfig
+from jittorinfer_b200.server.app import ServerContext, serve
+from jittorinfer_b200.server.chat import ChatTemplate, apply_deepseek2, split_reasoning
+from jittorinfer_b200.server.launch import build_from_config
+
+
+@pytest.fixture(scope="module")
+def server():
+    cfg = ServerConfig(random_init="tiny", n_ctx=2048, n_parallel=4, n_batch=64, port=0, enable_ge=False)
+    eng, tok, tpl = build_from_config(cfg, device=torch.device("cpu"))
+    ctx = ServerContext(eng, tok, cfg, ChatTemplate(tpl))
+    httpd = serve(ctx, "127.0.0.1", 0)
+    t = threading.Thread(target=httpd.serve_forever, daemon=True)
+    t.start()
+    yield f"http://127.0.0.1:{httpd.server_address[1]}", ctx
+    httpd.shutdown()
+    ctx.shutdown()
+
+
+def _post(url, body, stream=False):
+    req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=120) as r:
+        data = r.read().decode()
+    return data if stream else json.loads(data)
+
+
+def test_completion_and_usage(server):
+    url, ctx = server
+    r = _post(url + "/v1/completions", {"prompt": "hello there", "max_tokens": 8, "temperature": 0, "ignore_eos": True})
+    assert r["object"] == "text_completion" and r["choices"][0]["finish_reason"] == "length"
+    assert r["usage"]["completion_tokens"] == 8 and r["usage"]["prompt_tokens"] == len(ctx.tokenizer.encode("hello there"))
+    r2 = _post(url + "/v1/completions", {"prompt": "hello there", "max_tokens": 8, "temperature": 0, "ignore_eos": True})
+    assert r2["choices"][0]["text"] == r["choices"][0]["text"]          # greedy is deterministic (and hits the prefix cache)
+    r3 = _post(url + "/v1/completions", {"prompt": [5, 6, 7, 8], "max_tokens": 3, "temperature": 0.7, "seed": 1, "ignore_eos": True})
+    assert r3["usage"] == {"prompt_tokens": 4, "completion_tokens": 3, "total_tokens": 7}
+
+
+def test_chat_and_stream(server):
+    url, _ = server
+    body = {"messages": [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}], "max_tokens": 6,
+            "temperature": 0, "ignore_eos": True}
+    r = _post(url + "/v1/chat/completions", body)
+    assert r["object"] == "chat.completion" and r["choices"][0]["message"]["role"] == "assistant"
+    s = _post(url + "/v1/chat/completions", dict(body, stream=True), stream=True)
+    events = [json.loads(l[6:]) for l in s.split("\n") if l.startswith("data: ") and l != "data: [DONE]"]
+    assert s.rstrip().endswith("data: [DONE]")
+    text = "".join(e["choices"][0]["delta"].get("content", "") for e in events)
+    assert text == (r["choices"][0]["message"]["content"] or "")
+    assert events[-1]["choices"][0]["finish_reason"] == "length" and events[-1]["usage"]["completion_tokens"] == 6
+    assert all("usage" not in e for e in events[:-1])                   # usage only on the final chunk
+
+
+def test_stop_word_and_multi_prompt(server):
+    url, _ = server
+    full = _post(url + "/v1/completions", {"prompt": "abc", "max_tokens": 24, "temperature": 0, "ignore_eos": True})["choices"][0]["text"]
+    if len(full) >= 6:
+        stop = full[3:5]
+        cut = _post(url + "/v1/completions", {"prompt": "abc", "max_tokens": 24, "temperature": 0, "ignore_eos": True, "stop": [stop]})
+        assert cut["choices"][0]["finish_reason"] == "stop" and cut["choices"][0]["text"] == full[:full.find(stop)]
+    multi = _post(url + "/v1/completions", {"prompt": ["one", "two two"], "max_tokens": 4, "temperature": 0, "ignore_eos": True})
+    assert isinstance(multi, list) and len(multi) == 2
+
+
+def test_errors_and_introspection(server):
+    url, _ = server
+    for bad in ({"prompt": "x", "n": 2}, {"prompt": "x", "n_probs": 3}, {"prompt": "x", "echo": True}, {"messages": []}, {}):
+        path = "/v1/chat/completions" if "messages" in bad else "/v1/completions"
+        with pytest.raises(urllib.error.HTTPError) as e:
+            _post(url + path, bad)
+        assert e.value.code == 400 and "error" in json.loads(e.value.read())
+    assert json.loads(urllib.request.urlopen(url + "/health").read())["status"] == "ok"
+    m = urllib.request.urlopen(url + "/metrics").read().decode()
+    assert "jittorinfer_generation_tokens_total" in m and "jittorinfer_kv_blocks_total" in m
+    assert len(json.loads(urllib.request.urlopen(url + "/slots").read())) == 4
+    assert json.loads(urllib.request.urlopen(url + "/v1/models").read())["data"][0]["object"] == "model"
+
+
+def test_templates_and_reasoning():
+    msgs = [{"role": "system", "content": "S"}, {"role": "user", "content": "U"}, {"role": "assistant", "content": "A"},
+            {"role": "user", "content": [{"type": "text", "text": "U2"}]}]
+    assert apply_deepseek2(msgs) == "S\n\nUser: U\n\nAssistant: A<｜end▁of▁sentence｜>User: U2\n\nAssistant:"
+    t = ChatTemplate("{% for m in messages %}[{{ m.role }}]{{ m.content }}{% endfor %}{% if add_generation_prompt %}[assistant]{% endif %}")
+    assert t.render(msgs[:2]) == "[system]S[user]U[assistant]"
+    assert split_reasoning("<think>why</think>answer", True) == ("why", "answer")
+    assert split_reasoning("plain", True) == (None, "plain") and split_reasoning("<think>x</think>y", False) == (None, "<think>x</think>y")
