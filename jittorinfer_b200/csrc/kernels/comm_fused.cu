@@ -23,17 +23,24 @@
 
 #include "comm_fused.cuh"
 #include "jib_kernels.h"
+#include "pdl.cuh"
 
 namespace {
 
 typedef __nv_bfloat16 bf16;
 
-__global__ void epoch_bump_kernel(unsigned * epoch) { *epoch += 1; }
+__global__ void epoch_bump_kernel(unsigned * epoch) {
+    pdl_launch_dependents();
+    pdl_wait();
+    *epoch += 1;
+}
 
 // One CTA per (8 rows, 512 features).  x: fp32 or bf16 partial [T][d]; out bf16 [T][d] = sum over ranks + residual.
 template <typename TIn>
 __global__ void __launch_bounds__(128) allreduce_oneshot_kernel(const TIn * __restrict__ x, const bf16 * __restrict__ residual,
                                                                 bf16 * __restrict__ out, int T, int d, JibArCtx ar, int site) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const unsigned epoch = *ar.epoch;
     const int parity = (site + (int) (epoch % 2u) * (ar.n_sites & 1)) & 1;
     const int f0 = blockIdx.x * 512, r0 = blockIdx.y * 8;
@@ -106,7 +113,7 @@ JIB_EXPORT int jib_symm_close(void * ptr) { return cudaIpcCloseMemHandle(ptr) ==
 JIB_EXPORT int jib_symm_free(void * ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : JIB_E_DRIVER; }
 
 JIB_EXPORT int jib_ar_epoch_bump(unsigned * epoch, void * stream) {
-    epoch_bump_kernel<<<1, 1, 0, (cudaStream_t) stream>>>(epoch);
+    JIB_LAUNCH((epoch_bump_kernel), 1, 1, 0, (cudaStream_t) stream, epoch);
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 
@@ -118,9 +125,9 @@ JIB_EXPORT int jib_allreduce_oneshot(const void * x, int x_f32, const void * res
     dim3 grid((d + 511) / 512, (T + 7) / 8);
     if ((int) (grid.x * grid.y) > ar->max_tiles) return JIB_E_ARG;
     if (x_f32)
-        allreduce_oneshot_kernel<float><<<grid, 128, 0, (cudaStream_t) stream>>>((const float *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
+        JIB_LAUNCH((allreduce_oneshot_kernel<float>), grid, 128, 0, (cudaStream_t) stream, (const float *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
     else
-        allreduce_oneshot_kernel<bf16><<<grid, 128, 0, (cudaStream_t) stream>>>((const bf16 *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
+        JIB_LAUNCH((allreduce_oneshot_kernel<bf16>), grid, 128, 0, (cudaStream_t) stream, (const bf16 *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 

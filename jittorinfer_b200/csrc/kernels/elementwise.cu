@@ -11,6 +11,7 @@
 #include <stdint.h>
 
 #include "jib_kernels.h"
+#include "pdl.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -42,6 +43,8 @@ __device__ __forceinline__ float block_sum(float v, float * red) {
 // ---------------------------------------------------------------------------------------------
 __global__ void embed_gather_kernel(const bf16 * __restrict__ table, const int * __restrict__ ids, bf16 * __restrict__ out, int d,
                                     int n_vocab) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= n_vocab ? n_vocab - 1 : id);
@@ -55,6 +58,8 @@ template <int NT, int MAXV>
 __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x, const bf16 * __restrict__ residual,
                                                      const float * __restrict__ w, bf16 * __restrict__ out_norm,
                                                      bf16 * __restrict__ out_sum, int d, long long x_stride, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ float red[32];
     const int t = blockIdx.x;
     const bf16x8 * xr = (const bf16x8 *) (x + (size_t) t * x_stride);
@@ -111,6 +116,8 @@ __global__ void __launch_bounds__(NT) mla_qkv_post_kernel(const bf16 * __restric
                                                           const int * __restrict__ slot_mapping, bf16 * __restrict__ cache,
                                                           bf16 * __restrict__ q_out, int H, int dn, int dr, int r, int max_pos,
                                                           long long n_slots, int * status) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int slot = slot_mapping[t];
@@ -161,6 +168,8 @@ __device__ __forceinline__ uint32_t f2key(float f) {   // order-preserving float
 
 template <int NT>
 __global__ void __launch_bounds__(NT) argmax_kernel(const float * __restrict__ logits, int * __restrict__ out, int V) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ unsigned long long best_s[NT / 32];
     const float * row = logits + (size_t) blockIdx.x * V;
     // pack (key, ~index) so that max picks the largest value and, among equals, the lowest index
@@ -194,6 +203,8 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float * __restrict__ l
 template <int NT>
 __global__ void __launch_bounds__(NT) topk_kernel(const float * __restrict__ logits, float * __restrict__ vals, int * __restrict__ ids,
                                                   int V, int k) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ int hist[2048];
     __shared__ uint32_t s_prefix, s_mask;
     __shared__ int s_need, s_cnt_gt, s_cnt_eq;
@@ -272,6 +283,8 @@ __global__ void __launch_bounds__(NT) topk_kernel(const float * __restrict__ log
 
 __global__ void kv_block_copy_kernel(bf16 * cache, long long layer_stride, const int * __restrict__ src, const int * __restrict__ dst,
                                      int block_elems) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const int i = blockIdx.x, l = blockIdx.y;
     const uint4 * s = (const uint4 *) (cache + (size_t) l * layer_stride + (size_t) src[i] * block_elems);
     uint4 * d = (uint4 *) (cache + (size_t) l * layer_stride + (size_t) dst[i] * block_elems);
@@ -279,6 +292,8 @@ __global__ void kv_block_copy_kernel(bf16 * cache, long long layer_stride, const
 }
 
 __global__ void gather_rows_kernel(const bf16 * __restrict__ x, const int * __restrict__ src_row, bf16 * __restrict__ out, int d, int n_src) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const int rrow = blockIdx.x;
     const int s = src_row[rrow];
     if (s < 0 || s >= n_src) return;   // unowned / out-of-range row: leave the destination untouched
@@ -296,7 +311,7 @@ extern "C" {
 int jib_embed_gather(const void * table, const int * ids, void * out, int T, int d, int n_vocab, void * stream) {
     if (T <= 0) return 0;
     if (d % 8) return JIB_E_ARG;
-    embed_gather_kernel<<<T, 128, 0, (cudaStream_t) stream>>>((const bf16 *) table, ids, (bf16 *) out, d, n_vocab);
+    JIB_LAUNCH((embed_gather_kernel), T, 128, 0, (cudaStream_t) stream, (const bf16 *) table, ids, (bf16 *) out, d, n_vocab);
     return launched();
 }
 
@@ -307,13 +322,13 @@ int jib_rmsnorm(const void * x, const void * residual, const float * w, void * o
     cudaStream_t s = (cudaStream_t) stream;
     const int nv = d / 8;
     if (nv <= 128)
-        rmsnorm_kernel<128, 1><<<T, 128, 0, s>>>((const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<128, 1>), T, 128, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
     else if (nv <= 256)
-        rmsnorm_kernel<256, 1><<<T, 256, 0, s>>>((const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<256, 1>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
     else if (nv <= 1024)
-        rmsnorm_kernel<256, 4><<<T, 256, 0, s>>>((const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<256, 4>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
     else if (nv <= 2048)
-        rmsnorm_kernel<512, 4><<<T, 512, 0, s>>>((const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<512, 4>), T, 512, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
     else
         return JIB_E_ARG;
     return launched();
@@ -324,7 +339,7 @@ int jib_mla_qkv_post(const void * q, long long q_stride, const void * ckv, long 
                      int H, int dn, int dr, int r, int max_pos, long long n_slots, int * status, void * stream) {
     if (T <= 0) return 0;
     if ((dr & 1) || (dn & 1) || (r & 1) || (q_stride & 1)) return JIB_E_ARG;
-    mla_qkv_post_kernel<256><<<T, 256, 0, (cudaStream_t) stream>>>((const bf16 *) q, q_stride, (const bf16 *) ckv, ckv_stride, kv_norm_w,
+    JIB_LAUNCH((mla_qkv_post_kernel<256>), T, 256, 0, (cudaStream_t) stream, (const bf16 *) q, q_stride, (const bf16 *) ckv, ckv_stride, kv_norm_w,
                                                                     eps, rope_table, positions, slot_mapping, (bf16 *) cache,
                                                                     (bf16 *) q_out, H, dn, dr, r, max_pos, n_slots, status);
     return launched();
@@ -332,14 +347,14 @@ int jib_mla_qkv_post(const void * q, long long q_stride, const void * ckv, long 
 
 int jib_argmax(const float * logits, int * out, int n, int V, void * stream) {
     if (n <= 0) return 0;
-    argmax_kernel<1024><<<n, 1024, 0, (cudaStream_t) stream>>>(logits, out, V);
+    JIB_LAUNCH((argmax_kernel<1024>), n, 1024, 0, (cudaStream_t) stream, logits, out, V);
     return launched();
 }
 
 int jib_topk(const float * logits, float * vals, int * ids, int n, int V, int k, void * stream) {
     if (n <= 0) return 0;
     if (k < 1 || k > 128 || k > V) return JIB_E_ARG;
-    topk_kernel<1024><<<n, 1024, 0, (cudaStream_t) stream>>>(logits, vals, ids, V, k);
+    JIB_LAUNCH((topk_kernel<1024>), n, 1024, 0, (cudaStream_t) stream, logits, vals, ids, V, k);
     return launched();
 }
 
@@ -347,14 +362,14 @@ int jib_kv_block_copy(void * cache, long long layer_stride_elems, int n_layers, 
                       void * stream) {
     if (n <= 0) return 0;
     if (block_elems % 8) return JIB_E_ARG;
-    kv_block_copy_kernel<<<dim3(n, n_layers), 256, 0, (cudaStream_t) stream>>>((bf16 *) cache, layer_stride_elems, src, dst, block_elems);
+    JIB_LAUNCH((kv_block_copy_kernel), dim3(n, n_layers), 256, 0, (cudaStream_t) stream, (bf16 *) cache, layer_stride_elems, src, dst, block_elems);
     return launched();
 }
 
 int jib_gather_rows(const void * x, const int * src_row, void * out, int rows, int d, int n_src, void * stream) {
     if (rows <= 0) return 0;
     if (d % 8) return JIB_E_ARG;
-    gather_rows_kernel<<<rows, 128, 0, (cudaStream_t) stream>>>((const bf16 *) x, src_row, (bf16 *) out, d, n_src);
+    JIB_LAUNCH((gather_rows_kernel), rows, 128, 0, (cudaStream_t) stream, (const bf16 *) x, src_row, (bf16 *) out, d, n_src);
     return launched();
 }
 

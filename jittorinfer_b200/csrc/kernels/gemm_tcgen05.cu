@@ -29,6 +29,7 @@
 
 #include "comm_fused.cuh"
 #include "jib_kernels.h"
+#include "pdl.cuh"
 
 using namespace sm100;
 
@@ -54,6 +55,7 @@ struct GemmArgs {
     long long scratch_elems;
     JibArCtx ar;              // peer-memory all-reduce fused into the epilogue (ar_on != 0)
     int ar_on, ar_site;
+    int cluster_split;        // 1: the `splits` CTAs of a tile form a thread-block cluster and reduce through DSMEM
 };
 
 template <int BN, bool DUAL>
@@ -73,6 +75,18 @@ struct Cfg {
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
+// Cluster-wide barrier (all threads of all CTAs of the cluster) and a load from a peer CTA's shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_smem_addr, uint32_t cta_rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 template <int BN, bool DUAL>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
@@ -88,7 +102,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int row0 = blockIdx.y * BN;      // first token row of this tile, relative to the segment / matrix
     int rows_valid = args.T;         // rows of this batch's matrix
     int row_base = 0;                // grouped: offset of the expert's segment in the sorted rows
+    pdl_launch_dependents();
     if (args.seg != nullptr) {
+        pdl_wait();                  // segment offsets are produced by the routing kernels just before
         row_base = args.seg[batch];
         rows_valid = args.seg[batch + 1] - row_base;
     }
@@ -125,6 +141,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // Everything above touched only shared/tensor memory and launch-invariant data; activations, the residual,
+    // scratch and the output belong to the stream order from here on.
+    if (args.seg == nullptr) pdl_wait();
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -143,6 +162,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 tma_load_3d(st + (DUAL ? 2 : 1) * C::A_BYTES, &tmB, &full[s], k, row_base + row0, b_z);
             }
         }
+        __syncwarp();
+        if (args.cluster_split) { cluster_sync_all(); cluster_sync_all(); }
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (elect_one()) {
@@ -166,6 +187,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
             mma_commit(acc_ready);         // accumulators complete (also arrives after a failed wait)
         }
+        __syncwarp();
+        if (args.cluster_split) { cluster_sync_all(); cluster_sync_all(); }
     } else {
         // ================= epilogue (warps 2..5) =================
         const int q = warp & 3;                   // TMEM lane quarter this warp may access
@@ -180,7 +203,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         float * part = nullptr;
         bool do_final = true;
 
-        if (splits > 1) {
+        const bool csplit = args.cluster_split != 0;
+        float * stage = (float *) tiles;          // pipeline buffers are idle once the accumulators are complete
+        if (csplit) {
+            // split-K inside a cluster: CTAs 1..splits-1 park their fp32 partial in their own shared memory
+            // ([acc][BN tokens][128 features]); CTA 0 adds them to its accumulators through DSMEM.
+            if (split != 0 && acc_ok) {
+#pragma unroll 1
+                for (int a = 0; a < ACC; ++a)
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 16) {
+                        if (row0 + c >= rows_valid) break;
+                        uint32_t v[16];
+                        tmem_ld16(tbase + a * BN + c, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) stage[(a * BN + c + j) * BM + r] = __uint_as_float(v[j]);
+                    }
+            }
+            cluster_sync_all();
+            do_final = split == 0;
+        }
+
+        if (splits > 1 && !csplit) {
             // 1) publish this split's fp32 partial: layout [acc][BN tokens][128 features]
             part = args.scratch + ((size_t) tile_id * splits) * (ACC * BN * BM);
             float * mine = part + (size_t) split * (ACC * BN * BM);
@@ -211,7 +256,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (do_final) __threadfence();
         }
 
-        if (do_final && acc_ok && splits > 1 && ((long long) tile_id * splits + splits) * (ACC * BN * BM) > args.scratch_elems)
+        if (do_final && acc_ok && splits > 1 && !csplit && ((long long) tile_id * splits + splits) * (ACC * BN * BM) > args.scratch_elems)
             do_final = false;
         if (do_final && acc_ok) {
             const long long obase = (long long) batch * args.out_batch_stride;
@@ -228,15 +273,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int c = 0; c < BN; c += 16) {
                 if (row0 + c >= rows_valid) break;
                 float g[16], u[16];
-                if (splits > 1) {
+                if (splits > 1 && !csplit) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
+                    // only the valid token columns are summed; 4 splits per trip keep 4 x jn loads in flight
+                    const int jn = min(16, rows_valid - row0 - c);
+#pragma unroll 4
                     for (int s = 0; s < splits; ++s) {
                         const float * p = part + (size_t) s * (ACC * BN * BM);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            g[j] += __ldcg(p + (size_t) (c + j) * BM + r);
-                            if (DUAL) u[j] += __ldcg(p + (size_t) (BN + c + j) * BM + r);
+                            if (j < jn) {
+                                g[j] += __ldcg(p + (size_t) (c + j) * BM + r);
+                                if (DUAL) u[j] += __ldcg(p + (size_t) (BN + c + j) * BM + r);
+                            }
                         }
                     }
                 } else {
@@ -250,6 +300,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) u[j] = __uint_as_float(v[j]);
+                    }
+                    if (csplit) {
+                        const int jn = min(16, rows_valid - row0 - c);
+                        const uint32_t sbase = smem_u32(stage);
+                        for (int pr = 1; pr < splits; ++pr) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                if (j < jn) {
+                                    g[j] += ld_dsmem_f32(sbase + (uint32_t) (((c + j) * BM + r) * 4), pr);
+                                    if (DUAL) u[j] += ld_dsmem_f32(sbase + (uint32_t) (((BN + c + j) * BM + r) * 4), pr);
+                                }
+                            }
+                        }
                     }
                 }
                 if (n < args.N) {
@@ -298,6 +361,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
             }
         }
+        if (csplit) cluster_sync_all();           // peers keep their shared memory alive until CTA 0 has read it
     }
 
     // ---- teardown ----
@@ -372,6 +436,15 @@ int make_map(CUtensorMap * out, const void * ptr, long long rows, long long cols
     return 0;
 }
 
+// JIB_GEMM_CLUSTER=0 keeps split-K on the global-scratch path (A/B comparison, tests of both paths).
+bool jib_no_cluster() {
+    static const bool off = [] {
+        const char * e = getenv("JIB_GEMM_CLUSTER");
+        return e != nullptr && e[0] == '0';
+    }();
+    return off;
+}
+
 template <int BN, bool DUAL>
 int launch(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b, const GemmArgs & args, dim3 grid,
            cudaStream_t stream) {
@@ -382,7 +455,9 @@ int launch(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b,
         if (e != cudaSuccess) return JIB_E_LAUNCH;
         attr_done = true;
     }
-    gemm_kernel<BN, DUAL><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(a, a2, b, args);
+    const cudaError_t e = jib::launch_pdl_cluster(gemm_kernel<BN, DUAL>, grid, dim3(NUM_THREADS), C::SMEM_BYTES, stream,
+                                                  args.cluster_split ? args.splits : 1, a, a2, b, args);
+    if (e != cudaSuccess) { (void) cudaGetLastError(); return JIB_E_LAUNCH; }
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 
@@ -417,11 +492,14 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
             if (splits < 1) splits = 1;
         }
     }
+    const bool want_cluster = d->splits <= 0 || d->splits <= 8;      // automatic choice, or an explicit count a cluster can hold
+    if (d->splits <= 0 && splits > 8) splits = 8;                      // a portable cluster holds at most 8 CTAs
     if (splits > num_kb) splits = num_kb;
     int kbps = (num_kb + splits - 1) / splits;
     splits = (num_kb + kbps - 1) / kbps;                        // no empty split
+    const bool cluster_split = want_cluster && splits > 1 && splits <= 8 && !jib_no_cluster();
     const long long tiles_total = (long long) n_tiles * t_tiles * batch;
-    if (splits > 1) {
+    if (splits > 1 && !cluster_split) {
         const size_t need = (size_t) tiles_total * splits * (dual ? 2 : 1) * bn * BM * sizeof(float);
         if (d->scratch == nullptr || need > d->scratch_bytes || tiles_total > d->n_counters) {
             if (d->splits > 0) return JIB_E_SCRATCH;            // explicit request that cannot be met
@@ -451,6 +529,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     a.rows_total = grouped ? d->x_rows_total : d->T;
     a.scratch_elems = (long long) (d->scratch_bytes / sizeof(float));
     a.ar_on = 0; a.ar_site = 0;
+    a.cluster_split = cluster_split ? 1 : 0;
     memset(&a.ar, 0, sizeof(a.ar));
     if (d->ar != nullptr) {
         const JibArCtx * ar = (const JibArCtx *) d->ar;
@@ -460,21 +539,21 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
         a.ar = *ar; a.ar_on = 1; a.ar_site = d->ar_site;
     }
     dim3 grid(n_tiles, t_tiles, batch * splits);
-#define JIB_LAUNCH(BN_)                                                                           \
+#define JIB_GEMM_CASE(BN_)                                                                          \
     case BN_:                                                                                     \
         return dual ? launch<BN_, true>(ma, ma2, mb, a, grid, stream) : launch<BN_, false>(ma, ma2, mb, a, grid, stream);
     switch (bn) {
-        JIB_LAUNCH(16)
-        JIB_LAUNCH(32)
-        JIB_LAUNCH(64)
-        JIB_LAUNCH(128)
+        JIB_GEMM_CASE(16)
+        JIB_GEMM_CASE(32)
+        JIB_GEMM_CASE(64)
+        JIB_GEMM_CASE(128)
         case 256:
             if (dual) return JIB_E_ARG;
             return launch<256, false>(ma, ma2, mb, a, grid, stream);
         default:
             return JIB_E_ARG;
     }
-#undef JIB_LAUNCH
+#undef JIB_GEMM_CASE
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -586,6 +665,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.kb_per_split = p.kbps; a.out_f32 = 0; a.res_f32 = 0; a.rows_total = T;
     a.scratch_elems = (long long) (JIB_NOALLOC_SCRATCH_BYTES / sizeof(float));
     a.ar_on = 0; a.ar_site = 0;
+    a.cluster_split = 0;
     memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);
     switch (p.bn) {

@@ -13,6 +13,7 @@
 #include <stdint.h>
 
 #include "jib_kernels.h"
+#include "pdl.cuh"
 
 namespace {
 
@@ -29,6 +30,8 @@ __global__ void __launch_bounds__(NT) mla_attn_split_kernel(const bf16 * __restr
                                                             const int * __restrict__ seq_lens, const int * __restrict__ q_start, int n_seqs,
                                                             int H, int block_size, float scale, int n_splits, float * __restrict__ part_o,
                                                             float * __restrict__ part_ml, bf16 * __restrict__ o_lat) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     constexpr int D = R + DR;              // 576
     constexpr int ROWB = D * 2 + 16;       // padded smem row (bytes): conflict-free 16-byte reads across rows
     extern __shared__ __align__(16) uint8_t smem[];
@@ -172,6 +175,8 @@ __global__ void __launch_bounds__(NT) mla_attn_split_kernel(const bf16 * __restr
 template <int R>
 __global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_ml, int n_splits, int H,
                                         bf16 * __restrict__ o_lat) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     // n_splits <= 32: warp 0 turns the (m, l) pairs into normalised weights, then every thread sums its
     // dims over the splits with independent loads.
     __shared__ float wsm[32];
@@ -231,12 +236,12 @@ extern "C" int jib_mla_attention(const void * q, const void * cache, const int *
                 return JIB_E_LAUNCH;                                                                                             \
             attr = true;                                                                                                         \
         }                                                                                                                        \
-        mla_attn_split_kernel<R_, DR_><<<grid, NT, smem, s>>>((const bf16 *) q, (const bf16 *) cache, block_tables, max_blocks,  \
+        JIB_LAUNCH((mla_attn_split_kernel<R_, DR_>), grid, NT, smem, s, (const bf16 *) q, (const bf16 *) cache, block_tables, max_blocks,  \
                                                               seq_lens, q_start, n_seqs, H, block_size, scale, n_splits, part_o, \
                                                               part_ml, (bf16 *) o_lat);                                          \
         if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;                                                              \
         if (n_splits > 1) {                                                                                                      \
-            mla_attn_combine_kernel<R_><<<dim3(T, H), 128, 0, s>>>(part_o, part_ml, n_splits, H, (bf16 *) o_lat);                \
+            JIB_LAUNCH((mla_attn_combine_kernel<R_>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat);                \
             if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;                                                          \
         }                                                                                                                        \
         return 0;                                                                                                                \
@@ -253,8 +258,8 @@ extern "C" int jib_mla_combine(const float * part_o, const float * part_ml, int 
     if (T <= 0) return 0;
     if (n_splits < 1 || n_splits > 32) return JIB_E_ARG;
     cudaStream_t s = (cudaStream_t) stream;
-    if (r == 512) mla_attn_combine_kernel<512><<<dim3(T, H), 128, 0, s>>>(part_o, part_ml, n_splits, H, (bf16 *) o_lat);
-    else if (r == 64) mla_attn_combine_kernel<64><<<dim3(T, H), 128, 0, s>>>(part_o, part_ml, n_splits, H, (bf16 *) o_lat);
+    if (r == 512) JIB_LAUNCH((mla_attn_combine_kernel<512>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat);
+    else if (r == 64) JIB_LAUNCH((mla_attn_combine_kernel<64>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat);
     else return JIB_E_ARG;
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }

@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include "jib_kernels.h"
+#include "pdl.cuh"
 
 using namespace sm100;
 
@@ -136,7 +137,9 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     int total_tiles = 0;
     for (int p = 0; p < n_pass; ++p) total_tiles += pass_k1[p] > pass_k0[p] ? (pass_k1[p] - pass_k0[p] + KV_TILE - 1) / KV_TILE : 0;
 
+    pdl_launch_dependents();
     if (total_tiles == 0) {
+        pdl_wait();
         // nothing visible for this (group, split): publish an empty partial / zero output and leave
         const int wr = threadIdx.x;
         for (int idx = wr; idx < QT * 16; idx += NUM_THREADS) {
@@ -173,6 +176,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    pdl_wait();                                 // q, the latent cache rows written this step, and all outputs
     const uint32_t tm_S = tmem;                 // NQ columns
     const uint32_t tm_O = tmem + NQ;            // 4 x NQ columns
 
@@ -433,7 +437,7 @@ int launch_flash(const CUtensorMap & mq, const CUtensorMap & mkv, const FlashArg
             return JIB_E_LAUNCH;
         attr_done = true;
     }
-    mla_flash_kernel<QT><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(mq, mkv, a);
+    JIB_LAUNCH((mla_flash_kernel<QT>), grid, NUM_THREADS, C::SMEM_BYTES, stream, mq, mkv, a);
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 

@@ -11,6 +11,7 @@
 #include <stdint.h>
 
 #include "jib_kernels.h"
+#include "pdl.cuh"
 
 namespace {
 
@@ -32,6 +33,8 @@ constexpr int GATE_NT = 256;
 constexpr int GATE_MAXV = 8;      // float4 slices per thread: d <= 8 * 256 * 4 = 8192
 __global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
                                                                 float * __restrict__ logits, int T, int d, int E) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ float red[GATE_NT / 32][GATE_TG];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.x;
@@ -81,12 +84,15 @@ __global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __r
 // One warp per token: softmax/sigmoid over the logits, optional group-limited masking, k rounds of arg-max.
 __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__ logits, const float * __restrict__ bias,
                                                       int * __restrict__ ids, float * __restrict__ wts, int E, int k, int n_group,
-                                                      int topk_group, float scale, int norm, int sigmoid) {
+                                                      int topk_group, float scale, int norm, int sigmoid, int n_shared) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ float prob[MAX_E];
     __shared__ float sel[MAX_E];
     __shared__ float gscore[32];
     const int t = blockIdx.x;
     const int lane = threadIdx.x;
+    const int ld = k + n_shared;
     for (int e = lane; e < E; e += 32) prob[e] = logits[(size_t) t * E + e];
     __syncwarp();
     {
@@ -143,8 +149,8 @@ __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__
             }
             if (bi >= E) bi = 0;
             if (lane == 0) {
-                ids[(size_t) t * k + round] = bi;
-                wts[(size_t) t * k + round] = prob[bi];
+                ids[(size_t) t * ld + round] = bi;
+                wts[(size_t) t * ld + round] = prob[bi];
                 sel[bi] = -INFINITY;
                 // a -inf that was already masked can only be re-picked when fewer than k experts are eligible
             }
@@ -152,9 +158,13 @@ __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__
             __syncwarp();
         }
         if (lane < k) {
-            float w = wts[(size_t) t * k + lane];
+            float w = wts[(size_t) t * ld + lane];
             if (norm) w /= wsum;
-            wts[(size_t) t * k + lane] = w * scale;
+            wts[(size_t) t * ld + lane] = w * scale;
+        } else if (lane < ld) {
+            // shared experts ride along as always-selected experts E, E+1, ... with weight 1
+            ids[(size_t) t * ld + lane] = E + (lane - k);
+            wts[(size_t) t * ld + lane] = 1.f;
         }
     }
 }
@@ -163,6 +173,8 @@ __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__
 // seg[e] .. seg[e+1] delimit expert e's rows; src_token[row] = token feeding sorted row; dest[i] = row or -1.
 __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
                                                           int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ int count[MAX_E + 1];
     __shared__ int offs[MAX_E + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -208,6 +220,8 @@ __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restric
 __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
                                    const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
                                    int d) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < d / 8; i += blockDim.x) {
         float acc[8];
@@ -261,19 +275,19 @@ inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAU
 extern "C" {
 
 int jib_moe_gate(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int T, int d,
-                 int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, void * stream) {
+                 int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, int n_shared, void * stream) {
     if (T <= 0) return 0;
-    if (E > MAX_E || k > 32 || k > E || d % 4 || d > GATE_MAXV * GATE_NT * 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
-    router_logits_kernel<<<dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream>>>((const bf16 *) g, w_router, logits, T, d, E);
+    if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 4 || d > GATE_MAXV * GATE_NT * 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
+    JIB_LAUNCH((router_logits_kernel), dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, logits, T, d, E);
     if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;
-    moe_gate_kernel<<<T, 32, 0, (cudaStream_t) stream>>>(logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid);
+    JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared);
     return launched();
 }
 
 int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest, void * stream) {
     if (T <= 0) return 0;
     if (E_local > MAX_E) return JIB_E_ARG;
-    moe_permute_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(ids, T * k, k, expert_base, E_local, seg, src_token, dest);
+    JIB_LAUNCH((moe_permute_kernel), 1, 1024, 0, (cudaStream_t) stream, ids, T * k, k, expert_base, E_local, seg, src_token, dest);
     return launched();
 }
 
@@ -281,7 +295,7 @@ int jib_moe_combine(const void * y, const int * dest, const float * wts, const v
                     int k, int d, void * stream) {
     if (T <= 0) return 0;
     if (d % 8) return JIB_E_ARG;
-    moe_combine_kernel<<<T, 256, 0, (cudaStream_t) stream>>>((const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual,
+    JIB_LAUNCH((moe_combine_kernel), T, 256, 0, (cudaStream_t) stream, (const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual,
                                                               (bf16 *) out, k, d);
     return launched();
 }

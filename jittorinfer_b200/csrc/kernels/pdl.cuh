@@ -1,0 +1,67 @@
+// Programmatic dependent launch (PDL) helpers.
+//
+// Every kernel of the library is launched with the "programmatic stream serialization" attribute: its CTAs may
+// become resident while the previous kernel on the stream is still draining, run their prologue (barrier
+// initialisation, TMEM allocation, tensor-map prefetch, reading launch-invariant inputs) and then block in
+// pdl_wait() until the previous grid has completed and its writes are visible.  Rules every kernel follows:
+//   * pdl_launch_dependents() first thing (lets the next kernel's CTAs be scheduled early);
+//   * pdl_wait() before the first read of anything an earlier kernel produced, before ANY global write, and on
+//     every path that leaves the kernel — the chain "N waits for N-1" is what orders N against all earlier work.
+// Captured into CUDA graphs the attribute becomes a programmatic dependency edge.  JIB_PDL=0 turns it off.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdlib.h>
+#include <string.h>
+#include <utility>
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+namespace jib {
+
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char * e = getenv("JIB_PDL");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
+}
+
+// cluster_z > 1: consecutive blockIdx.z values form a thread-block cluster of that size.
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl_cluster(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_z,
+                                      A &&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned) cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<A>(args)...);
+}
+
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A &&... args) {
+    return launch_pdl_cluster(kern, grid, block, smem, stream, 1, std::forward<A>(args)...);
+}
+
+}  // namespace jib
+
+// kern may contain template commas: pass it in parentheses, e.g. JIB_LAUNCH((rmsnorm_kernel<256, 4>), grid, ...)
+#define JIB_LAUNCH(kern, grid, block, smem, stream, ...) (void) jib::launch_pdl(kern, dim3(grid), dim3(block), smem, stream, __VA_ARGS__)

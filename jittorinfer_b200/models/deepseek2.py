@@ -55,7 +55,7 @@ class ForwardBatch:
 class _Layer:
     __slots__ = ("attn_norm", "w_qkv_a", "q_a_norm", "w_q_b", "kv_a_norm", "w_uk", "w_uv", "w_o", "ffn_norm",
                  "w_gate", "w_up", "w_down", "w_router", "router_bias", "w_gate_exps", "w_up_exps", "w_down_exps",
-                 "w_gate_sh", "w_up_sh", "w_down_sh", "is_moe")
+                 "w_gate_sh", "w_up_sh", "w_down_sh", "is_moe", "n_shared_merged")
 
     def __init__(self):
         for s in self.__slots__:
@@ -165,6 +165,19 @@ class DeepSeek2Model:
                 raise KeyError(f"unknown tensor {name}")
         if self.w_out is None:
             self.w_out = self.tok_embd
+        if not self.spec.sharded:
+            # single-GPU: the shared experts have the routed experts' shape, so they become experts E, E+1, ... of the
+            # grouped GEMMs (two fewer launches per layer, better fill); the router appends them to every token
+            F = hp.n_ff_exp
+            for L in self.layers:
+                L.n_shared_merged = 0
+                if L.is_moe and L.w_gate_sh is not None and L.w_gate_sh.shape[0] % F == 0:
+                    ns, d = L.w_gate_sh.shape[0] // F, hp.n_embd
+                    L.w_gate_exps = torch.cat([L.w_gate_exps, L.w_gate_sh.view(ns, F, d)], dim=0)
+                    L.w_up_exps = torch.cat([L.w_up_exps, L.w_up_sh.view(ns, F, d)], dim=0)
+                    L.w_down_exps = torch.cat([L.w_down_exps, L.w_down_sh.view(d, ns, F).permute(1, 0, 2).contiguous()], dim=0)
+                    L.w_gate_sh = L.w_up_sh = L.w_down_sh = None
+                    L.n_shared_merged = ns
         for il, L in enumerate(self.layers):
             need = ["attn_norm", "w_qkv_a", "kv_a_norm", "w_uk", "w_o", "ffn_norm"]
             need += ["w_router", "w_gate_exps", "w_up_exps", "w_down_exps"] if L.is_moe else ["w_gate", "w_up", "w_down"]
@@ -222,7 +235,8 @@ class DeepSeek2Model:
             hmid = ops.gateup_silu(g, L.w_gate, L.w_up)
             return self._row_parallel(hmid, L.w_down, residual)
         ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
-                                hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid")
+                                hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid",
+                                L.n_shared_merged or 0)
         base = self.expert_base if self.spec.expert_parallel else 0
         if self.comm is not None and self.spec.sharded:
             part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,

@@ -140,7 +140,7 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tens
 
 
 def moe_gate(g: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], k: int, n_group: int,
-             topk_group: int, scale: float, norm: bool, sigmoid: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+             topk_group: int, scale: float, norm: bool, sigmoid: bool, n_shared: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Router matmul (fp32) + softmax/sigmoid + [group-limited] top-k + renorm/scale
     (src/llama-graph-ffn.cpp:145-197).  Returns ids [T,k] int32, weights [T,k] fp32."""
     logits = g.float() @ w_router.float().T
@@ -156,7 +156,12 @@ def moe_gate(g: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tenso
     w = torch.gather(probs, 1, ids)
     if norm:
         w = w / w.sum(-1, keepdim=True)
-    return ids.int(), (w * scale).float()
+    ids, w = ids.int(), (w * scale).float()
+    if n_shared:        # shared experts as always-selected experts E, E+1, ... with weight 1
+        sh = torch.arange(E, E + n_shared, dtype=torch.int32, device=ids.device)[None].expand(T, n_shared)
+        ids = torch.cat([ids, sh], dim=1)
+        w = torch.cat([w, torch.ones(T, n_shared, dtype=w.dtype, device=w.device)], dim=1)
+    return ids.contiguous(), w.contiguous()
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor,

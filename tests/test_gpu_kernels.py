@@ -134,6 +134,12 @@ def test_moe_gate(nat, E, k, ng, tg, sig):
     ids, w = nat.moe_gate(g, wr, None, k, ng, tg, 1.0, True, sig)
     ids2, w2 = ref.moe_gate(g, wr, None, k, ng, tg, 1.0, True, sig)
     close(w, w2, tol=1e-4)
+    # shared experts appended as always-selected experts E, E+1 with weight 1
+    ids, w = nat.moe_gate(g, wr, None, k, ng, tg, 16.0, False, sig, 2)
+    ids2, w2 = ref.moe_gate(g, wr, None, k, ng, tg, 16.0, False, sig, 2)
+    assert ids.shape == (T, k + 2) and torch.equal(ids.cpu(), ids2.cpu())
+    assert torch.equal(ids[:, k:].cpu(), torch.tensor([[E, E + 1]], dtype=torch.int32).expand(T, 2))
+    close(w, w2, tol=1e-4)
 
 
 @pytest.mark.parametrize("d", [512, 1536, 2048, 5120])
