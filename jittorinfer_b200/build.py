@@ -25,6 +25,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 RUNTIME_SO = os.path.join(LIBDIR, "libjib200_runtime.so")
 KERNELS_SO = os.path.join(LIBDIR, "libjib200_kernels.so")
+LLAMA_SO = os.path.join(LIBDIR, "libllama.so")
 
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
@@ -82,6 +83,45 @@ def build_runtime(force: bool = False, verbose: bool = False) -> str:
     return RUNTIME_SO
 
 
+def python_embed_flags() -> tuple:
+    """(include flags, link flags) for embedding the interpreter this module runs under."""
+    import sysconfig
+    inc = ["-I", sysconfig.get_paths()["include"]]
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    link = ([f"-L{libdir}", f"-Wl,-rpath,{libdir}"] if libdir else []) + [f"-lpython{ver}"]
+    return inc, link
+
+
+def build_capi(force: bool = False, verbose: bool = False) -> str:
+    """libllama.so: the llama.h C API (native GGUF / tokenizer / samplers / KV bookkeeping + the embedded-Python bridge)."""
+    rt = [os.path.join(CSRC, "runtime", f) for f in ("gguf.cpp", "kv_paged.cpp", "tokenizer.cpp")]
+    srcs = sorted(glob.glob(os.path.join(CSRC, "capi", "*.cpp"))) + rt
+    deps = srcs + glob.glob(os.path.join(CSRC, "capi", "*.h")) + glob.glob(os.path.join(CSRC, "runtime", "*.h")) + \
+        glob.glob(os.path.join(CSRC, "runtime", "*.inc")) + glob.glob(os.path.join(CSRC, "include", "*.h"))
+    os.makedirs(LIBDIR, exist_ok=True)
+    if force or _newer(deps, LLAMA_SO):
+        inc, link = python_embed_flags()
+        objdir = os.path.join(LIBDIR, "obj_capi")
+        os.makedirs(objdir, exist_ok=True)
+        objs, procs = [], []
+        for s in srcs:
+            o = os.path.join(objdir, os.path.basename(s) + ".o")
+            objs.append(o)
+            cmd = ["g++", "-std=c++17", "-O2", "-g", "-fPIC", "-fvisibility=hidden", "-DLLAMA_BUILD", "-Wall", "-Wno-unused-function",
+                   "-I", os.path.join(CSRC, "include"), "-I", os.path.join(CSRC, "runtime"), *inc, "-c", s, "-o", o]
+            if verbose:
+                print(" ".join(cmd), flush=True)
+            procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        for cmd, p in procs:
+            out, _ = p.communicate()
+            if p.returncode != 0:
+                sys.stderr.write(out)
+                raise RuntimeError(f"build failed: {cmd[-3]}")
+        _run(["g++", "-shared", "-o", LLAMA_SO] + objs + link + ["-lpthread", "-ldl"], verbose)
+    return LLAMA_SO
+
+
 def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[str] = ()) -> str:
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
     hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h"))
@@ -118,7 +158,7 @@ def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[
 
 
 def build_all(force: bool = False, verbose: bool = False):
-    return build_runtime(force, verbose), build_kernels(force, verbose)
+    return build_runtime(force, verbose), build_kernels(force, verbose), build_capi(force, verbose)
 
 
 if __name__ == "__main__":
