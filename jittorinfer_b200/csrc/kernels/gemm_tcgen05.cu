@@ -56,6 +56,8 @@ struct GemmArgs {
     JibArCtx ar;              // peer-memory all-reduce fused into the epilogue (ar_on != 0)
     int ar_on, ar_site;
     int cluster_split;        // 1: the `splits` CTAs of a tile form a thread-block cluster and reduce through DSMEM
+    void * const * row_ptr;   // null, or per output row the address of its bf16 row (rows scattered to other buffers,
+                              // possibly on other GPUs: the expert-parallel return path)
 };
 
 template <int BN, bool DUAL>
@@ -328,6 +330,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             for (int p = 0; p < args.ar.world; ++p) args.ar.recv[p][off] = y;
                             continue;
                         }
+                        if (args.row_ptr != nullptr) {
+                            __nv_bfloat16 * dst = (__nv_bfloat16 *) __ldg((const unsigned long long *) args.row_ptr + row);
+                            if (dst != nullptr) dst[n] = __float2bfloat16(y);
+                            continue;
+                        }
                         if (args.residual != nullptr) {
                             const long long ri = rbase + row * args.ldr + n;
                             y += args.res_f32 ? ((const float *) args.residual)[ri]
@@ -530,6 +537,8 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     a.scratch_elems = (long long) (d->scratch_bytes / sizeof(float));
     a.ar_on = 0; a.ar_site = 0;
     a.cluster_split = cluster_split ? 1 : 0;
+    a.row_ptr = (void * const *) d->out_row_ptr;
+    if (a.row_ptr != nullptr && (dual || d->out_f32 || d->residual != nullptr || d->ar != nullptr)) return JIB_E_ARG;
     memset(&a.ar, 0, sizeof(a.ar));
     if (d->ar != nullptr) {
         const JibArCtx * ar = (const JibArCtx *) d->ar;
@@ -666,6 +675,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.scratch_elems = (long long) (JIB_NOALLOC_SCRATCH_BYTES / sizeof(float));
     a.ar_on = 0; a.ar_site = 0;
     a.cluster_split = 0;
+    a.row_ptr = nullptr;
     memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);
     switch (p.bn) {

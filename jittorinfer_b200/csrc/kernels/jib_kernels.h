@@ -46,6 +46,8 @@ typedef struct jib_gemm_desc {
     int sm_count;
     int ar_site;               // fused all-reduce: call-site index (see comm_fused.cu)
     const void * ar;           // NULL, or a JibArCtx: the epilogue sums the tile over all ranks through peer memory
+    const void * out_row_ptr;  // NULL, or device array [rows] of bf16 row addresses (may be peer memory): row i of the result is
+                               // stored there instead of out + i * ldo (a NULL entry drops the row)
 } jib_gemm_desc;
 
 JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);
@@ -89,6 +91,13 @@ JIB_EXPORT int jib_mla_combine(const float * part_o, const float * part_ml, int 
 JIB_EXPORT int jib_mla_flash(const void * q, const void * cache, long long n_slots, const int * block_tables, int max_blocks,
                              const int * seq_lens, const int * q_start, int n_seqs, int T, int H, float scale, int n_splits, int qt,
                              float * part_o, float * part_ml, void * o_lat, int * status, void * stream);
+
+// ---- expert-parallel all-to-all over peer memory (ep_alltoall.cu); ctx is a JibEpCtx (ep_alltoall.h) ---------
+JIB_EXPORT int jib_ep_plan(const int * ids, int T, int k, const struct JibEpCtx * ctx, int site, int * seg, int * pair_dst, void * stream);
+JIB_EXPORT int jib_ep_push(const void * x, const int * pair_dst, int T, int k, const struct JibEpCtx * ctx, int site, const int * seg,
+                           int * done_counter, void * row_ptr, void * stream);
+JIB_EXPORT int jib_ep_combine(const float * wts, const int * pair_dst, const void * shared, const void * residual, void * out, int T,
+                              int k, const struct JibEpCtx * ctx, int site, void * stream);
 
 #ifdef __cplusplus
 }

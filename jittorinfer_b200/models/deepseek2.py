@@ -65,17 +65,23 @@ class _Layer:
 class DeepSeek2Model:
     def __init__(self, hp: DeepSeek2HParams, weights: Iterable[Tuple[str, torch.Tensor]],
                  dtype: torch.dtype = torch.bfloat16, device="cpu", spec: ShardSpec = ShardSpec(),
-                 comm=None, max_positions: int = 8192, block_size: int = 64):
+                 comm=None, max_positions: int = 8192, block_size: int = 64, ep=None):
         self.hp = hp
         self.dtype = dtype
         self.device = torch.device(device)
         self.spec = spec
         self.comm = comm
+        self.ep = ep                      # all-to-all dispatcher (data-parallel attention + expert parallelism)
         self.block_size = block_size
-        if hp.n_head % spec.tp_size:
-            raise ValueError("n_head must be divisible by tp_size")
-        self.n_head_local = hp.n_head // spec.tp_size
-        if spec.expert_parallel:
+        if spec.dp_attention:
+            if ep is None and spec.sharded:
+                raise ValueError("dp_attention needs an expert-parallel dispatcher (ep=...)")
+            self.n_head_local = hp.n_head
+        else:
+            if hp.n_head % spec.tp_size:
+                raise ValueError("n_head must be divisible by tp_size")
+            self.n_head_local = hp.n_head // spec.tp_size
+        if spec.expert_parallel or spec.dp_attention:
             if hp.n_expert % spec.tp_size:
                 raise ValueError("n_expert must be divisible by the expert-parallel size")
             self.n_expert_local = hp.n_expert // spec.tp_size
@@ -205,7 +211,7 @@ class DeepSeek2Model:
 
     def _row_parallel(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
         """y = all_reduce(x_shard @ w_shard^T) + residual.  One fused kernel when the communicator has it."""
-        if self.comm is not None and self.spec.sharded:
+        if self.comm is not None and self.spec.sharded and not self.spec.dp_attention:
             return self.comm.linear_all_reduce(x, w, residual)
         return ops.linear(x, w, residual=residual)
 
@@ -237,6 +243,11 @@ class DeepSeek2Model:
         ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
                                 hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid",
                                 L.n_shared_merged or 0)
+        if self.spec.dp_attention and self.spec.sharded:
+            shared = None
+            if L.w_gate_sh is not None:
+                shared = ops.linear(ops.gateup_silu(g, L.w_gate_sh, L.w_up_sh), L.w_down_sh)
+            return self.ep.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, shared)
         base = self.expert_base if self.spec.expert_parallel else 0
         if self.comm is not None and self.spec.sharded:
             part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
@@ -245,12 +256,29 @@ class DeepSeek2Model:
         return ops.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                            L.w_down_sh, base)
 
+    def _forward_idle(self) -> None:
+        """A data-parallel rank without tokens still serves its experts to the other ranks: it joins every MoE
+        layer's dispatch / combine with zero rows (the reference's llama_empty_run, src/llama-execute-decode.cpp:367-394)."""
+        hp = self.hp
+        x = torch.empty(0, hp.n_embd, dtype=self.dtype, device=self.device)
+        ids = torch.empty(0, hp.n_expert_used, dtype=torch.int32, device=self.device)
+        wts = torch.empty(0, hp.n_expert_used, dtype=torch.float32, device=self.device)
+        for L in self.layers:
+            if L.is_moe:
+                self.ep.moe_ffn(x, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, None)
+        return None
+
     @torch.no_grad()
-    def forward(self, batch: ForwardBatch, kv_cache: torch.Tensor) -> torch.Tensor:
-        """kv_cache [n_layer, n_slots, r+dr].  Returns fp32 logits [len(out_rows), n_vocab]."""
+    def forward(self, batch: Optional[ForwardBatch], kv_cache: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """kv_cache [n_layer, n_slots, r+dr].  Returns fp32 logits [len(out_rows), n_vocab].
+        ``batch=None`` (data-parallel attention only): this rank has no tokens in this step."""
         hp = self.hp
         if self.comm is not None:
             self.comm.begin_step()
+        if self.ep is not None:
+            self.ep.begin_step()
+        if batch is None:
+            return self._forward_idle()
         x = ops.embed_gather(self.tok_embd, batch.tokens)
         for il, L in enumerate(self.layers):
             h, _ = ops.rmsnorm(x, L.attn_norm, hp.rms_eps)

@@ -29,6 +29,8 @@ class ShardSpec:
     tp_rank: int = 0
     tp_size: int = 1
     expert_parallel: bool = False     # routed experts split on the expert axis over the tp group
+    dp_attention: bool = False        # attention / dense / shared experts replicated (every rank has its own tokens);
+                                      # only the routed experts are sharded, on the expert axis
 
     @property
     def sharded(self) -> bool:
@@ -77,6 +79,8 @@ def shard_dim(name: str, spec: ShardSpec) -> Optional[int]:
     if not spec.sharded:
         return None
     base = name.split(".")[-2] if name.startswith("blk.") else name
+    if spec.dp_attention:
+        return 0 if base in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps") else None
     if base in ("attn_q", "attn_q_b", "attn_kv_b", "ffn_gate", "ffn_up", "ffn_gate_shexp", "ffn_up_shexp"):
         return 0
     if base in ("attn_output", "ffn_down", "ffn_down_shexp"):

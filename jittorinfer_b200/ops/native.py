@@ -26,7 +26,7 @@ class GemmDesc(C.Structure):
                                             "out_batch_stride", "ldr", "res_batch_stride", "x_rows_total")] + \
                [("scratch_bytes", C.c_size_t)] + \
                [(n, C.c_int) for n in ("n_counters", "T", "N", "K", "batch", "max_rows", "active_hint", "out_f32", "res_f32",
-                                       "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p)]
+                                       "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p), ("out_row_ptr", C.c_void_p)]
 
 
 def load():
@@ -159,23 +159,35 @@ def gemm_batched(x_ptr: int, x_row_stride: int, x_batch_stride: int, w: torch.Te
     _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_batched")
 
 
+def gemm_grouped_raw(x_ptr: int, x_rows_total: int, K: int, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor],
+                     max_rows: int, active_hint: int, splits: int = 0, bn: int = 0, device=None,
+                     out_row_ptr: Optional[int] = None) -> Optional[torch.Tensor]:
+    """Grouped GEMM over a raw row buffer (e.g. a peer-mapped receive buffer).  With ``out_row_ptr`` (device array of
+    row addresses) every result row is stored through its pointer and nothing is returned."""
+    E, N, K2 = w.shape
+    assert K2 == K
+    device = device or w.device
+    out = None if out_row_ptr else torch.empty(x_rows_total, N, dtype=torch.bfloat16, device=device)
+    ws = workspace(device)
+    d = GemmDesc()
+    d.x, d.w, d.w2, d.residual = x_ptr, w.data_ptr(), _p(w2), None
+    d.out = out.data_ptr() if out is not None else ws.scratch.data_ptr()     # unused when rows go through pointers
+    d.seg, d.scratch, d.counters, d.status = seg.data_ptr(), ws.scratch.data_ptr(), ws.counters.data_ptr(), ws.status.data_ptr()
+    d.x_row_stride, d.x_batch_stride, d.w_row_stride, d.w_batch_stride = K, 0, K, N * K
+    d.ldo, d.out_batch_stride, d.ldr, d.res_batch_stride = N, 0, 0, 0
+    d.x_rows_total, d.scratch_bytes, d.n_counters = x_rows_total, ws.SCRATCH_BYTES, ws.N_COUNTERS
+    d.T, d.N, d.K, d.batch, d.max_rows, d.active_hint = max_rows, N, K, E, max_rows, active_hint
+    d.out_f32, d.res_f32, d.splits, d.bn, d.sm_count = 0, 0, splits, bn, ws.sm_count
+    d.out_row_ptr = out_row_ptr
+    _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_grouped")
+    return out
+
+
 def gemm_grouped(xp: torch.Tensor, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor], max_rows: int,
                  active_hint: int, splits: int = 0) -> torch.Tensor:
     """Rows of xp are sorted by expert; expert e owns rows seg[e]:seg[e+1] and weight w[e] ([E,N,K])."""
-    E, N, K = w.shape
-    R = xp.shape[0]
-    out = torch.empty(R, N, dtype=torch.bfloat16, device=xp.device)
-    ws = workspace(xp.device)
-    d = GemmDesc()
-    d.x, d.w, d.w2, d.out, d.residual = xp.data_ptr(), w.data_ptr(), _p(w2), out.data_ptr(), None
-    d.seg, d.scratch, d.counters, d.status = seg.data_ptr(), ws.scratch.data_ptr(), ws.counters.data_ptr(), ws.status.data_ptr()
-    d.x_row_stride, d.x_batch_stride, d.w_row_stride, d.w_batch_stride = xp.stride(0), 0, K, N * K
-    d.ldo, d.out_batch_stride, d.ldr, d.res_batch_stride = N, 0, 0, 0
-    d.x_rows_total, d.scratch_bytes, d.n_counters = R, ws.SCRATCH_BYTES, ws.N_COUNTERS
-    d.T, d.N, d.K, d.batch, d.max_rows, d.active_hint = max_rows, N, K, E, max_rows, active_hint
-    d.out_f32, d.res_f32, d.splits, d.bn, d.sm_count = 0, 0, splits, 0, ws.sm_count
-    _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_grouped")
-    return out
+    assert xp.stride(0) == xp.shape[1] and xp.stride(1) == 1
+    return gemm_grouped_raw(xp.data_ptr(), xp.shape[0], xp.shape[1], seg, w, w2, max_rows, active_hint, splits, device=xp.device)
 
 
 def linear(x, w, residual=None, out_dtype=None):
