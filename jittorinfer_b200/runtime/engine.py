@@ -124,6 +124,15 @@ class LLMEngine:
                       "h2d_bytes": 0, "d2h_bytes": 0, "defrag_moves": 0}
         self.graph_launches: Dict[Tuple[int, str], int] = {}    # launcher calls captured per decode graph
         self.launches = 0                                          # launcher calls executed (eager + replayed)
+        # Data-parallel attention + expert parallelism: every rank schedules its own requests, but the MoE layers are
+        # collective, so all ranks step together; a rank without tokens runs the idle forward.  Each step all-reduces
+        # an "I still have work" flag (the reference gathers per-rank token counts every decode for the same purpose,
+        # src/llama-context.cpp:538-556).
+        spec = getattr(model, "spec", None)
+        self.dp = bool(spec is not None and spec.dp_attention and spec.sharded)
+        self.dp_active = spec.tp_size if self.dp else 0
+        self._dp_flag = torch.zeros(1, dtype=torch.int32, device=self.device) if self.dp else None
+        self._idle_graph = None
 
     # ------------------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -187,10 +196,37 @@ class LLMEngine:
         if not ops.force_torch():
             self.graph_launches[key] = ops.nat().launch_count - n0
         self._graphs[key] = (g, out)
+        self._host_barrier()             # capture time differs per rank; re-align before the first replay
+        return self._graphs[key]
+
+    def _host_barrier(self):
         comm = getattr(self.model, "comm", None)
         if comm is not None and hasattr(comm, "host_barrier"):
-            comm.host_barrier()          # capture time differs per rank; re-align before the first replay
-        return self._graphs[key]
+            comm.host_barrier()
+        elif self.dp:
+            import torch.distributed as dist
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            dist.barrier()
+
+    def _idle_forward(self):
+        """This rank has no tokens in this step but must serve its experts to the others."""
+        if self._idle_graph is not None:
+            self._idle_graph.replay()
+        else:
+            self.model.forward(None, None)
+
+    def run_until_all_idle(self, max_steps: int = 1 << 30) -> int:
+        """Data-parallel serving loop: step until no rank has work left.  Every rank leaves at the same step."""
+        n = 0
+        while n < max_steps:
+            self.step()
+            n += 1
+            if not self.dp and not self.has_work():
+                break
+            if self.dp and self.dp_active == 0:
+                break
+        return n
 
     def warmup(self, modes: Iterable[str] = ("greedy",)):
         """Capture the decode graphs up front (the reference compiles its GE graph at context creation)."""
@@ -206,6 +242,20 @@ class LLMEngine:
             if b <= self.io.cap_seqs:
                 for m in modes:
                     self._graph_for(b, m)
+        if self.dp and self._idle_graph is None:
+            # every rank runs the same sequence here (two warm-up passes, one capture), so the collectives pair up
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(s):
+                for _ in range(2):
+                    self.model.forward(None, None)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.model.forward(None, None)
+            self._idle_graph = g
+            self._host_barrier()
 
     # ------------------------------------------------------------------------------------------
     def _maybe_defrag(self):
@@ -247,7 +297,15 @@ class LLMEngine:
         io = self.io
         info = self.sched.step(io.arrays)
         n_tokens, n_seqs, n_out, n_dec, max_q, _, n_copies = (int(x) for x in info[:7])
+        if self.dp:
+            import torch.distributed as dist
+            self._dp_flag.fill_(1 if (n_tokens > 0 or self.has_work()) else 0)
+            dist.all_reduce(self._dp_flag)
         if n_tokens == 0:
+            if self.dp:
+                self._idle_forward()
+                self.dp_active = int(self._dp_flag.item())
+                self.stats["idle_steps"] = self.stats.get("idle_steps", 0) + 1
             return self._drain_events()
         if n_copies:
             src, dst = self.kv.take_copies()
@@ -255,6 +313,9 @@ class LLMEngine:
         states = [self.requests[int(r)] for r in self.sched.out_reqs(n_out)] if n_out else []
         mode = "greedy" if all(s.sampler is None for s in states) else "topk"
         use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets)
+        if use_graph and self.dp:
+            # ranks capture in lockstep during warmup() only: a capture on first use would run collectives alone
+            use_graph = (next(b for b in self.cfg.graph_buckets if b >= n_seqs), mode) in self._graphs
         if use_graph:
             bucket = next(b for b in self.cfg.graph_buckets if b >= n_seqs)
             h = io.h
@@ -312,6 +373,8 @@ class LLMEngine:
             self.stats["tokens_out"] += n_out
         else:
             self.sched.commit(np.empty(0, dtype=np.int32), 0)
+        if self.dp:
+            self.dp_active = int(self._dp_flag.item())
         ev = self._drain_events()
         self._maybe_defrag()
         return ev
@@ -326,6 +389,8 @@ class LLMEngine:
             if max_new_tokens is not None:
                 sp = SamplingParams(**{**sp.__dict__, "max_tokens": max_new_tokens})
             ids.append(self.add_request(p, sp))
+        if self.dp:
+            self.run_until_all_idle()
         while self.has_work():
             self.step()
         outs = [self.requests[i].output for i in ids]

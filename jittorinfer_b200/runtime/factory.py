@@ -17,9 +17,12 @@ from .engine import EngineConfig, LLMEngine
 
 def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] = None, device="cuda",
                 dtype: torch.dtype = torch.bfloat16, world: int = 1, rank: int = 0, expert_parallel: bool = True,
-                comm=None, seed: int = 0, std: float = 0.02, max_positions: int = 8192, fast_random: bool = True
-                ) -> DeepSeek2Model:
-    spec = ShardSpec(rank, world, expert_parallel and world > 1)
+                comm=None, seed: int = 0, std: float = 0.02, max_positions: int = 8192, fast_random: bool = True,
+                dp_attention: bool = False, ep_max_tokens: int = 256) -> DeepSeek2Model:
+    """``dp_attention``: attention data-parallel (every rank serves its own requests), routed experts sharded over the
+    ranks and reached through the all-to-all dispatcher; ``ep_max_tokens`` bounds the tokens of one rank per step."""
+    dp_attention = dp_attention and world > 1
+    spec = ShardSpec(rank, world, (expert_parallel or dp_attention) and world > 1, dp_attention)
     if gguf_path is not None:
         from ..gguf.io import GGUFReader
         reader = GGUFReader(gguf_path)
@@ -30,19 +33,26 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
         dev = torch.device(device)
         weights = iter_random(hp, spec=spec, seed=seed, std=std, dtype=dtype if dev.type == "cuda" else torch.float32,
                               device=dev, fast=fast_random and dev.type == "cuda")
-    if world > 1 and comm is None:
+    ep = None
+    if dp_attention:
+        from ..parallel.ep import make_ep_dispatcher
+        ep = make_ep_dispatcher(torch.device(device), world, rank, hp.n_expert, hp.n_embd, hp.n_expert_used,
+                                hp.n_layer - hp.n_layer_dense_lead, max_tokens=ep_max_tokens)
+    elif world > 1 and comm is None:
         from ..parallel.comm import make_communicator
         comm = make_communicator(torch.device(device), world, rank, hp.n_embd, hp.n_layer)
-    return DeepSeek2Model(hp, weights, dtype=dtype, device=device, spec=spec, comm=comm, max_positions=max_positions)
+    return DeepSeek2Model(hp, weights, dtype=dtype, device=device, spec=spec, comm=comm, max_positions=max_positions, ep=ep)
 
 
 def build_engine(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] = None, device="cuda",
                  dtype: torch.dtype = torch.bfloat16, world: int = 1, rank: int = 0, n_parallel: int = 8,
                  n_ctx_slot: int = 2048, n_batch: int = 2048, seed: int = 0, graph_buckets: Sequence[int] = (1, 2, 4, 8),
                  cuda_graphs: bool = True, expert_parallel: bool = True, comm=None, n_ctx: Optional[int] = None,
-                 **engine_kw) -> LLMEngine:
+                 dp_attention: bool = False, ep_max_tokens: int = 256, **engine_kw) -> LLMEngine:
+    if dp_attention and world > 1:
+        n_batch = min(n_batch, ep_max_tokens)          # a step's tokens must fit the dispatcher's buffers
     model = build_model(hp, gguf_path, device, dtype, world, rank, expert_parallel, comm, seed,
-                        max_positions=max(n_ctx_slot, 64))
+                        max_positions=max(n_ctx_slot, 64), dp_attention=dp_attention, ep_max_tokens=ep_max_tokens)
     cfg = EngineConfig(n_ctx=n_ctx or n_ctx_slot * n_parallel, n_batch=n_batch, n_parallel=n_parallel, n_ctx_slot=n_ctx_slot,
                        graph_buckets=tuple(graph_buckets), cuda_graphs=cuda_graphs, **engine_kw)
     return LLMEngine(model, cfg)

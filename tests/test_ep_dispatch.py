@@ -90,11 +90,53 @@ def _worker(rank, world, port, backend, comm_impl, q):
         raise
 
 
-def _run(world, backend, comm_impl, timeout=180):
+def _engine_worker(rank, world, port, backend, comm_impl, q):
+    """Every rank serves its own requests through its own scheduler; the engines step together."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), JITTORINFER_COMM=comm_impl, NCCL_NVLS_ENABLE="0")
+    try:
+        from jittorinfer_b200.models.hparams import preset
+        from jittorinfer_b200.runtime.sampling import SamplingParams
+        gpu = backend == "nccl"
+        dev = torch.device("cuda", rank) if gpu else torch.device("cpu")
+        if gpu:
+            torch.cuda.set_device(dev)
+            dist.init_process_group(backend, rank=rank, world_size=world, device_id=dev)
+        else:
+            dist.init_process_group(backend, rank=rank, world_size=world)
+        hp = preset("tiny-v2")
+        from jittorinfer_b200.runtime.factory import build_model
+        from jittorinfer_b200.runtime.engine import EngineConfig, LLMEngine
+        model = build_model(hp, device=dev, dtype=torch.bfloat16 if gpu else torch.float32, world=world, rank=rank, std=0.05,
+                            max_positions=256, dp_attention=True, ep_max_tokens=64, fast_random=False)
+        eng = LLMEngine(model, EngineConfig(n_ctx=512, n_batch=48, n_parallel=2, graph_buckets=(1, 2), cuda_graphs=gpu))
+        eng.warmup()
+        prompts = _prompts(hp)
+        mine = [prompts[i] for i in range(len(prompts)) if i % world == rank]          # rank 0: prompts 0, 2; rank 1: 1, 3
+        news = [N_NEW[i] for i in range(len(prompts)) if i % world == rank]
+        ids = [eng.add_request(p, SamplingParams(ignore_eos=True, max_tokens=n)) for p, n in zip(mine, news)]
+        steps = eng.run_until_all_idle()
+        outs = [eng.requests[i].output for i in ids]
+        if gpu:
+            torch.cuda.synchronize()
+            from jittorinfer_b200.ops import native
+            native.check_status()
+        q.put((rank, outs, steps, eng.stats.get("idle_steps", 0), eng.stats["graph_steps"]))
+        dist.barrier()
+        model.ep.close()
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, "ERROR: " + traceback.format_exc(), 0, 0, 0))
+        raise
+
+
+def _run(world, backend, comm_impl, timeout=180, target=None):
+    target = target or _worker
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, backend, comm_impl, q)) for r in range(world)]
+    procs = [ctx.Process(target=target, args=(r, world, port, backend, comm_impl, q)) for r in range(world)]
     for p in procs:
         p.start()
     try:
@@ -128,6 +170,14 @@ def test_dp_attention_ep_two_cpu_ranks_match_oracle():
     assert res[0][2] > 0 and not res[0][3]
 
 
+def test_dp_engines_step_together_cpu():
+    res = _run(2, "gloo", "nccl", target=_engine_worker)
+    ref = _oracle(4, False)
+    assert res[0][1] == [ref[0], ref[2]] and res[1][1] == [ref[1], ref[3]]
+    assert res[0][2] == res[1][2]                      # both ranks left the loop at the same step
+    assert res[0][3] + res[1][3] > 0                   # the rank that finished first kept stepping idle
+
+
 def _agree(got, ref):
     # bf16 can flip an arg-max between near-equal logits; from then on the sequences differ legitimately
     n = 0
@@ -148,6 +198,19 @@ def test_dp_attention_ep_two_gpus(comm_impl):
     assert res[0][3] == (comm_impl == "fused")
     for r, want in zip(res, ref):
         assert _agree(r[1], want) >= min(4, len(want)), (r[1], want)
+
+
+@pytest.mark.gpu
+def test_dp_engines_fused_graphs_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, "nccl", "fused", target=_engine_worker)
+    ref = _oracle(4, True)
+    want = [[ref[0], ref[2]], [ref[1], ref[3]]]
+    for r, w in zip(res, want):
+        for got, exp in zip(r[1], w):
+            assert len(got) == len(exp) and _agree(got, exp) >= min(3, len(exp)), (got, exp)
+    assert res[0][2] == res[1][2] and res[0][4] > 0    # same step count; decode steps were graph replays
 
 
 @pytest.mark.gpu
