@@ -85,6 +85,62 @@ __global__ void __launch_bounds__(128) allreduce_oneshot_kernel(const TIn * __re
     }
 }
 
+// Two-shot variant for large T: one CTA per (32 rows, 512 features) tile.  The tile's partials go to one owner rank
+// (tile % world), which reduces them in rank order, adds the residual and stores the bf16 result into every rank's
+// result buffer (ar.out2); every rank's CTA of that tile returns once the owner has delivered.
+template <typename TIn>
+__global__ void __launch_bounds__(128) allreduce_twoshot_kernel(const TIn * __restrict__ x, const bf16 * __restrict__ residual, int T, int d,
+                                                                JibArCtx ar, int site) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const unsigned epoch = *ar.epoch;
+    const int parity = (site + (int) (epoch % 2u) * (ar.n_sites & 1)) & 1;
+    const int f0 = blockIdx.x * 512, r0 = blockIdx.y * 32;
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    const int owner = tile % ar.world;
+    const int f = f0 + threadIdx.x * 4;
+    const int rows = min(32, T - r0);
+    const size_t half = (size_t) ar.world * ar.max_rows2 * ar.d_max;
+    const size_t ohalf = (size_t) ar.max_rows2 * ar.d_max;
+    if (f < d) {
+        float * dst = ar.recv2[owner] + (size_t) parity * half;
+        for (int j = 0; j < rows; ++j) {
+            float4 v;
+            if (sizeof(TIn) == 4) {
+                v = *(const float4 *) ((const float *) x + (size_t) (r0 + j) * d + f);
+            } else {
+                const uint2 raw = *(const uint2 *) ((const bf16 *) x + (size_t) (r0 + j) * d + f);
+                const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                v = make_float4(a.x, a.y, b.x, b.y);
+            }
+            *(float4 *) (dst + ((size_t) ar.rank * ar.max_rows2 + (r0 + j)) * ar.d_max + f) = v;
+        }
+    }
+    const bool ok = jib_ar2_signal_owner(ar, site, tile, owner, epoch, 128, (int) threadIdx.x);
+    if (ar.rank == owner && ok && f < d) {
+        for (int j = 0; j < rows; ++j) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < ar.world; ++s) {
+                const float4 v = jib_ld_cg4(ar.recv2[ar.rank] + (size_t) parity * half + ((size_t) s * ar.max_rows2 + (r0 + j)) * ar.d_max + f);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            if (residual) {
+                const uint2 raw = *(const uint2 *) (residual + (size_t) (r0 + j) * d + f);
+                const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+            }
+            uint2 o;
+            *(__nv_bfloat162 *) &o.x = __floats2bfloat162_rn(acc.x, acc.y);
+            *(__nv_bfloat162 *) &o.y = __floats2bfloat162_rn(acc.z, acc.w);
+            const size_t oi = (size_t) parity * ohalf + (size_t) (r0 + j) * ar.d_max + f;
+            for (int p = 0; p < ar.world; ++p) *(uint2 *) ((bf16 *) ar.out2[p] + oi) = o;
+        }
+    }
+    jib_ar2_deliver_and_wait(ar, site, tile, owner, epoch, 128, (int) threadIdx.x);
+}
+
 }  // namespace
 
 extern "C" {
@@ -128,6 +184,22 @@ JIB_EXPORT int jib_allreduce_oneshot(const void * x, int x_f32, const void * res
         JIB_LAUNCH((allreduce_oneshot_kernel<float>), grid, 128, 0, (cudaStream_t) stream, (const float *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
     else
         JIB_LAUNCH((allreduce_oneshot_kernel<bf16>), grid, 128, 0, (cudaStream_t) stream, (const bf16 *) x, (const bf16 *) residual, (bf16 *) out, T, d, *ar, site);
+    return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
+}
+
+// Two-shot all-reduce of a [T][d] partial (+ residual); the bf16 result lands in ar->out2[rank] at the call site's
+// half (site & 1; n_sites must be even), row stride d_max.
+JIB_EXPORT int jib_allreduce_twoshot(const void * x, int x_f32, const void * residual, int T, int d, const JibArCtx * ar, int site,
+                                     void * stream) {
+    if (T <= 0) return 0;
+    if (d % 4 || d > ar->d_max || T > ar->max_rows2 || ar->recv2[0] == nullptr || (ar->n_sites & 1) || site < 0 || site >= ar->n_sites)
+        return JIB_E_ARG;
+    dim3 grid((d + 511) / 512, (T + 31) / 32);
+    if ((int) (grid.x * grid.y) > ar->max_tiles) return JIB_E_ARG;
+    if (x_f32)
+        JIB_LAUNCH((allreduce_twoshot_kernel<float>), grid, 128, 0, (cudaStream_t) stream, (const float *) x, (const bf16 *) residual, T, d, *ar, site);
+    else
+        JIB_LAUNCH((allreduce_twoshot_kernel<bf16>), grid, 128, 0, (cudaStream_t) stream, (const bf16 *) x, (const bf16 *) residual, T, d, *ar, site);
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 

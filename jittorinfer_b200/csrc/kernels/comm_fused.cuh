@@ -16,6 +16,12 @@ struct JibArCtx {
     unsigned * epoch;                     // this rank's step counter (device memory)
     int * status;                         // this rank's status words (code, site, block, extra)
     int world, rank, n_sites, max_rows, d_max, max_tiles;
+    // two-shot path for large batches (prefill): a tile's partials go to one owner rank only, the owner reduces and
+    // stores the bf16 result into every rank's result buffer.  All NULL / 0 when not allocated.
+    float * recv2[JIB_AR_MAX_WORLD];      // [2][world][max_rows2][d_max] fp32 partials of the tiles this rank owns
+    void * out2[JIB_AR_MAX_WORLD];        // [2][max_rows2][d_max] bf16 reduced result (identical on every rank)
+    unsigned * flags2[JIB_AR_MAX_WORLD];  // [n_sites][max_tiles] "tile reduced and delivered" flags
+    int max_rows2;
 };
 
 #ifdef __CUDACC__
@@ -58,5 +64,67 @@ __device__ __forceinline__ bool jib_ar_signal_and_wait(const JibArCtx & ar, int 
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     return s_ok != 0;
+}
+// Two-shot exchange for one tile, called by `nthreads` threads (named barrier 1) after they stored their fp32 partial
+// of the tile into slot [rank] of the owner's recv2.  Signals the owner; returns once the flag wait of this thread's
+// role is over.  Owner side: wait for every source's partial (returns true so that the caller reduces + delivers and
+// then calls jib_ar2_deliver_and_wait); non-owners skip straight to jib_ar2_deliver_and_wait.
+__device__ __forceinline__ bool jib_ar2_signal_owner(const JibArCtx & ar, int site, int tile, int owner, unsigned epoch, int nthreads,
+                                                     int local_tid) {
+    __shared__ int s_ok2;
+    __threadfence_system();
+    if (local_tid == 0) s_ok2 = 1;
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    const size_t slot = ((size_t) site * ar.world) * ar.max_tiles + tile;
+    if (local_tid == 0) jib_st_release_sys(ar.flags[owner] + slot + (size_t) ar.rank * ar.max_tiles, epoch);
+    if (ar.rank == owner && local_tid < ar.world) {
+        const unsigned * f = ar.flags[ar.rank] + slot + (size_t) local_tid * ar.max_tiles;
+        bool got = false;
+        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+            if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
+            __nanosleep(40);
+        }
+        if (!got) {
+            s_ok2 = 0;
+            if (ar.status != nullptr && atomicCAS(ar.status, 0, 1 /* wait timeout */) == 0) {
+                ar.status[1] = 50 + local_tid;    // site code: 50 + source rank (two-shot, partials)
+                ar.status[2] = tile;
+                ar.status[3] = site;
+            }
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    return s_ok2 != 0;
+}
+
+// Owner: after storing the reduced tile into every rank's out2, publish it.  Everyone: wait until the owner published.
+__device__ __forceinline__ bool jib_ar2_deliver_and_wait(const JibArCtx & ar, int site, int tile, int owner, unsigned epoch, int nthreads,
+                                                         int local_tid) {
+    __shared__ int s_ok3;
+    const size_t slot = (size_t) site * ar.max_tiles + tile;
+    if (ar.rank == owner) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        if (local_tid < ar.world) jib_st_release_sys(ar.flags2[local_tid] + slot, epoch);
+    }
+    if (local_tid == 0) {
+        s_ok3 = 1;
+        const unsigned * f = ar.flags2[ar.rank] + slot;
+        bool got = false;
+        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+            if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
+            __nanosleep(40);
+        }
+        if (!got) {
+            s_ok3 = 0;
+            if (ar.status != nullptr && atomicCAS(ar.status, 0, 1 /* wait timeout */) == 0) {
+                ar.status[1] = 58;                // two-shot: the owner never delivered
+                ar.status[2] = tile;
+                ar.status[3] = site;
+            }
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    return s_ok3 != 0;
 }
 #endif

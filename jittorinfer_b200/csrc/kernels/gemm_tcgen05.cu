@@ -75,6 +75,62 @@ struct Cfg {
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+// Reduction side of the fused all-reduce for one tile (rows [t_begin, t_end) x 128 features starting at n0), run by the
+// 128 epilogue threads.  The partials sit in global memory (`slots`: world slots of stride `slot_stride` floats), so the
+// mapping is free: a thread owns 4 adjacent features (one 16-byte load per slot) of every 4th row, and 4 rows are kept
+// in flight at once -- world x 4 independent loads per thread instead of a serial chain per row.  The sum runs in rank
+// order.  `store(row, n, float4)` receives each finished quad.
+template <typename Store>
+__device__ __forceinline__ void ar_reduce_tile(const float * slots, size_t slot_stride, int world, int d_max, long long row_base,
+                                               int t_begin, int t_end, int n0, int N, const void * residual, int res_f32, long long rbase,
+                                               long long ldr, int ltid, Store store) {
+    const int fq = (ltid & 31) * 4, rsub = ltid >> 5;
+    const int n = n0 + fq;
+    if (n >= N) return;
+    for (int t0 = t_begin + rsub; t0 < t_end; t0 += 16) {
+        float4 acc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < world; ++s) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int t = t0 + 4 * u;
+                v[u] = t < t_end ? __ldcg((const float4 *) (slots + (size_t) s * slot_stride + (size_t) (row_base + t) * d_max + n))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int t = t0 + 4 * u;
+            if (t >= t_end) break;
+            const long long row = row_base + t;
+            if (residual != nullptr) {
+                const long long ri = rbase + row * ldr + n;
+                if (res_f32) {
+                    const float4 rv = *(const float4 *) ((const float *) residual + ri);
+                    acc[u].x += rv.x; acc[u].y += rv.y; acc[u].z += rv.z; acc[u].w += rv.w;
+                } else {
+                    const uint2 raw = *(const uint2 *) ((const __nv_bfloat16 *) residual + ri);
+                    const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                    const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                    acc[u].x += a.x; acc[u].y += a.y; acc[u].z += b.x; acc[u].w += b.y;
+                }
+            }
+            store(row, n, acc[u]);
+        }
+    }
+}
+
+__device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
+    uint2 o;
+    *(__nv_bfloat162 *) &o.x = __floats2bfloat162_rn(v.x, v.y);
+    *(__nv_bfloat162 *) &o.y = __floats2bfloat162_rn(v.z, v.w);
+    return o;
+}
+
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 // Cluster-wide barrier (all threads of all CTAs of the cluster) and a load from a peer CTA's shared memory.
@@ -266,10 +322,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // fused all-reduce: the tile's fp32 values go to slot [rank] of every peer instead of `out`
             unsigned ar_epoch = 0;
             size_t ar_par = 0;
+            int ar_owner = 0;
+            size_t ar_opar = 0;           // two-shot: offset of this call site's half of the result buffer (elements)
             if (args.ar_on) {
                 ar_epoch = *args.ar.epoch;
-                const size_t ar_half = (size_t) args.ar.world * args.ar.max_rows * args.ar.d_max;
-                ar_par = (size_t) ((args.ar_site + (int) (ar_epoch % 2u) * (args.ar.n_sites & 1)) & 1) * ar_half;
+                const int par = (args.ar_site + (int) (ar_epoch % 2u) * (args.ar.n_sites & 1)) & 1;
+                const int mr = args.ar_on == 2 ? args.ar.max_rows2 : args.ar.max_rows;
+                ar_par = (size_t) par * ((size_t) args.ar.world * mr * args.ar.d_max);
+                ar_opar = (size_t) par * ((size_t) mr * args.ar.d_max);
+                ar_owner = tile_id % args.ar.world;
             }
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
@@ -325,6 +386,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         float y = DUAL ? silu(g[j]) * u[j] : g[j];
                         const long long row = row_base + t;
                         if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 5, (int) row); break; }
+                        if (args.ar_on == 2) {      // two-shot: the partial goes to the tile's owner only
+                            args.ar.recv2[ar_owner][ar_par + ((size_t) args.ar.rank * args.ar.max_rows2 + row) * args.ar.d_max + n] = y;
+                            continue;
+                        }
                         if (args.ar_on) {
                             const size_t off = ar_par + ((size_t) args.ar.rank * args.ar.max_rows + row) * args.ar.d_max + n;
                             for (int p = 0; p < args.ar.world; ++p) args.ar.recv[p][off] = y;
@@ -346,26 +411,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     }
                 }
             }
-            if (args.ar_on) {
+            if (args.ar_on == 2) {
+                // signal the owner; the owner waits (bounded) for every source, sums the slots in rank order, adds the
+                // residual and stores the bf16 tile into every rank's result buffer; everybody waits for that delivery
+                const int ltid = (int) threadIdx.x - 64;
+                const bool ok = jib_ar2_signal_owner(args.ar, args.ar_site, tile_id, ar_owner, ar_epoch, 128, ltid);
+                if (args.ar.rank == ar_owner && ok) {
+                    const int world = args.ar.world;
+                    ar_reduce_tile(args.ar.recv2[args.ar.rank] + ar_par, (size_t) args.ar.max_rows2 * args.ar.d_max, world, args.ar.d_max,
+                                   row_base, row0, min(rows_valid, row0 + BN), n0, args.N, args.residual, args.res_f32, rbase, args.ldr,
+                                   ltid, [&](long long row, int nn, float4 v) {
+                                       const uint2 o = pack_bf16x4(v);
+                                       const size_t oi = ar_opar + (size_t) row * args.ar.d_max + nn;
+                                       for (int p = 0; p < world; ++p) *(uint2 *) ((__nv_bfloat16 *) args.ar.out2[p] + oi) = o;
+                                   });
+                }
+                jib_ar2_deliver_and_wait(args.ar, args.ar_site, tile_id, ar_owner, ar_epoch, 128, ltid);
+            } else if (args.ar_on) {
                 // signal every peer, wait (bounded) for every source, then sum the slots in rank order
                 jib_ar_signal_and_wait(args.ar, args.ar_site, tile_id, ar_epoch, 128, (int) threadIdx.x - 64);
-                if (n < args.N) {
-                    const int t_end = min(rows_valid, row0 + BN);
-                    for (int t = row0; t < t_end; ++t) {
-                        const long long row = row_base + t;
-                        float y = 0.f;
-                        for (int s = 0; s < args.ar.world; ++s)
-                            y += __ldcg(args.ar.recv[args.ar.rank] + ar_par + ((size_t) s * args.ar.max_rows + row) * args.ar.d_max + n);
-                        if (args.residual != nullptr) {
-                            const long long ri = rbase + row * args.ldr + n;
-                            y += args.res_f32 ? ((const float *) args.residual)[ri]
-                                              : __bfloat162float(((const __nv_bfloat16 *) args.residual)[ri]);
-                        }
-                        const long long oi = obase + row * args.ldo + n;
-                        if (args.out_f32) ((float *) args.out)[oi] = y;
-                        else ((__nv_bfloat16 *) args.out)[oi] = __float2bfloat16(y);
-                    }
-                }
+                ar_reduce_tile(args.ar.recv[args.ar.rank] + ar_par, (size_t) args.ar.max_rows * args.ar.d_max, args.ar.world, args.ar.d_max,
+                               row_base, row0, min(rows_valid, row0 + BN), n0, args.N, args.residual, args.res_f32, rbase, args.ldr,
+                               (int) threadIdx.x - 64, [&](long long row, int nn, float4 v) {
+                                   const long long oi = obase + row * args.ldo + nn;
+                                   if (args.out_f32) *(float4 *) ((float *) args.out + oi) = v;
+                                   else *(uint2 *) ((__nv_bfloat16 *) args.out + oi) = pack_bf16x4(v);
+                               });
             }
         }
         if (csplit) cluster_sync_all();           // peers keep their shared memory alive until CTA 0 has read it
@@ -542,10 +613,13 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     memset(&a.ar, 0, sizeof(a.ar));
     if (d->ar != nullptr) {
         const JibArCtx * ar = (const JibArCtx *) d->ar;
-        if (dual || grouped || batch != 1 || d->N > ar->d_max || d->T > ar->max_rows || n_tiles * t_tiles > ar->max_tiles ||
-            d->ar_site < 0 || d->ar_site >= ar->n_sites)
+        const bool two_shot = d->T > ar->max_rows;        // large batches: partials to one owner per tile, result broadcast
+        if (dual || grouped || batch != 1 || d->N > ar->d_max || n_tiles * t_tiles > ar->max_tiles || d->ar_site < 0 ||
+            d->ar_site >= ar->n_sites)
             return JIB_E_ARG;
-        a.ar = *ar; a.ar_on = 1; a.ar_site = d->ar_site;
+        if (d->N % 4 || ar->d_max % 4 || d->ldo % 4 || (d->residual != nullptr && d->ldr % 4)) return JIB_E_ALIGN;
+        if (two_shot && (d->T > ar->max_rows2 || ar->recv2[0] == nullptr || (ar->n_sites & 1) || d->out_f32)) return JIB_E_ARG;
+        a.ar = *ar; a.ar_on = two_shot ? 2 : 1; a.ar_site = d->ar_site;
     }
     dim3 grid(n_tiles, t_tiles, batch * splits);
 #define JIB_GEMM_CASE(BN_)                                                                          \

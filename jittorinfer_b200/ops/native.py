@@ -99,6 +99,21 @@ def check_status(device=None) -> None:
             raise RuntimeError(f"kernel status: {names.get(st[0], st[0])} at site {st[1]} block {st[2]} extra {st[3]}")
 
 
+class _RawCudaBuffer:
+    """Adapter that lets torch wrap device memory it did not allocate (peer-mapped communication buffers)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    """A tensor view of raw device memory (no ownership: the caller keeps the allocation alive)."""
+    if dtype == torch.bfloat16:        # the array interface has no bf16: wrap as int16 and reinterpret
+        return torch.as_tensor(_RawCudaBuffer(ptr, shape, "<i2"), device=device).view(torch.bfloat16)
+    typestr = {torch.float32: "<f4", torch.int32: "<i4", torch.int64: "<i8", torch.float16: "<f2"}[dtype]
+    return torch.as_tensor(_RawCudaBuffer(ptr, shape, typestr), device=device)
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 

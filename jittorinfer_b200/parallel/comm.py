@@ -68,18 +68,23 @@ class Communicator:
 class ArCtx(C.Structure):
     _fields_ = [("recv", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("status", C.c_void_p),
                 ("world", C.c_int), ("rank", C.c_int), ("n_sites", C.c_int), ("max_rows", C.c_int), ("d_max", C.c_int),
-                ("max_tiles", C.c_int)]
+                ("max_tiles", C.c_int), ("recv2", C.c_void_p * 8), ("out2", C.c_void_p * 8), ("flags2", C.c_void_p * 8),
+                ("max_rows2", C.c_int)]
 
 
 class FusedCommunicator(Communicator):
     """One-shot all-reduce over peer memory, fused into the GEMM epilogue where a GEMM produces the partial."""
 
     fused = True
-    MAX_TILES = 512
+    MAX_TILES = 2048
 
     def __init__(self, device: torch.device, world: int, rank: int, d_max: int, n_sites: int, max_rows: int = 256,
-                 group=None):
+                 group=None, max_rows_large: int = 0):
+        """``max_rows``: largest batch of the one-shot path (decode; every rank receives every partial).
+        ``max_rows_large`` > 0 also allocates the two-shot path for batches up to that size (prefill): a tile's partials
+        go to one owner rank, which reduces and delivers the result to every rank."""
         super().__init__(world, rank, group)
+        n_sites += n_sites & 1            # even: the buffer half of a call site is the same in every step
         from ..ops import native
         self.native = native
         self.L = native.load()
@@ -88,7 +93,8 @@ class FusedCommunicator(Communicator):
         vp = C.c_void_p
         for name, args in (("jib_symm_alloc", [C.c_size_t, C.POINTER(vp), vp]), ("jib_symm_open", [vp, C.POINTER(vp)]),
                            ("jib_symm_close", [vp]), ("jib_symm_free", [vp]), ("jib_ar_epoch_bump", [vp, vp]),
-                           ("jib_allreduce_oneshot", [vp, C.c_int, vp, vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, vp])):
+                           ("jib_allreduce_oneshot", [vp, C.c_int, vp, vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, vp]),
+                           ("jib_allreduce_twoshot", [vp, C.c_int, vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, vp])):
             fn = getattr(self.L, name)
             fn.restype, fn.argtypes = C.c_int, args
         self._own, self._peers = [], []
@@ -103,6 +109,14 @@ class FusedCommunicator(Communicator):
         self.ctx.epoch, self.ctx.status = self.epoch.data_ptr(), ws.status.data_ptr()
         self.ctx.world, self.ctx.rank, self.ctx.n_sites = world, rank, n_sites
         self.ctx.max_rows, self.ctx.d_max, self.ctx.max_tiles = max_rows, d_max, self.MAX_TILES
+        self.max_rows_large = max_rows_large
+        self.ctx.max_rows2 = max_rows_large
+        if max_rows_large > 0:
+            recv2 = self._exchange(2 * world * max_rows_large * d_max * 4)
+            out2 = self._exchange(2 * max_rows_large * d_max * 2)
+            flags2 = self._exchange(n_sites * self.MAX_TILES * 4)
+            for i in range(world):
+                self.ctx.recv2[i], self.ctx.out2[i], self.ctx.flags2[i] = recv2[i], out2[i], flags2[i]
         self.site = 0
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
@@ -158,7 +172,15 @@ class FusedCommunicator(Communicator):
         T, d = x.shape
         site = self._next_site()
         if T > self.max_rows:
-            return Communicator.all_reduce(self, x, residual)
+            if T > self.max_rows_large or d != self.d_max:
+                return Communicator.all_reduce(self, x, residual)
+            self.n_collectives += 1
+            self.n_two_shot += 1
+            rc = self.L.jib_allreduce_twoshot(x.data_ptr(), int(x.dtype == torch.float32),
+                                              None if residual is None else residual.data_ptr(), T, d, C.byref(self.ctx), site,
+                                              torch.cuda.current_stream().cuda_stream)
+            self.native._ck(rc, "allreduce_twoshot")
+            return self._result_view(site, T)
         self.n_collectives += 1
         out = torch.empty(T, d, dtype=torch.bfloat16, device=x.device)
         rc = self.L.jib_allreduce_oneshot(x.data_ptr(), int(x.dtype == torch.float32),
@@ -169,14 +191,31 @@ class FusedCommunicator(Communicator):
 
     def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
         site = self._next_site()
-        if x.shape[0] > self.max_rows:
-            return Communicator.linear_all_reduce(self, x, w, residual)
+        T = x.shape[0]
+        if T > self.max_rows:
+            if T > self.max_rows_large or w.shape[0] != self.d_max:
+                return Communicator.linear_all_reduce(self, x, w, residual)
+            # two-shot: the GEMM's epilogue sends each tile's partial to its owner; the owner reduces and delivers
+            self.n_collectives += 1
+            self.n_two_shot += 1
+            out = self._result_view(site, T)
+            self.native.gemm(x, w, out=out, residual=residual, ar=self.ctx, ar_site=site)
+            return out
         self.n_collectives += 1
         return self.native.gemm(x, w, residual=residual, ar=self.ctx, ar_site=site)
+
+    n_two_shot = 0
+
+    def _result_view(self, site: int, T: int) -> torch.Tensor:
+        """This rank's copy of the two-shot result of call site ``site``: rows [0, T) of that site's half of the result
+        buffer.  Valid until the call site after the next one writes the same half."""
+        base = self.ctx.out2[self.rank] + (site & 1) * self.max_rows_large * self.d_max * 2
+        return self.native.tensor_from_ptr(base, (T, self.d_max), torch.bfloat16, self.device)
 
 
 def make_communicator(device: torch.device, world: int, rank: int, d_model: int, n_layer: int, group=None):
     impl = os.environ.get("JITTORINFER_COMM", "fused").lower()
     if device.type != "cuda" or impl == "nccl":
         return Communicator(world, rank, group)
-    return FusedCommunicator(device, world, rank, d_model, 2 * n_layer, group=group)
+    large = int(os.environ.get("JITTORINFER_AR_LARGE_ROWS", "2048"))
+    return FusedCommunicator(device, world, rank, d_model, 2 * n_layer, group=group, max_rows_large=large)

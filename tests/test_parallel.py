@@ -23,7 +23,10 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q):
+PROMPT_LENS = (20, 70)
+
+
+def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q, prompt_lens=PROMPT_LENS, n_batch=48):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), JITTORINFER_COMM=comm_impl, NCCL_NVLS_ENABLE="0")
     try:
@@ -45,29 +48,31 @@ def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl,
         comm = make_communicator(dev, world, rank, hp.n_embd, hp.n_layer)
         dtype = torch.bfloat16 if gpu else torch.float32
         model = DeepSeek2Model(hp, iter_random(hp, spec=spec, seed=0, std=0.05), dtype=dtype, device=dev, spec=spec, comm=comm)
-        eng = LLMEngine(model, EngineConfig(n_ctx=1024, n_batch=48, n_parallel=2, graph_buckets=(1, 2), cuda_graphs=graphs))
+        eng = LLMEngine(model, EngineConfig(n_ctx=1024, n_batch=n_batch, n_parallel=2, graph_buckets=(1, 2), cuda_graphs=graphs))
         g = torch.Generator().manual_seed(0)
-        prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (20, 70)]
+        prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in prompt_lens]
         outs = eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=12)
         if gpu:
             torch.cuda.synchronize()
             from jittorinfer_b200.ops import native
             native.check_status()
-        q.put((rank, outs, comm.n_collectives, getattr(comm, "fused", False), eng.stats["graph_steps"]))
+        q.put((rank, outs, comm.n_collectives, getattr(comm, "fused", False), eng.stats["graph_steps"], getattr(comm, "n_two_shot", 0)))
         dist.barrier()
         comm.close()
         dist.destroy_process_group()
     except Exception:  # pragma: no cover
         import traceback
-        q.put((rank, "ERROR: " + traceback.format_exc(), 0, False, 0))
+        q.put((rank, "ERROR: " + traceback.format_exc(), 0, False, 0, 0))
         raise
 
 
-def _run(world, backend, expert_parallel, preset_name="tiny-v2", comm_impl="nccl", graphs=True, timeout=150):
+def _run(world, backend, expert_parallel, preset_name="tiny-v2", comm_impl="nccl", graphs=True, timeout=150,
+         prompt_lens=PROMPT_LENS, n_batch=48):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q,
+                                               prompt_lens, n_batch))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -83,7 +88,7 @@ def _run(world, backend, expert_parallel, preset_name="tiny-v2", comm_impl="nccl
     return sorted(res)
 
 
-def _oracle(preset_name, bf16_weights):
+def _oracle(preset_name, bf16_weights, prompt_lens=PROMPT_LENS):
     from jittorinfer_b200.models.hparams import preset
     from jittorinfer_b200.models.oracle import OracleModel
     from jittorinfer_b200.models.weights import random_weights
@@ -93,7 +98,7 @@ def _oracle(preset_name, bf16_weights):
         w = {k: v.bfloat16().float() for k, v in w.items()}
     o = OracleModel(hp, w)
     g = torch.Generator().manual_seed(0)
-    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (20, 70)]
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in prompt_lens]
     return [o.generate(p, 12) for p in prompts]
 
 
@@ -116,3 +121,20 @@ def test_tp_ep_two_gpus(comm_impl, graphs):
     assert res[0][3] == (comm_impl == "fused") and (res[0][4] > 0) == graphs
     agree = sum(a == b for out, r in zip(res[0][1], ref) for a, b in zip(out, r))
     assert agree >= 12                              # bf16 vs fp32 greedy paths may split late
+
+
+@pytest.mark.gpu
+def test_tp_ep_two_gpus_large_prefill_two_shot():
+    """A 400-token prefill chunk exceeds the one-shot buffers: the GEMM epilogue and the MoE partial take the two-shot
+    path (partials to one owner per tile, result delivered to every rank)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    lens = (300, 100)
+    res = _run(2, "nccl", True, comm_impl="fused", graphs=True, prompt_lens=lens, n_batch=512)
+    lib = _run(2, "nccl", True, comm_impl="nccl", graphs=False, prompt_lens=lens, n_batch=512)
+    ref = _oracle("tiny-v2", True, lens)
+    assert res[0][1] == res[1][1] and res[0][5] > 0
+    for out, r in zip(res[0][1], ref):
+        assert out[0] == r[0]                        # the first sampled token comes straight from the prefill pass
+    agree = sum(a == b for out, r in zip(res[0][1], lib[0][1]) for a, b in zip(out, r))
+    assert agree >= 12                               # same kernels, different transport: late splits only
