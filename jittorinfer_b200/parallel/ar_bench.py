@@ -6,8 +6,9 @@ against the same GEMM followed by a library all-reduce.
 
 For every token count T the fused path is the one the model takes: the one-shot epilogue for T <= 256 (decode), the
 two-shot epilogue above (prefill).  Inputs rotate over ``--sets`` distinct weight matrices so that the weights come from
-HBM, as they do inside a model.  Both paths are captured in CUDA graphs; CUDA events on the launching stream, max
-over ranks.
+HBM, as they do inside a model.  Both paths run eagerly by default (each call then carries ~10 us of Python launch
+overhead, the same for both); ``--graph`` replays the fused path as a CUDA graph.  CUDA events on the launching stream,
+max over ranks.
 
 Roofline per call and rank: the slower of (a) FLOPs at the measured bf16 GEMM rate or the weight bytes at the measured
 HBM bandwidth, whichever is larger, and (b) bytes that must cross NVLink at the measured 770 GB/s per direction:
@@ -33,6 +34,7 @@ def main():
     ap.add_argument("--tokens", default="8,64,256,1024,2048")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--sets", type=int, default=6)
+    ap.add_argument("--graph", action="store_true", help="replay the fused path as a CUDA graph (default: both paths eager)")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -87,25 +89,24 @@ def main():
             torch.cuda.synchronize()
             native.check_status()
             err = float((y_f - y_l).abs().max())
-            # both paths are replayed as CUDA graphs (as the engine does for decode), so the numbers are device time
-            # and not Python launch overhead
-            def graphed(comm):
+            us_lib = timed(lambda: run(lib))
+            if args.graph:
+                # replay the fused calls as one CUDA graph (as the engine does for decode): device time without the Python
+                # launch overhead.  The library path stays eager.
                 st = torch.cuda.Stream()
                 st.wait_stream(torch.cuda.current_stream())
                 gr = torch.cuda.CUDAGraph()
                 with torch.cuda.stream(st):
-                    run(comm)
+                    run(fused)
                     torch.cuda.synchronize()
                     dist.barrier()
                     with torch.cuda.graph(gr, stream=st):
-                        run(comm)
+                        run(fused)
                 torch.cuda.synchronize()
                 dist.barrier()
-                return gr
-
-            g_lib, g_fused = graphed(lib), graphed(fused)
-            us_lib = timed(g_lib.replay)
-            us_fused = timed(g_fused.replay)
+                us_fused = timed(gr.replay)
+            else:
+                us_fused = timed(lambda: run(fused))
             native.check_status()
             flops = 2.0 * T * N * K
             t_math = max(flops / (float(peaks["bf16_tflops"]) * 1e12), N * K * 2 / (float(peaks["hbm_gbs"]) * 1e9)) * 1e6
@@ -121,7 +122,7 @@ def main():
                          "fraction_of_roofline": round(roof / us_fused, 3), "max_abs_diff": err})
     if rank == 0:
         print(json.dumps({"bench": "gemm_allreduce", "model": args.model, "n_gpus": world, "timing": "CUDA events, max over ranks",
-                          "rows": rows}))
+                          "fused_path": "cuda graph" if args.graph else "eager", "rows": rows}))
     dist.barrier()
     fused.close()
     dist.destroy_process_group()
