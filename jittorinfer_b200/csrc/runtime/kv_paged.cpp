@@ -154,6 +154,22 @@ std::vector<std::pair<int32_t, int32_t>> PagedKv::defrag(int max_moves) {
     return moves;
 }
 
+int PagedKv::reserve(int n) {
+    int got = 0;
+    while (got < n && !free_.empty()) {
+        reserved_.push_back(free_.back());
+        free_.pop_back();
+        ++got;
+    }
+    return got;
+}
+
+void PagedKv::unreserve() {
+    for (int32_t b : reserved_) free_.push_back(b);
+    reserved_.clear();
+    std::sort(free_.begin(), free_.end(), [](int32_t a, int32_t b) { return a > b; });
+}
+
 bool PagedKv::check() const {
     std::vector<int32_t> cnt(n_blocks_, 0);
     for (const auto & s : seqs_) {
@@ -167,6 +183,10 @@ bool PagedKv::check() const {
         if (cnt[b] != ref_[b]) return false;
     std::vector<char> is_free(n_blocks_, 0);
     for (int b : free_) {
+        if (ref_[b] != 0 || is_free[b]) return false;
+        is_free[b] = 1;
+    }
+    for (int b : reserved_) {
         if (ref_[b] != 0 || is_free[b]) return false;
         is_free[b] = 1;
     }

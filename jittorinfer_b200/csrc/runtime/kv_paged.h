@@ -56,6 +56,11 @@ class PagedKv {
     // (reference planner: src/llama-execute-kvupdate.cpp:12-149)
     std::vector<std::pair<int32_t, int32_t>> defrag(int max_moves);
 
+    // Memory-pressure injection for host-side fault tests: takes up to n free blocks out of circulation (returns how
+    // many) until unreserve() puts them back.  Reserved blocks count as used.
+    int reserve(int n);
+    void unreserve();
+
     // Consistency check used by tests and the bounds-check build: every block's refcount equals the
     // number of tables naming it, and free blocks have refcount 0.
     bool check() const;
@@ -69,6 +74,7 @@ class PagedKv {
     std::vector<int32_t> ref_;
     std::vector<int32_t> free_;    // kept sorted descending so pop_back() yields the lowest id
     std::vector<std::pair<int32_t, int32_t>> pending_;
+    std::vector<int32_t> reserved_;
 };
 
 }  // namespace jib

@@ -42,6 +42,8 @@ JIB_API int jib_kv_block_size(PagedKv * kv) { return kv->block_size(); }
 JIB_API int jib_kv_refcount(PagedKv * kv, int block) { return kv->refcount(block); }
 JIB_API float jib_kv_fragmentation(PagedKv * kv) { return kv->fragmentation(); }
 JIB_API int jib_kv_check(PagedKv * kv) { return kv->check() ? 1 : 0; }
+JIB_API int jib_kv_reserve(PagedKv * kv, int n) { return kv->reserve(n); }
+JIB_API void jib_kv_unreserve(PagedKv * kv) { kv->unreserve(); }
 // Pops up to cap queued copy-on-write copies.
 JIB_API int jib_kv_take_copies(PagedKv * kv, int32_t * src, int32_t * dst, int cap) {
     auto & p = kv->pending_copies();

@@ -174,6 +174,8 @@ class GGUFReader:
     """Parses header/KV/tensor table and maps the file; tensors are views of the mapping."""
 
     def __init__(self, path: str, populate: bool = False):
+        from ..utils import fault
+        fault.check("gguf_read")
         self.path = path
         self._f = open(path, "rb")
         size = os.fstat(self._f.fileno()).st_size

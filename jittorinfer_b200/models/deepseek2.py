@@ -28,6 +28,7 @@ from typing import Dict, Iterable, List, Optional, Tuple
 import torch
 
 from .. import ops
+from ..utils import trace as _trace
 from .hparams import DeepSeek2HParams
 from .weights import ShardSpec
 
@@ -108,6 +109,7 @@ class DeepSeek2Model:
         H, dn, dv, r = self.n_head_local, hp.qk_nope_head_dim, hp.v_head_dim, hp.kv_lora_rank
         pend: Dict[str, torch.Tensor] = {}
         for name, t in weights:
+            _trace.log_tensor(name, t.shape, t.dtype, f"rank {self.spec.tp_rank}/{self.spec.tp_size}" if self.spec.sharded else "")
             if name == "token_embd.weight":
                 self.tok_embd = self._dev(t)
             elif name == "output_norm.weight":
@@ -280,12 +282,17 @@ class DeepSeek2Model:
         if batch is None:
             return self._forward_idle()
         x = ops.embed_gather(self.tok_embd, batch.tokens)
+        nvtx = _trace.nvtx_enabled()
         for il, L in enumerate(self.layers):
+            if nvtx:
+                torch.cuda.nvtx.range_push(f"layer{il}")
             h, _ = ops.rmsnorm(x, L.attn_norm, hp.rms_eps)
             a = self._attention(L, h, batch, kv_cache[il])
             y = self._row_parallel(a, L.w_o, x)
             g, _ = ops.rmsnorm(y, L.ffn_norm, hp.rms_eps)
             x = self._mlp(L, g, y)
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         xo = ops.select_rows(x, batch.out_rows) if batch.out_rows is not None else x
         xo, _ = ops.rmsnorm(xo, self.out_norm, hp.rms_eps)
         return ops.linear(xo, self.w_out, out_dtype=torch.float32)

@@ -23,6 +23,9 @@ import numpy as np
 import torch
 
 from .. import ops
+from ..utils import fault
+from ..utils.trace import PhaseTimer, Tracer
+from ..utils import trace as _trace
 from ..models.deepseek2 import DeepSeek2Model, ForwardBatch
 from ..models.hparams import DeepSeek2HParams
 from .native_rt import PagedKV, Scheduler, StepArrays, i32p
@@ -133,6 +136,8 @@ class LLMEngine:
         self.dp_active = spec.tp_size if self.dp else 0
         self._dp_flag = torch.zeros(1, dtype=torch.int32, device=self.device) if self.dp else None
         self._idle_graph = None
+        self.tracer = Tracer()            # JSON-lines step trace when JITTORINFER_TRACE names a file
+        self._pressure = False            # free KV blocks held back by the kv_alloc fault site
 
     # ------------------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -216,6 +221,17 @@ class LLMEngine:
         else:
             self.model.forward(None, None)
 
+    def reset(self) -> None:
+        """Drop every request and all cached tokens (recovery after a failed step: the scheduler may have been left
+        between planning and commit).  Weights, cache memory and captured graphs stay."""
+        cfg = self.cfg
+        self.kv = PagedKV(self.n_blocks, cfg.block_size, cfg.n_parallel)
+        self.sched = Scheduler(self.kv, cfg.n_parallel, cfg.n_batch, self.n_ctx_slot, self.hp.eos_id, cfg.n_keep,
+                               cfg.cont_batching)
+        self.requests.clear()
+        self._pressure = False
+        self.stats["resets"] = self.stats.get("resets", 0) + 1
+
     def run_until_all_idle(self, max_steps: int = 1 << 30) -> int:
         """Data-parallel serving loop: step until no rank has work left.  Every rank leaves at the same step."""
         n = 0
@@ -295,8 +311,18 @@ class LLMEngine:
     def step(self) -> List[Tuple[int, int, Optional[str]]]:
         """Runs one engine step. Returns [(req_id, new_token, finish_reason_or_None)]."""
         io = self.io
+        fault.check("engine_step")
+        if self._pressure:
+            self.kv.unreserve()
+            self._pressure = False
+        if fault.armed("kv_alloc") and fault.hit("kv_alloc"):
+            self.kv.reserve(self.kv.n_blocks)          # this step sees an allocator without free blocks
+            self._pressure = True
+        pt = PhaseTimer() if self.tracer.enabled else None
         info = self.sched.step(io.arrays)
         n_tokens, n_seqs, n_out, n_dec, max_q, _, n_copies = (int(x) for x in info[:7])
+        if pt:
+            pt.mark("schedule")
         if self.dp:
             import torch.distributed as dist
             self._dp_flag.fill_(1 if (n_tokens > 0 or self.has_work()) else 0)
@@ -342,6 +368,8 @@ class LLMEngine:
             if self.device.type == "cuda" and not ops.force_torch():
                 self.launches += ops.nat().launch_count - n0
             self.stats["eager_steps"] += 1
+        if pt:
+            pt.mark("launch")
         self.stats["steps"] += 1
         self.stats["tokens_in"] += n_tokens
         self.stats["h2d_bytes"] += io.h2d_bytes
@@ -352,6 +380,8 @@ class LLMEngine:
             host.copy_(flat, non_blocking=True)
             if self.device.type == "cuda":
                 torch.cuda.current_stream(self.device).synchronize()
+            if pt:
+                pt.mark("wait")
             self.stats["d2h_bytes"] += n_el * 4
             res = host.numpy().reshape(out.shape[0], -1)
             sampled = np.empty(n_out, dtype=np.int32)
@@ -377,6 +407,12 @@ class LLMEngine:
             self.dp_active = int(self._dp_flag.item())
         ev = self._drain_events()
         self._maybe_defrag()
+        if pt:
+            pt.mark("finish")
+            self.tracer.emit("step", step=self.stats["steps"], tokens=n_tokens, seqs=n_seqs, outputs=n_out, max_q=max_q,
+                             mode="graph" if use_graph else "eager", kv_used=self.kv.used_blocks, kv_total=self.n_blocks,
+                             frag=round(self.kv.fragmentation(), 4), waiting=self.sched.n_waiting(), running=self.sched.n_running(),
+                             finished=sum(1 for e in ev if e[2] is not None), phase_ms=pt.ms)
         return ev
 
     # ------------------------------------------------------------------------------------------

@@ -59,6 +59,8 @@ def lib():
         for n in ("free_blocks", "used_blocks", "n_blocks", "block_size", "check"):
             sig("jib_kv_" + n, C.c_int, vp)
         sig("jib_kv_refcount", C.c_int, vp, C.c_int)
+        sig("jib_kv_reserve", C.c_int, vp, C.c_int)
+        sig("jib_kv_unreserve", None, vp)
         sig("jib_kv_fragmentation", C.c_float, vp)
         sig("jib_kv_take_copies", C.c_int, vp, i32p, i32p, C.c_int)
         sig("jib_kv_defrag", C.c_int, vp, C.c_int, i32p, i32p)
@@ -124,6 +126,8 @@ class PagedKV:
     def refcount(self, b): return self._L.jib_kv_refcount(self._h, b)
     def fragmentation(self): return float(self._L.jib_kv_fragmentation(self._h))
     def check(self): return bool(self._L.jib_kv_check(self._h))
+    def reserve(self, n: int) -> int: return self._L.jib_kv_reserve(self._h, n)      # memory-pressure injection (tests)
+    def unreserve(self) -> None: self._L.jib_kv_unreserve(self._h)
 
     def take_copies(self, cap: int = 4096) -> Tuple[np.ndarray, np.ndarray]:
         s = np.empty(cap, dtype=np.int32)

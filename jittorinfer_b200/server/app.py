@@ -139,6 +139,13 @@ class ServerContext:
         if self.world == 1:
             return tasks
         import torch.distributed as dist
+        from ..utils import fault
+        fault.check("transport")
+        hb = getattr(self, "heartbeat", None)
+        if hb is not None:
+            gone = hb.dead()
+            if gone:
+                raise RuntimeError(f"rank(s) {gone} stopped responding")
         wire = [None]
         if self.rank == 0:
             w = []
@@ -190,13 +197,17 @@ class ServerContext:
             t0 = time.time()
             try:
                 events = eng.step()
-            except Exception as e:       # fail the in-flight requests, keep serving (reference: abort)
+            except Exception as e:       # fail the in-flight requests with 503 and keep serving (reference: abort)
+                n_failed = len(self.streams)
                 for st in list(self.streams.values()):
                     st.q.put(("error", f"engine step failed: {e}"))
                     st.done = True
                 self.streams.clear()
-                self.metrics.inc("requests_failed_total")
-                raise
+                self.metrics.inc("requests_failed_total", max(n_failed, 1))
+                if self.world > 1:
+                    raise                # the ranks' schedulers have diverged: a coordinated restart is the launcher's job
+                eng.reset()
+                continue
             self.metrics.observe_step(time.time() - t0)
             for rid, tok, fin in events:
                 st = self.streams.get(rid)
