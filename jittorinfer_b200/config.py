@@ -59,6 +59,9 @@ class ServerConfig:
     gpu_memory_utilization: float = 0.9
     max_num_seqs: Optional[int] = None
     cuda_graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
+    attention_dp: bool = False         # ep_size ranks each serve their own requests (attention data-parallel), routed experts
+                                       # sharded over them and reached through the all-to-all dispatcher
+    ep_max_tokens: int = 256           # attention_dp: most tokens one rank schedules per step (sizes the dispatch buffers)
     random_init: str = ""              # preset name ("lite", "v2", "tiny"): serve random weights instead of a GGUF file
     ignored: Dict[str, Any] = field(default_factory=dict)
 
@@ -83,6 +86,8 @@ class ServerConfig:
             raise ValueError("tp_size / ep_size must be 1, 2, 4 or 8")       # reference: llama-model.cpp:467-476
         if self.ep_size > 1 and self.tp_size > 1 and self.ep_size != self.tp_size:
             raise ValueError("expert parallelism shares the tensor-parallel group: ep_size must equal tp_size")
+        if self.attention_dp and (self.ep_size < 2 or self.tp_size > 1):
+            raise ValueError("attention_dp needs ep_size >= 2 and tp_size == 1 (attention is replicated, not sharded)")
         if self.kv_block_size != 64:
             raise ValueError("kv_block_size must be 64 (the attention kernels are built for 64-token blocks)")
         if not (0.05 <= self.gpu_memory_utilization <= 0.98):

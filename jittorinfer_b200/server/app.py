@@ -40,6 +40,7 @@ class _Stream:
     t0: float = 0.0
     t_first: float = 0.0
     done: bool = False
+    tokens: List[int] = field(default_factory=list)      # generated ids (returned when the request sets return_tokens)
 
 
 class Metrics:
@@ -169,8 +170,81 @@ class ServerContext:
                 out.append(("cancel_rid", t[1]))
         return out
 
+    def _run_dp(self):
+        """Attention data-parallel serving: rank 0 assigns every request to one rank (round robin), all ranks step
+        together (a rank without tokens runs the idle forward), and every iteration the new tokens of all ranks are
+        gathered to rank 0, which owns the HTTP streams.  Per iteration: one broadcast (tasks, stop, step-or-not) and
+        one gather (events, has-work) on the host-side control group."""
+        import torch.distributed as dist
+        eng = self.engine
+        gid_of: Dict[int, int] = {}                  # this rank's engine request id -> global request id
+        rid_of: Dict[int, int] = {}
+        next_gid, rr, global_work = 1, 0, False
+        while True:
+            wire = [None]
+            if self.rank == 0:
+                w = []
+                for t in self._collect_tasks(block=not global_work):
+                    if t[0] == "add":
+                        _, st, prompt, params = t
+                        st.rid = next_gid
+                        self.streams[next_gid] = st
+                        w.append(("add", next_gid, rr % self.world, prompt, params.__dict__))
+                        next_gid += 1
+                        rr += 1
+                        self.metrics.inc("prompt_tokens_total", len(prompt))
+                    elif t[0] == "cancel":
+                        if t[1].rid >= 0:
+                            w.append(("cancel", t[1].rid))
+                        if not t[1].done:
+                            self._finish(t[1], "cancelled")
+                            self.metrics.inc("cancelled_total")
+                wire = [(w, self.stop_flag.is_set(), global_work or bool(w))]
+            dist.broadcast_object_list(wire, src=0, group=self.group)
+            w, stop, run_step = wire[0]
+            if stop:
+                self.stop_flag.set()
+                return
+            for t in w:
+                if t[0] == "add" and t[2] == self.rank:
+                    rid = eng.add_request(t[3], SamplingParams(**t[4]))
+                    gid_of[rid], rid_of[t[1]] = t[1], rid
+                elif t[0] == "cancel" and t[1] in rid_of:
+                    rid = rid_of.pop(t[1])
+                    eng.cancel(rid)
+                    eng.requests.pop(rid, None)
+                    gid_of.pop(rid, None)
+            events = []
+            if run_step:
+                t0 = time.time()
+                for rid, tok, fin in eng.step():
+                    gid = gid_of.get(rid)
+                    if gid is None:
+                        continue
+                    events.append((gid, tok, fin))
+                    if fin is not None:
+                        eng.requests.pop(rid, None)
+                        gid_of.pop(rid, None)
+                        rid_of.pop(gid, None)
+                self.metrics.observe_step(time.time() - t0)
+            gathered = [None] * self.world if self.rank == 0 else None
+            dist.gather_object((events, eng.has_work()), gathered, dst=0, group=self.group)
+            if self.rank == 0:
+                global_work = any(g[1] for g in gathered)
+                for evs, _ in gathered:
+                    for gid, tok, fin in evs:
+                        st = self.streams.get(gid)
+                        if st is None or st.done:
+                            continue
+                        if tok >= 0:
+                            self._on_token(st, tok)
+                        if fin is not None and not st.done:
+                            self._finish(st, "stop" if fin == "stop" else ("cancelled" if fin == "cancelled" else "length"))
+
     def run(self):
         eng = self.engine
+        if getattr(eng, "dp", False) and self.world > 1:
+            return self._run_dp()
         while not self.stop_flag.is_set():
             tasks = self._collect_tasks(block=not eng.has_work()) if self.rank == 0 else []
             tasks = self._share_tasks(tasks)
@@ -229,6 +303,7 @@ class ServerContext:
 
     def _on_token(self, st: _Stream, tok: int):
         st.n_gen += 1
+        st.tokens.append(int(tok))
         self.metrics.inc("generation_tokens_total")
         if st.n_gen == 1:
             st.t_first = time.time()
@@ -280,8 +355,10 @@ class ServerContext:
         eng = self.engine
         return {"requests_running": eng.sched.n_running(), "requests_waiting": eng.sched.n_waiting(),
                 "kv_blocks_used": eng.kv.used_blocks, "kv_blocks_total": eng.kv.n_blocks,
+                "kv_blocks_used_ratio": eng.kv.used_blocks / max(1, eng.kv.n_blocks),
                 "kv_fragmentation": eng.kv.fragmentation(), "graph_steps": eng.stats["graph_steps"],
-                "eager_steps": eng.stats["eager_steps"]}
+                "eager_steps": eng.stats["eager_steps"], "defrag_moves": eng.stats.get("defrag_moves", 0),
+                "preemptions": eng.sched.stats().get("preemptions", 0) if hasattr(eng.sched, "stats") else 0}
 
 
 # =================================================================================================
@@ -418,7 +495,10 @@ def make_handler(ctx: ServerContext):
                                                        st.n_prompt, st.n_gen, timings))
             if len(results) == 1:
                 st, text, reason, timings = results[0]
-                return self._json(200, P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, 0, timings))
+                body = P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, 0, timings)
+                if req.return_tokens:
+                    body["choices"][0]["tokens"] = list(st.tokens)
+                return self._json(200, body)
             out = [P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, i, timings)
                    for i, (st, text, reason, timings) in enumerate(results)]
             self._json(200, out)

@@ -22,7 +22,8 @@ def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
     common = dict(device=device, dtype=dtype, world=world, rank=rank, n_parallel=cfg.slots, n_ctx_slot=n_ctx_slot, n_ctx=cfg.n_ctx,
                   n_batch=cfg.n_batch, cuda_graphs=cfg.cuda_graphs, graph_buckets=tuple(b for b in cfg.cuda_graph_buckets if b <= cfg.slots) or (1,),
                   expert_parallel=cfg.ep_size > 1, n_keep=cfg.n_keep, cont_batching=cfg.cont_batching, defrag_thold=cfg.defrag_thold,
-                  presample_count=max(1, cfg.presample_count) if cfg.presample_count > 0 else 64)
+                  presample_count=max(1, cfg.presample_count) if cfg.presample_count > 0 else 64,
+                  dp_attention=bool(getattr(cfg, "attention_dp", False)) and world > 1, ep_max_tokens=getattr(cfg, "ep_max_tokens", 256))
     if cfg.random_init:
         hp = preset(cfg.random_init)
         eng = build_engine(hp, **common)

@@ -114,7 +114,7 @@ def parse_completion(body: Dict[str, Any], tokenizer, model_alias: str, default_
         raise BadRequest("\"prompt\" is required")
     params = sampling_from_body(body, default_max)
     return ParsedRequest(tokenize_prompts(tokenizer, body["prompt"]), params, bool(body.get("stream", False)), False,
-                         str(body.get("model", model_alias)), params.stop)
+                         str(body.get("model", model_alias)), params.stop, bool(body.get("return_tokens", False)))
 
 
 def parse_chat(body: Dict[str, Any], tokenizer, template, model_alias: str, default_max: int) -> ParsedRequest:

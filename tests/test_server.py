@@ -92,3 +92,18 @@ def test_templates_and_reasoning():
     assert t.render(msgs[:2]) == "[system]S[user]U[assistant]"
     assert split_reasoning("<think>why</think>answer", True) == ("why", "answer")
     assert split_reasoning("plain", True) == (None, "plain") and split_reasoning("<think>x</think>y", False) == (None, "<think>x</think>y")
+
+
+def test_serving_benchmark_poisson(server):
+    """The load generator against the in-process server: open-loop arrivals, streamed responses, client-side timings."""
+    from jittorinfer_b200.server import bench_serving
+    url, ctx = server
+    res = bench_serving.run(url, rate=50.0, num_requests=10, prompt_min=4, prompt_max=40, output_len=5, max_concurrency=4,
+                            n_vocab=1000, seed=1, timeout=120)
+    assert res["completed"] == 10 and res["failed"] == 0 and res["errors"] == []
+    assert res["output_tokens_per_s"] > 0 and res["ttft_ms"]["p50"] > 0 and res["e2e_ms"]["p99"] >= res["ttft_ms"]["p50"]
+    closed = bench_serving.run(url, rate=0.0, num_requests=6, prompt_min=4, prompt_max=8, output_len=3, max_concurrency=2,
+                               n_vocab=1000, seed=2, timeout=120)
+    assert closed["completed"] == 6 and closed["arrivals"].startswith("closed loop")
+    m = bench_serving.scrape_metrics(url)
+    assert "jittorinfer_kv_blocks_used_ratio" in m and m["jittorinfer_requests_total"] >= 16

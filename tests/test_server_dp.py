@@ -1,0 +1,97 @@
+"""Attention data-parallel serving on 2 CPU ranks: rank 0 serves HTTP and assigns requests round robin; both ranks step
+together; tokens generated on rank 1 reach the client through the per-iteration gather."""
+import json
+import multiprocessing as mp
+import os
+import socket
+import sys
+import time
+import urllib.request
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank(rank, world, master_port, http_port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(master_port), RANK=str(rank), WORLD_SIZE=str(world), JITTORINFER_COMM="nccl")
+    import torch.distributed as dist
+    from jittorinfer_b200.config import ServerConfig
+    from jittorinfer_b200.server.app import ServerContext, serve
+    from jittorinfer_b200.server.chat import ChatTemplate
+    from jittorinfer_b200.server.launch import build_from_config
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    control = dist.new_group(backend="gloo")
+    cfg = ServerConfig(random_init="tiny-v2", n_ctx=1024, n_parallel=2, n_batch=64, port=http_port, enable_ge=False, ep_size=world,
+                       attention_dp=True, ep_max_tokens=64)
+    cfg.validate()
+    eng, tok, tpl = build_from_config(cfg, device=torch.device("cpu"), world=world, rank=rank)
+    assert eng.dp
+    ctx = ServerContext(eng, tok, cfg, ChatTemplate(tpl), rank=rank, world=world, control_group=control)
+    if rank != 0:
+        ctx.run()
+        q.put((rank, eng.stats["tokens_out"], eng.stats.get("idle_steps", 0)))
+        return
+    httpd = serve(ctx, "127.0.0.1", http_port)
+    q.put(("ready", http_port, 0))
+    try:
+        httpd.serve_forever()       # until GET /exit
+    finally:
+        ctx.shutdown()              # joins the engine thread, whose last broadcast tells the other ranks to stop
+        httpd.server_close()
+    q.put((rank, eng.stats["tokens_out"], eng.stats.get("idle_steps", 0)))
+
+
+def _post(url, body):
+    req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=120) as r:
+        return json.loads(r.read().decode())
+
+
+def test_dp_server_two_cpu_ranks():
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.models.oracle import OracleModel
+    from jittorinfer_b200.models.weights import random_weights
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    mport, hport = _free_port(), _free_port()
+    procs = [ctx.Process(target=_rank, args=(r, 2, mport, hport, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        assert q.get(timeout=180)[0] == "ready"
+        url = f"http://127.0.0.1:{hport}"
+        hp = preset("tiny-v2")
+        oracle = OracleModel(hp, random_weights(hp, seed=0))
+        g = torch.Generator().manual_seed(4)
+        prompts = [torch.randint(1, hp.n_vocab, (n,), generator=g).tolist() for n in (12, 30, 7)]
+        import concurrent.futures as cf
+        with cf.ThreadPoolExecutor(3) as ex:             # three requests in flight: ranks 0, 1, 0
+            futs = [ex.submit(_post, url + "/v1/completions", {"prompt": p, "max_tokens": 6, "temperature": 0, "ignore_eos": True,
+                                                               "return_tokens": True}) for p in prompts]
+            outs = [f.result() for f in futs]
+        for p, o in zip(prompts, outs):
+            assert o["usage"]["completion_tokens"] == 6 and o["usage"]["prompt_tokens"] == len(p)
+        toks = [o["choices"][0].get("tokens") for o in outs]
+        if all(t is not None for t in toks):
+            assert toks == [oracle.generate(p, 6) for p in prompts]
+        try:
+            urllib.request.urlopen(url + "/exit", timeout=10).read()
+        except Exception:
+            pass
+        stats = sorted(q.get(timeout=120) for _ in range(2))
+        assert stats[0][1] + stats[1][1] == 18 and stats[1][1] == 6          # rank 1 generated the second request's tokens
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.terminate()
