@@ -31,6 +31,7 @@ class ParsedRequest:
     model: str
     stop: List[str] = field(default_factory=list)
     return_tokens: bool = False
+    grammar: Optional[str] = None      # GBNF text derived from response_format (not enforced at sampling time)
 
 
 def tokenize_mixed(tokenizer, prompt: Any, add_special: bool) -> List[int]:
@@ -128,9 +129,16 @@ def parse_chat(body: Dict[str, Any], tokenizer, template, model_alias: str, defa
         prompt = template.render(msgs, tools=body.get("tools"), add_generation_prompt=True)
     except ValueError as e:
         raise BadRequest(str(e))
+    grammar = None
+    if isinstance(rf, dict):
+        from .json_schema import SchemaError, grammar_for_response_format
+        try:
+            grammar = grammar_for_response_format(rf)
+        except (SchemaError, ValueError) as e:
+            raise BadRequest(f"response_format: {e}")
     params = sampling_from_body(body, default_max)
     return ParsedRequest([tokenizer.encode(prompt, add_special=True, parse_special=True)], params, bool(body.get("stream", False)),
-                         True, str(body.get("model", model_alias)), params.stop)
+                         True, str(body.get("model", model_alias)), params.stop, bool(body.get("return_tokens", False)), grammar)
 
 
 # ---- responses -------------------------------------------------------------------------------------
