@@ -56,10 +56,21 @@ def nvcc_path() -> str:
     return p
 
 
-def build_runtime(force: bool = False, verbose: bool = False) -> str:
+def build_runtime(force: bool = False, verbose: bool = False, sanitize: str = "") -> str:
+    """``sanitize``: e.g. "address,undefined" or "thread" builds a separate instrumented library
+    (libjib200_runtime_<san>.so) for running the host-side tests under the sanitizers; load it by pointing
+    JITTORINFER_RUNTIME_SO at it and preloading the sanitizer runtime (``gcc -print-file-name=libasan.so``)."""
     srcs = sorted(glob.glob(os.path.join(CSRC, "runtime", "*.cpp")))
     deps = srcs + glob.glob(os.path.join(CSRC, "runtime", "*.h")) + glob.glob(os.path.join(CSRC, "include", "*.h"))
     os.makedirs(LIBDIR, exist_ok=True)
+    if sanitize:
+        tag = sanitize.replace(",", "_")
+        out = os.path.join(LIBDIR, f"libjib200_runtime_{tag}.so")
+        if force or _newer(deps, out):
+            _run(["g++", "-std=c++17", "-O1", "-g", "-fPIC", "-fno-omit-frame-pointer", f"-fsanitize={sanitize}", "-fvisibility=hidden",
+                  "-I", os.path.join(CSRC, "include"), "-I", os.path.join(CSRC, "runtime"), "-shared", "-o", out] + srcs +
+                 ["-lpthread", "-ldl"], verbose)
+        return out
     if force or _newer(deps, RUNTIME_SO):
         objs = []
         objdir = os.path.join(LIBDIR, "obj")

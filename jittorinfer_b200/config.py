@@ -23,7 +23,7 @@ SPLIT_MODES = ("LLAMA_SPLIT_MODE_NONE", "LLAMA_SPLIT_MODE_LAYER", "LLAMA_SPLIT_M
 REASONING_FORMATS = ("COMMON_REASONING_FORMAT_NONE", "COMMON_REASONING_FORMAT_DEEPSEEK")
 
 # accepted for file compatibility; they tune the reference's CPU/NPU back ends and have no effect here
-IGNORED_KEYS = {"n_threads", "n_threads_batch", "use_mlock", "check_tensors", "offload_input", "n_gpu_layers", "tensor_split",
+IGNORED_KEYS = {"n_threads", "n_threads_batch", "use_mlock", "check_tensors", "offload_input", "n_gpu_layers",
                 "enable_cann_flash_attention", "enable_fused_moe", "reranking", "no_perf"}
 
 
@@ -57,8 +57,13 @@ class ServerConfig:
     ep_size: int = 1
     kv_block_size: int = 64
     gpu_memory_utilization: float = 0.9
+    kv_cache_auto: bool = False        # size the latent cache from the memory left after the weights (gpu_memory_utilization
+                                       # of the device) instead of n_ctx
+    max_seq_len: int = 0               # per-sequence token limit; 0 = n_ctx / slots as in the reference
     max_num_seqs: Optional[int] = None
     cuda_graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
+    layer_split_gpus: int = 1          # split_mode LAYER: consecutive layer ranges on this many GPUs of one process
+    tensor_split: Tuple[float, ...] = ()   # relative share of layers per GPU (reference key; empty = even)
     attention_dp: bool = False         # ep_size ranks each serve their own requests (attention data-parallel), routed experts
                                        # sharded over them and reached through the all-to-all dispatcher
     ep_max_tokens: int = 256           # attention_dp: most tokens one rank schedules per step (sizes the dispatch buffers)
@@ -112,6 +117,8 @@ def load_yaml(path: Optional[str]) -> ServerConfig:
         if k in known:
             if k == "cuda_graph_buckets":
                 v = tuple(int(x) for x in v)
+            if k == "tensor_split":
+                v = tuple(float(x) for x in (v or ()))
             if k == "n_parallel":
                 v = int(v)          # the reference clamps to 32 (cell bitset); block tables have no such limit
             setattr(cfg, k, v)

@@ -53,6 +53,31 @@ class ForwardBatch:
     attn_meta: Optional[object] = None
 
 
+def _batch_to(b: ForwardBatch, dev: torch.device) -> ForwardBatch:
+    mv = lambda t: None if t is None else t.to(dev, non_blocking=True)
+    return ForwardBatch(mv(b.tokens), mv(b.positions), mv(b.slot_mapping), mv(b.block_tables), mv(b.seq_lens), mv(b.q_start),
+                        mv(b.out_rows), b.max_q_len, None)
+
+
+def assign_layers(n_layer: int, devices, tensor_split=None):
+    """Contiguous layer ranges per device, proportional to ``tensor_split`` (even when omitted), every device getting
+    at least one layer when there are enough (reference: src/llama-model.cpp:495-540, 551-563)."""
+    devices = list(devices)
+    n = len(devices)
+    w = [float(x) for x in tensor_split][:n] if tensor_split else [1.0] * n
+    w += [0.0] * (n - len(w))
+    total = sum(w) or 1.0
+    bounds, acc = [], 0.0
+    for x in w:
+        acc += x
+        bounds.append(acc / total)
+    out = []
+    for il in range(n_layer):
+        frac = (il + 0.5) / n_layer
+        out.append(devices[next(i for i, b in enumerate(bounds) if frac <= b + 1e-9)])
+    return out
+
+
 class _Layer:
     __slots__ = ("attn_norm", "w_qkv_a", "q_a_norm", "w_q_b", "kv_a_norm", "w_uk", "w_uv", "w_o", "ffn_norm",
                  "w_gate", "w_up", "w_down", "w_router", "router_bias", "w_gate_exps", "w_up_exps", "w_down_exps",
@@ -66,12 +91,23 @@ class _Layer:
 class DeepSeek2Model:
     def __init__(self, hp: DeepSeek2HParams, weights: Iterable[Tuple[str, torch.Tensor]],
                  dtype: torch.dtype = torch.bfloat16, device="cpu", spec: ShardSpec = ShardSpec(),
-                 comm=None, max_positions: int = 8192, block_size: int = 64, ep=None):
+                 comm=None, max_positions: int = 8192, block_size: int = 64, ep=None, layer_devices=None):
         self.hp = hp
         self.dtype = dtype
         self.device = torch.device(device)
         self.spec = spec
         self.comm = comm
+        # Layer split (the reference's default LLAMA_SPLIT_MODE_LAYER, src/llama-model.cpp:495-540): consecutive layer
+        # ranges live on consecutive devices of this one process and the activations hop between them; no pipelining
+        # (the reference's scheduler cannot pipeline on its device back end either, ggml-cann.cpp:2301-2306).
+        self.layer_dev = [torch.device(d) for d in layer_devices] if layer_devices else [self.device] * hp.n_layer
+        if len(self.layer_dev) != hp.n_layer:
+            raise ValueError("layer_devices needs one entry per layer")
+        self.split = any(d != self.device for d in self.layer_dev)
+        if self.split and spec.sharded:
+            raise ValueError("layer split and tensor / expert parallelism are separate modes")
+        self.out_device = self.layer_dev[-1]
+        self._cur_dev = self.device
         self.ep = ep                      # all-to-all dispatcher (data-parallel attention + expert parallelism)
         self.block_size = block_size
         if spec.dp_attention:
@@ -99,10 +135,19 @@ class DeepSeek2Model:
         self.max_positions = max_positions
         self.rope_table = ops.ref.yarn_table(max_positions, hp.qk_rope_head_dim, hp.rope_freq_base, hp.freq_scale,
                                              hp.ext_factor, hp.rope_attn, lo, hi, device=self.device)
+        self._rope_by_dev = {}
+
+    def _rope(self, dev: torch.device) -> torch.Tensor:
+        if not self.split or dev == self.rope_table.device:
+            return self.rope_table
+        t = self._rope_by_dev.get(dev)
+        if t is None or t.shape != self.rope_table.shape:
+            t = self._rope_by_dev[dev] = self.rope_table.to(dev)
+        return t
 
     # ---- weight intake -------------------------------------------------------------------
     def _dev(self, t: torch.Tensor, dtype=None) -> torch.Tensor:
-        return t.to(device=self.device, dtype=dtype or self.dtype).contiguous()
+        return t.to(device=self._cur_dev, dtype=dtype or self.dtype).contiguous()
 
     def _load(self, weights: Iterable[Tuple[str, torch.Tensor]]):
         hp = self.hp
@@ -110,6 +155,10 @@ class DeepSeek2Model:
         pend: Dict[str, torch.Tensor] = {}
         for name, t in weights:
             _trace.log_tensor(name, t.shape, t.dtype, f"rank {self.spec.tp_rank}/{self.spec.tp_size}" if self.spec.sharded else "")
+            if name.startswith("blk."):
+                self._cur_dev = self.layer_dev[int(name.split(".", 2)[1])]
+            else:
+                self._cur_dev = self.out_device if name in ("output_norm.weight", "output.weight") else self.device
             if name == "token_embd.weight":
                 self.tok_embd = self._dev(t)
             elif name == "output_norm.weight":
@@ -171,8 +220,9 @@ class DeepSeek2Model:
                     raise KeyError(f"unknown tensor {name}")
             else:
                 raise KeyError(f"unknown tensor {name}")
+        self._cur_dev = self.device
         if self.w_out is None:
-            self.w_out = self.tok_embd
+            self.w_out = self.tok_embd if self.out_device == self.device else self.tok_embd.to(self.out_device)
         if not self.spec.sharded:
             # single-GPU: the shared experts have the routed experts' shape, so they become experts E, E+1, ... of the
             # grouped GEMMs (two fewer launches per layer, better fill); the router appends them to every token
@@ -230,7 +280,7 @@ class DeepSeek2Model:
             qa, _ = ops.rmsnorm(qkv[:, :nq], L.q_a_norm, hp.rms_eps)
             q = ops.linear(qa, L.w_q_b)
         q_full = torch.empty(T, H, r + dr, dtype=h.dtype, device=h.device)
-        q_nope = ops.mla_qkv_post(q, ckv, L.kv_a_norm, hp.rms_eps, self.rope_table, batch.positions,
+        q_nope = ops.mla_qkv_post(q, ckv, L.kv_a_norm, hp.rms_eps, self._rope(h.device), batch.positions,
                                   batch.slot_mapping, cache_l, q_full, H, dn, dr, r)
         ops.q_absorb(q_nope, L.w_uk, q_full, r)
         o_lat = ops.mla_attention(q_full, cache_l, batch.block_tables, batch.seq_lens, batch.q_start, hp.kq_scale,
@@ -283,7 +333,17 @@ class DeepSeek2Model:
             return self._forward_idle()
         x = ops.embed_gather(self.tok_embd, batch.tokens)
         nvtx = _trace.nvtx_enabled()
+        by_dev = {self.device: batch}
         for il, L in enumerate(self.layers):
+            if self.split:
+                dev = self.layer_dev[il]
+                if x.device != dev:
+                    x = x.to(dev, non_blocking=True)          # the hop between two layer ranges
+                    if dev.type == "cuda":
+                        torch.cuda.set_device(dev)            # launches follow the current device's stream
+                batch = by_dev.get(dev)
+                if batch is None:
+                    batch = by_dev[dev] = _batch_to(by_dev[self.device], dev)
             if nvtx:
                 torch.cuda.nvtx.range_push(f"layer{il}")
             h, _ = ops.rmsnorm(x, L.attn_norm, hp.rms_eps)
@@ -295,4 +355,7 @@ class DeepSeek2Model:
                 torch.cuda.nvtx.range_pop()
         xo = ops.select_rows(x, batch.out_rows) if batch.out_rows is not None else x
         xo, _ = ops.rmsnorm(xo, self.out_norm, hp.rms_eps)
-        return ops.linear(xo, self.w_out, out_dtype=torch.float32)
+        logits = ops.linear(xo, self.w_out, out_dtype=torch.float32)
+        if self.split and self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        return logits

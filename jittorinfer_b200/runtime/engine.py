@@ -97,6 +97,36 @@ class _StepIO:
         return self.dev_len * 4
 
 
+class SplitCache:
+    """Latent cache of a layer-split model: one [layers-on-device, n_slots, row] tensor per device; ``cache[il]`` is the
+    layer's slice on its own device."""
+
+    def __init__(self, layer_dev, n_slots: int, row: int, dtype, block_size: int):
+        self.block_size = block_size
+        self.by_dev: Dict[torch.device, torch.Tensor] = {}
+        self.index: List[Tuple[torch.device, int]] = []
+        counts: Dict[torch.device, int] = {}
+        for d in layer_dev:
+            self.index.append((d, counts.get(d, 0)))
+            counts[d] = counts.get(d, 0) + 1
+        for d, n in counts.items():
+            self.by_dev[d] = torch.zeros(n, n_slots, row, dtype=dtype, device=d)
+
+    def __getitem__(self, il: int) -> torch.Tensor:
+        d, i = self.index[il]
+        return self.by_dev[d][i]
+
+    def copy_blocks(self, src: np.ndarray, dst: np.ndarray) -> None:
+        for d, t in self.by_dev.items():
+            s = torch.from_numpy(np.ascontiguousarray(src)).to(d)
+            e = torch.from_numpy(np.ascontiguousarray(dst)).to(d)
+            if d.type == "cuda":
+                with torch.cuda.device(d):
+                    ops.kv_block_copy(t, s, e, self.block_size)
+            else:
+                ops.kv_block_copy(t, s, e, self.block_size)
+
+
 class LLMEngine:
     def __init__(self, model: DeepSeek2Model, cfg: EngineConfig = EngineConfig()):
         self.model = model
@@ -112,15 +142,18 @@ class LLMEngine:
         self.kv = PagedKV(self.n_blocks, bs, cfg.n_parallel)
         self.sched = Scheduler(self.kv, cfg.n_parallel, cfg.n_batch, self.n_ctx_slot, self.hp.eos_id, cfg.n_keep,
                                cfg.cont_batching)
-        self.kv_cache = torch.zeros(self.hp.n_layer, self.n_blocks * bs, self.hp.kv_row, dtype=model.dtype,
-                                    device=self.device)
+        if getattr(model, "split", False):
+            self.kv_cache = SplitCache(model.layer_dev, self.n_blocks * bs, self.hp.kv_row, model.dtype, bs)
+        else:
+            self.kv_cache = torch.zeros(self.hp.n_layer, self.n_blocks * bs, self.hp.kv_row, dtype=model.dtype,
+                                        device=self.device)
         cap_tokens = max(cfg.n_batch, max(cfg.graph_buckets))
         cap_seqs = max(cfg.n_parallel, max(cfg.graph_buckets))
         self.io = _StepIO(cap_tokens, cap_seqs, self.max_blocks, self.device)
         self.requests: Dict[int, RequestState] = {}
         self._next_id = 1
         self._graphs: Dict[Tuple[int, str], Tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
-        self._use_graphs = cfg.cuda_graphs and self.device.type == "cuda"
+        self._use_graphs = cfg.cuda_graphs and self.device.type == "cuda" and not getattr(model, "split", False)
         self._out_host = torch.zeros(cap_seqs * (1 + 2 * max(1, cfg.presample_count)), dtype=torch.int32,
                                      pin_memory=self.device.type == "cuda")
         self.stats = {"steps": 0, "graph_steps": 0, "eager_steps": 0, "tokens_in": 0, "tokens_out": 0,
@@ -178,6 +211,10 @@ class LLMEngine:
         return torch.cat([v.contiguous().view(torch.int32), i], dim=-1)
 
     def _forward_sample(self, batch: ForwardBatch, mode: str) -> torch.Tensor:
+        if getattr(self.model, "split", False) and self.device.type == "cuda":
+            logits = self.model.forward(batch, self.kv_cache)
+            with torch.cuda.device(logits.device):
+                return self._sample_device(logits, mode)
         logits = self.model.forward(batch, self.kv_cache)
         return self._sample_device(logits, mode)
 
@@ -287,6 +324,9 @@ class LLMEngine:
         return len(src)
 
     def _copy_blocks(self, src: np.ndarray, dst: np.ndarray):
+        if isinstance(self.kv_cache, SplitCache):
+            self.kv_cache.copy_blocks(src, dst)
+            return
         s = torch.from_numpy(np.ascontiguousarray(src)).to(self.device)
         d = torch.from_numpy(np.ascontiguousarray(dst)).to(self.device)
         ops.kv_block_copy(self.kv_cache, s, d, self.cfg.block_size)
@@ -379,7 +419,7 @@ class LLMEngine:
             host = self._out_host[:n_el]
             host.copy_(flat, non_blocking=True)
             if self.device.type == "cuda":
-                torch.cuda.current_stream(self.device).synchronize()
+                torch.cuda.current_stream(out.device).synchronize()
             if pt:
                 pt.mark("wait")
             self.stats["d2h_bytes"] += n_el * 4

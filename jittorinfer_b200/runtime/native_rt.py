@@ -30,8 +30,11 @@ def lib():
         if _lib is not None:
             return _lib
         from .. import build
-        path = build.RUNTIME_SO
-        if not os.path.exists(path) or os.environ.get("JITTORINFER_REBUILD"):
+        override = os.environ.get("JITTORINFER_RUNTIME_SO")      # e.g. a sanitizer-instrumented build
+        path = override or build.RUNTIME_SO
+        if override:
+            pass
+        elif not os.path.exists(path) or os.environ.get("JITTORINFER_REBUILD"):
             build.build_runtime()
         else:
             try:

@@ -18,12 +18,18 @@ def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
     if device is None:
         device = torch.device("cuda", cfg.main_gpu if world == 1 else rank) if torch.cuda.is_available() else torch.device("cpu")
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
-    n_ctx_slot = max(cfg.kv_block_size, cfg.n_ctx // cfg.slots)
-    common = dict(device=device, dtype=dtype, world=world, rank=rank, n_parallel=cfg.slots, n_ctx_slot=n_ctx_slot, n_ctx=cfg.n_ctx,
+    auto_kv = bool(getattr(cfg, "kv_cache_auto", False)) and device.type == "cuda"
+    n_ctx_slot = getattr(cfg, "max_seq_len", 0) or max(cfg.kv_block_size, cfg.n_ctx // cfg.slots)
+    common = dict(device=device, dtype=dtype, world=world, rank=rank, n_parallel=cfg.slots, n_ctx_slot=n_ctx_slot,
+                  n_ctx=None if auto_kv else cfg.n_ctx, gpu_memory_utilization=cfg.gpu_memory_utilization if auto_kv else None,
                   n_batch=cfg.n_batch, cuda_graphs=cfg.cuda_graphs, graph_buckets=tuple(b for b in cfg.cuda_graph_buckets if b <= cfg.slots) or (1,),
                   expert_parallel=cfg.ep_size > 1, n_keep=cfg.n_keep, cont_batching=cfg.cont_batching, defrag_thold=cfg.defrag_thold,
                   presample_count=max(1, cfg.presample_count) if cfg.presample_count > 0 else 64,
                   dp_attention=bool(getattr(cfg, "attention_dp", False)) and world > 1, ep_max_tokens=getattr(cfg, "ep_max_tokens", 256))
+    if world == 1 and device.type == "cuda" and getattr(cfg, "layer_split_gpus", 1) > 1 and cfg.split_mode == "LLAMA_SPLIT_MODE_LAYER":
+        n = min(cfg.layer_split_gpus, torch.cuda.device_count())
+        common.update(layer_devices=[torch.device("cuda", (cfg.main_gpu + i) % torch.cuda.device_count()) for i in range(n)],
+                      tensor_split=list(cfg.tensor_split) or None)
     if cfg.random_init:
         hp = preset(cfg.random_init)
         eng = build_engine(hp, **common)

@@ -37,3 +37,15 @@ def test_bad_values_rejected(tmp_path):
         p.write_text(body)
         with pytest.raises(ValueError):
             load_yaml(str(p))
+
+
+def test_kv_cache_sizing_from_memory_budget():
+    from jittorinfer_b200.runtime.factory import kv_tokens_for_budget
+    GB = 1 << 30
+    # DeepSeek-V2 on a 180 GB device with 60 GB of weights resident: 90 % occupancy leaves room for ~1.4 M tokens
+    n = kv_tokens_for_budget(180 * GB, 120 * GB, 0.9, n_layer=60, kv_row=576, elem_bytes=2)
+    assert n % 64 == 0 and 1_400_000 < n < 1_600_000
+    assert (180 * 0.9 - 60 - 2) * GB - n * 60 * 576 * 2 < 64 * 60 * 576 * 2 + GB        # fills the budget to within a block
+    assert kv_tokens_for_budget(180 * GB, 10 * GB, 0.9, 60, 576, 2) == 0                # weights already exceed the budget
+    cfg = ServerConfig(kv_cache_auto=True, max_seq_len=4352, gpu_memory_utilization=0.9)
+    cfg.validate()

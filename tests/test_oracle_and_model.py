@@ -78,3 +78,23 @@ def test_engine_sampling_modes_run():
     assert a == b and len(a[0]) == 12          # same seed -> same tokens
     c = eng.generate([[1, 2, 3, 4]], SamplingParams(temperature=0.8, seed=4, max_tokens=12, ignore_eos=True))
     assert len(c[0]) == 12
+
+
+def test_layer_split_matches_oracle():
+    """Layer ranges on different devices (two spellings of the CPU stand in for two GPUs): per-device cache tensors,
+    per-device copies of the step inputs, activations hopping between ranges."""
+    from jittorinfer_b200.models.deepseek2 import assign_layers
+    assert assign_layers(4, ["a", "b"]) == ["a", "a", "b", "b"]
+    assert assign_layers(5, ["a", "b"], [3, 1]) == ["a", "a", "a", "a", "b"]
+    assert assign_layers(3, ["a", "b", "c"], None) == ["a", "b", "c"]
+    hp = preset("tiny-v2")
+    w = random_weights(hp, seed=0)
+    devs = assign_layers(hp.n_layer, [torch.device("cpu"), torch.device("cpu", 0)])
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32, layer_devices=devs)
+    assert m.split and len({str(d) for d in m.layer_dev}) == 2
+    eng = LLMEngine(m, EngineConfig(n_ctx=1024, n_batch=32, n_parallel=2))
+    assert len(eng.kv_cache.by_dev) == 2
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (50, 9)]
+    ref = [OracleModel(hp, w).generate(p, 8) for p in prompts]
+    assert eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=8) == ref
