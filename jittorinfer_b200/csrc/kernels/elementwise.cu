@@ -10,6 +10,7 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "bounds_check.cuh"
 #include "jib_kernels.h"
 #include "pdl.cuh"
 #include "sm100.cuh"
@@ -47,6 +48,7 @@ __global__ void embed_gather_kernel(const bf16 * __restrict__ table, const int *
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const int t = blockIdx.x;
     int id = ids[t];
+    JIB_BC(id >= 0 && id < n_vocab, 12, id);
     id = id < 0 ? 0 : (id >= n_vocab ? n_vocab - 1 : id);
     const uint4 * src = (const uint4 *) (table + (size_t) id * d);
     uint4 * dst = (uint4 *) (out + (size_t) t * d);
@@ -296,6 +298,7 @@ __global__ void gather_rows_kernel(const bf16 * __restrict__ x, const int * __re
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const int rrow = blockIdx.x;
     const int s = src_row[rrow];
+    JIB_BC(s < n_src, 13, s);
     if (s < 0 || s >= n_src) return;   // unowned / out-of-range row: leave the destination untouched
     const uint4 * src = (const uint4 *) (x + (size_t) s * d);
     uint4 * dst = (uint4 *) (out + (size_t) rrow * d);
@@ -306,7 +309,18 @@ inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAU
 
 }  // namespace
 
+JIB_BC_DEFINE_SETTER(elementwise)
+
 extern "C" {
+
+// 1 when the library was built with -DJIB_BOUNDS_CHECK
+JIB_EXPORT int jib_bounds_check_enabled(void) {
+#ifdef JIB_BOUNDS_CHECK
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 int jib_embed_gather(const void * table, const int * ids, void * out, int T, int d, int n_vocab, void * stream) {
     if (T <= 0) return 0;

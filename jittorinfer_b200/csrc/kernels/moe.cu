@@ -10,6 +10,7 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "bounds_check.cuh"
 #include "jib_kernels.h"
 #include "pdl.cuh"
 
@@ -229,6 +230,7 @@ __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __re
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         for (int j = 0; j < k; ++j) {
             const int row = dest[(size_t) t * k + j];
+            JIB_BC(row < (int) gridDim.x * k, 14, row);
             if (row < 0) continue;
             const float w = wts[(size_t) t * k + j];
             const uint4 raw = ((const uint4 *) (y + (size_t) row * d))[i];
@@ -271,6 +273,8 @@ __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __re
 inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH; }
 
 }  // namespace
+
+JIB_BC_DEFINE_SETTER(moe)
 
 extern "C" {
 

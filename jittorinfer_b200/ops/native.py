@@ -34,7 +34,7 @@ def load():
     if _lib is not None:
         return _lib
     from .. import build
-    path = build.KERNELS_SO
+    path = os.environ.get("JITTORINFER_KERNELS_SO") or build.KERNELS_SO      # e.g. the bounds-check build
     if not os.path.exists(path):
         build.build_kernels()
     L = C.CDLL(path)
@@ -76,6 +76,13 @@ class Workspace:
         self.counters = torch.zeros(self.N_COUNTERS, dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        L = load()
+        if hasattr(L, "jib_bounds_check_enabled") and L.jib_bounds_check_enabled():
+            with torch.cuda.device(device):          # bounds-check build: clamped indices are also reported here
+                for unit in ("elementwise", "moe"):
+                    fn = getattr(L, "jib_bounds_status_" + unit)
+                    fn.restype, fn.argtypes = C.c_int, [C.c_void_p]
+                    fn(self.status.data_ptr())
 
 
 def workspace(device: torch.device) -> Workspace:
