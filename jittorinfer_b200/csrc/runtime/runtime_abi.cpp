@@ -151,3 +151,146 @@ JIB_API int jib_tok_bos(Tokenizer * t) { return t->config().bos; }
 JIB_API int jib_tok_eos(Tokenizer * t) { return t->config().eos; }
 JIB_API int jib_tok_eot(Tokenizer * t) { return t->config().eot; }
 JIB_API int jib_utf8_incomplete_tail(const char * s, int len) { return (int) utf8_incomplete_tail(std::string(s, len)); }
+
+// ---- GGUF reader ------------------------------------------------------------------------------
+#include "gguf.h"
+
+#include <cmath>
+#include <cstdio>
+#include <string>
+
+namespace {
+
+void json_escape(const std::string & in, std::string & out) {
+    out.push_back('"');
+    for (unsigned char c : in) {
+        switch (c) {
+            case '"': out += "\\\""; break;
+            case '\\': out += "\\\\"; break;
+            case '\n': out += "\\n"; break;
+            case '\r': out += "\\r"; break;
+            case '\t': out += "\\t"; break;
+            default:
+                if (c < 0x20) {
+                    char buf[8];
+                    snprintf(buf, sizeof(buf), "\\u%04x", c);
+                    out += buf;
+                } else {
+                    out.push_back((char) c);
+                }
+        }
+    }
+    out.push_back('"');
+}
+
+void json_number(double v, bool is_float, std::string & out) {
+    char buf[40];
+    if (!is_float) {
+        snprintf(buf, sizeof(buf), "%lld", (long long) v);
+    } else if (std::isfinite(v)) {
+        snprintf(buf, sizeof(buf), "%.17g", v);
+    } else {
+        snprintf(buf, sizeof(buf), "null");
+    }
+    out += buf;
+}
+
+template <typename T>
+void json_array(const uint8_t * p, uint64_t n, bool is_float, std::string & out) {
+    out.push_back('[');
+    for (uint64_t i = 0; i < n; ++i) {
+        T v;
+        memcpy(&v, p + i * sizeof(T), sizeof(T));
+        if (i) out.push_back(',');
+        json_number((double) v, is_float, out);
+    }
+    out.push_back(']');
+}
+
+std::string kv_to_json(const GgufFile & f) {
+    std::string out = "{";
+    bool first = true;
+    for (const auto & it : f.kv()) {
+        if (!first) out.push_back(',');
+        first = false;
+        json_escape(it.first, out);
+        out.push_back(':');
+        const GgufValue & v = it.second;
+        if (v.type == GT_STR) {
+            json_escape(v.s, out);
+        } else if (v.type == GT_ARR) {
+            if (v.arr_type == GT_STR) {
+                out.push_back('[');
+                for (size_t i = 0; i < v.arr_s.size(); ++i) {
+                    if (i) out.push_back(',');
+                    json_escape(v.arr_s[i], out);
+                }
+                out.push_back(']');
+            } else {
+                switch (v.arr_type) {
+                    case GT_U8: case GT_BOOL: json_array<uint8_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_I8: json_array<int8_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_U16: json_array<uint16_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_I16: json_array<int16_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_U32: json_array<uint32_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_I32: json_array<int32_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_U64: json_array<uint64_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_I64: json_array<int64_t>(v.arr_data, v.arr_n, false, out); break;
+                    case GT_F32: json_array<float>(v.arr_data, v.arr_n, true, out); break;
+                    case GT_F64: json_array<double>(v.arr_data, v.arr_n, true, out); break;
+                    default: out += "null";
+                }
+            }
+        } else if (v.type == GT_BOOL) {
+            out += v.u ? "true" : "false";
+        } else if (v.type == GT_F32 || v.type == GT_F64) {
+            json_number(v.f, true, out);
+        } else {
+            json_number((double) (int64_t) v.u, false, out);
+        }
+    }
+    out.push_back('}');
+    return out;
+}
+
+}  // namespace
+
+struct jib_gguf {
+    GgufFile file;
+    std::string kv_json;
+};
+
+// Opens and parses a GGUF file.  On failure returns NULL and writes the reason (NUL-terminated) into err.
+JIB_API jib_gguf * jib_gguf_open(const char * path, int populate, char * err, int err_cap) {
+    jib_gguf * g = new jib_gguf();
+    const std::string e = g->file.open(path ? path : "", populate != 0);
+    if (!e.empty()) {
+        if (err != nullptr && err_cap > 0) snprintf(err, (size_t) err_cap, "%s", e.c_str());
+        delete g;
+        return nullptr;
+    }
+    return g;
+}
+JIB_API void jib_gguf_close(jib_gguf * g) { delete g; }
+JIB_API int jib_gguf_version(jib_gguf * g) { return (int) g->file.version(); }
+JIB_API int jib_gguf_alignment(jib_gguf * g) { return (int) g->file.alignment(); }
+JIB_API int64_t jib_gguf_n_tensors(jib_gguf * g) { return (int64_t) g->file.tensors().size(); }
+// Tensor i: name (NUL-terminated, truncated to name_cap), ne[0..nd) in ggml order, ggml type, byte size, data pointer
+// into the read-only mapping (valid until close).  Returns the number of dimensions, or -1.
+JIB_API int jib_gguf_tensor_info(jib_gguf * g, int64_t i, char * name, int name_cap, uint64_t * ne, uint32_t * type, uint64_t * nbytes,
+                                 const void ** data) {
+    if (i < 0 || (size_t) i >= g->file.tensors().size()) return -1;
+    const GgufTensor & t = g->file.tensors()[(size_t) i];
+    if (name != nullptr && name_cap > 0) snprintf(name, (size_t) name_cap, "%s", t.name.c_str());
+    for (size_t d = 0; d < t.ne.size() && d < 8; ++d) ne[d] = t.ne[d];
+    *type = t.type;
+    *nbytes = t.nbytes;
+    *data = g->file.tensor_data(t);
+    return (int) t.ne.size();
+}
+// All key/value pairs as one JSON object (UTF-8).  Returns the byte length; copies min(length, cap) bytes.
+JIB_API int64_t jib_gguf_kv_json(jib_gguf * g, char * buf, int64_t cap) {
+    if (g->kv_json.empty()) g->kv_json = kv_to_json(g->file);
+    if (buf != nullptr && cap > 0) memcpy(buf, g->kv_json.data(), (size_t) std::min<int64_t>(cap, (int64_t) g->kv_json.size()));
+    return (int64_t) g->kv_json.size();
+}

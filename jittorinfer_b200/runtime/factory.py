@@ -25,7 +25,11 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
     dp_attention = dp_attention and world > 1
     spec = ShardSpec(rank, world, (expert_parallel or dp_attention) and world > 1, dp_attention)
     if gguf_path is not None:
-        from ..gguf.io import GGUFReader
+        import os
+        if os.environ.get("JITTORINFER_GGUF", "").lower() == "native":
+            from ..gguf.native_reader import NativeGGUFReader as GGUFReader      # C++ parser + mapping
+        else:
+            from ..gguf.io import GGUFReader
         reader = GGUFReader(gguf_path)
         hp = DeepSeek2HParams.from_gguf_kv(reader.kv, reader.tensors)
         weights = iter_gguf(reader, hp, spec)

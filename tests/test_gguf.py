@@ -54,3 +54,42 @@ def test_random_gguf_loads_back_and_shards_agree(tmp_path):
             assert all(torch.equal(from_file[k].float(), from_rng[k]) for k in from_rng)
     e = full["blk.1.ffn_gate_exps.weight"]
     assert torch.equal(dict(iter_gguf(r, hp2, ShardSpec(1, 2, True)))["blk.1.ffn_gate_exps.weight"], e[e.shape[0] // 2:])
+
+
+def test_native_reader_matches_python_reader(tmp_path, monkeypatch):
+    """The C++ parser sees the same key/values, tensor table and bytes as the Python one, and a model loaded through it
+    produces the same logits."""
+    import numpy as np
+    import torch
+    from jittorinfer_b200.gguf.io import GGUFReader
+    from jittorinfer_b200.gguf.native_reader import NativeGGUFReader
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.models.weights import write_random_gguf
+    p = str(tmp_path / "m.gguf")
+    write_random_gguf(p, preset("tiny"), seed=3, dtype=torch.bfloat16)
+    py, nat = GGUFReader(p), NativeGGUFReader(p)
+    assert nat.version == py.version and nat.alignment == py.alignment
+    assert set(nat.kv) == set(py.kv)
+    for k, v in py.kv.items():
+        w = nat.kv[k]
+        if isinstance(v, np.ndarray):
+            assert list(v.tolist()) == w, k
+        elif isinstance(v, float):
+            assert abs(v - w) <= 1e-6 * max(1.0, abs(v)), k
+        else:
+            assert v == w, k
+    assert list(nat.tensors) == list(py.tensors)
+    for name, ti in py.tensors.items():
+        tn = nat.tensors[name]
+        assert (tn.shape, tn.ggml_type, tn.nbytes) == (ti.shape, ti.ggml_type, ti.nbytes)
+        assert np.array_equal(nat.raw(name), py.raw(name)), name
+    a = nat.tensor_slice("blk.1.ffn_gate_exps.weight", 0, 1, 2)
+    b = py.tensor_slice("blk.1.ffn_gate_exps.weight", 0, 1, 2)
+    assert torch.equal(a, b)
+    with __import__("pytest").raises(ValueError):
+        NativeGGUFReader(str(tmp_path / "missing.gguf"))
+    from jittorinfer_b200.runtime.factory import build_model
+    m_py = build_model(gguf_path=p, device="cpu", dtype=torch.float32)
+    monkeypatch.setenv("JITTORINFER_GGUF", "native")
+    m_nat = build_model(gguf_path=p, device="cpu", dtype=torch.float32)
+    assert torch.equal(m_py.layers[1].w_gate_exps, m_nat.layers[1].w_gate_exps) and torch.equal(m_py.tok_embd, m_nat.tok_embd)
