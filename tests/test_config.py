@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_shipped_configs_load():
     files = sorted(glob.glob(os.path.join(ROOT, "configs", "*.yaml")))
-    assert len(files) == 4
+    assert len(files) == 5          # the four reference configs + EP with data-parallel attention
     for f in files:
         c = load_yaml(f)
         assert c.model.endswith(".gguf") and c.n_parallel >= 8
