@@ -83,7 +83,7 @@ def reference_arm(args):
     # (pip: "Neither 'setup.py' nor 'pyproject.toml' found"), no CUDA backend and cannot execute on this machine.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a C++/CANN (Ascend NPU) project: not pip-installable (no setup.py/pyproject.toml), "
-                      "no CUDA backend; its published numbers are in BASELINE.md"}))
+                      "no CUDA backend; only its published numbers (other hardware) exist"}))
     return 0
 
 

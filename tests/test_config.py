@@ -23,7 +23,7 @@ def test_reference_style_file_and_defaults(tmp_path):
     p.write_text("main_gpu: 1\nn_gpu_layers: 99\nsplit_mode: LLAMA_SPLIT_MODE_LAYER\ntensor_split: [0]\nuse_mmap: true\n"
                  "n_threads: 128\ndefrag_thold: 0.5\nenable_mla: false\nenable_fused_moe: true\noffload_input: true\n"
                  "enable_ge: true\npresample_count: -1\nenable_cann_flash_attention: true\nn_ctx: 65536\nn_batch: 16\n"
-                 "n_parallel: 16\nmodel: \"/root/data/x-f16.gguf\"\nport: 8084\nn_threads_http: 16\nhostname: \"127.0.0.1\"\n"
+                 "n_parallel: 16\nmodel: \"/data/x-f16.gguf\"\nport: 8084\nn_threads_http: 16\nhostname: \"127.0.0.1\"\n"
                  "reasoning_format: COMMON_REASONING_FORMAT_DEEPSEEK\n")
     c = load_yaml(str(p))
     assert c.port == 8084 and c.n_ctx == 65536 and c.presample_count == -1 and c.cuda_graphs
