@@ -268,10 +268,13 @@ class DeepSeek2Model:
         return ops.linear(x, w, residual=residual)
 
     def _attention(self, L: _Layer, h: torch.Tensor, batch: ForwardBatch, cache_l: torch.Tensor) -> torch.Tensor:
+        return self._attention_from_qkv(L, ops.linear(h, L.w_qkv_a), batch, cache_l)
+
+    def _attention_from_qkv(self, L: _Layer, qkv: torch.Tensor, batch: ForwardBatch, cache_l: torch.Tensor) -> torch.Tensor:
         hp = self.hp
         H, dn, dr, r = self.n_head_local, hp.qk_nope_head_dim, hp.qk_rope_head_dim, hp.kv_lora_rank
-        T = h.shape[0]
-        qkv = ops.linear(h, L.w_qkv_a)
+        T = qkv.shape[0]
+        h = qkv
         nq = qkv.shape[1] - hp.kv_row
         ckv = qkv[:, nq:]
         if hp.is_lite:
@@ -308,6 +311,49 @@ class DeepSeek2Model:
         return ops.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                            L.w_down_sh, base)
 
+    def _forward_sp(self, batch: ForwardBatch, kv_cache) -> torch.Tensor:
+        """Tensor-parallel forward with a sequence-parallel residual stream (large prefill batches): every rank keeps
+        R = ceil(T / N) token rows between the blocks; row-parallel GEMMs end in a reduce-scatter, column-parallel ones
+        start from an all-gather.  Attention, routing and the experts still see all tokens (the latent cache is
+        replicated and expert parallelism here replicates tokens), so only the norms, the residual adds and the
+        collectives' second halves shrink -- and every row is reduced by exactly one rank."""
+        hp, comm = self.hp, self.comm
+        W, rk = self.spec.tp_size, self.spec.tp_rank
+        T = batch.tokens.shape[0]
+        R = (T + W - 1) // W
+        Tp = R * W
+        b = batch
+        if Tp > T:       # pad with rows that belong to no sequence and write no cache slot
+            pad = Tp - T
+            z = torch.zeros(pad, dtype=batch.tokens.dtype, device=batch.tokens.device)
+            b = ForwardBatch(torch.cat([batch.tokens, z]), torch.cat([batch.positions, z]),
+                             torch.cat([batch.slot_mapping, torch.full_like(z, -1)]), batch.block_tables, batch.seq_lens,
+                             batch.q_start, batch.out_rows, batch.max_q_len, None)
+        x = ops.embed_gather(self.tok_embd, b.tokens)[rk * R:(rk + 1) * R].contiguous()
+        for il, L in enumerate(self.layers):
+            h_loc, _ = ops.rmsnorm(x, L.attn_norm, hp.rms_eps)
+            qkv = comm.allgather_linear(h_loc, L.w_qkv_a)
+            a = self._attention_from_qkv(L, qkv, b, kv_cache[il])
+            if Tp > T:
+                a[T:] = 0
+            y = comm.linear_reduce_scatter(a, L.w_o, x)
+            g_loc, _ = ops.rmsnorm(y, L.ffn_norm, hp.rms_eps)
+            if not L.is_moe:
+                hmid = comm.allgather_linear(g_loc, L.w_gate, L.w_up)
+                x = comm.linear_reduce_scatter(hmid, L.w_down, y)
+            else:
+                g = comm.all_gather_rows(g_loc)
+                ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
+                                        hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid", 0)
+                base = self.expert_base if self.spec.expert_parallel else 0
+                part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
+                                   L.w_down_sh, base)
+                x = comm.reduce_scatter_rows(part, y)
+        x_full = comm.all_gather_rows(x)
+        xo = ops.select_rows(x_full, batch.out_rows) if batch.out_rows is not None else x_full[:T]
+        xo, _ = ops.rmsnorm(xo, self.out_norm, hp.rms_eps)
+        return ops.linear(xo, self.w_out, out_dtype=torch.float32)
+
     def _forward_idle(self) -> None:
         """A data-parallel rank without tokens still serves its experts to the other ranks: it joins every MoE
         layer's dispatch / combine with zero rows (the reference's llama_empty_run, src/llama-execute-decode.cpp:367-394)."""
@@ -331,6 +377,9 @@ class DeepSeek2Model:
             self.ep.begin_step()
         if batch is None:
             return self._forward_idle()
+        sp_min = getattr(self.comm, "sp_min_tokens", 0) if self.comm is not None else 0
+        if sp_min and self.spec.sharded and not self.spec.dp_attention and batch.tokens.shape[0] >= sp_min and batch.max_q_len > 1:
+            return self._forward_sp(batch, kv_cache)
         x = ops.embed_gather(self.tok_embd, batch.tokens)
         nvtx = _trace.nvtx_enabled()
         by_dev = {self.device: batch}

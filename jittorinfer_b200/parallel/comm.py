@@ -54,6 +54,45 @@ class Communicator:
         out = Communicator.all_reduce(self, part, residual)      # the library path, also when a subclass calls in
         return out if residual is not None else out.to(x.dtype)
 
+    # ---- sequence-parallel prefill: the residual stream is sharded by token rows ---------------------------------
+    # With T tokens and N ranks, rank r keeps rows [r*R, (r+1)*R), R = ceil(T/N).  A row-parallel GEMM ends in a
+    # reduce-scatter instead of an all-reduce (same bytes on the wire, 1/N of the norm / residual work afterwards) and
+    # the next column-parallel GEMM starts from an all-gather.  These four methods are the library form (NCCL / gloo);
+    # a communicator with in-kernel collectives overrides them.
+    sp_min_tokens = int(os.environ.get("JITTORINFER_SP_MIN_TOKENS", "0"))      # 0 = sequence parallelism off
+
+    def all_gather_rows(self, x_loc: torch.Tensor) -> torch.Tensor:
+        self.n_collectives += 1
+        out = torch.empty(self.world * x_loc.shape[0], x_loc.shape[1], dtype=x_loc.dtype, device=x_loc.device)
+        dist.all_gather_into_tensor(out, x_loc.contiguous(), group=self.group)
+        return out
+
+    def allgather_linear(self, x_loc: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """(all_gather(x_loc) @ w^T), or silu(.. @ w^T) * (.. @ w2^T) with a second weight."""
+        from .. import ops
+        x = self.all_gather_rows(x_loc)
+        return ops.gateup_silu(x, w, w2) if w2 is not None else ops.linear(x, w)
+
+    def reduce_scatter_rows(self, part: torch.Tensor, residual_loc: Optional[torch.Tensor]) -> torch.Tensor:
+        """This rank's rows of sum-over-ranks(part) (+ residual_loc); part has world * R rows."""
+        self.n_collectives += 1
+        R = part.shape[0] // self.world
+        y = part.float().contiguous()
+        out = torch.empty(R, part.shape[1], dtype=torch.float32, device=part.device)
+        try:
+            dist.reduce_scatter_tensor(out, y, group=self.group)
+        except (RuntimeError, NotImplementedError):       # back ends without reduce-scatter (gloo): reduce, then slice
+            dist.all_reduce(y, group=self.group)
+            out = y[self.rank * R:(self.rank + 1) * R]
+        if residual_loc is not None:
+            out = out + residual_loc.float()
+        return out.to(residual_loc.dtype if residual_loc is not None else part.dtype)
+
+    def linear_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual_loc: Optional[torch.Tensor]) -> torch.Tensor:
+        from .. import ops
+        out = self.reduce_scatter_rows(ops.linear(x, w, out_dtype=torch.float32), residual_loc)
+        return out if residual_loc is not None else out.to(x.dtype)
+
     def host_barrier(self) -> None:
         """Align the ranks on the host (used after one-off slow host work such as CUDA-graph capture)."""
         if dist.is_initialized() and self.world > 1:

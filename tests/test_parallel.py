@@ -26,9 +26,11 @@ def _free_port():
 PROMPT_LENS = (20, 70)
 
 
-def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q, prompt_lens=PROMPT_LENS, n_batch=48):
+def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q, prompt_lens=PROMPT_LENS, n_batch=48,
+            sp_min_tokens=0):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), JITTORINFER_COMM=comm_impl, NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), JITTORINFER_COMM=comm_impl, NCCL_NVLS_ENABLE="0",
+                      JITTORINFER_SP_MIN_TOKENS=str(sp_min_tokens))
     try:
         from jittorinfer_b200.models.deepseek2 import DeepSeek2Model
         from jittorinfer_b200.models.hparams import preset
@@ -67,12 +69,12 @@ def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl,
 
 
 def _run(world, backend, expert_parallel, preset_name="tiny-v2", comm_impl="nccl", graphs=True, timeout=150,
-         prompt_lens=PROMPT_LENS, n_batch=48):
+         prompt_lens=PROMPT_LENS, n_batch=48, sp_min_tokens=0):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q,
-                                               prompt_lens, n_batch))
+                                               prompt_lens, n_batch, sp_min_tokens))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -108,6 +110,19 @@ def test_tp_ep_two_cpu_ranks_match_oracle(expert_parallel):
     ref = _oracle("tiny-v2", False)
     assert res[0][1] == res[1][1] == ref            # every rank samples the same tokens as the single-rank oracle
     assert res[0][2] > 0                            # collectives really ran
+
+
+@pytest.mark.parametrize("expert_parallel", [True, False])
+def test_sequence_parallel_prefill_cpu_ranks_match_oracle(expert_parallel):
+    """Prefill chunks of 2+ tokens take the sequence-parallel path (row-sharded residual stream, reduce-scatter after
+    the row-parallel GEMMs, all-gather before the column-parallel ones); one case has an odd token count so that the
+    rows need padding."""
+    if expert_parallel:
+        res = _run(2, "gloo", True, sp_min_tokens=2)
+    else:
+        res = _run(2, "gloo", False, sp_min_tokens=2, prompt_lens=(21, 70))
+    ref = _oracle("tiny-v2", False, (20, 70) if expert_parallel else (21, 70))
+    assert res[0][1] == res[1][1] == ref
 
 
 @pytest.mark.gpu
