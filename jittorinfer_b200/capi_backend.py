@@ -50,7 +50,11 @@ class _Context:
         dtype = m.model.dtype
         self.block_size = block_size
         self.presample = presample
-        self.cache = torch.zeros(hp.n_layer, n_blocks * block_size, hp.kv_row, dtype=dtype, device=m.device)
+        if getattr(m.model, "split", False):
+            from .runtime.engine import SplitCache
+            self.cache = SplitCache(m.model.layer_dev, n_blocks * block_size, hp.kv_row, dtype, block_size)
+        else:
+            self.cache = torch.zeros(hp.n_layer, n_blocks * block_size, hp.kv_row, dtype=dtype, device=m.device)
         if n_ctx > m.model.max_positions:
             lo, hi = hp.yarn_corr_dims()
             m.model.max_positions = n_ctx
@@ -59,7 +63,7 @@ class _Context:
 
 
 def load_model(path: str, use_gpu: int, main_gpu: int, tp_id: int, num_parallel: int, expert_parallel: int,
-               check_tensors: int, data_parallel: int) -> int:
+               check_tensors: int, data_parallel: int, layer_split: str = "") -> int:
     from .runtime.factory import build_model
     on_gpu = bool(use_gpu) and torch.cuda.is_available()
     if on_gpu:
@@ -72,8 +76,16 @@ def load_model(path: str, use_gpu: int, main_gpu: int, tp_id: int, num_parallel:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29533")
         torch.distributed.init_process_group("nccl" if on_gpu else "gloo", rank=tp_id, world_size=num_parallel)
+    layer_devices, tensor_split = None, None
+    if layer_split and on_gpu and num_parallel == 1 and torch.cuda.device_count() > 1:
+        n = torch.cuda.device_count()
+        if layer_split != "even":
+            tensor_split = [float(x) for x in layer_split.split(",")][:n]
+            if sum(tensor_split) <= 0:
+                tensor_split = None
+        layer_devices = [torch.device("cuda", (main_gpu + i) % n) for i in range(n)]
     model = build_model(gguf_path=path, device=device, dtype=torch.bfloat16 if on_gpu else torch.float32, world=num_parallel,
-                        rank=tp_id, expert_parallel=bool(expert_parallel))
+                        rank=tp_id, expert_parallel=bool(expert_parallel), layer_devices=layer_devices, tensor_split=tensor_split)
     if check_tensors:
         for L in model.layers:
             for name in L.__slots__:
@@ -105,6 +117,9 @@ def copy_blocks(ch: int, addr: int, n: int) -> int:
     """Device copies of whole cache blocks: ``n`` (src, dst) pairs (copy-on-write and defragmentation)."""
     c = _contexts[ch]
     pairs = torch.from_numpy(_i32(addr, 2 * n).reshape(n, 2).copy())
+    if not isinstance(c.cache, torch.Tensor):
+        c.cache.copy_blocks(pairs[:, 0].numpy(), pairs[:, 1].numpy())
+        return 0
     src = pairs[:, 0].contiguous().to(c.m.device)
     dst = pairs[:, 1].contiguous().to(c.m.device)
     ops.kv_block_copy(c.cache, src, dst, c.block_size)
@@ -137,7 +152,11 @@ def forward(ch: int, addr: int, T: int, B: int, max_blocks: int, n_out: int, max
     if n_out:
         if c.presample > 0:
             k = min(c.presample, logits.shape[1])
-            vals, ids = ops.topk_logits(logits.contiguous(), k)
+            if logits.is_cuda:
+                with torch.cuda.device(logits.device):       # a layer-split model ends on its last GPU
+                    vals, ids = ops.topk_logits(logits.contiguous(), k)
+            else:
+                vals, ids = ops.topk_logits(logits.contiguous(), k)
             v_host = np.ctypeslib.as_array(C.cast(out_addr, C.POINTER(C.c_float)), shape=(n_out, k))
             i_host = np.ctypeslib.as_array(C.cast(idx_addr, C.POINTER(C.c_int64)), shape=(n_out, k))
             torch.from_numpy(v_host).copy_(vals.float().cpu())

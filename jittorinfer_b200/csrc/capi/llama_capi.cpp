@@ -154,10 +154,20 @@ llama_model * llama_model_load_from_file(const char * path_model, llama_model_pa
         if (params.progress_callback && !params.progress_callback(0.0f, params.progress_callback_user_data)) return nullptr;
         std::string perr;
         const bool tp = params.enable_tensor_parallel || params.split_mode == LLAMA_SPLIT_MODE_ROW;
-        if (!jib::PyBridge::call("load_model", &m->py, &perr, "(siiiiiii)", m->path.c_str(), params.n_gpu_layers > 0 ? 1 : 0,
+        // LLAMA_SPLIT_MODE_LAYER in a single process: consecutive layer ranges over the visible GPUs, in the proportions of
+        // tensor_split (up to 8 entries; NULL = even).  Passed as a comma-separated string.
+        std::string split;
+        if (!tp && params.split_mode == LLAMA_SPLIT_MODE_LAYER) {
+            split = "even";
+            if (params.tensor_split != nullptr) {
+                split.clear();
+                for (int i = 0; i < 8; ++i) split += (i ? "," : "") + std::to_string(params.tensor_split[i]);
+            }
+        }
+        if (!jib::PyBridge::call("load_model", &m->py, &perr, "(siiiiiiis)", m->path.c_str(), params.n_gpu_layers > 0 ? 1 : 0,
                                  params.main_gpu, tp ? params.tp_id : 0, tp ? std::max(params.num_parallel, 1) : 1,
                                  params.enable_expert_parallel ? 1 : 0, params.check_tensors ? 1 : 0,
-                                 params.enable_data_parallel ? 1 : 0)) {
+                                 params.enable_data_parallel ? 1 : 0, split.c_str())) {
             log_err("llama_model_load_from_file", perr);
             return nullptr;
         }

@@ -98,3 +98,40 @@ def test_layer_split_matches_oracle():
     prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (50, 9)]
     ref = [OracleModel(hp, w).generate(p, 8) for p in prompts]
     assert eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=8) == ref
+
+
+def test_yarn_rope_nmse_on_the_reference_cases():
+    """The reference's only op-level check with a threshold (tests/ops/test_ops_speed.cpp:1125-1178, NMSE <= 1e-7 at
+    :361): YaRN RoPE with the DeepSeek-V2 decode parameters -- n_dims 64, adjacent pairs, n_ctx_orig 4096, freq_scale
+    1/40, ext_factor 1, attn_factor 1/(1 + 0.1 ln 40) -- on shapes {64,1,16}, {64,16,16}, {64,16,64}, {64,16,128}
+    (head dim, heads, tokens).  Here the table-driven rotation is compared with a scalar float64 restatement of the
+    per-element formula (theta_extrap = pos * base^(-2i/d), ramp mix with the correction range, magnitude scale)."""
+    import math
+    from jittorinfer_b200.ops import reference as ref
+    hp = preset("lite")
+    n_dims, base, n_orig, fs, ext = 64, hp.rope_freq_base, 4096, 0.025, 1.0
+    attn = 1.0 / (1.0 + 0.1 * math.log(40.0))
+    assert abs(attn - 0.730520) < 1e-6
+
+    def corr_dim(n_rot):
+        return n_dims * math.log(n_orig / (n_rot * 2 * math.pi)) / (2 * math.log(base))
+    lo, hi = max(0.0, math.floor(corr_dim(32.0))), min(n_dims - 1.0, math.ceil(corr_dim(1.0)))
+    assert (lo, hi) == tuple(hp.yarn_corr_dims())
+    for heads, tokens in ((1, 16), (16, 16), (16, 64), (16, 128)):
+        g = torch.Generator().manual_seed(heads * 1000 + tokens)
+        x = torch.randn(tokens, heads, n_dims, generator=g, dtype=torch.float64)
+        pos = torch.randint(0, 8192, (tokens,), generator=g)
+        table = ref.yarn_table(8192, n_dims, base, fs, ext, attn, lo, hi)
+        got = ref._rope(x.float(), table[pos]).double()
+        want = torch.empty_like(x)
+        mscale = attn * (1.0 + 0.1 * math.log(1.0 / fs))
+        for t in range(tokens):
+            for i in range(n_dims // 2):
+                te = float(pos[t]) * base ** (-2.0 * i / n_dims)
+                ramp = 1.0 - min(1.0, max(0.0, (i - lo) / max(0.001, hi - lo)))
+                theta = fs * te * (1.0 - ramp * ext) + te * ramp * ext
+                c, s = math.cos(theta) * mscale, math.sin(theta) * mscale
+                x0, x1 = x[t, :, 2 * i], x[t, :, 2 * i + 1]
+                want[t, :, 2 * i], want[t, :, 2 * i + 1] = x0 * c - x1 * s, x0 * s + x1 * c
+        nmse = float(((got - want) ** 2).sum() / (want ** 2).sum())
+        assert nmse <= 1e-7, (heads, tokens, nmse)

@@ -107,3 +107,13 @@ def test_serving_benchmark_poisson(server):
     assert closed["completed"] == 6 and closed["arrivals"].startswith("closed loop")
     m = bench_serving.scrape_metrics(url)
     assert "jittorinfer_kv_blocks_used_ratio" in m and m["jittorinfer_requests_total"] >= 16
+
+
+def test_generate_cli(capsys):
+    from jittorinfer_b200 import generate
+    rc = generate.main(["--random-init", "tiny", "--device", "cpu", "--tokens", "5,6,7,8,9", "-p", "hello", "-n", "5", "--ignore-eos",
+                        "--json"])
+    assert rc == 0
+    out = json.loads(capsys.readouterr().out)
+    assert [len(c["tokens"]) for c in out["completions"]] == [5, 5] and out["timing"]["generated_tokens"] == 10
+    assert generate.main(["--device", "cpu"]) == 2
