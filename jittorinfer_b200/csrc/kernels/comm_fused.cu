@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(128) allreduce_oneshot_kernel(const TIn * __re
 // result buffer (ar.out2); every rank's CTA of that tile returns once the owner has delivered.
 template <typename TIn>
 __global__ void __launch_bounds__(128) allreduce_twoshot_kernel(const TIn * __restrict__ x, const bf16 * __restrict__ residual, int T, int d,
-                                                                JibArCtx ar, int site) {
+                                                                JibArCtx ar, int site, int rs_rows) {
     pdl_launch_dependents();
     pdl_wait();
     const unsigned epoch = *ar.epoch;
@@ -135,10 +135,58 @@ __global__ void __launch_bounds__(128) allreduce_twoshot_kernel(const TIn * __re
             *(__nv_bfloat162 *) &o.x = __floats2bfloat162_rn(acc.x, acc.y);
             *(__nv_bfloat162 *) &o.y = __floats2bfloat162_rn(acc.z, acc.w);
             const size_t oi = (size_t) parity * ohalf + (size_t) (r0 + j) * ar.d_max + f;
-            for (int p = 0; p < ar.world; ++p) *(uint2 *) ((bf16 *) ar.out2[p] + oi) = o;
+            if (rs_rows > 0) {        // reduce-scatter: only the rank that owns this row gets it
+                *(uint2 *) ((bf16 *) ar.out2[min((r0 + j) / rs_rows, ar.world - 1)] + oi) = o;
+            } else {
+                for (int p = 0; p < ar.world; ++p) *(uint2 *) ((bf16 *) ar.out2[p] + oi) = o;
+            }
         }
     }
     jib_ar2_deliver_and_wait(ar, site, tile, owner, epoch, 128, (int) threadIdx.x);
+}
+
+// All-gather of token rows: this rank's R rows (x_loc [R][d] bf16) go to rows [rank*R, rank*R + R) of every rank's gather
+// buffer.  One warp per row.  The last block to finish publishes "my rows have landed" to every rank; with `wait` it
+// then also waits for every source (bounded), so that the buffer is complete when the kernel ends -- without it the
+// consumer (the GEMM's TMA warp) waits per token tile on the same flags.
+__global__ void __launch_bounds__(256) allgather_push_kernel(const bf16 * __restrict__ x_loc, int R, int d, JibArCtx ar, int site, int wait) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const unsigned epoch = *ar.epoch;
+    const int par = (site >> 1) & 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t half = (size_t) ar.max_rows2 * ar.d_max;
+    for (int i = blockIdx.x * 8 + warp; i < R; i += gridDim.x * 8) {
+        const uint4 * src = (const uint4 *) (x_loc + (size_t) i * d);
+        const size_t off = (size_t) par * half + ((size_t) ar.rank * R + i) * ar.d_max;
+        for (int p = 0; p < ar.world; ++p) {
+            uint4 * dst = (uint4 *) ((bf16 *) ar.xg[p] + off);
+            for (int v = lane; v < d / 8; v += 32) dst[v] = src[v];
+        }
+    }
+    __shared__ int s_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(ar.ag_counter, 1) == (int) gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    if (threadIdx.x == 0) *ar.ag_counter = 0;
+    __threadfence_system();
+    if ((int) threadIdx.x < ar.world)
+        jib_st_release_sys(ar.flags3[threadIdx.x] + (size_t) site * ar.world + ar.rank, epoch);
+    if (wait && (int) threadIdx.x < ar.world) {
+        const unsigned * f = ar.flags3[ar.rank] + (size_t) site * ar.world + threadIdx.x;
+        bool got = false;
+        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+            if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
+            __nanosleep(40);
+        }
+        if (!got && ar.status != nullptr && atomicCAS(ar.status, 0, 1 /* wait timeout */) == 0) {
+            ar.status[1] = 90 + (int) threadIdx.x;     // site code: 90 + source rank (all-gather)
+            ar.status[2] = 0;
+            ar.status[3] = site;
+        }
+    }
 }
 
 }  // namespace
@@ -189,17 +237,27 @@ JIB_EXPORT int jib_allreduce_oneshot(const void * x, int x_f32, const void * res
 
 // Two-shot all-reduce of a [T][d] partial (+ residual); the bf16 result lands in ar->out2[rank] at the call site's
 // half (site & 1; n_sites must be even), row stride d_max.
+// rs_rows > 0 turns it into a reduce-scatter by token rows: row i is delivered only to rank i / rs_rows.
 JIB_EXPORT int jib_allreduce_twoshot(const void * x, int x_f32, const void * residual, int T, int d, const JibArCtx * ar, int site,
-                                     void * stream) {
+                                     int rs_rows, void * stream) {
     if (T <= 0) return 0;
     if (d % 4 || d > ar->d_max || T > ar->max_rows2 || ar->recv2[0] == nullptr || (ar->n_sites & 1) || site < 0 || site >= ar->n_sites)
         return JIB_E_ARG;
     dim3 grid((d + 511) / 512, (T + 31) / 32);
     if ((int) (grid.x * grid.y) > ar->max_tiles) return JIB_E_ARG;
     if (x_f32)
-        JIB_LAUNCH((allreduce_twoshot_kernel<float>), grid, 128, 0, (cudaStream_t) stream, (const float *) x, (const bf16 *) residual, T, d, *ar, site);
+        JIB_LAUNCH((allreduce_twoshot_kernel<float>), grid, 128, 0, (cudaStream_t) stream, (const float *) x, (const bf16 *) residual, T, d, *ar, site, rs_rows);
     else
-        JIB_LAUNCH((allreduce_twoshot_kernel<bf16>), grid, 128, 0, (cudaStream_t) stream, (const bf16 *) x, (const bf16 *) residual, T, d, *ar, site);
+        JIB_LAUNCH((allreduce_twoshot_kernel<bf16>), grid, 128, 0, (cudaStream_t) stream, (const bf16 *) x, (const bf16 *) residual, T, d, *ar, site, rs_rows);
+    return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
+}
+
+// All-gather of [R][d] bf16 rows per rank into ar->xg[rank] (half (site >> 1) & 1, row stride d_max).
+JIB_EXPORT int jib_allgather_rows(const void * x_loc, int R, int d, const JibArCtx * ar, int site, int wait, void * stream) {
+    if (R <= 0) return 0;
+    if (d % 8 || d > ar->d_max || R * ar->world > ar->max_rows2 || ar->xg[0] == nullptr || site < 0 || site >= ar->n_sites) return JIB_E_ARG;
+    const int grid = (R + 7) / 8;
+    JIB_LAUNCH((allgather_push_kernel), grid, 256, 0, (cudaStream_t) stream, (const bf16 *) x_loc, R, d, *ar, site, wait);
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 

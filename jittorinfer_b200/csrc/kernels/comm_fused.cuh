@@ -22,6 +22,10 @@ struct JibArCtx {
     void * out2[JIB_AR_MAX_WORLD];        // [2][max_rows2][d_max] bf16 reduced result (identical on every rank)
     unsigned * flags2[JIB_AR_MAX_WORLD];  // [n_sites][max_tiles] "tile reduced and delivered" flags
     int max_rows2;
+    // all-gather of token rows (sequence-parallel prefill): every rank stores its rows into every rank's gather buffer
+    void * xg[JIB_AR_MAX_WORLD];          // [2][max_rows2][d_max] bf16 gathered rows
+    unsigned * flags3[JIB_AR_MAX_WORLD];  // [n_sites][world] "rows of source s have landed" flags
+    int * ag_counter;                     // this rank's block counter of the push kernel (zero between launches)
 };
 
 #ifdef __CUDACC__

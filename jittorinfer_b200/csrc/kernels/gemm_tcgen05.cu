@@ -56,6 +56,11 @@ struct GemmArgs {
     JibArCtx ar;              // peer-memory all-reduce fused into the epilogue (ar_on != 0)
     int ar_on, ar_site;
     int cluster_split;        // 1: the `splits` CTAs of a tile form a thread-block cluster and reduce through DSMEM
+    // all-gather fused into the activation loads: rows of source rank s are complete once ag_flags[s] == *ag_epoch
+    const unsigned * ag_flags;
+    const unsigned * ag_epoch;
+    int ag_rows, ag_world;    // rows per source rank, number of ranks
+    int ar_rs_rows;           // two-shot: > 0 delivers each reduced row only to rank row / ar_rs_rows (reduce-scatter)
     void * const * row_ptr;   // null, or per output row the address of its bf16 row (rows scattered to other buffers,
                               // possibly on other GPUs: the expert-parallel return path)
 };
@@ -208,6 +213,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (elect_one()) {
             const int a_z = batch;
             const int b_z = args.seg != nullptr ? 0 : batch;
+            if (args.ag_flags != nullptr) {
+                // the token rows of this tile were pushed by other ranks: wait (bounded) for the sources that cover
+                // them, then order the peers' generic-proxy stores before this thread's async-proxy (TMA) reads
+                const unsigned want = *args.ag_epoch;
+                const int lo = (int) ((row_base + row0) / args.ag_rows);
+                const int hi = min((int) ((row_base + row0 + BN - 1) / args.ag_rows), args.ag_world - 1);
+                for (int src = lo; src <= hi; ++src) {
+                    bool got = false;
+                    for (unsigned it = 0; it < JIB_AR_SPIN_LIMIT; ++it) {
+                        if (jib_ld_acquire_sys(args.ag_flags + src) == want) { got = true; break; }
+                        __nanosleep(40);
+                    }
+                    if (!got) jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 6, src);
+                }
+                asm volatile("fence.proxy.async;" ::: "memory");
+            }
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % C::STAGES;
                 const uint32_t ph = (i / C::STAGES) & 1;
@@ -423,7 +444,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                    ltid, [&](long long row, int nn, float4 v) {
                                        const uint2 o = pack_bf16x4(v);
                                        const size_t oi = ar_opar + (size_t) row * args.ar.d_max + nn;
-                                       for (int p = 0; p < world; ++p) *(uint2 *) ((__nv_bfloat16 *) args.ar.out2[p] + oi) = o;
+                                       if (args.ar_rs_rows > 0) {       // reduce-scatter: the row's owner only
+                                           const int p = min((int) (row / args.ar_rs_rows), world - 1);
+                                           *(uint2 *) ((__nv_bfloat16 *) args.ar.out2[p] + oi) = o;
+                                       } else {
+                                           for (int p = 0; p < world; ++p) *(uint2 *) ((__nv_bfloat16 *) args.ar.out2[p] + oi) = o;
+                                       }
                                    });
                 }
                 jib_ar2_deliver_and_wait(args.ar, args.ar_site, tile_id, ar_owner, ar_epoch, 128, ltid);
@@ -609,11 +635,16 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     a.ar_on = 0; a.ar_site = 0;
     a.cluster_split = cluster_split ? 1 : 0;
     a.row_ptr = (void * const *) d->out_row_ptr;
+    a.ag_flags = (const unsigned *) d->ag_flags; a.ag_epoch = (const unsigned *) d->ag_epoch;
+    a.ag_rows = d->ag_rows; a.ag_world = d->ag_world; a.ar_rs_rows = d->ar_rs_rows;
+    if (a.ag_flags != nullptr && (a.ag_epoch == nullptr || a.ag_rows <= 0 || a.ag_world <= 0 || grouped || batch != 1)) return JIB_E_ARG;
+    if (a.ar_rs_rows < 0) return JIB_E_ARG;
     if (a.row_ptr != nullptr && (dual || d->out_f32 || d->residual != nullptr || d->ar != nullptr)) return JIB_E_ARG;
     memset(&a.ar, 0, sizeof(a.ar));
     if (d->ar != nullptr) {
         const JibArCtx * ar = (const JibArCtx *) d->ar;
-        const bool two_shot = d->T > ar->max_rows;        // large batches: partials to one owner per tile, result broadcast
+        // large batches, or a reduce-scatter: partials to one owner per tile, result delivered from there
+        const bool two_shot = d->T > ar->max_rows || d->ar_rs_rows > 0;
         if (dual || grouped || batch != 1 || d->N > ar->d_max || n_tiles * t_tiles > ar->max_tiles || d->ar_site < 0 ||
             d->ar_site >= ar->n_sites)
             return JIB_E_ARG;
@@ -750,6 +781,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.ar_on = 0; a.ar_site = 0;
     a.cluster_split = 0;
     a.row_ptr = nullptr;
+    a.ag_flags = nullptr; a.ag_epoch = nullptr; a.ag_rows = 0; a.ag_world = 0; a.ar_rs_rows = 0;
     memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);
     switch (p.bn) {

@@ -48,6 +48,10 @@ typedef struct jib_gemm_desc {
     const void * ar;           // NULL, or a JibArCtx: the epilogue sums the tile over all ranks through peer memory
     const void * out_row_ptr;  // NULL, or device array [rows] of bf16 row addresses (may be peer memory): row i of the result is
                                // stored there instead of out + i * ldo (a NULL entry drops the row)
+    const void * ag_flags;     // NULL, or device unsigned[ag_world]: rows [s*ag_rows, (s+1)*ag_rows) of x are valid once
+    const void * ag_epoch;     //   ag_flags[s] == *ag_epoch (all-gather fused into the activation loads)
+    int ag_rows, ag_world;
+    int ar_rs_rows;            // with ar: > 0 = reduce-scatter by token rows (row i delivered to rank i / ar_rs_rows only)
 } jib_gemm_desc;
 
 JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);

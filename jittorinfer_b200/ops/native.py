@@ -26,7 +26,9 @@ class GemmDesc(C.Structure):
                                             "out_batch_stride", "ldr", "res_batch_stride", "x_rows_total")] + \
                [("scratch_bytes", C.c_size_t)] + \
                [(n, C.c_int) for n in ("n_counters", "T", "N", "K", "batch", "max_rows", "active_hint", "out_f32", "res_f32",
-                                       "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p), ("out_row_ptr", C.c_void_p)]
+                                       "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p), ("out_row_ptr", C.c_void_p), ("ag_flags", C.c_void_p),
+                                                                             ("ag_epoch", C.c_void_p), ("ag_rows", C.c_int),
+                                                                             ("ag_world", C.c_int), ("ar_rs_rows", C.c_int)]
 
 
 def load():
@@ -139,7 +141,7 @@ def _p(t: Optional[torch.Tensor]) -> Optional[int]:
 # ---- GEMM family ---------------------------------------------------------------------------------
 def gemm(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, *, out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, splits: int = 0, bn: int = 0,
-         ar=None, ar_site: int = 0) -> torch.Tensor:
+         ar=None, ar_site: int = 0, ar_rs_rows: int = 0, ag=None) -> torch.Tensor:
     """out[T,N] = x[T,K] @ w[N,K]^T  (w2: silu(x w^T) * (x w2^T)) (+ residual)."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(-1) == 1 and w.is_contiguous()
     T, K = x.shape
@@ -159,8 +161,10 @@ def gemm(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, *,
     d.out_f32 = int(out.dtype == torch.float32)
     d.res_f32 = int(residual is not None and residual.dtype == torch.float32)
     d.splits, d.bn, d.sm_count = splits, bn, ws.sm_count
-    if ar is not None:          # fused one-shot all-reduce over peer memory in the epilogue
-        d.ar, d.ar_site = C.addressof(ar), ar_site
+    if ar is not None:          # fused all-reduce (or, with ar_rs_rows, reduce-scatter by rows) over peer memory in the epilogue
+        d.ar, d.ar_site, d.ar_rs_rows = C.addressof(ar), ar_site, ar_rs_rows
+    if ag is not None:          # x is a gather buffer other ranks are still filling: (flags ptr, epoch ptr, rows per rank, world)
+        d.ag_flags, d.ag_epoch, d.ag_rows, d.ag_world = ag
     _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm")
     return out
 

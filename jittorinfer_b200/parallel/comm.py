@@ -108,7 +108,7 @@ class ArCtx(C.Structure):
     _fields_ = [("recv", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("status", C.c_void_p),
                 ("world", C.c_int), ("rank", C.c_int), ("n_sites", C.c_int), ("max_rows", C.c_int), ("d_max", C.c_int),
                 ("max_tiles", C.c_int), ("recv2", C.c_void_p * 8), ("out2", C.c_void_p * 8), ("flags2", C.c_void_p * 8),
-                ("max_rows2", C.c_int)]
+                ("max_rows2", C.c_int), ("xg", C.c_void_p * 8), ("flags3", C.c_void_p * 8), ("ag_counter", C.c_void_p)]
 
 
 class FusedCommunicator(Communicator):
@@ -133,7 +133,8 @@ class FusedCommunicator(Communicator):
         for name, args in (("jib_symm_alloc", [C.c_size_t, C.POINTER(vp), vp]), ("jib_symm_open", [vp, C.POINTER(vp)]),
                            ("jib_symm_close", [vp]), ("jib_symm_free", [vp]), ("jib_ar_epoch_bump", [vp, vp]),
                            ("jib_allreduce_oneshot", [vp, C.c_int, vp, vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, vp]),
-                           ("jib_allreduce_twoshot", [vp, C.c_int, vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, vp])):
+                           ("jib_allreduce_twoshot", [vp, C.c_int, vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, C.c_int, vp]),
+                           ("jib_allgather_rows", [vp, C.c_int, C.c_int, C.POINTER(ArCtx), C.c_int, C.c_int, vp])):
             fn = getattr(self.L, name)
             fn.restype, fn.argtypes = C.c_int, args
         self._own, self._peers = [], []
@@ -154,8 +155,13 @@ class FusedCommunicator(Communicator):
             recv2 = self._exchange(2 * world * max_rows_large * d_max * 4)
             out2 = self._exchange(2 * max_rows_large * d_max * 2)
             flags2 = self._exchange(n_sites * self.MAX_TILES * 4)
+            xg = self._exchange(2 * max_rows_large * d_max * 2)
+            flags3 = self._exchange(n_sites * world * 4)
             for i in range(world):
                 self.ctx.recv2[i], self.ctx.out2[i], self.ctx.flags2[i] = recv2[i], out2[i], flags2[i]
+                self.ctx.xg[i], self.ctx.flags3[i] = xg[i], flags3[i]
+            self._ag_counter = torch.zeros(1, dtype=torch.int32, device=device)
+            self.ctx.ag_counter = self._ag_counter.data_ptr()
         self.site = 0
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
@@ -216,7 +222,7 @@ class FusedCommunicator(Communicator):
             self.n_collectives += 1
             self.n_two_shot += 1
             rc = self.L.jib_allreduce_twoshot(x.data_ptr(), int(x.dtype == torch.float32),
-                                              None if residual is None else residual.data_ptr(), T, d, C.byref(self.ctx), site,
+                                              None if residual is None else residual.data_ptr(), T, d, C.byref(self.ctx), site, 0,
                                               torch.cuda.current_stream().cuda_stream)
             self.native._ck(rc, "allreduce_twoshot")
             return self._result_view(site, T)
@@ -245,6 +251,66 @@ class FusedCommunicator(Communicator):
 
     n_two_shot = 0
 
+    # ---- sequence-parallel prefill with in-kernel collectives (see Communicator for the contract) -----------------
+    def _sp_fits(self, rows_total: int, d: int) -> bool:
+        return 0 < rows_total <= self.max_rows_large and d == self.d_max and rows_total % self.world == 0
+
+    def _gather_view(self, site: int, rows: int, d: int) -> torch.Tensor:
+        base = self.ctx.xg[self.rank] + ((site >> 1) & 1) * self.max_rows_large * self.d_max * 2
+        return self.native.tensor_from_ptr(base, (rows, self.d_max), torch.bfloat16, self.device)[:, :d]
+
+    def _push_rows(self, x_loc: torch.Tensor, site: int, wait: bool) -> None:
+        R, d = x_loc.shape
+        rc = self.L.jib_allgather_rows(x_loc.contiguous().data_ptr(), R, d, C.byref(self.ctx), site, int(wait),
+                                       torch.cuda.current_stream().cuda_stream)
+        self.native._ck(rc, "allgather_rows")
+
+    def all_gather_rows(self, x_loc: torch.Tensor) -> torch.Tensor:
+        R, d = x_loc.shape
+        site = self._next_site()
+        if not self._sp_fits(R * self.world, d) or x_loc.dtype != torch.bfloat16:
+            return Communicator.all_gather_rows(self, x_loc)
+        self.n_collectives += 1
+        self._push_rows(x_loc, site, wait=True)          # complete when the kernel ends: any consumer may follow
+        return self._gather_view(site, R * self.world, d)
+
+    def allgather_linear(self, x_loc: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None) -> torch.Tensor:
+        R, d = x_loc.shape
+        site = self._next_site()
+        if not self._sp_fits(R * self.world, d) or x_loc.dtype != torch.bfloat16:
+            return Communicator.allgather_linear(self, x_loc, w, w2)
+        self.n_collectives += 1
+        # rows are pushed without waiting; the GEMM's TMA warp waits, per token tile, for the source ranks that cover it
+        self._push_rows(x_loc, site, wait=False)
+        x = self._gather_view(site, R * self.world, d)
+        flags = self.ctx.flags3[self.rank] + site * self.world * 4
+        return self.native.gemm(x, w, w2, ag=(flags, self.epoch.data_ptr(), R, self.world))
+
+    def reduce_scatter_rows(self, part: torch.Tensor, residual_loc: Optional[torch.Tensor]) -> torch.Tensor:
+        T, d = part.shape
+        site = self._next_site()
+        if not self._sp_fits(T, d):
+            return Communicator.reduce_scatter_rows(self, part, residual_loc)
+        self.n_collectives += 1
+        R = T // self.world
+        rc = self.L.jib_allreduce_twoshot(part.data_ptr(), int(part.dtype == torch.float32), None, T, d, C.byref(self.ctx), site, R,
+                                          torch.cuda.current_stream().cuda_stream)
+        self.native._ck(rc, "reduce_scatter_rows")
+        mine = self._result_view(site, T)[self.rank * R:(self.rank + 1) * R]
+        return mine + residual_loc if residual_loc is not None else mine.clone()
+
+    def linear_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual_loc: Optional[torch.Tensor]) -> torch.Tensor:
+        T = x.shape[0]
+        site = self._next_site()
+        if not self._sp_fits(T, w.shape[0]):
+            return Communicator.linear_reduce_scatter(self, x, w, residual_loc)
+        self.n_collectives += 1
+        R = T // self.world
+        out = self._result_view(site, T)
+        self.native.gemm(x, w, out=out, ar=self.ctx, ar_site=site, ar_rs_rows=R)     # epilogue: partials to tile owners,
+        mine = out[self.rank * R:(self.rank + 1) * R]                                # reduced rows to their row owners
+        return mine + residual_loc if residual_loc is not None else mine.clone()
+
     def _result_view(self, site: int, T: int) -> torch.Tensor:
         """This rank's copy of the two-shot result of call site ``site``: rows [0, T) of that site's half of the result
         buffer.  Valid until the call site after the next one writes the same half."""
@@ -257,4 +323,5 @@ def make_communicator(device: torch.device, world: int, rank: int, d_model: int,
     if device.type != "cuda" or impl == "nccl":
         return Communicator(world, rank, group)
     large = int(os.environ.get("JITTORINFER_AR_LARGE_ROWS", "2048"))
-    return FusedCommunicator(device, world, rank, d_model, 2 * n_layer, group=group, max_rows_large=large)
+    # call sites per forward pass: 2 per layer (all-reduce form) or 4 per layer + 1 (sequence-parallel form)
+    return FusedCommunicator(device, world, rank, d_model, 4 * n_layer + 2, group=group, max_rows_large=large)

@@ -153,3 +153,23 @@ def test_tp_ep_two_gpus_large_prefill_two_shot():
         assert out[0] == r[0]                        # the first sampled token comes straight from the prefill pass
     agree = sum(a == b for out, r in zip(res[0][1], lib[0][1]) for a, b in zip(out, r))
     assert agree >= 12                               # same kernels, different transport: late splits only
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(os.environ.get("JITTORINFER_TEST_SP_FUSED", "") != "1",
+                    reason="the in-kernel sequence-parallel collectives have been cross-compiled but not yet run on GPUs; "
+                           "set JITTORINFER_TEST_SP_FUSED=1 to try them")
+def test_sequence_parallel_prefill_fused_two_gpus():
+    """Sequence-parallel prefill with the in-kernel collectives: rows pushed into every rank's gather buffer with the
+    GEMM's TMA warp waiting per token tile, two-shot reduce-scatter to the row owners."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    lens = (300, 100)
+    res = _run(2, "nccl", True, comm_impl="fused", graphs=True, prompt_lens=lens, n_batch=512, sp_min_tokens=64)
+    lib = _run(2, "nccl", True, comm_impl="nccl", graphs=False, prompt_lens=lens, n_batch=512, sp_min_tokens=64)
+    ref = _oracle("tiny-v2", True, lens)
+    assert res[0][1] == res[1][1]
+    for out, r in zip(res[0][1], ref):
+        assert out[0] == r[0]
+    agree = sum(a == b for out, r in zip(res[0][1], lib[0][1]) for a, b in zip(out, r))
+    assert agree >= 12
