@@ -29,7 +29,7 @@ from ..utils import trace as _trace
 from ..models.deepseek2 import DeepSeek2Model, ForwardBatch
 from ..models.hparams import DeepSeek2HParams
 from .native_rt import PagedKV, Scheduler, StepArrays, i32p
-from .sampling import HostSampler, SamplingParams
+from .sampling import HostSampler, SamplingParams, make_sampler
 
 
 @dataclass
@@ -52,7 +52,7 @@ class EngineConfig:
 class RequestState:
     req_id: int
     params: SamplingParams
-    sampler: Optional[HostSampler]
+    sampler: Optional[object]          # NativeSampler or HostSampler
     n_prompt: int
     output: List[int] = field(default_factory=list)
     finish_reason: Optional[str] = None
@@ -177,7 +177,8 @@ class LLMEngine:
         params = params or SamplingParams()
         rid = self._next_id
         self._next_id += 1
-        st = RequestState(rid, params, None if params.greedy else HostSampler(params), len(prompt), t_submit=time.time())
+        smpl = None if params.greedy and params.dry_multiplier <= 0 else make_sampler(params, self.hp.n_vocab, self.hp.n_ctx_train)
+        st = RequestState(rid, params, smpl, len(prompt), t_submit=time.time())
         if st.sampler is not None:
             for t in prompt[-params.repeat_last_n:]:
                 st.sampler.accept(t)

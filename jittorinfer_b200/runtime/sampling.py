@@ -32,6 +32,13 @@ class SamplingParams:
     presence_penalty: float = 0.0
     repeat_last_n: int = 64
     logit_bias: Dict[int, float] = field(default_factory=dict)
+    dynatemp_range: float = 0.0       # > 0: temperature +- range scaled by the normalised entropy ** dynatemp_exponent
+    dynatemp_exponent: float = 1.0
+    dry_multiplier: float = 0.0       # > 0 enables the "don't repeat yourself" penalty
+    dry_base: float = 1.75
+    dry_allowed_length: int = 2
+    dry_penalty_last_n: int = -1
+    min_keep: int = 0
     seed: Optional[int] = None
     max_tokens: int = -1
     ignore_eos: bool = False
@@ -108,3 +115,69 @@ class HostSampler:
                 logit, ids = logit[above[-1]:], ids[above[-1]:]
         pr = softmax(logit / p.temperature)
         return int(ids[int(self.rng.choice(len(ids), p=pr))])
+
+
+class NativeSampler:
+    """The same per-request sampler over the C++ chain of ``libllama.so`` (``csrc/capi/samplers.cpp``), built in the
+    reference's order: penalties, dry, top_k, typical_p, top_p, min_p, xtc, temperature (entropy-scaled when
+    ``dynatemp_range`` > 0), then logit_bias and dist (common/sampling_local.cpp:128-210).  Candidates are the device's
+    top-k, as with the reference's presample path."""
+
+    def __init__(self, params: SamplingParams, n_vocab: int = 0, n_ctx_train: int = 4096):
+        import ctypes as C
+        from .. import capi
+        self.C, self.capi = C, capi
+        L = self.L = capi.load()
+        p = self.p = params
+        seed = p.seed if p.seed is not None else 0xFFFFFFFF
+        ch = self.chain = L.llama_sampler_chain_init(capi.SamplerChainParams(True))
+        add = lambda smpl: L.llama_sampler_chain_add(ch, smpl)
+        add(L.llama_sampler_init_penalties(p.repeat_last_n, p.repeat_penalty, p.frequency_penalty, p.presence_penalty))
+        if p.dry_multiplier > 0:
+            add(L.llama_sampler_init_dry(None, n_ctx_train, p.dry_multiplier, p.dry_base, p.dry_allowed_length, p.dry_penalty_last_n,
+                                         None, 0))
+        if p.temperature > 0:
+            add(L.llama_sampler_init_top_k(p.top_k))
+            add(L.llama_sampler_init_typical(p.typical_p, p.min_keep))
+            add(L.llama_sampler_init_top_p(p.top_p, p.min_keep))
+            add(L.llama_sampler_init_min_p(p.min_p, p.min_keep))
+            add(L.llama_sampler_init_xtc(p.xtc_probability, p.xtc_threshold, p.min_keep, seed & 0xFFFFFFFF))
+            add(L.llama_sampler_init_temp_ext(p.temperature, p.dynatemp_range, p.dynatemp_exponent))
+        if p.logit_bias:
+            arr = (capi.LogitBias * len(p.logit_bias))(*[(int(t), float(b)) for t, b in p.logit_bias.items()])
+            add(L.llama_sampler_init_logit_bias(n_vocab, len(p.logit_bias), arr))
+        add(L.llama_sampler_init_dist(seed & 0xFFFFFFFF) if p.temperature > 0 else L.llama_sampler_init_greedy())
+        self._buf = None
+
+    def __del__(self):
+        try:
+            if self.chain:
+                self.L.llama_sampler_free(self.chain)
+                self.chain = None
+        except Exception:
+            pass
+
+    def accept(self, token: int):
+        self.L.llama_sampler_accept(self.chain, int(token))
+
+    def sample(self, values: np.ndarray, ids: np.ndarray) -> int:
+        n = len(ids)
+        if self._buf is None or len(self._buf) < n:
+            self._buf = (self.capi.TokenData * n)()
+        buf = self._buf
+        for i in range(n):
+            buf[i].id, buf[i].logit, buf[i].p = int(ids[i]), float(values[i]), 0.0
+        arr = self.capi.TokenDataArray(self.C.cast(buf, self.C.POINTER(self.capi.TokenData)), n, -1, False)
+        self.L.llama_sampler_apply(self.chain, self.C.byref(arr))
+        return int(arr.data[arr.selected].id)
+
+
+def make_sampler(params: SamplingParams, n_vocab: int = 0, n_ctx_train: int = 4096):
+    """The native chain unless it cannot be loaded or ``JITTORINFER_SAMPLER=python`` asks for the numpy one."""
+    import os
+    if os.environ.get("JITTORINFER_SAMPLER", "native").lower() != "python":
+        try:
+            return NativeSampler(params, n_vocab, n_ctx_train)
+        except Exception:      # library not built / not loadable: the numpy chain has the same semantics minus dry and dynatemp
+            pass
+    return HostSampler(params)

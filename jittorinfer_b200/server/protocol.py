@@ -105,6 +105,10 @@ def sampling_from_body(body: Dict[str, Any], default_max: int) -> SamplingParams
         xtc_probability=num("xtc_probability", 0.0, 0.0, 1.0), xtc_threshold=num("xtc_threshold", 0.1, 0.0, 1.0),
         repeat_penalty=num("repeat_penalty", 1.0, 0.0), frequency_penalty=num("frequency_penalty", 0.0),
         presence_penalty=num("presence_penalty", 0.0), repeat_last_n=int(num("repeat_last_n", 64, -1, cast=int)),
+        dynatemp_range=num("dynatemp_range", 0.0, 0.0), dynatemp_exponent=num("dynatemp_exponent", 1.0, 0.0),
+        dry_multiplier=num("dry_multiplier", 0.0, 0.0), dry_base=num("dry_base", 1.75, 1.0),
+        dry_allowed_length=int(num("dry_allowed_length", 2, 1, cast=int)), dry_penalty_last_n=int(num("dry_penalty_last_n", -1, -1, cast=int)),
+        min_keep=int(num("min_keep", 0, 0, cast=int)),
         logit_bias=bias, seed=None if seed in (None, -1) else int(seed),
         max_tokens=-1 if max_tokens is None else int(max_tokens), ignore_eos=bool(body.get("ignore_eos", False)),
         stop=[str(s) for s in stop])

@@ -438,3 +438,39 @@ def test_c_program_embeds_the_engine(L, gguf_path, tmp_path):
     r = subprocess.run([exe, gguf_path] + [str(t) for t in prompt], capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     assert [int(x) for x in r.stdout.split()] == _oracle_tokens(prompt, 8)
+
+
+def test_engine_uses_the_native_sampler_chain():
+    """The engine's per-request sampler is the C++ chain: seeded runs repeat, dry and dynatemp are honoured, and with a
+    sharp distribution it agrees with the numpy chain."""
+    import numpy as np
+    from jittorinfer_b200.runtime.sampling import HostSampler, NativeSampler, SamplingParams, make_sampler
+    sp = SamplingParams(temperature=0.8, top_k=5, top_p=0.9, min_p=0.0, seed=7)
+    vals = np.array([4.0, 3.5, 1.0, 0.5, -2.0, -5.0], dtype=np.float32)
+    ids = np.array([10, 11, 12, 13, 14, 15], dtype=np.int32)
+    a, b = make_sampler(sp, 100), make_sampler(sp, 100)
+    assert isinstance(a, NativeSampler)
+    seq_a = [a.sample(vals, ids) for _ in range(40)]
+    assert seq_a == [b.sample(vals, ids) for _ in range(40)] and set(seq_a) <= {10, 11} | {12} and len(set(seq_a)) > 1
+    sharp = SamplingParams(temperature=0.01, top_k=0, top_p=1.0, min_p=0.0, seed=1)
+    assert NativeSampler(sharp, 100).sample(vals, ids) == HostSampler(sharp).sample(vals, ids) == 10
+    # penalties through accept(): token 10 was just produced twice, a strong repeat penalty moves the choice to 11
+    pen = NativeSampler(SamplingParams(temperature=0.0, repeat_penalty=4.0, repeat_last_n=8), 100)
+    pen.accept(10)
+    pen.accept(10)
+    assert pen.sample(vals, ids) == 11
+    # dry: history 20 21 22 20 21 -> 22 would repeat the sequence; the penalty hands the arg-max to another token
+    dry = NativeSampler(SamplingParams(temperature=0.0, dry_multiplier=5.0, dry_allowed_length=2), 100)
+    for t in (20, 21, 22, 20, 21):
+        dry.accept(t)
+    v2 = np.array([3.0, 2.9], dtype=np.float32)
+    assert dry.sample(v2, np.array([22, 23], dtype=np.int32)) == 23
+    # engine end to end with a sampled request
+    hp = preset("tiny")
+    from jittorinfer_b200.models.deepseek2 import DeepSeek2Model
+    from jittorinfer_b200.runtime.engine import EngineConfig, LLMEngine
+    outs = []
+    for _ in range(2):
+        eng = LLMEngine(DeepSeek2Model(hp, random_weights(hp, seed=0).items(), dtype=torch.float32), EngineConfig(n_ctx=512, n_batch=32, n_parallel=2))
+        outs.append(eng.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.9, seed=3, ignore_eos=True, dynatemp_range=0.3), max_new_tokens=8))
+    assert outs[0] == outs[1] and len(outs[0][0]) == 8
