@@ -283,6 +283,8 @@ class ServerContext:
                 eng.reset()
                 continue
             self.metrics.observe_step(time.time() - t0)
+            if getattr(self.cfg, "display_chat", False):
+                self._display_chat()
             for rid, tok, fin in events:
                 st = self.streams.get(rid)
                 if st is None or st.done:
@@ -295,6 +297,21 @@ class ServerContext:
                     self._finish(st, "stop" if fin == "stop" else ("cancelled" if fin == "cancelled" else "length"))
                 if fin is not None:
                     eng.requests.pop(rid, None)
+
+    def _display_chat(self, every: float = 0.25):
+        """Console view of what every active request has generated so far, redrawn a few times per second
+        (the reference's display_chat: examples/server/server.cpp:1509-1520)."""
+        now = time.time()
+        if now - getattr(self, "_last_display", 0.0) < every:
+            return
+        self._last_display = now
+        import sys
+        lines = ["\x1b[2J\x1b[H" if sys.stderr.isatty() else "---- active requests ----"]
+        for rid, st in sorted(self.streams.items()):
+            tail = st.text[-200:].replace("\n", " ")
+            lines.append(f"[req {rid}] prompt {st.n_prompt} tok, generated {st.n_gen}: {tail}")
+        sys.stderr.write("\n".join(lines) + "\n")
+        sys.stderr.flush()
 
     def _emit(self, st: _Stream, text: str):
         if text:
