@@ -596,12 +596,17 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
             if (splits < 1) splits = 1;
         }
     }
-    const bool want_cluster = d->splits <= 0 || d->splits <= 8;      // automatic choice, or an explicit count a cluster can hold
-    if (d->splits <= 0 && splits > 8) splits = 8;                      // a portable cluster holds at most 8 CTAs
+    // Two ways to add the splits up: inside a thread-block cluster through distributed shared memory (at most 8 CTAs,
+    // cheap reduction) or through a global scratch with a last-arriver reduction (any count).  Measured per decode GEMM
+    // on B200: with few tiles (qkv_a 17-29, q_b 24, shared / dense down 16) the cluster wins by 0.5-2.7 us; with 40
+    // tiles x 7 splits (o_proj at TP8) the scratch path is 4.4 us faster.  An explicit split count of up to 8 always
+    // takes the cluster (tests exercise both).
+    const bool cluster_ok = !jib_no_cluster() && (d->splits > 0 ? d->splits <= 8 : base_ctas <= 32);
+    if (d->splits <= 0 && cluster_ok && splits > 8) splits = 8;     // a portable cluster holds at most 8 CTAs
     if (splits > num_kb) splits = num_kb;
     int kbps = (num_kb + splits - 1) / splits;
     splits = (num_kb + kbps - 1) / kbps;                        // no empty split
-    const bool cluster_split = want_cluster && splits > 1 && splits <= 8 && !jib_no_cluster();
+    const bool cluster_split = cluster_ok && splits > 1 && splits <= 8;
     const long long tiles_total = (long long) n_tiles * t_tiles * batch;
     if (splits > 1 && !cluster_split) {
         const size_t need = (size_t) tiles_total * splits * (dual ? 2 : 1) * bn * BM * sizeof(float);
