@@ -600,8 +600,9 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     // cheap reduction) or through a global scratch with a last-arriver reduction (any count).  Measured per decode GEMM
     // on B200: with few tiles (qkv_a 17-29, q_b 24, shared / dense down 16) the cluster wins by 0.5-2.7 us; with 40
     // tiles x 7 splits (o_proj at TP8) the scratch path is 4.4 us faster.  An explicit split count of up to 8 always
-    // takes the cluster (tests exercise both).
-    const bool cluster_ok = !jib_no_cluster() && (d->splits > 0 ? d->splits <= 8 : base_ctas <= 32);
+    // takes the cluster (tests exercise both).  Launches with up to 4 splits keep the cluster as well (that is the
+    // configuration the single-GPU numbers were measured with).
+    const bool cluster_ok = !jib_no_cluster() && (d->splits > 0 ? d->splits <= 8 : (base_ctas <= 32 || splits <= 4));
     if (d->splits <= 0 && cluster_ok && splits > 8) splits = 8;     // a portable cluster holds at most 8 CTAs
     if (splits > num_kb) splits = num_kb;
     int kbps = (num_kb + splits - 1) / splits;
