@@ -32,6 +32,7 @@ class DeepSeek2HParams:
     expert_weights_scale: float = 1.0
     expert_weights_norm: bool = False
     expert_gating_func: str = "softmax"   # or "sigmoid"
+    router_bias: bool = False             # per-expert selection bias (blk.N.exp_probs_b.bias; DeepSeek-V3-shaped checkpoints)
     n_group: int = 1                  # group-limited routing (DeepSeek-V2: 8)
     topk_group: int = 1               # groups kept per token (DeepSeek-V2: 3)
     q_lora_rank: int = 0              # 0 => dense q projection ("Lite")
@@ -206,6 +207,8 @@ class DeepSeek2HParams:
         hp.n_vocab = int(nv)
         hp.bos_id = int(kv.get("tokenizer.ggml.bos_token_id", 11))
         hp.eos_id = int(kv.get("tokenizer.ggml.eos_token_id", 11))
+        if tensor_names is not None:
+            hp.router_bias = any(str(n).endswith("exp_probs_b.bias") for n in tensor_names)
         return hp
 
 
@@ -232,4 +235,21 @@ def preset(name: str) -> DeepSeek2HParams:
         return DeepSeek2HParams(
             n_embd=5120, n_layer=60, n_head=128, n_ff=12288, n_ff_exp=1536, n_expert=160, n_expert_used=6,
             n_expert_shared=2, expert_weights_scale=16.0, n_group=8, topk_group=3, q_lora_rank=1536)
+    if name in ("tiny-v3",):
+        # the DeepSeek-V3-shaped code paths at toy size: sigmoid gating with a selection bias, renormalised weights,
+        # group-limited routing, two leading dense layers, q-LoRA
+        return DeepSeek2HParams(
+            n_vocab=1024, n_embd=256, n_layer=4, n_head=4, n_layer_dense_lead=2, n_ff=512, n_ff_exp=128,
+            n_expert=16, n_expert_used=4, n_expert_shared=1, q_lora_rank=96, kv_lora_rank=64,
+            qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_ctx_train=4096,
+            n_group=4, topk_group=2, expert_weights_scale=2.5, expert_weights_norm=True, expert_gating_func="sigmoid",
+            router_bias=True, bos_id=0, eos_id=1)
+    if name in ("v3", "deepseek-v3"):
+        # DeepSeek-V3 / R1 shape (671B): the reference recognises it by layer count (src/llama-model.cpp:1203-1215).
+        # 1.3 TB of bf16 weights: shape only, for sizing and for checkpoints sharded over more memory than one node has.
+        return DeepSeek2HParams(
+            n_vocab=129280, n_embd=7168, n_layer=61, n_head=128, n_layer_dense_lead=3, n_ff=18432, n_ff_exp=2048,
+            n_expert=256, n_expert_used=8, n_expert_shared=1, expert_weights_scale=2.5, expert_weights_norm=True,
+            expert_gating_func="sigmoid", router_bias=True, n_group=8, topk_group=4, q_lora_rank=1536,
+            n_ctx_train=163840, rope_orig_ctx=4096)
     raise KeyError(name)

@@ -61,6 +61,8 @@ def tensor_table(hp: DeepSeek2HParams) -> Dict[str, Tuple[int, ...]]:
             t[p + "ffn_down.weight"] = (d, hp.n_ff)
         else:
             t[p + "ffn_gate_inp.weight"] = (hp.n_expert, d)
+            if hp.router_bias:
+                t[p + "exp_probs_b.bias"] = (hp.n_expert,)
             t[p + "ffn_gate_exps.weight"] = (hp.n_expert, hp.n_ff_exp, d)
             t[p + "ffn_up_exps.weight"] = (hp.n_expert, hp.n_ff_exp, d)
             t[p + "ffn_down_exps.weight"] = (hp.n_expert, d, hp.n_ff_exp)

@@ -135,3 +135,25 @@ def test_yarn_rope_nmse_on_the_reference_cases():
                 want[t, :, 2 * i], want[t, :, 2 * i + 1] = x0 * c - x1 * s, x0 * s + x1 * c
         nmse = float(((got - want) ** 2).sum() / (want ** 2).sum())
         assert nmse <= 1e-7, (heads, tokens, nmse)
+
+
+def test_v3_shaped_paths_match_oracle(tmp_path):
+    """Sigmoid gating with a selection bias, renormalised weights, group-limited routing and two leading dense layers
+    (the DeepSeek-V3-shaped branch of the architecture): module graph and engine against the oracle, also through a GGUF
+    round trip (the bias tensors switch the branch on)."""
+    from jittorinfer_b200.models.weights import write_random_gguf
+    from jittorinfer_b200.runtime.factory import build_engine
+    hp = preset("tiny-v3")
+    assert hp.router_bias and preset("v3").n_expert == 256
+    w = random_weights(hp, seed=0, std=0.05)
+    assert "blk.2.exp_probs_b.bias" in w and "blk.1.exp_probs_b.bias" not in w
+    o = OracleModel(hp, w)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    cache = torch.zeros(hp.n_layer, 4 * 64, hp.kv_row)
+    toks = torch.randint(0, hp.n_vocab, (40,), generator=torch.Generator().manual_seed(7)).tolist()
+    assert (m.forward(_batch(toks, 0), cache) - o.forward(torch.tensor(toks))).abs().max() < 1e-4
+    p = str(tmp_path / "v3.gguf")
+    write_random_gguf(p, hp, seed=0, std=0.05)
+    eng = build_engine(None, gguf_path=p, device="cpu", dtype=torch.float32, n_parallel=2, n_ctx_slot=256, n_batch=32)
+    assert eng.hp.router_bias and eng.hp.expert_gating_func == "sigmoid" and eng.hp.n_layer_dense_lead == 2
+    assert eng.generate([toks], SamplingParams(ignore_eos=True), max_new_tokens=8) == [OracleModel(hp, w).generate(toks, 8)]
