@@ -22,3 +22,55 @@ def test_every_entry_point_is_exported():
                  "jib_kv_block_copy", "jib_gather_rows", "jib_allreduce_oneshot", "jib_allreduce_twoshot", "jib_ar_epoch_bump",
                  "jib_ep_plan", "jib_ep_push", "jib_ep_combine", "jib_symm_alloc", "jib_symm_open"):
         assert hasattr(L, name), name
+
+
+ABI_PROBE = r"""
+#include <cstdio>
+#include <cstddef>
+#include <cuda_bf16.h>
+#include "comm_fused.cuh"
+#include "ep_alltoall.h"
+#include "jib_kernels.h"
+#define F(T, f) printf(#T "." #f " %zu\n", offsetof(T, f))
+int main() {
+    printf("JibArCtx %zu\n", sizeof(JibArCtx));
+    F(JibArCtx, flags); F(JibArCtx, epoch); F(JibArCtx, world); F(JibArCtx, max_tiles); F(JibArCtx, recv2); F(JibArCtx, out2);
+    F(JibArCtx, flags2); F(JibArCtx, max_rows2); F(JibArCtx, xg); F(JibArCtx, flags3); F(JibArCtx, ag_counter);
+    printf("JibEpCtx %zu\n", sizeof(JibEpCtx));
+    F(JibEpCtx, meta); F(JibEpCtx, counts); F(JibEpCtx, yret); F(JibEpCtx, flags); F(JibEpCtx, epoch); F(JibEpCtx, status);
+    F(JibEpCtx, world); F(JibEpCtx, E_local); F(JibEpCtx, max_pairs);
+    printf("jib_gemm_desc %zu\n", sizeof(jib_gemm_desc));
+    F(jib_gemm_desc, seg); F(jib_gemm_desc, x_row_stride); F(jib_gemm_desc, x_rows_total); F(jib_gemm_desc, scratch_bytes);
+    F(jib_gemm_desc, n_counters); F(jib_gemm_desc, T); F(jib_gemm_desc, splits); F(jib_gemm_desc, ar_site); F(jib_gemm_desc, ar);
+    F(jib_gemm_desc, out_row_ptr); F(jib_gemm_desc, ag_flags); F(jib_gemm_desc, ag_epoch); F(jib_gemm_desc, ag_rows);
+    F(jib_gemm_desc, ag_world); F(jib_gemm_desc, ar_rs_rows);
+    return 0;
+}
+"""
+
+
+def test_ctypes_structs_match_the_c_layouts(tmp_path):
+    """The structs passed by pointer or by value into the CUDA library are declared twice (C header, ctypes): a host
+    program prints the C sizes and offsets and they must equal the ctypes ones."""
+    import os
+    import subprocess
+    from jittorinfer_b200.ops.native import GemmDesc
+    from jittorinfer_b200.parallel.comm import ArCtx
+    from jittorinfer_b200.parallel.ep import EpCtx
+    src = tmp_path / "abi.cu"
+    src.write_text(ABI_PROBE)
+    exe = str(tmp_path / "abi")
+    subprocess.run([build.nvcc_path(), "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(build.CSRC, "kernels"),
+                    str(src), "-o", exe], check=True, capture_output=True)
+    lines = subprocess.run([exe], check=True, capture_output=True, text=True).stdout.split("\n")
+    py = {"JibArCtx": ArCtx, "JibEpCtx": EpCtx, "jib_gemm_desc": GemmDesc}
+    checked = 0
+    for line in filter(None, lines):
+        name, val = line.split()
+        if "." in name:
+            t, f = name.split(".")
+            assert getattr(py[t], f).offset == int(val), name
+        else:
+            assert C.sizeof(py[name]) == int(val), name
+        checked += 1
+    assert checked >= 35
