@@ -108,6 +108,7 @@ class DeepSeek2Model:
             raise ValueError("layer split and tensor / expert parallelism are separate modes")
         self.out_device = self.layer_dev[-1]
         self._cur_dev = self.device
+        self._uploaders = {}
         self.ep = ep                      # all-to-all dispatcher (data-parallel attention + expert parallelism)
         self.block_size = block_size
         if spec.dp_attention:
@@ -147,6 +148,12 @@ class DeepSeek2Model:
 
     # ---- weight intake -------------------------------------------------------------------
     def _dev(self, t: torch.Tensor, dtype=None) -> torch.Tensor:
+        if t.device.type == "cpu" and self._cur_dev.type == "cuda" and t.numel() * t.element_size() >= (256 << 20):
+            up = self._uploaders.get(self._cur_dev)
+            if up is None:
+                from .weights import StagedUploader
+                up = self._uploaders[self._cur_dev] = StagedUploader(self._cur_dev)
+            return up.upload(t, dtype or self.dtype)          # large tensors go through pinned staging buffers
         return t.to(device=self._cur_dev, dtype=dtype or self.dtype).contiguous()
 
     def _load(self, weights: Iterable[Tuple[str, torch.Tensor]]):
@@ -221,6 +228,7 @@ class DeepSeek2Model:
             else:
                 raise KeyError(f"unknown tensor {name}")
         self._cur_dev = self.device
+        self._uploaders.clear()               # release the pinned staging buffers
         if self.w_out is None:
             self.w_out = self.tok_embd if self.out_device == self.device else self.tok_embd.to(self.out_device)
         if not self.spec.sharded:

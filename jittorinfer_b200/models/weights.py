@@ -212,3 +212,46 @@ def iter_gguf(reader, hp: DeepSeek2HParams, spec: ShardSpec = ShardSpec()) -> It
     extra = [n for n in reader.tensors if n not in table and not n.endswith("exp_probs_b.bias")]
     if extra:
         raise ValueError(f"GGUF has {len(extra)} tensors the model does not use, e.g. {extra[:3]}")
+
+
+class StagedUploader:
+    """Host -> device copies of large checkpoint tensors through a ring of pinned staging buffers.
+
+    A tensor that is a view of the GGUF mapping is pageable memory: a plain ``.to(device)`` makes the driver stage it
+    synchronously in small pieces.  Here the file pages are copied into one of ``n_buffers`` pinned buffers (this is what
+    actually reads the file) while the previous buffer's asynchronous copy to the device is still in flight, so disk /
+    page-cache reads overlap the PCIe transfer.  The reference does the same with four 1 MiB buffers
+    (``load_all_data``, src/llama-model-loader.cpp:924-1167); at 50+ GB/s of PCIe a chunk of tens of MiB is needed to
+    amortise the per-copy cost.  Dtype conversion happens on the device after the raw bytes have arrived.
+    """
+
+    def __init__(self, device, chunk_bytes: int = 64 << 20, n_buffers: int = 3, min_bytes: int = 256 << 20):
+        self.device = torch.device(device)
+        self.chunk_bytes, self.min_bytes = int(chunk_bytes), int(min_bytes)
+        cuda = self.device.type == "cuda"
+        self.bufs = [torch.empty(self.chunk_bytes, dtype=torch.uint8, pin_memory=cuda) for _ in range(n_buffers)]
+        self.events = [torch.cuda.Event() if cuda else None for _ in range(n_buffers)]
+        self.n_chunks = 0
+
+    def upload(self, t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``t``: a CPU tensor.  Returns it on the device (converted to ``dtype`` there when given)."""
+        if t.device.type != "cpu" or t.numel() * t.element_size() < self.min_bytes:
+            return t.to(device=self.device, dtype=dtype or t.dtype).contiguous()
+        src = t.contiguous().view(-1).view(torch.uint8)
+        out = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+        dst = out.view(-1).view(torch.uint8)
+        n, k = src.numel(), 0
+        for off in range(0, n, self.chunk_bytes):
+            m = min(self.chunk_bytes, n - off)
+            i = k % len(self.bufs)
+            if self.events[i] is not None and k >= len(self.bufs):
+                self.events[i].synchronize()                 # the device copy that last used this buffer has finished
+            self.bufs[i][:m].copy_(src[off:off + m])         # file pages -> pinned memory
+            dst[off:off + m].copy_(self.bufs[i][:m], non_blocking=True)
+            if self.events[i] is not None:
+                self.events[i].record()
+            k += 1
+        self.n_chunks += k
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+        return out.to(dtype) if dtype is not None and dtype != out.dtype else out

@@ -93,3 +93,16 @@ def test_native_reader_matches_python_reader(tmp_path, monkeypatch):
     monkeypatch.setenv("JITTORINFER_GGUF", "native")
     m_nat = build_model(gguf_path=p, device="cpu", dtype=torch.float32)
     assert torch.equal(m_py.layers[1].w_gate_exps, m_nat.layers[1].w_gate_exps) and torch.equal(m_py.tok_embd, m_nat.tok_embd)
+
+
+def test_staged_uploader_chunks_and_converts():
+    import torch
+    from jittorinfer_b200.models.weights import StagedUploader
+    up = StagedUploader("cpu", chunk_bytes=1000, n_buffers=2, min_bytes=1)
+    t = torch.randn(37, 53)                                   # 7844 bytes -> 8 chunks, the last one partial
+    out = up.upload(t)
+    assert torch.equal(out, t) and up.n_chunks == 8
+    half = up.upload(t.half(), dtype=torch.bfloat16)
+    assert half.dtype == torch.bfloat16 and torch.equal(half, t.half().to(torch.bfloat16))
+    small = StagedUploader("cpu", min_bytes=1 << 20)
+    assert torch.equal(small.upload(t), t) and small.n_chunks == 0      # below the threshold: plain copy
