@@ -102,3 +102,43 @@ class Heartbeat:
                 return True
             time.sleep(min(self.interval, 0.05))
         return False
+
+
+class Watchdog:
+    """Background check that the given ranks are still alive; calls ``on_dead(ranks)`` once when one is not.
+
+    Worker ranks of the multi-process server watch rank 0 with it: a worker blocked in the task broadcast of a rank 0
+    that stopped (without closing its sockets) would otherwise wait forever, like the reference's workers in
+    ``MPI_Bcast``.  The default action logs and leaves the process with exit code 3 -- between steps from the point of
+    view of the device, because the worker is idle in a host-side wait when this fires."""
+
+    def __init__(self, heartbeat: Heartbeat, ranks: List[int], on_dead=None, period: float = 0.5):
+        self.hb, self.ranks, self.period = heartbeat, list(ranks), period
+        self.on_dead = on_dead or self._exit
+        self.fired = False
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+
+    @staticmethod
+    def _exit(ranks):
+        import logging
+        import os
+        logging.getLogger("jittorinfer_b200.health").error("rank(s) %s stopped responding: leaving", ranks)
+        os._exit(3)
+
+    def start(self) -> "Watchdog":
+        def loop():
+            while not self._stop.wait(self.period):
+                gone = self.hb.dead(self.ranks)
+                if gone:
+                    self.fired = True
+                    self.on_dead(gone)
+                    return
+        self._thread = threading.Thread(target=loop, name="watchdog", daemon=True)
+        self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2 * self.period + 1)

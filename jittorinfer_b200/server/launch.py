@@ -76,8 +76,24 @@ def main(argv=None, world: int = 1, rank: int = 0, control_group=None) -> int:
         template = ChatTemplate("")
     eng.warmup()
     ctx = ServerContext(eng, tok, cfg, template, rank=rank, world=world, control_group=control_group)
+    watchdog = None
+    if world > 1 and os.environ.get("JITTORINFER_HEARTBEAT", "1") != "0":
+        # failure detection: every rank publishes heartbeats through the rendezvous store; rank 0 refuses to broadcast to
+        # a dead worker (in-flight requests fail with 503), workers leave when rank 0 goes silent
+        try:
+            import torch.distributed as dist
+            from ..parallel.health import Heartbeat, Watchdog
+            store = dist.distributed_c10d._get_default_store()
+            timeout = float(os.environ.get("JITTORINFER_HEARTBEAT_TIMEOUT", "30"))
+            ctx.heartbeat = Heartbeat(store, rank, world, interval=1.0, timeout=timeout, prefix="jib_hb").start()
+            if rank != 0:
+                watchdog = Watchdog(ctx.heartbeat, [0], period=2.0).start()
+        except Exception as e:      # no store (unusual launchers): serve without failure detection
+            log.warning("heartbeats disabled: %s", e)
     if rank != 0:
         ctx.run()                 # worker ranks: follow rank 0's task broadcasts until told to stop
+        if watchdog is not None:
+            watchdog.stop()
         return 0
     httpd = serve(ctx, cfg.hostname, cfg.port, cfg.n_threads_http)
     log.info("listening on http://%s:%d  (slots=%d, n_ctx_slot=%d, kv blocks=%d)", cfg.hostname, cfg.port, eng.cfg.n_parallel,

@@ -231,3 +231,22 @@ def test_load_trace_lists_tensors(capfd, monkeypatch):
     DeepSeek2Model(hp, random_weights(hp, seed=0).items(), dtype=torch.float32)
     err = capfd.readouterr().err
     assert "load_tensor: token_embd.weight" in err and "blk.1.ffn_gate_exps.weight" in err
+
+
+def test_watchdog_fires_once_for_a_silent_rank():
+    import torch.distributed as dist
+    from jittorinfer_b200.parallel.health import Heartbeat, Watchdog
+    store = dist.HashStore()
+    me = Heartbeat(store, 1, 2, interval=0.05, timeout=0.3).start()
+    zero = Heartbeat(store, 0, 2, interval=0.05, timeout=0.3).start()
+    seen = []
+    wd = Watchdog(me, [0], on_dead=seen.append, period=0.05).start()
+    time.sleep(0.5)
+    assert not wd.fired                                  # rank 0 is beating
+    zero.stop()                                          # rank 0 goes silent
+    deadline = time.monotonic() + 10
+    while not wd.fired and time.monotonic() < deadline:
+        time.sleep(0.05)
+    assert wd.fired and seen == [[0]]
+    wd.stop()
+    me.stop()

@@ -95,3 +95,40 @@ def test_dp_server_two_cpu_ranks():
             p.join(timeout=60)
             if p.is_alive():
                 p.terminate()
+
+
+def test_mpi_server_launcher_two_cpu_ranks(tmp_path):
+    """The real entry point: ``python -m jittorinfer_b200.server.mpi_server --nproc 2`` spawns the ranks, rank 0 serves
+    HTTP, the ranks run tensor-parallel with identical schedulers, heartbeats are on, ``GET /exit`` stops every rank."""
+    import subprocess
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.models.oracle import OracleModel
+    from jittorinfer_b200.models.weights import random_weights
+    hport, mport = _free_port(), _free_port()
+    cfg = tmp_path / "c.yaml"
+    cfg.write_text(f"random_init: tiny-v2\nn_ctx: 1024\nn_parallel: 2\nn_batch: 64\nport: {hport}\nenable_ge: false\ntp_size: 2\nep_size: 2\n")
+    env = dict(os.environ, JITTORINFER_COMM="nccl", JITTORINFER_HEARTBEAT_TIMEOUT="20")
+    p = subprocess.Popen([sys.executable, "-m", "jittorinfer_b200.server.mpi_server", "--nproc", "2", "--master-port", str(mport),
+                          "-c", str(cfg)], cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        url = f"http://127.0.0.1:{hport}"
+        deadline = time.time() + 180
+        while time.time() < deadline:
+            try:
+                if urllib.request.urlopen(url + "/health", timeout=2).status == 200:
+                    break
+            except Exception:
+                assert p.poll() is None, p.stdout.read()[-3000:]
+                time.sleep(0.5)
+        hp = preset("tiny-v2")
+        prompt = torch.randint(1, hp.n_vocab, (15,), generator=torch.Generator().manual_seed(9)).tolist()
+        out = _post(url + "/v1/completions", {"prompt": prompt, "max_tokens": 5, "temperature": 0, "ignore_eos": True, "return_tokens": True})
+        assert out["choices"][0]["tokens"] == OracleModel(hp, random_weights(hp, seed=0)).generate(prompt, 5)
+        try:
+            urllib.request.urlopen(url + "/exit", timeout=10).read()
+        except Exception:
+            pass
+        assert p.wait(timeout=120) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()               # our own child, by handle
