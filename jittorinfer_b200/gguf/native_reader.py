@@ -11,7 +11,6 @@ from typing import Any, Dict
 
 import numpy as np
 
-from . import format as F
 from .io import GGUFReader, TensorInfo
 
 

@@ -25,11 +25,10 @@ import torch
 from .. import ops
 from ..utils import fault
 from ..utils.trace import PhaseTimer, Tracer
-from ..utils import trace as _trace
 from ..models.deepseek2 import DeepSeek2Model, ForwardBatch
 from ..models.hparams import DeepSeek2HParams
 from .native_rt import PagedKV, Scheduler, StepArrays, i32p
-from .sampling import HostSampler, SamplingParams, make_sampler
+from .sampling import SamplingParams, make_sampler
 
 
 @dataclass

@@ -5,7 +5,7 @@ context creation) for this runtime.
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import torch
 

@@ -11,7 +11,7 @@ log = logging.getLogger("jittorinfer_b200.server")
 
 def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
     import torch
-    from ..models.hparams import DeepSeek2HParams, preset
+    from ..models.hparams import preset
     from ..runtime.factory import build_engine
     from ..tokenizer import Tokenizer
     from ..utils.toy_vocab import toy_vocab_kv
