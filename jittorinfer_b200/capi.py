@@ -185,6 +185,7 @@ def load() -> C.CDLL:
     sig("llama_sampler_init_dry", vp, vp, i32, f32, f32, i32, i32, C.POINTER(cp), sz)
     sig("llama_sampler_init_logit_bias", vp, i32, i32, C.POINTER(LogitBias))
     sig("llama_sampler_init_grammar", vp, vp, cp, cp)
+    sig("jib_sampler_init_grammar_pieces", vp, C.POINTER(cp), C.POINTER(C.c_int32), i32, C.POINTER(llama_token), i32, llama_token, cp, cp)
     sig("llama_perf_context", PerfContext, vp)
     sig("llama_perf_context_print", None, vp)
     sig("llama_perf_context_reset", None, vp)

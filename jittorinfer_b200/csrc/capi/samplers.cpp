@@ -6,12 +6,14 @@
 // array is normally the GPU's top-k (64 entries, already sorted), so every sampler works on a short, usually sorted
 // array and none needs a bucket sort over the whole vocabulary.
 #include "capi_internal.h"
+#include "grammar.h"
 
 #include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <numeric>
 #include <random>
 #include <string>
@@ -400,11 +402,107 @@ llama_sampler * bias_clone(const llama_sampler * s) {
 }
 const llama_sampler_i bias_i = {bias_name, nullptr, bias_apply, nullptr, bias_clone, free_ctx<BiasCtx>};
 
-// ---- grammar (pass-through for the empty grammar) -------------------------------------------------------------------
+// ---- grammar ----------------------------------------------------------------------------------------------------------
+// Keeps only the candidates whose text can continue the grammar (end-of-generation tokens only where the text so far is a
+// complete sentence).  If none of the candidates can, one token that can is put in their place, so that generation
+// always stays inside the grammar even when the candidate list is a short device top-k.
+struct GrammarCtx {
+    std::string text, root;
+    jib::Grammar grammar;
+    std::unique_ptr<jib::GrammarMatcher> matcher;
+    std::vector<std::string> pieces;          // bytes of every token ("" = never allowed: control tokens)
+    std::vector<uint8_t> is_eog;
+    llama_token eos = -1;
+    std::string pending;                      // bytes of an incomplete UTF-8 sequence carried between tokens
+    std::vector<llama_token> history;         // accepted tokens (replayed by clone)
+    bool empty_grammar = false;
+
+    bool allows(llama_token t) const {
+        if (t < 0 || (size_t) t >= pieces.size()) return false;
+        if (is_eog[(size_t) t]) return matcher->complete() && pending.empty();
+        const std::string & piece = pieces[(size_t) t];
+        if (piece.empty()) return false;
+        std::vector<uint32_t> cps;
+        jib::Utf8Tail tail;
+        jib::utf8_decode(pending + piece, cps, tail);
+        if (tail.invalid) return false;               // would break a multi-byte character
+        return tail.pending ? matcher->would_accept_tail(cps, tail.lo, tail.hi) : matcher->would_accept(cps);
+    }
+};
 const char * grammar_name(const llama_sampler *) { return "grammar"; }
-void grammar_apply(llama_sampler *, arr_t *) {}
-llama_sampler * grammar_clone(const llama_sampler *) { return llama_sampler_init_grammar(nullptr, "", ""); }
-const llama_sampler_i grammar_i = {grammar_name, nullptr, grammar_apply, nullptr, grammar_clone, nullptr};
+void grammar_apply(llama_sampler * s, arr_t * a) {
+    auto * c = (GrammarCtx *) s->ctx;
+    if (c == nullptr || c->empty_grammar) return;
+    size_t keep = 0;
+    for (size_t i = 0; i < a->size; ++i)
+        if (c->allows(a->data[i].id)) a->data[keep++] = a->data[i];
+    if (keep == 0 && a->size > 0) {
+        llama_token pick = -1;
+        if (c->matcher->complete() && c->pending.empty() && c->eos >= 0) {
+            pick = c->eos;
+        } else {
+            for (size_t t = 0; t < c->pieces.size(); ++t)
+                if (!c->is_eog[t] && c->allows((llama_token) t)) { pick = (llama_token) t; break; }
+        }
+        if (pick >= 0) {
+            a->data[0] = llama_token_data{pick, 0.0f, 1.0f};
+            keep = 1;
+        }
+    }
+    if (keep > 0) a->size = keep;             // keep == 0: nothing in the whole vocabulary fits; leave the list alone
+    if (a->selected >= (int64_t) a->size) a->selected = -1;
+}
+void grammar_accept(llama_sampler * s, llama_token tok) {
+    auto * c = (GrammarCtx *) s->ctx;
+    if (c == nullptr || c->empty_grammar || tok < 0 || (size_t) tok >= c->pieces.size()) return;
+    c->history.push_back(tok);
+    if (c->is_eog[(size_t) tok]) return;
+    std::string bytes = c->pending + c->pieces[(size_t) tok];
+    std::vector<uint32_t> cps;
+    jib::Utf8Tail tail;
+    const size_t used = jib::utf8_decode(bytes, cps, tail);
+    for (uint32_t cp : cps)
+        if (!c->matcher->accept(cp)) break;   // a token the grammar rejects (sampled without apply): state stays put
+    c->pending = tail.invalid ? std::string() : bytes.substr(used);
+}
+void grammar_reset(llama_sampler * s) {
+    auto * c = (GrammarCtx *) s->ctx;
+    if (c == nullptr || c->empty_grammar) return;
+    c->matcher->reset();
+    c->pending.clear();
+    c->history.clear();
+}
+llama_sampler * grammar_clone(const llama_sampler * s);
+void grammar_free(llama_sampler * s) { delete (GrammarCtx *) s->ctx; }
+const llama_sampler_i grammar_i = {grammar_name, grammar_accept, grammar_apply, grammar_reset, grammar_clone, grammar_free};
+
+llama_sampler * grammar_make(std::vector<std::string> pieces, std::vector<uint8_t> is_eog, llama_token eos, const char * text,
+                             const char * root) {
+    auto * c = new GrammarCtx();
+    c->text = text ? text : "";
+    c->root = root && root[0] ? root : "root";
+    c->empty_grammar = c->text.find_first_not_of(" \t\r\n") == std::string::npos;
+    c->pieces = std::move(pieces);
+    c->is_eog = std::move(is_eog);
+    c->eos = eos;
+    if (!c->empty_grammar) {
+        const std::string err = c->grammar.parse(c->text, c->root);
+        if (!err.empty()) {
+            fprintf(stderr, "llama_sampler_init_grammar: %s\n", err.c_str());
+            delete c;
+            return nullptr;
+        }
+        c->matcher.reset(new jib::GrammarMatcher(&c->grammar));
+    }
+    return llama_sampler_init(&grammar_i, c);
+}
+llama_sampler * grammar_clone(const llama_sampler * s) {
+    auto * c = (const GrammarCtx *) s->ctx;
+    llama_sampler * r = grammar_make(c->pieces, c->is_eog, c->eos, c->text.c_str(), c->root.c_str());
+    if (r != nullptr)
+        for (llama_token t : c->history) grammar_accept(r, t);
+    return r;
+}
 
 // ---- chain ----------------------------------------------------------------------------------------------------------
 struct ChainCtx {
@@ -543,12 +641,46 @@ llama_sampler * llama_sampler_init_logit_bias(int32_t n_vocab, int32_t n_logit_b
     if (n_logit_bias > 0 && logit_bias != nullptr) c->bias.assign(logit_bias, logit_bias + n_logit_bias);
     return make(&bias_i, c);
 }
-llama_sampler * llama_sampler_init_grammar(const llama_vocab *, const char * grammar_str, const char *) {
-    if (grammar_str != nullptr && grammar_str[0] != 0) {
-        fprintf(stderr, "llama_sampler_init_grammar: grammar-constrained sampling is not implemented\n");
-        return nullptr;
+llama_sampler * llama_sampler_init_grammar(const llama_vocab * vocab, const char * grammar_str, const char * grammar_root) {
+    std::vector<std::string> pieces;
+    std::vector<uint8_t> eog;
+    llama_token eos = -1;
+    const bool has_text = grammar_str != nullptr && std::string(grammar_str).find_first_not_of(" \t\r\n") != std::string::npos;
+    if (has_text) {
+        if (vocab == nullptr || llama_vocab_n_tokens(vocab) <= 0) {
+            fprintf(stderr, "llama_sampler_init_grammar: a grammar needs a vocabulary with token texts\n");
+            return nullptr;
+        }
+        const int32_t V = llama_vocab_n_tokens(vocab);
+        pieces.resize((size_t) V);
+        eog.assign((size_t) V, 0);
+        std::vector<char> buf(512);
+        for (int32_t t = 0; t < V; ++t) {
+            eog[(size_t) t] = llama_vocab_is_eog(vocab, t) ? 1 : 0;
+            int32_t n = llama_token_to_piece(vocab, t, buf.data(), (int32_t) buf.size(), 0, false);
+            if (n < 0) {
+                buf.resize((size_t) -n);
+                n = llama_token_to_piece(vocab, t, buf.data(), (int32_t) buf.size(), 0, false);
+            }
+            if (n > 0) pieces[(size_t) t].assign(buf.data(), (size_t) n);
+        }
+        eos = llama_vocab_eos(vocab);
     }
-    return llama_sampler_init(&grammar_i, nullptr);
+    return grammar_make(std::move(pieces), std::move(eog), eos, grammar_str, grammar_root);
+}
+
+// The same sampler from a table of token texts instead of a llama_vocab (used by the Python engine, whose tokenizer is
+// not a llama_vocab).  pieces[i] / lens[i]: bytes of token i (length 0 = never allowed); eog: ids that end generation.
+MINI_API llama_sampler * jib_sampler_init_grammar_pieces(const char * const * pieces, const int32_t * lens, int32_t n_tokens,
+                                                         const llama_token * eog, int32_t n_eog, llama_token eos, const char * grammar_str,
+                                                         const char * grammar_root) {
+    std::vector<std::string> p((size_t) std::max(n_tokens, 0));
+    std::vector<uint8_t> e((size_t) std::max(n_tokens, 0), 0);
+    for (int32_t i = 0; i < n_tokens; ++i)
+        if (lens[i] > 0) p[(size_t) i].assign(pieces[i], (size_t) lens[i]);
+    for (int32_t i = 0; i < n_eog; ++i)
+        if (eog[i] >= 0 && eog[i] < n_tokens) e[(size_t) eog[i]] = 1;
+    return grammar_make(std::move(p), std::move(e), eos, grammar_str, grammar_root);
 }
 
 llama_perf_sampler_data llama_perf_sampler(const llama_sampler * chain) {

@@ -452,8 +452,10 @@ MINI_API struct llama_sampler * llama_sampler_init_dry(const struct llama_vocab 
                                                        float dry_base, int32_t dry_allowed_length, int32_t dry_penalty_last_n,
                                                        const char ** seq_breakers, size_t num_breakers);
 MINI_API struct llama_sampler * llama_sampler_init_logit_bias(int32_t n_vocab, int32_t n_logit_bias, const llama_logit_bias * logit_bias);
-/* Grammar-constrained sampling is not implemented (the original asserts on a non-empty grammar): an empty
- * grammar gives a pass-through sampler, a non-empty one returns NULL. */
+/* Grammar-constrained sampling over a GBNF grammar (the original declares this but asserts on a non-empty grammar):
+ * candidates whose text cannot continue the grammar are dropped, end-of-generation tokens are kept only where the text
+ * so far is complete; if no candidate fits, one token that does is substituted.  Returns NULL if the grammar does not
+ * parse.  An empty grammar gives a pass-through sampler. */
 MINI_API struct llama_sampler * llama_sampler_init_grammar(const struct llama_vocab * vocab, const char * grammar_str,
                                                            const char * grammar_root);
 

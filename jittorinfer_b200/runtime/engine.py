@@ -176,7 +176,8 @@ class LLMEngine:
         params = params or SamplingParams()
         rid = self._next_id
         self._next_id += 1
-        smpl = None if params.greedy and params.dry_multiplier <= 0 else make_sampler(params, self.hp.n_vocab, self.hp.n_ctx_train)
+        smpl = None if params.greedy and params.dry_multiplier <= 0 else \
+            make_sampler(params, self.hp.n_vocab, self.hp.n_ctx_train, getattr(self, "token_table", None))
         st = RequestState(rid, params, smpl, len(prompt), t_submit=time.time())
         if st.sampler is not None:
             for t in prompt[-params.repeat_last_n:]:

@@ -39,6 +39,7 @@ class SamplingParams:
     dry_allowed_length: int = 2
     dry_penalty_last_n: int = -1
     min_keep: int = 0
+    grammar: Optional[str] = None     # GBNF text: candidates that cannot continue it are dropped (needs the native chain)
     seed: Optional[int] = None
     max_tokens: int = -1
     ignore_eos: bool = False
@@ -47,7 +48,7 @@ class SamplingParams:
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0.0 and self.repeat_penalty == 1.0 and self.frequency_penalty == 0.0 \
-            and self.presence_penalty == 0.0 and not self.logit_bias
+            and self.presence_penalty == 0.0 and not self.logit_bias and not self.grammar
 
 
 class HostSampler:
@@ -123,7 +124,8 @@ class NativeSampler:
     ``dynatemp_range`` > 0), then logit_bias and dist (common/sampling_local.cpp:128-210).  Candidates are the device's
     top-k, as with the reference's presample path."""
 
-    def __init__(self, params: SamplingParams, n_vocab: int = 0, n_ctx_train: int = 4096):
+    def __init__(self, params: SamplingParams, n_vocab: int = 0, n_ctx_train: int = 4096, token_table=None):
+        """``token_table``: (pieces: list of bytes per token id, eog ids, eos id) -- needed only for ``params.grammar``."""
         import ctypes as C
         from .. import capi
         self.C, self.capi = C, capi
@@ -132,6 +134,17 @@ class NativeSampler:
         seed = p.seed if p.seed is not None else 0xFFFFFFFF
         ch = self.chain = L.llama_sampler_chain_init(capi.SamplerChainParams(True))
         add = lambda smpl: L.llama_sampler_chain_add(ch, smpl)
+        if p.grammar:
+            if token_table is None:
+                raise ValueError("a grammar needs the token texts (token_table)")
+            pieces, eog, eos = token_table
+            arr = (C.c_char_p * len(pieces))(*pieces)
+            lens = (C.c_int32 * len(pieces))(*[len(b) for b in pieces])
+            eog_a = (capi.llama_token * max(1, len(eog)))(*eog)
+            g = L.jib_sampler_init_grammar_pieces(arr, lens, len(pieces), eog_a, len(eog), int(eos), p.grammar.encode(), b"root")
+            if not g:
+                raise ValueError("the grammar does not parse")
+            add(g)                    # first: the other samplers then work on admissible candidates only
         add(L.llama_sampler_init_penalties(p.repeat_last_n, p.repeat_penalty, p.frequency_penalty, p.presence_penalty))
         if p.dry_multiplier > 0:
             add(L.llama_sampler_init_dry(None, n_ctx_train, p.dry_multiplier, p.dry_base, p.dry_allowed_length, p.dry_penalty_last_n,
@@ -172,9 +185,11 @@ class NativeSampler:
         return int(arr.data[arr.selected].id)
 
 
-def make_sampler(params: SamplingParams, n_vocab: int = 0, n_ctx_train: int = 4096):
+def make_sampler(params: SamplingParams, n_vocab: int = 0, n_ctx_train: int = 4096, token_table=None):
     """The native chain unless it cannot be loaded or ``JITTORINFER_SAMPLER=python`` asks for the numpy one."""
     import os
+    if params.grammar:
+        return NativeSampler(params, n_vocab, n_ctx_train, token_table)      # no fallback: the numpy chain has no grammar
     if os.environ.get("JITTORINFER_SAMPLER", "native").lower() != "python":
         try:
             return NativeSampler(params, n_vocab, n_ctx_train)

@@ -94,6 +94,7 @@ class ServerContext:
         self.inbox: "queue.Queue" = queue.Queue()
         self.streams: Dict[int, _Stream] = {}
         self.metrics = Metrics()
+        self.engine.tokenizer_for_grammar = tokenizer         # the table of token texts is built on the first grammar request
         self.stop_flag = threading.Event()
         self.thread: Optional[threading.Thread] = None
         self.model_alias = getattr(cfg, "model_alias", "") or "deepseek2"
@@ -468,6 +469,10 @@ def make_handler(ctx: ServerContext):
             except (json.JSONDecodeError, UnicodeDecodeError, ValueError) as e:
                 ctx.metrics.inc("requests_failed_total")
                 return self._json(400, P.error_body(f"invalid request: {e}", 400))
+            if req.grammar and getattr(ctx.cfg, "enforce_response_format", True):
+                req.params.grammar = req.grammar               # response_format is enforced token by token
+                if getattr(ctx.engine, "token_table", None) is None:
+                    ctx.engine.token_table = ctx.tokenizer.token_table()
             streams = [ctx.submit(p, SamplingParams(**req.params.__dict__), req.stop) for p in req.prompts]
             try:
                 if req.stream:

@@ -77,6 +77,15 @@ class Tokenizer:
     def eot(self): return self._L.jib_tok_eot(self._h)
     def is_eog(self, tid: int) -> bool: return bool(self._L.jib_tok_is_eog(self._h, tid))
 
+    def token_table(self):
+        """(bytes of every token with control tokens as b"", end-of-generation ids, eos id): what a grammar sampler needs."""
+        t = getattr(self, "_token_table", None)
+        if t is None:
+            pieces = [self.piece_bytes(i, special=False) for i in range(self.n_tokens)]
+            eog = [i for i in range(self.n_tokens) if self.is_eog(i)]
+            t = self._token_table = (pieces, eog, self.eos)
+        return t
+
     def encode(self, text: str, add_special: bool = True, parse_special: bool = True) -> List[int]:
         b = text.encode("utf-8")
         cap = len(b) + 8

@@ -85,3 +85,88 @@ def test_chat_request_carries_grammar_and_rejects_bad_schema():
     body["response_format"] = {"type": "json_schema", "json_schema": {"schema": {"type": "frob"}}}
     with pytest.raises(P.BadRequest):
         P.parse_chat(body, Tok(), ChatTemplate(""), "m", 16)
+
+
+def _toy_vocab_model(tmp_path):
+    from jittorinfer_b200 import capi
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.models.weights import write_random_gguf
+    L = capi.load()
+    p = str(tmp_path / "m.gguf")
+    write_random_gguf(p, preset("tiny"), seed=0)
+    mp = L.llama_model_default_params()
+    mp.vocab_only = True
+    model = L.llama_model_load_from_file(p.encode(), mp)
+    return L, capi, model, L.llama_model_get_vocab(model)
+
+
+def test_grammar_sampler_constrains_random_logits(tmp_path):
+    """The C API's grammar sampler: with random logits over the whole vocabulary every generated text is a sentence of
+    the grammar (here: the grammar of a JSON schema), and generation ends with an end-of-generation token."""
+    import ctypes as C
+    import random
+    L, capi, model, vocab = _toy_vocab_model(tmp_path)
+    schema = {"type": "object", "properties": {"color": {"enum": ["red", "green"]}, "n": {"type": "integer"}, "ok": {"type": "boolean"}},
+              "required": ["color", "n"]}
+    gbnf = json_schema_to_grammar(schema)
+    assert L.llama_sampler_init_grammar(vocab, b"root ::= (", b"root") is None          # syntax error -> NULL
+    V = L.llama_vocab_n_tokens(vocab)
+    rng = random.Random(0)
+    for trial in range(3):
+        smpl = L.llama_sampler_init_grammar(vocab, gbnf.encode(), b"root")
+        assert smpl
+        toks = []
+        for step in range(400):
+            arr, keep = capi.candidates([rng.gauss(0, 1) for _ in range(V)])
+            L.llama_sampler_apply(smpl, C.byref(arr))
+            assert arr.size >= 1
+            best = max(range(arr.size), key=lambda i: arr.data[i].logit)
+            tok = arr.data[best].id
+            L.llama_sampler_accept(smpl, tok)
+            if L.llama_vocab_is_eog(vocab, tok):
+                break
+            toks.append(tok)
+        else:
+            raise AssertionError("generation did not finish")
+        buf = C.create_string_buffer(4096)
+        ids = (capi.llama_token * len(toks))(*toks)
+        n = L.llama_detokenize(vocab, ids, len(toks), buf, 4096, False, False)
+        text = buf.raw[:n].decode()
+        doc = json.loads(text)
+        assert grammar_accepts(gbnf, text), text
+        assert doc["color"] in ("red", "green") and isinstance(doc["n"], int) and set(doc) <= {"color", "n", "ok"}
+        clone = L.llama_sampler_clone(smpl)
+        assert clone
+        L.llama_sampler_free(clone)
+        L.llama_sampler_free(smpl)
+    L.llama_model_free(model)
+
+
+def test_server_enforces_response_format():
+    """Through the server: a chat request with a JSON schema gets a document that parses and fits the schema even though
+    the model is random (the device top-k candidates are filtered; a dead end substitutes an admissible token)."""
+    import threading
+    import urllib.request
+    import torch
+    from jittorinfer_b200.config import ServerConfig
+    from jittorinfer_b200.server.app import ServerContext, serve
+    from jittorinfer_b200.server.chat import ChatTemplate
+    from jittorinfer_b200.server.launch import build_from_config
+    cfg = ServerConfig(random_init="tiny", n_ctx=2048, n_parallel=2, n_batch=64, port=0, enable_ge=False)
+    eng, tok, tpl = build_from_config(cfg, device=torch.device("cpu"))
+    ctx = ServerContext(eng, tok, cfg, ChatTemplate(tpl))
+    httpd = serve(ctx, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    try:
+        schema = {"type": "object", "properties": {"answer": {"enum": ["yes", "no"]}, "score": {"type": "integer"}}, "required": ["answer", "score"]}
+        body = {"messages": [{"role": "user", "content": "judge"}], "max_tokens": 200, "temperature": 0.7, "seed": 5,
+                "response_format": {"type": "json_schema", "json_schema": {"schema": schema}}}
+        req = urllib.request.Request(f"http://127.0.0.1:{httpd.server_address[1]}/v1/chat/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        out = json.loads(urllib.request.urlopen(req, timeout=120).read())
+        doc = json.loads(out["choices"][0]["message"]["content"])
+        assert doc["answer"] in ("yes", "no") and isinstance(doc["score"], int)
+        assert out["choices"][0]["finish_reason"] == "stop"
+    finally:
+        httpd.shutdown()
+        ctx.shutdown()
