@@ -171,6 +171,11 @@ class ServerContext:
                 out.append(("cancel_rid", t[1]))
         return out
 
+    def _prepare_grammar(self, params: SamplingParams) -> None:
+        """Every rank that samples a grammar-constrained request needs the table of token texts."""
+        if params.grammar and getattr(self.engine, "token_table", None) is None:
+            self.engine.token_table = self.tokenizer.token_table()
+
     def _run_dp(self):
         """Attention data-parallel serving: rank 0 assigns every request to one rank (round robin), all ranks step
         together (a rank without tokens runs the idle forward), and every iteration the new tokens of all ranks are
@@ -208,7 +213,9 @@ class ServerContext:
                 return
             for t in w:
                 if t[0] == "add" and t[2] == self.rank:
-                    rid = eng.add_request(t[3], SamplingParams(**t[4]))
+                    sp = SamplingParams(**t[4])
+                    self._prepare_grammar(sp)
+                    rid = eng.add_request(t[3], sp)
                     gid_of[rid], rid_of[t[1]] = t[1], rid
                 elif t[0] == "cancel" and t[1] in rid_of:
                     rid = rid_of.pop(t[1])
@@ -252,6 +259,7 @@ class ServerContext:
             for t in tasks:
                 if t[0] == "add":
                     _, st, prompt, params = t
+                    self._prepare_grammar(params)
                     rid = eng.add_request(prompt, params)
                     if st is not None:
                         st.rid = rid
