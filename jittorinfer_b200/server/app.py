@@ -259,8 +259,15 @@ class ServerContext:
             for t in tasks:
                 if t[0] == "add":
                     _, st, prompt, params = t
-                    self._prepare_grammar(params)
-                    rid = eng.add_request(prompt, params)
+                    try:
+                        self._prepare_grammar(params)
+                        rid = eng.add_request(prompt, params)
+                    except Exception as e:             # a request the engine refuses fails alone
+                        if st is not None:
+                            st.q.put(("error", f"request rejected: {e}"))
+                            st.done = True
+                        self.metrics.inc("requests_failed_total")
+                        continue
                     if st is not None:
                         st.rid = rid
                         self.streams[rid] = st
@@ -481,6 +488,12 @@ def make_handler(ctx: ServerContext):
                 req.params.grammar = req.grammar               # response_format is enforced token by token
                 if getattr(ctx.engine, "token_table", None) is None:
                     ctx.engine.token_table = ctx.tokenizer.token_table()
+                try:                                           # compile it here: a grammar the engine cannot build is a 400
+                    from ..runtime.sampling import NativeSampler
+                    NativeSampler(SamplingParams(grammar=req.grammar), token_table=ctx.engine.token_table)
+                except Exception as e:
+                    ctx.metrics.inc("requests_failed_total")
+                    return self._json(400, P.error_body(f"response_format: {e}", 400))
             streams = [ctx.submit(p, SamplingParams(**req.params.__dict__), req.stop) for p in req.prompts]
             try:
                 if req.stream:

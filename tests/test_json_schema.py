@@ -170,3 +170,34 @@ def test_server_enforces_response_format():
     finally:
         httpd.shutdown()
         ctx.shutdown()
+
+
+def test_server_rejects_a_grammar_the_engine_cannot_build():
+    import threading
+    import urllib.error
+    import urllib.request
+    import torch
+    from jittorinfer_b200.config import ServerConfig
+    from jittorinfer_b200.server.app import ServerContext, serve
+    from jittorinfer_b200.server.chat import ChatTemplate
+    from jittorinfer_b200.server.launch import build_from_config
+    cfg = ServerConfig(random_init="tiny", n_ctx=1024, n_parallel=2, n_batch=64, port=0, enable_ge=False)
+    eng, tok, tpl = build_from_config(cfg, device=torch.device("cpu"))
+    ctx = ServerContext(eng, tok, cfg, ChatTemplate(tpl))
+    httpd = serve(ctx, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    url = f"http://127.0.0.1:{httpd.server_address[1]}/v1/chat/completions"
+    try:
+        body = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 8,
+                "response_format": {"type": "json_schema", "json_schema": {"schema": {"type": "string", "maxLength": 100000}}}}
+        req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(req, timeout=60)
+        assert e.value.code == 400
+        body["response_format"] = {"type": "json_object"}      # the server is still healthy
+        body["temperature"] = 0
+        req = urllib.request.Request(url, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+        assert json.loads(urllib.request.urlopen(req, timeout=60).read())["object"] == "chat.completion"
+    finally:
+        httpd.shutdown()
+        ctx.shutdown()

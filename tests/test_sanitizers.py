@@ -35,3 +35,75 @@ def test_runtime_tests_pass_under_asan_ubsan():
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0, tail
     assert "ERROR: AddressSanitizer" not in tail and "runtime error:" not in tail
+
+
+GRAMMAR_HARNESS = r"""
+#include "grammar.h"
+#include <cstdio>
+#include <fstream>
+#include <sstream>
+// argv[1]: file with a GBNF grammar, argv[2]: file with a text.  Prints "parse-error", "accept" or "reject".
+int main(int argc, char ** argv) {
+    if (argc < 3) return 2;
+    std::stringstream g, t;
+    g << std::ifstream(argv[1]).rdbuf();
+    t << std::ifstream(argv[2]).rdbuf();
+    jib::Grammar grammar;
+    if (!grammar.parse(g.str(), "root").empty()) { puts("parse-error"); return 0; }
+    jib::GrammarMatcher m(&grammar);
+    std::vector<uint32_t> cps;
+    jib::Utf8Tail tail;
+    jib::utf8_decode(t.str(), cps, tail);
+    for (uint32_t cp : cps)
+        if (!m.accept(cp)) { puts("reject"); return 0; }
+    puts(m.complete() ? "accept" : "reject");
+    return 0;
+}
+"""
+
+
+@pytest.mark.timeout(900)
+def test_grammar_engine_under_asan_with_hostile_input(tmp_path):
+    """Grammar text arrives in requests: the parser and matcher run under ASan + UBSan over valid grammars, truncated
+    and mutated ones and random bytes; they must answer (accept / reject / parse-error) and never trip a sanitizer."""
+    import random
+    from jittorinfer_b200.server.json_schema import grammar_accepts, json_schema_to_grammar
+    if _san_runtime("libasan.so") is None:
+        pytest.skip("no libasan in this toolchain")
+    src = tmp_path / "harness.cpp"
+    src.write_text(GRAMMAR_HARNESS)
+    exe = str(tmp_path / "harness")
+    capi_dir = os.path.join(build.CSRC, "capi")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-I", capi_dir,
+                    str(src), os.path.join(capi_dir, "grammar.cpp"), "-o", exe], check=True)
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1")
+
+    def run(grammar: bytes, text: bytes) -> str:
+        (tmp_path / "g.txt").write_bytes(grammar)
+        (tmp_path / "t.txt").write_bytes(text)
+        r = subprocess.run([exe, str(tmp_path / "g.txt"), str(tmp_path / "t.txt")], capture_output=True, text=True, env=env, timeout=60)
+        assert r.returncode == 0, r.stderr[-2000:]
+        return r.stdout.strip()
+
+    schema = {"type": "object", "properties": {"name": {"type": "string", "maxLength": 8}, "tags": {"type": "array", "items": {"enum": ["a", "b"]}},
+                                               "n": {"type": "number"}}, "required": ["name"]}
+    g = json_schema_to_grammar(schema)
+    docs = ['{"name": "x"}', '{"name":"é✓","tags":["a","b"],"n":-1.5e3}', '{"tags": []}', '{"name": "toolongname"}', '[1]', '']
+    for d in docs:                                        # the C++ matcher agrees with the Python one
+        assert run(g.encode(), d.encode()) == ("accept" if grammar_accepts(g, d) else "reject"), d
+    rng = random.Random(0)
+    raw = g.encode()
+    for _ in range(40):                                   # truncations, byte flips, random bytes
+        kind = rng.randrange(3)
+        if kind == 0:
+            bad = raw[: rng.randrange(len(raw))]
+        elif kind == 1:
+            b = bytearray(raw)
+            for _ in range(rng.randrange(1, 6)):
+                b[rng.randrange(len(b))] = rng.randrange(256)
+            bad = bytes(b)
+        else:
+            bad = bytes(rng.randrange(256) for _ in range(rng.randrange(1, 200)))
+        assert run(bad, b'{"name": "x"}') in ("accept", "reject", "parse-error")
+    assert run(b'root ::= root "a" | "a"', b"aaa") in ("accept", "reject")       # left recursion: bounded, no crash
+    assert run(b'root ::= ("a" | "b"){2,3} [^x-z]* "\\u00e9"', "abqé".encode()) == "accept"
