@@ -45,13 +45,20 @@ class ChatMessage(C.Structure):
     _fields_ = [("role", C.c_char_p), ("content", C.c_char_p)]
 
 
+class KvOverride(C.Structure):
+    class _V(C.Union):
+        _fields_ = [("val_i64", C.c_int64), ("val_f64", C.c_double), ("val_bool", C.c_bool), ("val_str", C.c_char * 128)]
+    _anonymous_ = ("v",)
+    _fields_ = [("tag", C.c_int), ("key", C.c_char * 128), ("v", _V)]
+
+
 class ModelParams(C.Structure):
     _fields_ = [("devices", C.c_void_p), ("n_gpu_layers", C.c_int32), ("split_mode", C.c_int), ("main_gpu", C.c_int32),
                 ("tensor_split", C.POINTER(C.c_float)),
                 ("enable_tensor_parallel", C.c_bool), ("enable_expert_parallel", C.c_bool), ("enable_data_parallel", C.c_bool),
                 ("enable_mpi", C.c_bool), ("offload_input", C.c_bool), ("enable_mla", C.c_bool),
                 ("enable_cann_flash_attention", C.c_bool), ("tp_id", C.c_int), ("num_parallel", C.c_int),
-                ("progress_callback", progress_cb_t), ("progress_callback_user_data", C.c_void_p), ("kv_overrides", C.c_void_p),
+                ("progress_callback", progress_cb_t), ("progress_callback_user_data", C.c_void_p), ("kv_overrides", C.POINTER(KvOverride)),
                 ("vocab_only", C.c_bool), ("use_mmap", C.c_bool), ("use_mlock", C.c_bool), ("check_tensors", C.c_bool),
                 ("enable_fused_moe", C.c_bool)]
 

@@ -63,7 +63,7 @@ class _Context:
 
 
 def load_model(path: str, use_gpu: int, main_gpu: int, tp_id: int, num_parallel: int, expert_parallel: int,
-               check_tensors: int, data_parallel: int, layer_split: str = "") -> int:
+               check_tensors: int, data_parallel: int, layer_split: str = "", kv_overrides: str = "{}") -> int:
     from .runtime.factory import build_model
     on_gpu = bool(use_gpu) and torch.cuda.is_available()
     if on_gpu:
@@ -85,7 +85,8 @@ def load_model(path: str, use_gpu: int, main_gpu: int, tp_id: int, num_parallel:
                 tensor_split = None
         layer_devices = [torch.device("cuda", (main_gpu + i) % n) for i in range(n)]
     model = build_model(gguf_path=path, device=device, dtype=torch.bfloat16 if on_gpu else torch.float32, world=num_parallel,
-                        rank=tp_id, expert_parallel=bool(expert_parallel), layer_devices=layer_devices, tensor_split=tensor_split)
+                        rank=tp_id, expert_parallel=bool(expert_parallel), layer_devices=layer_devices, tensor_split=tensor_split,
+                        kv_overrides=__import__("json").loads(kv_overrides or "{}"))
     if check_tensors:
         for L in model.layers:
             for name in L.__slots__:

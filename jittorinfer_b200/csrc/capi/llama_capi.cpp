@@ -164,10 +164,32 @@ llama_model * llama_model_load_from_file(const char * path_model, llama_model_pa
                 for (int i = 0; i < 8; ++i) split += (i ? "," : "") + std::to_string(params.tensor_split[i]);
             }
         }
-        if (!jib::PyBridge::call("load_model", &m->py, &perr, "(siiiiiiis)", m->path.c_str(), params.n_gpu_layers > 0 ? 1 : 0,
+        // metadata overrides (the list ends at an empty key), as a JSON object for the loader
+        std::string ov = "{";
+        for (const llama_model_kv_override * o = params.kv_overrides; o != nullptr && o->key[0] != 0; ++o) {
+            if (ov.size() > 1) ov += ",";
+            ov += "\"" + std::string(o->key, strnlen(o->key, sizeof(o->key))) + "\":";
+            switch (o->tag) {
+                case LLAMA_KV_OVERRIDE_TYPE_INT: ov += std::to_string((long long) o->val_i64); break;
+                case LLAMA_KV_OVERRIDE_TYPE_FLOAT: { char b[40]; snprintf(b, sizeof(b), "%.17g", o->val_f64); ov += b; break; }
+                case LLAMA_KV_OVERRIDE_TYPE_BOOL: ov += o->val_bool ? "true" : "false"; break;
+                case LLAMA_KV_OVERRIDE_TYPE_STR: {
+                    ov += "\"";
+                    for (size_t i = 0; i < strnlen(o->val_str, sizeof(o->val_str)); ++i) {
+                        const char ch = o->val_str[i];
+                        if (ch == '"' || ch == '\\') ov += '\\';
+                        if ((unsigned char) ch >= 0x20) ov += ch;
+                    }
+                    ov += "\"";
+                    break;
+                }
+            }
+        }
+        ov += "}";
+        if (!jib::PyBridge::call("load_model", &m->py, &perr, "(siiiiiiiss)", m->path.c_str(), params.n_gpu_layers > 0 ? 1 : 0,
                                  params.main_gpu, tp ? params.tp_id : 0, tp ? std::max(params.num_parallel, 1) : 1,
                                  params.enable_expert_parallel ? 1 : 0, params.check_tensors ? 1 : 0,
-                                 params.enable_data_parallel ? 1 : 0, split.c_str())) {
+                                 params.enable_data_parallel ? 1 : 0, split.c_str(), ov.c_str())) {
             log_err("llama_model_load_from_file", perr);
             return nullptr;
         }

@@ -19,7 +19,7 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
                 dtype: torch.dtype = torch.bfloat16, world: int = 1, rank: int = 0, expert_parallel: bool = True,
                 comm=None, seed: int = 0, std: float = 0.02, max_positions: int = 8192, fast_random: bool = True,
                 dp_attention: bool = False, ep_max_tokens: int = 256, layer_devices=None,
-                tensor_split=None) -> DeepSeek2Model:
+                tensor_split=None, kv_overrides=None) -> DeepSeek2Model:
     """``dp_attention``: attention data-parallel (every rank serves its own requests), routed experts sharded over the
     ranks and reached through the all-to-all dispatcher; ``ep_max_tokens`` bounds the tokens of one rank per step."""
     dp_attention = dp_attention and world > 1
@@ -31,6 +31,8 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
         else:
             from ..gguf.io import GGUFReader
         reader = GGUFReader(gguf_path)
+        if kv_overrides:                 # metadata overrides (llama_model_params.kv_overrides)
+            reader.kv.update(kv_overrides)
         hp = DeepSeek2HParams.from_gguf_kv(reader.kv, reader.tensors)
         weights = iter_gguf(reader, hp, spec)
     else:

@@ -474,3 +474,33 @@ def test_engine_uses_the_native_sampler_chain():
         eng = LLMEngine(DeepSeek2Model(hp, random_weights(hp, seed=0).items(), dtype=torch.float32), EngineConfig(n_ctx=512, n_batch=32, n_parallel=2))
         outs.append(eng.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.9, seed=3, ignore_eos=True, dynatemp_range=0.3), max_new_tokens=8))
     assert outs[0] == outs[1] and len(outs[0][0]) == 8
+
+
+def test_kv_overrides_change_the_loaded_hyperparameters(L, gguf_path):
+    """llama_model_params.kv_overrides: metadata of the file is replaced before the hyper-parameters are read -- here the
+    number of experts used per token, which changes the logits."""
+    def first_logits(overrides):
+        mp = L.llama_model_default_params()
+        mp.n_gpu_layers = 0
+        keep = None
+        if overrides:
+            keep = (capi.KvOverride * (len(overrides) + 1))()
+            for i, (k, v) in enumerate(overrides.items()):
+                keep[i].tag, keep[i].key, keep[i].val_i64 = 0, k.encode(), v
+            mp.kv_overrides = keep
+        m = L.llama_model_load_from_file(gguf_path.encode(), mp)
+        assert m
+        cp = L.llama_context_default_params()
+        cp.n_ctx, cp.n_batch, cp.n_seq_max = 128, 32, 1
+        ctx = L.llama_init_from_model(m, cp)
+        toks = (capi.llama_token * 6)(3, 9, 27, 81, 243, 729)
+        assert L.llama_decode(ctx, L.llama_batch_get_one(toks, 6), False) == 0
+        lg = L.llama_get_logits_ith(ctx, -1)
+        out = [lg.values[i] for i in range(32)]
+        L.llama_free(ctx)
+        L.llama_model_free(m)
+        return out
+    base = first_logits(None)
+    same = first_logits({"deepseek2.expert_used_count": 2})       # the file's own value
+    one = first_logits({"deepseek2.expert_used_count": 1})
+    assert base == same and base != one
