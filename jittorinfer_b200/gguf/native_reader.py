@@ -74,6 +74,10 @@ class NativeGGUFReader(GGUFReader):
 
     def raw(self, name: str) -> np.ndarray:
         ti = self.tensors[name]
-        arr = np.ctypeslib.as_array(C.cast(self._ptr[name], C.POINTER(C.c_uint8)), shape=(ti.nbytes,))
+        # The array (and every tensor made from it) keeps this reader alive: the mapping is released only when the last
+        # view is gone -- on the CPU a float32 tensor "moved" to the CPU is still a view of the file.
+        buf = (C.c_uint8 * ti.nbytes).from_address(self._ptr[name])
+        buf._owner = self
+        arr = np.frombuffer(buf, dtype=np.uint8)
         arr.flags.writeable = False
         return arr

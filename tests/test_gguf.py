@@ -93,6 +93,15 @@ def test_native_reader_matches_python_reader(tmp_path, monkeypatch):
     monkeypatch.setenv("JITTORINFER_GGUF", "native")
     m_nat = build_model(gguf_path=p, device="cpu", dtype=torch.float32)
     assert torch.equal(m_py.layers[1].w_gate_exps, m_nat.layers[1].w_gate_exps) and torch.equal(m_py.tok_embd, m_nat.tok_embd)
+    # on the CPU the float32 weights are views of the mapping: it must outlive the reader object that created it
+    import gc
+    del nat, py
+    gc.collect()
+    from jittorinfer_b200.runtime.engine import EngineConfig, LLMEngine
+    from jittorinfer_b200.runtime.sampling import SamplingParams
+    outs = [LLMEngine(m, EngineConfig(n_ctx=256, n_batch=32, n_parallel=1)).generate([[1, 2, 3, 4]], SamplingParams(ignore_eos=True), 4)
+            for m in (m_py, m_nat)]
+    assert outs[0] == outs[1]
 
 
 def test_staged_uploader_chunks_and_converts():
