@@ -44,8 +44,9 @@ class _Model:
 
 
 class _Context:
-    def __init__(self, m: _Model, n_blocks: int, block_size: int, presample: int, n_ctx: int):
+    def __init__(self, m: _Model, n_blocks: int, block_size: int, presample: int, n_ctx: int, rope: dict):
         self.m = m
+        self._rope_changed = _rope_overrides(m.model, rope)
         hp = m.model.hp
         dtype = m.model.dtype
         self.block_size = block_size
@@ -55,11 +56,37 @@ class _Context:
             self.cache = SplitCache(m.model.layer_dev, n_blocks * block_size, hp.kv_row, dtype, block_size)
         else:
             self.cache = torch.zeros(hp.n_layer, n_blocks * block_size, hp.kv_row, dtype=dtype, device=m.device)
-        if n_ctx > m.model.max_positions:
+        if n_ctx > m.model.max_positions or self._rope_changed:
             lo, hi = hp.yarn_corr_dims()
-            m.model.max_positions = n_ctx
+            m.model.max_positions = max(n_ctx, m.model.max_positions)
+            n_ctx = m.model.max_positions
             m.model.rope_table = ops.ref.yarn_table(n_ctx, hp.qk_rope_head_dim, hp.rope_freq_base, hp.freq_scale, hp.ext_factor,
                                                     hp.rope_attn, lo, hi, device=m.device)
+
+
+def _rope_overrides(model, rope: dict) -> bool:
+    """llama_context_params.rope_freq_base / rope_freq_scale / yarn_attn_factor / yarn_orig_ctx / rope_scaling_type: values
+    that differ from "keep the model's" replace the hyper-parameters (the attention scale follows: it depends on the
+    frequency scale through the YaRN magnitude factor).  The model object is shared by the contexts made from it."""
+    import dataclasses
+    hp, ch = model.hp, {}
+    if rope.get("freq_base", 0) > 0 and rope["freq_base"] != hp.rope_freq_base:
+        ch["rope_freq_base"] = float(rope["freq_base"])
+    st = int(rope.get("scaling_type", -1))
+    if st == 0 and hp.rope_scaling_type != "none":
+        ch["rope_scaling_type"] = "none"
+    elif st == 2 and hp.rope_scaling_type != "yarn":
+        ch["rope_scaling_type"] = "yarn"
+    if rope.get("freq_scale", 0) > 0 and abs(1.0 / rope["freq_scale"] - hp.rope_scaling_factor) > 1e-9:
+        ch["rope_scaling_factor"] = 1.0 / float(rope["freq_scale"])
+    if rope.get("attn_factor", 0) > 0 and rope["attn_factor"] != 1.0 and rope["attn_factor"] != hp.rope_attn_factor:
+        ch["rope_attn_factor"] = float(rope["attn_factor"])
+    if rope.get("orig_ctx", 0) > 0 and rope["orig_ctx"] != hp.rope_orig_ctx:
+        ch["rope_orig_ctx"] = int(rope["orig_ctx"])
+    if not ch:
+        return False
+    model.hp = dataclasses.replace(hp, **ch)
+    return True
 
 
 def load_model(path: str, use_gpu: int, main_gpu: int, tp_id: int, num_parallel: int, expert_parallel: int,
@@ -103,9 +130,9 @@ def free_model(h: int) -> int:
     return 0
 
 
-def create_context(mh: int, n_blocks: int, block_size: int, presample: int, n_ctx: int) -> int:
+def create_context(mh: int, n_blocks: int, block_size: int, presample: int, n_ctx: int, rope: str = "{}") -> int:
     h = _handle()
-    _contexts[h] = _Context(_models[mh], n_blocks, block_size, presample, n_ctx)
+    _contexts[h] = _Context(_models[mh], n_blocks, block_size, presample, n_ctx, __import__("json").loads(rope or "{}"))
     return h
 
 

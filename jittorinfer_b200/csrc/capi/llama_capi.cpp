@@ -233,8 +233,13 @@ llama_context * llama_init_from_model(llama_model * model, llama_context_params 
     const int n_blocks = (int) ((c->params.n_ctx + c->block_size - 1) / c->block_size + c->params.n_seq_max);
     c->kv.reset(new jib::PagedKv(n_blocks, c->block_size, (int) c->params.n_seq_max));
     std::string err;
-    if (!jib::PyBridge::call("create_context", &c->py, &err, "(Liiii)", model->py, n_blocks, c->block_size,
-                             c->params.presample_count, (int) c->params.n_ctx)) {
+    // RoPE overrides of the context parameters (0 / negative = keep the model's values)
+    char rope[160];
+    snprintf(rope, sizeof(rope), "{\"freq_base\":%.9g,\"freq_scale\":%.9g,\"attn_factor\":%.9g,\"orig_ctx\":%u,\"scaling_type\":%d}",
+             (double) params.rope_freq_base, (double) params.rope_freq_scale, (double) params.yarn_attn_factor, params.yarn_orig_ctx,
+             (int) params.rope_scaling_type);
+    if (!jib::PyBridge::call("create_context", &c->py, &err, "(Liiiis)", model->py, n_blocks, c->block_size,
+                             c->params.presample_count, (int) c->params.n_ctx, rope)) {
         log_err("llama_init_from_model", err);
         return nullptr;
     }

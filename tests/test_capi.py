@@ -504,3 +504,24 @@ def test_kv_overrides_change_the_loaded_hyperparameters(L, gguf_path):
     same = first_logits({"deepseek2.expert_used_count": 2})       # the file's own value
     one = first_logits({"deepseek2.expert_used_count": 1})
     assert base == same and base != one
+
+
+def test_context_rope_overrides(L, gguf_path):
+    """llama_context_params RoPE fields: the defaults keep the model's values; a different frequency base changes the
+    positions' rotation and therefore the logits of every token after the first."""
+    def logits(freq_base):
+        mp = L.llama_model_default_params()
+        mp.n_gpu_layers = 0
+        m = L.llama_model_load_from_file(gguf_path.encode(), mp)
+        cp = L.llama_context_default_params()
+        cp.n_ctx, cp.n_batch, cp.n_seq_max, cp.rope_freq_base = 128, 32, 1, freq_base
+        ctx = L.llama_init_from_model(m, cp)
+        toks = (capi.llama_token * 5)(11, 22, 33, 44, 55)
+        assert L.llama_decode(ctx, L.llama_batch_get_one(toks, 5), False) == 0
+        lg = L.llama_get_logits_ith(ctx, -1)
+        out = [lg.values[i] for i in range(16)]
+        L.llama_free(ctx)
+        L.llama_model_free(m)
+        return out
+    assert logits(0.0) == logits(10000.0)          # 10000 is the file's own base
+    assert logits(0.0) != logits(500000.0)
