@@ -109,6 +109,11 @@ class DeepSeek2Model:
         self.out_device = self.layer_dev[-1]
         self._cur_dev = self.device
         self._uploaders = {}
+        # Debug tap, the counterpart of the reference's per-node eval callback (cb_eval, include/llama.h:563-564;
+        # ggml/src/ggml-backend.cpp:1543-1580): when set, called as tensor_hook(name, tensor) with the block outputs of
+        # every layer ("blk.3.attn_out", "blk.3.ffn_inp", "blk.3.ffn_out") and "result_norm" / "result_output".  The engine
+        # runs eagerly while a hook is installed (a hook cannot run inside a captured graph).
+        self.tensor_hook = None
         self.ep = ep                      # all-to-all dispatcher (data-parallel attention + expert parallelism)
         self.block_size = block_size
         if spec.dp_attention:
@@ -408,11 +413,18 @@ class DeepSeek2Model:
             y = self._row_parallel(a, L.w_o, x)
             g, _ = ops.rmsnorm(y, L.ffn_norm, hp.rms_eps)
             x = self._mlp(L, g, y)
+            if self.tensor_hook is not None:
+                self.tensor_hook(f"blk.{il}.attn_out", a)
+                self.tensor_hook(f"blk.{il}.ffn_inp", y)
+                self.tensor_hook(f"blk.{il}.ffn_out", x)
             if nvtx:
                 torch.cuda.nvtx.range_pop()
         xo = ops.select_rows(x, batch.out_rows) if batch.out_rows is not None else x
         xo, _ = ops.rmsnorm(xo, self.out_norm, hp.rms_eps)
         logits = ops.linear(xo, self.w_out, out_dtype=torch.float32)
+        if self.tensor_hook is not None:
+            self.tensor_hook("result_norm", xo)
+            self.tensor_hook("result_output", logits)
         if self.split and self.device.type == "cuda":
             torch.cuda.set_device(self.device)
         return logits

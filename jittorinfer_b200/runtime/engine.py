@@ -379,7 +379,8 @@ class LLMEngine:
             self._copy_blocks(src, dst)
         states = [self.requests[int(r)] for r in self.sched.out_reqs(n_out)] if n_out else []
         mode = "greedy" if all(s.sampler is None for s in states) else "topk"
-        use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets)
+        use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets) \
+            and getattr(self.model, "tensor_hook", None) is None
         if use_graph and self.dp:
             # ranks capture in lockstep during warmup() only: a capture on first use would run collectives alone
             use_graph = (next(b for b in self.cfg.graph_buckets if b >= n_seqs), mode) in self._graphs

@@ -157,3 +157,18 @@ def test_v3_shaped_paths_match_oracle(tmp_path):
     eng = build_engine(None, gguf_path=p, device="cpu", dtype=torch.float32, n_parallel=2, n_ctx_slot=256, n_batch=32)
     assert eng.hp.router_bias and eng.hp.expert_gating_func == "sigmoid" and eng.hp.n_layer_dense_lead == 2
     assert eng.generate([toks], SamplingParams(ignore_eos=True), max_new_tokens=8) == [OracleModel(hp, w).generate(toks, 8)]
+
+
+def test_tensor_hook_sees_every_block_output():
+    hp = preset("tiny-v2")
+    w = random_weights(hp, seed=0)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    seen = {}
+    m.tensor_hook = lambda name, t: seen.__setitem__(name, tuple(t.shape))
+    cache = torch.zeros(hp.n_layer, 2 * 64, hp.kv_row)
+    logits = m.forward(_batch([1, 2, 3, 4, 5], 0), cache)
+    names = [f"blk.{il}.{k}" for il in range(hp.n_layer) for k in ("attn_out", "ffn_inp", "ffn_out")] + ["result_norm", "result_output"]
+    assert list(seen) == names
+    assert seen["blk.0.ffn_out"] == (5, hp.n_embd) and seen["result_output"] == tuple(logits.shape)
+    m.tensor_hook = None
+    assert torch.equal(m.forward(_batch([1, 2, 3, 4, 5], 0), cache), logits)
