@@ -525,3 +525,16 @@ def test_context_rope_overrides(L, gguf_path):
         return out
     assert logits(0.0) == logits(10000.0)          # 10000 is the file's own base
     assert logits(0.0) != logits(500000.0)
+
+
+def test_example_program_builds_and_runs(gguf_path, tmp_path):
+    """examples/simple.c (tokenise, decode with the device top-k, sampler chain, detokenise) against the tiny model."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "simple")
+    subprocess.run(["gcc", "-std=c11", "-O1", "-Wall", "-Werror", "-I", os.path.join(build.CSRC, "include"),
+                    os.path.join(root, "examples", "simple.c"), "-o", exe, f"-L{build.LIBDIR}", "-lllama", f"-Wl,-rpath,{build.LIBDIR}"],
+                   check=True)
+    env = dict(os.environ, JITTORINFER_PYTHON=sys.executable)
+    r = subprocess.run([exe, gguf_path, "hello there", "6", "0"], capture_output=True, text=True, timeout=600, env=env, errors="replace")
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "eval time" in r.stderr and len(r.stdout) >= 1
