@@ -172,3 +172,22 @@ def test_tensor_hook_sees_every_block_output():
     assert seen["blk.0.ffn_out"] == (5, hp.n_embd) and seen["result_output"] == tuple(logits.shape)
     m.tensor_hook = None
     assert torch.equal(m.forward(_batch([1, 2, 3, 4, 5], 0), cache), logits)
+
+
+def test_engine_under_kv_pressure_preempts_and_still_matches_oracle():
+    """More requests than the cache can hold at once, with defragmentation on: sequences are preempted (youngest first),
+    recomputed later, blocks are compacted -- and every request still produces exactly the oracle's tokens."""
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    # 10 blocks of 64 tokens for 6 slots of up to 256 tokens: at most two or three long sequences fit together
+    eng = LLMEngine(m, EngineConfig(n_ctx=640, n_batch=96, n_parallel=6, n_ctx_slot=256, defrag_thold=0.05))
+    g = torch.Generator().manual_seed(11)
+    lens = (150, 90, 170, 40, 120, 60, 200, 30)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in lens]
+    outs = eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=24)
+    o = OracleModel(hp, w)
+    assert outs == [o.generate(p, 24) for p in prompts]
+    st = eng.sched.stats()
+    assert st["preemptions"] >= 1 and st["finished"] == len(prompts)
+    assert eng.kv.check() and eng.kv.used_blocks <= eng.kv.n_blocks
