@@ -117,3 +117,41 @@ def test_generate_cli(capsys):
     out = json.loads(capsys.readouterr().out)
     assert [len(c["tokens"]) for c in out["completions"]] == [5, 5] and out["timing"]["generated_tokens"] == 10
     assert generate.main(["--device", "cpu"]) == 2
+
+
+def test_clients_that_disconnect_free_their_slots(server):
+    """Streaming clients that go away mid-generation: the server cancels their requests (reference: server.cpp:1216-1220),
+    the slots return to idle, and requests that stayed connected complete normally."""
+    import http.client
+    import concurrent.futures as cf
+    import time
+    url, ctx = server
+    host, port = url.replace("http://", "").split(":")
+
+    def quitter(i):
+        c = http.client.HTTPConnection(host, int(port), timeout=60)
+        body = json.dumps({"prompt": f"quit early {i}", "max_tokens": 400, "temperature": 0, "ignore_eos": True, "stream": True})
+        c.request("POST", "/v1/completions", body=body, headers={"Content-Type": "application/json"})
+        r = c.getresponse()
+        r.read(40)                      # the first bytes of the stream, then hang up
+        c.close()
+        return True
+
+    def stayer(i):
+        return _post(url + "/v1/completions", {"prompt": f"stay {i}", "max_tokens": 12, "temperature": 0, "ignore_eos": True})
+
+    with cf.ThreadPoolExecutor(8) as ex:
+        q = [ex.submit(quitter, i) for i in range(4)]
+        s = [ex.submit(stayer, i) for i in range(4)]
+        assert all(f.result() for f in q)
+        done = [f.result() for f in s]
+    assert all(d["usage"]["completion_tokens"] == 12 for d in done)
+    deadline = time.time() + 30
+    while time.time() < deadline:
+        slots = json.loads(urllib.request.urlopen(url + "/slots", timeout=10).read())
+        if all(sl["state"] == "IDLE" for sl in slots) and not ctx.streams:
+            break
+        time.sleep(0.1)
+    assert all(sl["state"] == "IDLE" for sl in slots) and not ctx.streams
+    assert ctx.engine.kv.check()
+    assert _post(url + "/v1/completions", {"prompt": "after", "max_tokens": 3, "temperature": 0, "ignore_eos": True})["usage"]["completion_tokens"] == 3
