@@ -79,6 +79,8 @@ JIB_EXPORT int jib_moe_gate(const void * g, const float * w_router, const float 
 // Stable counting sort of the (token, k) pairs by local expert. dest[t*k+j] = sorted row or -1 (not local).
 JIB_EXPORT int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
                                void * stream);
+JIB_EXPORT int jib_moe_permute_multi(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
+                                     int * tmp, void * stream);
 JIB_EXPORT int jib_moe_combine(const void * y, const int * dest, const float * wts, const void * shared, const void * residual,
                                void * out, int T, int k, int d, void * stream);
 

@@ -217,6 +217,93 @@ __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restric
     }
 }
 
+// ---- the same sort for large n (prefill) on many CTAs: histogram per 1024-pair chunk, scan, stable scatter ----------
+// tmp: int[n_chunks][E_local], chunk c covers pairs [c*1024, (c+1)*1024).
+constexpr int PERM_CHUNK = 1024;
+
+__global__ void __launch_bounds__(PERM_CHUNK) permute_count_kernel(const int * __restrict__ ids, int n, int expert_base, int E_local,
+                                                                   int * __restrict__ tmp) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ int hist[MAX_E];
+    for (int e = threadIdx.x; e < E_local; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PERM_CHUNK + threadIdx.x;
+    if (i < n) {
+        const int le = ids[i] - expert_base;
+        if (le >= 0 && le < E_local) atomicAdd(&hist[le], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E_local; e += blockDim.x) tmp[(size_t) blockIdx.x * E_local + e] = hist[e];
+}
+
+// One CTA: tmp[c][e] becomes the first sorted row of chunk c's pairs of expert e; seg[e] the expert's first row.
+__global__ void __launch_bounds__(MAX_E) permute_scan_kernel(int * __restrict__ tmp, int n_chunks, int E_local, int n, int * __restrict__ seg,
+                                                            int * __restrict__ src_token) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ int total[MAX_E + 1];
+    const int e = threadIdx.x;
+    int acc = 0;
+    if (e < E_local) {
+        for (int c = 0; c < n_chunks; ++c) {
+            const int v = tmp[(size_t) c * E_local + e];
+            tmp[(size_t) c * E_local + e] = acc;       // rows of expert e in earlier chunks
+            acc += v;
+        }
+        total[e] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int x = 0; x < E_local; ++x) { const int v = total[x]; total[x] = run; run += v; }
+        total[E_local] = run;
+    }
+    __syncthreads();
+    if (e < E_local) {
+        seg[e] = total[e];
+        for (int c = 0; c < n_chunks; ++c) tmp[(size_t) c * E_local + e] += total[e];
+    }
+    if (threadIdx.x == 0) seg[E_local] = total[E_local];
+    for (int i = total[E_local] + threadIdx.x; i < n; i += blockDim.x) src_token[i] = -1;      // rows no local expert owns
+}
+
+__global__ void __launch_bounds__(PERM_CHUNK) permute_scatter_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
+                                                                     const int * __restrict__ tmp, int * __restrict__ src_token,
+                                                                     int * __restrict__ dest) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int warp_cnt[];              // [32 warps][E_local]: pairs of expert e in warp w, then their prefix over w
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int x = threadIdx.x; x < 32 * E_local; x += blockDim.x) warp_cnt[x] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PERM_CHUNK + threadIdx.x;
+    int le = -1;
+    if (i < n) {
+        le = ids[i] - expert_base;
+        if (le < 0 || le >= E_local) le = -1;
+    }
+    // lanes of this warp with the same expert: rank among them keeps the order of the pair indices
+    const unsigned same = __match_any_sync(0xffffffffu, le);
+    const int rank = __popc(same & ((1u << lane) - 1));
+    if (le >= 0 && rank == 0) warp_cnt[warp * E_local + le] = __popc(same);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E_local; e += blockDim.x) {      // exclusive prefix over the 32 warps
+        int run = 0;
+        for (int w = 0; w < 32; ++w) { const int v = warp_cnt[w * E_local + e]; warp_cnt[w * E_local + e] = run; run += v; }
+    }
+    __syncthreads();
+    if (i < n) {
+        if (le < 0) {
+            dest[i] = -1;
+        } else {
+            const int row = tmp[(size_t) blockIdx.x * E_local + le] + warp_cnt[warp * E_local + le] + rank;
+            dest[i] = row;
+            if (row < n) src_token[row] = i / k;
+        }
+    }
+}
+
 // out[t] = residual[t] + shared[t] + sum_j wts[t][j] * y[dest[t][j]]   (fp32 accumulate, bf16 out)
 __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
                                    const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
@@ -292,6 +379,22 @@ int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local,
     if (T <= 0) return 0;
     if (E_local > MAX_E) return JIB_E_ARG;
     JIB_LAUNCH((moe_permute_kernel), 1, 1024, 0, (cudaStream_t) stream, ids, T * k, k, expert_base, E_local, seg, src_token, dest);
+    return launched();
+}
+
+// Same contract as jib_moe_permute, for large n: three launches over ceil(n / 1024) CTAs.  tmp: device int[ceil(T*k/1024) * E_local].
+int jib_moe_permute_multi(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest, int * tmp,
+                          void * stream) {
+    if (T <= 0) return 0;
+    if (E_local > MAX_E || tmp == nullptr) return JIB_E_ARG;
+    const int n = T * k;
+    const int n_chunks = (n + PERM_CHUNK - 1) / PERM_CHUNK;
+    const size_t smem = (size_t) 32 * E_local * sizeof(int);
+    if (smem > 48 * 1024) return JIB_E_ARG;
+    JIB_LAUNCH((permute_count_kernel), n_chunks, PERM_CHUNK, 0, (cudaStream_t) stream, ids, n, expert_base, E_local, tmp);
+    JIB_LAUNCH((permute_scan_kernel), 1, MAX_E, 0, (cudaStream_t) stream, tmp, n_chunks, E_local, n, seg, src_token);
+    JIB_LAUNCH((permute_scatter_kernel), n_chunks, PERM_CHUNK, smem, (cudaStream_t) stream, ids, n, k, expert_base, E_local,
+               (const int *) tmp, src_token, dest);
     return launched();
 }
 

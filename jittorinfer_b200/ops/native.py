@@ -16,6 +16,11 @@ _lib = None
 _ws: Dict[int, "Workspace"] = {}
 launch_count = 0            # kernels launched through this module (bench.py reports it)
 
+# The multi-CTA expert sort has been cross-compiled and its algorithm checked against a stable sort on the host, but it
+# has not run on a GPU yet: off unless JIB_PERMUTE_MULTI=1.
+PERMUTE_MULTI = os.environ.get("JIB_PERMUTE_MULTI", "0") == "1"
+PERMUTE_MULTI_MIN = 4096
+
 ERRORS = {-1: "unsupported shape/argument", -2: "pointer or stride not 16-byte aligned", -3: "driver entry point missing",
           -4: "tensor map encode failed", -5: "kernel launch failed", -6: "scratch too small for requested split"}
 
@@ -57,6 +62,7 @@ def load():
     sig("jib_gather_rows", vp, ip, vp, i, i, i, vp)
     sig("jib_moe_gate", vp, fp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, i, vp)
     sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
+    sig("jib_moe_permute_multi", ip, i, i, i, i, ip, ip, ip, ip, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
     sig("jib_mla_attention", vp, vp, ip, i, ip, ip, i, i, i, i, i, i, f, i, fp, fp, vp, vp)
     sig("jib_mla_combine", fp, fp, i, i, i, i, vp, vp)
@@ -327,6 +333,12 @@ def moe_permute(ids, expert_base, E_local):
     seg = torch.empty(E_local + 1, dtype=torch.int32, device=dev)
     src = torch.empty(T * k, dtype=torch.int32, device=dev)
     dest = torch.empty(T, k, dtype=torch.int32, device=dev)
+    if PERMUTE_MULTI and T * k >= PERMUTE_MULTI_MIN:
+        # large batches (prefill): histogram / scan / stable scatter over many CTAs instead of one CTA scanning every pair
+        tmp = torch.empty(((T * k + 1023) // 1024) * E_local, dtype=torch.int32, device=dev)
+        _ck(load().jib_moe_permute_multi(ids.data_ptr(), T, k, expert_base, E_local, seg.data_ptr(), src.data_ptr(), dest.data_ptr(),
+                                         tmp.data_ptr(), _stream()), "moe_permute_multi")
+        return seg, src, dest
     _ck(load().jib_moe_permute(ids.data_ptr(), T, k, expert_base, E_local, seg.data_ptr(), src.data_ptr(), dest.data_ptr(),
                                _stream()), "moe_permute")
     return seg, src, dest

@@ -214,3 +214,22 @@ def test_kv_block_copy(nat):
     nat.kv_block_copy(cache, src, dst, bs)
     ref.kv_block_copy(exp, src, dst, bs)
     assert torch.equal(cache, exp)
+
+
+@pytest.mark.skipif(__import__("os").environ.get("JIB_PERMUTE_MULTI", "") != "1",
+                    reason="the multi-CTA expert sort has not run on a GPU yet: set JIB_PERMUTE_MULTI=1 to try it")
+@pytest.mark.parametrize("T,k,E", [(1024, 6, 64), (2048, 8, 66), (700, 6, 160)])
+def test_moe_permute_multi_cta(nat, T, k, E):
+    """With JIB_PERMUTE_MULTI=1 batches of 4096 pairs and more take the histogram / scan / scatter kernels: same stable
+    sort by expert as the single-CTA kernel."""
+    ids = torch.randint(0, E, (T, k), device="cuda", dtype=torch.int32)
+    assert nat.PERMUTE_MULTI and T * k >= nat.PERMUTE_MULTI_MIN
+    seg, src, dest = nat.moe_permute(ids, 0, E)
+    flat = ids.flatten().long().cpu()
+    order = torch.sort(flat, stable=True).indices
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(T * k)
+    assert torch.equal(dest.flatten().cpu().long(), inv)
+    assert torch.equal(src.cpu().long(), order // k)
+    counts = torch.bincount(flat, minlength=E)
+    assert torch.equal(seg.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]))

@@ -86,3 +86,51 @@ def test_scheduler_prefix_reuse_and_preemption():
     sched.add(4, list(range(60, 120)), max_new=60)
     out = _run(sched, io, lambda rid: 5)
     assert len(out[3]) == 60 and len(out[4]) == 60 and sched.stats()["preemptions"] >= 1 and kv.check()
+
+
+def test_multi_cta_expert_sort_algorithm_matches_a_stable_sort():
+    """Host restatement of the three-kernel expert sort used for large batches (per-chunk histogram, scan over chunks and
+    experts, scatter with the rank inside the warp and the prefix over the warps of the chunk): the result must be the
+    stable sort by expert that the single-CTA kernel produces, including pairs of experts this rank does not own."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    for n, k, E_total, base, E_local in ((5000, 6, 64, 0, 64), (16384, 8, 66, 0, 66), (3000, 6, 160, 40, 20), (1024, 2, 8, 0, 8)):
+        ids = rng.integers(0, E_total, size=n).astype(np.int64)
+        le = ids - base
+        le[(le < 0) | (le >= E_local)] = -1
+        chunk = 1024
+        n_chunks = (n + chunk - 1) // chunk
+        tmp = np.zeros((n_chunks, E_local), dtype=np.int64)
+        for c in range(n_chunks):                                         # permute_count_kernel
+            part = le[c * chunk:(c + 1) * chunk]
+            for e in part[part >= 0]:
+                tmp[c, e] += 1
+        total = tmp.sum(0)                                                # permute_scan_kernel
+        tmp = np.cumsum(tmp, axis=0) - tmp
+        seg = np.concatenate([[0], np.cumsum(total)])
+        tmp += seg[:-1][None, :]
+        dest = np.full(n, -1, dtype=np.int64)
+        src = np.full(n, -1, dtype=np.int64)
+        for c in range(n_chunks):                                         # permute_scatter_kernel
+            warp_cnt = np.zeros((32, E_local), dtype=np.int64)
+            ranks = {}
+            for t in range(chunk):
+                i = c * chunk + t
+                if i >= n or le[i] < 0:
+                    continue
+                w, lane = divmod(t, 32)
+                lanes = [l for l in range(32) if c * chunk + w * 32 + l < n and le[c * chunk + w * 32 + l] == le[i]]
+                ranks[i] = (w, lanes.index(lane))
+                warp_cnt[w, le[i]] = len(lanes)
+            warp_off = np.cumsum(warp_cnt, axis=0) - warp_cnt
+            for i, (w, r) in ranks.items():
+                row = tmp[c, le[i]] + warp_off[w, le[i]] + r
+                dest[i] = row
+                src[row] = i // k
+        owned = np.nonzero(le >= 0)[0]
+        order = owned[np.argsort(le[owned], kind="stable")]
+        want = np.full(n, -1, dtype=np.int64)
+        want[order] = np.arange(len(order))
+        assert np.array_equal(dest, want)
+        assert np.array_equal(src[:len(order)], order // k) and np.all(src[len(order):] == -1)
+        assert seg[-1] == len(order)
