@@ -1,0 +1,216 @@
+"""Interleaving model of the peer-memory protocols (no GPU, no processes).
+
+The fused collectives never reset a flag and reuse two buffer halves, so their safety rests on an ordering argument: a
+rank can run ahead of the slowest rank only until its next wait, and that is never far enough to overwrite data somebody
+has yet to read.  Here every rank is a little program of single memory operations (store a tagged value into a peer's
+buffer, store a flag, wait for flags, load and check a tag) and a scheduler runs the ranks in random orders -- thousands
+of interleavings per protocol, including "one rank races ahead as far as it can".  A load that sees a value written for
+another call site or another step is a protocol bug.  The programs mirror the kernels:
+
+* one-shot all-reduce (comm_fused.cu / the GEMM epilogue, ``args.ar``): push to every peer, signal, wait, reduce;
+* two-shot all-reduce and its reduce-scatter form (partials to a tile owner, delivery to all ranks / to the row owner);
+* expert-parallel all-to-all (ep_alltoall.cu): counts, rows, returned outputs, three flag phases per call site;
+* the sequence-parallel layer (all-gather, GEMM+reduce-scatter, all-gather, reduce-scatter) with the gather buffer
+  indexed by ``(site >> 1) & 1`` and the reduce buffers by ``site & 1``.
+
+What the model cannot show is memory ordering inside one GPU (release/acquire, proxy fences): that is by construction
+in the kernels (``st.release.sys`` after ``__threadfence_system``, ``ld.acquire.sys`` before the loads).
+"""
+import random
+
+import pytest
+
+
+class Sim:
+    """Shared memory = dict; ranks = generators yielding ("store", key, value) | ("wait", fn) | ("check", key, value)."""
+
+    def __init__(self, programs, seed, bias=None):
+        self.mem = {}
+        self.programs = programs
+        self.pending = [None] * len(programs)
+        self.done = [False] * len(programs)
+        self.rng = random.Random(seed)
+        self.bias = bias                    # rank that is scheduled whenever it can run (races ahead)
+        self.steps = 0
+
+    def _next(self, r):
+        if self.pending[r] is None and not self.done[r]:
+            try:
+                self.pending[r] = next(self.programs[r])
+            except StopIteration:
+                self.done[r] = True
+        return self.pending[r]
+
+    def _runnable(self, r):
+        op = self._next(r)
+        if op is None:
+            return False
+        return op[0] != "wait" or op[1](self.mem)
+
+    def run(self, max_steps=2_000_000):
+        n = len(self.programs)
+        while not all(self.done):
+            ready = [r for r in range(n) if self._runnable(r)]
+            if not ready and all(self.done):
+                break
+            assert ready, "deadlock: every rank waits"
+            if self.bias is not None and self.bias in ready and self.rng.random() < 0.9:
+                r = self.bias
+            else:
+                r = self.rng.choice(ready)
+            op = self.pending[r]
+            self.pending[r] = None
+            if op[0] == "store":
+                self.mem[op[1]] = op[2]
+            elif op[0] == "check":
+                got = self.mem.get(op[1])
+                assert got == op[2], f"rank {r}: {op[1]} holds {got}, expected {op[2]}"
+            self.steps += 1
+            assert self.steps < max_steps
+
+
+def parity(site, n_sites, epoch):
+    return (site + (epoch % 2) * (n_sites & 1)) & 1
+
+
+# ---- programs ---------------------------------------------------------------------------------------------------------
+def one_shot(rank, world, n_sites, n_epochs):
+    for epoch in range(1, n_epochs + 1):
+        for site in range(n_sites):
+            par = parity(site, n_sites, epoch)
+            for p in range(world):
+                yield ("store", ("recv", p, par, rank), (epoch, site))
+            for p in range(world):
+                yield ("store", ("flag", p, site, rank), epoch)
+            yield ("wait", lambda m, s=site, e=epoch: all(m.get(("flag", rank, s, src)) == e for src in range(world)))
+            for src in range(world):
+                yield ("check", ("recv", rank, par, src), (epoch, site))
+
+
+def two_shot(rank, world, n_sites, n_epochs, n_tiles=3, rows_per_rank=0):
+    """rows_per_rank > 0: reduce-scatter form -- tile t's result is delivered to rank (t % world) only ("row owner"),
+    which is the only one that reads it; every rank still waits for the owner's delivery flag."""
+    for epoch in range(1, n_epochs + 1):
+        for site in range(n_sites):
+            par = site & 1
+            for tile in range(n_tiles):
+                owner = (tile + site) % world
+                yield ("store", ("recv2", owner, par, tile, rank), (epoch, site))
+                yield ("store", ("flag", owner, site, tile, rank), epoch)
+                if rank == owner:
+                    yield ("wait", lambda m, s=site, t=tile, e=epoch: all(m.get(("flag", rank, s, t, src)) == e for src in range(world)))
+                    for src in range(world):
+                        yield ("check", ("recv2", rank, par, tile, src), (epoch, site))
+                    targets = [tile % world] if rows_per_rank else range(world)
+                    for p in targets:
+                        yield ("store", ("out2", p, par, tile), (epoch, site))
+                    for p in range(world):
+                        yield ("store", ("flag2", p, site, tile), epoch)
+                yield ("wait", lambda m, s=site, t=tile, e=epoch: m.get(("flag2", rank, s, t)) == e)
+            # the consumer (next kernel on the stream) reads the result after the whole kernel
+            for tile in range(n_tiles):
+                if not rows_per_rank or tile % world == rank:
+                    yield ("check", ("out2", rank, par, tile), (epoch, site))
+
+
+def ep_layer(rank, world, n_sites, n_epochs):
+    for epoch in range(1, n_epochs + 1):
+        for site in range(n_sites):
+            par = parity(site, n_sites, epoch)
+            tag = (epoch, site)
+            for p in range(world):                                   # plan: counts to everybody
+                yield ("store", ("counts", p, par, rank), tag)
+            for p in range(world):
+                yield ("store", ("f0", p, site, rank), epoch)
+            yield ("wait", lambda m, s=site, e=epoch: all(m.get(("f0", rank, s, src)) == e for src in range(world)))
+            for src in range(world):
+                yield ("check", ("counts", rank, par, src), tag)
+            for p in range(world):                                   # push: my rows into the owners' buffers
+                yield ("store", ("xrecv", p, par, rank), tag)
+            for p in range(world):
+                yield ("store", ("f1", p, site, rank), epoch)
+            yield ("wait", lambda m, s=site, e=epoch: all(m.get(("f1", rank, s, src)) == e for src in range(world)))
+            for src in range(world):                                 # expert GEMMs read what arrived ...
+                yield ("check", ("xrecv", rank, par, src), tag)
+            for src in range(world):                                 # ... and store the results into the sources
+                yield ("store", ("yret", src, par, rank), tag)
+            for p in range(world):                                   # combine: signal, wait, read
+                yield ("store", ("f2", p, site, rank), epoch)
+            yield ("wait", lambda m, s=site, e=epoch: all(m.get(("f2", rank, s, src)) == e for src in range(world)))
+            for owner in range(world):
+                yield ("check", ("yret", rank, par, owner), tag)
+
+
+def sp_layers(rank, world, n_layers, n_epochs):
+    """Per layer: all-gather (site 4l), GEMM+reduce-scatter (4l+1), all-gather (4l+2), reduce-scatter (4l+3)."""
+    def gather(site, epoch):
+        par = (site >> 1) & 1
+        for p in range(world):
+            yield ("store", ("xg", p, par, rank), (epoch, site))
+        for p in range(world):
+            yield ("store", ("f3", p, site, rank), epoch)
+        yield ("wait", lambda m: all(m.get(("f3", rank, site, src)) == epoch for src in range(world)))
+        for src in range(world):
+            yield ("check", ("xg", rank, par, src), (epoch, site))
+
+    for epoch in range(1, n_epochs + 1):
+        for layer in range(n_layers):
+            for which, site in enumerate(range(4 * layer, 4 * layer + 4)):
+                if which % 2 == 0:
+                    yield from gather(site, epoch)
+                else:
+                    par = site & 1
+                    owner = site % world                         # one tile per call site, its owner rotates
+                    yield ("store", ("recv2", owner, par, rank), (epoch, site))
+                    yield ("store", ("flag", owner, site, rank), epoch)
+                    if rank == owner:
+                        yield ("wait", lambda m, s=site, e=epoch: all(m.get(("flag", rank, s, src)) == e for src in range(world)))
+                        for src in range(world):
+                            yield ("check", ("recv2", rank, par, src), (epoch, site))
+                        for p in range(world):                   # each rank's rows of the tile
+                            yield ("store", ("out2", p, par), (epoch, site))
+                        for p in range(world):
+                            yield ("store", ("flag2", p, site), epoch)
+                    yield ("wait", lambda m, s=site, e=epoch: m.get(("flag2", rank, s)) == e)
+                    yield ("check", ("out2", rank, par), (epoch, site))
+
+
+PROTOCOLS = {
+    "one_shot_even_sites": lambda r, w: one_shot(r, w, 4, 3),
+    "one_shot_odd_sites": lambda r, w: one_shot(r, w, 3, 4),
+    "two_shot": lambda r, w: two_shot(r, w, 4, 3),
+    "two_shot_reduce_scatter": lambda r, w: two_shot(r, w, 4, 3, rows_per_rank=1),
+    "ep_all_to_all_even_sites": lambda r, w: ep_layer(r, w, 2, 3),
+    "ep_all_to_all_odd_sites": lambda r, w: ep_layer(r, w, 3, 4),
+    "sequence_parallel_layers": lambda r, w: sp_layers(r, w, 2, 3),
+}
+
+
+@pytest.mark.parametrize("name", sorted(PROTOCOLS))
+@pytest.mark.parametrize("world", [2, 4])
+def test_no_interleaving_reads_stale_or_overwritten_data(name, world):
+    for seed in range(60):
+        Sim([PROTOCOLS[name](r, world) for r in range(world)], seed).run()
+    for fast in range(world):                                   # one rank always runs when it can
+        for seed in range(10):
+            Sim([PROTOCOLS[name](r, world) for r in range(world)], 1000 + seed, bias=fast).run()
+
+
+def test_the_model_catches_a_protocol_without_double_buffering():
+    """Sanity of the tool itself: with one buffer half instead of two, a rank that races ahead overwrites a slot that a
+    slower rank has not reduced yet -- some interleaving must trip the check."""
+    def single_buffer(rank, world, n_sites, n_epochs):
+        for op in one_shot(rank, world, n_sites, n_epochs):
+            if op[0] in ("store", "check") and op[1][0] == "recv":
+                key = list(op[1])
+                key[2] = 0                                       # every call site uses half 0
+                op = (op[0], tuple(key), op[2])
+            yield op
+
+    tripped = 0
+    for seed in range(200):
+        try:
+            Sim([single_buffer(r, 2, 4, 3) for r in range(2)], seed, bias=seed % 2).run()
+        except AssertionError:
+            tripped += 1
+    assert tripped > 0
