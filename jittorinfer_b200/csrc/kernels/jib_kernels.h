@@ -75,7 +75,7 @@ JIB_EXPORT int jib_gather_rows(const void * x, const int * src_row, void * out, 
 // n_shared columns name the shared experts (ids E, E+1, ...; weight 1) so that they run in the grouped GEMMs.
 JIB_EXPORT int jib_moe_gate(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int T,
                             int d, int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, int n_shared,
-                            void * stream);
+                            int group_top2, void * stream);
 // Stable counting sort of the (token, k) pairs by local expert. dest[t*k+j] = sorted row or -1 (not local).
 JIB_EXPORT int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
                                void * stream);

@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __r
 // One warp per token: softmax/sigmoid over the logits, optional group-limited masking, k rounds of arg-max.
 __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__ logits, const float * __restrict__ bias,
                                                       int * __restrict__ ids, float * __restrict__ wts, int E, int k, int n_group,
-                                                      int topk_group, float scale, int norm, int sigmoid, int n_shared) {
+                                                      int topk_group, float scale, int norm, int sigmoid, int n_shared,
+                                                      int group_top2) {
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ float prob[MAX_E];
@@ -118,9 +119,13 @@ __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__
         if (n_group > 1) {
             const int gs = E / n_group;
             if (lane < n_group) {
-                float m = -FLT_MAX;
-                for (int j = 0; j < gs; ++j) m = fmaxf(m, sel[lane * gs + j]);
-                gscore[lane] = m;
+                // a group's score: its best expert (DeepSeek-V2) or the sum of its two best (DeepSeek-V3)
+                float m = -FLT_MAX, m2 = -FLT_MAX;
+                for (int j = 0; j < gs; ++j) {
+                    const float v = sel[lane * gs + j];
+                    if (v > m) { m2 = m; m = v; } else if (v > m2) { m2 = v; }
+                }
+                gscore[lane] = (group_top2 && gs >= 2) ? m + m2 : m;
             }
             __syncwarp();
             // keep the topk_group best groups (ties -> lower group id): rank of my group
@@ -366,12 +371,13 @@ JIB_BC_DEFINE_SETTER(moe)
 extern "C" {
 
 int jib_moe_gate(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int T, int d,
-                 int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, int n_shared, void * stream) {
+                 int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, int n_shared, int group_top2,
+                 void * stream) {
     if (T <= 0) return 0;
     if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 4 || d > GATE_MAXV * GATE_NT * 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
     JIB_LAUNCH((router_logits_kernel), dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, logits, T, d, E);
     if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;
-    JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared);
+    JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2);
     return launched();
 }
 

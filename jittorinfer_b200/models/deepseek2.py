@@ -310,7 +310,7 @@ class DeepSeek2Model:
             return self._row_parallel(hmid, L.w_down, residual)
         ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
                                 hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid",
-                                L.n_shared_merged or 0)
+                                L.n_shared_merged or 0, hp.group_score_top2)
         if self.spec.dp_attention and self.spec.sharded:
             shared = None
             if L.w_gate_sh is not None:
@@ -357,7 +357,8 @@ class DeepSeek2Model:
             else:
                 g = comm.all_gather_rows(g_loc)
                 ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
-                                        hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid", 0)
+                                        hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid", 0,
+                                        hp.group_score_top2)
                 base = self.expert_base if self.spec.expert_parallel else 0
                 part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                                    L.w_down_sh, base)

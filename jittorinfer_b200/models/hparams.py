@@ -32,6 +32,7 @@ class DeepSeek2HParams:
     expert_weights_scale: float = 1.0
     expert_weights_norm: bool = False
     expert_gating_func: str = "softmax"   # or "sigmoid"
+    group_score_top2: bool = False        # group-limited routing scores a group by its two best experts (V3) instead of its best (V2)
     router_bias: bool = False             # per-expert selection bias (blk.N.exp_probs_b.bias; DeepSeek-V3-shaped checkpoints)
     n_group: int = 1                  # group-limited routing (DeepSeek-V2: 8)
     topk_group: int = 1               # groups kept per token (DeepSeek-V2: 3)
@@ -192,6 +193,7 @@ class DeepSeek2HParams:
         hp.expert_weights_norm = bool(g("expert_weights_norm", False))
         gf = int(g("expert_gating_func", 1))
         hp.expert_gating_func = "sigmoid" if gf == 2 else "softmax"
+        hp.group_score_top2 = gf == 2          # DeepSeek-V3 routing: sigmoid scores, groups ranked by their two best experts
         hp.n_group = int(g("expert_group_count", 1))
         hp.topk_group = int(g("expert_group_used_count", 1))
         st = g("rope.scaling.type", "none")
@@ -243,13 +245,13 @@ def preset(name: str) -> DeepSeek2HParams:
             n_expert=16, n_expert_used=4, n_expert_shared=1, q_lora_rank=96, kv_lora_rank=64,
             qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, n_ctx_train=4096,
             n_group=4, topk_group=2, expert_weights_scale=2.5, expert_weights_norm=True, expert_gating_func="sigmoid",
-            router_bias=True, bos_id=0, eos_id=1)
+            router_bias=True, group_score_top2=True, bos_id=0, eos_id=1)
     if name in ("v3", "deepseek-v3"):
         # DeepSeek-V3 / R1 shape (671B): the reference recognises it by layer count (src/llama-model.cpp:1203-1215).
         # 1.3 TB of bf16 weights: shape only, for sizing and for checkpoints sharded over more memory than one node has.
         return DeepSeek2HParams(
             n_vocab=129280, n_embd=7168, n_layer=61, n_head=128, n_layer_dense_lead=3, n_ff=18432, n_ff_exp=2048,
             n_expert=256, n_expert_used=8, n_expert_shared=1, expert_weights_scale=2.5, expert_weights_norm=True,
-            expert_gating_func="sigmoid", router_bias=True, n_group=8, topk_group=4, q_lora_rank=1536,
+            expert_gating_func="sigmoid", router_bias=True, group_score_top2=True, n_group=8, topk_group=4, q_lora_rank=1536,
             n_ctx_train=163840, rope_orig_ctx=4096)
     raise KeyError(name)

@@ -69,7 +69,7 @@ def gate_topk(hp: DeepSeek2HParams, logits: torch.Tensor, bias: Optional[torch.T
     if hp.n_group > 1:
         T, E = sel.shape
         g = sel.view(T, hp.n_group, E // hp.n_group)
-        gscore = g.max(dim=-1).values
+        gscore = g.topk(2, dim=-1).values.sum(-1) if hp.group_score_top2 and g.shape[-1] >= 2 else g.max(dim=-1).values
         keep = torch.topk(gscore, hp.topk_group, dim=-1, sorted=False).indices
         mask = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, keep, True)
         sel = sel.masked_fill(~mask[:, :, None].expand_as(g).reshape(T, E), float("-inf"))

@@ -60,7 +60,7 @@ def load():
     sig("jib_topk", fp, fp, ip, i, i, i, vp)
     sig("jib_kv_block_copy", vp, ll, i, ip, ip, i, i, vp)
     sig("jib_gather_rows", vp, ip, vp, i, i, i, vp)
-    sig("jib_moe_gate", vp, fp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, i, vp)
+    sig("jib_moe_gate", vp, fp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, i, i, vp)
     sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
     sig("jib_moe_permute_multi", ip, i, i, i, i, ip, ip, ip, ip, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
@@ -316,14 +316,14 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
 
 
 # ---- MoE -----------------------------------------------------------------------------------------
-def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0):
+def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False):
     T, d = g.shape
     E = w_router.shape[0]
     ids = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
     wts = torch.empty(T, k + n_shared, dtype=torch.float32, device=g.device)
     logits = torch.empty(T, E, dtype=torch.float32, device=g.device)
     _ck(load().jib_moe_gate(g.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, d,
-                            E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared, _stream()), "moe_gate")
+                            E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared, int(group_top2), _stream()), "moe_gate")
     return ids, wts
 
 

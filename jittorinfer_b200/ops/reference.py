@@ -140,7 +140,8 @@ def mla_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tens
 
 
 def moe_gate(g: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], k: int, n_group: int,
-             topk_group: int, scale: float, norm: bool, sigmoid: bool, n_shared: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+             topk_group: int, scale: float, norm: bool, sigmoid: bool, n_shared: int = 0,
+             group_top2: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Router matmul (fp32) + softmax/sigmoid + [group-limited] top-k + renorm/scale
     (src/llama-graph-ffn.cpp:145-197).  Returns ids [T,k] int32, weights [T,k] fp32."""
     logits = g.float() @ w_router.float().T
@@ -148,7 +149,8 @@ def moe_gate(g: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tenso
     sel = probs if bias is None else probs + bias.float()
     T, E = sel.shape
     if n_group > 1:
-        gs = sel.view(T, n_group, E // n_group).max(dim=-1).values
+        grouped = sel.view(T, n_group, E // n_group)
+        gs = grouped.topk(2, dim=-1).values.sum(-1) if group_top2 and E // n_group >= 2 else grouped.max(dim=-1).values
         order = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :topk_group]
         mask = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, order, True)
         sel = sel.masked_fill(~mask[:, :, None].expand(T, n_group, E // n_group).reshape(T, E), float("-inf"))
