@@ -237,6 +237,9 @@ class StagedUploader:
         """``t``: a CPU tensor.  Returns it on the device (converted to ``dtype`` there when given)."""
         if t.device.type != "cpu" or t.numel() * t.element_size() < self.min_bytes:
             return t.to(device=self.device, dtype=dtype or t.dtype).contiguous()
+        if self.device.type == "cuda" and self.device.index is not None and torch.cuda.current_device() != self.device.index:
+            with torch.cuda.device(self.device):             # events and copies must share the target device's stream
+                return self.upload(t, dtype)
         src = t.contiguous().view(-1).view(torch.uint8)
         out = torch.empty(t.shape, dtype=t.dtype, device=self.device)
         dst = out.view(-1).view(torch.uint8)
