@@ -170,6 +170,10 @@ class LLMEngine:
         self._idle_graph = None
         self.tracer = Tracer()            # JSON-lines step trace when JITTORINFER_TRACE names a file
         self._pressure = False            # free KV blocks held back by the kv_alloc fault site
+        from ..utils import graphdump
+        il = graphdump.requested_layer()  # LLAMA_PRINT_LAYER=<il>: the first step writes that layer's op graph as dot text
+        if il is not None:
+            graphdump.dump_on_first_step(self, il)
 
     # ------------------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:

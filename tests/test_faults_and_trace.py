@@ -250,3 +250,30 @@ def test_watchdog_fires_once_for_a_silent_rank():
     assert wd.fired and seen == [[0]]
     wd.stop()
     me.stop()
+
+
+def test_layer_graph_dump_as_dot(tmp_path, monkeypatch):
+    """LLAMA_PRINT_LAYER=<il>: the first engine step writes the op graph of that layer (the reference writes a dot file of
+    its graph-engine layer graph, src/llama-context-load-utils.cpp:154-162)."""
+    import torch
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.runtime.factory import build_engine
+    from jittorinfer_b200.runtime.sampling import SamplingParams
+    monkeypatch.setenv("LLAMA_PRINT_LAYER", "1")
+    monkeypatch.chdir(tmp_path)
+    eng = build_engine(preset("tiny"), device="cpu", dtype=torch.float32, n_parallel=2, n_ctx_slot=64, n_batch=32, cuda_graphs=False)
+    out = eng.generate([[3, 4, 5, 6, 7]], SamplingParams(ignore_eos=True), max_new_tokens=3)
+    assert len(out[0]) == 3
+    dot = (tmp_path / "jittorinfer_graph_1.dot").read_text()
+    assert dot.startswith("digraph forward {") and dot.rstrip().endswith("}")
+    for op in ("rmsnorm", "linear", "mla_qkv_post", "q_absorb", "mla_attention", "v_up", "moe_gate", "moe_ffn"):
+        assert op in dot, op
+    assert "embed_gather" not in dot.split("style=dashed")[0] or "blk 0" in dot       # layer 1 starts from layer 0's output
+    assert dot.count("->") >= 8
+    g = eng.graph_dump
+    layers = {n["layer"] for n in g.nodes}
+    assert layers == set(range(eng.hp.n_layer + 1))                                    # blocks + the output head
+    # the attention chain is connected: mla_attention reads what q_absorb wrote (through q_full)
+    ids = {n["id"]: n for n in g.nodes}
+    assert any(ids[a]["op"] == "q_absorb" and ids[b]["op"] == "mla_attention" for a, b in g.edges) or \
+        any(ids[a]["op"] == "mla_qkv_post" and ids[b]["op"] == "mla_attention" for a, b in g.edges)
