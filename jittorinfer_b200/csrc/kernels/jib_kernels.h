@@ -76,6 +76,12 @@ JIB_EXPORT int jib_gather_rows(const void * x, const int * src_row, void * out, 
 JIB_EXPORT int jib_moe_gate(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int T,
                             int d, int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, int n_shared,
                             int group_top2, void * stream);
+// jib_moe_gate + jib_moe_permute (over the k + n_shared id columns) in one launch, for T <= 64.  counter: one device int that is
+// zero between launches.
+JIB_EXPORT int jib_moe_route_fused(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts,
+                                   int * seg, int * src_token, int * dest, int * counter, int T, int d, int E, int k, int n_group,
+                                   int topk_group, float scale, int norm, int sigmoid, int n_shared, int group_top2, int expert_base,
+                                   int E_local, void * stream);
 // Stable counting sort of the (token, k) pairs by local expert. dest[t*k+j] = sorted row or -1 (not local).
 JIB_EXPORT int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
                                void * stream);

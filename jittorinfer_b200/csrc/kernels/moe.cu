@@ -309,6 +309,201 @@ __global__ void __launch_bounds__(PERM_CHUNK) permute_scatter_kernel(const int *
     }
 }
 
+// ---- decode batches (T <= 64): router logits, gating and the expert sort in ONE launch ------------------------------
+// grid (E), 256 threads.  CTA e computes the logits of expert e for all tokens (as router_logits_kernel does); the CTA
+// that finishes last (a counter that it also resets) then gates every token, one warp per token, and sorts the
+// (token, slot) pairs by local expert -- the work of moe_gate_kernel and moe_permute_kernel, whose bodies are repeated
+// here until this kernel has been checked on hardware.  Two launches fewer per MoE layer of a decode step.
+constexpr int ROUTE_MAX_T = 64;
+__global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
+                                                                  const float * __restrict__ bias, float * __restrict__ logits,
+                                                                  int * __restrict__ ids, float * __restrict__ wts, int * __restrict__ seg,
+                                                                  int * __restrict__ src_token, int * __restrict__ dest,
+                                                                  int * __restrict__ counter, int T, int d, int E, int k, int n_group,
+                                                                  int topk_group, float scale, int norm, int sigmoid, int n_shared,
+                                                                  int group_top2, int expert_base, int E_local) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    __shared__ float red[GATE_NT / 32][GATE_TG];
+    __shared__ int s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        const int e = blockIdx.x;
+        const int nv = d / 4;
+        const float4 * wr = (const float4 *) (w_router + (size_t) e * d);
+        float4 w[GATE_MAXV];
+#pragma unroll
+        for (int v = 0; v < GATE_MAXV; ++v) {
+            const int i = threadIdx.x + v * GATE_NT;
+            w[v] = i < nv ? wr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int t0 = 0; t0 < T; t0 += GATE_TG) {
+            float acc[GATE_TG];
+#pragma unroll
+            for (int j = 0; j < GATE_TG; ++j) acc[j] = 0.f;
+#pragma unroll
+            for (int v = 0; v < GATE_MAXV; ++v) {
+                const int i = threadIdx.x + v * GATE_NT;
+                if (i < nv) {
+#pragma unroll
+                    for (int j = 0; j < GATE_TG; ++j) {
+                        const int t = min(t0 + j, T - 1);
+                        const uint2 raw = *(const uint2 *) (g + (size_t) t * d + 4 * i);
+                        const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                        const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                        acc[j] += w[v].x * a.x + w[v].y * a.y + w[v].z * b.x + w[v].w * b.y;
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < GATE_TG; ++j) {
+                const float s = warp_sum(acc[j]);
+                if (lane == 0) red[warp][j] = s;
+            }
+            __syncthreads();
+            if (threadIdx.x < GATE_TG && t0 + threadIdx.x < T) {
+                float s = 0.f;
+#pragma unroll
+                for (int q = 0; q < GATE_NT / 32; ++q) s += red[q][threadIdx.x];
+                logits[(size_t) (t0 + threadIdx.x) * E + e] = s;
+            }
+            __syncthreads();
+        }
+    }
+    // ---- last CTA to finish carries on ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(counter, 1) == (int) gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    if (threadIdx.x == 0) *counter = 0;      // ready for the next launch
+    __threadfence();
+
+    // ---- gating: warp w takes tokens w, w + 8, ... ----
+    __shared__ float prob_s[GATE_NT / 32][MAX_E];
+    __shared__ float sel_s[GATE_NT / 32][MAX_E];
+    __shared__ float gscore_s[GATE_NT / 32][32];
+    float * prob = prob_s[warp];
+    float * sel = sel_s[warp];
+    float * gscore = gscore_s[warp];
+    const int ld = k + n_shared;
+    for (int t = warp; t < T; t += GATE_NT / 32) {
+        for (int e = lane; e < E; e += 32) prob[e] = __ldcg(logits + (size_t) t * E + e);     // written by other CTAs: from L2
+        __syncwarp();
+        float mx = -FLT_MAX;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = sigmoid ? 1.f / (1.f + expf(-prob[e])) : expf(prob[e] - mx);
+            prob[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) {
+            if (!sigmoid) prob[e] = prob[e] / sum;
+            sel[e] = prob[e] + (bias ? bias[e] : 0.f);
+        }
+        __syncwarp();
+        if (n_group > 1) {
+            const int gs = E / n_group;
+            if (lane < n_group) {
+                float m = -FLT_MAX, m2 = -FLT_MAX;
+                for (int j = 0; j < gs; ++j) {
+                    const float v = sel[lane * gs + j];
+                    if (v > m) { m2 = m; m = v; } else if (v > m2) { m2 = v; }
+                }
+                gscore[lane] = (group_top2 && gs >= 2) ? m + m2 : m;
+            }
+            __syncwarp();
+            if (lane < n_group) {
+                int rank = 0;
+                const float mine = gscore[lane];
+                for (int j = 0; j < n_group; ++j) rank += (gscore[j] > mine) || (gscore[j] == mine && j < lane);
+                if (rank >= topk_group)
+                    for (int j = 0; j < gs; ++j) sel[lane * gs + j] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        float wsum = 0.f;
+        for (int round = 0; round < k; ++round) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = sel[e];
+                if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (bi >= E) bi = 0;
+            if (lane == 0) {
+                ids[(size_t) t * ld + round] = bi;
+                wts[(size_t) t * ld + round] = prob[bi];
+                sel[bi] = -INFINITY;
+            }
+            wsum += prob[bi];
+            __syncwarp();
+        }
+        if (lane < k) {
+            float w = wts[(size_t) t * ld + lane];
+            if (norm) w /= wsum;
+            wts[(size_t) t * ld + lane] = w * scale;
+        } else if (lane < ld) {
+            ids[(size_t) t * ld + lane] = E + (lane - k);
+            wts[(size_t) t * ld + lane] = 1.f;
+        }
+        __syncwarp();
+    }
+    __syncthreads();         // ids of all tokens are written (and visible to the whole CTA)
+
+    // ---- stable counting sort of the n = T * ld pairs by local expert ----
+    __shared__ int count[MAX_E + 1];
+    __shared__ int offs[MAX_E + 1];
+    const int n = T * ld, nw = GATE_NT / 32;
+    for (int e = warp; e < E_local; e += nw) {
+        int c = 0;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < n && ids[i] - expert_base == e;
+            c += __popc(__ballot_sync(0xffffffffu, hit));
+        }
+        if (lane == 0) count[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < E_local; ++e) { offs[e] = acc; acc += count[e]; }
+        offs[E_local] = acc;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E_local; e += blockDim.x) seg[e] = offs[e];
+    for (int i = offs[E_local] + threadIdx.x; i < n; i += blockDim.x) src_token[i] = -1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int le = ids[i] - expert_base;
+        if (le < 0 || le >= E_local) dest[i] = -1;
+    }
+    for (int e = warp; e < E_local; e += nw) {
+        int base = offs[e];
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < n && ids[i] - expert_base == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int row = base + __popc(m & ((1u << lane) - 1));
+                dest[i] = row;
+                if (row < n) src_token[row] = i / ld;
+            }
+            base += __popc(m);
+        }
+    }
+}
+
 // out[t] = residual[t] + shared[t] + sum_j wts[t][j] * y[dest[t][j]]   (fp32 accumulate, bf16 out)
 __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
                                    const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
@@ -378,6 +573,19 @@ int jib_moe_gate(const void * g, const float * w_router, const float * bias, flo
     JIB_LAUNCH((router_logits_kernel), dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, logits, T, d, E);
     if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;
     JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2);
+    return launched();
+}
+
+// jib_moe_gate followed by jib_moe_permute (over the k + n_shared columns) in one launch; T <= 64.  counter: one device int,
+// zero between launches.
+int jib_moe_route_fused(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int * seg,
+                        int * src_token, int * dest, int * counter, int T, int d, int E, int k, int n_group, int topk_group, float scale,
+                        int norm, int sigmoid, int n_shared, int group_top2, int expert_base, int E_local, void * stream) {
+    if (T <= 0) return 0;
+    if (T > ROUTE_MAX_T || counter == nullptr || E_local > MAX_E || E_local < 1) return JIB_E_ARG;
+    if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 4 || d > GATE_MAXV * GATE_NT * 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
+    JIB_LAUNCH((moe_route_fused_kernel), E, GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, bias, logits, ids, wts, seg,
+               src_token, dest, counter, T, d, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, expert_base, E_local);
     return launched();
 }
 

@@ -308,15 +308,17 @@ class DeepSeek2Model:
         if not L.is_moe:
             hmid = ops.gateup_silu(g, L.w_gate, L.w_up)
             return self._row_parallel(hmid, L.w_down, residual)
+        dp = self.spec.dp_attention and self.spec.sharded
+        base = self.expert_base if self.spec.expert_parallel else 0
         ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
                                 hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid",
-                                L.n_shared_merged or 0, hp.group_score_top2)
-        if self.spec.dp_attention and self.spec.sharded:
+                                L.n_shared_merged or 0, hp.group_score_top2,
+                                route=None if dp else (base, L.w_gate_exps.shape[0]))     # the local expert sort follows
+        if dp:
             shared = None
             if L.w_gate_sh is not None:
                 shared = ops.linear(ops.gateup_silu(g, L.w_gate_sh, L.w_up_sh), L.w_down_sh)
             return self.ep.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, shared)
-        base = self.expert_base if self.spec.expert_parallel else 0
         if self.comm is not None and self.spec.sharded:
             part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                                L.w_down_sh, base)

@@ -87,9 +87,11 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
     return ref.mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size)
 
 
-def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False):
-    f = nat().moe_gate if use_native(g) else ref.moe_gate
-    return f(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2)
+def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False, route=None):
+    """``route=(expert_base, E_local)`` tells the CUDA path which local expert sort follows (see ``native.moe_gate``)."""
+    if use_native(g):
+        return nat().moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, route)
+    return ref.moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2)
 
 
 def moe_experts(x, ids, wts, wg, wu, wd, expert_base=0):

@@ -20,6 +20,11 @@ launch_count = 0            # kernels launched through this module (bench.py rep
 # has not run on a GPU yet: off unless JIB_PERMUTE_MULTI=1.
 PERMUTE_MULTI = os.environ.get("JIB_PERMUTE_MULTI", "0") == "1"
 PERMUTE_MULTI_MIN = 4096
+# Router logits + gating + expert sort in one launch for decode batches (<= 64 tokens): same state (cross-compiled, not
+# yet run on a GPU), off unless JIB_FUSED_ROUTE=1.
+FUSED_ROUTE = os.environ.get("JIB_FUSED_ROUTE", "0") == "1"
+FUSED_ROUTE_MAX_T = 64
+_route_stash: Dict[tuple, tuple] = {}       # (ids ptr, expert_base, E_local) -> (seg, src, dest) produced by the fused launch
 
 ERRORS = {-1: "unsupported shape/argument", -2: "pointer or stride not 16-byte aligned", -3: "driver entry point missing",
           -4: "tensor map encode failed", -5: "kernel launch failed", -6: "scratch too small for requested split"}
@@ -62,6 +67,7 @@ def load():
     sig("jib_gather_rows", vp, ip, vp, i, i, i, vp)
     sig("jib_moe_gate", vp, fp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, i, i, vp)
     sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
+    sig("jib_moe_route_fused", vp, fp, fp, fp, ip, fp, ip, ip, ip, ip, i, i, i, i, i, i, f, i, i, i, i, i, i, vp)
     sig("jib_moe_permute_multi", ip, i, i, i, i, ip, ip, ip, ip, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
     sig("jib_mla_attention", vp, vp, ip, i, ip, ip, i, i, i, i, i, i, f, i, fp, fp, vp, vp)
@@ -83,6 +89,7 @@ class Workspace:
         self.scratch = torch.empty(self.SCRATCH_BYTES, dtype=torch.uint8, device=device)
         self.counters = torch.zeros(self.N_COUNTERS, dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.route_counter = torch.zeros(1, dtype=torch.int32, device=device)      # last-CTA detection of the fused router
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         L = load()
         if hasattr(L, "jib_bounds_check_enabled") and L.jib_bounds_check_enabled():
@@ -316,12 +323,27 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
 
 
 # ---- MoE -----------------------------------------------------------------------------------------
-def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False):
+def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False, route=None):
+    """``route=(expert_base, E_local)``: the caller will sort these ids by local expert next (``moe_permute``); for decode
+    batches both steps then run as one launch and ``moe_permute`` picks the result up."""
     T, d = g.shape
     E = w_router.shape[0]
     ids = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
     wts = torch.empty(T, k + n_shared, dtype=torch.float32, device=g.device)
     logits = torch.empty(T, E, dtype=torch.float32, device=g.device)
+    if FUSED_ROUTE and route is not None and T <= FUSED_ROUTE_MAX_T:
+        expert_base, E_local = route
+        n = T * (k + n_shared)
+        seg = torch.empty(E_local + 1, dtype=torch.int32, device=g.device)
+        src = torch.empty(n, dtype=torch.int32, device=g.device)
+        dest = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
+        _ck(load().jib_moe_route_fused(g.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+                                       seg.data_ptr(), src.data_ptr(), dest.data_ptr(), workspace(g.device).route_counter.data_ptr(),
+                                       T, d, E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared,
+                                       int(group_top2), expert_base, E_local, _stream()), "moe_route_fused")
+        _route_stash.clear()                       # at most one pending result: the sort that follows this gate
+        _route_stash[(ids.data_ptr(), expert_base, E_local)] = (seg, src, dest, ids)
+        return ids, wts
     _ck(load().jib_moe_gate(g.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, d,
                             E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared, int(group_top2), _stream()), "moe_gate")
     return ids, wts
@@ -330,6 +352,9 @@ def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_
 def moe_permute(ids, expert_base, E_local):
     T, k = ids.shape
     dev = ids.device
+    hit = _route_stash.pop((ids.data_ptr(), expert_base, E_local), None)
+    if hit is not None and hit[3] is ids:          # the fused router launch already sorted exactly these ids
+        return hit[0], hit[1], hit[2]
     seg = torch.empty(E_local + 1, dtype=torch.int32, device=dev)
     src = torch.empty(T * k, dtype=torch.int32, device=dev)
     dest = torch.empty(T, k, dtype=torch.int32, device=dev)

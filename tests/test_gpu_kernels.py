@@ -233,3 +233,30 @@ def test_moe_permute_multi_cta(nat, T, k, E):
     assert torch.equal(src.cpu().long(), order // k)
     counts = torch.bincount(flat, minlength=E)
     assert torch.equal(seg.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]))
+
+
+@pytest.mark.skipif(__import__("os").environ.get("JIB_FUSED_ROUTE", "") != "1",
+                    reason="the one-launch router has not run on a GPU yet: set JIB_FUSED_ROUTE=1 to try it")
+@pytest.mark.parametrize("T,d,E,k,n_group,topk_group,n_shared,base,E_local",
+                         [(1, 2048, 64, 6, 1, 1, 2, 0, 66), (8, 2048, 64, 6, 1, 1, 2, 0, 66), (64, 2048, 64, 6, 1, 1, 0, 0, 64),
+                          (8, 5120, 160, 6, 8, 3, 0, 40, 20), (33, 5120, 160, 6, 8, 3, 0, 0, 160)])
+def test_fused_route_matches_the_separate_kernels(nat, T, d, E, k, n_group, topk_group, n_shared, base, E_local):
+    """Router logits + gating + expert sort in one launch (decode batches): bitwise the ids, weights and sort of the
+    three separate launches; a second call checks that the last-CTA counter was left at zero."""
+    g = rnd(T, d)
+    w_router = torch.randn(E, d, device=DEV, dtype=torch.float32) * 0.05
+    assert nat.FUSED_ROUTE
+    for _ in range(2):
+        nat.FUSED_ROUTE = False
+        ids0, wts0 = nat.moe_gate(g, w_router, None, k, n_group, topk_group, 1.0, False, False, n_shared)
+        seg0, src0, dest0 = nat.moe_permute(ids0, base, E_local)
+        nat.FUSED_ROUTE = True
+        ids1, wts1 = nat.moe_gate(g, w_router, None, k, n_group, topk_group, 1.0, False, False, n_shared, False, (base, E_local))
+        seg1, src1, dest1 = nat.moe_permute(ids1, base, E_local)
+        torch.cuda.synchronize()
+        assert not nat._route_stash                       # the sort came from the fused launch
+        assert torch.equal(ids0, ids1) and torch.equal(wts0, wts1)
+        assert torch.equal(seg0, seg1) and torch.equal(dest0, dest1)
+        n_local = int(seg0[-1])
+        assert torch.equal(src0[:n_local], src1[:n_local]) and bool((src1[n_local:] == -1).all())
+        assert int(nat.workspace(g.device).route_counter.item()) == 0
