@@ -395,6 +395,9 @@ class ServerContext:
 
 
 # =================================================================================================
+MAX_BODY_BYTES = 64 << 20          # largest accepted request body
+
+
 def make_handler(ctx: ServerContext):
     class Handler(BaseHTTPRequestHandler):
         protocol_version = "HTTP/1.1"
@@ -459,6 +462,9 @@ def make_handler(ctx: ServerContext):
             path = self.path.split("?")[0]
             try:
                 n = int(self.headers.get("Content-Length", "0"))
+                if n < 0 or n > MAX_BODY_BYTES:          # a negative length would read until the peer closes
+                    self.close_connection = True
+                    return self._json(413, P.error_body(f"request body must be 0..{MAX_BODY_BYTES} bytes", 413))
                 body = json.loads(self.rfile.read(n) or b"{}")
                 if not isinstance(body, dict):
                     raise P.BadRequest("request body must be a JSON object")
@@ -472,7 +478,6 @@ def make_handler(ctx: ServerContext):
                     return self._json(200, {"content": ctx.tokenizer.decode(list(body.get("tokens", [])))})
                 else:
                     return self._json(404, P.error_body("not found", 404, "not_found_error"))
-                limit = ctx.engine.n_ctx_slot
                 for p in req.prompts:
                     if not p:
                         raise P.BadRequest("empty prompt")

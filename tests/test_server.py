@@ -77,6 +77,20 @@ def test_errors_and_introspection(server):
         with pytest.raises(urllib.error.HTTPError) as e:
             _post(url + path, bad)
         assert e.value.code == 400 and "error" in json.loads(e.value.read())
+    # malformed JSON and absurd body lengths are refused without touching the engine
+    import http.client
+    host, port = url.replace("http://", "").split(":")
+    for headers, payload, want in (({"Content-Length": "7"}, b"{not js", 400), ({"Content-Length": "-5"}, b"", 413),
+                                   ({"Content-Length": str(1 << 40)}, b"", 413)):
+        c = http.client.HTTPConnection(host, int(port), timeout=10)
+        c.putrequest("POST", "/v1/completions")
+        for k, v in headers.items():
+            c.putheader(k, v)
+        c.endheaders()
+        c.send(payload)
+        r = c.getresponse()
+        assert r.status == want and "error" in json.loads(r.read())
+        c.close()
     assert json.loads(urllib.request.urlopen(url + "/health").read())["status"] == "ok"
     m = urllib.request.urlopen(url + "/metrics").read().decode()
     assert "jittorinfer_generation_tokens_total" in m and "jittorinfer_kv_blocks_total" in m
