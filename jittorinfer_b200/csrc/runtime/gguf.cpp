@@ -1,5 +1,6 @@
 #include "gguf.h"
 
+#include <cstdint>
 #include <cstring>
 #include <fcntl.h>
 #include <sys/mman.h>
@@ -120,6 +121,7 @@ std::string GgufFile::open(const std::string & path, bool populate) {
             v.arr_type = c.get<uint32_t>();
             v.arr_n = c.get<uint64_t>();
             if (v.arr_type == GT_STR) {
+                if (v.arr_n > (uint64_t) (c.end - c.p) / 8) { c.ok = false; break; }      // every string has an 8-byte length
                 v.arr_s.reserve(v.arr_n);
                 for (uint64_t k = 0; k < v.arr_n && c.ok; ++k) v.arr_s.push_back(c.str());
             } else {
@@ -136,6 +138,7 @@ std::string GgufFile::open(const std::string & path, bool populate) {
     if (!c.ok) { close(); return "corrupt GGUF metadata"; }
     if (const GgufValue * a = find("general.alignment")) alignment_ = (uint32_t) a->as_i64();
     if (alignment_ == 0 || (alignment_ & (alignment_ - 1))) { close(); return "bad general.alignment"; }
+    if (n_tensors > (uint64_t) (c.end - c.p) / 24) { close(); return "corrupt GGUF tensor table"; }      // name length + dims + type + offset
     tensors_.reserve(n_tensors);
     for (uint64_t i = 0; i < n_tensors && c.ok; ++i) {
         GgufTensor t;
@@ -145,8 +148,10 @@ std::string GgufFile::open(const std::string & path, bool populate) {
         uint64_t n = 1;
         for (uint32_t d = 0; d < nd; ++d) {
             t.ne.push_back(c.get<uint64_t>());
+            if (t.ne.back() != 0 && n > UINT64_MAX / 64 / t.ne.back()) { c.ok = false; break; }      // element count (x block bytes) must not wrap
             n *= t.ne.back();
         }
+        if (!c.ok) break;
         t.type = c.get<uint32_t>();
         t.offset = c.get<uint64_t>();
         const uint64_t blk = type_block(t.type);
@@ -159,7 +164,7 @@ std::string GgufFile::open(const std::string & path, bool populate) {
     const uint64_t pos = (uint64_t) (c.p - base_);
     data_offset_ = (pos + alignment_ - 1) / alignment_ * alignment_;
     for (const GgufTensor & t : tensors_)
-        if (data_offset_ + t.offset + t.nbytes > size_) {
+        if (data_offset_ > size_ || t.offset > size_ - data_offset_ || t.nbytes > size_ - data_offset_ - t.offset) {
             const std::string name = t.name;
             close();
             return "tensor " + name + " runs past the end of the file";

@@ -26,7 +26,10 @@ struct GgufValue {
 
     bool is_int() const { return type != GT_F32 && type != GT_F64 && type != GT_STR && type != GT_ARR; }
     double as_f64() const { return (type == GT_F32 || type == GT_F64) ? f : (double) (int64_t) u; }
-    int64_t as_i64() const { return (type == GT_F32 || type == GT_F64) ? (int64_t) f : (int64_t) u; }
+    int64_t as_i64() const {
+        if (type != GT_F32 && type != GT_F64) return (int64_t) u;
+        return f >= -9.2e18 && f <= 9.2e18 ? (int64_t) f : 0;          // NaN and out-of-range values have no integer reading
+    }
 };
 
 struct GgufTensor {
