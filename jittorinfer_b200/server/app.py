@@ -579,9 +579,28 @@ def make_handler(ctx: ServerContext):
     return Handler
 
 
+class PooledHTTPServer(ThreadingHTTPServer):
+    """``n_threads_http`` of the configuration (reference: common_local.h, ``n_threads_http``): connections are handled by a
+    fixed pool of worker threads instead of one new thread each; further connections wait in the pool's queue."""
+
+    def __init__(self, addr, handler, n_threads: int):
+        super().__init__(addr, handler)
+        from concurrent.futures import ThreadPoolExecutor
+        self._pool = ThreadPoolExecutor(max_workers=n_threads, thread_name_prefix="http")
+
+    def process_request(self, request, client_address):
+        self._pool.submit(self.process_request_thread, request, client_address)
+
+    def server_close(self):
+        super().server_close()
+        self._pool.shutdown(wait=False, cancel_futures=True)
+
+
 def serve(ctx: ServerContext, host: str, port: int, n_threads: int = -1) -> ThreadingHTTPServer:
-    """Starts the engine thread and returns the (not yet serving) HTTP server; call serve_forever() on it."""
-    httpd = ThreadingHTTPServer((host, port), make_handler(ctx))
+    """Starts the engine thread and returns the (not yet serving) HTTP server; call serve_forever() on it.
+    ``n_threads`` > 0 bounds the number of HTTP worker threads; otherwise every connection gets its own thread."""
+    httpd = PooledHTTPServer((host, port), make_handler(ctx), n_threads) if n_threads and n_threads > 0 \
+        else ThreadingHTTPServer((host, port), make_handler(ctx))
     httpd.daemon_threads = True
     ctx.start()
     return httpd

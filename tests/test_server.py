@@ -169,3 +169,26 @@ def test_clients_that_disconnect_free_their_slots(server):
     assert all(sl["state"] == "IDLE" for sl in slots) and not ctx.streams
     assert ctx.engine.kv.check()
     assert _post(url + "/v1/completions", {"prompt": "after", "max_tokens": 3, "temperature": 0, "ignore_eos": True})["usage"]["completion_tokens"] == 3
+
+
+def test_bounded_http_worker_pool():
+    """n_threads_http > 0: a fixed pool of HTTP workers; more simultaneous requests than workers still all complete."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from jittorinfer_b200.server.app import PooledHTTPServer
+    cfg = ServerConfig(random_init="tiny", n_ctx=1024, n_parallel=4, n_batch=64, port=0, enable_ge=False, n_threads_http=2)
+    eng, tok, tpl = build_from_config(cfg, device=torch.device("cpu"))
+    ctx = ServerContext(eng, tok, cfg, ChatTemplate(tpl))
+    httpd = serve(ctx, "127.0.0.1", 0, cfg.n_threads_http)
+    assert isinstance(httpd, PooledHTTPServer)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    url = f"http://127.0.0.1:{httpd.server_address[1]}"
+    try:
+        with ThreadPoolExecutor(6) as ex:
+            outs = list(ex.map(lambda i: _post(url + "/v1/completions", {"prompt": f"p{i}", "max_tokens": 4, "temperature": 0, "ignore_eos": True}), range(6)))
+        assert all(o["usage"]["completion_tokens"] == 4 for o in outs)
+        assert sum(t.name.startswith("http") for t in threading.enumerate()) <= 2
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
+        ctx.shutdown()
