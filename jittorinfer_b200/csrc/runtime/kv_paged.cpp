@@ -32,7 +32,16 @@ void PagedKv::release_block(int b) {
     if (--ref_[b] == 0) {
         free_.push_back(b);
         std::push_heap(free_.begin(), free_.end(), std::greater<int32_t>());
+        if (track_freed_) freed_.push_back(b);
     }
+}
+
+std::vector<int32_t> PagedKv::take_freed() {
+    std::vector<int32_t> out;
+    for (int32_t b : freed_)
+        if (ref_[b] == 0 && std::find(out.begin(), out.end(), b) == out.end()) out.push_back(b);      // still free: not handed out again
+    freed_.clear();
+    return out;
 }
 
 int PagedKv::blocks_needed(int seq, int n) const {

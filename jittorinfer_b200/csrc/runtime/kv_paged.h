@@ -61,6 +61,12 @@ class PagedKv {
     int reserve(int n);
     void unreserve();
 
+    // Debug aid ("poison freed blocks"): with tracking on, every block whose reference count drops to zero is remembered;
+    // take_freed() returns those that are still free (not handed out again since) and forgets them.  The engine fills
+    // them with NaN so that a read through a stale block table shows up in the logits.
+    void track_freed(bool on) { track_freed_ = on; if (!on) freed_.clear(); }
+    std::vector<int32_t> take_freed();
+
     // Consistency check used by tests and the bounds-check build: every block's refcount equals the
     // number of tables naming it, and free blocks have refcount 0.
     bool check() const;
@@ -75,6 +81,8 @@ class PagedKv {
     std::vector<int32_t> free_;    // kept sorted descending so pop_back() yields the lowest id
     std::vector<std::pair<int32_t, int32_t>> pending_;
     std::vector<int32_t> reserved_;
+    std::vector<int32_t> freed_;
+    bool track_freed_ = false;
 };
 
 }  // namespace jib

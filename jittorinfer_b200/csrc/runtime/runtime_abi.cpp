@@ -44,6 +44,14 @@ JIB_API float jib_kv_fragmentation(PagedKv * kv) { return kv->fragmentation(); }
 JIB_API int jib_kv_check(PagedKv * kv) { return kv->check() ? 1 : 0; }
 JIB_API int jib_kv_reserve(PagedKv * kv, int n) { return kv->reserve(n); }
 JIB_API void jib_kv_unreserve(PagedKv * kv) { kv->unreserve(); }
+JIB_API void jib_kv_track_freed(PagedKv * kv, int on) { kv->track_freed(on != 0); }
+// Blocks freed since the last call that are still free; returns the count (at most cap are written).
+JIB_API int jib_kv_take_freed(PagedKv * kv, int32_t * out, int cap) {
+    const std::vector<int32_t> f = kv->take_freed();
+    const int n = std::min<int>((int) f.size(), cap);
+    for (int i = 0; i < n; ++i) out[i] = f[i];
+    return n;
+}
 // Pops up to cap queued copy-on-write copies.
 JIB_API int jib_kv_take_copies(PagedKv * kv, int32_t * src, int32_t * dst, int cap) {
     auto & p = kv->pending_copies();

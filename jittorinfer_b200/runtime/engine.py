@@ -15,6 +15,7 @@ by design:
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
@@ -170,6 +171,13 @@ class LLMEngine:
         self._idle_graph = None
         self.tracer = Tracer()            # JSON-lines step trace when JITTORINFER_TRACE names a file
         self._pressure = False            # free KV blocks held back by the kv_alloc fault site
+        # Debug aid: JITTORINFER_KV_POISON=1 fills every cache block with NaN when its last reference goes away and checks the
+        # logits of every (then eager) step: a read through a stale block table cannot pass unnoticed.
+        self._poison = os.environ.get("JITTORINFER_KV_POISON", "") == "1"
+        if self._poison:
+            self.kv.track_freed(True)
+            self._use_graphs = False
+            self.stats["poisoned_blocks"] = 0
         from ..utils import graphdump
         il = graphdump.requested_layer()  # LLAMA_PRINT_LAYER=<il>: the first step writes that layer's op graph as dot text
         if il is not None:
@@ -221,7 +229,21 @@ class LLMEngine:
             with torch.cuda.device(logits.device):
                 return self._sample_device(logits, mode)
         logits = self.model.forward(batch, self.kv_cache)
+        if self._poison and bool(torch.isnan(logits).any()):
+            raise RuntimeError("NaN logits with poisoned free blocks: a sequence read a cache block it does not own")
         return self._sample_device(logits, mode)
+
+    def _poison_freed(self) -> None:
+        blocks = self.kv.take_freed()
+        if blocks.size == 0:
+            return
+        bs = self.cfg.block_size
+        for il in range(self.hp.n_layer):
+            layer = self.kv_cache[il]
+            rows = (torch.from_numpy(blocks.astype(np.int64)).to(layer.device)[:, None] * bs +
+                    torch.arange(bs, device=layer.device)[None, :]).reshape(-1)
+            layer[rows] = float("nan")
+        self.stats["poisoned_blocks"] += int(blocks.size)
 
     def _graph_for(self, bucket: int, mode: str):
         key = (bucket, mode)
@@ -272,6 +294,8 @@ class LLMEngine:
                                cfg.cont_batching)
         self.requests.clear()
         self._pressure = False
+        if self._poison:
+            self.kv.track_freed(True)
         self.stats["resets"] = self.stats.get("resets", 0) + 1
 
     def run_until_all_idle(self, max_steps: int = 1 << 30) -> int:
@@ -381,6 +405,8 @@ class LLMEngine:
         if n_copies:
             src, dst = self.kv.take_copies()
             self._copy_blocks(src, dst)
+        if self._poison:
+            self._poison_freed()             # after the copies: a block may be freed while a copy out of it is still queued
         states = [self.requests[int(r)] for r in self.sched.out_reqs(n_out)] if n_out else []
         mode = "greedy" if all(s.sampler is None for s in states) else "topk"
         use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets) \

@@ -64,6 +64,8 @@ def lib():
         sig("jib_kv_refcount", C.c_int, vp, C.c_int)
         sig("jib_kv_reserve", C.c_int, vp, C.c_int)
         sig("jib_kv_unreserve", None, vp)
+        sig("jib_kv_track_freed", None, vp, C.c_int)
+        sig("jib_kv_take_freed", C.c_int, vp, i32p, C.c_int)
         sig("jib_kv_fragmentation", C.c_float, vp)
         sig("jib_kv_take_copies", C.c_int, vp, i32p, i32p, C.c_int)
         sig("jib_kv_defrag", C.c_int, vp, C.c_int, i32p, i32p)
@@ -131,6 +133,13 @@ class PagedKV:
     def check(self): return bool(self._L.jib_kv_check(self._h))
     def reserve(self, n: int) -> int: return self._L.jib_kv_reserve(self._h, n)      # memory-pressure injection (tests)
     def unreserve(self) -> None: self._L.jib_kv_unreserve(self._h)
+
+    def track_freed(self, on: bool) -> None: self._L.jib_kv_track_freed(self._h, int(on))
+
+    def take_freed(self) -> np.ndarray:
+        """Blocks whose last reference went away since the previous call and that are still free (debug poisoning)."""
+        out = np.empty(self.n_blocks, dtype=np.int32)
+        return out[:self._L.jib_kv_take_freed(self._h, _p32(out), out.shape[0])]
 
     def take_copies(self, cap: int = 4096) -> Tuple[np.ndarray, np.ndarray]:
         s = np.empty(cap, dtype=np.int32)

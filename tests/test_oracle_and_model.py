@@ -1,4 +1,5 @@
 """fp32 oracle self-consistency and the module graph + engine against it (CPU)."""
+import pytest
 import torch
 
 from jittorinfer_b200.models.deepseek2 import DeepSeek2Model, ForwardBatch
@@ -191,3 +192,44 @@ def test_engine_under_kv_pressure_preempts_and_still_matches_oracle():
     st = eng.sched.stats()
     assert st["preemptions"] >= 1 and st["finished"] == len(prompts)
     assert eng.kv.check() and eng.kv.used_blocks <= eng.kv.n_blocks
+
+
+def test_poisoned_free_blocks_never_reach_the_logits(monkeypatch):
+    """JITTORINFER_KV_POISON=1: blocks are filled with NaN when their last reference goes away and every step's logits are
+    checked.  Preemption, recomputation, shared prefixes, cancellation and defragmentation must still give the oracle's
+    tokens; a block table that names a freed block (made by hand here) must be caught."""
+    monkeypatch.setenv("JITTORINFER_KV_POISON", "1")
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    eng = LLMEngine(m, EngineConfig(n_ctx=640, n_batch=96, n_parallel=6, n_ctx_slot=256, defrag_thold=0.05))
+    g = torch.Generator().manual_seed(12)
+    shared = torch.randint(0, hp.n_vocab, (70,), generator=g).tolist()                     # a prefix that several requests share
+    lens = (150, 90, 40, 120, 60, 30)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in lens] + [shared + [5, 6], shared + [7]]
+    victim = eng.add_request(torch.randint(0, hp.n_vocab, (100,), generator=g).tolist(), SamplingParams(ignore_eos=True, max_tokens=50))
+    eng.step()
+    eng.cancel(victim)                                                                      # frees blocks in mid-flight
+    outs = eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=20)
+    o = OracleModel(hp, w)
+    assert outs == [o.generate(p, 20) for p in prompts]
+    assert eng.stats["poisoned_blocks"] > 0 and eng.kv.check()
+    assert eng.sched.stats()["preemptions"] >= 1
+
+    # negative control: a sequence whose table points at a freed (poisoned) block
+    rid = eng.add_request(prompts[0][:80], SamplingParams(ignore_eos=True, max_tokens=8))
+    eng.step()
+    free_poisoned = [b for b in range(eng.kv.n_blocks) if eng.kv.refcount(b) == 0]
+    assert free_poisoned
+    eng.kv_cache[:, free_poisoned[0] * 64:(free_poisoned[0] + 1) * 64] = float("nan")     # as the engine leaves a freed block
+    real = eng.sched.step
+
+    def stale(arrays):
+        info = real(arrays)
+        eng.io.h["block_tables"][0] = free_poisoned[0]              # first block of the first scheduled sequence
+        return info
+    eng.sched.step = stale
+    with pytest.raises(RuntimeError, match="poisoned"):
+        eng.step()
+    eng.sched.step = real
+    eng.cancel(rid)
