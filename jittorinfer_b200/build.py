@@ -133,14 +133,12 @@ def build_capi(force: bool = False, verbose: bool = False) -> str:
     return LLAMA_SO
 
 
-def build_kernels_bounds_check(force: bool = False, verbose: bool = False) -> str:
-    """The kernels with -DJIB_BOUNDS_CHECK (see csrc/kernels/bounds_check.cuh) as libjib200_kernels_bc.so; select it with
-    JITTORINFER_KERNELS_SO=<path>."""
+def _build_kernels_variant(define: str, suffix: str, force: bool, verbose: bool) -> str:
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
     hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h"))
-    out = os.path.join(LIBDIR, "libjib200_kernels_bc.so")
+    out = os.path.join(LIBDIR, f"libjib200_kernels_{suffix}.so")
     if force or _newer(srcs + hdrs, out):
-        objdir = os.path.join(LIBDIR, "obj_bc")
+        objdir = os.path.join(LIBDIR, "obj_" + suffix)
         os.makedirs(objdir, exist_ok=True)
         nvcc = nvcc_path()
         objs, procs = [], []
@@ -148,7 +146,7 @@ def build_kernels_bounds_check(force: bool = False, verbose: bool = False) -> st
             o = os.path.join(objdir, os.path.basename(s) + ".o")
             objs.append(o)
             cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", *NVCC_ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
-                   "-DJIB_BOUNDS_CHECK", "-I", os.path.join(CSRC, "kernels"), "-c", s, "-o", o]
+                   "-D" + define, "-I", os.path.join(CSRC, "kernels"), "-c", s, "-o", o]
             procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         for cmd, p in procs:
             o, _ = p.communicate()
@@ -157,6 +155,18 @@ def build_kernels_bounds_check(force: bool = False, verbose: bool = False) -> st
                 raise RuntimeError(f"build failed: {cmd[-3]}")
         _run([nvcc, "-shared", *NVCC_ARCH, "-o", out] + objs, verbose)
     return out
+
+
+def build_kernels_bounds_check(force: bool = False, verbose: bool = False) -> str:
+    """The kernels with -DJIB_BOUNDS_CHECK (see csrc/kernels/bounds_check.cuh) as libjib200_kernels_bc.so; select it with
+    JITTORINFER_KERNELS_SO=<path>."""
+    return _build_kernels_variant("JIB_BOUNDS_CHECK", "bc", force, verbose)
+
+
+def build_kernels_timeline(force: bool = False, verbose: bool = False) -> str:
+    """The kernels with -DJIB_TIMELINE (device time stamps of the collective phases, csrc/kernels/timeline.cuh) as
+    libjib200_kernels_tl.so; select it with JITTORINFER_KERNELS_SO=<path> and read the stamps with parallel/timeline.py."""
+    return _build_kernels_variant("JIB_TIMELINE", "tl", force, verbose)
 
 
 def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[str] = ()) -> str:

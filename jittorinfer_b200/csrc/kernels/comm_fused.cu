@@ -191,7 +191,18 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const bf16 * __rest
 
 }  // namespace
 
+JIB_TL_DEFINE_SETTER(comm)
+
 extern "C" {
+
+// 1 when the library was built with -DJIB_TIMELINE
+JIB_EXPORT int jib_timeline_enabled(void) {
+#ifdef JIB_TIMELINE
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 // ---- IPC plumbing (cudaMalloc'd buffers exchanged as 64-byte handles by the Python side) --------------------
 JIB_EXPORT int jib_symm_alloc(size_t bytes, void ** ptr_out, void * handle_out /*64 bytes*/) {

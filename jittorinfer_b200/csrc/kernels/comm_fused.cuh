@@ -29,6 +29,7 @@ struct JibArCtx {
 };
 
 #ifdef __CUDACC__
+#include "timeline.cuh"
 __device__ __forceinline__ void jib_st_release_sys(unsigned * p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -50,6 +51,7 @@ __device__ __forceinline__ bool jib_ar_signal_and_wait(const JibArCtx & ar, int 
     const size_t slot = ((size_t) site * ar.world) * ar.max_tiles + tile;
     if (local_tid < ar.world)                     // tell peer `local_tid` that slot [rank] of this tile is complete
         jib_st_release_sys(ar.flags[local_tid] + slot + (size_t) ar.rank * ar.max_tiles, epoch);
+    if (local_tid == 0) JIB_TS(10, site, tile, ar.rank);
     if (local_tid < ar.world) {                   // wait for source `local_tid`
         const unsigned * f = ar.flags[ar.rank] + slot + (size_t) local_tid * ar.max_tiles;
         bool got = false;
@@ -57,6 +59,7 @@ __device__ __forceinline__ bool jib_ar_signal_and_wait(const JibArCtx & ar, int 
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }
+        JIB_TS(11, site, tile, local_tid);
         if (!got) {
             s_ok = 0;
             if (ar.status != nullptr && atomicCAS(ar.status, 0, 1 /* wait timeout */) == 0) {
@@ -67,6 +70,7 @@ __device__ __forceinline__ bool jib_ar_signal_and_wait(const JibArCtx & ar, int 
         }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    if (local_tid == 0) JIB_TS(12, site, tile, ar.rank);
     return s_ok != 0;
 }
 // Two-shot exchange for one tile, called by `nthreads` threads (named barrier 1) after they stored their fp32 partial
@@ -80,7 +84,10 @@ __device__ __forceinline__ bool jib_ar2_signal_owner(const JibArCtx & ar, int si
     if (local_tid == 0) s_ok2 = 1;
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     const size_t slot = ((size_t) site * ar.world) * ar.max_tiles + tile;
-    if (local_tid == 0) jib_st_release_sys(ar.flags[owner] + slot + (size_t) ar.rank * ar.max_tiles, epoch);
+    if (local_tid == 0) {
+        jib_st_release_sys(ar.flags[owner] + slot + (size_t) ar.rank * ar.max_tiles, epoch);
+        JIB_TS(20, site, tile, owner);
+    }
     if (ar.rank == owner && local_tid < ar.world) {
         const unsigned * f = ar.flags[ar.rank] + slot + (size_t) local_tid * ar.max_tiles;
         bool got = false;
@@ -88,6 +95,7 @@ __device__ __forceinline__ bool jib_ar2_signal_owner(const JibArCtx & ar, int si
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }
+        JIB_TS(21, site, tile, local_tid);
         if (!got) {
             s_ok2 = 0;
             if (ar.status != nullptr && atomicCAS(ar.status, 0, 1 /* wait timeout */) == 0) {
@@ -119,6 +127,7 @@ __device__ __forceinline__ bool jib_ar2_deliver_and_wait(const JibArCtx & ar, in
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }
+        JIB_TS(22, site, tile, owner);
         if (!got) {
             s_ok3 = 0;
             if (ar.status != nullptr && atomicCAS(ar.status, 0, 1 /* wait timeout */) == 0) {

@@ -278,6 +278,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tc_fence_after();
         const uint32_t tbase = tmem + ((uint32_t) (q * 32) << 16);
         const int tile_id = (batch * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        if (args.ar_on != 0 && (threadIdx.x & 127) == 0) JIB_TS(30, args.ar_site, tile_id, split);
         constexpr int ACC = DUAL ? 2 : 1;
         float * part = nullptr;
         bool do_final = true;
@@ -566,6 +567,8 @@ int launch(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b,
 }
 
 }  // namespace
+
+JIB_TL_DEFINE_SETTER(gemm)
 
 extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_) {
     cudaStream_t stream = (cudaStream_t) stream_;

@@ -35,6 +35,9 @@ def main():
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--sets", type=int, default=6)
     ap.add_argument("--graph", action="store_true", help="replay the fused path as a CUDA graph (default: both paths eager)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with the timeline build of the kernels (JITTORINFER_KERNELS_SO): per shape, how long tiles wait for "
+                         "each peer after their own partial is out")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -56,6 +59,10 @@ def main():
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     g_same = torch.Generator(device=dev).manual_seed(7)         # the residual stream is replicated: same on every rank
     rows = []
+    tl = None
+    if args.timeline:
+        from jittorinfer_b200.parallel.timeline import Timeline, summarize
+        tl = Timeline(dev)
 
     def timed(fn):
         for _ in range(3):
@@ -106,8 +113,15 @@ def main():
                 dist.barrier()
                 us_fused = timed(gr.replay)
             else:
+                if tl is not None:
+                    tl.clear()
                 us_fused = timed(lambda: run(fused))
             native.check_status()
+            waits = None
+            if tl is not None:          # every rank reads its own ring; rank 0's view is reported
+                sm = summarize(tl.read())
+                waits = {"wait_us_mean": round(sm.get("wait_us_mean", 0.0), 2), "dropped": tl.dropped(),
+                         "late_us_by_source": {r: round(e["late_us_mean"], 2) for r, e in sm["sources"].items()}}
             flops = 2.0 * T * N * K
             t_math = max(flops / (float(peaks["bf16_tflops"]) * 1e12), N * K * 2 / (float(peaks["hbm_gbs"]) * 1e9)) * 1e6
             if T <= fused.max_rows:
@@ -120,6 +134,8 @@ def main():
                          "us_library": round(us_lib, 2), "us_fused": round(us_fused, 2), "speedup": round(us_lib / us_fused, 2),
                          "roofline_us": round(roof, 2), "bound": "nvlink" if t_link > t_math else "gemm",
                          "fraction_of_roofline": round(roof / us_fused, 3), "max_abs_diff": err})
+            if waits is not None:
+                rows[-1]["timeline"] = waits
     if rank == 0:
         print(json.dumps({"bench": "gemm_allreduce", "model": args.model, "n_gpus": world, "timing": "CUDA events, max over ranks",
                           "fused_path": "cuda graph" if args.graph else "eager", "rows": rows}))

@@ -15,6 +15,49 @@ def test_bounds_check_build_compiles_and_identifies_itself():
     assert not hasattr(normal, "jib_bounds_status_moe")
 
 
+def test_timeline_build_compiles_and_identifies_itself():
+    """-DJIB_TIMELINE adds the device time stamps of the collective phases and the ring setters; the normal library has
+    neither (the stamps compile to nothing there)."""
+    normal = C.CDLL(build.build_kernels())
+    timed = C.CDLL(build.build_kernels_timeline())
+    assert normal.jib_timeline_enabled() == 0 and timed.jib_timeline_enabled() == 1
+    for unit in ("gemm", "comm"):
+        assert hasattr(timed, "jib_timeline_set_" + unit) and not hasattr(normal, "jib_timeline_set_" + unit)
+
+
+def test_timeline_analysis_on_synthetic_stamps():
+    """Two call sites, two visits each, four ranks: rank 3 is always the last to arrive at site 1."""
+    import json
+
+    import numpy as np
+    from jittorinfer_b200.parallel.timeline import STAMP_DTYPE, format_summary, summarize, to_chrome_trace
+    rows, t = [], 1_000_000
+    for visit in range(2):
+        for site in (0, 1):
+            rows.append((t, 30, site, 5, 0))                       # accumulators done
+            t += 2_000
+            rows.append((t, 10, site, 5, 1))                       # my partial is out (I am rank 1)
+            t0 = t
+            for src, lag in ((1, 100), (0, 900), (2, 1_500), (3, 6_000 if site == 1 else 1_200)):
+                rows.append((t0 + lag, 11, site, 5, src))
+            t = t0 + (6_300 if site == 1 else 1_800)
+            rows.append((t, 12, site, 5, 1))
+            t += 50_000
+    stamps = np.array(rows, dtype=STAMP_DTYPE)
+    assert STAMP_DTYPE.itemsize == 24
+    s = summarize(stamps)
+    assert s["n_stamps"] == len(rows) and set(s["sites"]) == {0, 1}
+    assert abs(s["sites"][1]["wait_us_mean"] - 6.3) < 1e-6 and abs(s["sites"][0]["wait_us_mean"] - 1.8) < 1e-6
+    assert s["sites"][1]["last_source"] == {3: 2} and s["sites"][0]["last_source"] == {2: 2}
+    assert abs(s["sites"][0]["push_us_mean"] - 2.0) < 1e-6
+    assert abs(s["sources"][3]["late_us_mean"] - (6.0 + 1.2) / 2) < 1e-6 and s["sources"][1]["arrivals"] == 4
+    text = format_summary(s)
+    assert "last source" in text and text.splitlines()[0].startswith(f"{len(rows)} stamps")
+    ev = json.loads(to_chrome_trace(stamps, rank=1))["traceEvents"]
+    assert len(ev) == len(rows) and ev[0]["name"] == "gemm_accumulators_done" and ev[1]["ts"] == 2.0
+    assert summarize(stamps[:0])["sites"] == {}
+
+
 def test_every_entry_point_is_exported():
     L = C.CDLL(build.build_kernels())
     for name in ("jib_gemm_bf16", "jib_gemm_bf16_noalloc", "jib_mla_flash", "jib_mla_attention", "jib_mla_combine", "jib_moe_gate",
