@@ -101,6 +101,9 @@ def main():
     ap.add_argument("--ops", default="native", choices=["native", "torch"], help="torch = PyTorch/cuBLAS baseline ops")
     ap.add_argument("--sweep", action="store_true", help="also report concurrency 1/2/4")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="diagnostic (needs JITTORINFER_KERNELS_SO = the timeline build): report how long the fused all-reduces "
+                         "wait for their peers during the timed steps; the stamps cost time, so the tokens/s of such a run is not a result")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -193,8 +196,20 @@ def main():
     note(f"model built: {eng.model.weight_bytes() / 2**30:.1f} GiB of weights on this rank")
     eng.warmup()
     note("decode graphs captured")
+    tl = None
+    if args.timeline:
+        from jittorinfer_b200.parallel.timeline import Timeline, format_summary, summarize
+        tl = Timeline(dev, capacity=1 << 22)
     ms_step, clocks, launches = timed_decode(C, K, W, True)
     note(f"timed region done: {ms_step:.3f} ms/step")
+    timeline_summary = None
+    if tl is not None:
+        sm = summarize(tl.read())                  # includes prefill and warm-up steps of this measurement
+        timeline_summary = {"wait_us_mean": sm.get("wait_us_mean"), "wait_us_total": sm.get("wait_us_total"), "dropped": tl.dropped(),
+                            "late_us_by_source": {r: e["late_us_mean"] for r, e in sm["sources"].items()}}
+        if rank == 0:
+            print(format_summary(sm), file=sys.stderr, flush=True)
+        tl.close()
     value = C * 1000.0 / ms_step
 
     # bare graph replay (no host work between steps): explains how much of a step is device time
@@ -258,6 +273,9 @@ def main():
         }
         if by_conc:
             out["by_concurrency"] = by_conc
+        if timeline_summary is not None:
+            out["timeline"] = timeline_summary
+            out["invalid_as_result"] = "run with device time stamps enabled (diagnostic)"
         print(json.dumps(out))
     note("done")
     sys.stdout.flush()
