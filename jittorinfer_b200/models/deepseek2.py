@@ -321,10 +321,10 @@ class DeepSeek2Model:
             return self.ep.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, shared)
         if self.comm is not None and self.spec.sharded:
             part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
-                               L.w_down_sh, base)
+                               L.w_down_sh, base, n_expert=hp.n_expert)
             return self.comm.all_reduce(part, residual)
         return ops.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
-                           L.w_down_sh, base)
+                           L.w_down_sh, base, n_expert=hp.n_expert)
 
     def _forward_sp(self, batch: ForwardBatch, kv_cache) -> torch.Tensor:
         """Tensor-parallel forward with a sequence-parallel residual stream (large prefill batches): every rank keeps

@@ -100,9 +100,10 @@ def moe_experts(x, ids, wts, wg, wu, wd, expert_base=0):
     return ref.moe_experts(x, ids, wts, wg, wu, wd, expert_base)
 
 
-def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0):
+def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0, n_expert=None):
+    """``n_expert``: size of the router's expert set (lets the CUDA path estimate how many local experts a batch hits)."""
     if use_native(x) and x.dtype == torch.bfloat16:
-        return nat().moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base)
+        return nat().moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base, n_expert)
     return ref.moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base)
 
 

@@ -23,6 +23,8 @@ PERMUTE_MULTI_MIN = 4096
 # Router logits + gating + expert sort in one launch for decode batches (<= 64 tokens): same state (cross-compiled, not
 # yet run on a GPU), off unless JIB_FUSED_ROUTE=1.
 FUSED_ROUTE = os.environ.get("JIB_FUSED_ROUTE", "0") == "1"
+# Grouped-GEMM split-K hint from the expected number of experts hit (off until measured: JIB_ACTIVE_HINT=1).
+ACTIVE_HINT_EXPECTED = os.environ.get("JIB_ACTIVE_HINT", "0") == "1"
 FUSED_ROUTE_MAX_T = 64
 _route_stash: Dict[tuple, tuple] = {}       # (ids ptr, expert_base, E_local) -> (seg, src, dest) produced by the fused launch
 
@@ -385,7 +387,17 @@ def moe_combine(y, dest, wts, shared, residual):
     return out
 
 
-def moe_routed(x, ids, wts, wg, wu, wd, expert_base=0):
+def expected_active_experts(T: int, k: int, E_local: int, n_expert: int) -> int:
+    """Expected number of distinct local experts that T tokens with k choices each out of n_expert hit (uniform routing);
+    columns beyond the router's k (merged shared experts: E_local > local share of n_expert) always count."""
+    always = max(0, E_local - n_expert) if E_local > n_expert else 0
+    routed_local = E_local - always
+    k_routed = max(1, k - always)
+    p_hit = 1.0 - (1.0 - min(1.0, k_routed / max(1, n_expert))) ** T
+    return max(1, min(E_local, always + int(routed_local * p_hit + 0.999)))
+
+
+def moe_routed(x, ids, wts, wg, wu, wd, expert_base=0, n_expert=None):
     """Expert-sorted rows -> grouped gate|up GEMM (SiLU*mul epilogue) -> grouped down GEMM.
     Returns (y [T*k, d] in sorted order, dest [T,k])."""
     T, k = ids.shape
@@ -393,6 +405,8 @@ def moe_routed(x, ids, wts, wg, wu, wd, expert_base=0):
     seg, src, dest = moe_permute(ids, expert_base, E_local)
     xp = gather_rows(x, src)
     active = min(E_local, T * k)
+    if ACTIVE_HINT_EXPECTED and n_expert:        # split-K sized for the experts a batch is expected to hit, not for all
+        active = min(active, expected_active_experts(T, k, E_local, n_expert))
     h = gemm_grouped(xp, seg, wg, wu, T, active)
     y = gemm_grouped(h, seg, wd, None, T, active)
     return y, dest
@@ -404,9 +418,9 @@ def moe_experts(x, ids, wts, wg, wu, wd, expert_base=0):
     return moe_combine(y, dest, wts, None, None).float()
 
 
-def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0):
+def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0, n_expert=None):
     """residual + shared_experts(x) + sum_k w_k expert_k(x), bf16; residual/shared may be None."""
-    y, dest = moe_routed(x, ids, wts, wg, wu, wd, expert_base)
+    y, dest = moe_routed(x, ids, wts, wg, wu, wd, expert_base, n_expert)
     shared = None
     if wgs is not None:
         shared = gemm(gemm(x, wgs, wus), wds)

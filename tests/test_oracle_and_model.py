@@ -233,3 +233,13 @@ def test_poisoned_free_blocks_never_reach_the_logits(monkeypatch):
         eng.step()
     eng.sched.step = real
     eng.cancel(rid)
+
+
+def test_expected_active_experts_hint():
+    """Split-K hint of the grouped GEMMs: expected distinct local experts under uniform routing (merged shared experts
+    always count)."""
+    from jittorinfer_b200.ops.native import expected_active_experts as f
+    assert f(8, 6, 20, 160) == 6            # V2, 8 ranks, 8 tokens: 20 * (1 - (1 - 6/160)^8) = 5.3
+    assert f(8, 8, 66, 64) == 37            # Lite with the two shared experts merged: 2 + 64 * (1 - (1 - 6/64)^8) = 36.9
+    assert f(1, 8, 66, 64) == 8 and f(1, 6, 160, 160) == 6
+    assert f(2048, 6, 20, 160) == 20 and f(64, 6, 20, 160) == 19
