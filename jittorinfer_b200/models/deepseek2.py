@@ -365,7 +365,7 @@ class DeepSeek2Model:
                 part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                                    L.w_down_sh, base)
                 x = comm.reduce_scatter_rows(part, y)
-        x_full = comm.all_gather_rows(x)
+        x_full = comm.all_gather_rows(x, final=True)
         xo = ops.select_rows(x_full, batch.out_rows) if batch.out_rows is not None else x_full[:T]
         xo, _ = ops.rmsnorm(xo, self.out_norm, hp.rms_eps)
         return ops.linear(xo, self.w_out, out_dtype=torch.float32)

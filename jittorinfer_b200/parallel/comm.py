@@ -61,7 +61,8 @@ class Communicator:
     # a communicator with in-kernel collectives overrides them.
     sp_min_tokens = int(os.environ.get("JITTORINFER_SP_MIN_TOKENS", "0"))      # 0 = sequence parallelism off
 
-    def all_gather_rows(self, x_loc: torch.Tensor) -> torch.Tensor:
+    def all_gather_rows(self, x_loc: torch.Tensor, final: bool = False) -> torch.Tensor:
+        """``final``: the gather after the last layer (matters to communicators that reuse buffers between passes)."""
         self.n_collectives += 1
         out = torch.empty(self.world * x_loc.shape[0], x_loc.shape[1], dtype=x_loc.dtype, device=x_loc.device)
         dist.all_gather_into_tensor(out, x_loc.contiguous(), group=self.group)
@@ -265,9 +266,14 @@ class FusedCommunicator(Communicator):
                                        torch.cuda.current_stream().cuda_stream)
         self.native._ck(rc, "allgather_rows")
 
-    def all_gather_rows(self, x_loc: torch.Tensor) -> torch.Tensor:
+    def all_gather_rows(self, x_loc: torch.Tensor, final: bool = False) -> torch.Tensor:
         R, d = x_loc.shape
         site = self._next_site()
+        if final:
+            # The gather buffer has two halves, chosen by bit 1 of the call site.  The next forward pass starts with a
+            # gather at site 0 (half 0) and nothing orders it after the other ranks' reads of this result, so the last
+            # gather of a pass goes to the one call site reserved for it, whose half is 1.
+            site = next(t for t in range(self.n_sites - 1, -1, -1) if (t >> 1) & 1)      # 4 * n_layer + 2 for a model's communicator
         if not self._sp_fits(R * self.world, d) or x_loc.dtype != torch.bfloat16:
             return Communicator.all_gather_rows(self, x_loc)
         self.n_collectives += 1
@@ -323,5 +329,6 @@ def make_communicator(device: torch.device, world: int, rank: int, d_model: int,
     if device.type != "cuda" or impl == "nccl":
         return Communicator(world, rank, group)
     large = int(os.environ.get("JITTORINFER_AR_LARGE_ROWS", "2048"))
-    # call sites per forward pass: 2 per layer (all-reduce form) or 4 per layer + 1 (sequence-parallel form)
-    return FusedCommunicator(device, world, rank, d_model, 4 * n_layer + 2, group=group, max_rows_large=large)
+    # call sites per forward pass: 2 per layer (all-reduce form) or 4 per layer (sequence-parallel form) plus the final
+    # gather, which uses site 4 * n_layer + 2 (a multiple of 4 plus 2: gather-buffer half 1)
+    return FusedCommunicator(device, world, rank, d_model, 4 * n_layer + 4, group=group, max_rows_large=large)

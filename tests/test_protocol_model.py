@@ -141,8 +141,12 @@ def ep_layer(rank, world, n_sites, n_epochs):
                 yield ("check", ("yret", rank, par, owner), tag)
 
 
-def sp_layers(rank, world, n_layers, n_epochs):
-    """Per layer: all-gather (site 4l), GEMM+reduce-scatter (4l+1), all-gather (4l+2), reduce-scatter (4l+3)."""
+def sp_layers(rank, world, n_layers, n_epochs, final_site=None):
+    """Per layer: all-gather (site 4l), GEMM+reduce-scatter (4l+1), all-gather (4l+2), reduce-scatter (4l+3); after the
+    last layer one more all-gather (the rows for the output head) at ``final_site`` (default 4 * n_layers + 2, whose
+    gather-buffer half differs from the half the next pass's first gather uses)."""
+    if final_site is None:
+        final_site = 4 * n_layers + 2
     def gather(site, epoch):
         par = (site >> 1) & 1
         for p in range(world):
@@ -173,6 +177,7 @@ def sp_layers(rank, world, n_layers, n_epochs):
                             yield ("store", ("flag2", p, site), epoch)
                     yield ("wait", lambda m, s=site, e=epoch: m.get(("flag2", rank, s)) == e)
                     yield ("check", ("out2", rank, par), (epoch, site))
+        yield from gather(final_site, epoch)
 
 
 PROTOCOLS = {
@@ -194,6 +199,19 @@ def test_no_interleaving_reads_stale_or_overwritten_data(name, world):
     for fast in range(world):                                   # one rank always runs when it can
         for seed in range(10):
             Sim([PROTOCOLS[name](r, world) for r in range(world)], 1000 + seed, bias=fast).run()
+
+
+def test_the_model_catches_a_final_gather_that_shares_its_half_with_the_next_pass():
+    """The gather after the last layer must not use the buffer half that the next forward pass's first gather uses: a
+    rank that runs ahead would overwrite rows a slower rank has not read yet.  Site 4 * n_layers has that flaw (half 0,
+    like site 0); the model finds it."""
+    tripped = 0
+    for seed in range(200):
+        try:
+            Sim([sp_layers(r, 2, 2, 3, final_site=8) for r in range(2)], seed, bias=seed % 2).run()
+        except AssertionError:
+            tripped += 1
+    assert tripped > 0
 
 
 def test_the_model_catches_a_protocol_without_double_buffering():
