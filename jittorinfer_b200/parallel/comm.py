@@ -273,7 +273,7 @@ class FusedCommunicator(Communicator):
             # The gather buffer has two halves, chosen by bit 1 of the call site.  The next forward pass starts with a
             # gather at site 0 (half 0) and nothing orders it after the other ranks' reads of this result, so the last
             # gather of a pass goes to the one call site reserved for it, whose half is 1.
-            site = next(t for t in range(self.n_sites - 1, -1, -1) if (t >> 1) & 1)      # 4 * n_layer + 2 for a model's communicator
+            site = next(t for t in range(self.n_sites - 1, -1, -1) if (t >> 1) & 1)      # the last site with bit 1 set
         if not self._sp_fits(R * self.world, d) or x_loc.dtype != torch.bfloat16:
             return Communicator.all_gather_rows(self, x_loc)
         self.n_collectives += 1
@@ -330,5 +330,5 @@ def make_communicator(device: torch.device, world: int, rank: int, d_model: int,
         return Communicator(world, rank, group)
     large = int(os.environ.get("JITTORINFER_AR_LARGE_ROWS", "2048"))
     # call sites per forward pass: 2 per layer (all-reduce form) or 4 per layer (sequence-parallel form) plus the final
-    # gather, which uses site 4 * n_layer + 2 (a multiple of 4 plus 2: gather-buffer half 1)
+    # gather, which takes a site of the spare group of four whose gather-buffer half is 1
     return FusedCommunicator(device, world, rank, d_model, 4 * n_layer + 4, group=group, max_rows_large=large)
