@@ -101,6 +101,8 @@ def main():
     ap.add_argument("--ops", default="native", choices=["native", "torch"], help="torch = PyTorch/cuBLAS baseline ops")
     ap.add_argument("--sweep", action="store_true", help="also report concurrency 1/2/4")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--run-ahead", action="store_true",
+                    help="launch decode step k+1 before the ids of step k reach the host (EngineConfig.run_ahead)")
     ap.add_argument("--timeline", action="store_true",
                     help="diagnostic (needs JITTORINFER_KERNELS_SO = the timeline build): report how long the fused all-reduces "
                          "wait for their peers during the timed steps; the stamps cost time, so the tokens/s of such a run is not a result")
@@ -148,7 +150,8 @@ def main():
             print(f"[bench +{time.time() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
 
     eng = build_engine(hp, device=dev, world=world, rank=rank, n_parallel=C, n_ctx_slot=total_len + 64,
-                       n_batch=2048, seed=0, graph_buckets=tuple(b for b in (1, 2, 4, 8, 16, 32, 64) if b <= max(C, 1)) or (1,))
+                       n_batch=2048, seed=0, graph_buckets=tuple(b for b in (1, 2, 4, 8, 16, 32, 64) if b <= max(C, 1)) or (1,),
+                       run_ahead=args.run_ahead)
     g = torch.Generator().manual_seed(1234)
 
     def prompts(n):
@@ -267,7 +270,8 @@ def main():
             "config": {"model": f"DeepSeek-V2{'-Lite' if model_name == 'lite' else ''} ({hp.n_layer} layers)" if model_name != "tiny" else "tiny",
                        "global_batch": C, "seq_len": total_len, "prompt_len": args.prompt_len, "gen_len": args.gen_len,
                        "parallelism": par, "l2": "weights (>= 30 GB per GPU) exceed L2; no flush needed",
-                       "timed": "K LLMEngine.step() decode steps: H2D step inputs + CUDA-graph replay + D2H sampled ids"},
+                       "timed": "K LLMEngine.step() decode steps: H2D step inputs + CUDA-graph replay + D2H sampled ids"
+                                + (" (one step in flight: ids are read one step late)" if args.run_ahead else "")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "graph_only_ms": graph_only_ms,
             "launches_per_step": launches // max(1, K),
         }

@@ -89,6 +89,9 @@ JIB_API int jib_sched_step(jib_sched * s, StepArrays * arrays, int32_t * info_ou
     return i.n_tokens;
 }
 JIB_API void jib_sched_commit(jib_sched * s, const int32_t * sampled, int n_out) { s->sched.commit(sampled, n_out, &s->events); }
+JIB_API int jib_sched_can_run_ahead(jib_sched * s) { return s->sched.can_run_ahead() ? 1 : 0; }
+JIB_API void jib_sched_commit_deferred(jib_sched * s, int n_out) { s->sched.commit_deferred(n_out); }
+JIB_API void jib_sched_resolve(jib_sched * s, const int32_t * sampled, int n_out) { s->sched.resolve(sampled, n_out, &s->events); }
 // Pops queued events; each is 6 x int64: req_id, slot, token, finish, n_prompt, n_decoded.
 JIB_API int jib_sched_take_events(jib_sched * s, int64_t * out, int cap) {
     int n = std::min<int>((int) s->events.size(), cap);

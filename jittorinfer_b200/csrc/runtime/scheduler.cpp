@@ -284,4 +284,67 @@ void Scheduler::commit(const int32_t * sampled, int n_out, std::vector<StepEvent
     last_out_slots_.clear();
 }
 
+bool Scheduler::can_run_ahead() const {
+    if (!waiting_.empty() || !deferred_.empty()) return false;
+    int active = 0, new_blocks = 0;
+    for (const auto & s : slots_) {
+        if (s.state == SLOT_IDLE) continue;
+        if (s.out_row < 0) return false;                   // still inside its prompt: the next step is not a pure decode step
+        ++active;
+        new_blocks += kv_->blocks_needed(s.id, 1);         // incl. a copy-on-write block
+    }
+    // every block the next step can ask for is free now: nothing is evicted, nobody is preempted
+    return active > 0 && active == (int) last_out_slots_.size() && new_blocks <= kv_->free_blocks();
+}
+
+void Scheduler::commit_deferred(int n_out) {
+    deferred_.clear();
+    for (int i = 0; i < n_out && i < (int) last_out_slots_.size(); ++i) {
+        Slot & s = slots_[last_out_slots_[i]];
+        Deferred d{s.id, s.req_id, FINISH_NONE, s.n_prompt_orig, 0, s.n_past};
+        if (s.state == SLOT_IDLE) {                        // cancelled since the step was assembled: nothing to resolve
+            d.req_id = -1;
+            deferred_.push_back(d);
+            continue;
+        }
+        ++s.n_decoded;
+        ++stats_.decode_tokens;
+        s.state = SLOT_GENERATING;
+        s.pending_token = TOKEN_UNKNOWN;
+        d.n_decoded = s.n_decoded;
+        if (s.max_new >= 0 && s.n_decoded >= s.max_new) d.finish = FINISH_LENGTH;
+        else if (s.n_past + 1 >= n_ctx_slot_) d.finish = FINISH_LENGTH;
+        if (d.finish != FINISH_NONE) {
+            ++stats_.finished;
+            release(s, true);
+        }
+        deferred_.push_back(d);
+    }
+    last_out_slots_.clear();
+}
+
+void Scheduler::resolve(const int32_t * sampled, int n_out, std::vector<StepEvent> * events) {
+    for (int i = 0; i < n_out && i < (int) deferred_.size(); ++i) {
+        const Deferred & d = deferred_[i];
+        if (d.req_id < 0) continue;
+        const int32_t tok = sampled[i];
+        if (d.finish != FINISH_NONE) {                     // ended by a length limit: the slot is free already
+            if (events) events->push_back({d.req_id, d.slot, tok, d.finish, d.n_prompt, d.n_decoded});
+            continue;
+        }
+        Slot & s = slots_[d.slot];
+        if (s.state == SLOT_IDLE || s.req_id != d.req_id) continue;       // cancelled meanwhile (its event is out already)
+        if (s.pending_token == TOKEN_UNKNOWN) s.pending_token = tok;
+        else if (d.token_index < (int) s.tokens.size() && s.tokens[d.token_index] == TOKEN_UNKNOWN) s.tokens[d.token_index] = tok;
+        int finish = FINISH_NONE;
+        if (!s.ignore_eos && tok == eos_id_) finish = FINISH_STOP;
+        if (events) events->push_back({d.req_id, d.slot, tok, finish, d.n_prompt, d.n_decoded});
+        if (finish != FINISH_NONE) {
+            ++stats_.finished;
+            release(s, true);                              // a step that already carries this slot's next token drops its output
+        }
+    }
+    deferred_.clear();
+}
+
 }  // namespace jib

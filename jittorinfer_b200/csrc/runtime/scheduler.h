@@ -92,6 +92,21 @@ class Scheduler {
     // Feeds the sampled token of every output row of the last step() back; appends events.
     void commit(const int32_t * sampled, int n_out, std::vector<StepEvent> * events);
 
+    // ---- running one step ahead of the sampled ids ------------------------------------------------------------------
+    // With greedy sampling on the device the ids of a step are not needed on the host to launch the next decode step:
+    // the device feeds them forward itself.  commit_deferred() does what commit() does for a step whose ids are still
+    // on their way (counts, length limits, slot release), marking the tokens TOKEN_UNKNOWN; resolve() later supplies
+    // the ids in the same order, patches the token histories, applies the end-of-sequence rule (a sequence that ended
+    // has then been fed one token too many, whose output is dropped) and appends the events.  At most one deferred
+    // commit may be outstanding.  can_run_ahead() tells whether the next step() can be assembled without knowing the
+    // ids of the last step: every active slot produced an output in it, nothing waits for a slot, and no step() can
+    // run out of blocks (so nothing with an unknown token is ever preempted or re-queued).
+    static constexpr int32_t TOKEN_UNKNOWN = -2;
+    bool can_run_ahead() const;
+    void commit_deferred(int n_out);
+    void resolve(const int32_t * sampled, int n_out, std::vector<StepEvent> * events);
+    int n_deferred() const { return (int) deferred_.size(); }
+
     bool idle() const;
     int n_waiting() const { return (int) waiting_.size(); }
     int n_running() const;
@@ -116,6 +131,14 @@ class Scheduler {
     int64_t clock_ = 0;
     std::vector<int32_t> last_out_slots_;
     SchedStats stats_;
+    struct Deferred {
+        int32_t slot;
+        int64_t req_id;
+        int32_t finish;        // decided at commit time (length limits) or FINISH_NONE
+        int32_t n_prompt, n_decoded;
+        int32_t token_index;   // where the token lands in the slot's history once it is scheduled
+    };
+    std::vector<Deferred> deferred_;
 };
 
 }  // namespace jib

@@ -45,6 +45,8 @@ class EngineConfig:
     cuda_graphs: bool = True
     graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
     defrag_thold: float = -1.0         # <0 disables automatic defrag
+    run_ahead: bool = False            # greedy requests: launch decode step k+1 before the ids of step k reach the host
+                                       # (also JITTORINFER_RUN_AHEAD=1)
     defrag_max_moves: int = 256
 
 
@@ -59,6 +61,16 @@ class RequestState:
     t_submit: float = 0.0
     t_first: float = 0.0
     t_done: float = 0.0
+
+
+@dataclass
+class _InFlight:
+    """A launched step whose sampled ids have not been read yet."""
+    out: torch.Tensor                  # device ids (a graph's static output or an eager result)
+    host: torch.Tensor                 # pinned buffer the ids are being copied into
+    event: Optional[object]            # CUDA event after that copy (None on the CPU)
+    n_out: int
+    out_slots: np.ndarray              # scheduler slot of each output row
 
 
 class _StepIO:
@@ -78,16 +90,29 @@ class _StepIO:
         # seq_slots / out_slots are host-only: the device copy stops before them
         self.dev_len = self.off["seq_slots"][0]
         pin = device.type == "cuda"
-        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
+        self._pin = pin
         self.dev = torch.zeros(self.dev_len, dtype=torch.int32, device=device)
-        self.np = self.host.numpy()
-        self.h = {k: self.np[o:o + n] for k, (o, n) in self.off.items()}
         self.d = {k: self.dev[o:o + n] for k, (o, n) in self.off.items() if o < self.dev_len}
-        self.arrays = StepArrays()
+        self._stages = [self._make_stage()]
+        self.use_stage(0)
+
+    def _make_stage(self):
+        host = torch.zeros(self.total, dtype=torch.int32, pin_memory=self._pin)
+        arr = host.numpy()
+        h = {k: arr[o:o + n] for k, (o, n) in self.off.items()}
+        arrays = StepArrays()
         for k in ("tokens", "positions", "slot_mapping", "q_start", "seq_lens", "seq_slots", "block_tables", "out_rows",
                   "out_slots"):
-            setattr(self.arrays, k, self.h[k].ctypes.data_as(i32p))
-        self.arrays.cap_tokens, self.arrays.cap_seqs, self.arrays.max_blocks_per_seq = cap_tokens, cap_seqs, max_blocks
+            setattr(arrays, k, h[k].ctypes.data_as(i32p))
+        arrays.cap_tokens, arrays.cap_seqs, arrays.max_blocks_per_seq = self.cap_tokens, self.cap_seqs, self.max_blocks
+        return host, arr, h, arrays
+
+    def use_stage(self, i: int) -> None:
+        """Selects the pinned host buffer the next step is assembled in.  A second stage exists only when the engine runs
+        one step ahead: the asynchronous upload of step k may still be reading its buffer while step k + 1 is assembled."""
+        while len(self._stages) <= i:
+            self._stages.append(self._make_stage())
+        self.host, self.np, self.h, self.arrays = self._stages[i]
 
     def upload(self):
         self.dev.copy_(self.host[: self.dev_len], non_blocking=True)
@@ -171,6 +196,13 @@ class LLMEngine:
         self._idle_graph = None
         self.tracer = Tracer()            # JSON-lines step trace when JITTORINFER_TRACE names a file
         self._pressure = False            # free KV blocks held back by the kv_alloc fault site
+        self._run_ahead = bool(cfg.run_ahead or os.environ.get("JITTORINFER_RUN_AHEAD", "") == "1") and not self.dp \
+            and not getattr(model, "split", False)
+        self._inflight: Optional[_InFlight] = None
+        self._stage = 0
+        self._out_hosts = [self._out_host, torch.zeros_like(self._out_host).pin_memory() if self.device.type == "cuda"
+                           else torch.zeros_like(self._out_host)] if self._run_ahead else [self._out_host]
+        self._flip = 0
         # Debug aid: JITTORINFER_KV_POISON=1 fills every cache block with NaN when its last reference goes away and checks the
         # logits of every (then eager) step: a read through a stale block table cannot pass unnoticed.
         self._poison = os.environ.get("JITTORINFER_KV_POISON", "") == "1"
@@ -204,7 +236,7 @@ class LLMEngine:
         return ok
 
     def has_work(self) -> bool:
-        return not self.sched.idle()
+        return not self.sched.idle() or self._inflight is not None
 
     # ------------------------------------------------------------------------------------------
     def _batch_views(self, n_tokens: int, n_seqs: int, n_out: int, max_q_len: int) -> ForwardBatch:
@@ -294,6 +326,7 @@ class LLMEngine:
                                cfg.cont_batching)
         self.requests.clear()
         self._pressure = False
+        self._inflight = None
         if self._poison:
             self.kv.track_freed(True)
         self.stats["resets"] = self.stats.get("resets", 0) + 1
@@ -376,9 +409,165 @@ class LLMEngine:
             out.append((rid, tok, fin))
         return out
 
-    @torch.no_grad()
     def step(self) -> List[Tuple[int, int, Optional[str]]]:
         """Runs one engine step. Returns [(req_id, new_token, finish_reason_or_None)]."""
+        if self._run_ahead:
+            return self._step_ahead()
+        return self._step_sync()
+
+    # ---- running one step ahead (opt-in) -----------------------------------------------------------------------------
+    # With greedy sampling on the device, the ids a step produces are the next step's input tokens: they can stay on the
+    # device.  The engine then launches decode step k + 1 (its token buffer filled by a device copy from step k's output)
+    # before it reads step k's ids, so the host's share of a step -- scheduling, packing, the upload, the graph launch and
+    # the read-back -- overlaps the device's.  Events reach the caller one step later.  What cannot be known without the
+    # ids is the end-of-sequence token: a sequence that produced it has by then been fed one token too many; that
+    # output is dropped (Scheduler::resolve).  Whenever the next step is not a pure decode step of the same sequences
+    # (a waiting request, a prompt chunk, scarce blocks, a sampler that needs the host), the engine first reads the ids
+    # and continues synchronously.
+    def _all_greedy(self) -> bool:
+        return all(st.sampler is None for st in self.requests.values() if st.finish_reason is None)
+
+    def _collect(self, infl: _InFlight) -> np.ndarray:
+        if infl.event is not None:
+            infl.event.synchronize()
+        self.stats["d2h_bytes"] += infl.n_out * 4
+        return infl.host[:infl.n_out].numpy().astype(np.int32, copy=True)
+
+    def _launch_greedy(self, n_tokens: int, n_seqs: int, n_out: int, max_q: int, feedback: Optional[_InFlight]) -> _InFlight:
+        io = self.io
+        use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets) \
+            and getattr(self.model, "tensor_hook", None) is None
+        bucket = next(b for b in self.cfg.graph_buckets if b >= n_seqs) if use_graph else 0
+        if use_graph and bucket > n_seqs:
+            h = io.h
+            h["tokens"][n_seqs:bucket] = 0
+            h["positions"][n_seqs:bucket] = 0
+            h["slot_mapping"][n_seqs:bucket] = -1
+            h["seq_lens"][n_seqs:bucket] = 0
+            h["q_start"][n_seqs:bucket + 1] = np.arange(n_seqs, bucket + 1)
+            h["out_rows"][n_out:bucket] = np.arange(n_out, bucket)
+            h["block_tables"][n_seqs * self.max_blocks: bucket * self.max_blocks] = 0
+        io.upload()
+        if feedback is not None:
+            # this step's tokens are the ids the step in flight sampled: a device-to-device copy, in output-row order
+            row_of = {int(sl): i for i, sl in enumerate(feedback.out_slots)}
+            src = np.fromiter((row_of[int(sl)] for sl in io.h["seq_slots"][:n_seqs]), dtype=np.int64, count=n_seqs)
+            prev = feedback.out.reshape(-1)
+            if np.array_equal(src, np.arange(n_seqs)):
+                io.d["tokens"][:n_seqs].copy_(prev[:n_seqs])
+            else:
+                io.d["tokens"][:n_seqs].copy_(prev.index_select(0, torch.from_numpy(src).to(prev.device)))
+        if use_graph:
+            g, out = self._graph_for(bucket, "greedy")
+            g.replay()
+            self.launches += self.graph_launches.get((bucket, "greedy"), 0)
+            self.stats["graph_steps"] += 1
+        else:
+            batch = self._batch_views(n_tokens, n_seqs, n_out, max_q)
+            n0 = ops.nat().launch_count if self.device.type == "cuda" and not ops.force_torch() else 0
+            out = self._forward_sample(batch, "greedy")
+            if self.device.type == "cuda" and not ops.force_torch():
+                self.launches += ops.nat().launch_count - n0
+            self.stats["eager_steps"] += 1
+        host = self._out_hosts[self._flip]
+        self._flip ^= 1
+        host[:n_out].copy_(out.reshape(-1)[:n_out], non_blocking=True)
+        event = None
+        if self.device.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+        self.stats["steps"] += 1
+        self.stats["tokens_in"] += n_tokens
+        self.stats["tokens_out"] += n_out
+        self.stats["h2d_bytes"] += io.h2d_bytes
+        return _InFlight(out, host, event, n_out, io.h["out_slots"][:n_out].copy())
+
+    def _trace_ahead(self, pt, ev, launched, n_tokens=0, n_seqs=0, n_out=0, max_q=0) -> None:
+        """Step trace of the run-ahead path: "step" for a call that launched one (its events belong to the step before),
+        "collect" for a call that only read the ids of the step in flight."""
+        if pt is None:
+            return
+        pt.mark("finish")
+        common = dict(kv_used=self.kv.used_blocks, kv_total=self.n_blocks, waiting=self.sched.n_waiting(),
+                      running=self.sched.n_running(), finished=sum(1 for e in ev if e[2] is not None), phase_ms=pt.ms)
+        if launched:
+            self.tracer.emit("step", step=self.stats["steps"], tokens=n_tokens, seqs=n_seqs, outputs=n_out, max_q=max_q,
+                             mode="ahead", frag=round(self.kv.fragmentation(), 4), **common)
+        else:
+            self.tracer.emit("collect", **common)
+
+    @torch.no_grad()
+    def _step_ahead(self) -> List[Tuple[int, int, Optional[str]]]:
+        io, infl = self.io, self._inflight
+        pt = PhaseTimer() if self.tracer.enabled else None
+        usable = self._all_greedy() and not self._poison and not fault.armed("kv_alloc") and not fault.armed("engine_step")
+        if not usable:                       # finish what is in flight, then step the ordinary way (its events are queued)
+            if infl is not None:
+                self.sched.commit(self._collect(infl), infl.n_out)
+                self._inflight = None
+            return self._step_sync()
+        if infl is not None:
+            if self.sched.can_run_ahead():
+                self.sched.commit_deferred(infl.n_out)
+                self._stage ^= 1
+                io.use_stage(self._stage)
+                info = self.sched.step(io.arrays)
+                n_tokens, n_seqs, n_out, _, max_q, _, n_copies = (int(x) for x in info[:7])
+                if pt:
+                    pt.mark("schedule")
+                nxt = None
+                if n_tokens > 0:
+                    if n_copies:
+                        src, dst = self.kv.take_copies()
+                        self._copy_blocks(src, dst)
+                    nxt = self._launch_greedy(n_tokens, n_seqs, n_out, max_q, infl)
+                    self.stats["run_ahead_steps"] = self.stats.get("run_ahead_steps", 0) + 1
+                if pt:
+                    pt.mark("launch")
+                self.sched.resolve(self._collect(infl), infl.n_out)
+                self._inflight = nxt
+                if pt:
+                    pt.mark("wait")
+                ev = self._drain_events()
+                self._maybe_defrag()
+                self._trace_ahead(pt, ev, nxt is not None, n_tokens, n_seqs, n_out, max_q)
+                return ev
+            self.sched.commit(self._collect(infl), infl.n_out)
+            self._inflight = None
+            ev = self._drain_events()
+            self._maybe_defrag()
+            self._trace_ahead(pt, ev, False)
+            return ev
+        self._stage ^= 1
+        io.use_stage(self._stage)
+        info = self.sched.step(io.arrays)
+        n_tokens, n_seqs, n_out, _, max_q, _, n_copies = (int(x) for x in info[:7])
+        if n_tokens == 0:
+            return self._drain_events()
+        if pt:
+            pt.mark("schedule")
+        if n_copies:
+            src, dst = self.kv.take_copies()
+            self._copy_blocks(src, dst)
+        if n_out == 0:                       # a prompt chunk without an output row: nothing to wait for
+            io.upload()
+            self.model.forward(self._batch_views(n_tokens, n_seqs, 0, max_q), self.kv_cache)
+            self.stats["steps"] += 1
+            self.stats["eager_steps"] += 1
+            self.stats["tokens_in"] += n_tokens
+            self.stats["h2d_bytes"] += io.h2d_bytes
+            self.sched.commit(np.empty(0, dtype=np.int32), 0)
+        else:
+            self._inflight = self._launch_greedy(n_tokens, n_seqs, n_out, max_q, None)
+        if pt:
+            pt.mark("launch")
+        ev = self._drain_events()
+        self._maybe_defrag()
+        self._trace_ahead(pt, ev, True, n_tokens, n_seqs, n_out, max_q)
+        return ev
+
+    @torch.no_grad()
+    def _step_sync(self) -> List[Tuple[int, int, Optional[str]]]:
         io = self.io
         fault.check("engine_step")
         if self._pressure:

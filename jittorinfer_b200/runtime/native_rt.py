@@ -75,6 +75,9 @@ def lib():
         sig("jib_sched_cancel", C.c_int, vp, C.c_int64)
         sig("jib_sched_step", C.c_int, vp, C.POINTER(StepArrays), i32p)
         sig("jib_sched_commit", None, vp, i32p, C.c_int)
+        sig("jib_sched_can_run_ahead", C.c_int, vp)
+        sig("jib_sched_commit_deferred", None, vp, C.c_int)
+        sig("jib_sched_resolve", None, vp, i32p, C.c_int)
         sig("jib_sched_take_events", C.c_int, vp, i64p, C.c_int)
         for n in ("idle", "n_waiting", "n_running"):
             sig("jib_sched_" + n, C.c_int, vp)
@@ -192,6 +195,16 @@ class Scheduler:
 
     def commit(self, sampled: np.ndarray, n_out: int):
         self._L.jib_sched_commit(self._h, _p32(sampled), n_out)
+
+    # running one step ahead of the sampled ids (csrc/runtime/scheduler.h)
+    def can_run_ahead(self) -> bool:
+        return bool(self._L.jib_sched_can_run_ahead(self._h))
+
+    def commit_deferred(self, n_out: int) -> None:
+        self._L.jib_sched_commit_deferred(self._h, n_out)
+
+    def resolve(self, sampled: np.ndarray, n_out: int) -> None:
+        self._L.jib_sched_resolve(self._h, _p32(sampled), n_out)
 
     def take_events(self) -> List[Tuple[int, int, int, Optional[str], int, int]]:
         n = self._L.jib_sched_take_events(self._h, self._ev.ctypes.data_as(i64p), len(self._ev) // 6)

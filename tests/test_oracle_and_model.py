@@ -243,3 +243,93 @@ def test_expected_active_experts_hint():
     assert f(8, 8, 66, 64) == 37            # Lite with the two shared experts merged: 2 + 64 * (1 - (1 - 6/64)^8) = 36.9
     assert f(1, 8, 66, 64) == 8 and f(1, 6, 160, 160) == 6
     assert f(2048, 6, 20, 160) == 20 and f(64, 6, 20, 160) == 19
+
+
+def _run_ahead_engine(hp, w, **kw):
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    return LLMEngine(m, EngineConfig(n_ctx=2048, n_batch=64, n_parallel=4, n_ctx_slot=256, run_ahead=True, **kw))
+
+
+def test_run_ahead_decoding_matches_the_oracle():
+    """The engine launches decode step k + 1 before it has read the ids of step k (greedy requests): same tokens as the
+    oracle for requests of different lengths (they leave the batch at different steps), with a request that joins in
+    mid-stream, one that is cancelled while a step is in flight, and an end-of-sequence stop."""
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    o = OracleModel(hp, w)
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (9, 33, 70, 5)]
+    news = (20, 7, 13, 1)
+    eng = _run_ahead_engine(hp, w)
+    ids = [eng.add_request(p, SamplingParams(ignore_eos=True, max_tokens=n)) for p, n in zip(prompts, news)]
+    late = None
+    victim = eng.add_request(prompts[0][:6], SamplingParams(ignore_eos=True, max_tokens=40))      # waits for a free slot
+    n_calls = 0
+    while eng.has_work():
+        eng.step()
+        n_calls += 1
+        if n_calls == 6:
+            late = eng.add_request(prompts[1][:12], SamplingParams(ignore_eos=True, max_tokens=9))
+        if n_calls == 14:
+            eng.cancel(victim)
+        assert n_calls < 400
+    for rid, p, n in zip(ids, prompts, news):
+        assert eng.requests[rid].output == o.generate(p, n), (rid, n)
+        assert eng.requests[rid].finish_reason == "length"
+    assert eng.requests[late].output == o.generate(prompts[1][:12], 9)
+    v = eng.requests[victim]
+    assert v.finish_reason == "cancelled" and v.output == o.generate(prompts[0][:6], 40)[:len(v.output)]
+    assert eng.stats.get("run_ahead_steps", 0) >= 10 and eng.kv.check()
+
+    # end of sequence: declare a token that the model is known to produce mid-way the end-of-sequence token
+    ref = o.generate(prompts[2], 13)
+    eos = ref[6]
+    stop_at = ref.index(eos)
+    hp2 = hp.replace(eos_id=eos)
+    eng2 = _run_ahead_engine(hp2, w)
+    a = eng2.add_request(prompts[2], SamplingParams(max_tokens=13))
+    b = eng2.add_request(prompts[0], SamplingParams(ignore_eos=True, max_tokens=20))
+    while eng2.has_work():
+        eng2.step()
+    assert eng2.requests[a].output == ref[:stop_at + 1] and eng2.requests[a].finish_reason == "stop"
+    assert eng2.requests[b].output == o.generate(prompts[0], 20)
+    # the slot that ended early can be reused with its cached prefix
+    c = eng2.add_request(prompts[2], SamplingParams(ignore_eos=True, max_tokens=5))
+    while eng2.has_work():
+        eng2.step()
+    assert eng2.requests[c].output == ref[:5] and eng2.kv.check()
+    # the synchronous engine gives the same events, one step earlier
+    eng3 = LLMEngine(DeepSeek2Model(hp, w.items(), dtype=torch.float32), EngineConfig(n_ctx=2048, n_batch=64, n_parallel=4, n_ctx_slot=256))
+    assert eng3.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=6) == \
+        _run_ahead_engine(hp, w).generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=6)
+
+
+def test_run_ahead_under_kv_pressure_and_with_a_host_sampler(tmp_path, monkeypatch):
+    """Scarce blocks (preemption possible) and a request whose sampler runs on the host both make the engine read the ids
+    before it plans the next step; outputs stay those of the oracle, and the step trace covers the run-ahead calls."""
+    from jittorinfer_b200.utils.trace import Tracer
+    monkeypatch.setenv("JITTORINFER_TRACE", str(tmp_path / "t.jsonl"))
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    o = OracleModel(hp, w)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    eng = LLMEngine(m, EngineConfig(n_ctx=640, n_batch=96, n_parallel=6, n_ctx_slot=256, defrag_thold=0.05, run_ahead=True))
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (150, 90, 170, 40, 120, 60, 200, 30)]
+    outs = eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=24)
+    assert outs == [o.generate(p, 24) for p in prompts]
+    assert eng.sched.stats()["preemptions"] >= 1 and eng.kv.check()
+    # a sampled (non-greedy) request next to a greedy one: the greedy one is unaffected
+    a = eng.add_request(prompts[3], SamplingParams(ignore_eos=True, max_tokens=10))
+    b = eng.add_request(prompts[5], SamplingParams(ignore_eos=True, max_tokens=10, temperature=0.9, seed=3))
+    while eng.has_work():
+        eng.step()
+    assert eng.requests[a].output == o.generate(prompts[3], 10) and len(eng.requests[b].output) == 10
+    ahead_before = eng.stats.get("run_ahead_steps", 0)
+    assert eng.generate(prompts[3:5], SamplingParams(ignore_eos=True), max_new_tokens=12) == [o.generate(p, 12) for p in prompts[3:5]]
+    assert eng.stats["run_ahead_steps"] >= ahead_before + 8          # with room in the cache the engine runs ahead again
+    eng.tracer.close()
+    recs = Tracer.read(str(tmp_path / "t.jsonl"))
+    steps = [r for r in recs if r["kind"] == "step"]
+    assert len(steps) == eng.stats["steps"] and any(r["mode"] == "ahead" for r in steps)
+    assert sum(r["finished"] for r in recs if r["kind"] in ("step", "collect")) == len(prompts) + 4

@@ -134,3 +134,64 @@ def test_multi_cta_expert_sort_algorithm_matches_a_stable_sort():
         assert np.array_equal(dest, want)
         assert np.array_equal(src[:len(order)], order // k) and np.all(src[len(order):] == -1)
         assert seg[-1] == len(order)
+
+
+def test_scheduler_deferred_commit_gives_the_synchronous_events():
+    """commit_deferred / resolve (the engine runs one step ahead of the sampled ids): the same requests, with a
+    deterministic "sampler" that depends on the request and its step, end with the same tokens and reasons as with
+    commit(); the unknown-token marker never survives in a slot's history; an end-of-sequence token costs exactly one
+    extra fed token, whose output is dropped."""
+    EOS = 7
+
+    def sample(rid, n):                                  # request 2 produces the end-of-sequence token as its 4th token
+        return EOS if (rid == 2 and n == 3) else 100 + 10 * rid + n
+
+    def run(deferred):
+        kv = PagedKV(64, 16, 4)
+        sched = Scheduler(kv, 4, 64, 256, EOS)
+        io = _StepIO(64, 4, 16, torch.device("cpu"))
+        sched.add(1, list(range(20, 40)), max_new=9)
+        sched.add(2, list(range(40, 45)), max_new=30)
+        sched.add(3, list(range(50, 83)), max_new=3, ignore_eos=True)
+        count, out, fed, pending = {}, {}, 0, None
+        for _ in range(200):
+            if pending is not None and deferred and sched.can_run_ahead():
+                sched.commit_deferred(len(pending))
+                info = sched.step(io.arrays)
+                fed += int(info[0])
+                nxt = None
+                if int(info[0]):
+                    assert (io.h["tokens"][:int(info[0])] == -2).all()          # only ids still on the device are fed
+                    nxt = [int(r) for r in sched.out_reqs(int(info[2]))]
+                toks = np.array([sample(r, count.setdefault(r, 0)) for r in pending], dtype=np.int32)
+                for r in pending:
+                    count[r] += 1
+                sched.resolve(toks, len(pending))
+                pending = nxt
+            else:
+                if pending is not None:
+                    toks = np.array([sample(r, count.setdefault(r, 0)) for r in pending], dtype=np.int32)
+                    for r in pending:
+                        count[r] += 1
+                    sched.commit(toks, len(pending))
+                    pending = None
+                else:
+                    info = sched.step(io.arrays)
+                    fed += int(info[0])
+                    if int(info[0]) == 0 and sched.idle():
+                        break
+                    if int(info[2]):
+                        pending = [int(r) for r in sched.out_reqs(int(info[2]))]
+                    else:
+                        sched.commit(np.empty(0, dtype=np.int32), 0)
+            for rid, slot, tok, fin, npmt, ndec in sched.take_events():
+                out.setdefault(rid, []).append((tok, fin))
+        assert kv.check() and sched.idle()
+        return out, fed
+
+    sync, fed_sync = run(False)
+    ahead, fed_ahead = run(True)
+    assert sync == ahead
+    assert [t for t, _ in sync[2]] == [120, 121, 122, EOS] and sync[2][-1][1] == "stop"
+    assert len(sync[1]) == 9 and sync[1][-1][1] == "length" and len(sync[3]) == 3
+    assert fed_ahead == fed_sync + 1                     # the token fed to request 2 after its end-of-sequence token
