@@ -89,6 +89,9 @@ JIB_EXPORT int jib_moe_permute_multi(const int * ids, int T, int k, int expert_b
                                      int * tmp, void * stream);
 JIB_EXPORT int jib_moe_combine(const void * y, const int * dest, const float * wts, const void * shared, const void * residual,
                                void * out, int T, int k, int d, void * stream);
+// The same followed by RMSNorm(out) * norm_w (fp32 weights, as jib_rmsnorm) in one launch; bitwise the two-launch results.
+JIB_EXPORT int jib_moe_combine_norm(const void * y, const int * dest, const float * wts, const void * shared, const void * residual,
+                                    const float * norm_w, void * out, void * out_norm, int T, int k, int d, float eps, void * stream);
 
 // ---- attention (mla_attention.cu) -------------------------------------------------------------
 // Split-KV absorbed MLA over the paged latent cache. q [T][H][r+dr] bf16; o_lat [T][H][r] bf16.

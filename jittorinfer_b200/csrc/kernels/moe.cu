@@ -557,6 +557,108 @@ __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __re
     }
 }
 
+// ---- combine fused with the RMSNorm that follows it (the next block's attention norm) ---------------------------------
+// One CTA per token keeps the token's whole output row in registers: out = bf16(residual + shared + sum_j w_j y_j) as
+// moe_combine_kernel computes it, then out_norm = rmsnorm(out) * norm_w from the bf16-rounded values, with the thread
+// mapping and reduction order of rmsnorm_kernel<NT, MAXV> (elementwise.cu), so both results equal the two-launch path
+// bit for bit.  One launch fewer per MoE layer.
+template <int NT>
+__device__ __forceinline__ float block_sum_nt(float v, float * red) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    float t = l < NT / 32 ? red[l] : 0.f;
+    t = warp_sum(t);
+    __syncthreads();
+    return t;
+}
+
+template <int NT, int MAXV>
+__global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest,
+                                                              const float * __restrict__ wts, const bf16 * __restrict__ shared,
+                                                              const bf16 * __restrict__ residual, const float * __restrict__ norm_w,
+                                                              bf16 * __restrict__ out, bf16 * __restrict__ out_norm, int k, int d,
+                                                              float eps) {
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int nv = d / 8;
+    float vals[MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < MAXV; ++it) {
+        const int i = threadIdx.x + it * NT;
+        if (i < nv) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int j = 0; j < k; ++j) {
+                const int row = dest[(size_t) t * k + j];
+                if (row < 0) continue;
+                const float w = wts[(size_t) t * k + j];
+                const uint4 raw = ((const uint4 *) (y + (size_t) row * d))[i];
+                const __nv_bfloat162 * p = (const __nv_bfloat162 *) &raw;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __bfloat1622float2(p[q]);
+                    acc[2 * q] += w * f.x;
+                    acc[2 * q + 1] += w * f.y;
+                }
+            }
+            if (shared) {
+                const uint4 raw = ((const uint4 *) (shared + (size_t) t * d))[i];
+                const __nv_bfloat162 * p = (const __nv_bfloat162 *) &raw;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __bfloat1622float2(p[q]);
+                    acc[2 * q] += f.x;
+                    acc[2 * q + 1] += f.y;
+                }
+            }
+            if (residual) {
+                const uint4 raw = ((const uint4 *) (residual + (size_t) t * d))[i];
+                const __nv_bfloat162 * p = (const __nv_bfloat162 *) &raw;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __bfloat1622float2(p[q]);
+                    acc[2 * q] += f.x;
+                    acc[2 * q + 1] += f.y;
+                }
+            }
+            uint4 o;
+            __nv_bfloat162 * po = (__nv_bfloat162 *) &o;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) po[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+            ((uint4 *) (out + (size_t) t * d))[i] = o;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {                 // the norm sees what the next kernel would have read back
+                const float2 f = __bfloat1622float2(po[q]);
+                vals[it][2 * q] = f.x;
+                vals[it][2 * q + 1] = f.y;
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+    ss = block_sum_nt<NT>(ss, red);
+    const float inv = rsqrtf(ss / (float) d + eps);
+#pragma unroll
+    for (int it = 0; it < MAXV; ++it) {
+        const int i = threadIdx.x + it * NT;
+        if (i < nv) {
+            const float4 w0 = ((const float4 *) norm_w)[2 * i], w1 = ((const float4 *) norm_w)[2 * i + 1];
+            uint4 o;
+            __nv_bfloat162 * po = (__nv_bfloat162 *) &o;
+            po[0] = __floats2bfloat162_rn(vals[it][0] * inv * w0.x, vals[it][1] * inv * w0.y);
+            po[1] = __floats2bfloat162_rn(vals[it][2] * inv * w0.z, vals[it][3] * inv * w0.w);
+            po[2] = __floats2bfloat162_rn(vals[it][4] * inv * w1.x, vals[it][5] * inv * w1.y);
+            po[3] = __floats2bfloat162_rn(vals[it][6] * inv * w1.z, vals[it][7] * inv * w1.w);
+            ((uint4 *) (out_norm + (size_t) t * d))[i] = o;
+        }
+    }
+}
+
 inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH; }
 
 }  // namespace
@@ -618,6 +720,25 @@ int jib_moe_combine(const void * y, const int * dest, const float * wts, const v
     if (d % 8) return JIB_E_ARG;
     JIB_LAUNCH((moe_combine_kernel), T, 256, 0, (cudaStream_t) stream, (const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual,
                                                               (bf16 *) out, k, d);
+    return launched();
+}
+
+// jib_moe_combine followed by jib_rmsnorm(out, norm_w) in one launch: out [T][d] and out_norm [T][d], both bf16.
+int jib_moe_combine_norm(const void * y, const int * dest, const float * wts, const void * shared, const void * residual,
+                         const float * norm_w, void * out, void * out_norm, int T, int k, int d, float eps, void * stream) {
+    if (T <= 0) return 0;
+    if (d % 8 || norm_w == nullptr || out_norm == nullptr) return JIB_E_ARG;
+    const int nv = d / 8;
+    cudaStream_t s = (cudaStream_t) stream;
+#define JIB_CN(NT, MAXV)                                                                                                         \
+    JIB_LAUNCH((moe_combine_norm_kernel<NT, MAXV>), T, NT, 0, s, (const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual, \
+               norm_w, (bf16 *) out, (bf16 *) out_norm, k, d, eps)
+    if (nv <= 128) JIB_CN(128, 1);            // the same (threads, values per thread) choice as jib_rmsnorm
+    else if (nv <= 256) JIB_CN(256, 1);
+    else if (nv <= 1024) JIB_CN(256, 4);
+    else if (nv <= 2048) JIB_CN(512, 4);
+    else return JIB_E_ARG;
+#undef JIB_CN
     return launched();
 }
 

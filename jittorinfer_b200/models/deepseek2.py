@@ -303,7 +303,8 @@ class DeepSeek2Model:
                                   r, self.block_size, batch.max_q_len, batch.attn_meta)
         return ops.v_up(o_lat, L.w_uv)
 
-    def _mlp(self, L: _Layer, g: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    def _mlp(self, L: _Layer, g: torch.Tensor, residual: torch.Tensor, norm=None):
+        """``norm=(weight, eps)`` (unsharded MoE blocks only): returns (x, rmsnorm(x) * weight)."""
         hp = self.hp
         if not L.is_moe:
             hmid = ops.gateup_silu(g, L.w_gate, L.w_up)
@@ -324,7 +325,7 @@ class DeepSeek2Model:
                                L.w_down_sh, base, n_expert=hp.n_expert)
             return self.comm.all_reduce(part, residual)
         return ops.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
-                           L.w_down_sh, base, n_expert=hp.n_expert)
+                           L.w_down_sh, base, n_expert=hp.n_expert, norm=norm)
 
     def _forward_sp(self, batch: ForwardBatch, kv_cache) -> torch.Tensor:
         """Tensor-parallel forward with a sequence-parallel residual stream (large prefill batches): every rank keeps
@@ -399,6 +400,9 @@ class DeepSeek2Model:
         x = ops.embed_gather(self.tok_embd, batch.tokens)
         nvtx = _trace.nvtx_enabled()
         by_dev = {self.device: batch}
+        # single process, single device: a MoE block's combine can also produce the next block's attention norm
+        fuse_norm = ops.fused_combine_norm() and not self.spec.sharded and not self.split
+        h_next = None
         for il, L in enumerate(self.layers):
             if self.split:
                 dev = self.layer_dev[il]
@@ -411,11 +415,15 @@ class DeepSeek2Model:
                     batch = by_dev[dev] = _batch_to(by_dev[self.device], dev)
             if nvtx:
                 torch.cuda.nvtx.range_push(f"layer{il}")
-            h, _ = ops.rmsnorm(x, L.attn_norm, hp.rms_eps)
+            h = h_next if h_next is not None else ops.rmsnorm(x, L.attn_norm, hp.rms_eps)[0]
+            h_next = None
             a = self._attention(L, h, batch, kv_cache[il])
             y = self._row_parallel(a, L.w_o, x)
             g, _ = ops.rmsnorm(y, L.ffn_norm, hp.rms_eps)
-            x = self._mlp(L, g, y)
+            if fuse_norm and L.is_moe and il + 1 < len(self.layers):
+                x, h_next = self._mlp(L, g, y, norm=(self.layers[il + 1].attn_norm, hp.rms_eps))
+            else:
+                x = self._mlp(L, g, y)
             if self.tensor_hook is not None:
                 self.tensor_hook(f"blk.{il}.attn_out", a)
                 self.tensor_hook(f"blk.{il}.ffn_inp", y)

@@ -100,11 +100,18 @@ def moe_experts(x, ids, wts, wg, wu, wd, expert_base=0):
     return ref.moe_experts(x, ids, wts, wg, wu, wd, expert_base)
 
 
-def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0, n_expert=None):
-    """``n_expert``: size of the router's expert set (lets the CUDA path estimate how many local experts a batch hits)."""
+def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0, n_expert=None, norm=None):
+    """``n_expert``: size of the router's expert set (lets the CUDA path estimate how many local experts a batch hits).
+    ``norm=(weight, eps)``: returns (out, rmsnorm(out) * weight) -- the CUDA path computes both in the combine launch."""
     if use_native(x) and x.dtype == torch.bfloat16:
-        return nat().moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base, n_expert)
-    return ref.moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base)
+        return nat().moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base, n_expert, norm)
+    out = ref.moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base)
+    return (out, ref.rmsnorm(out, norm[0], norm[1])[0]) if norm is not None else out
+
+
+def fused_combine_norm() -> bool:
+    """Whether the model should ask ``moe_ffn`` for the next block's norm (JIB_FUSED_COMBINE_NORM=1 on the CUDA path)."""
+    return bool(_native is not None and _native.FUSED_COMBINE_NORM) or os.environ.get("JIB_FUSED_COMBINE_NORM", "0") == "1"
 
 
 def argmax(logits):

@@ -25,6 +25,8 @@ PERMUTE_MULTI_MIN = 4096
 FUSED_ROUTE = os.environ.get("JIB_FUSED_ROUTE", "0") == "1"
 # Grouped-GEMM split-K hint from the expected number of experts hit (off until measured: JIB_ACTIVE_HINT=1).
 ACTIVE_HINT_EXPECTED = os.environ.get("JIB_ACTIVE_HINT", "0") == "1"
+# Expert combine fused with the RMSNorm of the next block (one launch fewer per MoE layer): JIB_FUSED_COMBINE_NORM=1.
+FUSED_COMBINE_NORM = os.environ.get("JIB_FUSED_COMBINE_NORM", "0") == "1"
 FUSED_ROUTE_MAX_T = 64
 _route_stash: Dict[tuple, tuple] = {}       # (ids ptr, expert_base, E_local) -> (seg, src, dest) produced by the fused launch
 
@@ -72,6 +74,7 @@ def load():
     sig("jib_moe_route_fused", vp, fp, fp, fp, ip, fp, ip, ip, ip, ip, i, i, i, i, i, i, f, i, i, i, i, i, i, vp)
     sig("jib_moe_permute_multi", ip, i, i, i, i, ip, ip, ip, ip, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
+    sig("jib_moe_combine_norm", vp, ip, fp, vp, vp, fp, vp, vp, i, i, i, f, vp)
     sig("jib_mla_attention", vp, vp, ip, i, ip, ip, i, i, i, i, i, i, f, i, fp, fp, vp, vp)
     sig("jib_mla_combine", fp, fp, i, i, i, i, vp, vp)
     sig("jib_mla_flash", vp, vp, ll, ip, i, ip, ip, i, i, i, f, i, i, fp, fp, vp, ip, vp)
@@ -378,10 +381,16 @@ def gather_rows(x, src_row):
     return out
 
 
-def moe_combine(y, dest, wts, shared, residual):
+def moe_combine(y, dest, wts, shared, residual, norm=None):
+    """``norm=(weight, eps)``: also return rmsnorm(out) * weight from the same launch -> (out, normed)."""
     T, k = dest.shape
     d = y.shape[1]
     out = torch.empty(T, d, dtype=torch.bfloat16, device=y.device)
+    if norm is not None:
+        normed = torch.empty(T, d, dtype=torch.bfloat16, device=y.device)
+        _ck(load().jib_moe_combine_norm(y.data_ptr(), dest.data_ptr(), wts.data_ptr(), _p(shared), _p(residual), norm[0].data_ptr(),
+                                        out.data_ptr(), normed.data_ptr(), T, k, d, float(norm[1]), _stream()), "moe_combine_norm")
+        return out, normed
     _ck(load().jib_moe_combine(y.data_ptr(), dest.data_ptr(), wts.data_ptr(), _p(shared), _p(residual), out.data_ptr(), T, k, d,
                                _stream()), "moe_combine")
     return out
@@ -418,13 +427,14 @@ def moe_experts(x, ids, wts, wg, wu, wd, expert_base=0):
     return moe_combine(y, dest, wts, None, None).float()
 
 
-def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0, n_expert=None):
-    """residual + shared_experts(x) + sum_k w_k expert_k(x), bf16; residual/shared may be None."""
+def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0, n_expert=None, norm=None):
+    """residual + shared_experts(x) + sum_k w_k expert_k(x), bf16; residual/shared may be None.
+    ``norm=(weight, eps)``: returns (out, rmsnorm(out) * weight), the norm computed by the combine launch."""
     y, dest = moe_routed(x, ids, wts, wg, wu, wd, expert_base, n_expert)
     shared = None
     if wgs is not None:
         shared = gemm(gemm(x, wgs, wus), wds)
-    return moe_combine(y, dest, wts, shared, residual)
+    return moe_combine(y, dest, wts, shared, residual, norm)
 
 
 # ---- sampling / cache ----------------------------------------------------------------------------

@@ -260,3 +260,27 @@ def test_fused_route_matches_the_separate_kernels(nat, T, d, E, k, n_group, topk
         n_local = int(seg0[-1])
         assert torch.equal(src0[:n_local], src1[:n_local]) and bool((src1[n_local:] == -1).all())
         assert int(nat.workspace(g.device).route_counter.item()) == 0
+
+
+@pytest.mark.skipif(__import__("os").environ.get("JIB_FUSED_COMBINE_NORM", "") != "1",
+                    reason="the combine + norm kernel has not run on a GPU yet: set JIB_FUSED_COMBINE_NORM=1 to try it")
+@pytest.mark.parametrize("T,k,d,with_shared", [(1, 8, 2048, False), (8, 8, 2048, False), (64, 6, 2048, True), (8, 6, 5120, True),
+                                               (300, 6, 5120, False), (5, 6, 512, False)])
+def test_combine_fused_with_the_next_norm(nat, T, k, d, with_shared):
+    """Expert combine + the RMSNorm that follows it in one launch: the same two tensors as the two launches (the kernel
+    keeps the reduction order of the norm kernel; a last-bit difference from instruction selection is tolerated)."""
+    n_rows = T * k
+    y = rnd(n_rows, d)
+    dest = torch.randperm(n_rows, device=DEV).int().view(T, k)
+    dest[0, 0] = -1                                       # a pair whose expert lives elsewhere
+    wts = torch.rand(T, k, device=DEV, dtype=torch.float32)
+    shared = rnd(T, d) if with_shared else None
+    residual = rnd(T, d)
+    w = torch.rand(d, device=DEV, dtype=torch.float32) + 0.5
+    out0 = nat.moe_combine(y, dest, wts, shared, residual)
+    norm0, _ = nat.rmsnorm(out0, w, 1e-6)
+    out1, norm1 = nat.moe_combine(y, dest, wts, shared, residual, norm=(w, 1e-6))
+    torch.cuda.synchronize()
+    assert torch.equal(out0, out1)
+    assert (norm0.float() - norm1.float()).abs().max().item() <= 2 ** -7 * norm0.float().abs().max().item()
+    assert (norm0 != norm1).float().mean().item() < 0.01
