@@ -56,6 +56,11 @@ typedef struct jib_gemm_desc {
 
 JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);
 
+// ---- sampling (sampling.cu) ---------------------------------------------------------------------
+// One id per row from the row's top-k candidates (vals / ids [n][k], sorted by value, descending; k <= 128).
+// params [n][5] fp32: temperature (<= 0: best candidate), top_k (<= 0: all), top_p (>= 1: off), min_p (<= 0: off), u in [0, 1).
+JIB_EXPORT int jib_sample_topk(const float * vals, const int * ids, const float * params, int * out, int n, int k, void * stream);
+
 // ---- memory-bound kernels (elementwise.cu) ----------------------------------------------------
 JIB_EXPORT int jib_embed_gather(const void * table, const int * ids, void * out, int T, int d, int n_vocab, void * stream);
 JIB_EXPORT int jib_rmsnorm(const void * x, const void * residual, const float * w, void * out_norm, void * out_sum, int T, int d,

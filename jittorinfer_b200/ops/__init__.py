@@ -122,6 +122,11 @@ def topk_logits(logits, k):
     return nat().topk_logits(logits, k) if use_native(logits) else ref.topk_logits(logits, k)
 
 
+def sample_topk(vals, ids, params):
+    """One id per row from sorted top-k candidates: top-k / top-p / min-p / temperature and one uniform per row."""
+    return nat().sample_topk(vals, ids, params) if use_native(vals) else ref.sample_topk(vals, ids, params)
+
+
 def kv_block_copy(cache, src_blocks, dst_blocks, block_size):
     f = nat().kv_block_copy if use_native(cache) else ref.kv_block_copy
     return f(cache, src_blocks, dst_blocks, block_size)

@@ -67,6 +67,7 @@ def load():
     sig("jib_mla_qkv_post", vp, ll, vp, ll, fp, f, fp, ip, ip, vp, vp, i, i, i, i, i, i, ll, ip, vp)
     sig("jib_argmax", fp, ip, i, i, vp)
     sig("jib_topk", fp, fp, ip, i, i, i, vp)
+    sig("jib_sample_topk", fp, ip, fp, ip, i, i, vp)
     sig("jib_kv_block_copy", vp, ll, i, ip, ip, i, i, vp)
     sig("jib_gather_rows", vp, ip, vp, i, i, i, vp)
     sig("jib_moe_gate", vp, fp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, i, i, vp)
@@ -453,6 +454,15 @@ def topk_logits(logits, k):
     ids = torch.empty(n, k, dtype=torch.int32, device=logits.device)
     _ck(load().jib_topk(logits.data_ptr(), vals.data_ptr(), ids.data_ptr(), n, V, k, _stream()), "topk")
     return vals, ids
+
+
+def sample_topk(vals, ids, params):
+    n, k = vals.shape
+    assert vals.dtype == torch.float32 and ids.dtype == torch.int32 and params.dtype == torch.float32
+    assert vals.is_contiguous() and ids.is_contiguous() and params.is_contiguous() and params.shape == (n, 5)
+    out = torch.empty(n, dtype=torch.int32, device=vals.device)
+    _ck(load().jib_sample_topk(vals.data_ptr(), ids.data_ptr(), params.data_ptr(), out.data_ptr(), n, k, _stream()), "sample_topk")
+    return out
 
 
 def kv_block_copy(cache, src_blocks, dst_blocks, block_size):

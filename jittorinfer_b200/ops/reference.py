@@ -206,6 +206,34 @@ def topk_logits(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tenso
     return v, i.int()
 
 
+def sample_topk(vals: torch.Tensor, ids: torch.Tensor, params: torch.Tensor) -> torch.Tensor:
+    """One token id per row from its top-k candidates, the device form of the chain top_k -> top_p -> min_p -> temperature
+    -> dist (common/sampling_local.cpp:153-209).  ``vals`` / ``ids`` [n, k] sorted by value, descending; ``params`` [n, 5]
+    fp32 = temperature (<= 0: best candidate), top_k (<= 0: all), top_p (>= 1: off), min_p (<= 0: off), u in [0, 1).
+    Sorted candidates make every truncation a prefix: rank < top_k; probability mass before the candidate < top_p (softmax
+    of the untempered logits of the top-k set); logit >= best + ln(min_p)."""
+    v = vals.float()
+    n, k = v.shape
+    pr = params.float()
+    temp, top_k, top_p, min_p, u = (pr[:, i:i + 1] for i in range(5))
+    rank = torch.arange(k, device=v.device)[None]
+    keep = (top_k <= 0) | (rank < top_k)
+    m = v[:, :1]
+    e = torch.exp(v - m) * keep
+    before = (torch.cumsum(e, -1) - e) / e.sum(-1, keepdim=True)
+    keep = keep & ((top_p >= 1.0) | (before < top_p))
+    keep = keep & ((min_p <= 0) | (v >= m + torch.log(min_p.clamp_min(1e-30))))
+    keep[:, 0] = True
+    keep = torch.cumprod(keep.int(), -1).bool()                       # a prefix, as the sequential form breaks at the first miss
+    w = torch.exp((v - m) / temp.clamp_min(1e-6)) * keep
+    cdf = torch.cumsum(w, -1)
+    pick = (cdf <= u * cdf[:, -1:]).sum(-1)
+    last = keep.sum(-1) - 1
+    pick = torch.minimum(pick, last)
+    pick = torch.where(temp[:, 0] <= 0, torch.zeros_like(pick), pick)
+    return ids.gather(1, pick[:, None].long())[:, 0].int()
+
+
 def kv_block_copy(cache: torch.Tensor, src_blocks: torch.Tensor, dst_blocks: torch.Tensor, block_size: int) -> None:
     """Defrag move list (src/llama-graph-defrag.cpp:23-85) on paged blocks. cache [L, n_slots, row]."""
     L = cache.shape[0]

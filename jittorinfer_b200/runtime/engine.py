@@ -29,7 +29,7 @@ from ..utils.trace import PhaseTimer, Tracer
 from ..models.deepseek2 import DeepSeek2Model, ForwardBatch
 from ..models.hparams import DeepSeek2HParams
 from .native_rt import PagedKV, Scheduler, StepArrays, i32p
-from .sampling import SamplingParams, make_sampler
+from .sampling import DeviceSampler, SamplingParams, device_samplable, make_sampler
 
 
 @dataclass
@@ -45,6 +45,8 @@ class EngineConfig:
     cuda_graphs: bool = True
     graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
     defrag_thold: float = -1.0         # <0 disables automatic defrag
+    device_sampling: bool = False      # requests that need only top-k / top-p / min-p / temperature are sampled on the device
+                                       # (ops.sample_topk; also JITTORINFER_DEVICE_SAMPLING=1); the others use the host chain
     run_ahead: bool = False            # greedy requests: launch decode step k+1 before the ids of step k reach the host
                                        # (also JITTORINFER_RUN_AHEAD=1)
     defrag_max_moves: int = 256
@@ -61,6 +63,7 @@ class RequestState:
     t_submit: float = 0.0
     t_first: float = 0.0
     t_done: float = 0.0
+    dev: Optional[DeviceSampler] = None    # sampled on the device (then sampler is None)
 
 
 @dataclass
@@ -80,7 +83,8 @@ class _StepIO:
         self.cap_tokens, self.cap_seqs, self.max_blocks = cap_tokens, cap_seqs, max_blocks
         sizes = [("tokens", cap_tokens), ("positions", cap_tokens), ("slot_mapping", cap_tokens),
                  ("q_start", cap_seqs + 1), ("seq_lens", cap_seqs), ("out_rows", cap_seqs),
-                 ("block_tables", cap_seqs * max_blocks), ("seq_slots", cap_seqs), ("out_slots", cap_seqs)]
+                 ("block_tables", cap_seqs * max_blocks), ("samp", cap_seqs * 5),      # samp: fp32 sampling rows, bit-cast
+                 ("seq_slots", cap_seqs), ("out_slots", cap_seqs)]
         off = 0
         self.off: Dict[str, Tuple[int, int]] = {}
         for name, n in sizes:
@@ -196,6 +200,7 @@ class LLMEngine:
         self._idle_graph = None
         self.tracer = Tracer()            # JSON-lines step trace when JITTORINFER_TRACE names a file
         self._pressure = False            # free KV blocks held back by the kv_alloc fault site
+        self._device_sampling = bool(cfg.device_sampling or os.environ.get("JITTORINFER_DEVICE_SAMPLING", "") == "1")
         self._run_ahead = bool(cfg.run_ahead or os.environ.get("JITTORINFER_RUN_AHEAD", "") == "1") and not self.dp \
             and not getattr(model, "split", False)
         self._inflight: Optional[_InFlight] = None
@@ -220,9 +225,10 @@ class LLMEngine:
         params = params or SamplingParams()
         rid = self._next_id
         self._next_id += 1
-        smpl = None if params.greedy and params.dry_multiplier <= 0 else \
+        dev = DeviceSampler(params) if self._device_sampling and device_samplable(params) else None
+        smpl = None if dev is not None or (params.greedy and params.dry_multiplier <= 0) else \
             make_sampler(params, self.hp.n_vocab, self.hp.n_ctx_train, getattr(self, "token_table", None))
-        st = RequestState(rid, params, smpl, len(prompt), t_submit=time.time())
+        st = RequestState(rid, params, smpl, len(prompt), t_submit=time.time(), dev=dev)
         if st.sampler is not None:
             for t in prompt[-params.repeat_last_n:]:
                 st.sampler.accept(t)
@@ -253,7 +259,31 @@ class LLMEngine:
             return ops.argmax(logits)
         k = min(self.cfg.presample_count, logits.shape[-1])
         v, i = ops.topk_logits(logits, k)
+        if mode == "sample":             # truncation, temperature and the draw on the device: only the id comes back
+            n = logits.shape[0]
+            rows = self.io.d["samp"].view(torch.float32).view(-1, 5)[:n]
+            return ops.sample_topk(v.contiguous(), i.contiguous(), rows)
         return torch.cat([v.contiguous().view(torch.int32), i], dim=-1)
+
+    def _step_mode(self, states) -> str:
+        """greedy: ids by arg-max; sample: at least one request is sampled on the device, none needs the host chain;
+        topk: candidates go to the host chain."""
+        if any(s.sampler is not None for s in states):
+            return "topk"
+        return "sample" if any(s.dev is not None for s in states) else "greedy"
+
+    def _fill_sampling_rows(self, states, n_rows: int) -> list:
+        """One (temperature, top_k, top_p, min_p, u) row per output row into the step's host buffer (temperature 0 = take
+        the best candidate, for greedy requests and padding rows).  Returns the rows of device-sampled requests."""
+        buf = self.io.h["samp"].view(np.float32).reshape(-1, 5)
+        buf[:n_rows] = 0.0
+        rows = []
+        for i, st in enumerate(states):
+            r = st.dev.row() if st.dev is not None else None
+            rows.append(r)
+            if r is not None:
+                buf[i] = r
+        return rows
 
     def _forward_sample(self, batch: ForwardBatch, mode: str) -> torch.Tensor:
         if getattr(self.model, "split", False) and self.device.type == "cuda":
@@ -425,6 +455,7 @@ class LLMEngine:
     # (a waiting request, a prompt chunk, scarce blocks, a sampler that needs the host), the engine first reads the ids
     # and continues synchronously.
     def _all_greedy(self) -> bool:
+        """No live request needs the host sampler chain (ids are chosen on the device: arg-max or the device sampler)."""
         return all(st.sampler is None for st in self.requests.values() if st.finish_reason is None)
 
     def _collect(self, infl: _InFlight) -> np.ndarray:
@@ -434,7 +465,12 @@ class LLMEngine:
         return infl.host[:infl.n_out].numpy().astype(np.int32, copy=True)
 
     def _launch_greedy(self, n_tokens: int, n_seqs: int, n_out: int, max_q: int, feedback: Optional[_InFlight]) -> _InFlight:
+        """Launches a step whose ids are chosen on the device (arg-max, or the device sampler for requests that use it)."""
         io = self.io
+        states = [self.requests[int(r)] for r in self.sched.out_reqs(n_out)]
+        mode = self._step_mode(states)
+        if mode == "sample":
+            self._fill_sampling_rows(states, io.cap_seqs)
         use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets) \
             and getattr(self.model, "tensor_hook", None) is None
         bucket = next(b for b in self.cfg.graph_buckets if b >= n_seqs) if use_graph else 0
@@ -458,14 +494,14 @@ class LLMEngine:
             else:
                 io.d["tokens"][:n_seqs].copy_(prev.index_select(0, torch.from_numpy(src).to(prev.device)))
         if use_graph:
-            g, out = self._graph_for(bucket, "greedy")
+            g, out = self._graph_for(bucket, mode)
             g.replay()
-            self.launches += self.graph_launches.get((bucket, "greedy"), 0)
+            self.launches += self.graph_launches.get((bucket, mode), 0)
             self.stats["graph_steps"] += 1
         else:
             batch = self._batch_views(n_tokens, n_seqs, n_out, max_q)
             n0 = ops.nat().launch_count if self.device.type == "cuda" and not ops.force_torch() else 0
-            out = self._forward_sample(batch, "greedy")
+            out = self._forward_sample(batch, mode)
             if self.device.type == "cuda" and not ops.force_torch():
                 self.launches += ops.nat().launch_count - n0
             self.stats["eager_steps"] += 1
@@ -597,7 +633,8 @@ class LLMEngine:
         if self._poison:
             self._poison_freed()             # after the copies: a block may be freed while a copy out of it is still queued
         states = [self.requests[int(r)] for r in self.sched.out_reqs(n_out)] if n_out else []
-        mode = "greedy" if all(s.sampler is None for s in states) else "topk"
+        mode = self._step_mode(states)
+        samp_rows = self._fill_sampling_rows(states, io.cap_seqs) if mode != "greedy" else None
         use_graph = self._use_graphs and max_q == 1 and n_seqs == n_tokens and n_seqs <= max(self.cfg.graph_buckets) \
             and getattr(self.model, "tensor_hook", None) is None
         if use_graph and self.dp:
@@ -646,14 +683,16 @@ class LLMEngine:
             self.stats["d2h_bytes"] += n_el * 4
             res = host.numpy().reshape(out.shape[0], -1)
             sampled = np.empty(n_out, dtype=np.int32)
-            if mode == "greedy":
+            if mode in ("greedy", "sample"):
                 sampled[:] = res[:n_out, 0]
             else:
                 k = res.shape[1] // 2
                 for i, st in enumerate(states):
                     vals = res[i, :k].view(np.float32)
                     ids = res[i, k:]
-                    if st.sampler is None:
+                    if st.dev is not None:
+                        sampled[i] = st.dev.sample_host(vals, ids, samp_rows[i])
+                    elif st.sampler is None:
                         sampled[i] = ids[int(np.argmax(vals))]
                     else:
                         sampled[i] = st.sampler.sample(vals, ids)

@@ -185,6 +185,40 @@ class NativeSampler:
         return int(arr.data[arr.selected].id)
 
 
+def device_samplable(p: SamplingParams) -> bool:
+    """True when a request needs only what the on-device sampler implements: top-k, top-p, min-p, temperature and a seeded
+    draw (``ops.sample_topk``).  Penalties, DRY, grammar, logit bias, typical and XTC sampling need the host chain."""
+    return (p.temperature > 0.0 and p.repeat_penalty == 1.0 and p.frequency_penalty == 0.0 and p.presence_penalty == 0.0
+            and not p.logit_bias and p.typical_p >= 1.0 and p.xtc_probability <= 0.0 and p.dynatemp_range <= 0.0
+            and p.dry_multiplier <= 0.0 and not p.grammar and p.min_keep <= 1)
+
+
+class DeviceSampler:
+    """Host half of the on-device sampler: the request's truncation settings and its random stream.  Every step in which
+    the request has an output row takes one uniform number from the stream; it travels to the device with the step's
+    other inputs, so the draw depends on the seed and the step count only -- not on when the host reads the result."""
+
+    def __init__(self, params: SamplingParams):
+        self.p = params
+        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else None))
+
+    def row(self) -> tuple:
+        p = self.p
+        return (float(p.temperature), float(p.top_k), float(p.top_p), float(p.min_p), float(self.rng.random()))
+
+    def accept(self, token: int) -> None:
+        pass
+
+    def sample_host(self, values: np.ndarray, ids: np.ndarray, row: tuple) -> int:
+        """The same draw on the host (a step whose other requests need the host chain hands out candidates, not ids)."""
+        import torch
+
+        from ..ops import reference as ref
+        v = torch.from_numpy(np.ascontiguousarray(values, dtype=np.float32))[None]
+        i = torch.from_numpy(np.ascontiguousarray(ids, dtype=np.int32))[None]
+        return int(ref.sample_topk(v, i, torch.tensor([row], dtype=torch.float32))[0])
+
+
 def make_sampler(params: SamplingParams, n_vocab: int = 0, n_ctx_train: int = 4096, token_table=None):
     """The native chain unless it cannot be loaded or ``JITTORINFER_SAMPLER=python`` asks for the numpy one."""
     import os

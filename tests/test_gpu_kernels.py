@@ -284,3 +284,28 @@ def test_combine_fused_with_the_next_norm(nat, T, k, d, with_shared):
     assert torch.equal(out0, out1)
     assert (norm0.float() - norm1.float()).abs().max().item() <= 2 ** -7 * norm0.float().abs().max().item()
     assert (norm0 != norm1).float().mean().item() < 0.01
+
+
+@pytest.mark.skipif(__import__("os").environ.get("JITTORINFER_DEVICE_SAMPLING", "") != "1",
+                    reason="the device sampler has not run on a GPU yet: set JITTORINFER_DEVICE_SAMPLING=1 to try it")
+@pytest.mark.parametrize("k", [8, 64, 128])
+def test_device_sampler_matches_the_reference(nat, k):
+    """top-k / top-p / min-p / temperature + one draw per row: the ids of the PyTorch fp32 restatement, except for draws
+    that land within rounding distance of a boundary."""
+    n = 4096
+    g = torch.Generator(device="cuda").manual_seed(3)
+    vals = torch.sort(torch.randn(n, k, device=DEV, generator=g) * 2.5, dim=-1, descending=True).values.contiguous()
+    ids = torch.stack([torch.randperm(50000, device=DEV, generator=g)[:k] for _ in range(8)]).repeat(n // 8, 1).int().contiguous()
+    params = torch.zeros(n, 5, device=DEV)
+    params[:, 0] = torch.tensor([0.0, 0.6, 1.0, 1.7], device=DEV).repeat(n // 4)
+    params[:, 1] = torch.tensor([0.0, 5.0, 40.0, 500.0], device=DEV).repeat_interleave(n // 4)
+    params[:, 2] = torch.rand(n, device=DEV, generator=g).clamp(0.2, 1.0)
+    params[:, 3] = torch.rand(n, device=DEV, generator=g) * 0.1 * (torch.rand(n, device=DEV, generator=g) < 0.5)
+    params[:, 4] = torch.rand(n, device=DEV, generator=g)
+    got = nat.sample_topk(vals, ids, params)
+    want = ref.sample_topk(vals, ids, params)
+    torch.cuda.synchronize()
+    agree = (got == want).float().mean().item()
+    assert agree > 0.995, agree
+    greedy = params[:, 0] <= 0
+    assert torch.equal(got[greedy], ids[greedy, 0])
