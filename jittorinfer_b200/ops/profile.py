@@ -31,7 +31,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 import torch
 
 OPS = ("embed_gather", "select_rows", "rmsnorm", "linear", "gateup_silu", "mla_qkv_post", "q_absorb", "v_up", "mla_attention",
-       "moe_gate", "moe_experts", "moe_ffn", "argmax", "topk_logits", "kv_block_copy")
+       "moe_gate", "moe_experts", "moe_ffn", "argmax", "topk_logits", "sample_topk", "kv_block_copy")
 
 
 def _sig(args, kwargs) -> str:
