@@ -116,10 +116,11 @@ JIB_API int jib_sched_n_waiting(jib_sched * s) { return s->sched.n_waiting(); }
 JIB_API int jib_sched_n_running(jib_sched * s) { return s->sched.n_running(); }
 JIB_API void jib_sched_set_n_batch(jib_sched * s, int n) { s->sched.set_n_batch(n); }
 JIB_API int jib_sched_slot_state(jib_sched * s, int slot) { return s->sched.slots()[slot].state; }
-// stats_out: steps, prompt_tokens, decode_tokens, preemptions, finished, prefix_hits
+// stats_out (7 values): steps, prompt_tokens, decode_tokens, preemptions, finished, prefix_hits, prefix_shared
 JIB_API void jib_sched_stats(jib_sched * s, int64_t * o) {
     const SchedStats & st = s->sched.stats();
     o[0] = st.steps; o[1] = st.prompt_tokens; o[2] = st.decode_tokens; o[3] = st.preemptions; o[4] = st.finished; o[5] = st.prefix_hits;
+    o[6] = st.prefix_shared;
 }
 
 // ---- tokenizer ------------------------------------------------------------------------------

@@ -168,6 +168,24 @@ StepInfo Scheduler::step(StepArrays & out) {
         Request r = std::move(waiting_.front());
         waiting_.pop_front();
         if (r.prompt.empty()) r.prompt.push_back(eos_id_);
+        // A longer prefix may sit in another slot's sequence (idle or running): share its full blocks by reference.
+        // Whole blocks only, so that neither sequence ever has to copy one on its next write.
+        {
+            const int bs = kv_->block_size();
+            int donor = -1, best = lcp;
+            for (const auto & o : slots_) {
+                if (o.id == sid) continue;
+                const int cached = std::min<int>((int) o.tokens.size(), kv_->seq_len(o.id));
+                if (cached < best + bs) continue;
+                const int l = std::min(common_prefix(o.tokens, r.prompt), cached) / bs * bs;
+                if (l >= best + bs) { best = l; donor = o.id; }
+            }
+            if (donor >= 0 && kv_->seq_cp(donor, sid, 0, best)) {
+                slots_[sid].tokens.assign(r.prompt.begin(), r.prompt.begin() + best);
+                lcp = best;
+                ++stats_.prefix_shared;
+            }
+        }
         launch(slots_[sid], r, lcp);
     }
     for (auto & s : slots_) { s.out_row = -1; s.in_batch = false; }

@@ -6,7 +6,9 @@
 // follow the reference's slot state machine (server.cpp:41-47).  Deliberate differences: request
 // `max_tokens` / `ignore_eos` are honoured; when the cache is full the *youngest* running request is
 // preempted and re-queued (the reference releases every slot, server.cpp:1493-1500); idle slots keep
-// their blocks for prefix reuse only until someone else needs them.
+// their blocks for prefix reuse only until someone else needs them; a new request whose prompt starts like the tokens
+// of ANOTHER slot's sequence (idle or running, e.g. a common system prompt) shares that sequence's full blocks by
+// reference instead of recomputing them.
 #pragma once
 #include <cstdint>
 #include <deque>
@@ -77,6 +79,7 @@ struct StepInfo {
 
 struct SchedStats {
     int64_t steps = 0, prompt_tokens = 0, decode_tokens = 0, preemptions = 0, finished = 0, prefix_hits = 0;
+    int64_t prefix_shared = 0;     // requests that started from blocks shared with another slot's sequence
 };
 
 class Scheduler {

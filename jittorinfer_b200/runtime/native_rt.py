@@ -227,6 +227,7 @@ class Scheduler:
     def slot_state(self, slot): return SLOT_STATES[self._L.jib_sched_slot_state(self._h, slot)]
 
     def stats(self) -> dict:
-        o = np.zeros(6, dtype=np.int64)
+        o = np.zeros(8, dtype=np.int64)
         self._L.jib_sched_stats(self._h, o.ctypes.data_as(i64p))
-        return dict(zip(("steps", "prompt_tokens", "decode_tokens", "preemptions", "finished", "prefix_hits"), map(int, o)))
+        return dict(zip(("steps", "prompt_tokens", "decode_tokens", "preemptions", "finished", "prefix_hits", "prefix_shared"),
+                        map(int, o)))

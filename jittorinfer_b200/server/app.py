@@ -392,6 +392,7 @@ class ServerContext:
                 "kv_fragmentation": eng.kv.fragmentation(), "graph_steps": eng.stats["graph_steps"],
                 "eager_steps": eng.stats["eager_steps"], "defrag_moves": eng.stats.get("defrag_moves", 0),
                 "preemptions": eng.sched.stats().get("preemptions", 0) if hasattr(eng.sched, "stats") else 0,
+                "prefix_shared": eng.sched.stats().get("prefix_shared", 0) if hasattr(eng.sched, "stats") else 0,
                 "kernel_launches": eng.launches, "h2d_bytes": eng.stats["h2d_bytes"], "d2h_bytes": eng.stats["d2h_bytes"],
                 "engine_resets": eng.stats.get("resets", 0),
                 # collectives this rank took part in (in-kernel or library) and how many used the two-shot (prefill) form

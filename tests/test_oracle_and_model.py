@@ -333,3 +333,37 @@ def test_run_ahead_under_kv_pressure_and_with_a_host_sampler(tmp_path, monkeypat
     steps = [r for r in recs if r["kind"] == "step"]
     assert len(steps) == eng.stats["steps"] and any(r["mode"] == "ahead" for r in steps)
     assert sum(r["finished"] for r in recs if r["kind"] in ("step", "collect")) == len(prompts) + 4
+
+
+def test_prefix_blocks_are_shared_across_slots(monkeypatch):
+    """Requests whose prompts start like the tokens another slot already holds (a common system prompt) start from that
+    slot's full blocks by reference: fewer prompt tokens are evaluated, the outputs are still the oracle's, also while the
+    donor keeps generating and after it has gone; poisoning of freed blocks is on to catch any use of a released block."""
+    monkeypatch.setenv("JITTORINFER_KV_POISON", "1")
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    o = OracleModel(hp, w)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    eng = LLMEngine(m, EngineConfig(n_ctx=4096, n_batch=256, n_parallel=4, n_ctx_slot=512))
+    g = torch.Generator().manual_seed(31)
+    system = torch.randint(0, hp.n_vocab, (150,), generator=g).tolist()          # two full blocks + 22 tokens
+    tails = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (9, 17, 30)]
+    first = eng.add_request(system + tails[0], SamplingParams(ignore_eos=True, max_tokens=30))
+    eng.step()                                                                   # the donor's prompt is in the cache now
+    before = eng.sched.stats()["prompt_tokens"]
+    second = eng.add_request(system + tails[1], SamplingParams(ignore_eos=True, max_tokens=12))
+    third = eng.add_request(system[:140] + tails[2], SamplingParams(ignore_eos=True, max_tokens=12))
+    while eng.has_work():
+        eng.step()
+    st = eng.sched.stats()
+    assert st["prefix_shared"] == 2
+    assert st["prompt_tokens"] - before == (150 + 17 - 128) + (140 + 30 - 128)   # only what lies beyond the shared blocks
+    assert eng.requests[first].output == o.generate(system + tails[0], 30)
+    assert eng.requests[second].output == o.generate(system + tails[1], 12)
+    assert eng.requests[third].output == o.generate(system[:140] + tails[2], 12)
+    assert eng.kv.check()
+    # the donor's slot is reused by an unrelated prompt (its blocks lose one reference each); a sharer's cache still serves
+    other = torch.randint(0, hp.n_vocab, (200,), generator=g).tolist()
+    outs = eng.generate([other, other[:50], system + tails[1] + [1, 2, 3]], SamplingParams(ignore_eos=True), max_new_tokens=8)
+    assert outs == [o.generate(p, 8) for p in (other, other[:50], system + tails[1] + [1, 2, 3])]
+    assert eng.kv.check() and eng.stats["poisoned_blocks"] >= 0
