@@ -145,6 +145,7 @@ std::vector<std::pair<int32_t, int32_t>> PagedKv::defrag(int max_moves) {
         remap[src] = dst;
         ref_[dst] = ref_[src];
         ref_[src] = 0;
+        if (track_freed_) freed_.push_back(src);
         moves.emplace_back(src, dst);
         --src;
     }
@@ -158,7 +159,7 @@ std::vector<std::pair<int32_t, int32_t>> PagedKv::defrag(int max_moves) {
     }
     free_.clear();
     for (int b = 0; b < n_blocks_; ++b)
-        if (ref_[b] == 0) free_.push_back(b);
+        if (ref_[b] == 0 && std::find(reserved_.begin(), reserved_.end(), b) == reserved_.end()) free_.push_back(b);
     std::make_heap(free_.begin(), free_.end(), std::greater<int32_t>());
     return moves;
 }
