@@ -177,7 +177,7 @@ int PagedKv::reserve(int n) {
 void PagedKv::unreserve() {
     for (int32_t b : reserved_) free_.push_back(b);
     reserved_.clear();
-    std::sort(free_.begin(), free_.end(), [](int32_t a, int32_t b) { return a > b; });
+    std::make_heap(free_.begin(), free_.end(), std::greater<int32_t>());      // the same min-heap order alloc_block() relies on
 }
 
 bool PagedKv::check() const {

@@ -78,7 +78,7 @@ class PagedKv {
     int n_blocks_, block_size_;
     std::vector<KvSeq> seqs_;
     std::vector<int32_t> ref_;
-    std::vector<int32_t> free_;    // kept sorted descending so pop_back() yields the lowest id
+    std::vector<int32_t> free_;    // min-heap (std::greater): alloc_block() hands out the lowest free id
     std::vector<std::pair<int32_t, int32_t>> pending_;
     std::vector<int32_t> reserved_;
     std::vector<int32_t> freed_;
