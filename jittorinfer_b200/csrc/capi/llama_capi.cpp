@@ -355,7 +355,7 @@ int32_t llama_decode(llama_context * ctx, llama_batch batch, bool sync_all_serve
         for (int j = a; j < b; ++j) pos[order[j]] = base + (j - a);
         a = b;
     }
-    // capacity: all or nothing
+    // capacity: all or nothing for the appends (a tail that the batch's positions dropped above stays dropped)
     {
         int need = 0;
         for (int a = 0; a < n;) {
