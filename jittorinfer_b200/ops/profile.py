@@ -26,7 +26,7 @@ import argparse
 import json
 import sys
 import time
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, Iterable, List, Sequence, Tuple
 
 import torch
 

@@ -64,7 +64,6 @@ class ChatTemplate:
         self._jinja = None
         if self.source not in ("deepseek2", "deepseek"):
             try:
-                import jinja2
                 from jinja2.sandbox import ImmutableSandboxedEnvironment
                 env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
                 env.filters.setdefault("tojson", lambda v, **kw: json.dumps(v, ensure_ascii=False))

@@ -12,7 +12,7 @@ from jittorinfer_b200.models.hparams import preset
 from jittorinfer_b200.models.weights import random_weights
 from jittorinfer_b200.ops import reference as ref
 from jittorinfer_b200.runtime.engine import EngineConfig, LLMEngine
-from jittorinfer_b200.runtime.sampling import DeviceSampler, HostSampler, SamplingParams, device_samplable
+from jittorinfer_b200.runtime.sampling import HostSampler, SamplingParams, device_samplable
 
 
 def _expected(v, temp, top_k, top_p, min_p):

@@ -1,6 +1,4 @@
 """Native BPE tokenizer: pre-split rules, merges, specials, byte-level round trip."""
-import ctypes as C
-
 from jittorinfer_b200.tokenizer import Tokenizer
 from jittorinfer_b200.utils.toy_vocab import gpt2_byte_alphabet, toy_vocab_kv
 
@@ -37,7 +35,6 @@ def test_bos_and_special_token_partition():
 
 
 def test_pre_split_rules():
-    from jittorinfer_b200.runtime import native_rt
     tok, _ = _tok()
     # words keep one leading space; digits split from letters; newlines are single pieces; trailing spaces group
     cases = {"Hello world": ["Hello", " world"], "abc123def": ["abc", "123", "def"], "a\n\nb": ["a", "\n", "\n", "b"],
