@@ -101,9 +101,12 @@ def scrape_metrics(url: str) -> Dict[str, float]:
 
 
 def run(url: str, rate: float, num_requests: int, prompt_min: int, prompt_max: int, output_len: int, max_concurrency: int,
-        n_vocab: int, seed: int = 0, timeout: float = 600.0) -> Dict[str, object]:
+        n_vocab: int, seed: int = 0, timeout: float = 600.0, shared_prefix: int = 0) -> Dict[str, object]:
+    """``shared_prefix`` > 0: every prompt starts with the same that many tokens (a common system prompt), followed by its
+    own random tokens -- the workload in which the server's cross-request prefix sharing shows."""
     rng = random.Random(seed)
-    prompts = [[rng.randrange(1, n_vocab) for _ in range(rng.randint(prompt_min, prompt_max))] for _ in range(num_requests)]
+    common = [rng.randrange(1, n_vocab) for _ in range(shared_prefix)]
+    prompts = [common + [rng.randrange(1, n_vocab) for _ in range(rng.randint(prompt_min, prompt_max))] for _ in range(num_requests)]
     gaps = [rng.expovariate(rate) if rate > 0 else 0.0 for _ in range(num_requests)]
     results: List[Optional[RequestResult]] = [None] * num_requests
     gate = threading.Semaphore(max_concurrency)
@@ -149,7 +152,7 @@ def run(url: str, rate: float, num_requests: int, prompt_min: int, prompt_max: i
     return {
         "bench": "serving", "url": url, "arrivals": f"poisson {rate}/s" if rate > 0 else f"closed loop, {max_concurrency} users",
         "requests": num_requests, "completed": len(done), "failed": failed, "duration_s": round(dur, 3),
-        "prompt_len": [prompt_min, prompt_max], "output_len": output_len, "max_concurrency": max_concurrency,
+        "prompt_len": [prompt_min, prompt_max], "shared_prefix": shared_prefix, "output_len": output_len, "max_concurrency": max_concurrency,
         "request_throughput_per_s": round(len(done) / dur, 3) if dur > 0 else 0.0,
         "output_tokens_per_s": round(out_tokens / dur, 2) if dur > 0 else 0.0,
         "total_tokens_per_s": round((out_tokens + sum(r.n_prompt for r in done)) / dur, 2) if dur > 0 else 0.0,
@@ -173,9 +176,10 @@ def main(argv=None) -> int:
     ap.add_argument("--max-concurrency", type=int, default=64)
     ap.add_argument("--n-vocab", type=int, default=102400)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--shared-prefix", type=int, default=0, help="tokens of a prompt prefix common to all requests")
     ap.add_argument("--timeout", type=float, default=600.0)
     a = ap.parse_args(argv)
-    res = run(a.url, a.rate, a.num_requests, a.prompt_min, a.prompt_max, a.output_len, a.max_concurrency, a.n_vocab, a.seed, a.timeout)
+    res = run(a.url, a.rate, a.num_requests, a.prompt_min, a.prompt_max, a.output_len, a.max_concurrency, a.n_vocab, a.seed, a.timeout, a.shared_prefix)
     print(json.dumps(res))
     return 0 if res["failed"] == 0 else 1
 

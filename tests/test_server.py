@@ -121,6 +121,12 @@ def test_serving_benchmark_poisson(server):
     assert closed["completed"] == 6 and closed["arrivals"].startswith("closed loop")
     m = bench_serving.scrape_metrics(url)
     assert "jittorinfer_kv_blocks_used_ratio" in m and m["jittorinfer_requests_total"] >= 16
+    # a common system prompt: later requests start from the blocks an earlier one computed
+    shared0 = m.get("jittorinfer_prefix_shared", 0)
+    sp = bench_serving.run(url, rate=0.0, num_requests=6, prompt_min=4, prompt_max=10, output_len=3, max_concurrency=2,
+                           n_vocab=1000, seed=3, timeout=120, shared_prefix=150)
+    assert sp["completed"] == 6 and sp["shared_prefix"] == 150
+    assert bench_serving.scrape_metrics(url)["jittorinfer_prefix_shared"] > shared0
 
 
 def test_generate_cli(capsys):
