@@ -321,6 +321,10 @@ class DeepSeek2Model:
                 shared = ops.linear(ops.gateup_silu(g, L.w_gate_sh, L.w_up_sh), L.w_down_sh)
             return self.ep.moe_ffn(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, shared)
         if self.comm is not None and self.spec.sharded:
+            if getattr(self.comm, "fused_combine", False) and self.comm.fused and g.is_cuda and g.shape[0] <= self.comm.max_rows:
+                # decode batches: combine, all-reduce, residual (and the next block's norm) in one launch
+                return self.comm.moe_ffn_all_reduce(g, residual, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh,
+                                                    L.w_up_sh, L.w_down_sh, base, hp.n_expert, norm)
             part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                                L.w_down_sh, base, n_expert=hp.n_expert)
             return self.comm.all_reduce(part, residual)
@@ -401,7 +405,9 @@ class DeepSeek2Model:
         nvtx = _trace.nvtx_enabled()
         by_dev = {self.device: batch}
         # single process, single device: a MoE block's combine can also produce the next block's attention norm
-        fuse_norm = ops.fused_combine_norm() and not self.spec.sharded and not self.split
+        fuse_norm = (ops.fused_combine_norm() and not self.spec.sharded and not self.split) or \
+            (self.spec.sharded and not self.spec.dp_attention and getattr(self.comm, "fused_combine", False)
+             and getattr(self.comm, "fused", False) and x.is_cuda and x.shape[0] <= self.comm.max_rows)
         h_next = None
         for il, L in enumerate(self.layers):
             if self.split:

@@ -252,6 +252,35 @@ class FusedCommunicator(Communicator):
 
     n_two_shot = 0
 
+    # ---- MoE block tail in one launch: expert combine + all-reduce + residual (+ the next block's norm) -----------
+    # Cross-compiled, not yet run on a GPU: off unless JIB_FUSED_COMBINE_AR=1.
+    fused_combine = os.environ.get("JIB_FUSED_COMBINE_AR", "0") == "1"
+
+    def moe_ffn_all_reduce(self, x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base, n_expert=None, norm=None):
+        """residual + all-reduce(local experts' weighted sum + this rank's shard of the shared experts) for a decode
+        batch; ``norm=(weight, eps)`` adds rmsnorm(result) * weight -> (out, normed).  One launch after the expert GEMMs
+        instead of combine, all-reduce and norm."""
+        T, d = x.shape
+        site = self._next_site()
+        nat = self.native
+        y, dest = nat.moe_routed(x, ids, wts, wg, wu, wd, expert_base, n_expert)
+        shared = nat.gemm(nat.gemm(x, wgs, wus), wds) if wgs is not None else None
+        out = torch.empty(T, d, dtype=torch.bfloat16, device=x.device)
+        normed = torch.empty(T, d, dtype=torch.bfloat16, device=x.device) if norm is not None else None
+        fn = self.L.jib_moe_combine_allreduce
+        if not getattr(fn, "_typed", False):
+            vp = C.c_void_p
+            fn.restype, fn.argtypes = C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float,
+                                               C.POINTER(ArCtx), C.c_int, vp]
+            fn._typed = True
+        self.n_collectives += 1
+        rc = fn(y.data_ptr(), dest.data_ptr(), wts.data_ptr(), None if shared is None else shared.data_ptr(),
+                None if residual is None else residual.data_ptr(), None if norm is None else norm[0].data_ptr(), out.data_ptr(),
+                None if normed is None else normed.data_ptr(), T, dest.shape[1], d, float(norm[1]) if norm is not None else 0.0,
+                C.byref(self.ctx), site, torch.cuda.current_stream().cuda_stream)
+        nat._ck(rc, "moe_combine_allreduce")
+        return (out, normed) if norm is not None else out
+
     # ---- sequence-parallel prefill with in-kernel collectives (see Communicator for the contract) -----------------
     def _sp_fits(self, rows_total: int, d: int) -> bool:
         return 0 < rows_total <= self.max_rows_large and d == self.d_max and rows_total % self.world == 0

@@ -26,7 +26,7 @@ import numpy as np
 STAMP_DTYPE = np.dtype([("t", "<u8"), ("kind", "<i4"), ("a", "<i4"), ("b", "<i4"), ("c", "<i4")])      # JibStamp
 KIND_NAMES = {10: "oneshot_signalled", 11: "oneshot_source_arrived", 12: "oneshot_all_seen", 20: "twoshot_signalled",
               21: "twoshot_owner_source_arrived", 22: "twoshot_delivered", 30: "gemm_accumulators_done"}
-UNITS = ("gemm", "comm")
+UNITS = ("gemm", "comm", "combine_ar")
 
 
 class Timeline:

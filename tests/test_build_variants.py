@@ -21,7 +21,7 @@ def test_timeline_build_compiles_and_identifies_itself():
     normal = C.CDLL(build.build_kernels())
     timed = C.CDLL(build.build_kernels_timeline())
     assert normal.jib_timeline_enabled() == 0 and timed.jib_timeline_enabled() == 1
-    for unit in ("gemm", "comm"):
+    for unit in ("gemm", "comm", "combine_ar"):
         assert hasattr(timed, "jib_timeline_set_" + unit) and not hasattr(normal, "jib_timeline_set_" + unit)
 
 

@@ -173,3 +173,20 @@ def test_sequence_parallel_prefill_fused_two_gpus():
         assert out[0] == r[0]
     agree = sum(a == b for out, r in zip(res[0][1], lib[0][1]) for a, b in zip(out, r))
     assert agree >= 12
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(os.environ.get("JIB_FUSED_COMBINE_AR", "") != "1",
+                    reason="the combine + all-reduce + norm kernel has been cross-compiled but not yet run on GPUs; "
+                           "set JIB_FUSED_COMBINE_AR=1 to try it")
+@pytest.mark.parametrize("graphs", [False, True])
+def test_moe_tail_in_one_launch_two_gpus(graphs):
+    """Decode steps with the MoE block's tail (expert combine, all-reduce over peer memory, residual, next block's norm)
+    as one kernel: ranks agree bit for bit and the tokens track the NCCL build and the oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, "nccl", True, comm_impl="fused", graphs=graphs)
+    ref = _oracle("tiny-v2", True)
+    assert res[0][1] == res[1][1] and res[0][3]
+    agree = sum(a == b for out, r in zip(res[0][1], ref) for a, b in zip(out, r))
+    assert agree >= 12
