@@ -63,7 +63,8 @@ def test_every_entry_point_is_exported():
     for name in ("jib_gemm_bf16", "jib_gemm_bf16_noalloc", "jib_mla_flash", "jib_mla_attention", "jib_mla_combine", "jib_moe_gate",
                  "jib_moe_permute", "jib_moe_combine", "jib_rmsnorm", "jib_mla_qkv_post", "jib_embed_gather", "jib_argmax", "jib_topk",
                  "jib_kv_block_copy", "jib_gather_rows", "jib_allreduce_oneshot", "jib_allreduce_twoshot", "jib_ar_epoch_bump",
-                 "jib_ep_plan", "jib_ep_push", "jib_ep_combine", "jib_symm_alloc", "jib_symm_open"):
+                 "jib_ep_plan", "jib_ep_push", "jib_ep_combine", "jib_symm_alloc", "jib_symm_open", "jib_allgather_rows",
+                 "jib_moe_permute_multi", "jib_moe_route_fused", "jib_moe_combine_norm", "jib_moe_combine_allreduce", "jib_sample_topk"):
         assert hasattr(L, name), name
 
 
