@@ -101,6 +101,9 @@ def main():
     ap.add_argument("--ops", default="native", choices=["native", "torch"], help="torch = PyTorch/cuBLAS baseline ops")
     ap.add_argument("--sweep", action="store_true", help="also report concurrency 1/2/4")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu: dry run of this script's whole flow on the reference ops with --model tiny (a check of the "
+                         "script, not a measurement)")
     ap.add_argument("--run-ahead", action="store_true",
                     help="launch decode step k+1 before the ids of step k reach the host (EngineConfig.run_ahead)")
     ap.add_argument("--timeline", action="store_true",
@@ -124,8 +127,25 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+    cuda = args.device == "cuda"
+    if cuda:
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        new_event = lambda: torch.cuda.Event(enable_timing=True)      # noqa: E731
+        synchronize = torch.cuda.synchronize
+    else:
+        if world > 1 or (args.model or "lite") != "tiny":
+            raise SystemExit("--device cpu is a single-process dry run with --model tiny")
+        dev = torch.device("cpu")
+
+        class _HostEvent:
+            def record(self):
+                self.t = time.perf_counter()
+
+            def elapsed_time(self, other):
+                return (other.t - self.t) * 1e3
+        new_event = _HostEvent
+        synchronize = lambda: None                                     # noqa: E731
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     if args.ops == "torch":
@@ -160,7 +180,7 @@ def main():
     def barrier():
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+        synchronize()
 
     def max_over_ranks(x: float) -> float:
         if world == 1:
@@ -182,7 +202,7 @@ def main():
         if sampler:
             sampler.start()
         l0 = eng.launches
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1 = new_event(), new_event()
         e0.record()
         for _ in range(k_steps):
             eng.step()
@@ -221,7 +241,7 @@ def main():
     if key in eng._graphs:
         gr = eng._graphs[key][0]
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1 = new_event(), new_event()
         for _ in range(3):
             gr.replay()
         e0.record()
@@ -255,8 +275,8 @@ def main():
                "d2h_bytes_per_step": (eng.stats["d2h_bytes"] - io_d2h0) // max(1, n_steps),
                "what": f"LLMEngine.generate(): {C} requests x ({args.prompt_len} prompt + {args.gen_len} generated), "
                        f"prefill included, {n_steps} engine steps, wall clock"}
-    torch.cuda.synchronize()
-    if args.ops == "native":
+    synchronize()
+    if args.ops == "native" and cuda:
         ops.nat().check_status()
 
     if rank == 0:
