@@ -195,3 +195,86 @@ def test_scheduler_deferred_commit_gives_the_synchronous_events():
     assert [t for t, _ in sync[2]] == [120, 121, 122, EOS] and sync[2][-1][1] == "stop"
     assert len(sync[1]) == 9 and sync[1][-1][1] == "length" and len(sync[3]) == 3
     assert fed_ahead == fed_sync + 1                     # the token fed to request 2 after its end-of-sequence token
+
+
+def test_scheduler_random_workloads_sync_and_deferred_agree():
+    """Seeded random workloads (prompt lengths, token limits, end-of-sequence hits, cancellations, arrivals over time, a
+    cache small enough to force eviction and preemption): the scheduler driven with commit() and the one driven with
+    commit_deferred() / resolve() whenever can_run_ahead() allows give every request the same tokens and finish reason;
+    the allocator stays consistent; no unknown-token marker is ever fed except as a step's device-fed input."""
+    import random
+    EOS = 3
+
+    def sample(rid, n, eos_at):
+        return EOS if eos_at.get(rid) == n else 10 + (rid * 7919 + n * 104729) % 900
+
+    def run(seed, deferred):
+        rng = random.Random(seed)
+        n_slots = rng.choice([2, 3, 4])
+        bs = rng.choice([4, 8, 16])
+        kv = PagedKV(rng.choice([12, 24, 64]), bs, n_slots)
+        n_ctx_slot = bs * rng.choice([4, 6])
+        sched = Scheduler(kv, n_slots, rng.choice([8, 32]), n_ctx_slot, EOS)
+        io = _StepIO(64, n_slots, n_ctx_slot // bs + 1, torch.device("cpu"))
+        n_req = rng.randint(3, 9)
+        arrivals, eos_at, cancels = {}, {}, {}
+        for rid in range(1, n_req + 1):
+            arrivals.setdefault(rng.randint(0, 12), []).append(
+                (rid, [rng.randint(10, 900) for _ in range(rng.randint(1, n_ctx_slot - 2))], rng.choice([-1, 1, 3, 9, 30]), rng.random() < 0.2))
+            if rng.random() < 0.4:
+                eos_at[rid] = rng.randint(0, 12)
+            if rng.random() < 0.2:
+                cancels[rid] = rng.randint(1, 25)
+        count, out, pending, n_deferred = {}, {}, None, 0
+        for it in range(600):
+            for rid, prompt, max_new, ign in arrivals.get(it, []):
+                sched.add(rid, prompt, max_new=max_new, ignore_eos=ign)
+            for rid, when in cancels.items():
+                if when == it:
+                    sched.cancel(rid)
+
+            def ids_of(p):
+                toks = np.array([sample(r, count.setdefault(r, 0), eos_at) for r in p], dtype=np.int32)
+                for r in p:
+                    count[r] += 1
+                return toks
+            if pending is not None and deferred and sched.can_run_ahead():
+                sched.commit_deferred(len(pending))
+                n_deferred += 1
+                info = sched.step(io.arrays)
+                nxt = [int(r) for r in sched.out_reqs(int(info[2]))] if int(info[0]) else None
+                sched.resolve(ids_of(pending), len(pending))
+                pending = nxt
+            elif pending is not None:
+                sched.commit(ids_of(pending), len(pending))
+                pending = None
+            else:
+                info = sched.step(io.arrays)
+                if int(info[0]) == 0:
+                    if sched.idle() and it > 14:
+                        break
+                elif int(info[2]):
+                    pending = [int(r) for r in sched.out_reqs(int(info[2]))]
+                else:
+                    sched.commit(np.empty(0, dtype=np.int32), 0)
+            for rid, slot, tok, fin, npmt, ndec in sched.take_events():
+                out.setdefault(rid, []).append((tok, fin))
+            assert kv.check()
+        assert sched.idle(), seed
+        return out, n_deferred
+
+    total_deferred = 0
+    for seed in range(60):
+        a, _ = run(seed, False)
+        b, nd = run(seed, True)
+        total_deferred += nd
+        # a cancelled request may have produced one token more or less by the time the cancel lands (ids arrive a step
+        # later when running ahead); everything else must be identical
+        for rid in set(a) | set(b):
+            ta, tb = a.get(rid, []), b.get(rid, [])
+            if any(f == "cancelled" for _, f in ta + tb):
+                n = min(len(ta), len(tb)) - 1
+                assert [t for t, _ in ta[:n]] == [t for t, _ in tb[:n]], (seed, rid)
+            else:
+                assert ta == tb, (seed, rid, ta, tb)
+    assert total_deferred > 100
