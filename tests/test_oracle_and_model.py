@@ -367,3 +367,42 @@ def test_prefix_blocks_are_shared_across_slots(monkeypatch):
     outs = eng.generate([other, other[:50], system + tails[1] + [1, 2, 3]], SamplingParams(ignore_eos=True), max_new_tokens=8)
     assert outs == [o.generate(p, 8) for p in (other, other[:50], system + tails[1] + [1, 2, 3])]
     assert eng.kv.check() and eng.stats["poisoned_blocks"] >= 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_serving_scenarios_match_the_oracle(seed, monkeypatch):
+    """Seeded random scenarios -- slots, cache size (some small enough to preempt), prompts that share prefixes, token
+    limits, arrivals spread over steps, run-ahead on or freed-block poisoning on: every request's tokens are the oracle's."""
+    import random
+    rng = random.Random(seed)
+    run_ahead = seed % 2 == 0
+    if not run_ahead:
+        monkeypatch.setenv("JITTORINFER_KV_POISON", "1")
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    o = OracleModel(hp, w)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    n_slots = rng.choice([2, 3, 4])
+    eng = LLMEngine(m, EngineConfig(n_ctx=rng.choice([512, 768, 2048]), n_batch=rng.choice([48, 128]), n_parallel=n_slots, n_ctx_slot=320,
+                                    defrag_thold=rng.choice([-1.0, 0.05]), run_ahead=run_ahead))
+    base = [rng.randrange(hp.n_vocab) for _ in range(200)]
+    reqs = []
+    for _ in range(rng.randint(4, 7)):
+        if rng.random() < 0.5:
+            prompt = base[:rng.choice([64, 130, 190])] + [rng.randrange(hp.n_vocab) for _ in range(rng.randint(1, 30))]
+        else:
+            prompt = [rng.randrange(hp.n_vocab) for _ in range(rng.randint(1, 150))]
+        reqs.append((rng.randint(0, 10), prompt, rng.randint(1, 18)))
+    ids, step = {}, 0
+    while step < 12 or eng.has_work():
+        for i, (when, prompt, n_new) in enumerate(reqs):
+            if when == step:
+                ids[i] = eng.add_request(prompt, SamplingParams(ignore_eos=True, max_tokens=n_new))
+        eng.step()
+        step += 1
+        assert step < 2000
+    for i, (_, prompt, n_new) in enumerate(reqs):
+        st = eng.requests[ids[i]]
+        assert st.output == o.generate(prompt, n_new), (seed, i)
+        assert st.finish_reason == "length"
+    assert eng.kv.check()
