@@ -172,7 +172,7 @@ class OpProfile:
 def comm_hooks(model) -> List[Tuple[object, Sequence[str]]]:
     """The collective entry points of a model's communicator / expert dispatcher, for ``OpProfile(extra=...)``."""
     return [(getattr(model, "comm", None), ("all_reduce", "linear_all_reduce", "all_gather_rows", "allgather_linear",
-                                            "reduce_scatter_rows", "linear_reduce_scatter")),
+                                            "reduce_scatter_rows", "linear_reduce_scatter", "moe_ffn_all_reduce")),
             (getattr(model, "ep", None), ("moe_ffn",))]
 
 
