@@ -16,6 +16,10 @@ the table shows where the *step* goes rather than what the kernels cost.  Nested
 Command line (random-init weights; one prefill chunk and a few eager decode steps)::
 
     python -m jittorinfer_b200.ops.profile --model lite --prefill 2048 --decode-batch 8 --json breakdown.json
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m jittorinfer_b200.ops.profile --model v2
+
+(under ``torchrun`` the model is tensor/expert-parallel over the ranks, the collectives appear as rows of their own, and
+rank 0 prints its view).
 
 This is the counterpart of the reference's per-op timing helpers (``llama_perf_context`` gives totals only; its op-speed
 test times single ops: tests/test_ops_speed.cpp).
@@ -24,6 +28,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 import time
 from typing import Dict, Iterable, List, Sequence, Tuple
@@ -228,16 +233,31 @@ def main(argv=None) -> int:
     hp = preset(args.model)
     if args.layers:
         hp = dataclasses.replace(hp, n_layer=args.layers, n_layer_dense_lead=min(hp.n_layer_dense_lead, args.layers))
+    # under torchrun (WORLD_SIZE > 1) the model is tensor/expert-parallel over the ranks; rank 0 reports its own view
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     dev = torch.device(args.device)
+    if world > 1:
+        import torch.distributed as dist
+        if dev.type == "cuda":
+            dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+            torch.cuda.set_device(dev)
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            dist.init_process_group("gloo")
     n_slot = max(args.prefill + 64, 256)
-    eng = build_engine(hp, device=dev, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32,
+    eng = build_engine(hp, device=dev, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32, world=world, rank=rank,
                        n_parallel=max(args.decode_batch, 1) + 2, n_ctx_slot=n_slot, n_batch=max(args.prefill, 64),
                        cuda_graphs=False)
     res = profile_engine(eng, args.prefill, args.decode_batch, args.decode_steps, leaves=args.leaves)
-    for phase, prof in res.items():
-        print(f"== {phase} ==")
-        print(prof.format())
-        print()
+    if rank == 0:
+        for phase, prof in res.items():
+            print(f"== {phase} ==")
+            print(prof.format())
+            print()
+    if world > 1:
+        dist.barrier()
+        if rank != 0:
+            return 0
     if args.json:
         with open(args.json, "w") as f:
             json.dump({"model": args.model, "layers": hp.n_layer, "prefill_tokens": args.prefill, "decode_batch": args.decode_batch,
