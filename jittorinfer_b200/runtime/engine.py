@@ -64,6 +64,8 @@ class RequestState:
     t_first: float = 0.0
     t_done: float = 0.0
     dev: Optional[DeviceSampler] = None    # sampled on the device (then sampler is None)
+    logprobs: List[Tuple[int, float, List[Tuple[int, float]]]] = field(default_factory=list)
+    # per generated token (params.logprobs): (token id, its log-probability, [(id, log-probability)] of the top alternatives)
 
 
 @dataclass
@@ -263,11 +265,16 @@ class LLMEngine:
             n = logits.shape[0]
             rows = self.io.d["samp"].view(torch.float32).view(-1, 5)[:n]
             return ops.sample_topk(v.contiguous(), i.contiguous(), rows)
+        if mode == "topk_lp":            # candidates plus the row's log-normaliser: log-probabilities on the host
+            lse = torch.logsumexp(logits.float(), dim=-1, keepdim=True)
+            return torch.cat([v.contiguous().view(torch.int32), i, lse.contiguous().view(torch.int32)], dim=-1)
         return torch.cat([v.contiguous().view(torch.int32), i], dim=-1)
 
     def _step_mode(self, states) -> str:
         """greedy: ids by arg-max; sample: at least one request is sampled on the device, none needs the host chain;
         topk: candidates go to the host chain."""
+        if any(s.params.logprobs for s in states):
+            return "topk_lp"
         if any(s.sampler is not None for s in states):
             return "topk"
         return "sample" if any(s.dev is not None for s in states) else "greedy"
@@ -456,7 +463,7 @@ class LLMEngine:
     # and continues synchronously.
     def _all_greedy(self) -> bool:
         """No live request needs the host sampler chain (ids are chosen on the device: arg-max or the device sampler)."""
-        return all(st.sampler is None for st in self.requests.values() if st.finish_reason is None)
+        return all(st.sampler is None and not st.params.logprobs for st in self.requests.values() if st.finish_reason is None)
 
     def _collect(self, infl: _InFlight) -> np.ndarray:
         if infl.event is not None:
@@ -689,13 +696,19 @@ class LLMEngine:
                 k = res.shape[1] // 2
                 for i, st in enumerate(states):
                     vals = res[i, :k].view(np.float32)
-                    ids = res[i, k:]
+                    ids = res[i, k:2 * k]
                     if st.dev is not None:
                         sampled[i] = st.dev.sample_host(vals, ids, samp_rows[i])
                     elif st.sampler is None:
                         sampled[i] = ids[int(np.argmax(vals))]
                     else:
                         sampled[i] = st.sampler.sample(vals, ids)
+                    if mode == "topk_lp" and st.params.logprobs:
+                        lp = vals.astype(np.float64) - float(res[i, 2 * k:2 * k + 1].view(np.float32)[0])
+                        hit = np.nonzero(ids == sampled[i])[0]
+                        n_alt = max(0, min(int(st.params.top_logprobs), k))
+                        st.logprobs.append((int(sampled[i]), float(lp[hit[0]]) if hit.size else float("-inf"),
+                                            [(int(ids[j]), float(lp[j])) for j in range(n_alt)]))
             for i, st in enumerate(states):
                 if st.sampler is not None:
                     st.sampler.accept(int(sampled[i]))

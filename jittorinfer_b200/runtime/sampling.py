@@ -40,6 +40,8 @@ class SamplingParams:
     dry_penalty_last_n: int = -1
     min_keep: int = 0
     grammar: Optional[str] = None     # GBNF text: candidates that cannot continue it are dropped (needs the native chain)
+    logprobs: bool = False            # report the log-probability of every generated token ...
+    top_logprobs: int = 0             # ... and of this many most likely alternatives (at most the device top-k width)
     seed: Optional[int] = None
     max_tokens: int = -1
     ignore_eos: bool = False

@@ -41,6 +41,7 @@ class _Stream:
     t_first: float = 0.0
     done: bool = False
     tokens: List[int] = field(default_factory=list)      # generated ids (returned when the request sets return_tokens)
+    logprobs: list = field(default_factory=list)          # per generated token (id, logprob, alternatives) when requested
 
 
 class Metrics:
@@ -308,6 +309,9 @@ class ServerContext:
                         eng.requests.pop(rid, None)
                     continue
                 if tok >= 0:
+                    es = eng.requests.get(rid)
+                    if es is not None and es.params.logprobs and len(es.logprobs) > len(st.logprobs):
+                        st.logprobs.append(es.logprobs[len(st.logprobs)])      # this rank sampled it: the entry is there
                     self._on_token(st, tok)
                 if fin is not None and not st.done:
                     self._finish(st, "stop" if fin == "stop" else ("cancelled" if fin == "cancelled" else "length"))
@@ -495,6 +499,10 @@ def make_handler(ctx: ServerContext):
             except (json.JSONDecodeError, UnicodeDecodeError, ValueError) as e:
                 ctx.metrics.inc("requests_failed_total")
                 return self._json(400, P.error_body(f"invalid request: {e}", 400))
+            if req.params.logprobs and getattr(ctx.engine, "dp", False) and ctx.world > 1:
+                # with data-parallel attention a request is sampled on the rank that owns it; only ids travel back
+                ctx.metrics.inc("requests_failed_total")
+                return self._json(400, P.error_body("logprobs are not available with attention_dp", 400))
             if req.grammar and getattr(ctx.cfg, "enforce_response_format", True):
                 req.params.grammar = req.grammar               # response_format is enforced token by token
                 if getattr(ctx.engine, "token_table", None) is None:
@@ -542,16 +550,21 @@ def make_handler(ctx: ServerContext):
                     else:
                         return self._json(503, P.error_body(item[1], 503, "unavailable_error"))
                 results.append((st, text, reason, timings))
+            piece = lambda t: ctx.tokenizer.piece_bytes(t, special=True).decode("utf-8", errors="replace")      # noqa: E731
             if req.chat:
                 st, text, reason, timings = results[0]
                 reasoning, content = split_reasoning(text, ctx.reasoning)
-                return self._json(200, P.chat_response(rid, req.model, content, reasoning, parse_tool_call(content), reason,
-                                                       st.n_prompt, st.n_gen, timings))
+                body = P.chat_response(rid, req.model, content, reasoning, parse_tool_call(content), reason, st.n_prompt, st.n_gen, timings)
+                if req.params.logprobs:
+                    body["choices"][0]["logprobs"] = P.chat_logprobs(st.logprobs, piece)
+                return self._json(200, body)
             if len(results) == 1:
                 st, text, reason, timings = results[0]
                 body = P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, 0, timings)
                 if req.return_tokens:
                     body["choices"][0]["tokens"] = list(st.tokens)
+                if req.params.logprobs:
+                    body["choices"][0]["logprobs"] = P.completion_logprobs(st.logprobs, piece)
                 return self._json(200, body)
             out = [P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, i, timings)
                    for i, (st, text, reason, timings) in enumerate(results)]
@@ -575,6 +588,10 @@ def make_handler(ctx: ServerContext):
                     usage = {"prompt_tokens": st.n_prompt, "completion_tokens": st.n_gen, "total_tokens": st.n_prompt + st.n_gen}
                     obj = P.chat_chunk(rid, req.model, {}, item[1], usage) if req.chat else P.completion_chunk(rid, req.model, "", item[1], usage)
                     obj["timings"] = item[2]
+                    if req.params.logprobs:      # streamed text is cut at code-point boundaries, not token boundaries: the
+                        piece = lambda t: ctx.tokenizer.piece_bytes(t, special=True).decode("utf-8", errors="replace")      # noqa: E731
+                        obj["choices"][0]["logprobs"] = (P.chat_logprobs if req.chat else P.completion_logprobs)(st.logprobs, piece)
+                        # per-token log-probabilities of the whole answer come with the final chunk
                     self._chunk(P.sse(obj))
                 else:
                     self._chunk(P.sse(P.error_body(item[1], 503, "unavailable_error")))

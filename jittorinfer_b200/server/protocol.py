@@ -81,8 +81,12 @@ def sampling_from_body(body: Dict[str, Any], default_max: int) -> SamplingParams
             raise BadRequest(f"\"{key}\" out of range")
         return v
 
-    if int(body.get("n_probs", body.get("logprobs", 0)) or 0) != 0:
-        raise BadRequest("n_probs / logprobs are not supported")                   # as in the reference (server.cpp:1555)
+    if int(body.get("n_probs", 0) or 0) != 0:
+        raise BadRequest("n_probs is not supported (use the OpenAI \"logprobs\" field)")      # as in the reference (server.cpp:1555)
+    # OpenAI forms: completions "logprobs": n (0..20 alternatives per token); chat "logprobs": true + "top_logprobs": n
+    lp = body.get("logprobs")
+    want_lp = lp is not None and lp is not False
+    n_alt = num("top_logprobs", 0, 0, 20, cast=int) if isinstance(lp, bool) or lp is None else num("logprobs", 0, 0, 20, cast=int)
     if int(body.get("n", 1) or 1) != 1:
         raise BadRequest("Only one completion choice is allowed")
     for k in ("best_of", "echo", "suffix"):
@@ -111,7 +115,7 @@ def sampling_from_body(body: Dict[str, Any], default_max: int) -> SamplingParams
         min_keep=int(num("min_keep", 0, 0, cast=int)),
         logit_bias=bias, seed=None if seed in (None, -1) else int(seed),
         max_tokens=-1 if max_tokens is None else int(max_tokens), ignore_eos=bool(body.get("ignore_eos", False)),
-        stop=[str(s) for s in stop])
+        stop=[str(s) for s in stop], logprobs=bool(want_lp), top_logprobs=int(n_alt))
 
 
 def parse_completion(body: Dict[str, Any], tokenizer, model_alias: str, default_max: int) -> ParsedRequest:
@@ -193,6 +197,25 @@ def chat_chunk(rid: str, model: str, delta: Dict[str, Any], finish: Optional[str
     if usage:
         r["usage"] = usage
     return r
+
+
+def completion_logprobs(entries, piece) -> Dict[str, Any]:
+    """OpenAI text-completion form.  ``entries``: [(token id, logprob, [(id, logprob)])]; ``piece``: id -> text."""
+    toks = [piece(t) for t, _, _ in entries]
+    offs, pos = [], 0
+    for t in toks:
+        offs.append(pos)
+        pos += len(t)
+    return {"tokens": toks, "token_logprobs": [lp for _, lp, _ in entries],
+            "top_logprobs": [{piece(i): v for i, v in alts} for _, _, alts in entries], "text_offset": offs}
+
+
+def chat_logprobs(entries, piece) -> Dict[str, Any]:
+    """OpenAI chat form: ``{"content": [{"token", "logprob", "bytes", "top_logprobs": [...]}]}``."""
+    def one(i, v):
+        text = piece(i)
+        return {"token": text, "logprob": v, "bytes": list(text.encode("utf-8"))}
+    return {"content": [dict(one(t, lp), top_logprobs=[one(i, v) for i, v in alts]) for t, lp, alts in entries]}
 
 
 def sse(obj: Union[Dict[str, Any], str]) -> bytes:

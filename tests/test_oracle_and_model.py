@@ -406,3 +406,32 @@ def test_random_serving_scenarios_match_the_oracle(seed, monkeypatch):
         assert st.output == o.generate(prompt, n_new), (seed, i)
         assert st.finish_reason == "length"
     assert eng.kv.check()
+
+
+def test_logprobs_of_generated_tokens_match_the_oracle():
+    """params.logprobs: per generated token its log-probability and the most likely alternatives, from the device top-k
+    and the row's log-normaliser; compared with log_softmax of the oracle's logits."""
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    o = OracleModel(hp, w)
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.float32)
+    eng = LLMEngine(m, EngineConfig(n_ctx=1024, n_batch=64, n_parallel=2, n_ctx_slot=256, run_ahead=True))
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, hp.n_vocab, (19,), generator=g).tolist()
+    a = eng.add_request(prompt, SamplingParams(ignore_eos=True, max_tokens=6, logprobs=True, top_logprobs=3))
+    b = eng.add_request(prompt[:7], SamplingParams(ignore_eos=True, max_tokens=6))                  # a neighbour without
+    while eng.has_work():
+        eng.step()
+    st = eng.requests[a]
+    assert st.output == o.generate(prompt, 6) and eng.requests[b].logprobs == [] and len(st.logprobs) == 6
+    o.reset()
+    seq = list(prompt)
+    for n, (tok, lp, alts) in enumerate(st.logprobs):
+        o.reset()
+        ref = torch.log_softmax(o.forward(torch.tensor(seq))[-1].double(), -1)
+        assert tok == st.output[n] == int(ref.argmax())
+        assert abs(lp - float(ref[tok])) < 1e-4
+        top = torch.topk(ref, 3)
+        assert [t for t, _ in alts] == top.indices.tolist()
+        assert all(abs(x - float(y)) < 1e-4 for (_, x), y in zip(alts, top.values))
+        seq.append(tok)

@@ -200,3 +200,27 @@ def test_bounded_http_worker_pool():
         httpd.shutdown()
         httpd.server_close()
         ctx.shutdown()
+
+
+def test_logprobs_in_completions_and_chat(server):
+    url, ctx = server
+    r = _post(url + "/v1/completions", {"prompt": "hello", "max_tokens": 5, "temperature": 0, "ignore_eos": True, "logprobs": 3,
+                                        "return_tokens": True})
+    lp = r["choices"][0]["logprobs"]
+    assert len(lp["tokens"]) == len(lp["token_logprobs"]) == len(lp["top_logprobs"]) == len(lp["text_offset"]) == 5
+    assert all(v <= 1e-6 for v in lp["token_logprobs"]) and all(len(d) <= 3 for d in lp["top_logprobs"])
+    for t, v, alts in zip(lp["tokens"], lp["token_logprobs"], lp["top_logprobs"]):      # greedy: the token is the best alternative
+        assert abs(max(alts.values()) - v) < 1e-6
+    c = _post(url + "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0,
+                                             "ignore_eos": True, "logprobs": True, "top_logprobs": 2})
+    content = c["choices"][0]["logprobs"]["content"]
+    assert len(content) == 4 and all(len(e["top_logprobs"]) == 2 and e["logprob"] <= 1e-6 and isinstance(e["bytes"], list) for e in content)
+    plain = _post(url + "/v1/completions", {"prompt": "hello", "max_tokens": 5, "temperature": 0, "ignore_eos": True})
+    assert plain["choices"][0]["logprobs"] is None and plain["choices"][0]["text"] == r["choices"][0]["text"]
+    s = _post(url + "/v1/completions", {"prompt": "hello", "max_tokens": 3, "temperature": 0, "ignore_eos": True, "logprobs": 1,
+                                        "stream": True}, stream=True)
+    chunks = [json.loads(ln[6:]) for ln in s.splitlines() if ln.startswith("data: {")]
+    assert len(chunks[-1]["choices"][0]["logprobs"]["tokens"]) == 3
+    with pytest.raises(urllib.error.HTTPError) as e:
+        _post(url + "/v1/completions", {"prompt": "x", "logprobs": 50})
+    assert e.value.code == 400
