@@ -1,0 +1,75 @@
+"""The CUDA branch of the op front-end without a GPU: every call the model makes through ``ops`` must fit the signature
+of the function in ``ops.native`` that it reaches on a GPU.  A stand-in for the native module checks each call against
+the real signature (``inspect.signature(...).bind``) and then computes the result with the reference op, so a bf16 model
+pass through the "native" branch must equal the same pass through the reference branch."""
+import inspect
+import types
+
+import pytest
+import torch
+
+from jittorinfer_b200 import ops
+from jittorinfer_b200.models.deepseek2 import DeepSeek2Model
+from jittorinfer_b200.models.hparams import preset
+from jittorinfer_b200.models.weights import random_weights
+from jittorinfer_b200.ops import native
+from jittorinfer_b200.ops import reference as ref
+from jittorinfer_b200.runtime.engine import EngineConfig, LLMEngine
+from jittorinfer_b200.runtime.sampling import SamplingParams
+
+
+def _stand_in(calls, fused_norm):
+    def make(name):
+        nsig = inspect.signature(getattr(native, name))
+        rfn = getattr(ref, name)
+        n_ref = len(inspect.signature(rfn).parameters)
+
+        def f(*a, **k):
+            ba = nsig.bind(*a, **k)                     # TypeError here = the front-end does not fit the native signature
+            ba.apply_defaults()
+            calls.append(name)
+            out = rfn(*list(ba.arguments.values())[:n_ref])
+            if name == "moe_ffn" and ba.arguments.get("norm") is not None:
+                w, eps = ba.arguments["norm"]
+                return out, ref.rmsnorm(out, w, eps)[0]
+            return out
+        return f
+    names = [n for n in dir(native) if not n.startswith("_") and inspect.isfunction(getattr(native, n)) and hasattr(ref, n)]
+    fns = {n: make(n) for n in names}
+
+    def gather_rows(*a, **k):                           # the one front-end target without a reference twin
+        ba = inspect.signature(native.gather_rows).bind(*a, **k)
+        calls.append("gather_rows")
+        x, rows = list(ba.arguments.values())[:2]
+        return x[rows.long()].contiguous()
+    fns["gather_rows"] = gather_rows
+    return types.SimpleNamespace(FUSED_COMBINE_NORM=fused_norm, **fns), names
+
+
+@pytest.mark.parametrize("fused_norm", [False, True])
+@pytest.mark.parametrize("name", ["tiny", "tiny-v2", "tiny-v3"])
+def test_model_calls_fit_the_native_signatures(monkeypatch, name, fused_norm):
+    hp = preset(name)
+    w = random_weights(hp, seed=0)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (9, 30)]
+
+    def run():
+        m = DeepSeek2Model(hp, w.items(), dtype=torch.bfloat16)
+        eng = LLMEngine(m, EngineConfig(n_ctx=512, n_batch=32, n_parallel=2, n_ctx_slot=128, device_sampling=True))
+        a = eng.add_request(prompts[0], SamplingParams(ignore_eos=True, max_tokens=4))
+        b = eng.add_request(prompts[1], SamplingParams(ignore_eos=True, max_tokens=4, temperature=0.9, seed=2))
+        while eng.has_work():
+            eng.step()
+        return eng.requests[a].output, eng.requests[b].output
+
+    want = run()                                          # reference branch, bf16
+    calls = []
+    fake, names = _stand_in(calls, fused_norm)
+    monkeypatch.setattr(ops, "_native", fake)
+    monkeypatch.setattr(ops, "use_native", lambda t: True)
+    got = run()
+    assert got == want
+    used = set(calls)
+    assert {"rmsnorm", "linear", "mla_qkv_post", "q_absorb", "mla_attention", "v_up", "moe_gate", "moe_ffn", "argmax", "topk_logits",
+            "sample_topk", "embed_gather"} <= used, sorted(used)
