@@ -63,3 +63,39 @@ def test_ctypes_declarations_and_call_sites_match_the_c_prototypes():
             if want is not None and n not in want:
                 problems.append(f"{f}:{line}: {name} called with {n} arguments, C prototype has {sorted(want)}")
     assert not problems, "\n".join(problems)
+
+
+def test_descriptor_field_names_exist():
+    """ctypes structures accept assignments to names that are not fields (they become plain attributes and never reach the
+    library): every ``d.<name> = ...`` on a GEMM descriptor and every ``ctx.<name>`` write on the communicator / dispatcher
+    contexts must name a declared field."""
+    from jittorinfer_b200.ops.native import GemmDesc
+    from jittorinfer_b200.parallel.comm import ArCtx
+    from jittorinfer_b200.parallel.ep import EpCtx
+    checks = [(os.path.join(PKG, "ops", "native.py"), "d", {n for n, _ in GemmDesc._fields_}),
+              (os.path.join(PKG, "parallel", "comm.py"), "ctx", {n for n, _ in ArCtx._fields_}),
+              (os.path.join(PKG, "parallel", "ep.py"), "ctx", {n for n, _ in EpCtx._fields_})]
+    bad = []
+    for path, var, fields in checks:
+        tree = ast.parse(open(path).read())
+        n_seen = 0
+        for node in ast.walk(tree):
+            targets = []
+            if isinstance(node, ast.Assign):
+                for t in node.targets:
+                    targets += list(t.elts) if isinstance(t, ast.Tuple) else [t]
+            elif isinstance(node, ast.AugAssign):
+                targets = [node.target]
+            for t in targets:
+                base = t.value if isinstance(t, ast.Attribute) else (t.value.value if isinstance(t, ast.Subscript) and isinstance(t.value, ast.Attribute) else None)
+                attr = t.attr if isinstance(t, ast.Attribute) else (t.value.attr if isinstance(t, ast.Subscript) and isinstance(t.value, ast.Attribute) else None)
+                if attr is None:
+                    continue
+                owner = base
+                name = owner.id if isinstance(owner, ast.Name) else (owner.attr if isinstance(owner, ast.Attribute) else None)
+                if name == var:
+                    n_seen += 1
+                    if attr not in fields:
+                        bad.append(f"{os.path.relpath(path, ROOT)}:{t.lineno}: {var}.{attr} is not a field")
+        assert n_seen > 5, path
+    assert not bad, "\n".join(bad)
