@@ -319,7 +319,7 @@ void Scheduler::commit_deferred(int n_out) {
     deferred_.clear();
     for (int i = 0; i < n_out && i < (int) last_out_slots_.size(); ++i) {
         Slot & s = slots_[last_out_slots_[i]];
-        Deferred d{s.id, s.req_id, FINISH_NONE, s.n_prompt_orig, 0, s.n_past};
+        Deferred d{s.id, s.req_id, FINISH_NONE, s.n_prompt_orig, 0, s.n_past, s.ignore_eos};
         if (s.state == SLOT_IDLE) {                        // cancelled since the step was assembled: nothing to resolve
             d.req_id = -1;
             deferred_.push_back(d);
@@ -347,7 +347,9 @@ void Scheduler::resolve(const int32_t * sampled, int n_out, std::vector<StepEven
         if (d.req_id < 0) continue;
         const int32_t tok = sampled[i];
         if (d.finish != FINISH_NONE) {                     // ended by a length limit: the slot is free already
-            if (events) events->push_back({d.req_id, d.slot, tok, d.finish, d.n_prompt, d.n_decoded});
+            // the end-of-sequence token on the very step of the limit reads "stop", as commit() reports it
+            const int32_t fin = (!d.ignore_eos && tok == eos_id_) ? FINISH_STOP : d.finish;
+            if (events) events->push_back({d.req_id, d.slot, tok, fin, d.n_prompt, d.n_decoded});
             continue;
         }
         Slot & s = slots_[d.slot];

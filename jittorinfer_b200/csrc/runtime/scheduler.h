@@ -140,6 +140,7 @@ class Scheduler {
         int32_t finish;        // decided at commit time (length limits) or FINISH_NONE
         int32_t n_prompt, n_decoded;
         int32_t token_index;   // where the token lands in the slot's history once it is scheduled
+        bool ignore_eos;
     };
     std::vector<Deferred> deferred_;
 };

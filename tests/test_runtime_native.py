@@ -218,15 +218,21 @@ def test_scheduler_random_workloads_sync_and_deferred_agree():
         io = _StepIO(64, n_slots, n_ctx_slot // bs + 1, torch.device("cpu"))
         n_req = rng.randint(3, 9)
         arrivals, eos_at, cancels = {}, {}, {}
+        common = [rng.randint(10, 900) for _ in range(2 * n_ctx_slot)]          # some prompts share a prefix, some exceed the slot
         for rid in range(1, n_req + 1):
-            arrivals.setdefault(rng.randint(0, 12), []).append(
-                (rid, [rng.randint(10, 900) for _ in range(rng.randint(1, n_ctx_slot - 2))], rng.choice([-1, 1, 3, 9, 30]), rng.random() < 0.2))
+            n_tok = rng.randint(1, n_ctx_slot - 2) if rng.random() < 0.8 else rng.randint(n_ctx_slot, 2 * n_ctx_slot)
+            prompt = [rng.randint(10, 900) for _ in range(n_tok)]
+            if rng.random() < 0.5:
+                cut = rng.randint(1, n_tok)
+                prompt[:cut] = common[:cut]
+            arrivals.setdefault(rng.randint(0, 12), []).append((rid, prompt, rng.choice([-1, 1, 3, 9, 30]), rng.random() < 0.2))
             if rng.random() < 0.4:
                 eos_at[rid] = rng.randint(0, 12)
             if rng.random() < 0.2:
                 cancels[rid] = rng.randint(1, 25)
         count, out, pending, n_deferred = {}, {}, None, 0
         for it in range(600):
+            done = False
             for rid, prompt, max_new, ign in arrivals.get(it, []):
                 sched.add(rid, prompt, max_new=max_new, ignore_eos=ign)
             for rid, when in cancels.items():
@@ -251,8 +257,7 @@ def test_scheduler_random_workloads_sync_and_deferred_agree():
             else:
                 info = sched.step(io.arrays)
                 if int(info[0]) == 0:
-                    if sched.idle() and it > 14:
-                        break
+                    done = sched.idle() and it > 14
                 elif int(info[2]):
                     pending = [int(r) for r in sched.out_reqs(int(info[2]))]
                 else:
@@ -260,6 +265,8 @@ def test_scheduler_random_workloads_sync_and_deferred_agree():
             for rid, slot, tok, fin, npmt, ndec in sched.take_events():
                 out.setdefault(rid, []).append((tok, fin))
             assert kv.check()
+            if done:
+                break
         assert sched.idle(), seed
         return out, n_deferred
 
