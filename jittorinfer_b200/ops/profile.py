@@ -191,6 +191,7 @@ def profile_engine(engine, prefill_tokens: int, decode_batch: int, decode_steps:
     out: Dict[str, OpProfile] = {}
     extra = comm_hooks(engine.model)
     sp = SamplingParams(ignore_eos=True, max_tokens=decode_steps + 8)
+    ahead = engine.set_run_ahead(False)            # every profiled step() must contain its own forward pass
     if prefill_tokens > 0:
         warm = engine.add_request(torch.randint(0, n_vocab, (prefill_tokens,), generator=g).tolist(), sp)      # untimed: first-call costs
         engine.step()
@@ -212,6 +213,7 @@ def profile_engine(engine, prefill_tokens: int, decode_batch: int, decode_steps:
         out["decode"] = prof
         for r in rids:
             engine.cancel(r)
+    engine.set_run_ahead(ahead)
     return out
 
 

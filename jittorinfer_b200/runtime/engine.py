@@ -461,6 +461,19 @@ class LLMEngine:
     # output is dropped (Scheduler::resolve).  Whenever the next step is not a pure decode step of the same sequences
     # (a waiting request, a prompt chunk, scarce blocks, a sampler that needs the host), the engine first reads the ids
     # and continues synchronously.
+    def set_run_ahead(self, on: bool) -> bool:
+        """Switches run-ahead stepping on or off (tools that time single steps need the synchronous form); a step still in
+        flight is completed first.  Returns the previous setting."""
+        prev = self._run_ahead
+        if self._inflight is not None:
+            self.sched.commit(self._collect(self._inflight), self._inflight.n_out)
+            self._inflight = None
+        self._run_ahead = bool(on) and not self.dp and not getattr(self.model, "split", False)
+        if self._run_ahead and len(self._out_hosts) < 2:
+            extra = torch.zeros_like(self._out_host)
+            self._out_hosts.append(extra.pin_memory() if self.device.type == "cuda" else extra)
+        return prev
+
     def _all_greedy(self) -> bool:
         """No live request needs the host sampler chain (ids are chosen on the device: arg-max or the device sampler)."""
         return all(st.sampler is None and not st.params.logprobs for st in self.requests.values() if st.finish_reason is None)
