@@ -384,7 +384,10 @@ class LLMEngine:
         """Capture the decode graphs up front (the reference compiles its GE graph at context creation)."""
         if not self._use_graphs:
             return
+        if self._device_sampling and "sample" not in modes:
+            modes = tuple(modes) + ("sample",)      # requests sampled on the device replay their own graphs
         h = self.io.h
+        h["samp"][:] = 0
         h["slot_mapping"][:] = -1
         h["seq_lens"][:] = 0
         h["q_start"][:] = np.arange(len(h["q_start"]))
