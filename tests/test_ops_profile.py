@@ -52,3 +52,20 @@ def test_command_line_writes_json(tmp_path, capsys):
     data = json.loads(out.read_text())
     assert data["prefill"]["n_calls"] > 0 and data["decode"]["by_op"]
     assert "== prefill ==" in capsys.readouterr().out
+
+
+def test_expected_memory_time_tool(capsys):
+    """ops/expected.py: launches of one MoE layer with their algorithmic bytes; the totals match a hand count."""
+    from jittorinfer_b200.ops.expected import layer_launches, main, report
+    hp = preset("lite")
+    rows = layer_launches(hp, 8, 1100, 1)
+    assert len(rows) == 16
+    by = {k: b for k, b, _ in rows}
+    assert by["GEMM q + kv_a"] == (16 * 192 + 576) * 2048 * 2
+    hit = 64 * (1 - (1 - 6 / 64) ** 8)
+    assert abs(by["grouped GEMM down"] - (hit + 2) * 1408 * 2048 * 2) < 1
+    assert len(layer_launches(preset("v2"), 8, 1100, 8)) == 21
+    text = report(hp, 8, 1100, 1, 6.5e12, measured_ms=5.0, launches=406)
+    assert "one MoE layer" in text and "of the bound" in text
+    assert main(["--model", "v2", "--world", "8", "--bandwidth-gbs", "6538"]) == 0
+    assert "59 MoE layers" in capsys.readouterr().out
