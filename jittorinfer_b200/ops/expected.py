@@ -9,6 +9,7 @@ uniform routing, ``E_local * (1 - (1 - k/E)^T)``.
 
     python -m jittorinfer_b200.ops.expected --model lite --tokens 8 --cached 1100
     python -m jittorinfer_b200.ops.expected --model v2 --world 8 --tokens 8 --cached 1100 --measured-ms 15.27 --launches 1199
+    python -m jittorinfer_b200.ops.expected --model lite --prefill 2048 --measured-ms 55          # a prefill chunk: FLOPs and bytes
 
 The bandwidth defaults to ``hbm_gbs`` of a ``MEASURED_PEAKS.json`` next to the package if there is one, else 6.65 TB/s.
 """
@@ -75,6 +76,66 @@ def layer_launches(hp: DeepSeek2HParams, T: int, S: int, world: int = 1) -> List
     return out
 
 
+def prefill_launches(hp: DeepSeek2HParams, T: int, world: int = 1) -> List[Tuple[str, float, float, str]]:
+    """(launch, FLOPs, bytes, note) of one MoE layer for a prefill chunk of ``T`` tokens of one sequence (causal), per rank."""
+    d, H = hp.n_embd, hp.n_head // world
+    dn, dr, dv, r = hp.qk_nope_head_dim, hp.qk_rope_head_dim, hp.v_head_dim, hp.kv_lora_rank
+    E, k, nff, sh = hp.n_expert, hp.n_expert_used, hp.n_ff_exp, hp.n_expert_shared
+    out: List[Tuple[str, float, float, str]] = []
+
+    def gemm(kern, n, kk, rows=T, note="", weights=None):
+        out.append((kern, 2.0 * rows * n * kk, float((weights if weights is not None else n * kk) * 2 + rows * (n + kk) * 2), note))
+
+    def elem(kern, byts, note=""):
+        out.append((kern, 0.0, float(byts), note))
+    elem("rmsnorm (attn_norm)", T * d * 2 * 2)
+    if hp.q_lora_rank:
+        gemm("GEMM q_a + kv_a", hp.q_lora_rank + r + dr, d)
+        elem("rmsnorm (q_a_norm)", T * hp.q_lora_rank * 4)
+        gemm("GEMM q_b", H * (dn + dr), hp.q_lora_rank)
+    else:
+        gemm("GEMM q + kv_a", H * (dn + dr) + r + dr, d)
+    elem("mla_qkv_post (kv norm, RoPE, cache write)", T * (H * (dn + dr) + r + dr) * 2 * 2)
+    gemm("GEMM q_absorb (batched per head)", H * r, dn, note="per head 128 -> 512", weights=H * dn * r)
+    out.append(("flash MLA (absorbed, causal)", 2.0 * H * (T * T / 2) * ((r + dr) + r), float(T * (r + dr) * 2 + T * H * (2 * r + dr) * 2),
+                "scores over 576 dims, values over 512"))
+    gemm("GEMM v_up (batched per head)", H * dv, r, note="per head 512 -> 128", weights=H * r * dv)
+    gemm("GEMM o_proj (+ residual" + (", + all-reduce" if world > 1 else "") + ")", d, H * dv)
+    elem("rmsnorm (ffn_norm)", T * d * 2 * 2)
+    out.append(("router logits (fp32)", 2.0 * T * E * d, float(E * d * 4 + T * d * 2), ""))
+    elem("gate (top-k)", T * E * 4)
+    elem("expert sort", T * k * 4 * 4)
+    elem("gather rows", T * k * d * 2 * 2)
+    e_local = E // world
+    pairs = T * k / world if world > 1 else T * (k + sh)          # rows that reach this rank's experts
+    n_exp = e_local + (sh if world == 1 else 0)
+    gemm("grouped GEMM gate|up", 2 * nff, d, rows=pairs, weights=n_exp * 2 * nff * d, note=f"{pairs / n_exp:.0f} rows per expert")
+    gemm("grouped GEMM down", d, nff, rows=pairs, weights=n_exp * nff * d)
+    if world > 1:
+        gemm("GEMM shared gate|up", 2 * sh * nff // world, d)
+        gemm("GEMM shared down", d, sh * nff // world)
+    elem("combine (+ residual)", T * (k + 2) * d * 2)
+    if world > 1:
+        elem("all-reduce (two-shot)", T * d * (4 + 2) * (world - 1) / world, "bytes over NVLink per rank")
+    return out
+
+
+def report_prefill(hp: DeepSeek2HParams, T: int, world: int, bandwidth: float, tflops: float, measured_ms: float = 0.0) -> str:
+    rows = prefill_launches(hp, T, world)
+    lines = [f"| launch | GFLOP | MB | bound, us (max of {tflops:.0f} TFLOP/s and {bandwidth / 1e12:.2f} TB/s) | note |", "|---|---|---|---|---|"]
+    total = 0.0
+    for kern, fl, b, note in rows:
+        t = max(fl / (tflops * 1e12), b / bandwidth) * 1e6
+        total += t
+        lines.append(f"| {kern} | {fl / 1e9:.1f} | {b / 1e6:.1f} | {t:.1f} | {note} |")
+    lines.append(f"| **one MoE layer, {T} tokens** | {sum(r[1] for r in rows) / 1e9:.0f} | {sum(r[2] for r in rows) / 1e6:.0f} | **{total:.0f}** | {len(rows)} launches |")
+    n_moe = hp.n_layer - hp.n_layer_dense_lead
+    tail = f"\n{hp.n_layer} layers x ~{total:.0f} us = {hp.n_layer * total / 1e3:.1f} ms per {T}-token chunk at the bound"
+    if measured_ms > 0:
+        tail += f"; measured ~{measured_ms} ms ({hp.n_layer * total / 1e3 / measured_ms:.2f} of the bound)"
+    return "\n".join(lines) + tail + "."
+
+
 def report(hp: DeepSeek2HParams, T: int, S: int, world: int, bandwidth: float, measured_ms: float = 0.0, launches: int = 0) -> str:
     rows = layer_launches(hp, T, S, world)
     us = [b / bandwidth * 1e6 for _, b, _ in rows]
@@ -101,9 +162,14 @@ def main(argv=None) -> int:
     ap.add_argument("--bandwidth-gbs", type=float, default=0.0, help="copy bandwidth in GB/s (default: measured peaks file, else 6650)")
     ap.add_argument("--measured-ms", type=float, default=0.0)
     ap.add_argument("--launches", type=int, default=0)
+    ap.add_argument("--prefill", type=int, default=0, help="instead of a decode step: one prefill chunk of this many tokens")
+    ap.add_argument("--tflops", type=float, default=1360.0, help="sustained bf16 GEMM rate for the prefill bound")
     a = ap.parse_args(argv)
     bw = a.bandwidth_gbs * 1e9 if a.bandwidth_gbs > 0 else default_bandwidth()
-    print(report(preset(a.model), a.tokens, a.cached, a.world, bw, a.measured_ms, a.launches))
+    if a.prefill > 0:
+        print(report_prefill(preset(a.model), a.prefill, a.world, bw, a.tflops, a.measured_ms))
+    else:
+        print(report(preset(a.model), a.tokens, a.cached, a.world, bw, a.measured_ms, a.launches))
     return 0
 
 

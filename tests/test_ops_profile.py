@@ -69,3 +69,14 @@ def test_expected_memory_time_tool(capsys):
     assert "one MoE layer" in text and "of the bound" in text
     assert main(["--model", "v2", "--world", "8", "--bandwidth-gbs", "6538"]) == 0
     assert "59 MoE layers" in capsys.readouterr().out
+
+
+def test_expected_prefill_bounds():
+    from jittorinfer_b200.ops.expected import prefill_launches, report_prefill
+    hp = preset("lite")
+    rows = {k: (f, b) for k, f, b, _ in prefill_launches(hp, 2048, 1)}
+    assert rows["GEMM o_proj (+ residual)"][0] == 2.0 * 2048 * 2048 * 2048
+    assert abs(rows["flash MLA (absorbed, causal)"][0] - 2.0 * 16 * (2048 * 2048 / 2) * (576 + 512)) < 1
+    assert abs(rows["grouped GEMM gate|up"][0] - 2.0 * 2048 * 8 * 2 * 1408 * 2048) < 1
+    text = report_prefill(hp, 2048, 1, 6.5e12, 1360.0, measured_ms=55)
+    assert "27 layers" in text and "of the bound" in text
