@@ -177,10 +177,10 @@ class GGUFReader:
         from ..utils import fault
         fault.check("gguf_read")
         self.path = path
-        self._f = open(path, "rb")
-        size = os.fstat(self._f.fileno()).st_size
-        flags = mmap.MAP_PRIVATE | (getattr(mmap, "MAP_POPULATE", 0) if populate else 0)
-        self._mm = mmap.mmap(self._f.fileno(), size, flags=flags, prot=mmap.PROT_READ)
+        with open(path, "rb") as f:          # the mapping keeps its own descriptor: the file object is not needed after it
+            size = os.fstat(f.fileno()).st_size
+            flags = mmap.MAP_PRIVATE | (getattr(mmap, "MAP_POPULATE", 0) if populate else 0)
+            self._mm = mmap.mmap(f.fileno(), size, flags=flags, prot=mmap.PROT_READ)
         self._buf = memoryview(self._mm)
         self.kv: Dict[str, Any] = {}
         self.kv_types: Dict[str, int] = {}
@@ -193,7 +193,6 @@ class GGUFReader:
             self._mm.close()
         except BufferError:   # views still alive; the mapping is released with them
             pass
-        self._f.close()
 
     def __enter__(self):
         return self
