@@ -116,6 +116,7 @@ def test_server_fails_inflight_with_503_and_keeps_serving():
         assert ctx.metrics.c["requests_failed_total"] >= 1 and eng.stats["resets"] == 1
     finally:
         httpd.shutdown()
+        httpd.server_close()
         ctx.shutdown()
 
 

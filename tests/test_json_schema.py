@@ -169,6 +169,7 @@ def test_server_enforces_response_format():
         assert out["choices"][0]["finish_reason"] == "stop"
     finally:
         httpd.shutdown()
+        httpd.server_close()
         ctx.shutdown()
 
 
@@ -200,4 +201,5 @@ def test_server_rejects_a_grammar_the_engine_cannot_build():
         assert json.loads(urllib.request.urlopen(req, timeout=60).read())["object"] == "chat.completion"
     finally:
         httpd.shutdown()
+        httpd.server_close()
         ctx.shutdown()

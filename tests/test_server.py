@@ -23,6 +23,7 @@ def server():
     t.start()
     yield f"http://127.0.0.1:{httpd.server_address[1]}", ctx
     httpd.shutdown()
+    httpd.server_close()
     ctx.shutdown()
 
 
