@@ -67,6 +67,7 @@ class ServerConfig:
     attention_dp: bool = False         # ep_size ranks each serve their own requests (attention data-parallel), routed experts
                                        # sharded over them and reached through the all-to-all dispatcher
     ep_max_tokens: int = 256           # attention_dp: most tokens one rank schedules per step (sizes the dispatch buffers)
+    mixed_prompt_budget: int = 0       # most prompt tokens per step while requests are generating (0 = n_batch)
     device_sampling: bool = False      # sample on the device when a request needs only top-k / top-p / min-p / temperature
     run_ahead: bool = False            # greedy requests: launch decode step k+1 before the ids of step k reach the host
     enforce_response_format: bool = True   # chat response_format (json_object / json_schema) constrains sampling with a grammar

@@ -115,6 +115,7 @@ JIB_API int jib_sched_idle(jib_sched * s) { return s->sched.idle() ? 1 : 0; }
 JIB_API int jib_sched_n_waiting(jib_sched * s) { return s->sched.n_waiting(); }
 JIB_API int jib_sched_n_running(jib_sched * s) { return s->sched.n_running(); }
 JIB_API void jib_sched_set_n_batch(jib_sched * s, int n) { s->sched.set_n_batch(n); }
+JIB_API void jib_sched_set_mixed_prompt_budget(jib_sched * s, int n) { s->sched.set_mixed_prompt_budget(n); }
 JIB_API int jib_sched_slot_state(jib_sched * s, int slot) { return s->sched.slots()[slot].state; }
 // stats_out (7 values): steps, prompt_tokens, decode_tokens, preemptions, finished, prefix_hits, prefix_shared
 JIB_API void jib_sched_stats(jib_sched * s, int64_t * o) {

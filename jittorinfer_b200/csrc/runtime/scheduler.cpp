@@ -243,7 +243,8 @@ StepInfo Scheduler::step(StepArrays & out) {
         emit_seq(s, 1, true);
         ++info.n_decode_seqs;
     }
-    // 3. prompt chunks until the token budget is used
+    // 3. prompt chunks until the token budget is used (a smaller budget while sequences are generating, if configured)
+    const int prompt_budget = (mixed_prompt_budget_ > 0 && n_tok > 0) ? std::min(budget, n_tok + mixed_prompt_budget_) : budget;
     if (cont_batching_ || n_tok == 0) {
         order.clear();
         for (auto & s : slots_)
@@ -252,9 +253,9 @@ StepInfo Scheduler::step(StepArrays & out) {
         for (int sid : order) {
             Slot & s = slots_[sid];
             if (s.state != SLOT_STARTED && s.state != SLOT_PROCESSING_PROMPT) continue;
-            if (n_tok >= budget || n_seq >= out.cap_seqs) break;
+            if (n_tok >= prompt_budget || n_seq >= out.cap_seqs) break;
             int remaining = (int) s.tokens.size() - s.n_past;
-            int chunk = std::min(remaining, budget - n_tok);
+            int chunk = std::min(remaining, prompt_budget - n_tok);
             if (chunk <= 0) continue;
             if (!ensure_blocks(sid, chunk, -1)) {
                 // shrink the chunk to what fits right now; if nothing fits, wait for a later step

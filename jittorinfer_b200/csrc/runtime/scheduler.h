@@ -118,6 +118,10 @@ class Scheduler {
     const std::vector<int32_t> & last_out_slots() const { return last_out_slots_; }
     int n_batch() const { return n_batch_; }
     void set_n_batch(int n) { n_batch_ = n; }
+    // Most prompt tokens a step may carry while sequences are generating (0 = no extra limit).  A long prompt chunk makes
+    // every running sequence wait for it; a smaller share keeps their token-to-token latency bounded at the price of more
+    // steps for the prompt.
+    void set_mixed_prompt_budget(int n) { mixed_prompt_budget_ = n; }
 
   private:
     int pick_slot(const Request & r, int * lcp_out);
@@ -130,6 +134,7 @@ class Scheduler {
     std::vector<Slot> slots_;
     std::deque<Request> waiting_;
     int n_batch_, n_ctx_slot_, eos_id_, n_keep_;
+    int mixed_prompt_budget_ = 0;
     bool cont_batching_;
     int64_t clock_ = 0;
     std::vector<int32_t> last_out_slots_;

@@ -45,6 +45,8 @@ class EngineConfig:
     cuda_graphs: bool = True
     graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
     defrag_thold: float = -1.0         # <0 disables automatic defrag
+    mixed_prompt_budget: int = 0       # most prompt tokens per step while sequences are generating (0 = n_batch): bounds
+                                       # the token-to-token latency of running requests during somebody else's prefill
     device_sampling: bool = False      # requests that need only top-k / top-p / min-p / temperature are sampled on the device
                                        # (ops.sample_topk; also JITTORINFER_DEVICE_SAMPLING=1); the others use the host chain
     run_ahead: bool = False            # greedy requests: launch decode step k+1 before the ids of step k reach the host
@@ -173,6 +175,8 @@ class LLMEngine:
         self.kv = PagedKV(self.n_blocks, bs, cfg.n_parallel)
         self.sched = Scheduler(self.kv, cfg.n_parallel, cfg.n_batch, self.n_ctx_slot, self.hp.eos_id, cfg.n_keep,
                                cfg.cont_batching)
+        if cfg.mixed_prompt_budget > 0:
+            self.sched.set_mixed_prompt_budget(cfg.mixed_prompt_budget)
         if getattr(model, "split", False):
             self.kv_cache = SplitCache(model.layer_dev, self.n_blocks * bs, self.hp.kv_row, model.dtype, bs)
         else:
@@ -361,6 +365,8 @@ class LLMEngine:
         self.kv = PagedKV(self.n_blocks, cfg.block_size, cfg.n_parallel)
         self.sched = Scheduler(self.kv, cfg.n_parallel, cfg.n_batch, self.n_ctx_slot, self.hp.eos_id, cfg.n_keep,
                                cfg.cont_batching)
+        if cfg.mixed_prompt_budget > 0:
+            self.sched.set_mixed_prompt_budget(cfg.mixed_prompt_budget)
         self.requests.clear()
         self._pressure = False
         self._inflight = None

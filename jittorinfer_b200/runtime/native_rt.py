@@ -82,6 +82,7 @@ def lib():
         for n in ("idle", "n_waiting", "n_running"):
             sig("jib_sched_" + n, C.c_int, vp)
         sig("jib_sched_set_n_batch", None, vp, C.c_int)
+        sig("jib_sched_set_mixed_prompt_budget", None, vp, C.c_int)
         sig("jib_sched_slot_state", C.c_int, vp, C.c_int)
         sig("jib_sched_stats", None, vp, i64p)
         sig("jib_sched_out_reqs", C.c_int, vp, i64p, C.c_int)
@@ -224,6 +225,7 @@ class Scheduler:
     def n_waiting(self): return self._L.jib_sched_n_waiting(self._h)
     def n_running(self): return self._L.jib_sched_n_running(self._h)
     def set_n_batch(self, n): self._L.jib_sched_set_n_batch(self._h, n)
+    def set_mixed_prompt_budget(self, n): self._L.jib_sched_set_mixed_prompt_budget(self._h, n)
     def slot_state(self, slot): return SLOT_STATES[self._L.jib_sched_slot_state(self._h, slot)]
 
     def stats(self) -> dict:

@@ -26,7 +26,8 @@ def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
                   expert_parallel=cfg.ep_size > 1, n_keep=cfg.n_keep, cont_batching=cfg.cont_batching, defrag_thold=cfg.defrag_thold,
                   presample_count=max(1, cfg.presample_count) if cfg.presample_count > 0 else 64,
                   dp_attention=bool(getattr(cfg, "attention_dp", False)) and world > 1, ep_max_tokens=getattr(cfg, "ep_max_tokens", 256),
-                  run_ahead=bool(getattr(cfg, "run_ahead", False)), device_sampling=bool(getattr(cfg, "device_sampling", False)))
+                  run_ahead=bool(getattr(cfg, "run_ahead", False)), device_sampling=bool(getattr(cfg, "device_sampling", False)),
+                  mixed_prompt_budget=int(getattr(cfg, "mixed_prompt_budget", 0)))
     if world == 1 and device.type == "cuda" and getattr(cfg, "layer_split_gpus", 1) > 1 and cfg.split_mode == "LLAMA_SPLIT_MODE_LAYER":
         n = min(cfg.layer_split_gpus, torch.cuda.device_count())
         common.update(layer_devices=[torch.device("cuda", (cfg.main_gpu + i) % torch.cuda.device_count()) for i in range(n)],

@@ -285,3 +285,30 @@ def test_scheduler_random_workloads_sync_and_deferred_agree():
             else:
                 assert ta == tb, (seed, rid, ta, tb)
     assert total_deferred > 100
+
+
+def test_mixed_prompt_budget_bounds_prefill_next_to_decoding_sequences():
+    """With a budget for prompt tokens in steps that also decode, a long prompt arriving while another request generates is
+    fed in small chunks (the running request gets a token every step), and in full-size chunks once nothing decodes."""
+    kv = PagedKV(64, 16, 4)
+    sched = Scheduler(kv, 4, 64, 512, 2)
+    sched.set_mixed_prompt_budget(8)
+    io = _StepIO(64, 4, 33, torch.device("cpu"))
+    sched.add(1, list(range(10, 20)), max_new=12, ignore_eos=True)
+    info = sched.step(io.arrays)
+    assert int(info[0]) == 10                               # nothing decodes yet: the whole prompt in one step
+    sched.commit(np.array([50], dtype=np.int32), 1)
+    sched.add(2, list(range(100, 200)), max_new=2, ignore_eos=True)
+    sizes = []
+    for _ in range(40):
+        info = sched.step(io.arrays)
+        n_tok, n_out = int(info[0]), int(info[2])
+        if n_tok == 0:
+            break
+        sizes.append((n_tok, int(info[3])))                 # tokens in the step, decoding sequences in it
+        sched.commit(np.full(n_out, 60, dtype=np.int32), n_out)
+        sched.take_events()
+    mixed = [n for n, dec in sizes if dec >= 1 and n > dec]
+    assert mixed and max(mixed) <= 1 + 8                    # one decode token + at most 8 prompt tokens
+    assert any(n > 9 and dec == 0 for n, dec in sizes)      # after request 1 ended, the rest of the prompt goes at full width
+    assert kv.check()
