@@ -62,7 +62,8 @@ class ServerConfig:
     max_seq_len: int = 0               # per-sequence token limit; 0 = n_ctx / slots as in the reference
     max_num_seqs: Optional[int] = None
     cuda_graph_buckets: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
-    layer_split_gpus: int = 1          # split_mode LAYER: consecutive layer ranges on this many GPUs of one process
+    layer_split_gpus: int = 0          # split_mode LAYER: consecutive layer ranges on this many GPUs of one process;
+                                       # 0 = as many as the weights need (1 when they fit on main_gpu)
     tensor_split: Tuple[float, ...] = ()   # relative share of layers per GPU (reference key; empty = even)
     attention_dp: bool = False         # ep_size ranks each serve their own requests (attention data-parallel), routed experts
                                        # sharded over them and reached through the all-to-all dispatcher

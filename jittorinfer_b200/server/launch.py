@@ -28,12 +28,23 @@ def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
                   dp_attention=bool(getattr(cfg, "attention_dp", False)) and world > 1, ep_max_tokens=getattr(cfg, "ep_max_tokens", 256),
                   run_ahead=bool(getattr(cfg, "run_ahead", False)), device_sampling=bool(getattr(cfg, "device_sampling", False)),
                   mixed_prompt_budget=int(getattr(cfg, "mixed_prompt_budget", 0)))
-    if world == 1 and device.type == "cuda" and getattr(cfg, "layer_split_gpus", 1) > 1 and cfg.split_mode == "LLAMA_SPLIT_MODE_LAYER":
-        n = min(cfg.layer_split_gpus, torch.cuda.device_count())
-        common.update(layer_devices=[torch.device("cuda", (cfg.main_gpu + i) % torch.cuda.device_count()) for i in range(n)],
-                      tensor_split=list(cfg.tensor_split) or None)
+    hp_known = preset(cfg.random_init) if cfg.random_init else None
+    if world == 1 and device.type == "cuda" and cfg.split_mode == "LLAMA_SPLIT_MODE_LAYER":
+        n = int(getattr(cfg, "layer_split_gpus", 1))
+        if n <= 0:          # automatic, as the reference spreads layers over all devices by free memory (src/llama-model.cpp:495-540)
+            if hp_known is None:
+                from ..gguf.io import GGUFReader
+                from ..models.hparams import DeepSeek2HParams
+                with GGUFReader(cfg.model) as rd:
+                    hp_known = DeepSeek2HParams.from_gguf_kv(rd.kv, rd.tensors)
+            free = [torch.cuda.mem_get_info(i)[0] for i in range(torch.cuda.device_count())]
+            n = auto_layer_split(hp_known.n_params() * 2, free)
+        n = min(max(n, 1), torch.cuda.device_count())
+        if n > 1:
+            common.update(layer_devices=[torch.device("cuda", (cfg.main_gpu + i) % torch.cuda.device_count()) for i in range(n)],
+                          tensor_split=list(cfg.tensor_split) or None)
     if cfg.random_init:
-        hp = preset(cfg.random_init)
+        hp = hp_known
         eng = build_engine(hp, **common)
         kv = {k: (v[1] if isinstance(v, tuple) else v) for k, v in toy_vocab_kv(hp.n_vocab, hp.bos_id, hp.eos_id).items()}
         kv["tokenizer.ggml.bos_token_id"], kv["tokenizer.ggml.eos_token_id"] = hp.bos_id, hp.eos_id
@@ -47,6 +58,17 @@ def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
         reader.close()
         eng = build_engine(None, gguf_path=cfg.model, **common)
     return eng, tok, (cfg.chat_template or template_src or "")
+
+
+def auto_layer_split(weight_bytes: int, free_bytes, headroom: float = 0.8) -> int:
+    """Smallest number of GPUs (taken in order) whose free memory, kept to ``headroom`` of it so that the cache and
+    activations have room, holds the weights; all of them if even that is not enough."""
+    acc = 0.0
+    for n, f in enumerate(free_bytes, 1):
+        acc += headroom * f
+        if acc >= weight_bytes:
+            return n
+    return max(1, len(free_bytes))
 
 
 def main(argv=None, world: int = 1, rank: int = 0, control_group=None) -> int:

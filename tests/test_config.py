@@ -49,3 +49,16 @@ def test_kv_cache_sizing_from_memory_budget():
     assert kv_tokens_for_budget(180 * GB, 10 * GB, 0.9, 60, 576, 2) == 0                # weights already exceed the budget
     cfg = ServerConfig(kv_cache_auto=True, max_seq_len=4352, gpu_memory_utilization=0.9)
     cfg.validate()
+
+
+def test_automatic_layer_split_by_weight_size():
+    """split_mode LAYER with layer_split_gpus = 0 (default): as many GPUs as the weights need, one when they fit."""
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.server.launch import auto_layer_split
+    gib = 1 << 30
+    free8 = [178 * gib] * 8
+    assert auto_layer_split(preset("lite").n_params() * 2, free8) == 1          # 31 GB
+    n_v2 = auto_layer_split(preset("v2").n_params() * 2, free8)                  # ~470 GB of bf16 weights
+    assert 3 <= n_v2 <= 4
+    assert auto_layer_split(10 ** 15, free8) == 8 and auto_layer_split(1, []) == 1
+    assert ServerConfig().layer_split_gpus == 0
