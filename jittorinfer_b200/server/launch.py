@@ -60,6 +60,18 @@ def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
     return eng, tok, (cfg.chat_template or template_src or "")
 
 
+def apply_world(cfg, world: int) -> None:
+    """A configuration written for the reference has no tp_size / ep_size: started as N ranks it means what the reference's
+    multi-process server forces on -- tensor parallelism plus expert parallelism over all ranks
+    (examples/mpi_server/server.cpp:888-916).  Explicit sizes are kept (they must match the number of ranks)."""
+    if world <= 1:
+        return
+    if cfg.tp_size == 1 and cfg.ep_size == 1:
+        cfg.tp_size = cfg.ep_size = world
+    if cfg.world_size != world:
+        raise SystemExit(f"configuration asks for {cfg.world_size} ranks (tp_size / ep_size), started with {world}")
+
+
 def auto_layer_split(weight_bytes: int, free_bytes, headroom: float = 0.8) -> int:
     """Smallest number of GPUs (taken in order) whose free memory, kept to ``headroom`` of it so that the cache and
     activations have room, holds the weights; all of them if even that is not enough."""
@@ -92,6 +104,7 @@ def main(argv=None, world: int = 1, rank: int = 0, control_group=None) -> int:
     if not cfg.model and not cfg.random_init:
         print("config has no \"model\" (GGUF path) and no random_init preset", file=sys.stderr)
         return 2
+    apply_world(cfg, world)
     eng, tok, template_src = build_from_config(cfg, world=world, rank=rank)
     try:
         template = ChatTemplate(template_src)

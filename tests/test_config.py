@@ -62,3 +62,17 @@ def test_automatic_layer_split_by_weight_size():
     assert 3 <= n_v2 <= 4
     assert auto_layer_split(10 ** 15, free8) == 8 and auto_layer_split(1, []) == 1
     assert ServerConfig().layer_split_gpus == 0
+
+
+def test_reference_yaml_under_n_ranks_means_tp_plus_ep():
+    from jittorinfer_b200.server.launch import apply_world
+    cfg = ServerConfig()
+    apply_world(cfg, 1)
+    assert (cfg.tp_size, cfg.ep_size) == (1, 1)
+    apply_world(cfg, 8)
+    assert (cfg.tp_size, cfg.ep_size) == (8, 8)
+    dp = ServerConfig(ep_size=4, attention_dp=True)
+    apply_world(dp, 4)
+    assert (dp.tp_size, dp.ep_size) == (1, 4)
+    with pytest.raises(SystemExit):
+        apply_world(ServerConfig(tp_size=2), 4)
