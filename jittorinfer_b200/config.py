@@ -134,5 +134,9 @@ def load_yaml(path: Optional[str]) -> ServerConfig:
             cfg.ignored[k] = v
     if cfg.split_mode == "LLAMA_SPLIT_MODE_ROW" and cfg.tp_size == 1 and "tp_size" not in data:
         log.info("split_mode ROW without tp_size: set tp_size/ep_size to shard the model over GPUs")
+    if cfg.n_batch < 64:
+        # the reference's graph-engine configuration sets n_batch to its padded decode width (e.g. 16); here n_batch is
+        # the token budget of a step, i.e. the prompt chunk size
+        log.warning("n_batch %d: prompts will be processed %d tokens per step; 512-2048 is the useful range here", cfg.n_batch, cfg.n_batch)
     cfg.validate()
     return cfg
