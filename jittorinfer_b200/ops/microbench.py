@@ -57,7 +57,7 @@ def report(name, ms, nbytes, flops, extra=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gateup", "moe", "attn", "prefill_gemm"])
+    ap.add_argument("case", choices=["gemm", "gateup", "moe", "attn", "prefill_gemm", "route", "combine_norm", "permute", "sample"])
     ap.add_argument("--T", type=int, default=8)
     ap.add_argument("--N", type=int, default=32768)
     ap.add_argument("--K", type=int, default=2048)
@@ -153,6 +153,57 @@ def main(argv=None):
         ms = timeit(fn, a.iters, a.warmup)
         report(f"mla decode B={B} S={S} H={H} impl={nat.ATTN_IMPL}" + (" [torch]" if a.torch else ""), ms, B * S * 576 * 2,
                2.0 * B * H * S * (576 + 512))
+    elif a.case == "route":
+        # router chain of one MoE layer: logits + gating + expert sort as three launches vs the one-launch kernel
+        E, k, d, T = a.E, a.k, a.d, a.T
+        gx = rnd(T, d)
+        wr = torch.randn(E, d, device=dev, generator=g) * 0.05
+        for fused in (False, True):
+            nat.FUSED_ROUTE = fused
+
+            def fn():
+                ids, wts = nat.moe_gate(gx, wr, None, k, 1, 1, 1.0, False, False, 0, False, (0, E))
+                return nat.moe_permute(ids, 0, E)
+
+            ms = timeit(fn, a.iters, a.warmup)
+            report(f"route T={T} E={E} k={k} d={d} " + ("one launch" if fused else "three launches"), ms, E * d * 4 + T * d * 2, 2.0 * T * E * d)
+    elif a.case == "combine_norm":
+        # expert combine followed by the next block's RMSNorm: two launches vs one
+        k, d, T = a.k, a.d, a.T
+        y = rnd(T * k, d)
+        dest = torch.randperm(T * k, device=dev).int().view(T, k)
+        wts = torch.rand(T, k, device=dev)
+        res = rnd(T, d)
+        w = torch.ones(d, device=dev)
+        for fused in (False, True):
+            def fn():
+                if fused:
+                    return nat.moe_combine(y, dest, wts, None, res, norm=(w, 1e-6))
+                out = nat.moe_combine(y, dest, wts, None, res)
+                return out, nat.rmsnorm(out, w, 1e-6)[0]
+
+            ms = timeit(fn, a.iters, a.warmup)
+            report(f"combine+norm T={T} k={k} d={d} " + ("one launch" if fused else "two launches"), ms, T * (k + 3) * d * 2, 0.0)
+    elif a.case == "permute":
+        # expert sort of a prefill chunk: one CTA vs the histogram / scan / scatter kernels
+        E, k, T = a.E, a.k, a.T
+        ids = torch.randint(0, E, (T, k), device=dev, dtype=torch.int32)
+        for multi in (False, True):
+            nat.PERMUTE_MULTI = multi
+            ms = timeit(lambda: nat.moe_permute(ids, 0, E), a.iters, a.warmup)
+            report(f"permute T={T} k={k} E={E} " + ("multi-CTA" if multi else "one CTA"), ms, T * k * 4 * 4, 0.0)
+    elif a.case == "sample":
+        # device top-k followed by the device sampler, against the host round trip it replaces (top-k values to the host)
+        V, T, kk = a.N, a.T, 64
+        logits = torch.randn(T, V, device=dev, generator=g)
+        params = torch.tensor([[0.8, 40.0, 0.95, 0.05, 0.5]], device=dev).repeat(T, 1)
+
+        def fn():
+            v, i = nat.topk_logits(logits, kk)
+            return nat.sample_topk(v, i, params)
+
+        ms = timeit(fn, a.iters, a.warmup)
+        report(f"top-k + device sampler rows={T} vocab={V}", ms, T * V * 4, 0.0)
     torch.cuda.synchronize()
     nat.check_status()
 
