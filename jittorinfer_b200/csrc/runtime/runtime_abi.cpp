@@ -111,6 +111,7 @@ JIB_API int jib_sched_out_reqs(jib_sched * s, int64_t * out, int cap) {
     return n;
 }
 JIB_API int64_t jib_sched_slot_req(jib_sched * s, int slot) { return s->sched.slots()[slot].req_id; }
+JIB_API int jib_sched_slot_cached(jib_sched * s, int slot) { return s->sched.slots()[slot].n_cached; }
 JIB_API int jib_sched_idle(jib_sched * s) { return s->sched.idle() ? 1 : 0; }
 JIB_API int jib_sched_n_waiting(jib_sched * s) { return s->sched.n_waiting(); }
 JIB_API int jib_sched_n_running(jib_sched * s) { return s->sched.n_running(); }

@@ -81,6 +81,7 @@ void Scheduler::launch(Slot & s, const Request & r, int lcp) {
     if (n_past > 0) ++stats_.prefix_hits;
     s.tokens.swap(prompt);
     s.n_past = n_past;
+    s.n_cached = n_past;
     s.pending_token = -1;
     s.state = SLOT_STARTED;
     s.t_started = ++clock_;

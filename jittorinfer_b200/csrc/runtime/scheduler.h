@@ -39,6 +39,7 @@ struct Slot {
     int32_t n_prompt = 0;          // prompt length after truncation
     int32_t n_prompt_orig = 0;
     int32_t n_past = 0;            // tokens already evaluated into the cache
+    int32_t n_cached = 0;          // prompt tokens found in the cache when the request was (last) launched
     int32_t n_decoded = 0;
     int32_t max_new = -1;
     bool ignore_eos = false;

@@ -66,6 +66,7 @@ class RequestState:
     t_first: float = 0.0
     t_done: float = 0.0
     dev: Optional[DeviceSampler] = None    # sampled on the device (then sampler is None)
+    n_cached: int = 0                      # prompt tokens that were found in the cache (own slot or another sequence's blocks)
     logprobs: List[Tuple[int, float, List[Tuple[int, float]]]] = field(default_factory=list)
     # per generated token (params.logprobs): (token id, its log-probability, [(id, log-probability)] of the top alternatives)
 
@@ -449,6 +450,8 @@ class LLMEngine:
                 st.output.append(tok)
                 if len(st.output) == 1:
                     st.t_first = time.time()
+                    if slot >= 0:
+                        st.n_cached = self.sched.slot_cached(slot)
             if fin is not None:
                 st.finish_reason = fin
                 st.t_done = time.time()

@@ -84,6 +84,7 @@ def lib():
         sig("jib_sched_set_n_batch", None, vp, C.c_int)
         sig("jib_sched_set_mixed_prompt_budget", None, vp, C.c_int)
         sig("jib_sched_slot_state", C.c_int, vp, C.c_int)
+        sig("jib_sched_slot_cached", C.c_int, vp, C.c_int)
         sig("jib_sched_stats", None, vp, i64p)
         sig("jib_sched_out_reqs", C.c_int, vp, i64p, C.c_int)
         sig("jib_sched_slot_req", C.c_int64, vp, C.c_int)
@@ -227,6 +228,7 @@ class Scheduler:
     def set_n_batch(self, n): self._L.jib_sched_set_n_batch(self._h, n)
     def set_mixed_prompt_budget(self, n): self._L.jib_sched_set_mixed_prompt_budget(self._h, n)
     def slot_state(self, slot): return SLOT_STATES[self._L.jib_sched_slot_state(self._h, slot)]
+    def slot_cached(self, slot): return self._L.jib_sched_slot_cached(self._h, slot)      # prompt tokens reused at launch
 
     def stats(self) -> dict:
         o = np.zeros(8, dtype=np.int64)

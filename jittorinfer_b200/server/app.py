@@ -42,6 +42,7 @@ class _Stream:
     done: bool = False
     tokens: List[int] = field(default_factory=list)      # generated ids (returned when the request sets return_tokens)
     logprobs: list = field(default_factory=list)          # per generated token (id, logprob, alternatives) when requested
+    n_cached: int = 0                                     # prompt tokens served from the cache
 
 
 class Metrics:
@@ -310,6 +311,8 @@ class ServerContext:
                     continue
                 if tok >= 0:
                     es = eng.requests.get(rid)
+                    if es is not None:
+                        st.n_cached = es.n_cached
                     if es is not None and es.params.logprobs and len(es.logprobs) > len(st.logprobs):
                         st.logprobs.append(es.logprobs[len(st.logprobs)])      # this rank sampled it: the entry is there
                     self._on_token(st, tok)
@@ -554,19 +557,20 @@ def make_handler(ctx: ServerContext):
             if req.chat:
                 st, text, reason, timings = results[0]
                 reasoning, content = split_reasoning(text, ctx.reasoning)
-                body = P.chat_response(rid, req.model, content, reasoning, parse_tool_call(content), reason, st.n_prompt, st.n_gen, timings)
+                body = P.chat_response(rid, req.model, content, reasoning, parse_tool_call(content), reason, st.n_prompt, st.n_gen, timings,
+                                       st.n_cached)
                 if req.params.logprobs:
                     body["choices"][0]["logprobs"] = P.chat_logprobs(st.logprobs, piece)
                 return self._json(200, body)
             if len(results) == 1:
                 st, text, reason, timings = results[0]
-                body = P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, 0, timings)
+                body = P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, 0, timings, st.n_cached)
                 if req.return_tokens:
                     body["choices"][0]["tokens"] = list(st.tokens)
                 if req.params.logprobs:
                     body["choices"][0]["logprobs"] = P.completion_logprobs(st.logprobs, piece)
                 return self._json(200, body)
-            out = [P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, i, timings)
+            out = [P.completion_response(rid, req.model, text, reason, st.n_prompt, st.n_gen, i, timings, st.n_cached)
                    for i, (st, text, reason, timings) in enumerate(results)]
             self._json(200, out)
 
@@ -585,7 +589,8 @@ def make_handler(ctx: ServerContext):
                     obj = P.chat_chunk(rid, req.model, {"content": item[1]}, None) if req.chat else P.completion_chunk(rid, req.model, item[1], None)
                     self._chunk(P.sse(obj))
                 elif item[0] == "done":
-                    usage = {"prompt_tokens": st.n_prompt, "completion_tokens": st.n_gen, "total_tokens": st.n_prompt + st.n_gen}
+                    usage = {"prompt_tokens": st.n_prompt, "completion_tokens": st.n_gen, "total_tokens": st.n_prompt + st.n_gen,
+                             "prompt_tokens_details": {"cached_tokens": st.n_cached}}
                     obj = P.chat_chunk(rid, req.model, {}, item[1], usage) if req.chat else P.completion_chunk(rid, req.model, "", item[1], usage)
                     obj["timings"] = item[2]
                     if req.params.logprobs:      # streamed text is cut at code-point boundaries, not token boundaries: the

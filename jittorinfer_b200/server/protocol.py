@@ -150,8 +150,9 @@ def parse_chat(body: Dict[str, Any], tokenizer, template, model_alias: str, defa
 
 
 # ---- responses -------------------------------------------------------------------------------------
-def _usage(n_prompt: int, n_gen: int) -> Dict[str, int]:
-    return {"prompt_tokens": n_prompt, "completion_tokens": n_gen, "total_tokens": n_prompt + n_gen}
+def _usage(n_prompt: int, n_gen: int, n_cached: int = 0) -> Dict[str, Any]:
+    return {"prompt_tokens": n_prompt, "completion_tokens": n_gen, "total_tokens": n_prompt + n_gen,
+            "prompt_tokens_details": {"cached_tokens": n_cached}}
 
 
 def new_id(chat: bool) -> str:
@@ -159,9 +160,9 @@ def new_id(chat: bool) -> str:
 
 
 def completion_response(rid: str, model: str, text: str, finish: str, n_prompt: int, n_gen: int, index: int = 0,
-                        timings: Optional[dict] = None) -> Dict[str, Any]:
+                        timings: Optional[dict] = None, n_cached: int = 0) -> Dict[str, Any]:
     r = {"id": rid, "object": "text_completion", "created": int(time.time()), "model": model,
-         "choices": [{"text": text, "index": index, "logprobs": None, "finish_reason": finish}], "usage": _usage(n_prompt, n_gen)}
+         "choices": [{"text": text, "index": index, "logprobs": None, "finish_reason": finish}], "usage": _usage(n_prompt, n_gen, n_cached)}
     if timings:
         r["timings"] = timings
     return r
@@ -176,7 +177,7 @@ def completion_chunk(rid: str, model: str, text: str, finish: Optional[str], usa
 
 
 def chat_response(rid: str, model: str, content: str, reasoning: Optional[str], tool_call: Optional[dict], finish: str,
-                  n_prompt: int, n_gen: int, timings: Optional[dict] = None) -> Dict[str, Any]:
+                  n_prompt: int, n_gen: int, timings: Optional[dict] = None, n_cached: int = 0) -> Dict[str, Any]:
     msg: Dict[str, Any] = {"role": "assistant", "content": content}
     if reasoning is not None:
         msg["reasoning_content"] = reasoning
@@ -185,7 +186,7 @@ def chat_response(rid: str, model: str, content: str, reasoning: Optional[str], 
         msg["tool_calls"] = [dict(tool_call, id="call_" + uuid.uuid4().hex[:16])]
         finish = "tool_calls"
     r = {"id": rid, "object": "chat.completion", "created": int(time.time()), "model": model,
-         "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": _usage(n_prompt, n_gen)}
+         "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": _usage(n_prompt, n_gen, n_cached)}
     if timings:
         r["timings"] = timings
     return r

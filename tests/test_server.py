@@ -41,8 +41,11 @@ def test_completion_and_usage(server):
     assert r["usage"]["completion_tokens"] == 8 and r["usage"]["prompt_tokens"] == len(ctx.tokenizer.encode("hello there"))
     r2 = _post(url + "/v1/completions", {"prompt": "hello there", "max_tokens": 8, "temperature": 0, "ignore_eos": True})
     assert r2["choices"][0]["text"] == r["choices"][0]["text"]          # greedy is deterministic (and hits the prefix cache)
+    assert r["usage"]["prompt_tokens_details"]["cached_tokens"] == 0
+    assert r2["usage"]["prompt_tokens_details"]["cached_tokens"] == r2["usage"]["prompt_tokens"] - 1      # all but the token that yields logits
     r3 = _post(url + "/v1/completions", {"prompt": [5, 6, 7, 8], "max_tokens": 3, "temperature": 0.7, "seed": 1, "ignore_eos": True})
-    assert r3["usage"] == {"prompt_tokens": 4, "completion_tokens": 3, "total_tokens": 7}
+    assert {k: r3["usage"][k] for k in ("prompt_tokens", "completion_tokens", "total_tokens")} == \
+        {"prompt_tokens": 4, "completion_tokens": 3, "total_tokens": 7}
 
 
 def test_chat_and_stream(server):
