@@ -27,10 +27,10 @@ PROMPT_LENS = (20, 70)
 
 
 def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q, prompt_lens=PROMPT_LENS, n_batch=48,
-            sp_min_tokens=0):
+            sp_min_tokens=0, run_ahead=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), JITTORINFER_COMM=comm_impl, NCCL_NVLS_ENABLE="0",
-                      JITTORINFER_SP_MIN_TOKENS=str(sp_min_tokens))
+                      JITTORINFER_SP_MIN_TOKENS=str(sp_min_tokens), JITTORINFER_RUN_AHEAD="1" if run_ahead else "0")
     try:
         from jittorinfer_b200.models.deepseek2 import DeepSeek2Model
         from jittorinfer_b200.models.hparams import preset
@@ -69,12 +69,12 @@ def _worker(rank, world, port, backend, expert_parallel, preset_name, comm_impl,
 
 
 def _run(world, backend, expert_parallel, preset_name="tiny-v2", comm_impl="nccl", graphs=True, timeout=150,
-         prompt_lens=PROMPT_LENS, n_batch=48, sp_min_tokens=0):
+         prompt_lens=PROMPT_LENS, n_batch=48, sp_min_tokens=0, run_ahead=False):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, backend, expert_parallel, preset_name, comm_impl, graphs, q,
-                                               prompt_lens, n_batch, sp_min_tokens))
+                                               prompt_lens, n_batch, sp_min_tokens, run_ahead))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -110,6 +110,13 @@ def test_tp_ep_two_cpu_ranks_match_oracle(expert_parallel):
     ref = _oracle("tiny-v2", False)
     assert res[0][1] == res[1][1] == ref            # every rank samples the same tokens as the single-rank oracle
     assert res[0][2] > 0                            # collectives really ran
+
+
+def test_tp_ep_two_cpu_ranks_running_one_step_ahead():
+    """Run-ahead stepping on tensor/expert-parallel ranks: every rank takes the same scheduling decisions without seeing
+    the ids, so the ranks stay in lockstep and produce the oracle's tokens."""
+    res = _run(2, "gloo", True, run_ahead=True)
+    assert res[0][1] == res[1][1] == _oracle("tiny-v2", False)
 
 
 @pytest.mark.parametrize("expert_parallel", [True, False])
