@@ -401,7 +401,7 @@ class ServerContext:
                 "preemptions": eng.sched.stats().get("preemptions", 0) if hasattr(eng.sched, "stats") else 0,
                 "prefix_shared": eng.sched.stats().get("prefix_shared", 0) if hasattr(eng.sched, "stats") else 0,
                 "kernel_launches": eng.launches, "h2d_bytes": eng.stats["h2d_bytes"], "d2h_bytes": eng.stats["d2h_bytes"],
-                "engine_resets": eng.stats.get("resets", 0),
+                "engine_resets": eng.stats.get("resets", 0), "run_ahead_steps": eng.stats.get("run_ahead_steps", 0),
                 # collectives this rank took part in (in-kernel or library) and how many used the two-shot (prefill) form
                 "collectives": getattr(getattr(eng.model, "comm", None), "n_collectives", 0),
                 "collectives_two_shot": getattr(getattr(eng.model, "comm", None), "n_two_shot", 0)}
