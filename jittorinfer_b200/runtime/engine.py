@@ -230,6 +230,8 @@ class LLMEngine:
     # ------------------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
         params = params or SamplingParams()
+        if len(prompt) and (min(prompt) < 0 or max(prompt) >= self.hp.n_vocab):
+            raise ValueError(f"prompt token ids must be in [0, {self.hp.n_vocab})")
         rid = self._next_id
         self._next_id += 1
         dev = DeviceSampler(params) if self._device_sampling and device_samplable(params) else None

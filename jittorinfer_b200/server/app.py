@@ -491,9 +491,12 @@ def make_handler(ctx: ServerContext):
                     return self._json(200, {"content": ctx.tokenizer.decode(list(body.get("tokens", [])))})
                 else:
                     return self._json(404, P.error_body("not found", 404, "not_found_error"))
+                n_vocab = ctx.engine.hp.n_vocab
                 for p in req.prompts:
                     if not p:
                         raise P.BadRequest("empty prompt")
+                    if min(p) < 0 or max(p) >= n_vocab:
+                        raise P.BadRequest(f"prompt token ids must be in [0, {n_vocab})")
                 if req.stream and len(req.prompts) != 1:
                     raise P.BadRequest("streaming supports a single prompt")
             except P.BadRequest as e:
