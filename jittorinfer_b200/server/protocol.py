@@ -77,6 +77,8 @@ def sampling_from_body(body: Dict[str, Any], default_max: int) -> SamplingParams
             v = cast(v)
         except (TypeError, ValueError):
             raise BadRequest(f"\"{key}\" must be a number")
+        if v != v or v in (float("inf"), float("-inf")):
+            raise BadRequest(f"\"{key}\" must be finite")
         if (lo is not None and v < lo) or (hi is not None and v > hi):
             raise BadRequest(f"\"{key}\" out of range")
         return v

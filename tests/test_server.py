@@ -77,7 +77,8 @@ def test_stop_word_and_multi_prompt(server):
 def test_errors_and_introspection(server):
     url, _ = server
     for bad in ({"prompt": "x", "n": 2}, {"prompt": "x", "n_probs": 3}, {"prompt": "x", "echo": True}, {"messages": []}, {},
-                {"prompt": [5, 10 ** 9]}, {"prompt": [3, -4]}):
+                {"prompt": [5, 10 ** 9]}, {"prompt": [3, -4]}, {"prompt": "x", "temperature": float("nan")},
+                {"prompt": "x", "top_p": float("inf")}):
         path = "/v1/chat/completions" if "messages" in bad else "/v1/completions"
         with pytest.raises(urllib.error.HTTPError) as e:
             _post(url + path, bad)
