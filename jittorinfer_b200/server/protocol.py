@@ -115,7 +115,7 @@ def sampling_from_body(body: Dict[str, Any], default_max: int) -> SamplingParams
         dry_multiplier=num("dry_multiplier", 0.0, 0.0), dry_base=num("dry_base", 1.75, 1.0),
         dry_allowed_length=int(num("dry_allowed_length", 2, 1, cast=int)), dry_penalty_last_n=int(num("dry_penalty_last_n", -1, -1, cast=int)),
         min_keep=int(num("min_keep", 0, 0, cast=int)),
-        logit_bias=bias, seed=None if seed in (None, -1) else int(seed),
+        logit_bias=bias, seed=None if seed in (None, -1) else int(seed) & 0xFFFFFFFFFFFFFFFF,
         max_tokens=-1 if max_tokens is None else int(max_tokens), ignore_eos=bool(body.get("ignore_eos", False)),
         stop=[str(s) for s in stop], logprobs=bool(want_lp), top_logprobs=int(n_alt))
 
