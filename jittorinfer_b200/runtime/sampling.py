@@ -58,7 +58,7 @@ class HostSampler:
 
     def __init__(self, params: SamplingParams):
         self.p = params
-        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else None))
+        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else 0xFFFFFFFF))      # as NativeSampler
         self.history: List[int] = []
 
     def accept(self, token: int):
