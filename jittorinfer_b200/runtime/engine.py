@@ -234,6 +234,11 @@ class LLMEngine:
             raise ValueError(f"prompt token ids must be in [0, {self.hp.n_vocab})")
         rid = self._next_id
         self._next_id += 1
+        spec = getattr(self.model, "spec", None)
+        if params.seed is None and not params.greedy and spec is not None and spec.sharded and not spec.dp_attention:
+            # tensor/expert-parallel ranks each run the sampler over identical logits: an unseeded request gets a seed
+            # that every rank derives alike (request ids advance in lockstep), or the ranks would draw different tokens
+            params = SamplingParams(**{**params.__dict__, "seed": (0x9E3779B97F4A7C15 * rid + 0x1234567) & 0xFFFFFFFF})
         dev = DeviceSampler(params) if self._device_sampling and device_samplable(params) else None
         smpl = None if dev is not None or (params.greedy and params.dry_multiplier <= 0) else \
             make_sampler(params, self.hp.n_vocab, self.hp.n_ctx_train, getattr(self, "token_table", None))

@@ -58,7 +58,7 @@ class HostSampler:
 
     def __init__(self, params: SamplingParams):
         self.p = params
-        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else 0xFFFFFFFF))      # as NativeSampler
+        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else None))
         self.history: List[int] = []
 
     def accept(self, token: int):
@@ -202,9 +202,7 @@ class DeviceSampler:
 
     def __init__(self, params: SamplingParams):
         self.p = params
-        # no seed: the same fixed default as the native chain, so that tensor-parallel ranks (which each run their own
-        # sampler over identical logits) draw alike; the server gives every unseeded request a random seed of its own
-        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else 0xFFFFFFFF))
+        self.rng = np.random.Generator(np.random.PCG64(params.seed if params.seed is not None else None))      # None: OS entropy
 
     def row(self) -> tuple:
         p = self.p
