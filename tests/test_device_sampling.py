@@ -120,3 +120,26 @@ def test_device_sampled_request_next_to_a_host_chain_request():
         eng.step()
     assert eng.requests[b].sampler is not None and len(eng.requests[b].output) == 12
     assert eng.requests[a].output == alone
+
+
+def test_unseeded_sampled_requests_get_the_same_seed_on_every_sharded_rank():
+    """Tensor/expert-parallel ranks sample independently over identical logits: without a request seed the engine derives
+    one from the request id, which advances alike on all ranks -- two engines standing in for two ranks draw the same
+    tokens; an unsharded engine leaves the seed to chance."""
+    import types
+    hp = preset("tiny")
+    w = random_weights(hp, seed=0)
+    prompt = list(range(5, 25))
+    outs = []
+    for _ in range(2):
+        eng = _engine(hp, w)
+        eng.model.spec = types.SimpleNamespace(sharded=True, dp_attention=False, tp_size=2, tp_rank=0, expert_parallel=True)
+        rid = eng.add_request(prompt, SamplingParams(temperature=1.3, top_k=50, ignore_eos=True, max_tokens=10))
+        assert eng.requests[rid].params.seed is not None
+        while eng.has_work():
+            eng.step()
+        outs.append(eng.requests[rid].output)
+    assert outs[0] == outs[1] and len(outs[0]) == 10
+    plain = _engine(hp, w)
+    rid = plain.add_request(prompt, SamplingParams(temperature=1.3, ignore_eos=True, max_tokens=2))
+    assert plain.requests[rid].params.seed is None
