@@ -117,6 +117,7 @@ class ServerContext:
 
     # ---- engine thread ------------------------------------------------------------------------------
     def start(self):
+        self._refresh_snapshot()
         self.thread = threading.Thread(target=self.run, name="engine", daemon=True)
         self.thread.start()
 
@@ -237,6 +238,7 @@ class ServerContext:
                         gid_of.pop(rid, None)
                         rid_of.pop(gid, None)
                 self.metrics.observe_step(time.time() - t0)
+                self._refresh_snapshot()
             gathered = [None] * self.world if self.rank == 0 else None
             dist.gather_object((events, eng.has_work()), gathered, dst=0, group=self.group)
             if self.rank == 0:
@@ -285,6 +287,8 @@ class ServerContext:
                     eng.cancel(t[1])
                     eng.requests.pop(t[1], None)
             if not eng.has_work():
+                if tasks:
+                    self._refresh_snapshot()      # a cancel or a rejected request changed what the endpoints show
                 continue
             t0 = time.time()
             try:
@@ -301,6 +305,7 @@ class ServerContext:
                 eng.reset()
                 continue
             self.metrics.observe_step(time.time() - t0)
+            self._refresh_snapshot()
             if getattr(self.cfg, "display_chat", False):
                 self._display_chat()
             for rid, tok, fin in events:
@@ -391,7 +396,27 @@ class ServerContext:
         self.streams.pop(st.rid, None)
 
     # ---- introspection ------------------------------------------------------------------------------
+    # The runtime objects belong to the engine thread.  HTTP threads read a snapshot that the engine thread refreshes after
+    # every step (and while idle), never the live allocator / scheduler.
+    def _refresh_snapshot(self) -> None:
+        eng = self.engine
+        self._snapshot = (self._gauges_now(), [{"id": i, "state": eng.sched.slot_state(i), "n_past": eng.kv.seq_len(i)}
+                                              for i in range(eng.cfg.n_parallel)])
+
+    def _snap(self):
+        snap = getattr(self, "_snapshot", None)
+        if snap is None or self.thread is None:
+            self._refresh_snapshot()              # no engine thread to race with
+            snap = self._snapshot
+        return snap
+
     def gauges(self) -> Dict[str, float]:
+        return self._snap()[0]
+
+    def slots(self) -> list:
+        return self._snap()[1]
+
+    def _gauges_now(self) -> Dict[str, float]:
         eng = self.engine
         return {"requests_running": eng.sched.n_running(), "requests_waiting": eng.sched.n_waiting(),
                 "kv_blocks_used": eng.kv.used_blocks, "kv_blocks_total": eng.kv.n_blocks,
@@ -452,7 +477,7 @@ def make_handler(ctx: ServerContext):
                 return self._json(200, {"object": "list", "data": [{"id": ctx.model_alias, "object": "model", "owned_by": "jittorinfer_b200"}]})
             if path == "/slots":
                 eng = ctx.engine
-                return self._json(200, [{"id": i, "state": eng.sched.slot_state(i), "n_past": eng.kv.seq_len(i)} for i in range(eng.cfg.n_parallel)])
+                return self._json(200, ctx.slots())
             if path == "/props":
                 eng = ctx.engine
                 return self._json(200, {"model_alias": ctx.model_alias, "n_ctx_slot": eng.n_ctx_slot, "total_slots": eng.cfg.n_parallel,
