@@ -66,6 +66,7 @@ uint64_t GgufFile::type_block(uint32_t t) {
     switch (t) {
         case 0: case 1: case 30: case 24: case 25: case 26: case 27: case 28: return 1;      // F32 F16 BF16 I8 I16 I32 I64 F64
         case 2: case 3: case 6: case 7: case 8: case 9: return 32;                            // Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q8_1
+        case 10: case 11: case 12: case 13: case 14: case 15: return 256;                     // Q2_K Q3_K Q4_K Q5_K Q6_K Q8_K
         default: return 0;
     }
 }
@@ -74,6 +75,7 @@ uint64_t GgufFile::type_block_bytes(uint32_t t) {
         case 0: return 4; case 1: return 2; case 30: return 2; case 24: return 1; case 25: return 2; case 26: return 4;
         case 27: return 8; case 28: return 8;
         case 2: return 18; case 3: return 20; case 6: return 22; case 7: return 24; case 8: return 34; case 9: return 36;
+        case 10: return 84; case 11: return 110; case 12: return 144; case 13: return 176; case 14: return 210; case 15: return 292;
         default: return 0;
     }
 }

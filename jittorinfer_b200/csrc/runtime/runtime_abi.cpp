@@ -167,6 +167,7 @@ JIB_API int jib_tok_eot(Tokenizer * t) { return t->config().eot; }
 JIB_API int jib_utf8_incomplete_tail(const char * s, int len) { return (int) utf8_incomplete_tail(std::string(s, len)); }
 
 // ---- GGUF reader ------------------------------------------------------------------------------
+#include "dequant.h"
 #include "gguf.h"
 
 #include <cmath>
@@ -286,6 +287,14 @@ JIB_API jib_gguf * jib_gguf_open(const char * path, int populate, char * err, in
     return g;
 }
 JIB_API void jib_gguf_close(jib_gguf * g) { delete g; }
+
+// Expands block-quantised tensor data to float (dst_bf16 == 0) or bf16.  0 ok, -1 type not handled, -2 partial block.
+JIB_API int jib_dequantize(uint32_t ggml_type, const void * src, uint64_t n_elements, void * dst, int dst_bf16, int n_threads) {
+    if ((src == nullptr || dst == nullptr) && n_elements != 0) return -3;
+    return jib::dequantize(ggml_type, src, n_elements, dst, dst_bf16 != 0, n_threads);
+}
+JIB_API uint64_t jib_quant_block_elems(uint32_t ggml_type) { return jib::quant_block_elems(ggml_type); }
+JIB_API uint64_t jib_quant_block_bytes(uint32_t ggml_type) { return jib::quant_block_bytes(ggml_type); }
 JIB_API int jib_gguf_version(jib_gguf * g) { return (int) g->file.version(); }
 JIB_API int jib_gguf_alignment(jib_gguf * g) { return (int) g->file.alignment(); }
 JIB_API int64_t jib_gguf_n_tensors(jib_gguf * g) { return (int64_t) g->file.tensors().size(); }

@@ -33,14 +33,21 @@ TYPE_BY_NAME = {
 # tensor element types (ggml_type numbering)
 GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q8_0, GGML_BF16 = 0, 1, 2, 8, 30
 GGML_I8, GGML_I16, GGML_I32 = 24, 25, 26
+GGML_Q4_1, GGML_Q5_0, GGML_Q5_1 = 3, 6, 7
+GGML_Q2_K, GGML_Q3_K, GGML_Q4_K, GGML_Q5_K, GGML_Q6_K, GGML_Q8_K = 10, 11, 12, 13, 14, 15
 
 # (block elements, block bytes)
 TYPE_TRAITS = {
     GGML_F32: (1, 4), GGML_F16: (1, 2), GGML_BF16: (1, 2), GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34),
     GGML_I8: (1, 1), GGML_I16: (1, 2), GGML_I32: (1, 4),
+    GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24),
+    GGML_Q2_K: (256, 84), GGML_Q3_K: (256, 110), GGML_Q4_K: (256, 144), GGML_Q5_K: (256, 176), GGML_Q6_K: (256, 210),
+    GGML_Q8_K: (256, 292),
 }
+QUANTIZED = frozenset(t for t, (blk, _) in TYPE_TRAITS.items() if blk > 1)
 TYPE_NAMES = {GGML_F32: "F32", GGML_F16: "F16", GGML_BF16: "BF16", GGML_Q4_0: "Q4_0", GGML_Q8_0: "Q8_0",
-              GGML_I8: "I8", GGML_I16: "I16", GGML_I32: "I32"}
+              GGML_I8: "I8", GGML_I16: "I16", GGML_I32: "I32", GGML_Q4_1: "Q4_1", GGML_Q5_0: "Q5_0", GGML_Q5_1: "Q5_1",
+              GGML_Q2_K: "Q2_K", GGML_Q3_K: "Q3_K", GGML_Q4_K: "Q4_K", GGML_Q5_K: "Q5_K", GGML_Q6_K: "Q6_K", GGML_Q8_K: "Q8_K"}
 
 
 def align_up(x: int, a: int) -> int:

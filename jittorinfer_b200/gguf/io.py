@@ -97,10 +97,8 @@ class GGUFWriter:
                 raw = t.to(torch.float16).numpy().tobytes()
             elif ggml_type == F.GGML_F32:
                 raw = t.to(torch.float32).numpy().tobytes()
-            elif ggml_type == F.GGML_Q8_0:
-                raw = F.quantize_q8_0(t.to(torch.float32).numpy()).tobytes()
-            elif ggml_type == F.GGML_Q4_0:
-                raw = F.quantize_q4_0(t.to(torch.float32).numpy()).tobytes()
+            elif ggml_type in F.QUANTIZED:
+                raw = self._quantize(name, ggml_type, t.to(torch.float32).numpy())
             else:
                 raise ValueError(f"cannot write ggml type {ggml_type}")
         else:
@@ -108,13 +106,20 @@ class GGUFWriter:
             shape = tuple(a.shape)
             if ggml_type is None:
                 ggml_type = {np.dtype(np.float32): F.GGML_F32, np.dtype(np.float16): F.GGML_F16}[a.dtype]
-            if ggml_type == F.GGML_Q8_0:
-                raw = F.quantize_q8_0(a.astype(np.float32)).tobytes()
-            elif ggml_type == F.GGML_Q4_0:
-                raw = F.quantize_q4_0(a.astype(np.float32)).tobytes()
+            if ggml_type in F.QUANTIZED:
+                raw = self._quantize(name, ggml_type, a.astype(np.float32))
             else:
                 raw = a.tobytes()
         self.tensors.append((name, shape, ggml_type, raw))
+
+    @staticmethod
+    def _quantize(name: str, ggml_type: int, x: np.ndarray) -> bytes:
+        from . import quants
+        blk = F.TYPE_TRAITS[ggml_type][0]
+        if x.ndim == 0 or x.shape[-1] % blk:
+            raise ValueError(f"tensor {name}: rows of {x.shape[-1] if x.ndim else 1} elements do not hold whole "
+                             f"{F.TYPE_NAMES[ggml_type]} blocks of {blk}")
+        return quants.quantize(ggml_type, x).tobytes()
 
     # -- serialisation ----------------------------------------------------------------------
     @staticmethod
@@ -286,10 +291,8 @@ class GGUFReader:
                 t = torch.from_numpy(raw.view(np.float16)).view(ti.shape)
             elif ti.ggml_type == F.GGML_BF16:
                 t = torch.from_numpy(raw.view(np.int16)).view(torch.bfloat16).view(ti.shape)
-            elif ti.ggml_type == F.GGML_Q8_0:
-                t = torch.from_numpy(F.dequantize_q8_0(raw, ti.n_elements)).view(ti.shape)
-            elif ti.ggml_type == F.GGML_Q4_0:
-                t = torch.from_numpy(F.dequantize_q4_0(raw, ti.n_elements)).view(ti.shape)
+            elif ti.ggml_type in F.QUANTIZED:
+                t, count = self._dequant_shard(ti, raw, dim, index, count)
             elif ti.ggml_type == F.GGML_I32:
                 t = torch.from_numpy(raw.view(np.int32)).view(ti.shape)
             else:
@@ -301,6 +304,36 @@ class GGUFReader:
             step = n // count
             t = t.narrow(dim, index * step, step)
         return t
+
+    # dtype of tensors expanded from a block-quantised type: float32, or bfloat16 when the loader stores bf16 on the device
+    # anyway (halves the host memory and the bytes sent to the device)
+    quant_out_dtype = None
+
+    def _dequant_shard(self, ti: TensorInfo, raw: np.ndarray, dim: int, index: int, count: int):
+        """Expands shard ``index`` of ``count`` along ``dim`` of a block-quantised tensor, touching only that shard's blocks
+        when the cut falls on block boundaries.  Returns (tensor, parts still to cut by the caller)."""
+        from . import quants
+        blk, bsz = F.TYPE_TRAITS[ti.ggml_type]
+        shape = tuple(ti.shape)
+        if not shape or shape[-1] % blk:
+            raise ValueError(f"tensor {ti.name}: rows of {shape[-1] if shape else 1} elements do not hold whole "
+                             f"{F.TYPE_NAMES[ti.ggml_type]} blocks")
+        blocks = raw.reshape(shape[:-1] + (shape[-1] // blk, bsz))
+        out_shape = list(shape)
+        if count > 1:
+            d = dim % len(shape)
+            n = shape[d]
+            if n % count:
+                raise ValueError(f"tensor {ti.name}: dim {dim} of size {n} not divisible by {count}")
+            step = n // count
+            if d < len(shape) - 1:
+                blocks = blocks[(slice(None),) * d + (slice(index * step, (index + 1) * step),)]
+                out_shape[d], count = step, 1
+            elif step % blk == 0:
+                blocks = blocks[..., index * step // blk:(index + 1) * step // blk, :]
+                out_shape[d], count = step, 1
+        t = quants.dequantize_torch(ti.ggml_type, blocks, self.quant_out_dtype)
+        return t.view(out_shape), count
 
     def describe(self) -> str:
         lines = [f"GGUF v{self.version} {self.path}: {len(self.kv)} kv, {len(self.tensors)} tensors"]

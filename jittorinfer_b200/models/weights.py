@@ -174,9 +174,21 @@ def random_weights(hp: DeepSeek2HParams, **kw) -> Dict[str, torch.Tensor]:
 
 
 def write_random_gguf(path: str, hp: DeepSeek2HParams, seed: int = 0, std: float = 0.02,
-                      dtype: torch.dtype = torch.float32, vocab: bool = True) -> None:
-    """Emit a random-init GGUF with the reference's key/tensor layout (and a byte-level toy vocab)."""
+                      dtype: torch.dtype = torch.float32, vocab: bool = True, quant: Optional[int] = None) -> None:
+    """Emit a random-init GGUF with the reference's key/tensor layout (and a byte-level toy vocab).
+
+    ``quant``: a block-quantised ggml type for the matrices.  As offline quantisers do, a matrix whose rows do not hold
+    whole blocks of that type falls back to Q8_0 (or stays in ``dtype``), and norms and router weights stay f32."""
+    from ..gguf import format as F
     from ..gguf.io import GGUFWriter
+
+    def pick(name: str, t: torch.Tensor):
+        if quant is None or "ffn_gate_inp" in name:
+            return None
+        for cand in (quant, F.GGML_Q8_0):
+            if t.shape[-1] % F.TYPE_TRAITS[cand][0] == 0:
+                return cand
+        return None
     w = GGUFWriter(path)
     w.add_dict(hp.to_gguf_kv())
     if vocab:
@@ -185,6 +197,8 @@ def write_random_gguf(path: str, hp: DeepSeek2HParams, seed: int = 0, std: float
     for name, t in iter_random(hp, seed=seed, std=std, dtype=torch.float32):
         if t.dim() == 1:
             w.add_tensor(name, t)                      # norms stay f32, as in real checkpoints
+        elif pick(name, t) is not None:
+            w.add_tensor(name, t, pick(name, t))
         else:
             w.add_tensor(name, t.to(dtype))
     w.write()

@@ -31,6 +31,8 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
         else:
             from ..gguf.io import GGUFReader
         reader = GGUFReader(gguf_path)
+        if dtype == torch.bfloat16 and torch.device(device).type == "cuda":
+            reader.quant_out_dtype = torch.bfloat16      # block-quantised tensors are expanded straight to the stored dtype
         if kv_overrides:                 # metadata overrides (llama_model_params.kv_overrides)
             reader.kv.update(kv_overrides)
         hp = DeepSeek2HParams.from_gguf_kv(reader.kv, reader.tensors)

@@ -31,7 +31,7 @@ def test_runtime_tests_pass_under_asan_ubsan():
     env = dict(os.environ, JITTORINFER_RUNTIME_SO=so, LD_PRELOAD=asan,
                ASAN_OPTIONS="detect_leaks=0:abort_on_error=1:halt_on_error=1", UBSAN_OPTIONS="halt_on_error=1:print_stacktrace=1")
     r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider", "tests/test_runtime_native.py",
-                        "tests/test_tokenizer.py"], cwd=ROOT, env=env, capture_output=True, text=True, timeout=800)
+                        "tests/test_tokenizer.py", "tests/test_quants.py"], cwd=ROOT, env=env, capture_output=True, text=True, timeout=800)
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0, tail
     assert "ERROR: AddressSanitizer" not in tail and "runtime error:" not in tail
