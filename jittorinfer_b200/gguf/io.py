@@ -112,6 +112,16 @@ class GGUFWriter:
                 raw = a.tobytes()
         self.tensors.append((name, shape, ggml_type, raw))
 
+    def add_tensor_lazy(self, name: str, shape, ggml_type: int, producer):
+        """Registers a tensor whose bytes ``producer()`` returns only when the file is written, so that a checkpoint larger
+        than host memory can be converted one tensor at a time.  ``producer`` returns what ``add_tensor`` accepts."""
+        shape = tuple(int(x) for x in shape)
+        n = 1
+        for x in shape:
+            n *= x
+        self.tensors.append((name, shape, ggml_type, _LazyBytes(self, name, shape, ggml_type, producer,
+                                                                  F.tensor_nbytes(ggml_type, n))))
+
     @staticmethod
     def _quantize(name: str, ggml_type: int, x: np.ndarray) -> bytes:
         from . import quants
@@ -167,11 +177,32 @@ class GGUFWriter:
                 if o > pos:
                     f.write(b"\0" * (o - pos))
                     pos = o
-                f.write(raw)
-                pos += len(raw)
+                data = raw.get() if isinstance(raw, _LazyBytes) else raw
+                f.write(data)
+                pos += len(data)
             end = F.align_up(pos, self.alignment)
             if end > pos:
                 f.write(b"\0" * (end - pos))
+
+
+class _LazyBytes:
+    """Stand-in for the bytes of a tensor that is produced at write time; knows its length for the offset table."""
+
+    def __init__(self, writer, name, shape, ggml_type, producer, nbytes):
+        self.writer, self.name, self.shape, self.ggml_type, self.producer, self.nbytes = writer, name, shape, ggml_type, producer, nbytes
+
+    def __len__(self):
+        return self.nbytes
+
+    def get(self) -> bytes:
+        tmp = GGUFWriter.__new__(GGUFWriter)
+        tmp.tensors = []
+        tmp.add_tensor(self.name, self.producer(), self.ggml_type)
+        _, shape, _, raw = tmp.tensors[0]
+        if tuple(shape) != self.shape or len(raw) != self.nbytes:
+            raise ValueError(f"tensor {self.name}: produced shape {tuple(shape)} ({len(raw)} bytes), announced {self.shape} "
+                             f"({self.nbytes} bytes)")
+        return raw
 
 
 # ----------------------------------------------------------------------------------------------

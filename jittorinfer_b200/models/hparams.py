@@ -202,6 +202,8 @@ class DeepSeek2HParams:
         hp.rope_orig_ctx = int(g("rope.scaling.original_context_length", hp.n_ctx_train))
         hp.rope_yarn_log_mul = float(g("rope.scaling.yarn_log_multiplier", 0.0))
         hp.rope_attn_factor = float(g("rope.scaling.attn_factor", 1.0))
+        hp.yarn_beta_fast = float(g("rope.scaling.yarn_beta_fast", hp.yarn_beta_fast))
+        hp.yarn_beta_slow = float(g("rope.scaling.yarn_beta_slow", hp.yarn_beta_slow))
         nv = g("vocab_size")
         if nv is None:
             toks = kv.get("tokenizer.ggml.tokens")
