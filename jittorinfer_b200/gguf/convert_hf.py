@@ -51,10 +51,11 @@ def hparams_from_hf_config(cfg: Dict[str, Any]) -> DeepSeek2HParams:
     hp.n_layer_dense_lead = int(cfg.get("first_k_dense_replace") or 0) if hp.n_expert else hp.n_layer
     hp.expert_weights_scale = float(cfg.get("routed_scaling_factor") or 1.0)
     hp.expert_weights_norm = bool(cfg.get("norm_topk_prob") or False)
-    sigmoid = cfg.get("scoring_func", "softmax") == "sigmoid"
+    v3 = mt == "deepseek_v3"                # sigmoid scores, bias-corrected group-limited choice: implied by the model type
+    sigmoid = cfg.get("scoring_func", "sigmoid" if v3 else "softmax") == "sigmoid"
     hp.expert_gating_func = "sigmoid" if sigmoid else "softmax"
     hp.group_score_top2 = sigmoid
-    method = cfg.get("topk_method") or "greedy"
+    method = cfg.get("topk_method") or ("noaux_tc" if v3 else "greedy")
     if method in ("group_limited_greedy", "noaux_tc"):
         hp.n_group, hp.topk_group = int(cfg.get("n_group") or 1), int(cfg.get("topk_group") or 1)
     else:

@@ -246,3 +246,49 @@ def test_vocabulary_conversion_agrees_with_the_tokenizers_library(tmp_path):
     assert mine.encode("x", add_special=True)[0] == tok.token_to_id(bos)
     special = mine.encode(f"a{eos}b<tool_call>", add_special=False, parse_special=True)
     assert tok.token_to_id(eos) in special and tok.token_to_id("<tool_call>") in special
+
+
+def test_v3_structure_matches_the_library_model(tmp_path):
+    """Sigmoid scores, bias-corrected group-limited choice (groups ranked by their two best experts), normalised and scaled
+    weights, and the softmax-scale correction of YaRN (mscale_all_dim = 1: scale x (1 + 0.1 ln 40)^2), which the library's V3
+    model applies like the original model does."""
+    try:
+        from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+    except Exception:                                           # pragma: no cover
+        pytest.skip("this transformers release has no DeepseekV3 model")
+    cfg = DeepseekV3Config(vocab_size=512, hidden_size=256, intermediate_size=384, num_hidden_layers=3, num_attention_heads=4,
+                           num_key_value_heads=4, first_k_dense_replace=1, kv_lora_rank=64, q_lora_rank=48, n_routed_experts=16,
+                           n_shared_experts=1, qk_nope_head_dim=32, qk_rope_head_dim=32, v_head_dim=48, num_experts_per_tok=4,
+                           moe_intermediate_size=96, routed_scaling_factor=2.5, n_group=4, topk_group=2, norm_topk_prob=True,
+                           max_position_embeddings=2560, bos_token_id=0, eos_token_id=1,
+                           rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 40.0,
+                                            "original_max_position_embeddings": 64, "beta_fast": 32.0, "beta_slow": 1.0,
+                                            "mscale": 1.0, "mscale_all_dim": 1.0})
+    torch.manual_seed(7)
+    model = DeepseekV3ForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for mod in model.modules():
+            if hasattr(mod, "e_score_correction_bias"):
+                mod.e_score_correction_bias.copy_(torch.randn_like(mod.e_score_correction_bias) * 0.1)
+    d = str(tmp_path / "hf")
+    model.save_pretrained(d, safe_serialization=True)
+    out = str(tmp_path / "m.gguf")
+    hp = convert(d, out, "f32", toy_vocab=True)
+    assert (hp.expert_gating_func, hp.group_score_top2, hp.router_bias, hp.expert_weights_norm) == ("sigmoid", True, True, True)
+    assert (hp.n_group, hp.topk_group, hp.expert_weights_scale) == (4, 2, 2.5) and abs(hp.rope_yarn_log_mul - 0.1) < 1e-12
+    ids = torch.randint(2, 512, (1, 160), generator=torch.Generator().manual_seed(8))
+    with torch.no_grad():
+        ref = model(ids).logits[0]
+    _, oracle, rd = oracle_from(out)
+    assert "blk.1.exp_probs_b.bias" in rd.tensors
+    got = oracle.forward(ids[0])
+    assert (got - ref).abs().max().item() < 2e-5 * max(1.0, ref.abs().max().item())
+    rd.close()
+    from jittorinfer_b200.runtime.factory import build_engine
+    from jittorinfer_b200.runtime.sampling import SamplingParams
+    eng = build_engine(None, gguf_path=out, device="cpu", dtype=torch.float32, n_parallel=2, n_ctx_slot=256, cuda_graphs=False)
+    prompt = ids[0, :70].tolist()                               # past the original context of 64
+    mine = eng.generate([prompt], SamplingParams(ignore_eos=True), max_new_tokens=6)[0]
+    with torch.no_grad():
+        theirs = model.generate(ids[:, :70], max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)[0, 70:].tolist()
+    assert mine == theirs
