@@ -74,6 +74,16 @@ class GGUFWriter:
             t = F.TYPE_BY_NAME[vtype]
         self.kv.append((key, t, value, None))
 
+    def add_typed(self, key: str, value: Any, t: int, et: Optional[int] = None):
+        """A key with its GGUF value type (and element type, for arrays) given as numbers: what a reader reports."""
+        if t == F.T_ARR:
+            if et is None:
+                raise ValueError(f"{key}: an array needs its element type")
+            value = [x.item() if isinstance(x, np.generic) else x for x in value]
+        elif isinstance(value, np.generic):
+            value = value.item()
+        self.kv.append((key, t, value, et))
+
     def add_dict(self, d: Dict[str, Any]):
         for k, v in d.items():
             self.add(k, v)
@@ -121,6 +131,11 @@ class GGUFWriter:
             n *= x
         self.tensors.append((name, shape, ggml_type, _LazyBytes(self, name, shape, ggml_type, producer,
                                                                   F.tensor_nbytes(ggml_type, n))))
+
+    def add_tensor_bytes(self, name: str, shape, ggml_type: int, producer):
+        """Like ``add_tensor_lazy`` for data that is already encoded: ``producer()`` returns the tensor's bytes."""
+        self.add_tensor_lazy(name, shape, ggml_type, producer)
+        self.tensors[-1][3].encoded = True
 
     @staticmethod
     def _quantize(name: str, ggml_type: int, x: np.ndarray) -> bytes:
@@ -194,7 +209,14 @@ class _LazyBytes:
     def __len__(self):
         return self.nbytes
 
+    encoded = False
+
     def get(self) -> bytes:
+        if self.encoded:
+            raw = bytes(self.producer())
+            if len(raw) != self.nbytes:
+                raise ValueError(f"tensor {self.name}: produced {len(raw)} bytes, announced {self.nbytes}")
+            return raw
         tmp = GGUFWriter.__new__(GGUFWriter)
         tmp.tensors = []
         tmp.add_tensor(self.name, self.producer(), self.ggml_type)
@@ -247,6 +269,8 @@ class GGUFReader:
         n_tensors, n_kv = struct.unpack_from("<QQ", buf, 8)
         pos = 24
 
+        last_elem_type = [0]
+
         def rd_str(p):
             n, = struct.unpack_from("<Q", buf, p)
             return bytes(buf[p + 8:p + 8 + n]).decode("utf-8", errors="replace"), p + 8 + n
@@ -257,6 +281,7 @@ class GGUFReader:
             if t == F.T_ARR:
                 et, n = struct.unpack_from("<IQ", buf, p)
                 p += 12
+                last_elem_type[0] = et
                 if et == F.T_STR:
                     out = []
                     for _ in range(n):
@@ -270,6 +295,7 @@ class GGUFReader:
             v, = struct.unpack_from(fmt, buf, p)
             return v, p + struct.calcsize(fmt)
 
+        self.kv_elem_types: Dict[str, int] = {}
         for _ in range(n_kv):
             key, pos = rd_str(pos)
             t, = struct.unpack_from("<I", buf, pos)
@@ -277,6 +303,8 @@ class GGUFReader:
             v, pos = rd_val(t, pos)
             self.kv[key] = v
             self.kv_types[key] = t
+            if t == F.T_ARR:
+                self.kv_elem_types[key] = last_elem_type[0]
         self.alignment = int(self.kv.get("general.alignment", F.DEFAULT_ALIGNMENT))
         for _ in range(n_tensors):
             name, pos = rd_str(pos)

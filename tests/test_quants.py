@@ -194,3 +194,34 @@ def test_model_from_quantised_file_equals_model_from_its_expanded_weights(tmp_pa
         eng = build_engine(None, gguf_path=path, device="cpu", dtype=torch.float32, n_parallel=2, n_ctx_slot=64, cuda_graphs=False)
         outs.append(eng.generate(prompt, SamplingParams(ignore_eos=True), max_new_tokens=8))
     assert outs[0] == outs[1]
+
+
+def test_requantise_keeps_keys_and_re_encodes_tensors(tmp_path):
+    from jittorinfer_b200.gguf.requant import main, requantize
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.models.weights import write_random_gguf
+    src, q, back = str(tmp_path / "a.gguf"), str(tmp_path / "q.gguf"), str(tmp_path / "b.gguf")
+    write_random_gguf(src, preset("tiny"), seed=1, std=0.05)
+    names = []
+    n = requantize(src, q, "q5_k", progress=names.append)
+    with GGUFReader(src) as a, GGUFReader(q) as b:
+        assert list(a.kv) == list(b.kv) and a.kv_types == b.kv_types and a.kv_elem_types == b.kv_elem_types
+        for k in a.kv:
+            va, vb = a.kv[k], b.kv[k]
+            assert (list(va) == list(vb)) if isinstance(va, (list, np.ndarray)) else (va == vb), k
+        assert list(a.tensors) == list(b.tensors) == names
+        kinds = {ti.ggml_type for ti in b.tensors.values()}
+        assert kinds == {F.GGML_F32, F.GGML_Q5_K, F.GGML_Q8_0} and 0 < n < len(names)
+        for name, ti in a.tensors.items():
+            x, y = a.tensor(name), b.tensor(name)
+            if b.tensors[name].ggml_type == F.GGML_F32:
+                assert torch.equal(x, y)                              # norms and the router: byte for byte
+            else:
+                assert (x - y).abs().max().item() < 0.05 * x.abs().max().item() + 1e-6
+    assert main([q, back, "--type", "bf16", "-q"]) == 0               # expanded once: a plain view of the file from then on
+    with GGUFReader(q) as b, GGUFReader(back) as c:
+        for name in b.tensors:
+            if c.tensors[name].ggml_type == F.GGML_BF16:
+                assert torch.equal(c.tensor(name), b.tensor(name).to(torch.bfloat16)), name
+    with pytest.raises(ValueError):
+        requantize(src, q + "x", "q8_k")
