@@ -113,13 +113,7 @@ def load_model(path: str, use_gpu: int, main_gpu: int, tp_id: int, num_parallel:
         layer_devices = [torch.device("cuda", (main_gpu + i) % n) for i in range(n)]
     model = build_model(gguf_path=path, device=device, dtype=torch.bfloat16 if on_gpu else torch.float32, world=num_parallel,
                         rank=tp_id, expert_parallel=bool(expert_parallel), layer_devices=layer_devices, tensor_split=tensor_split,
-                        kv_overrides=__import__("json").loads(kv_overrides or "{}"))
-    if check_tensors:
-        for L in model.layers:
-            for name in L.__slots__:
-                t = getattr(L, name)
-                if isinstance(t, torch.Tensor) and t.is_floating_point() and not bool(torch.isfinite(t).all()):
-                    raise ValueError(f"tensor {name} contains NaN/Inf")
+                        kv_overrides=__import__("json").loads(kv_overrides or "{}"), check_tensors=bool(check_tensors))
     h = _handle()
     _models[h] = _Model(model, device, num_parallel, tp_id, bool(data_parallel))
     return h

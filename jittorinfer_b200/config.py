@@ -23,7 +23,7 @@ SPLIT_MODES = ("LLAMA_SPLIT_MODE_NONE", "LLAMA_SPLIT_MODE_LAYER", "LLAMA_SPLIT_M
 REASONING_FORMATS = ("COMMON_REASONING_FORMAT_NONE", "COMMON_REASONING_FORMAT_DEEPSEEK")
 
 # accepted for file compatibility; they tune the reference's CPU/NPU back ends and have no effect here
-IGNORED_KEYS = {"n_threads", "n_threads_batch", "use_mlock", "check_tensors", "offload_input", "n_gpu_layers",
+IGNORED_KEYS = {"n_threads", "n_threads_batch", "use_mlock", "offload_input", "n_gpu_layers",
                 "enable_cann_flash_attention", "enable_fused_moe", "reranking", "no_perf"}
 
 
@@ -33,6 +33,7 @@ class ServerConfig:
     main_gpu: int = 0
     split_mode: str = "LLAMA_SPLIT_MODE_LAYER"
     use_mmap: bool = True
+    check_tensors: bool = False        # verify that every weight is finite while loading
     enable_mla: bool = True            # always true here: the latent cache is the only KV layout
     enable_ge: bool = True             # maps to cuda_graphs (persistent compiled decode graph)
     presample_count: int = 64          # device top-k width handed to the host sampler chain; -1 = full logits

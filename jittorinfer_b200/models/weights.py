@@ -228,6 +228,18 @@ def iter_gguf(reader, hp: DeepSeek2HParams, spec: ShardSpec = ShardSpec()) -> It
         raise ValueError(f"GGUF has {len(extra)} tensors the model does not use, e.g. {extra[:3]}")
 
 
+def checked(weights: Iterator[Tuple[str, torch.Tensor]]) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Passes the tensors on after verifying that every floating-point value is finite -- what the reference's
+    ``check_tensors`` asks of its loader (src/llama-model-loader.cpp:924-1167 validates each tensor's data while reading).
+    A truncated download or a bad conversion shows as NaN / Inf long before it shows in the output text."""
+    for name, t in weights:
+        if t.is_floating_point():
+            bad = int((~torch.isfinite(t)).sum())
+            if bad:
+                raise ValueError(f"tensor {name}: {bad} of {t.numel()} values are NaN or infinite")
+        yield name, t
+
+
 class StagedUploader:
     """Host -> device copies of large checkpoint tensors through a ring of pinned staging buffers.
 

@@ -19,7 +19,7 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
                 dtype: torch.dtype = torch.bfloat16, world: int = 1, rank: int = 0, expert_parallel: bool = True,
                 comm=None, seed: int = 0, std: float = 0.02, max_positions: int = 8192, fast_random: bool = True,
                 dp_attention: bool = False, ep_max_tokens: int = 256, layer_devices=None,
-                tensor_split=None, kv_overrides=None) -> DeepSeek2Model:
+                tensor_split=None, kv_overrides=None, check_tensors: bool = False) -> DeepSeek2Model:
     """``dp_attention``: attention data-parallel (every rank serves its own requests), routed experts sharded over the
     ranks and reached through the all-to-all dispatcher; ``ep_max_tokens`` bounds the tokens of one rank per step."""
     dp_attention = dp_attention and world > 1
@@ -37,6 +37,9 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
             reader.kv.update(kv_overrides)
         hp = DeepSeek2HParams.from_gguf_kv(reader.kv, reader.tensors)
         weights = iter_gguf(reader, hp, spec)
+        if check_tensors:                # llama_model_params.check_tensors / the YAML key of the same name
+            from ..models.weights import checked
+            weights = checked(weights)
     else:
         assert hp is not None
         dev = torch.device(device)
@@ -77,14 +80,14 @@ def build_engine(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str]
                  n_ctx_slot: int = 2048, n_batch: int = 2048, seed: int = 0, graph_buckets: Sequence[int] = (1, 2, 4, 8),
                  cuda_graphs: bool = True, expert_parallel: bool = True, comm=None, n_ctx: Optional[int] = None,
                  dp_attention: bool = False, ep_max_tokens: int = 256, layer_devices=None, tensor_split=None,
-                 gpu_memory_utilization: Optional[float] = None, **engine_kw) -> LLMEngine:
+                 gpu_memory_utilization: Optional[float] = None, check_tensors: bool = False, **engine_kw) -> LLMEngine:
     """``gpu_memory_utilization`` (with ``n_ctx`` None or 0): size the latent cache from the memory left after the weights
     are loaded, so that the process fills that share of the GPU."""
     if dp_attention and world > 1:
         n_batch = min(n_batch, ep_max_tokens)          # a step's tokens must fit the dispatcher's buffers
     model = build_model(hp, gguf_path, device, dtype, world, rank, expert_parallel, comm, seed,
                         max_positions=max(n_ctx_slot, 64), dp_attention=dp_attention, ep_max_tokens=ep_max_tokens,
-                        layer_devices=layer_devices, tensor_split=tensor_split)
+                        layer_devices=layer_devices, tensor_split=tensor_split, check_tensors=check_tensors)
     dev = torch.device(device)
     if not n_ctx and gpu_memory_utilization and dev.type == "cuda":
         free, total = torch.cuda.mem_get_info(dev)

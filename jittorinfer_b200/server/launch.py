@@ -27,7 +27,8 @@ def build_from_config(cfg, device=None, world: int = 1, rank: int = 0):
                   presample_count=max(1, cfg.presample_count) if cfg.presample_count > 0 else 64,
                   dp_attention=bool(getattr(cfg, "attention_dp", False)) and world > 1, ep_max_tokens=getattr(cfg, "ep_max_tokens", 256),
                   run_ahead=bool(getattr(cfg, "run_ahead", False)), device_sampling=bool(getattr(cfg, "device_sampling", False)),
-                  mixed_prompt_budget=int(getattr(cfg, "mixed_prompt_budget", 0)))
+                  mixed_prompt_budget=int(getattr(cfg, "mixed_prompt_budget", 0)),
+                  check_tensors=bool(getattr(cfg, "check_tensors", False)))
     hp_known = preset(cfg.random_init) if cfg.random_init else None
     if world == 1 and device.type == "cuda" and cfg.split_mode == "LLAMA_SPLIT_MODE_LAYER":
         n = int(getattr(cfg, "layer_split_gpus", 1))

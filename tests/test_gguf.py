@@ -115,3 +115,34 @@ def test_staged_uploader_chunks_and_converts():
     assert half.dtype == torch.bfloat16 and torch.equal(half, t.half().to(torch.bfloat16))
     small = StagedUploader("cpu", min_bytes=1 << 20)
     assert torch.equal(small.upload(t), t) and small.n_chunks == 0      # below the threshold: plain copy
+
+
+def test_check_tensors_rejects_a_file_with_non_finite_weights(tmp_path):
+    """``check_tensors`` (model parameter of the C API, key of the YAML files) verifies every weight while loading."""
+    import pytest
+    from jittorinfer_b200.config import ServerConfig, load_yaml
+    from jittorinfer_b200.gguf.io import GGUFReader, GGUFWriter
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.runtime.factory import build_model
+    good, bad = str(tmp_path / "good.gguf"), str(tmp_path / "bad.gguf")
+    write_random_gguf(good, preset("tiny"), seed=2)
+    with GGUFReader(good) as rd:
+        w = GGUFWriter(bad)
+        for k, v in rd.kv.items():
+            if k != "general.alignment":
+                w.add_typed(k, v, rd.kv_types[k], rd.kv_elem_types.get(k))
+        for name in rd.tensors:
+            t = rd.tensor(name).clone()
+            if name == "blk.1.ffn_up_exps.weight":
+                t[3, 5, 7] = float("nan")
+                t[0, 0, 0] = float("inf")
+            w.add_tensor(name, t)
+        w.write()
+    build_model(gguf_path=good, device="cpu", dtype=torch.float32, check_tensors=True)
+    build_model(gguf_path=bad, device="cpu", dtype=torch.float32)                       # not asked: loads
+    with pytest.raises(ValueError, match="blk.1.ffn_up_exps.weight: 2 of"):
+        build_model(gguf_path=bad, device="cpu", dtype=torch.float32, check_tensors=True)
+    y = tmp_path / "c.yaml"
+    y.write_text("model: x.gguf\ncheck_tensors: true\nuse_mlock: true\n")
+    cfg = load_yaml(str(y))
+    assert cfg.check_tensors is True and "use_mlock" in cfg.ignored and ServerConfig().check_tensors is False
