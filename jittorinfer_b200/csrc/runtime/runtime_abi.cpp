@@ -80,6 +80,17 @@ JIB_API void jib_sched_add(jib_sched * s, int64_t req_id, const int32_t * prompt
     r.ignore_eos = ignore_eos != 0;
     s->sched.add_request(r);
 }
+// As jib_sched_add, with the request's own n_keep (<0: keep the whole prompt's head when it must be cut).
+JIB_API void jib_sched_add_keep(jib_sched * s, int64_t req_id, const int32_t * prompt, int n_prompt, int max_new, int ignore_eos,
+                                int n_keep) {
+    Request r;
+    r.id = req_id;
+    r.prompt.assign(prompt, prompt + n_prompt);
+    r.max_new = max_new;
+    r.ignore_eos = ignore_eos != 0;
+    r.n_keep = n_keep;
+    s->sched.add_request(r);
+}
 JIB_API int jib_sched_cancel(jib_sched * s, int64_t req_id) { return s->sched.cancel(req_id, &s->events) ? 1 : 0; }
 // info_out: n_tokens, n_seqs, n_out, n_decode_seqs, max_q_len, n_preempted, n_copies
 JIB_API int jib_sched_step(jib_sched * s, StepArrays * arrays, int32_t * info_out) {

@@ -59,11 +59,14 @@ void Scheduler::launch(Slot & s, const Request & r, int lcp) {
     s.n_decoded = r.n_decoded_before;
     s.n_prompt_orig = r.n_prompt_orig > 0 ? r.n_prompt_orig : (int) r.prompt.size();
     s.truncated = false;
+    s.n_keep = r.n_keep;
     std::vector<int32_t> prompt = r.prompt;
     // A prompt that does not fit the slot loses blocks from its middle, keeping n_keep head tokens
     // (same policy as the reference, examples/server/server.cpp:1395-1415).
     if ((int) prompt.size() >= n_ctx_slot_ && n_ctx_slot_ > 4) {
-        int n_keep = std::min(n_keep_, n_ctx_slot_ - 4);
+        int n_keep = r.n_keep == KEEP_DEFAULT ? n_keep_ : r.n_keep;
+        if (n_keep < 0) n_keep = (int) prompt.size();          // "keep the prompt": as much of its head as fits
+        n_keep = std::min(n_keep, n_ctx_slot_ - 4);
         int n_left = n_ctx_slot_ - n_keep;
         int n_block = std::max(1, n_left / 2);
         int erased = ((int) prompt.size() - n_keep - n_block) / n_block;
@@ -113,6 +116,7 @@ void Scheduler::preempt(Slot & s) {
     r.ignore_eos = s.ignore_eos;
     r.n_decoded_before = s.n_decoded;
     r.n_prompt_orig = s.n_prompt_orig;
+    r.n_keep = s.n_keep;
     waiting_.push_front(r);
     release(s, false);
     ++stats_.preemptions;

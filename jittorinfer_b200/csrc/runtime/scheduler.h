@@ -22,6 +22,8 @@ enum SlotState : int32_t { SLOT_IDLE = 0, SLOT_STARTED, SLOT_PROCESSING_PROMPT, 
 
 enum FinishReason : int32_t { FINISH_NONE = 0, FINISH_STOP = 1, FINISH_LENGTH = 2, FINISH_CANCELLED = 3, FINISH_ERROR = 4 };
 
+constexpr int32_t KEEP_DEFAULT = INT32_MIN;
+
 struct Request {
     int64_t id = 0;
     std::vector<int32_t> prompt;
@@ -29,6 +31,7 @@ struct Request {
     bool ignore_eos = false;
     int32_t n_decoded_before = 0;  // >0 when re-queued after preemption
     int32_t n_prompt_orig = 0;
+    int32_t n_keep = KEEP_DEFAULT; // head tokens kept when the prompt is cut to fit; <0: the whole prompt; KEEP_DEFAULT: the scheduler's
 };
 
 struct Slot {
@@ -37,6 +40,7 @@ struct Slot {
     int64_t req_id = -1;
     std::vector<int32_t> tokens;   // tokens whose KV is cached or scheduled (prompt + generated)
     int32_t n_prompt = 0;          // prompt length after truncation
+    int32_t n_keep = KEEP_DEFAULT; // the request's n_keep (carried over a preemption)
     int32_t n_prompt_orig = 0;
     int32_t n_past = 0;            // tokens already evaluated into the cache
     int32_t n_cached = 0;          // prompt tokens found in the cache when the request was (last) launched

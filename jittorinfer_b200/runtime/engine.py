@@ -247,7 +247,7 @@ class LLMEngine:
             for t in prompt[-params.repeat_last_n:]:
                 st.sampler.accept(t)
         self.requests[rid] = st
-        self.sched.add(rid, prompt, params.max_tokens, params.ignore_eos)
+        self.sched.add(rid, prompt, params.max_tokens, params.ignore_eos, getattr(params, "n_keep", None))
         return rid
 
     def cancel(self, req_id: int) -> bool:

@@ -72,6 +72,7 @@ def lib():
         sig("jib_sched_create", vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int)
         sig("jib_sched_destroy", None, vp)
         sig("jib_sched_add", None, vp, C.c_int64, i32p, C.c_int, C.c_int, C.c_int)
+        sig("jib_sched_add_keep", None, vp, C.c_int64, i32p, C.c_int, C.c_int, C.c_int, C.c_int)
         sig("jib_sched_cancel", C.c_int, vp, C.c_int64)
         sig("jib_sched_step", C.c_int, vp, C.POINTER(StepArrays), i32p)
         sig("jib_sched_commit", None, vp, i32p, C.c_int)
@@ -183,9 +184,13 @@ class Scheduler:
         except Exception:
             pass
 
-    def add(self, req_id: int, prompt, max_new: int = -1, ignore_eos: bool = False):
+    def add(self, req_id: int, prompt, max_new: int = -1, ignore_eos: bool = False, n_keep=None):
+        """``n_keep``: head tokens kept if the prompt must be cut to fit a slot (None: the scheduler's; <0: all that fits)."""
         p = np.ascontiguousarray(prompt, dtype=np.int32)
-        self._L.jib_sched_add(self._h, req_id, _p32(p), len(p), max_new, int(ignore_eos))
+        if n_keep is None:
+            self._L.jib_sched_add(self._h, req_id, _p32(p), len(p), max_new, int(ignore_eos))
+        else:
+            self._L.jib_sched_add_keep(self._h, req_id, _p32(p), len(p), max_new, int(ignore_eos), int(n_keep))
 
     def cancel(self, req_id: int) -> bool:
         return bool(self._L.jib_sched_cancel(self._h, req_id))

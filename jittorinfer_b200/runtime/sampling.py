@@ -45,6 +45,7 @@ class SamplingParams:
     seed: Optional[int] = None
     max_tokens: int = -1
     ignore_eos: bool = False
+    n_keep: Optional[int] = None      # head tokens kept if the prompt must be cut to fit (None: engine default; <0: all that fits)
     stop: List[str] = field(default_factory=list)
 
     @property

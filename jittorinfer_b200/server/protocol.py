@@ -105,7 +105,11 @@ def sampling_from_body(body: Dict[str, Any], default_max: int) -> SamplingParams
     if isinstance(stop, str):
         stop = [stop]
     seed = body.get("seed")
+    n_keep = body.get("n_keep")                # per request, as the reference reads it (examples/server/server.cpp:90, 1390-1393)
+    if n_keep is not None:
+        n_keep = int(num("n_keep", 0, cast=int))
     return SamplingParams(
+        n_keep=n_keep,
         temperature=num("temperature", 0.8, 0.0), top_k=int(num("top_k", 40, 0, cast=int)), top_p=num("top_p", 0.95, 0.0, 1.0),
         min_p=num("min_p", 0.05, 0.0, 1.0), typical_p=num("typical_p", 1.0, 0.0, 1.0),
         xtc_probability=num("xtc_probability", 0.0, 0.0, 1.0), xtc_threshold=num("xtc_threshold", 0.1, 0.0, 1.0),

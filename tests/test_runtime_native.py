@@ -312,3 +312,25 @@ def test_mixed_prompt_budget_bounds_prefill_next_to_decoding_sequences():
     assert mixed and max(mixed) <= 1 + 8                    # one decode token + at most 8 prompt tokens
     assert any(n > 9 and dec == 0 for n, dec in sizes)      # after request 1 ended, the rest of the prompt goes at full width
     assert kv.check()
+
+
+def test_per_request_n_keep_decides_which_head_survives_a_cut():
+    """A prompt longer than a slot loses whole chunks from its middle; the head that stays is the request's ``n_keep``
+    (examples/server/server.cpp:90, 1390-1415 reads it per request), the scheduler's default when the request names none,
+    and "as much of the prompt as fits" when it is negative -- also after a preemption re-queues the request."""
+    def first_step_tokens(n_keep, default_keep=0):
+        kv = PagedKV(64, 16, 2)
+        sched = Scheduler(kv, 2, 512, 64, eos_id=7, n_keep=default_keep)
+        io = _StepIO(512, 2, 8, torch.device("cpu"))
+        sched.add(1, list(range(1000, 1200)), max_new=2, n_keep=n_keep)        # 200 tokens into a slot of 64
+        info = sched.step(io.arrays)
+        return io.h["tokens"][: int(info[0])].tolist()
+
+    t0 = first_step_tokens(None)
+    assert t0[0] != 1000 and t0[-1] == 1199 and len(t0) < 64               # default 0: nothing of the head is kept
+    t5 = first_step_tokens(5)
+    assert t5[:5] == [1000, 1001, 1002, 1003, 1004] and t5[5] > 1004 and t5[-1] == 1199 and len(t5) < 64
+    assert first_step_tokens(None, default_keep=5) == t5                    # the engine-wide default does the same
+    assert first_step_tokens(0, default_keep=5) == t0                       # and a request may ask for less
+    tall = first_step_tokens(-1)
+    assert tall[:60] == list(range(1000, 1060)) and tall[-1] == 1199 and len(tall) < 64

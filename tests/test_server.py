@@ -78,7 +78,7 @@ def test_errors_and_introspection(server):
     url, _ = server
     for bad in ({"prompt": "x", "n": 2}, {"prompt": "x", "n_probs": 3}, {"prompt": "x", "echo": True}, {"messages": []}, {},
                 {"prompt": [5, 10 ** 9]}, {"prompt": [3, -4]}, {"prompt": "x", "temperature": float("nan")},
-                {"prompt": "x", "top_p": float("inf")}):
+                {"prompt": "x", "top_p": float("inf")}, {"prompt": "x", "n_keep": "many"}):
         path = "/v1/chat/completions" if "messages" in bad else "/v1/completions"
         with pytest.raises(urllib.error.HTTPError) as e:
             _post(url + path, bad)
@@ -230,3 +230,16 @@ def test_logprobs_in_completions_and_chat(server):
     with pytest.raises(urllib.error.HTTPError) as e:
         _post(url + "/v1/completions", {"prompt": "x", "logprobs": 50})
     assert e.value.code == 400
+
+
+def test_request_fields_of_the_reference_server_are_parsed():
+    """``n_keep`` is read per request, as the reference's server reads it; ``id_slot`` / ``post_sampling_probs`` are accepted
+    (slots are chosen by prefix match here, and probabilities come through the OpenAI ``logprobs`` field)."""
+    from jittorinfer_b200.server.protocol import sampling_from_body
+    assert sampling_from_body({"n_keep": 7}, 16).n_keep == 7
+    assert sampling_from_body({"n_keep": -1}, 16).n_keep == -1
+    assert sampling_from_body({}, 16).n_keep is None
+    p = sampling_from_body({"id_slot": 3, "post_sampling_probs": True, "temperature": 0.5}, 16)
+    assert p.n_keep is None and p.temperature == 0.5
+    from jittorinfer_b200.runtime.sampling import SamplingParams
+    assert SamplingParams(**p.__dict__) == p                      # what the data-parallel server sends to the owning rank
