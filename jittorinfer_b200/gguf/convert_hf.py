@@ -49,6 +49,8 @@ def hparams_from_hf_config(cfg: Dict[str, Any]) -> DeepSeek2HParams:
     hp.n_expert_used = int(cfg.get("num_experts_per_tok") or 0)
     hp.n_expert_shared = int(cfg.get("n_shared_experts") or 0)
     hp.n_layer_dense_lead = int(cfg.get("first_k_dense_replace") or 0) if hp.n_expert else hp.n_layer
+    if hp.n_expert and int(cfg.get("moe_layer_freq") or 1) != 1:
+        raise ValueError("moe_layer_freq != 1: the deepseek2 layout has dense blocks only at the front")
     hp.expert_weights_scale = float(cfg.get("routed_scaling_factor") or 1.0)
     hp.expert_weights_norm = bool(cfg.get("norm_topk_prob") or False)
     v3 = mt == "deepseek_v3"                # sigmoid scores, bias-corrected group-limited choice: implied by the model type

@@ -156,6 +156,11 @@ def test_original_config_layout_and_errors(tmp_path):
         hparams_from_hf_config(dict(cfg, rope_scaling={"type": "linear", "factor": 2}))
     with pytest.raises(ValueError):
         hparams_from_hf_config(dict(cfg, num_key_value_heads=8))
+    with pytest.raises(ValueError):
+        hparams_from_hf_config(dict(cfg, moe_layer_freq=2))
+    lite = hparams_from_hf_config(dict(cfg, q_lora_rank=None, topk_method="greedy", n_group=1, topk_group=1, moe_layer_freq=1,
+                                       num_hidden_layers=27, ep_size=1, aux_loss_alpha=0.001, seq_aux=True))
+    assert lite.q_lora_rank == 0 and lite.is_lite and (lite.n_group, lite.topk_group) == (1, 1)
 
 
 def test_missing_and_foreign_tensors_are_reported(tmp_path):
