@@ -297,3 +297,25 @@ def test_v3_structure_matches_the_library_model(tmp_path):
     with torch.no_grad():
         theirs = model.generate(ids[:, :70], max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)[0, 70:].tolist()
     assert mine == theirs
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(os.environ.get("JITTORINFER_TEST_HF_GPU", "") != "1",
+                    reason="the GPU engine against the library model has not yet been run on a GPU; "
+                           "set JITTORINFER_TEST_HF_GPU=1 to try it")
+def test_gpu_engine_on_a_converted_checkpoint_follows_the_library_model(tmp_path):
+    """bf16 kernels against the library's fp32 model: the first tokens of a greedy continuation agree and the logits of the
+    prompt's last position agree to bf16 resolution (read through the engine's top-k log-probabilities)."""
+    model, d = make_hf(tmp_path, LITE, 0)
+    out = str(tmp_path / "m.gguf")
+    convert(d, out, "bf16", toy_vocab=True)
+    from jittorinfer_b200.runtime.factory import build_engine
+    from jittorinfer_b200.runtime.sampling import SamplingParams
+    ids = torch.tensor([[5, 17, 200, 33, 7, 450, 2, 99, 311, 64, 12, 12, 400]])
+    eng = build_engine(None, gguf_path=out, device="cuda", n_parallel=2, n_ctx_slot=64, cuda_graphs=False)
+    mine = eng.generate([ids[0].tolist()], SamplingParams(ignore_eos=True), max_new_tokens=4)[0]
+    with torch.no_grad():
+        theirs = model.generate(ids, max_new_tokens=4, do_sample=False, eos_token_id=None, pad_token_id=0)[0, ids.shape[1]:].tolist()
+        ref = model(ids).logits[0, -1]
+    assert mine[0] == theirs[0] or ref[mine[0]] > ref.max() - 0.05         # bf16 may swap a near tie
+    assert sum(a == b for a, b in zip(mine, theirs)) >= 2
