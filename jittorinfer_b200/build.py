@@ -135,7 +135,8 @@ def build_capi(force: bool = False, verbose: bool = False) -> str:
 
 def _build_kernels_variant(define: str, suffix: str, force: bool, verbose: bool) -> str:
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
-    hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h"))
+    hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h")) + \
+        [os.path.join(CSRC, "include", "jib_quant_layout.h")]
     out = os.path.join(LIBDIR, f"libjib200_kernels_{suffix}.so")
     if force or _newer(srcs + hdrs, out):
         objdir = os.path.join(LIBDIR, "obj_" + suffix)
@@ -146,7 +147,7 @@ def _build_kernels_variant(define: str, suffix: str, force: bool, verbose: bool)
             o = os.path.join(objdir, os.path.basename(s) + ".o")
             objs.append(o)
             cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", *NVCC_ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
-                   "-D" + define, "-I", os.path.join(CSRC, "kernels"), "-c", s, "-o", o]
+                   "-D" + define, "-I", os.path.join(CSRC, "kernels"), "-I", os.path.join(CSRC, "include"), "-c", s, "-o", o]
             procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         for cmd, p in procs:
             o, _ = p.communicate()
@@ -171,7 +172,8 @@ def build_kernels_timeline(force: bool = False, verbose: bool = False) -> str:
 
 def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[str] = ()) -> str:
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
-    hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h"))
+    hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h")) + \
+        [os.path.join(CSRC, "include", "jib_quant_layout.h")]
     os.makedirs(LIBDIR, exist_ok=True)
     if not srcs:
         raise RuntimeError("no CUDA sources found")
@@ -186,7 +188,7 @@ def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[
             if force or _newer([s] + hdrs, o):
                 cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", *NVCC_ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden",
                        "--expt-relaxed-constexpr", "-Xptxas", "-v", *extra_flags,
-                       "-I", os.path.join(CSRC, "kernels"), "-c", s, "-o", o]
+                       "-I", os.path.join(CSRC, "kernels"), "-I", os.path.join(CSRC, "include"), "-c", s, "-o", o]
                 if verbose:
                     print(" ".join(cmd), flush=True)
                 procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -61,6 +61,9 @@ JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);
 // params [n][5] fp32: temperature (<= 0: best candidate), top_k (<= 0: all), top_p (>= 1: off), min_p (<= 0: off), u in [0, 1).
 JIB_EXPORT int jib_sample_topk(const float * vals, const int * ids, const float * params, int * out, int n, int k, void * stream);
 
+// Block-quantised checkpoint data (ggml types Q4_0 .. Q8_K) -> bf16, at load time (dequant.cu).
+JIB_EXPORT int jib_dequantize_bf16(unsigned ggml_type, const void * src, unsigned long long n_elements, void * dst, void * stream);
+
 // ---- memory-bound kernels (elementwise.cu) ----------------------------------------------------
 JIB_EXPORT int jib_embed_gather(const void * table, const int * ids, void * out, int T, int d, int n_vocab, void * stream);
 JIB_EXPORT int jib_rmsnorm(const void * x, const void * residual, const float * w, void * out_norm, void * out_sum, int T, int d,

@@ -11,6 +11,8 @@
 //                      its top two bits at 2g of byte 32 h + l of the second array, scale 8 h + 2 g + l/16.
 #include "dequant.h"
 
+#include "jib_quant_layout.h"
+
 #include <algorithm>
 #include <cstring>
 #include <thread>
@@ -202,6 +204,17 @@ void run_range(const Traits * tr, const uint8_t * src, uint64_t b0, uint64_t b1,
 
 uint64_t quant_block_elems(uint32_t t) { const Traits * x = find(t); return x ? x->elems : 0; }
 uint64_t quant_block_bytes(uint32_t t) { const Traits * x = find(t); return x ? x->bytes : 0; }
+
+// One element at a time through the layout function that device code shares (include/jib_quant_layout.h): slow, exists so
+// that the function can be checked against the block expanders above.
+int dequantize_elementwise(uint32_t ggml_type, const void * src, uint64_t n_elements, float * dst) {
+    uint32_t elems = 0, bytes = 0;
+    if (!jib_quant_traits(ggml_type, &elems, &bytes)) return -1;
+    if (n_elements % elems) return -2;
+    const uint8_t * p = (const uint8_t *) src;
+    for (uint64_t i = 0; i < n_elements; ++i) dst[i] = jib_quant_elem(ggml_type, p + (i / elems) * bytes, (int) (i % elems));
+    return 0;
+}
 
 int dequantize(uint32_t ggml_type, const void * src, uint64_t n_elements, void * dst, bool dst_bf16, int n_threads) {
     const Traits * tr = find(ggml_type);

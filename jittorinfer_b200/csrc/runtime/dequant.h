@@ -16,4 +16,7 @@ uint64_t quant_block_bytes(uint32_t ggml_type);
 // Returns 0, -1 (type not handled) or -2 (n_elements is not a whole number of blocks).
 int dequantize(uint32_t ggml_type, const void * src, uint64_t n_elements, void * dst, bool dst_bf16, int n_threads);
 
+// The same expansion through the per-element layout function shared with device code; for cross-checking only.
+int dequantize_elementwise(uint32_t ggml_type, const void * src, uint64_t n_elements, float * dst);
+
 }  // namespace jib

@@ -304,6 +304,10 @@ JIB_API int jib_dequantize(uint32_t ggml_type, const void * src, uint64_t n_elem
     if ((src == nullptr || dst == nullptr) && n_elements != 0) return -3;
     return jib::dequantize(ggml_type, src, n_elements, dst, dst_bf16 != 0, n_threads);
 }
+JIB_API int jib_dequantize_elementwise(uint32_t ggml_type, const void * src, uint64_t n_elements, float * dst) {
+    if ((src == nullptr || dst == nullptr) && n_elements != 0) return -3;
+    return jib::dequantize_elementwise(ggml_type, src, n_elements, dst);
+}
 JIB_API uint64_t jib_quant_block_elems(uint32_t ggml_type) { return jib::quant_block_elems(ggml_type); }
 JIB_API uint64_t jib_quant_block_bytes(uint32_t ggml_type) { return jib::quant_block_bytes(ggml_type); }
 JIB_API int jib_gguf_version(jib_gguf * g) { return (int) g->file.version(); }

@@ -367,6 +367,9 @@ class GGUFReader:
     # dtype of tensors expanded from a block-quantised type: float32, or bfloat16 when the loader stores bf16 on the device
     # anyway (halves the host memory and the bytes sent to the device)
     quant_out_dtype = None
+    # a CUDA device: the quantised bytes of a shard are sent there and expanded to bf16 by a kernel (ops/native.py:
+    # dequantize_bf16); tensors of quantised types then come back as device tensors
+    quant_device = None
 
     def _dequant_shard(self, ti: TensorInfo, raw: np.ndarray, dim: int, index: int, count: int):
         """Expands shard ``index`` of ``count`` along ``dim`` of a block-quantised tensor, touching only that shard's blocks
@@ -391,7 +394,10 @@ class GGUFReader:
             elif step % blk == 0:
                 blocks = blocks[..., index * step // blk:(index + 1) * step // blk, :]
                 out_shape[d], count = step, 1
-        t = quants.dequantize_torch(ti.ggml_type, blocks, self.quant_out_dtype)
+        if self.quant_device is not None:
+            t = quants.dequantize_on_device(ti.ggml_type, blocks, self.quant_device)
+        else:
+            t = quants.dequantize_torch(ti.ggml_type, blocks, self.quant_out_dtype)
         return t.view(out_shape), count
 
     def describe(self) -> str:

@@ -387,3 +387,20 @@ def dequantize_torch(ggml_type: int, blocks: np.ndarray, dtype=None, native: boo
             raise ValueError(f"jib_dequantize({NAMES[ggml_type]}) failed with {rc}")
         return out
     return torch.from_numpy(dequantize(ggml_type, flat, n)).to(dtype)
+
+
+def dequantize_on_device(ggml_type: int, blocks: np.ndarray, device):
+    """As ``dequantize_torch`` with the expansion on ``device``: the quantised bytes cross PCIe (a quarter to a half of the
+    bf16 size), a kernel writes bf16 there.  Returns a 1-D bf16 tensor on ``device``."""
+    import warnings
+
+    import torch
+
+    from ..ops import native
+    blk, bsz = TRAITS[ggml_type]
+    assert blocks.dtype == np.uint8 and blocks.shape[-1] == bsz
+    flat = np.ascontiguousarray(blocks).reshape(-1)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")                            # read-only mapping
+        raw = torch.from_numpy(flat).to(device, non_blocking=False)
+    return native.dequantize_bf16(raw, ggml_type, flat.size // bsz * blk)

@@ -465,6 +465,18 @@ def sample_topk(vals, ids, params):
     return out
 
 
+def dequantize_bf16(raw, ggml_type: int, n_elements: int):
+    """``raw``: uint8 CUDA tensor holding ``n_elements`` elements of a block-quantised ggml type -> bf16 [n_elements]."""
+    L = load()
+    fn = L.jib_dequantize_bf16                   # bound on first use: libraries built before this entry point still load
+    fn.restype, fn.argtypes = C.c_int, [C.c_uint, C.c_void_p, C.c_ulonglong, C.c_void_p, C.c_void_p]
+    assert raw.dtype == torch.uint8 and raw.is_cuda and raw.is_contiguous()
+    out = torch.empty(n_elements, dtype=torch.bfloat16, device=raw.device)
+    with torch.cuda.device(raw.device):
+        _ck(fn(int(ggml_type), raw.data_ptr(), int(n_elements), out.data_ptr(), _stream()), "dequantize_bf16")
+    return out
+
+
 def kv_block_copy(cache, src_blocks, dst_blocks, block_size):
     L, n_slots, row = cache.shape
     _ck(load().jib_kv_block_copy(cache.data_ptr(), n_slots * row, L, src_blocks.data_ptr(), dst_blocks.data_ptr(),

@@ -1,4 +1,6 @@
 """sm_100a kernels vs the plain-PyTorch fp32 reference of the same op (tile-edge shapes included)."""
+import os
+
 import pytest
 import torch
 
@@ -309,3 +311,22 @@ def test_device_sampler_matches_the_reference(nat, k):
     assert agree > 0.995, agree
     greedy = params[:, 0] <= 0
     assert torch.equal(got[greedy], ids[greedy, 0])
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(os.environ.get("JITTORINFER_DEVICE_DEQUANT", "") != "1",
+                    reason="the device expander of block-quantised checkpoints has been cross-compiled but not yet run on a GPU; "
+                           "set JITTORINFER_DEVICE_DEQUANT=1 to try it")
+def test_device_dequantize_matches_the_host_expander():
+    import numpy as np
+    from jittorinfer_b200.gguf import quants as Q
+    from jittorinfer_b200.ops import native
+    rng = np.random.default_rng(0)
+    for t, (blk, bsz) in Q.TRAITS.items():
+        x = rng.standard_normal(blk * 4099).astype(np.float32)          # an odd number of blocks: the last thread block is partial
+        raw = Q.quantize(t, x)
+        want = Q.dequantize_torch(t, raw.reshape(-1, bsz), torch.bfloat16)
+        got = native.dequantize_bf16(torch.from_numpy(raw).cuda(), t, x.size).cpu()
+        diff = (got.float() - want.float()).abs()
+        assert float((diff / want.float().abs().clamp_min(1e-3)).max()) < 1e-2, Q.NAMES[t]      # fused multiply-add may move one bf16 ulp
+        assert float((got != want).float().mean()) < 1e-3, Q.NAMES[t]

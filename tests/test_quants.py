@@ -225,3 +225,19 @@ def test_requantise_keeps_keys_and_re_encodes_tensors(tmp_path):
                 assert torch.equal(c.tensor(name), b.tensor(name).to(torch.bfloat16)), name
     with pytest.raises(ValueError):
         requantize(src, q + "x", "q8_k")
+
+
+@pytest.mark.parametrize("t", TYPES, ids=[Q.NAMES[t] for t in TYPES])
+def test_layout_function_shared_with_device_code_equals_the_block_expanders(t):
+    """``jib_quant_elem`` (csrc/include/jib_quant_layout.h) is what the device kernel evaluates per element; on the host it
+    gives exactly what the per-block expanders give, for every element of random blocks."""
+    from jittorinfer_b200.runtime.native_rt import lib
+    L = lib()
+    L.jib_dequantize_elementwise.restype = C.c_int
+    L.jib_dequantize_elementwise.argtypes = [C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p]
+    blocks = random_blocks(t, 97, seed=50 + t)
+    n = blocks.shape[0] * Q.TRAITS[t][0]
+    out = np.empty(n, dtype=np.float32)
+    assert L.jib_dequantize_elementwise(t, blocks.ctypes.data, n, out.ctypes.data) == 0
+    np.testing.assert_array_equal(out, native(t, blocks).numpy())
+    assert L.jib_dequantize_elementwise(16, blocks.ctypes.data, n, out.ctypes.data) == -1
