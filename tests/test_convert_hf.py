@@ -7,12 +7,17 @@ import os
 import pytest
 import torch
 
-transformers = pytest.importorskip("transformers")
-pytest.importorskip("safetensors")
-try:
-    from transformers import DeepseekV2Config, DeepseekV2ForCausalLM
-except Exception:                                               # pragma: no cover
-    pytest.skip("this transformers release has no DeepseekV2 model", allow_module_level=True)
+
+def _library():
+    """The third-party model classes, imported on first use (collection stays cheap and free of side effects)."""
+    pytest.importorskip("transformers")
+    pytest.importorskip("safetensors")
+    try:
+        from transformers import DeepseekV2Config, DeepseekV2ForCausalLM
+    except Exception:                                           # pragma: no cover
+        pytest.skip("this transformers release has no DeepseekV2 model")
+    return DeepseekV2Config, DeepseekV2ForCausalLM
+
 
 from jittorinfer_b200.gguf import format as F
 from jittorinfer_b200.gguf.convert_hf import convert, hparams_from_hf_config, vocab_kv_from_hf
@@ -38,6 +43,7 @@ V2 = dict(vocab_size=512, hidden_size=256, intermediate_size=384, num_hidden_lay
 
 
 def make_hf(tmp_path, kw, seed):
+    DeepseekV2Config, DeepseekV2ForCausalLM = _library()
     torch.manual_seed(seed)
     model = DeepseekV2ForCausalLM(DeepseekV2Config(**kw)).eval()
     d = str(tmp_path / "hf")
@@ -164,8 +170,8 @@ def test_original_config_layout_and_errors(tmp_path):
 
 
 def test_missing_and_foreign_tensors_are_reported(tmp_path):
-    from safetensors.torch import load_file, save_file
     _, d = make_hf(tmp_path, LITE, 4)
+    from safetensors.torch import load_file, save_file
     p = os.path.join(d, "model.safetensors")
     sd = {k: v.clone() for k, v in load_file(p).items()}           # own memory: the file is rewritten below
     extra = dict(sd)
