@@ -1,5 +1,6 @@
 """OpenAI-compatible server end to end on CPU: tiny random model, toy byte-level vocabulary."""
 import json
+import os
 import threading
 import urllib.error
 import urllib.request
@@ -243,3 +244,16 @@ def test_request_fields_of_the_reference_server_are_parsed():
     assert p.n_keep is None and p.temperature == 0.5
     from jittorinfer_b200.runtime.sampling import SamplingParams
     assert SamplingParams(**p.__dict__) == p                      # what the data-parallel server sends to the owning rank
+
+
+def test_example_client_streams_both_routes(server, capsys):
+    import importlib.util
+    url, _ = server
+    spec = importlib.util.spec_from_file_location("example_client", os.path.join(os.path.dirname(__file__), "..", "examples", "client.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    pieces = list(mod.stream(url + "/v1/completions", {"prompt": "the", "max_tokens": 6, "temperature": 0, "ignore_eos": True}))
+    whole = _post(url + "/v1/completions", {"prompt": "the", "max_tokens": 6, "temperature": 0, "ignore_eos": True})
+    assert "".join(pieces) == whole["choices"][0]["text"]
+    assert mod.main(["--url", url, "--max-tokens", "5", "--temperature", "0", "hello"]) == 0
+    assert capsys.readouterr().out.endswith("\n")
