@@ -1,19 +1,23 @@
 #!/usr/bin/env python
-"""Headline benchmark: decode output tokens/s at concurrency C (default 8).
+"""Headline benchmark: decode output tokens/s at concurrency 1/2/4/8 (the headline value is the one at 8).
 
 * N = 1: DeepSeek-V2-Lite (27 layers, 64 experts top-6 + 2 shared, MLA) on one B200.
 * N > 1: DeepSeek-V2 (236B architecture) tensor/expert-parallel over N GPUs, layer count scaled
-  as 60 * N / 8 so that per-GPU work is fixed ("weak").
+  as 60 * N / 8 (the full 60 layers on 8 GPUs), global batch fixed.
+* every N: a `same_model` sub-record -- DeepSeek-V2 architecture with a fixed 12 layers (fits one GPU) run at TP=N
+  with the same global batch: the strong-scaling curve of one model, which the headline (a different model per N,
+  as the published baseline is) cannot give.
 
 Workload (random-init bf16 weights, synthetic uniform-random token ids): C concurrent requests,
 each a 1024-token prompt followed by greedy decoding with EOS ignored.  After the prompts have been
-prefilled, W warm-up decode steps run untimed and then EXACTLY K engine decode steps are timed with
-CUDA events on the launching stream (barrier + synchronize on both sides, max over ranks).  Every
-timed step is a full engine step through the public API (`LLMEngine.step()`): the scheduler writes
-the step inputs into pinned host memory, one H2D copy, one CUDA-graph replay of the whole model
-with on-device greedy sampling, one D2H copy of the sampled ids, scheduler commit.  `value` is
-C * K / time.  `e2e` repeats the measurement over whole requests (`LLMEngine.generate()`:
-prefill + all decode steps, wall clock) and `graph_only_ms` is the bare graph replay time.
+prefilled, W warm-up decode steps run untimed and then R regions of EXACTLY K engine decode steps each are timed with
+CUDA events on the launching stream (barrier + synchronize on both sides, max over ranks); `ms_per_step` / `value` come
+from the median region and min / max are reported beside them.  Every timed step is a full engine step through the
+public API (`LLMEngine.step()`): the scheduler writes the step inputs into pinned host memory, one H2D copy, one
+CUDA-graph replay of the whole model with on-device greedy sampling, one D2H copy of the sampled ids, scheduler commit.
+`e2e` repeats the measurement over whole requests (`LLMEngine.generate()`: prefill + all decode steps, wall clock),
+`http` drives the OpenAI-compatible server over a socket with the reference harness' workload (1 GPU), and
+`graph_only_ms` is the bare graph replay time.
 
 Weights (tens of GB) exceed the 126 MB L2, so every step streams them from HBM: no L2 flush needed.
 """
@@ -33,7 +37,7 @@ BASELINE = {("lite", 1): 73.3, ("lite", 2): 114.43, ("lite", 4): 166.82, ("lite"
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed regions run (read-only queries)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -44,12 +48,13 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -58,7 +63,7 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        time.sleep(0.15)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -90,8 +95,9 @@ def reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each (fewer if the generation budget is short)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--concurrency", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -99,8 +105,12 @@ def main():
     ap.add_argument("--model", default=None, help="lite | v2 | tiny (default: lite for 1 GPU, v2 otherwise)")
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--ops", default="native", choices=["native", "torch"], help="torch = PyTorch/cuBLAS baseline ops")
-    ap.add_argument("--sweep", action="store_true", help="also report concurrency 1/2/4")
+    ap.add_argument("--sweep", action="store_true", help="kept for compatibility: the concurrency sweep is always reported")
+    ap.add_argument("--no-sweep", action="store_true", help="headline concurrency only")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-same-model", action="store_true", help="skip the fixed-model strong-scaling sub-record")
+    ap.add_argument("--no-http", action="store_true", help="skip the through-the-server sub-record (1 GPU only)")
+    ap.add_argument("--same-model-layers", type=int, default=12)
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: dry run of this script's whole flow on the reference ops with --model tiny (a check of the "
                          "script, not a measurement)")
@@ -119,6 +129,7 @@ def main():
     import torch.distributed as dist
     from jittorinfer_b200 import ops
     from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.ops.expected import default_bandwidth, step_memory_bytes
     from jittorinfer_b200.runtime.factory import build_engine
     from jittorinfer_b200.runtime.sampling import SamplingParams
 
@@ -162,20 +173,14 @@ def main():
     K, W = args.steps, args.warmup
     if W + K >= args.gen_len:
         raise SystemExit("steps + warmup must be smaller than --gen-len")
+    R = max(1, min(args.regions, (args.gen_len - W - 4) // K))
+    bandwidth = default_bandwidth()
 
     t_start = time.time()
 
     def note(msg):
         if rank == 0:
             print(f"[bench +{time.time() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
-
-    eng = build_engine(hp, device=dev, world=world, rank=rank, n_parallel=C, n_ctx_slot=total_len + 64,
-                       n_batch=2048, seed=0, graph_buckets=tuple(b for b in (1, 2, 4, 8, 16, 32, 64) if b <= max(C, 1)) or (1,),
-                       run_ahead=args.run_ahead)
-    g = torch.Generator().manual_seed(1234)
-
-    def prompts(n):
-        return [torch.randint(0, hp.n_vocab, (args.prompt_len,), generator=g).tolist() for _ in range(n)]
 
     def barrier():
         if world > 1:
@@ -189,42 +194,87 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed_decode(conc: int, k_steps: int, w_steps: int, sample_clocks: bool):
-        """Prefill `conc` prompts, then time k_steps decode steps. Returns (ms_per_step, clocks, launches)."""
+    gen = torch.Generator().manual_seed(1234)
+
+    def prompts(hp_, n, length=None):
+        return [torch.randint(0, hp_.n_vocab, (length or args.prompt_len,), generator=gen).tolist() for _ in range(n)]
+
+    def buckets(c):
+        return tuple(b for b in (1, 2, 4, 8, 16, 32, 64) if b <= max(c, 1)) or (1,)
+
+    def timed_decode(eng, hp_, conc: int):
+        """Prefill `conc` prompts, W warm-up steps, then R regions of K timed decode steps.
+        Returns (list of ms per step, one per region; kernels launched inside the regions)."""
         sp = SamplingParams(max_tokens=args.gen_len, ignore_eos=True)
-        ids = [eng.add_request(p, sp) for p in prompts(conc)]
+        ids = [eng.add_request(p, sp) for p in prompts(hp_, conc)]
         while any(len(eng.requests[i].output) == 0 for i in ids):     # chunked prefill until every request decodes
             eng.step()
-        for _ in range(w_steps):
+        for _ in range(W):
             eng.step()
-        sampler = ClockSampler(local) if sample_clocks and rank == 0 else None
-        barrier()
-        if sampler:
-            sampler.start()
-        l0 = eng.launches
-        e0, e1 = new_event(), new_event()
-        e0.record()
-        for _ in range(k_steps):
-            eng.step()
-        e1.record()
-        barrier()
-        ms = max_over_ranks(e0.elapsed_time(e1))
-        clocks = sampler.stop() if sampler else None
-        launches = eng.launches - l0
+        regions, launches = [], 0
+        for _ in range(R):
+            barrier()
+            l0 = eng.launches
+            e0, e1 = new_event(), new_event()
+            e0.record()
+            for _ in range(K):
+                eng.step()
+            e1.record()
+            barrier()
+            regions.append(max_over_ranks(e0.elapsed_time(e1)) / K)
+            launches += eng.launches - l0
         for i in ids:
             eng.cancel(i)
             eng.requests.pop(i, None)
-        return ms / k_steps, clocks, launches
+        return regions, launches
 
-    note(f"model built: {eng.model.weight_bytes() / 2**30:.1f} GiB of weights on this rank")
+    def record(eng, hp_, conc: int, with_e2e: bool):
+        """One concurrency: decode regions (+ whole requests through generate())."""
+        regions, launches = timed_decode(eng, hp_, conc)
+        med = statistics.median(regions)
+        bound_ms = step_memory_bytes(hp_, conc, args.prompt_len + args.gen_len // 2, world) / bandwidth * 1e3
+        out = {"value": round(conc * 1000.0 / med, 2), "ms_per_step": round(med, 4),
+               "ms_per_step_min": round(min(regions), 4), "ms_per_step_max": round(max(regions), 4), "regions": len(regions),
+               "us_per_layer": round(med * 1e3 / hp_.n_layer, 2), "membound_ms": round(bound_ms, 4),
+               "fraction_of_membound": round(bound_ms / med, 3), "launches_per_step": launches // max(1, K * len(regions)),
+               "gpu_launches": launches}
+        if with_e2e:
+            ps = prompts(hp_, conc)
+            h0, d0, s0 = eng.stats["h2d_bytes"], eng.stats["d2h_bytes"], eng.stats["steps"]
+            barrier()
+            t0 = time.perf_counter()
+            outs = eng.generate(ps, SamplingParams(ignore_eos=True), max_new_tokens=args.gen_len)
+            barrier()
+            dt = max_over_ranks(time.perf_counter() - t0)
+            n_steps = eng.stats["steps"] - s0
+            out["e2e"] = {"value": round(sum(len(o) for o in outs) / dt, 2), "unit": "tokens/s",
+                          "h2d_bytes_per_step": (eng.stats["h2d_bytes"] - h0) // max(1, n_steps),
+                          "d2h_bytes_per_step": (eng.stats["d2h_bytes"] - d0) // max(1, n_steps),
+                          "what": f"LLMEngine.generate(): {conc} requests x ({args.prompt_len} prompt + {args.gen_len} generated), "
+                                  f"prefill included, {n_steps} engine steps, wall clock"}
+        return out
+
+    eng = build_engine(hp, device=dev, world=world, rank=rank, n_parallel=C, n_ctx_slot=total_len + 64,
+                       n_batch=2048, seed=0, graph_buckets=buckets(C), run_ahead=args.run_ahead)
+    weight_gib = eng.model.weight_bytes() / 2**30
+    note(f"model built: {weight_gib:.1f} GiB of weights on this rank")
     eng.warmup()
     note("decode graphs captured")
     tl = None
     if args.timeline:
         from jittorinfer_b200.parallel.timeline import Timeline, format_summary, summarize
         tl = Timeline(dev, capacity=1 << 22)
-    ms_step, clocks, launches = timed_decode(C, K, W, True)
-    note(f"timed region done: {ms_step:.3f} ms/step")
+
+    sampler = ClockSampler(local).start() if rank == 0 and cuda else None
+    concs = [C] if args.no_sweep else sorted({c for c in (1, 2, 4, 8) if c < C} | {C})
+    by_conc = {}
+    for c in concs:
+        by_conc[str(c)] = record(eng, hp, c, not args.no_e2e)
+        note(f"concurrency {c}: {by_conc[str(c)]['ms_per_step']:.3f} ms/step "
+             f"({by_conc[str(c)]['fraction_of_membound']:.2f} of the memory bound)")
+    clocks = sampler.stop() if sampler else {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["not sampled"]}
+    head = by_conc[str(C)]
+
     timeline_summary = None
     if tl is not None:
         sm = summarize(tl.read())                  # includes prefill and warm-up steps of this measurement
@@ -233,7 +283,6 @@ def main():
         if rank == 0:
             print(format_summary(sm), file=sys.stderr, flush=True)
         tl.close()
-    value = C * 1000.0 / ms_step
 
     # bare graph replay (no host work between steps): explains how much of a step is device time
     graph_only_ms = None
@@ -249,54 +298,77 @@ def main():
             gr.replay()
         e1.record()
         barrier()
-        graph_only_ms = max_over_ranks(e0.elapsed_time(e1)) / 32
+        graph_only_ms = round(max_over_ranks(e0.elapsed_time(e1)) / 32, 4)
 
-    by_conc = {}
-    if args.sweep:
-        for c in (1, 2, 4):
-            if c < C:
-                ms_c, _, _ = timed_decode(c, min(K, 64), W, False)
-                by_conc[str(c)] = round(c * 1000.0 / ms_c, 2)
-        by_conc[str(C)] = round(value, 2)
+    # ---- through the server (1 GPU): the reference harness' workload over HTTP ---------------------------------
+    http = None
+    if world == 1 and not args.no_http and not args.timeline:
+        try:
+            http = http_record(eng, hp, C, cuda, duration_s=6.0 if cuda else 0.5)
+            note(f"http: {http['output_tokens_per_s']} tok/s through the server at {C} users")
+        except Exception as e:        # the headline must not depend on a free port
+            http = {"error": f"{type(e).__name__}: {e}"}
 
-    e2e = None
-    if not args.no_e2e:
-        # whole requests through the public API: prefill + gen_len decode steps, wall clock
-        ps = prompts(C)
-        io_h2d0, io_d2h0, steps0 = eng.stats["h2d_bytes"], eng.stats["d2h_bytes"], eng.stats["steps"]
-        barrier()
-        t0 = time.perf_counter()
-        outs = eng.generate(ps, SamplingParams(ignore_eos=True), max_new_tokens=args.gen_len)
-        barrier()
-        dt = max_over_ranks(time.perf_counter() - t0)
-        n_steps = eng.stats["steps"] - steps0
-        e2e = {"value": round(sum(len(o) for o in outs) / dt, 2), "unit": "tokens/s",
-               "h2d_bytes_per_step": (eng.stats["h2d_bytes"] - io_h2d0) // max(1, n_steps),
-               "d2h_bytes_per_step": (eng.stats["d2h_bytes"] - io_d2h0) // max(1, n_steps),
-               "what": f"LLMEngine.generate(): {C} requests x ({args.prompt_len} prompt + {args.gen_len} generated), "
-                       f"prefill included, {n_steps} engine steps, wall clock"}
     synchronize()
     if args.ops == "native" and cuda:
         ops.nat().check_status()
 
+    # ---- the same model at every N: DeepSeek-V2 architecture, fixed layer count, TP = N (strong scaling) ----------
+    same_model = None
+    if not args.no_same_model and model_name in ("lite", "v2") and not args.timeline and not args.layers:
+        comm = getattr(eng.model, "comm", None)
+        del eng
+        if cuda:
+            torch.cuda.empty_cache()
+        hp2 = preset("v2").replace(n_layer=args.same_model_layers)
+        eng2 = build_engine(hp2, device=dev, world=world, rank=rank, n_parallel=C, n_ctx_slot=total_len + 64, n_batch=2048,
+                            seed=0, graph_buckets=buckets(C), comm=comm)
+        note(f"same_model built: {eng2.model.weight_bytes() / 2**30:.1f} GiB on this rank")
+        eng2.warmup()
+        rec = {}
+        for c in ([C] if args.no_sweep else sorted({1, C})):
+            rec[str(c)] = record(eng2, hp2, c, False)
+        same_model = {"model": f"DeepSeek-V2 architecture, {hp2.n_layer} layers, random init", "parallelism": f"tp{world}+ep{world}" if world > 1 else "single GPU",
+                      "scaling": "strong", "global_batch": C, "value": rec[str(C)]["value"], "unit": "tokens/s", "by_concurrency": rec}
+        synchronize()
+        if args.ops == "native" and cuda:
+            ops.nat().check_status()
+        note(f"same_model: {same_model['value']} tok/s at concurrency {C}")
+
     if rank == 0:
-        base = BASELINE.get((model_name, C)) if (model_name == "lite" and world == 1) or (model_name == "v2" and world == 8 and hp.n_layer == 60) else None
+        full = (model_name == "lite" and world == 1 and hp.n_layer == 27) or (model_name == "v2" and world == 8 and hp.n_layer == 60)
+        base = BASELINE.get((model_name, C)) if full else None
         par = "single GPU" if world == 1 else f"tp{world}+ep{world} (attention heads and routed experts sharded, fused GEMM+all-reduce)"
+        for c, r in by_conc.items():
+            b = BASELINE.get((model_name, int(c))) if full else None
+            r["vs_baseline"] = round(r["value"] / b, 3) if b else None
         out = {
-            "metric": f"decode output tokens/s at concurrency {C}", "value": round(value, 2), "unit": "tokens/s",
-            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": round(value / base, 3) if base else None, "dtype": "bf16",
+            "metric": f"decode output tokens/s at concurrency {C}", "value": head["value"], "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "regions": head["regions"], "ms_per_step": head["ms_per_step"],
+            "ms_per_step_min": head["ms_per_step_min"], "ms_per_step_max": head["ms_per_step_max"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": round(head["value"] / base, 3) if base else None, "dtype": "bf16",
             "data": "synthetic (uniform-random token ids, random-init weights)", "impl": "ours", "ops": args.ops,
             "config": {"model": f"DeepSeek-V2{'-Lite' if model_name == 'lite' else ''} ({hp.n_layer} layers)" if model_name != "tiny" else "tiny",
                        "global_batch": C, "seq_len": total_len, "prompt_len": args.prompt_len, "gen_len": args.gen_len,
-                       "parallelism": par, "l2": "weights (>= 30 GB per GPU) exceed L2; no flush needed",
-                       "timed": "K LLMEngine.step() decode steps: H2D step inputs + CUDA-graph replay + D2H sampled ids"
+                       "parallelism": par, "layers": hp.n_layer, "weight_gib_per_rank": round(weight_gib, 1),
+                       "scaling_note": "N = 1 runs DeepSeek-V2-Lite, N > 1 runs DeepSeek-V2 with 60 * N / 8 layers at a fixed global batch "
+                                       "(per-GPU weight bytes roughly constant); tokens/s across N therefore compares different models: "
+                                       "the same_model record is the strong-scaling curve of one model",
+                       "l2": "weights (>= 30 GB per GPU) exceed L2; no flush needed",
+                       "timed": f"{head['regions']} regions of K LLMEngine.step() decode steps (median reported): H2D step inputs + "
+                                "CUDA-graph replay + D2H sampled ids"
                                 + (" (one step in flight: ids are read one step late)" if args.run_ahead else "")},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "graph_only_ms": graph_only_ms,
-            "launches_per_step": launches // max(1, K),
+            "layers": hp.n_layer, "us_per_layer": head["us_per_layer"],
+            "weight_bytes_per_step": int(step_memory_bytes(hp, C, args.prompt_len + args.gen_len // 2, world)),
+            "membound_ms": head["membound_ms"], "fraction_of_membound": head["fraction_of_membound"],
+            "membound_bandwidth_gbs": round(bandwidth / 1e9, 1),
+            "clocks": clocks, "e2e": head.get("e2e"), "gpu_launches": head["gpu_launches"], "graph_only_ms": graph_only_ms,
+            "launches_per_step": head["launches_per_step"], "by_concurrency": by_conc,
         }
-        if by_conc:
-            out["by_concurrency"] = by_conc
+        if http is not None:
+            out["http"] = http
+        if same_model is not None:
+            out["same_model"] = same_model
         if timeline_summary is not None:
             out["timeline"] = timeline_summary
             out["invalid_as_result"] = "run with device time stamps enabled (diagnostic)"
@@ -310,6 +382,47 @@ def main():
         # process group is gone can block at exit
         os._exit(0)
     return 0
+
+
+def http_record(eng, hp, users: int, cuda: bool, duration_s: float = 6.0):
+    """Serve `eng` through the OpenAI-compatible HTTP server on a loopback port and drive it with the closed-loop load
+    generator: `users` virtual users, ~5-token prompts, 110 generated tokens each (the reference harness' workload,
+    script/test_benchmark.sh:8-13,72-82, shortened to a few seconds).  Tokenisation, HTTP, SSE streaming and the
+    scheduler's admission are inside the measurement."""
+    import socket
+
+    from jittorinfer_b200.config import ServerConfig
+    from jittorinfer_b200.server.app import ServerContext, serve
+    from jittorinfer_b200.server.bench_serving import run as run_load
+    from jittorinfer_b200.server.chat import ChatTemplate
+    from jittorinfer_b200.tokenizer import Tokenizer
+    from jittorinfer_b200.utils.toy_vocab import toy_vocab_kv
+    kv = {k: (v[1] if isinstance(v, tuple) else v) for k, v in toy_vocab_kv(hp.n_vocab, hp.bos_id, hp.eos_id).items()}
+    kv["tokenizer.ggml.bos_token_id"], kv["tokenizer.ggml.eos_token_id"] = hp.bos_id, hp.eos_id
+    tok = Tokenizer.from_gguf_kv(kv)
+    cfg = ServerConfig()
+    cfg.n_parallel = eng.cfg.n_parallel
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = ServerContext(eng, tok, cfg, ChatTemplate(""))
+    httpd = serve(ctx, "127.0.0.1", port, 16)             # also starts the engine thread
+    th = threading.Thread(target=httpd.serve_forever, daemon=True)
+    th.start()
+    try:
+        url = f"http://127.0.0.1:{port}"
+        run_load(url, 0.0, users, 4, 6, 16, users, hp.n_vocab, seed=1)                    # warm-up round
+        n_req = max(users, int(users * duration_s * 1.2))                                   # ~duration at >= 100 tok/s/user
+        res = run_load(url, 0.0, n_req, 4, 6, 110, users, hp.n_vocab, seed=2)
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
+        ctx.shutdown()
+    return {"what": f"closed loop, {users} users, 4-6 token prompts, 110 generated tokens, SSE streaming over loopback HTTP "
+                    "(server/app.py driven by server/bench_serving.py)", "requests": res["completed"], "failed": res["failed"],
+            "duration_s": res["duration_s"], "output_tokens_per_s": res["output_tokens_per_s"], "ttft_ms": res["ttft_ms"],
+            "inter_token_ms": res["inter_token_ms"], "errors": res["errors"]}
 
 
 if __name__ == "__main__":

@@ -13,6 +13,7 @@
 #include "bounds_check.cuh"
 #include "jib_kernels.h"
 #include "pdl.cuh"
+#include "timeline.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -44,8 +45,10 @@ __device__ __forceinline__ float block_sum(float v, float * red) {
 // ---------------------------------------------------------------------------------------------
 __global__ void embed_gather_kernel(const bf16 * __restrict__ table, const int * __restrict__ ids, bf16 * __restrict__ out, int d,
                                     int n_vocab) {
+    JIB_KS(6, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(6, 1);
     const int t = blockIdx.x;
     int id = ids[t];
     JIB_BC(id >= 0 && id < n_vocab, 12, id);
@@ -53,6 +56,7 @@ __global__ void embed_gather_kernel(const bf16 * __restrict__ table, const int *
     const uint4 * src = (const uint4 *) (table + (size_t) id * d);
     uint4 * dst = (uint4 *) (out + (size_t) t * d);
     for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
+    JIB_KS(6, 9);
 }
 
 // out_sum = x + residual (bf16-rounded), out_norm = rmsnorm(out_sum) * w.  One block per row.
@@ -60,8 +64,10 @@ template <int NT, int MAXV>
 __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x, const bf16 * __restrict__ residual,
                                                      const float * __restrict__ w, bf16 * __restrict__ out_norm,
                                                      bf16 * __restrict__ out_sum, int d, long long x_stride, float eps) {
+    JIB_KS(4, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(4, 1);
     __shared__ float red[32];
     const int t = blockIdx.x;
     const bf16x8 * xr = (const bf16x8 *) (x + (size_t) t * x_stride);
@@ -107,6 +113,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x
             ((bf16x8 *) (out_norm + (size_t) t * d))[i] = o;
         }
     }
+    JIB_KS(4, 9);
 }
 
 // One block per token: c = rmsnorm(ckv[:r]) * w -> cache[slot][:r]; k_pe = rope(ckv[r:]) -> cache[slot][r:];
@@ -118,8 +125,10 @@ __global__ void __launch_bounds__(NT) mla_qkv_post_kernel(const bf16 * __restric
                                                           const int * __restrict__ slot_mapping, bf16 * __restrict__ cache,
                                                           bf16 * __restrict__ q_out, int H, int dn, int dr, int r, int max_pos,
                                                           long long n_slots, int * status) {
+    JIB_KS(5, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(5, 1);
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int slot = slot_mapping[t];
@@ -160,6 +169,7 @@ __global__ void __launch_bounds__(NT) mla_qkv_post_kernel(const bf16 * __restric
         const float c = cs[2 * p], s = cs[2 * p + 1];
         *(__nv_bfloat162 *) (qo + (size_t) h * (r + dr) + r + 2 * p) = __floats2bfloat162_rn(f.x * c - f.y * s, f.x * s + f.y * c);
     }
+    JIB_KS(5, 9);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -170,8 +180,10 @@ __device__ __forceinline__ uint32_t f2key(float f) {   // order-preserving float
 
 template <int NT>
 __global__ void __launch_bounds__(NT) argmax_kernel(const float * __restrict__ logits, int * __restrict__ out, int V) {
+    JIB_KS(8, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(8, 1);
     __shared__ unsigned long long best_s[NT / 32];
     const float * row = logits + (size_t) blockIdx.x * V;
     // pack (key, ~index) so that max picks the largest value and, among equals, the lowest index
@@ -198,6 +210,7 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float * __restrict__ l
         }
         if (threadIdx.x == 0) out[blockIdx.x] = 0x7fffffff - (int) (best & 0xffffffffu);
     }
+    JIB_KS(8, 9);
 }
 
 // Exact top-k (k <= 128) of one row per block: 3-pass radix select of the k-th key (11+11+10 bits), then
@@ -205,8 +218,10 @@ __global__ void __launch_bounds__(NT) argmax_kernel(const float * __restrict__ l
 template <int NT>
 __global__ void __launch_bounds__(NT) topk_kernel(const float * __restrict__ logits, float * __restrict__ vals, int * __restrict__ ids,
                                                   int V, int k) {
+    JIB_KS(15, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(15, 1);
     __shared__ int hist[2048];
     __shared__ uint32_t s_prefix, s_mask;
     __shared__ int s_need, s_cnt_gt, s_cnt_eq;
@@ -281,6 +296,7 @@ __global__ void __launch_bounds__(NT) topk_kernel(const float * __restrict__ log
         vals[(size_t) blockIdx.x * k + rank] = v;
         ids[(size_t) blockIdx.x * k + rank] = id;
     }
+    JIB_KS(15, 9);
 }
 
 __global__ void kv_block_copy_kernel(bf16 * cache, long long layer_stride, const int * __restrict__ src, const int * __restrict__ dst,
@@ -294,8 +310,10 @@ __global__ void kv_block_copy_kernel(bf16 * cache, long long layer_stride, const
 }
 
 __global__ void gather_rows_kernel(const bf16 * __restrict__ x, const int * __restrict__ src_row, bf16 * __restrict__ out, int d, int n_src) {
+    JIB_KS(7, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(7, 1);
     const int rrow = blockIdx.x;
     const int s = src_row[rrow];
     JIB_BC(s < n_src, 13, s);
@@ -303,6 +321,7 @@ __global__ void gather_rows_kernel(const bf16 * __restrict__ x, const int * __re
     const uint4 * src = (const uint4 *) (x + (size_t) s * d);
     uint4 * dst = (uint4 *) (out + (size_t) rrow * d);
     for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
+    JIB_KS(7, 9);
 }
 
 inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH; }
@@ -310,6 +329,7 @@ inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAU
 }  // namespace
 
 JIB_BC_DEFINE_SETTER(elementwise)
+JIB_TL_DEFINE_SETTER(elementwise)
 
 extern "C" {
 

@@ -63,6 +63,8 @@ struct GemmArgs {
     int ar_rs_rows;           // two-shot: > 0 delivers each reduced row only to rank row / ar_rs_rows (reduce-scatter)
     void * const * row_ptr;   // null, or per output row the address of its bf16 row (rows scattered to other buffers,
                               // possibly on other GPUs: the expert-parallel return path)
+    const int * src_token;    // grouped, decode batches: x holds the T token rows unsorted, every expert multiplies all of
+                              // them (one token tile) and sorted row i of the result is accumulator column src_token[i]
 };
 
 template <int BN, bool DUAL>
@@ -165,6 +167,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int row0 = blockIdx.y * BN;      // first token row of this tile, relative to the segment / matrix
     int rows_valid = args.T;         // rows of this batch's matrix
     int row_base = 0;                // grouped: offset of the expert's segment in the sorted rows
+    JIB_KS(1, 0);
     pdl_launch_dependents();
     if (args.seg != nullptr) {
         pdl_wait();                  // segment offsets are produced by the routing kernels just before
@@ -206,13 +209,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint32_t tmem = *tmem_slot;
     // Everything above touched only shared/tensor memory and launch-invariant data; activations, the residual,
     // scratch and the output belong to the stream order from here on.
-    if (args.seg == nullptr) pdl_wait();
+    const bool early = args.seg == nullptr;     // grouped launches waited above (they need the segment table)
 
     if (warp == 0) {
         // ================= TMA producer =================
         if (elect_one()) {
             const int a_z = batch;
             const int b_z = args.seg != nullptr ? 0 : batch;
+            const int b_row = args.src_token != nullptr ? 0 : row_base + row0;
+            // Weights are launch-invariant: their tiles of the first ring pass are requested BEFORE the wait for the
+            // previous kernel, so the HBM latency of the stream's head overlaps that kernel's tail.  The activation
+            // tile of each stage follows after the wait and completes the same barrier phase.
+            int pre = 0;
+            if (early && args.ag_flags == nullptr) {
+                pre = min(nkb, C::STAGES);
+                for (int i = 0; i < pre; ++i) {
+                    uint8_t * st = tiles + i * C::STAGE_BYTES;
+                    mbar_expect_tx(&full[i], C::STAGE_BYTES);
+                    const int k = (kb0 + i) * BK;
+                    tma_load_3d(st, &tmA, &full[i], k, n0, a_z);
+                    if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[i], k, n0, a_z);
+                }
+            }
+            if (early) pdl_wait();
+            JIB_KS_ANY(1, 1);
             if (args.ag_flags != nullptr) {
                 // the token rows of this tile were pushed by other ranks: wait (bounded) for the sources that cover
                 // them, then order the peers' generic-proxy stores before this thread's async-proxy (TMA) reads
@@ -232,19 +252,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % C::STAGES;
                 const uint32_t ph = (i / C::STAGES) & 1;
-                if (!mbar_wait(&empty[s], ph ^ 1)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 1, i); break; }
                 uint8_t * st = tiles + s * C::STAGE_BYTES;
-                mbar_expect_tx(&full[s], C::STAGE_BYTES);
                 const int k = (kb0 + i) * BK;
-                tma_load_3d(st, &tmA, &full[s], k, n0, a_z);
-                if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[s], k, n0, a_z);
-                tma_load_3d(st + (DUAL ? 2 : 1) * C::A_BYTES, &tmB, &full[s], k, row_base + row0, b_z);
+                if (i >= pre) {
+                    if (!mbar_wait(&empty[s], ph ^ 1)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 1, i); break; }
+                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    tma_load_3d(st, &tmA, &full[s], k, n0, a_z);
+                    if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[s], k, n0, a_z);
+                }
+                tma_load_3d(st + (DUAL ? 2 : 1) * C::A_BYTES, &tmB, &full[s], k, b_row, b_z);
             }
+            JIB_KS_ANY(1, 2);
+        } else if (early) {
+            pdl_wait();
         }
         __syncwarp();
         if (args.cluster_split) { cluster_sync_all(); cluster_sync_all(); }
     } else if (warp == 1) {
         // ================= MMA issuer =================
+        if (early) pdl_wait();
         if (elect_one()) {
             constexpr uint32_t idesc = idesc_bf16(BM, BN);
             bool ok = true;
@@ -270,12 +296,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (args.cluster_split) { cluster_sync_all(); cluster_sync_all(); }
     } else {
         // ================= epilogue (warps 2..5) =================
+        if (early) pdl_wait();
         const int q = warp & 3;                   // TMEM lane quarter this warp may access
         const int r = q * 32 + lane;              // feature row inside the tile
         const int n = n0 + r;
         const bool acc_ok = mbar_wait(acc_ready, 0);
         if (!acc_ok) jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 3, 0);
         tc_fence_after();
+        JIB_KS_T(1, 4, 64);
         const uint32_t tbase = tmem + ((uint32_t) (q * 32) << 16);
         const int tile_id = (batch * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
         if (args.ar_on != 0 && (threadIdx.x & 127) == 0) JIB_TS(30, args.ar_site, tile_id, split);
@@ -284,16 +312,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         bool do_final = true;
 
         const bool csplit = args.cluster_split != 0;
+        const bool src_mode = args.src_token != nullptr;
+        // accumulator columns that hold data: the tile's valid token rows, or (src mode) all T tokens
+        const int ncols = src_mode ? min(BN, args.T) : min(BN, rows_valid - row0);
         float * stage = (float *) tiles;          // pipeline buffers are idle once the accumulators are complete
+        const long long obase = (long long) batch * args.out_batch_stride;
+        const long long rbase = (long long) batch * args.res_batch_stride;
+        // fused all-reduce: the tile's fp32 values go to slot [rank] of every peer instead of `out`
+        unsigned ar_epoch = 0;
+        size_t ar_par = 0;
+        int ar_owner = 0;
+        size_t ar_opar = 0;           // two-shot: offset of this call site's half of the result buffer (elements)
+        if (args.ar_on) {
+            ar_epoch = *args.ar.epoch;
+            const int par = (args.ar_site + (int) (ar_epoch % 2u) * (args.ar.n_sites & 1)) & 1;
+            const int mr = args.ar_on == 2 ? args.ar.max_rows2 : args.ar.max_rows;
+            ar_par = (size_t) par * ((size_t) args.ar.world * mr * args.ar.d_max);
+            ar_opar = (size_t) par * ((size_t) mr * args.ar.d_max);
+            ar_owner = tile_id % args.ar.world;
+        }
+        // One finished element: feature n of row (row_base + t_rel); gv / uv are the summed accumulators.
+        auto finish = [&](int t_rel, float gv, float uv) {
+            float y = DUAL ? silu(gv) * uv : gv;
+            const long long row = row_base + t_rel;
+            if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 5, (int) row); return; }
+            if (args.ar_on == 2) {      // two-shot: the partial goes to the tile's owner only
+                args.ar.recv2[ar_owner][ar_par + ((size_t) args.ar.rank * args.ar.max_rows2 + row) * args.ar.d_max + n] = y;
+                return;
+            }
+            if (args.ar_on) {
+                const size_t off = ar_par + ((size_t) args.ar.rank * args.ar.max_rows + row) * args.ar.d_max + n;
+                for (int p = 0; p < args.ar.world; ++p) args.ar.recv[p][off] = y;
+                return;
+            }
+            if (args.row_ptr != nullptr) {
+                __nv_bfloat16 * dst = (__nv_bfloat16 *) __ldg((const unsigned long long *) args.row_ptr + row);
+                if (dst != nullptr) dst[n] = __float2bfloat16(y);
+                return;
+            }
+            if (args.residual != nullptr) {
+                const long long ri = rbase + row * args.ldr + n;
+                y += args.res_f32 ? ((const float *) args.residual)[ri] : __bfloat162float(((const __nv_bfloat16 *) args.residual)[ri]);
+            }
+            const long long oi = obase + row * args.ldo + n;
+            if (args.out_f32) ((float *) args.out)[oi] = y;
+            else ((__nv_bfloat16 *) args.out)[oi] = __float2bfloat16(y);
+        };
+
         if (csplit) {
-            // split-K inside a cluster: CTAs 1..splits-1 park their fp32 partial in their own shared memory
-            // ([acc][BN tokens][128 features]); CTA 0 adds them to its accumulators through DSMEM.
-            if (split != 0 && acc_ok) {
+            // split-K inside a cluster: every CTA parks its fp32 partial in its own shared memory ([acc][BN tokens][128
+            // features]).  Without a fused collective the reduction is spread over the cluster: CTA `split` sums token
+            // columns split, split + splits, ... of all peers through DSMEM (in split order, so the sum does not depend on
+            // who computes it) and finishes them -- splits x fewer remote loads per thread than one CTA reducing the
+            // whole tile.  With a fused collective CTA 0 reduces the tile, because the exchange is signalled per tile.
+            const bool spread = args.ar_on == 0;
+            if ((split != 0 || spread) && acc_ok) {
 #pragma unroll 1
                 for (int a = 0; a < ACC; ++a)
 #pragma unroll 1
                     for (int c = 0; c < BN; c += 16) {
-                        if (row0 + c >= rows_valid) break;
+                        if (c >= ncols) break;
                         uint32_t v[16];
                         tmem_ld16(tbase + a * BN + c, v);
                         tmem_ld_wait();
@@ -302,7 +380,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     }
             }
             cluster_sync_all();
-            do_final = split == 0;
+            JIB_KS_T(1, 5, 64);
+            do_final = split == 0 && !spread;
+            if (spread) {
+                const uint32_t sbase = smem_u32(stage);
+                const int n_items = src_mode ? rows_valid : ncols;
+#pragma unroll 1
+                for (int it = split; it < n_items; it += splits) {
+                    const int col = src_mode ? min(max(__ldg(args.src_token + row_base + it), 0), BN - 1) : it;
+                    float gsum[8], usum[8];
+#pragma unroll
+                    for (int pr = 0; pr < 8; ++pr) {
+                        gsum[pr] = pr < splits ? ld_dsmem_f32(sbase + (uint32_t) ((col * BM + r) * 4), pr) : 0.f;
+                        if (DUAL) usum[pr] = pr < splits ? ld_dsmem_f32(sbase + (uint32_t) (((BN + col) * BM + r) * 4), pr) : 0.f;
+                    }
+                    float gv = 0.f, uv = 0.f;
+#pragma unroll
+                    for (int pr = 0; pr < 8; ++pr) { gv += gsum[pr]; if (DUAL) uv += usum[pr]; }
+                    if (n < args.N) finish(src_mode ? it : row0 + it, gv, uv);
+                }
+            }
         }
 
         if (splits > 1 && !csplit) {
@@ -316,6 +413,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 for (int a = 0; a < ACC; ++a)
 #pragma unroll 1
                     for (int c = 0; c < BN; c += 16) {
+                        if (c >= ncols) break;
                         uint32_t v[16];
                         tmem_ld16(tbase + a * BN + c, v);
                         tmem_ld_wait();
@@ -334,35 +432,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             asm volatile("bar.sync 1, 128;" ::: "memory");
             do_final = *flag != 0;
             if (do_final) __threadfence();
+            JIB_KS_T(1, 5, 64);
+            if (do_final && !in_scratch) do_final = false;
         }
 
-        if (do_final && acc_ok && splits > 1 && !csplit && ((long long) tile_id * splits + splits) * (ACC * BN * BM) > args.scratch_elems)
-            do_final = false;
-        if (do_final && acc_ok) {
-            const long long obase = (long long) batch * args.out_batch_stride;
-            const long long rbase = (long long) batch * args.res_batch_stride;
-            // fused all-reduce: the tile's fp32 values go to slot [rank] of every peer instead of `out`
-            unsigned ar_epoch = 0;
-            size_t ar_par = 0;
-            int ar_owner = 0;
-            size_t ar_opar = 0;           // two-shot: offset of this call site's half of the result buffer (elements)
-            if (args.ar_on) {
-                ar_epoch = *args.ar.epoch;
-                const int par = (args.ar_site + (int) (ar_epoch % 2u) * (args.ar.n_sites & 1)) & 1;
-                const int mr = args.ar_on == 2 ? args.ar.max_rows2 : args.ar.max_rows;
-                ar_par = (size_t) par * ((size_t) args.ar.world * mr * args.ar.d_max);
-                ar_opar = (size_t) par * ((size_t) mr * args.ar.d_max);
-                ar_owner = tile_id % args.ar.world;
+        if (do_final && acc_ok && src_mode) {
+            // one sorted row at a time: its token's accumulator column (summed over the splits when there are several)
+#pragma unroll 1
+            for (int it = 0; it < rows_valid; ++it) {
+                const int col = min(max(__ldg(args.src_token + row_base + it), 0), BN - 1);
+                float gv = 0.f, uv = 0.f;
+                if (splits > 1) {
+                    for (int s = 0; s < splits; ++s) {
+                        const float * p = part + (size_t) s * (ACC * BN * BM);
+                        gv += __ldcg(p + (size_t) col * BM + r);
+                        if (DUAL) uv += __ldcg(p + (size_t) (BN + col) * BM + r);
+                    }
+                } else {
+                    gv = __uint_as_float(tmem_ld1(tbase + col));
+                    if (DUAL) uv = __uint_as_float(tmem_ld1(tbase + BN + col));
+                    tmem_ld_wait();
+                }
+                if (n < args.N) finish(it, gv, uv);
             }
+        } else if (do_final && acc_ok) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
-                if (row0 + c >= rows_valid) break;
+                if (c >= ncols) break;
                 float g[16], u[16];
                 if (splits > 1 && !csplit) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
                     // only the valid token columns are summed; 4 splits per trip keep 4 x jn loads in flight
-                    const int jn = min(16, rows_valid - row0 - c);
+                    const int jn = min(16, ncols - c);
 #pragma unroll 4
                     for (int s = 0; s < splits; ++s) {
                         const float * p = part + (size_t) s * (ACC * BN * BM);
@@ -378,6 +480,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     uint32_t v[16];
                     tmem_ld16(tbase + c, v);
                     tmem_ld_wait();
+                    if (c == 0) JIB_KS_T(1, 7, 64);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) g[j] = __uint_as_float(v[j]);
                     if (DUAL) {
@@ -387,7 +490,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         for (int j = 0; j < 16; ++j) u[j] = __uint_as_float(v[j]);
                     }
                     if (csplit) {
-                        const int jn = min(16, rows_valid - row0 - c);
+                        const int jn = min(16, ncols - c);
                         const uint32_t sbase = smem_u32(stage);
                         for (int pr = 1; pr < splits; ++pr) {
 #pragma unroll
@@ -403,36 +506,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (n < args.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int t = row0 + c + j;
-                        if (t >= rows_valid) break;
-                        float y = DUAL ? silu(g[j]) * u[j] : g[j];
-                        const long long row = row_base + t;
-                        if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 5, (int) row); break; }
-                        if (args.ar_on == 2) {      // two-shot: the partial goes to the tile's owner only
-                            args.ar.recv2[ar_owner][ar_par + ((size_t) args.ar.rank * args.ar.max_rows2 + row) * args.ar.d_max + n] = y;
-                            continue;
-                        }
-                        if (args.ar_on) {
-                            const size_t off = ar_par + ((size_t) args.ar.rank * args.ar.max_rows + row) * args.ar.d_max + n;
-                            for (int p = 0; p < args.ar.world; ++p) args.ar.recv[p][off] = y;
-                            continue;
-                        }
-                        if (args.row_ptr != nullptr) {
-                            __nv_bfloat16 * dst = (__nv_bfloat16 *) __ldg((const unsigned long long *) args.row_ptr + row);
-                            if (dst != nullptr) dst[n] = __float2bfloat16(y);
-                            continue;
-                        }
-                        if (args.residual != nullptr) {
-                            const long long ri = rbase + row * args.ldr + n;
-                            y += args.res_f32 ? ((const float *) args.residual)[ri]
-                                              : __bfloat162float(((const __nv_bfloat16 *) args.residual)[ri]);
-                        }
-                        const long long oi = obase + row * args.ldo + n;
-                        if (args.out_f32) ((float *) args.out)[oi] = y;
-                        else ((__nv_bfloat16 *) args.out)[oi] = __float2bfloat16(y);
+                        if (c + j >= ncols) break;
+                        finish(row0 + c + j, g[j], DUAL ? u[j] : 0.f);
                     }
                 }
             }
+        }
+        JIB_KS_T(1, 8, 64);
+        if (do_final && acc_ok) {
             if (args.ar_on == 2) {
                 // signal the owner; the owner waits (bounded) for every source, sums the slots in rank order, adds the
                 // residual and stores the bf16 tile into every rank's result buffer; everybody waits for that delivery
@@ -466,6 +547,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                });
             }
         }
+        JIB_KS_T(1, 6, 64);
         if (csplit) cluster_sync_all();           // peers keep their shared memory alive until CTA 0 has read it
     }
 
@@ -473,6 +555,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
+    JIB_KS(1, 9);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -554,12 +637,8 @@ template <int BN, bool DUAL>
 int launch(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b, const GemmArgs & args, dim3 grid,
            cudaStream_t stream) {
     using C = Cfg<BN, DUAL>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return JIB_E_LAUNCH;
-        attr_done = true;
-    }
+    static std::atomic<unsigned char> attr_done[jib::MAX_DEVICES];
+    if (!jib::ensure_dyn_smem(gemm_kernel<BN, DUAL>, C::SMEM_BYTES, attr_done)) return JIB_E_LAUNCH;
     const cudaError_t e = jib::launch_pdl_cluster(gemm_kernel<BN, DUAL>, grid, dim3(NUM_THREADS), C::SMEM_BYTES, stream,
                                                   args.cluster_split ? args.splits : 1, a, a2, b, args);
     if (e != cudaSuccess) { (void) cudaGetLastError(); return JIB_E_LAUNCH; }
@@ -576,7 +655,9 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     const bool dual = d->w2 != nullptr;
     const bool grouped = d->seg != nullptr;
     const int batch = d->batch > 0 ? d->batch : 1;
-    const int rows_bound = grouped ? (d->max_rows > 0 ? d->max_rows : d->T) : d->T;
+    const bool src_mode = d->src_token != nullptr;
+    if (src_mode && (!grouped || d->src_rows <= 0 || d->src_rows > 256 || d->ar != nullptr)) return JIB_E_ARG;
+    const int rows_bound = src_mode ? d->src_rows : grouped ? (d->max_rows > 0 ? d->max_rows : d->T) : d->T;
     int bn = d->bn;
     if (bn == 0) {
         bn = 16;
@@ -630,20 +711,22 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     } else {
         ma2 = ma;
     }
-    const long long x_rows = grouped ? d->x_rows_total : d->T;
+    const long long x_rows = src_mode ? d->src_rows : grouped ? d->x_rows_total : d->T;
+    if (src_mode && t_tiles != 1) return JIB_E_ARG;
     rc = make_map(&mb, d->x, x_rows, d->K, grouped ? 1 : batch, d->x_row_stride, d->x_batch_stride, bn);
     if (rc) return rc;
 
     GemmArgs a;
     a.out = d->out; a.residual = d->residual; a.seg = d->seg; a.scratch = (float *) d->scratch; a.counters = d->counters;
     a.status = d->status; a.ldo = d->ldo; a.out_batch_stride = d->out_batch_stride; a.ldr = d->ldr;
-    a.res_batch_stride = d->res_batch_stride; a.T = d->T; a.N = d->N; a.K = d->K; a.splits = splits; a.kb_per_split = kbps;
+    a.res_batch_stride = d->res_batch_stride; a.T = src_mode ? d->src_rows : d->T; a.N = d->N; a.K = d->K; a.splits = splits; a.kb_per_split = kbps;
     a.out_f32 = d->out_f32; a.res_f32 = d->res_f32;
     a.rows_total = grouped ? d->x_rows_total : d->T;
     a.scratch_elems = (long long) (d->scratch_bytes / sizeof(float));
     a.ar_on = 0; a.ar_site = 0;
     a.cluster_split = cluster_split ? 1 : 0;
     a.row_ptr = (void * const *) d->out_row_ptr;
+    a.src_token = d->src_token;
     a.ag_flags = (const unsigned *) d->ag_flags; a.ag_epoch = (const unsigned *) d->ag_epoch;
     a.ag_rows = d->ag_rows; a.ag_world = d->ag_world; a.ar_rs_rows = d->ar_rs_rows;
     if (a.ag_flags != nullptr && (a.ag_epoch == nullptr || a.ag_rows <= 0 || a.ag_world <= 0 || grouped || batch != 1)) return JIB_E_ARG;
@@ -790,6 +873,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.ar_on = 0; a.ar_site = 0;
     a.cluster_split = 0;
     a.row_ptr = nullptr;
+    a.src_token = nullptr;
     a.ag_flags = nullptr; a.ag_epoch = nullptr; a.ag_rows = 0; a.ag_world = 0; a.ar_rs_rows = 0;
     memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);

@@ -52,6 +52,10 @@ typedef struct jib_gemm_desc {
     const void * ag_epoch;     //   ag_flags[s] == *ag_epoch (all-gather fused into the activation loads)
     int ag_rows, ag_world;
     int ar_rs_rows;            // with ar: > 0 = reduce-scatter by token rows (row i delivered to rank i / ar_rs_rows only)
+    const int * src_token;     // grouped, small batches: x is NOT expert-sorted but holds the src_rows token rows themselves; every
+    int src_rows;              //   non-empty expert multiplies all of them (src_rows <= the token tile) and result row i (in the
+                               //   expert-sorted order that seg describes) is the accumulator column src_token[i]: the gather of
+                               //   token rows into sorted order is never materialised
 } jib_gemm_desc;
 
 JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);
@@ -85,11 +89,11 @@ JIB_EXPORT int jib_moe_gate(const void * g, const float * w_router, const float 
                             int d, int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, int n_shared,
                             int group_top2, void * stream);
 // jib_moe_gate + jib_moe_permute (over the k + n_shared id columns) in one launch, for T <= 64.  counter: one device int that is
-// zero between launches.
+// zero between launches.  norm_w != NULL: the rows of g are RMS-normalised first (as jib_rmsnorm would) and stored to g_out.
 JIB_EXPORT int jib_moe_route_fused(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts,
                                    int * seg, int * src_token, int * dest, int * counter, int T, int d, int E, int k, int n_group,
                                    int topk_group, float scale, int norm, int sigmoid, int n_shared, int group_top2, int expert_base,
-                                   int E_local, void * stream);
+                                   int E_local, const float * norm_w, float eps, void * g_out, void * stream);
 // Stable counting sort of the (token, k) pairs by local expert. dest[t*k+j] = sorted row or -1 (not local).
 JIB_EXPORT int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
                                void * stream);

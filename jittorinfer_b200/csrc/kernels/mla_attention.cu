@@ -14,6 +14,7 @@
 
 #include "jib_kernels.h"
 #include "pdl.cuh"
+#include "timeline.cuh"
 
 namespace {
 
@@ -175,8 +176,10 @@ __global__ void __launch_bounds__(NT) mla_attn_split_kernel(const bf16 * __restr
 template <int R>
 __global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_ml, int n_splits, int H,
                                         bf16 * __restrict__ o_lat) {
+    JIB_KS(3, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(3, 1);
     // n_splits <= 32: warp 0 turns the (m, l) pairs into normalised weights, then every thread sums its
     // dims over the splits with independent loads.
     __shared__ float wsm[32];
@@ -214,9 +217,12 @@ __global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const
         po[0] = __floats2bfloat162_rn(acc.x, acc.y);
         po[1] = __floats2bfloat162_rn(acc.z, acc.w);
     }
+    JIB_KS(3, 9);
 }
 
 }  // namespace
+
+JIB_TL_DEFINE_SETTER(attn)
 
 extern "C" int jib_mla_attention(const void * q, const void * cache, const int * block_tables, int max_blocks, const int * seq_lens,
                                  const int * q_start, int n_seqs, int T, int H, int r, int dr, int block_size, float scale, int n_splits,

@@ -24,6 +24,7 @@
 
 #include "jib_kernels.h"
 #include "pdl.cuh"
+#include "timeline.cuh"
 
 using namespace sm100;
 
@@ -137,6 +138,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     int total_tiles = 0;
     for (int p = 0; p < n_pass; ++p) total_tiles += pass_k1[p] > pass_k0[p] ? (pass_k1[p] - pass_k0[p] + KV_TILE - 1) / KV_TILE : 0;
 
+    JIB_KS(2, 0);
     pdl_launch_dependents();
     if (total_tiles == 0) {
         pdl_wait();
@@ -177,6 +179,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     pdl_wait();                                 // q, the latent cache rows written this step, and all outputs
+    JIB_KS(2, 1);
     const uint32_t tm_S = tmem;                 // NQ columns
     const uint32_t tm_O = tmem + NQ;            // 4 x NQ columns
 
@@ -290,6 +293,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int kb = pass_k0[p]; kb < pass_k1[p] && ok; kb += KV_TILE, ++it) {
                 if (!mbar_wait(s_ready, it & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 27, it); ok = false; break; }
                 tc_fence_after();
+                if (it == 0) JIB_KS_T(2, 4, 64);
                 float s[NQ];
 #pragma unroll
                 for (int c = 0; c < NQ; c += 16) {
@@ -409,6 +413,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
+    JIB_KS(2, 9);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -431,17 +436,15 @@ EncodeTiledFn encode_fn() {
 template <int QT>
 int launch_flash(const CUtensorMap & mq, const CUtensorMap & mkv, const FlashArgs & a, dim3 grid, cudaStream_t stream) {
     using C = FCfg<QT>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(mla_flash_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-            return JIB_E_LAUNCH;
-        attr_done = true;
-    }
+    static std::atomic<unsigned char> attr_done[jib::MAX_DEVICES];
+    if (!jib::ensure_dyn_smem(mla_flash_kernel<QT>, C::SMEM_BYTES, attr_done)) return JIB_E_LAUNCH;
     JIB_LAUNCH((mla_flash_kernel<QT>), grid, NUM_THREADS, C::SMEM_BYTES, stream, mq, mkv, a);
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 
 }  // namespace
+
+JIB_TL_DEFINE_SETTER(flash)
 
 // q [T][H][576] bf16, cache [n_blocks*64][576] bf16 (one layer), o_lat [T][H][512] bf16.
 // qt: query tokens per CTA (1 for decode batches, 2 for prompt chunks).  n_splits > 1 writes partials that

@@ -13,6 +13,7 @@
 #include "bounds_check.cuh"
 #include "jib_kernels.h"
 #include "pdl.cuh"
+#include "timeline.cuh"
 
 namespace {
 
@@ -26,43 +27,98 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // Router logits in fp32: logits[t][e] = sum_i g[t][i] * w_router[e][i].
-// grid (E, ceil(T/64)), 256 threads: one expert per CTA, the d axis spread over all threads (its router row
-// slice stays in registers), tokens walked in groups of 8 so that every load of a group is independent —
-// the kernel is latency-bound, so memory-level parallelism is what matters.
+// One expert per CTA, 256 threads; thread i owns the 8-element chunks i, i + 256, ... of the d axis (its router row slice
+// stays in registers), tokens are walked in groups of 8 so that every load of a group is independent -- the kernel is
+// latency-bound, so memory-level parallelism is what matters.
+//
+// With norm_w the rows of x are first RMS-normalised: thread mapping, accumulation order and reduction tree are those of
+// rmsnorm_kernel<256, *> (elementwise.cu), so the bf16 row the dot product sees -- and the row CTA (t mod gridDim.x)
+// stores to g_out -- is bit for bit what that kernel would have produced.
 constexpr int GATE_TG = 8;
 constexpr int GATE_NT = 256;
-constexpr int GATE_MAXV = 8;      // float4 slices per thread: d <= 8 * 256 * 4 = 8192
-__global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
-                                                                float * __restrict__ logits, int T, int d, int E) {
-    pdl_launch_dependents();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    __shared__ float red[GATE_NT / 32][GATE_TG];
+constexpr int GATE_MAXC = 4;      // 8-element chunks per thread: d <= 4 * 256 * 8 = 8192
+
+struct alignas(16) bf16x8 {
+    __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void router_rows(const bf16 * __restrict__ x, const float * __restrict__ w_router, const float * __restrict__ norm_w,
+                                            float eps, bf16 * __restrict__ g_out, float * __restrict__ logits, int t_begin, int t_end,
+                                            int T, int d, int E, int e, float (*red)[GATE_TG], float * inv_s) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.x;
-    const int nv = d / 4;
-    const float4 * wr = (const float4 *) (w_router + (size_t) e * d);
-    float4 w[GATE_MAXV];
+    const int nv = d / 8;
+    float4 w[GATE_MAXC][2];
+    float4 nw[GATE_MAXC][2];
 #pragma unroll
-    for (int v = 0; v < GATE_MAXV; ++v) {
-        const int i = threadIdx.x + v * GATE_NT;
-        w[v] = i < nv ? wr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < GATE_MAXC; ++c) {
+        const int i = threadIdx.x + c * GATE_NT;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        w[c][0] = i < nv ? ((const float4 *) (w_router + (size_t) e * d))[2 * i] : z;
+        w[c][1] = i < nv ? ((const float4 *) (w_router + (size_t) e * d))[2 * i + 1] : z;
+        nw[c][0] = (norm_w != nullptr && i < nv) ? ((const float4 *) norm_w)[2 * i] : z;
+        nw[c][1] = (norm_w != nullptr && i < nv) ? ((const float4 *) norm_w)[2 * i + 1] : z;
     }
-    const int t_end = min(T, (int) (blockIdx.y + 1) * 64);
-    for (int t0 = blockIdx.y * 64; t0 < t_end; t0 += GATE_TG) {
+    for (int t0 = t_begin; t0 < t_end; t0 += GATE_TG) {
+        if (norm_w != nullptr) {
+            // sum of squares per token, then 1 / rms: warp w finishes token t0 + w
+            float ss[GATE_TG];
+#pragma unroll
+            for (int j = 0; j < GATE_TG; ++j) ss[j] = 0.f;
+#pragma unroll
+            for (int c = 0; c < GATE_MAXC; ++c) {
+                const int i = threadIdx.x + c * GATE_NT;
+                if (i < nv) {
+#pragma unroll
+                    for (int j = 0; j < GATE_TG; ++j) {
+                        const int t = min(t0 + j, T - 1);
+                        const bf16x8 a = ((const bf16x8 *) (x + (size_t) t * d))[i];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float2 f = __bfloat1622float2(a.v[q]);
+                            ss[j] += f.x * f.x + f.y * f.y;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < GATE_TG; ++j) {
+                const float s = warp_sum(ss[j]);
+                if (lane == 0) red[warp][j] = s;
+            }
+            __syncthreads();
+            {
+                float t = lane < GATE_NT / 32 ? red[lane][warp] : 0.f;
+                t = warp_sum(t);
+                if (lane == 0) inv_s[warp] = rsqrtf(t / (float) d + eps);
+            }
+            __syncthreads();
+        }
         float acc[GATE_TG];
 #pragma unroll
         for (int j = 0; j < GATE_TG; ++j) acc[j] = 0.f;
 #pragma unroll
-        for (int v = 0; v < GATE_MAXV; ++v) {
-            const int i = threadIdx.x + v * GATE_NT;
+        for (int c = 0; c < GATE_MAXC; ++c) {
+            const int i = threadIdx.x + c * GATE_NT;
             if (i < nv) {
 #pragma unroll
                 for (int j = 0; j < GATE_TG; ++j) {
                     const int t = min(t0 + j, T - 1);
-                    const uint2 raw = *(const uint2 *) (g + (size_t) t * d + 4 * i);
-                    const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
-                    const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
-                    acc[j] += w[v].x * a.x + w[v].y * a.y + w[v].z * b.x + w[v].w * b.y;
+                    bf16x8 a = ((const bf16x8 *) (x + (size_t) t * d))[i];
+                    if (norm_w != nullptr) {
+                        const float inv = inv_s[j];
+                        const float2 f0 = __bfloat1622float2(a.v[0]), f1 = __bfloat1622float2(a.v[1]);
+                        const float2 f2 = __bfloat1622float2(a.v[2]), f3 = __bfloat1622float2(a.v[3]);
+                        a.v[0] = __floats2bfloat162_rn(f0.x * inv * nw[c][0].x, f0.y * inv * nw[c][0].y);
+                        a.v[1] = __floats2bfloat162_rn(f1.x * inv * nw[c][0].z, f1.y * inv * nw[c][0].w);
+                        a.v[2] = __floats2bfloat162_rn(f2.x * inv * nw[c][1].x, f2.y * inv * nw[c][1].y);
+                        a.v[3] = __floats2bfloat162_rn(f3.x * inv * nw[c][1].z, f3.y * inv * nw[c][1].w);
+                        if (g_out != nullptr && t0 + j < t_end && (t0 + j) % (int) gridDim.x == (int) blockIdx.x)
+                            ((bf16x8 *) (g_out + (size_t) (t0 + j) * d))[i] = a;
+                    }
+                    const float2 f0 = __bfloat1622float2(a.v[0]), f1 = __bfloat1622float2(a.v[1]);
+                    const float2 f2 = __bfloat1622float2(a.v[2]), f3 = __bfloat1622float2(a.v[3]);
+                    acc[j] += w[c][0].x * f0.x + w[c][0].y * f0.y + w[c][0].z * f1.x + w[c][0].w * f1.y +
+                              w[c][1].x * f2.x + w[c][1].y * f2.y + w[c][1].z * f3.x + w[c][1].w * f3.y;
                 }
             }
         }
@@ -82,107 +138,131 @@ __global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __r
     }
 }
 
-// One warp per token: softmax/sigmoid over the logits, optional group-limited masking, k rounds of arg-max.
+// grid (E, ceil(T/64))
+__global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
+                                                                float * __restrict__ logits, int T, int d, int E) {
+    JIB_KS(9, 0);
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(9, 1);
+    __shared__ float red[GATE_NT / 32][GATE_TG];
+    router_rows(g, w_router, nullptr, 0.f, nullptr, logits, blockIdx.y * 64, min(T, (int) (blockIdx.y + 1) * 64), T, d, E, blockIdx.x, red,
+                nullptr);
+    JIB_KS(9, 9);
+}
+
+// Gating of one token by one warp: softmax/sigmoid over the logits, optional group-limited masking, k rounds of arg-max.
+// prob / sel: MAX_E floats each, gscore: 32 floats, all private to the warp.
+__device__ __forceinline__ void gate_token(const float * __restrict__ logits_row, const float * __restrict__ bias, int * __restrict__ ids,
+                                           float * __restrict__ wts, int t, int E, int k, int n_group, int topk_group, float scale,
+                                           int norm, int sigmoid, int n_shared, int group_top2, float * prob, float * sel,
+                                           float * gscore, int * ids_copy = nullptr) {
+    const int lane = threadIdx.x & 31;
+    const int ld = k + n_shared;
+    for (int e = lane; e < E; e += 32) prob[e] = __ldcg(logits_row + e);      // possibly written by other CTAs: from L2
+    __syncwarp();
+    // softmax / sigmoid over E (E <= 256 -> 8 per lane)
+    float mx = -FLT_MAX;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float p = sigmoid ? 1.f / (1.f + expf(-prob[e])) : expf(prob[e] - mx);
+        prob[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+        if (!sigmoid) prob[e] = prob[e] / sum;
+        sel[e] = prob[e] + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    if (n_group > 1) {
+        const int gs = E / n_group;
+        if (lane < n_group) {
+            // a group's score: its best expert (DeepSeek-V2) or the sum of its two best (DeepSeek-V3)
+            float m = -FLT_MAX, m2 = -FLT_MAX;
+            for (int j = 0; j < gs; ++j) {
+                const float v = sel[lane * gs + j];
+                if (v > m) { m2 = m; m = v; } else if (v > m2) { m2 = v; }
+            }
+            gscore[lane] = (group_top2 && gs >= 2) ? m + m2 : m;
+        }
+        __syncwarp();
+        // keep the topk_group best groups (ties -> lower group id): rank of my group
+        if (lane < n_group) {
+            int rank = 0;
+            const float mine = gscore[lane];
+            for (int j = 0; j < n_group; ++j) rank += (gscore[j] > mine) || (gscore[j] == mine && j < lane);
+            if (rank >= topk_group)
+                for (int j = 0; j < gs; ++j) sel[lane * gs + j] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    // k rounds of warp arg-max (ties -> lower expert id); lane `round` keeps that round's pick
+    float wsum = 0.f, my_w = 0.f;
+    int my_id = 0;
+    for (int round = 0; round < k; ++round) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sel[e];
+            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi >= E) bi = 0;     // a -inf that was already masked can only be re-picked when fewer than k experts are eligible
+        const float p = prob[bi];
+        if (lane == round) { my_id = bi; my_w = p; }
+        if (lane == 0) sel[bi] = -INFINITY;
+        wsum += p;
+        __syncwarp();
+    }
+    if (lane < k) {
+        float w = my_w;
+        if (norm) w /= wsum;
+        ids[(size_t) t * ld + lane] = my_id;
+        wts[(size_t) t * ld + lane] = w * scale;
+        if (ids_copy != nullptr) ids_copy[t * ld + lane] = my_id;
+    } else if (lane < ld) {
+        // shared experts ride along as always-selected experts E, E+1, ... with weight 1
+        ids[(size_t) t * ld + lane] = E + (lane - k);
+        wts[(size_t) t * ld + lane] = 1.f;
+        if (ids_copy != nullptr) ids_copy[t * ld + lane] = E + (lane - k);
+    }
+}
+
+// One warp per token.
 __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__ logits, const float * __restrict__ bias,
                                                       int * __restrict__ ids, float * __restrict__ wts, int E, int k, int n_group,
                                                       int topk_group, float scale, int norm, int sigmoid, int n_shared,
                                                       int group_top2) {
+    JIB_KS(10, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(10, 1);
     __shared__ float prob[MAX_E];
     __shared__ float sel[MAX_E];
     __shared__ float gscore[32];
     const int t = blockIdx.x;
-    const int lane = threadIdx.x;
-    const int ld = k + n_shared;
-    for (int e = lane; e < E; e += 32) prob[e] = logits[(size_t) t * E + e];
-    __syncwarp();
-    {
-        // softmax / sigmoid over E (E <= 256 -> 8 per lane)
-        float mx = -FLT_MAX;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) {
-            const float p = sigmoid ? 1.f / (1.f + expf(-prob[e])) : expf(prob[e] - mx);
-            prob[e] = p;
-            sum += p;
-        }
-        sum = warp_sum(sum);
-        __syncwarp();
-        for (int e = lane; e < E; e += 32) {
-            if (!sigmoid) prob[e] = prob[e] / sum;
-            sel[e] = prob[e] + (bias ? bias[e] : 0.f);
-        }
-        __syncwarp();
-        if (n_group > 1) {
-            const int gs = E / n_group;
-            if (lane < n_group) {
-                // a group's score: its best expert (DeepSeek-V2) or the sum of its two best (DeepSeek-V3)
-                float m = -FLT_MAX, m2 = -FLT_MAX;
-                for (int j = 0; j < gs; ++j) {
-                    const float v = sel[lane * gs + j];
-                    if (v > m) { m2 = m; m = v; } else if (v > m2) { m2 = v; }
-                }
-                gscore[lane] = (group_top2 && gs >= 2) ? m + m2 : m;
-            }
-            __syncwarp();
-            // keep the topk_group best groups (ties -> lower group id): rank of my group
-            if (lane < n_group) {
-                int rank = 0;
-                const float mine = gscore[lane];
-                for (int j = 0; j < n_group; ++j) rank += (gscore[j] > mine) || (gscore[j] == mine && j < lane);
-                if (rank >= topk_group)
-                    for (int j = 0; j < gs; ++j) sel[lane * gs + j] = -INFINITY;
-            }
-            __syncwarp();
-        }
-        // k rounds of warp arg-max (ties -> lower expert id)
-        float wsum = 0.f;
-        for (int round = 0; round < k; ++round) {
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-            for (int e = lane; e < E; e += 32) {
-                const float v = sel[e];
-                if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-            }
-            if (bi >= E) bi = 0;
-            if (lane == 0) {
-                ids[(size_t) t * ld + round] = bi;
-                wts[(size_t) t * ld + round] = prob[bi];
-                sel[bi] = -INFINITY;
-                // a -inf that was already masked can only be re-picked when fewer than k experts are eligible
-            }
-            wsum += prob[bi];
-            __syncwarp();
-        }
-        if (lane < k) {
-            float w = wts[(size_t) t * ld + lane];
-            if (norm) w /= wsum;
-            wts[(size_t) t * ld + lane] = w * scale;
-        } else if (lane < ld) {
-            // shared experts ride along as always-selected experts E, E+1, ... with weight 1
-            ids[(size_t) t * ld + lane] = E + (lane - k);
-            wts[(size_t) t * ld + lane] = 1.f;
-        }
-    }
+    gate_token(logits + (size_t) t * E, bias, ids, wts, t, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, prob,
+               sel, gscore);
+    JIB_KS(10, 9);
 }
 
-// Single-block stable counting sort of n = T*k (token,slot) pairs by local expert id.
+// Stable counting sort of n (token, slot) pairs by local expert id, by all threads of one CTA (a multiple of 32).
 // seg[e] .. seg[e+1] delimit expert e's rows; src_token[row] = token feeding sorted row; dest[i] = row or -1.
-__global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
-                                                          int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest) {
-    pdl_launch_dependents();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    __shared__ int count[MAX_E + 1];
-    __shared__ int offs[MAX_E + 1];
+// Every warp walks the id list twice per expert it owns, so `ids` should sit in shared memory (SORT_SMEM_MAX ids fit the
+// callers' staging buffers); a global pointer works too, at an L2 round trip per 32 ids.
+constexpr int SORT_SMEM_MAX = 4096;
+__device__ __forceinline__ void sort_pairs(const int * __restrict__ ids, int n, int k, int expert_base, int E_local, int * __restrict__ seg,
+                                           int * __restrict__ src_token, int * __restrict__ dest, int * count, int * offs) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int e = warp; e < E_local; e += nw) {
         int c = 0;
@@ -194,10 +274,22 @@ __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restric
         if (lane == 0) count[e] = c;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int e = 0; e < E_local; ++e) { offs[e] = acc; acc += count[e]; }
-        offs[E_local] = acc;
+    if (threadIdx.x < 32) {
+        // exclusive prefix over the experts by one warp (E_local <= 256: 8 per lane)
+        int run = 0;
+        for (int e0 = 0; e0 < E_local; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < E_local ? count[e] : 0;
+            int inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += v;
+            }
+            if (e < E_local) offs[e] = run + inc - c;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) offs[E_local] = run;
     }
     __syncthreads();
     for (int e = threadIdx.x; e <= E_local; e += blockDim.x) seg[e] = offs[e];
@@ -220,6 +312,23 @@ __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restric
             base += __popc(m);
         }
     }
+}
+
+__global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
+                                                          int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest) {
+    JIB_KS(11, 0);
+    pdl_launch_dependents();
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(11, 1);
+    __shared__ int count[MAX_E + 1];
+    __shared__ int offs[MAX_E + 1];
+    __shared__ int ids_s[SORT_SMEM_MAX];
+    if (n <= SORT_SMEM_MAX) {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) ids_s[i] = ids[i];
+        __syncthreads();
+    }
+    sort_pairs(n <= SORT_SMEM_MAX ? ids_s : ids, n, k, expert_base, E_local, seg, src_token, dest, count, offs);
+    JIB_KS(11, 9);
 }
 
 // ---- the same sort for large n (prefill) on many CTAs: histogram per 1024-pair chunk, scan, stable scatter ----------
@@ -309,11 +418,11 @@ __global__ void __launch_bounds__(PERM_CHUNK) permute_scatter_kernel(const int *
     }
 }
 
-// ---- decode batches (T <= 64): router logits, gating and the expert sort in ONE launch ------------------------------
-// grid (E), 256 threads.  CTA e computes the logits of expert e for all tokens (as router_logits_kernel does); the CTA
-// that finishes last (a counter that it also resets) then gates every token, one warp per token, and sorts the
-// (token, slot) pairs by local expert -- the work of moe_gate_kernel and moe_permute_kernel, whose bodies are repeated
-// here until this kernel has been checked on hardware.  Two launches fewer per MoE layer of a decode step.
+// ---- decode batches (T <= 64): [RMSNorm,] router logits, gating and the expert sort in ONE launch -------------------
+// grid (E), 256 threads.  CTA e computes the logits of expert e for all tokens (router_rows; with norm_w it normalises the
+// rows itself and the CTAs share out the stores of the normalised rows to g_out); the CTA that finishes last (a counter
+// that it also resets) then gates every token, one warp per token, and sorts the (token, slot) pairs by local expert.
+// Three (with the norm: four) launches fewer per MoE layer of a decode step.
 constexpr int ROUTE_MAX_T = 64;
 __global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
                                                                   const float * __restrict__ bias, float * __restrict__ logits,
@@ -321,55 +430,17 @@ __global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * _
                                                                   int * __restrict__ src_token, int * __restrict__ dest,
                                                                   int * __restrict__ counter, int T, int d, int E, int k, int n_group,
                                                                   int topk_group, float scale, int norm, int sigmoid, int n_shared,
-                                                                  int group_top2, int expert_base, int E_local) {
+                                                                  int group_top2, int expert_base, int E_local,
+                                                                  const float * __restrict__ norm_w, float eps, bf16 * __restrict__ g_out) {
+    JIB_KS(14, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(14, 1);
     __shared__ float red[GATE_NT / 32][GATE_TG];
+    __shared__ float inv_s[GATE_TG];
     __shared__ int s_last;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    {
-        const int e = blockIdx.x;
-        const int nv = d / 4;
-        const float4 * wr = (const float4 *) (w_router + (size_t) e * d);
-        float4 w[GATE_MAXV];
-#pragma unroll
-        for (int v = 0; v < GATE_MAXV; ++v) {
-            const int i = threadIdx.x + v * GATE_NT;
-            w[v] = i < nv ? wr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        for (int t0 = 0; t0 < T; t0 += GATE_TG) {
-            float acc[GATE_TG];
-#pragma unroll
-            for (int j = 0; j < GATE_TG; ++j) acc[j] = 0.f;
-#pragma unroll
-            for (int v = 0; v < GATE_MAXV; ++v) {
-                const int i = threadIdx.x + v * GATE_NT;
-                if (i < nv) {
-#pragma unroll
-                    for (int j = 0; j < GATE_TG; ++j) {
-                        const int t = min(t0 + j, T - 1);
-                        const uint2 raw = *(const uint2 *) (g + (size_t) t * d + 4 * i);
-                        const float2 a = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
-                        const float2 b = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
-                        acc[j] += w[v].x * a.x + w[v].y * a.y + w[v].z * b.x + w[v].w * b.y;
-                    }
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < GATE_TG; ++j) {
-                const float s = warp_sum(acc[j]);
-                if (lane == 0) red[warp][j] = s;
-            }
-            __syncthreads();
-            if (threadIdx.x < GATE_TG && t0 + threadIdx.x < T) {
-                float s = 0.f;
-#pragma unroll
-                for (int q = 0; q < GATE_NT / 32; ++q) s += red[q][threadIdx.x];
-                logits[(size_t) (t0 + threadIdx.x) * E + e] = s;
-            }
-            __syncthreads();
-        }
-    }
+    const int warp = threadIdx.x >> 5;
+    router_rows(g, w_router, norm_w, eps, g_out, logits, 0, T, T, d, E, blockIdx.x, red, inv_s);
     // ---- last CTA to finish carries on ----
     __threadfence();
     __syncthreads();
@@ -383,133 +454,27 @@ __global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * _
     __shared__ float prob_s[GATE_NT / 32][MAX_E];
     __shared__ float sel_s[GATE_NT / 32][MAX_E];
     __shared__ float gscore_s[GATE_NT / 32][32];
-    float * prob = prob_s[warp];
-    float * sel = sel_s[warp];
-    float * gscore = gscore_s[warp];
-    const int ld = k + n_shared;
+    __shared__ int ids_s[ROUTE_MAX_T * 32];      // k + n_shared <= 32 columns
     for (int t = warp; t < T; t += GATE_NT / 32) {
-        for (int e = lane; e < E; e += 32) prob[e] = __ldcg(logits + (size_t) t * E + e);     // written by other CTAs: from L2
-        __syncwarp();
-        float mx = -FLT_MAX;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) {
-            const float p = sigmoid ? 1.f / (1.f + expf(-prob[e])) : expf(prob[e] - mx);
-            prob[e] = p;
-            sum += p;
-        }
-        sum = warp_sum(sum);
-        __syncwarp();
-        for (int e = lane; e < E; e += 32) {
-            if (!sigmoid) prob[e] = prob[e] / sum;
-            sel[e] = prob[e] + (bias ? bias[e] : 0.f);
-        }
-        __syncwarp();
-        if (n_group > 1) {
-            const int gs = E / n_group;
-            if (lane < n_group) {
-                float m = -FLT_MAX, m2 = -FLT_MAX;
-                for (int j = 0; j < gs; ++j) {
-                    const float v = sel[lane * gs + j];
-                    if (v > m) { m2 = m; m = v; } else if (v > m2) { m2 = v; }
-                }
-                gscore[lane] = (group_top2 && gs >= 2) ? m + m2 : m;
-            }
-            __syncwarp();
-            if (lane < n_group) {
-                int rank = 0;
-                const float mine = gscore[lane];
-                for (int j = 0; j < n_group; ++j) rank += (gscore[j] > mine) || (gscore[j] == mine && j < lane);
-                if (rank >= topk_group)
-                    for (int j = 0; j < gs; ++j) sel[lane * gs + j] = -INFINITY;
-            }
-            __syncwarp();
-        }
-        float wsum = 0.f;
-        for (int round = 0; round < k; ++round) {
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-            for (int e = lane; e < E; e += 32) {
-                const float v = sel[e];
-                if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-            }
-            if (bi >= E) bi = 0;
-            if (lane == 0) {
-                ids[(size_t) t * ld + round] = bi;
-                wts[(size_t) t * ld + round] = prob[bi];
-                sel[bi] = -INFINITY;
-            }
-            wsum += prob[bi];
-            __syncwarp();
-        }
-        if (lane < k) {
-            float w = wts[(size_t) t * ld + lane];
-            if (norm) w /= wsum;
-            wts[(size_t) t * ld + lane] = w * scale;
-        } else if (lane < ld) {
-            ids[(size_t) t * ld + lane] = E + (lane - k);
-            wts[(size_t) t * ld + lane] = 1.f;
-        }
+        gate_token(logits + (size_t) t * E, bias, ids, wts, t, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2,
+                   prob_s[warp], sel_s[warp], gscore_s[warp], ids_s);
         __syncwarp();
     }
-    __syncthreads();         // ids of all tokens are written (and visible to the whole CTA)
-
-    // ---- stable counting sort of the n = T * ld pairs by local expert ----
+    __syncthreads();         // ids of all tokens are in shared memory
     __shared__ int count[MAX_E + 1];
     __shared__ int offs[MAX_E + 1];
-    const int n = T * ld, nw = GATE_NT / 32;
-    for (int e = warp; e < E_local; e += nw) {
-        int c = 0;
-        for (int i0 = 0; i0 < n; i0 += 32) {
-            const int i = i0 + lane;
-            const bool hit = i < n && ids[i] - expert_base == e;
-            c += __popc(__ballot_sync(0xffffffffu, hit));
-        }
-        if (lane == 0) count[e] = c;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int e = 0; e < E_local; ++e) { offs[e] = acc; acc += count[e]; }
-        offs[E_local] = acc;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e <= E_local; e += blockDim.x) seg[e] = offs[e];
-    for (int i = offs[E_local] + threadIdx.x; i < n; i += blockDim.x) src_token[i] = -1;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int le = ids[i] - expert_base;
-        if (le < 0 || le >= E_local) dest[i] = -1;
-    }
-    for (int e = warp; e < E_local; e += nw) {
-        int base = offs[e];
-        for (int i0 = 0; i0 < n; i0 += 32) {
-            const int i = i0 + lane;
-            const bool hit = i < n && ids[i] - expert_base == e;
-            const unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                const int row = base + __popc(m & ((1u << lane) - 1));
-                dest[i] = row;
-                if (row < n) src_token[row] = i / ld;
-            }
-            base += __popc(m);
-        }
-    }
+    sort_pairs(ids_s, T * (k + n_shared), k + n_shared, expert_base, E_local, seg, src_token, dest, count, offs);
+    JIB_KS(14, 9);
 }
 
 // out[t] = residual[t] + shared[t] + sum_j wts[t][j] * y[dest[t][j]]   (fp32 accumulate, bf16 out)
 __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
                                    const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
                                    int d) {
+    JIB_KS(12, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(12, 1);
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < d / 8; i += blockDim.x) {
         float acc[8];
@@ -555,6 +520,7 @@ __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __re
         for (int q = 0; q < 4; ++q) po[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
         ((uint4 *) (out + (size_t) t * d))[i] = o;
     }
+    JIB_KS(12, 9);
 }
 
 // ---- combine fused with the RMSNorm that follows it (the next block's attention norm) ---------------------------------
@@ -580,8 +546,10 @@ __global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __res
                                                               const bf16 * __restrict__ residual, const float * __restrict__ norm_w,
                                                               bf16 * __restrict__ out, bf16 * __restrict__ out_norm, int k, int d,
                                                               float eps) {
+    JIB_KS(13, 0);
     pdl_launch_dependents();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(13, 1);
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int nv = d / 8;
@@ -657,6 +625,7 @@ __global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __res
             ((uint4 *) (out_norm + (size_t) t * d))[i] = o;
         }
     }
+    JIB_KS(13, 9);
 }
 
 inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH; }
@@ -664,6 +633,7 @@ inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAU
 }  // namespace
 
 JIB_BC_DEFINE_SETTER(moe)
+JIB_TL_DEFINE_SETTER(moe)
 
 extern "C" {
 
@@ -671,7 +641,7 @@ int jib_moe_gate(const void * g, const float * w_router, const float * bias, flo
                  int E, int k, int n_group, int topk_group, float scale, int norm, int sigmoid, int n_shared, int group_top2,
                  void * stream) {
     if (T <= 0) return 0;
-    if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 4 || d > GATE_MAXV * GATE_NT * 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
+    if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 8 || d > GATE_MAXC * GATE_NT * 8 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
     JIB_LAUNCH((router_logits_kernel), dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, logits, T, d, E);
     if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;
     JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2);
@@ -679,15 +649,19 @@ int jib_moe_gate(const void * g, const float * w_router, const float * bias, flo
 }
 
 // jib_moe_gate followed by jib_moe_permute (over the k + n_shared columns) in one launch; T <= 64.  counter: one device int,
-// zero between launches.
+// zero between launches.  norm_w != NULL: g holds un-normalised rows; they are RMS-normalised (weights norm_w, eps) on the
+// fly and also stored to g_out [T][d] -- what jib_rmsnorm would have produced.
 int jib_moe_route_fused(const void * g, const float * w_router, const float * bias, float * logits, int * ids, float * wts, int * seg,
                         int * src_token, int * dest, int * counter, int T, int d, int E, int k, int n_group, int topk_group, float scale,
-                        int norm, int sigmoid, int n_shared, int group_top2, int expert_base, int E_local, void * stream) {
+                        int norm, int sigmoid, int n_shared, int group_top2, int expert_base, int E_local, const float * norm_w, float eps,
+                        void * g_out, void * stream) {
     if (T <= 0) return 0;
     if (T > ROUTE_MAX_T || counter == nullptr || E_local > MAX_E || E_local < 1) return JIB_E_ARG;
-    if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 4 || d > GATE_MAXV * GATE_NT * 4 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
+    if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 8 || d > GATE_MAXC * GATE_NT * 8 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
+    if (norm_w != nullptr && g_out == nullptr) return JIB_E_ARG;
     JIB_LAUNCH((moe_route_fused_kernel), E, GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, bias, logits, ids, wts, seg,
-               src_token, dest, counter, T, d, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, expert_base, E_local);
+               src_token, dest, counter, T, d, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, expert_base, E_local,
+               norm_w, eps, (bf16 *) g_out);
     return launched();
 }
 

@@ -10,6 +10,7 @@
 // Captured into CUDA graphs the attribute becomes a programmatic dependency edge.  JIB_PDL=0 turns it off.
 #pragma once
 #include <cuda_runtime.h>
+#include <atomic>
 #include <stdlib.h>
 #include <string.h>
 #include <utility>
@@ -25,6 +26,19 @@ inline bool pdl_enabled() {
         return !(e != nullptr && e[0] == '0');
     }();
     return on;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to one (function, device) pair: a process that launches on several
+// GPUs (layer split) has to set it on each.  `done` is the caller's per-kernel table, one atomic flag per device ordinal.
+constexpr int MAX_DEVICES = 64;
+template <typename K>
+inline bool ensure_dyn_smem(K kern, int bytes, std::atomic<unsigned char> (&done)[MAX_DEVICES]) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return false;
+    if (done[dev].load(std::memory_order_acquire)) return true;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    done[dev].store(1, std::memory_order_release);
+    return true;
 }
 
 // cluster_z > 1: consecutive blockIdx.z values form a thread-block cluster of that size.

@@ -12,6 +12,12 @@
 //        21 two-shot, owner: the partial of source rank c has arrived
 //        22 two-shot: the owner's reduced tile has been delivered here
 //        30 GEMM with a fused collective: accumulators complete (main loop over)  (a = call site, b = tile, c = split)
+//        100 + kernel id: phase stamps of a kernel's CTAs (a = linear block index, b = blocks in the grid, c = phase:
+//            0 entry, 1 past the wait for the previous kernel, 9 exit; 2..8 kernel specific).  Kernel ids: 1 gemm
+//            (2 operand loads issued, 4 accumulators complete, 5 split partial published, 6 result stored), 2 mla_flash
+//            (4 first score tile, 6 result stored), 3 mla_combine, 4 rmsnorm, 5 mla_qkv_post, 6 embed_gather,
+//            7 gather_rows, 8 argmax, 9 router_logits, 10 moe_gate, 11 moe_permute, 12 moe_combine, 13 moe_combine_norm,
+//            14 moe_route_fused, 15 topk
 // Times are per GPU (%globaltimer of the stamping GPU): compare stamps of one rank only.
 #pragma once
 #include <cuda_runtime.h>
@@ -40,6 +46,18 @@ __device__ __forceinline__ void jib_stamp(int kind, int a, int b, int c) {
     buf[i].c = c;
 }
 #define JIB_TS(kind, a, b, c) jib_stamp((kind), (int) (a), (int) (b), (int) (c))
+// phase stamp by thread `tid` of every CTA
+#define JIB_KS_T(id, phase, tid)                                                                                     \
+    do {                                                                                                             \
+        if (threadIdx.x == (tid))                                                                                    \
+            jib_stamp(100 + (id), (int) (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),            \
+                      (int) (gridDim.x * gridDim.y * gridDim.z), (phase));                                           \
+    } while (0)
+#define JIB_KS(id, phase) JIB_KS_T(id, phase, 0)
+// the same by whichever single thread executes it
+#define JIB_KS_ANY(id, phase)                                                                                  \
+    jib_stamp(100 + (id), (int) (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)),              \
+              (int) (gridDim.x * gridDim.y * gridDim.z), (phase))
 #define JIB_TL_DEFINE_SETTER(unit)                                                                        \
     extern "C" JIB_EXPORT int jib_timeline_set_##unit(void * buf, unsigned * head, unsigned cap) {        \
         JibStamp * b = (JibStamp *) buf;                                                                  \
@@ -49,6 +67,15 @@ __device__ __forceinline__ void jib_stamp(int kind, int a, int b, int c) {
     }
 #else
 #define JIB_TS(kind, a, b, c) \
+    do {                      \
+    } while (0)
+#define JIB_KS_T(id, phase, tid) \
+    do {                         \
+    } while (0)
+#define JIB_KS(id, phase) \
+    do {                  \
+    } while (0)
+#define JIB_KS_ANY(id, phase) \
     do {                      \
     } while (0)
 #define JIB_TL_DEFINE_SETTER(unit)

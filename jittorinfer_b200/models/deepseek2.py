@@ -303,18 +303,21 @@ class DeepSeek2Model:
                                   r, self.block_size, batch.max_q_len, batch.attn_meta)
         return ops.v_up(o_lat, L.w_uv)
 
-    def _mlp(self, L: _Layer, g: torch.Tensor, residual: torch.Tensor, norm=None):
-        """``norm=(weight, eps)`` (unsharded MoE blocks only): returns (x, rmsnorm(x) * weight)."""
+    def _mlp(self, L: _Layer, residual: torch.Tensor, norm=None):
+        """The feed-forward block on ``residual`` (its input norm included): returns residual + ffn(rmsnorm(residual)).
+        ``norm=(weight, eps)`` (MoE blocks): returns (x, rmsnorm(x) * weight), the next block's input norm."""
         hp = self.hp
         if not L.is_moe:
+            g, _ = ops.rmsnorm(residual, L.ffn_norm, hp.rms_eps)
             hmid = ops.gateup_silu(g, L.w_gate, L.w_up)
             return self._row_parallel(hmid, L.w_down, residual)
         dp = self.spec.dp_attention and self.spec.sharded
         base = self.expert_base if self.spec.expert_parallel else 0
-        ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
-                                hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid",
-                                L.n_shared_merged or 0, hp.group_score_top2,
-                                route=None if dp else (base, L.w_gate_exps.shape[0]))     # the local expert sort follows
+        # the router launch of a decode batch also normalises its input rows and sorts the pairs by local expert
+        ids, wts, g = ops.moe_gate(residual, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
+                                   hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid",
+                                   L.n_shared_merged or 0, hp.group_score_top2,
+                                   route=None if dp else (base, L.w_gate_exps.shape[0]), pre_norm=(L.ffn_norm, hp.rms_eps))
         if dp:
             shared = None
             if L.w_gate_sh is not None:
@@ -425,11 +428,10 @@ class DeepSeek2Model:
             h_next = None
             a = self._attention(L, h, batch, kv_cache[il])
             y = self._row_parallel(a, L.w_o, x)
-            g, _ = ops.rmsnorm(y, L.ffn_norm, hp.rms_eps)
             if fuse_norm and L.is_moe and il + 1 < len(self.layers):
-                x, h_next = self._mlp(L, g, y, norm=(self.layers[il + 1].attn_norm, hp.rms_eps))
+                x, h_next = self._mlp(L, y, norm=(self.layers[il + 1].attn_norm, hp.rms_eps))
             else:
-                x = self._mlp(L, g, y)
+                x = self._mlp(L, y)
             if self.tensor_hook is not None:
                 self.tensor_hook(f"blk.{il}.attn_out", a)
                 self.tensor_hook(f"blk.{il}.ffn_inp", y)

@@ -87,10 +87,15 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
     return ref.mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_size)
 
 
-def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False, route=None):
-    """``route=(expert_base, E_local)`` tells the CUDA path which local expert sort follows (see ``native.moe_gate``)."""
+def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False, route=None, pre_norm=None):
+    """``route=(expert_base, E_local)`` tells the CUDA path which local expert sort follows (see ``native.moe_gate``).
+    ``pre_norm=(weight, eps)``: ``g`` is the un-normalised block input; returns (ids, wts, rmsnorm(g) * weight) -- on the CUDA
+    path the router launch of a decode batch normalises the rows itself."""
     if use_native(g):
-        return nat().moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, route)
+        return nat().moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, route, pre_norm)
+    if pre_norm is not None:
+        g, _ = ref.rmsnorm(g, pre_norm[0], pre_norm[1])
+        return ref.moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2) + (g,)
     return ref.moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2)
 
 
@@ -110,8 +115,9 @@ def moe_ffn(x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base=0, n_e
 
 
 def fused_combine_norm() -> bool:
-    """Whether the model should ask ``moe_ffn`` for the next block's norm (JIB_FUSED_COMBINE_NORM=1 on the CUDA path)."""
-    return bool(_native is not None and _native.FUSED_COMBINE_NORM) or os.environ.get("JIB_FUSED_COMBINE_NORM", "0") == "1"
+    """Whether the model should ask ``moe_ffn`` for the next block's norm as well (one launch on the CUDA path;
+    JIB_FUSED_COMBINE_NORM=0 keeps the two launches for A/B measurements)."""
+    return os.environ.get("JIB_FUSED_COMBINE_NORM", "1") == "1"
 
 
 def argmax(logits):

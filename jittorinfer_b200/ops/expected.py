@@ -76,6 +76,19 @@ def layer_launches(hp: DeepSeek2HParams, T: int, S: int, world: int = 1) -> List
     return out
 
 
+def step_memory_bytes(hp: DeepSeek2HParams, T: int, S: int, world: int = 1) -> float:
+    """Bytes one rank must read in one decode step of ``T`` sequences with ``S`` cached tokens each: every layer's launches
+    (dense leading layers stream their whole FFN instead of the experts hit) plus the output head.  Divided by the copy
+    bandwidth this is the memory-bound time a measured step is held against."""
+    rows = layer_launches(hp, T, S, world)
+    moe = sum(b for _, b, _ in rows)
+    attn = sum(b for k, b, _ in rows[: next(i for i, r in enumerate(rows) if r[0].startswith("rmsnorm (ffn_norm)")) + 1])
+    dense = attn + 3 * hp.n_ff * hp.n_embd * 2 / world
+    head = hp.n_vocab * hp.n_embd * 2
+    n_dense = hp.n_layer_dense_lead if hp.n_layer > hp.n_layer_dense_lead else 0
+    return n_dense * dense + (hp.n_layer - n_dense) * moe + head
+
+
 def prefill_launches(hp: DeepSeek2HParams, T: int, world: int = 1) -> List[Tuple[str, float, float, str]]:
     """(launch, FLOPs, bytes, note) of one MoE layer for a prefill chunk of ``T`` tokens of one sequence (causal), per rank."""
     d, H = hp.n_embd, hp.n_head // world

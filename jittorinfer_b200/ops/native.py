@@ -16,17 +16,19 @@ _lib = None
 _ws: Dict[int, "Workspace"] = {}
 launch_count = 0            # kernels launched through this module (bench.py reports it)
 
-# The multi-CTA expert sort has been cross-compiled and its algorithm checked against a stable sort on the host, but it
-# has not run on a GPU yet: off unless JIB_PERMUTE_MULTI=1.
-PERMUTE_MULTI = os.environ.get("JIB_PERMUTE_MULTI", "0") == "1"
+# Switches for A/B measurements (each defaults to the faster path; "0" selects the separate launches).
+# Expert sort over many CTAs (histogram / scan / scatter) for batches of PERMUTE_MULTI_MIN (token, expert) pairs and more.
+PERMUTE_MULTI = os.environ.get("JIB_PERMUTE_MULTI", "1") == "1"
 PERMUTE_MULTI_MIN = 4096
-# Router logits + gating + expert sort in one launch for decode batches (<= 64 tokens): same state (cross-compiled, not
-# yet run on a GPU), off unless JIB_FUSED_ROUTE=1.
-FUSED_ROUTE = os.environ.get("JIB_FUSED_ROUTE", "0") == "1"
-# Grouped-GEMM split-K hint from the expected number of experts hit (off until measured: JIB_ACTIVE_HINT=1).
+# [RMSNorm +] router logits + gating + expert sort in one launch for decode batches (<= FUSED_ROUTE_MAX_T tokens).
+FUSED_ROUTE = os.environ.get("JIB_FUSED_ROUTE", "1") == "1"
+# Grouped-GEMM split-K hint from the expected number of experts hit instead of all local experts.
 ACTIVE_HINT_EXPECTED = os.environ.get("JIB_ACTIVE_HINT", "0") == "1"
-# Expert combine fused with the RMSNorm of the next block (one launch fewer per MoE layer): JIB_FUSED_COMBINE_NORM=1.
-FUSED_COMBINE_NORM = os.environ.get("JIB_FUSED_COMBINE_NORM", "0") == "1"
+# Expert combine fused with the RMSNorm of the next block (one launch fewer per MoE layer).
+FUSED_COMBINE_NORM = os.environ.get("JIB_FUSED_COMBINE_NORM", "1") == "1"
+# Decode batches: the grouped gate|up GEMM reads the token rows in place (no gather into expert order).
+GROUPED_SRC = os.environ.get("JIB_GROUPED_SRC", "1") == "1"
+GROUPED_SRC_MAX_T = 64
 FUSED_ROUTE_MAX_T = 64
 _route_stash: Dict[tuple, tuple] = {}       # (ids ptr, expert_base, E_local) -> (seg, src, dest) produced by the fused launch
 
@@ -42,7 +44,8 @@ class GemmDesc(C.Structure):
                [(n, C.c_int) for n in ("n_counters", "T", "N", "K", "batch", "max_rows", "active_hint", "out_f32", "res_f32",
                                        "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p), ("out_row_ptr", C.c_void_p), ("ag_flags", C.c_void_p),
                                                                              ("ag_epoch", C.c_void_p), ("ag_rows", C.c_int),
-                                                                             ("ag_world", C.c_int), ("ar_rs_rows", C.c_int)]
+                                                                             ("ag_world", C.c_int), ("ar_rs_rows", C.c_int),
+                                                                             ("src_token", C.c_void_p), ("src_rows", C.c_int)]
 
 
 def load():
@@ -72,7 +75,7 @@ def load():
     sig("jib_gather_rows", vp, ip, vp, i, i, i, vp)
     sig("jib_moe_gate", vp, fp, fp, fp, ip, fp, i, i, i, i, i, i, f, i, i, i, i, vp)
     sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
-    sig("jib_moe_route_fused", vp, fp, fp, fp, ip, fp, ip, ip, ip, ip, i, i, i, i, i, i, f, i, i, i, i, i, i, vp)
+    sig("jib_moe_route_fused", vp, fp, fp, fp, ip, fp, ip, ip, ip, ip, i, i, i, i, i, i, f, i, i, i, i, i, i, fp, f, vp, vp)
     sig("jib_moe_permute_multi", ip, i, i, i, i, ip, ip, ip, ip, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
     sig("jib_moe_combine_norm", vp, ip, fp, vp, vp, fp, vp, vp, i, i, i, f, vp)
@@ -206,9 +209,11 @@ def gemm_batched(x_ptr: int, x_row_stride: int, x_batch_stride: int, w: torch.Te
 
 def gemm_grouped_raw(x_ptr: int, x_rows_total: int, K: int, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor],
                      max_rows: int, active_hint: int, splits: int = 0, bn: int = 0, device=None,
-                     out_row_ptr: Optional[int] = None) -> Optional[torch.Tensor]:
+                     out_row_ptr: Optional[int] = None, src_token: Optional[torch.Tensor] = None, src_rows: int = 0) -> Optional[torch.Tensor]:
     """Grouped GEMM over a raw row buffer (e.g. a peer-mapped receive buffer).  With ``out_row_ptr`` (device array of
-    row addresses) every result row is stored through its pointer and nothing is returned."""
+    row addresses) every result row is stored through its pointer and nothing is returned.  With ``src_token`` the
+    buffer holds the ``src_rows`` token rows unsorted and sorted result row i is computed from token ``src_token[i]``
+    (``x_rows_total`` stays the number of sorted rows, i.e. rows of the result)."""
     E, N, K2 = w.shape
     assert K2 == K
     device = device or w.device
@@ -224,6 +229,8 @@ def gemm_grouped_raw(x_ptr: int, x_rows_total: int, K: int, seg: torch.Tensor, w
     d.T, d.N, d.K, d.batch, d.max_rows, d.active_hint = max_rows, N, K, E, max_rows, active_hint
     d.out_f32, d.res_f32, d.splits, d.bn, d.sm_count = 0, 0, splits, bn, ws.sm_count
     d.out_row_ptr = out_row_ptr
+    if src_token is not None:
+        d.src_token, d.src_rows = src_token.data_ptr(), src_rows
     _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_grouped")
     return out
 
@@ -329,30 +336,40 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
 
 
 # ---- MoE -----------------------------------------------------------------------------------------
-def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False, route=None):
+def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False, route=None,
+             pre_norm=None):
     """``route=(expert_base, E_local)``: the caller will sort these ids by local expert next (``moe_permute``); for decode
-    batches both steps then run as one launch and ``moe_permute`` picks the result up."""
+    batches both steps then run as one launch and ``moe_permute`` picks the result up.
+    ``pre_norm=(weight, eps)``: ``g`` holds un-normalised rows; returns (ids, wts, rmsnorm(g) * weight), the norm done by
+    the router launch itself for decode batches."""
     T, d = g.shape
+    fused = FUSED_ROUTE and route is not None and T <= FUSED_ROUTE_MAX_T
+    g_in = g
+    if pre_norm is not None and not fused:
+        g, _ = rmsnorm(g, pre_norm[0], pre_norm[1])
     E = w_router.shape[0]
     ids = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
     wts = torch.empty(T, k + n_shared, dtype=torch.float32, device=g.device)
     logits = torch.empty(T, E, dtype=torch.float32, device=g.device)
-    if FUSED_ROUTE and route is not None and T <= FUSED_ROUTE_MAX_T:
+    if fused:
         expert_base, E_local = route
         n = T * (k + n_shared)
         seg = torch.empty(E_local + 1, dtype=torch.int32, device=g.device)
         src = torch.empty(n, dtype=torch.int32, device=g.device)
         dest = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
-        _ck(load().jib_moe_route_fused(g.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(),
+        assert g_in.dtype == torch.bfloat16 and g_in.is_contiguous()
+        g_out = torch.empty_like(g_in) if pre_norm is not None else None
+        _ck(load().jib_moe_route_fused(g_in.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(),
                                        seg.data_ptr(), src.data_ptr(), dest.data_ptr(), workspace(g.device).route_counter.data_ptr(),
                                        T, d, E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared,
-                                       int(group_top2), expert_base, E_local, _stream()), "moe_route_fused")
+                                       int(group_top2), expert_base, E_local, pre_norm[0].data_ptr() if pre_norm is not None else None,
+                                       float(pre_norm[1]) if pre_norm is not None else 0.0, _p(g_out), _stream()), "moe_route_fused")
         _route_stash.clear()                       # at most one pending result: the sort that follows this gate
         _route_stash[(ids.data_ptr(), expert_base, E_local)] = (seg, src, dest, ids)
-        return ids, wts
+        return (ids, wts, g_out) if pre_norm is not None else (ids, wts)
     _ck(load().jib_moe_gate(g.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, d,
                             E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared, int(group_top2), _stream()), "moe_gate")
-    return ids, wts
+    return (ids, wts, g) if pre_norm is not None else (ids, wts)
 
 
 def moe_permute(ids, expert_base, E_local):
@@ -413,11 +430,15 @@ def moe_routed(x, ids, wts, wg, wu, wd, expert_base=0, n_expert=None):
     T, k = ids.shape
     E_local = wg.shape[0]
     seg, src, dest = moe_permute(ids, expert_base, E_local)
-    xp = gather_rows(x, src)
     active = min(E_local, T * k)
     if ACTIVE_HINT_EXPECTED and n_expert:        # split-K sized for the experts a batch is expected to hit, not for all
         active = min(active, expected_active_experts(T, k, E_local, n_expert))
-    h = gemm_grouped(xp, seg, wg, wu, T, active)
+    if GROUPED_SRC and T <= GROUPED_SRC_MAX_T and x.is_contiguous():
+        # decode batches: every expert that has rows multiplies the whole (tiny) token tile and picks its tokens' columns in the
+        # epilogue, so the token rows are never gathered into expert order
+        h = gemm_grouped_raw(x.data_ptr(), T * k, x.shape[1], seg, wg, wu, T, active, device=x.device, src_token=src, src_rows=T)
+    else:
+        h = gemm_grouped(gather_rows(x, src), seg, wg, wu, T, active)
     y = gemm_grouped(h, seg, wd, None, T, active)
     return y, dest
 

@@ -26,7 +26,7 @@ import numpy as np
 STAMP_DTYPE = np.dtype([("t", "<u8"), ("kind", "<i4"), ("a", "<i4"), ("b", "<i4"), ("c", "<i4")])      # JibStamp
 KIND_NAMES = {10: "oneshot_signalled", 11: "oneshot_source_arrived", 12: "oneshot_all_seen", 20: "twoshot_signalled",
               21: "twoshot_owner_source_arrived", 22: "twoshot_delivered", 30: "gemm_accumulators_done"}
-UNITS = ("gemm", "comm", "combine_ar")
+UNITS = ("gemm", "comm", "combine_ar", "elementwise", "moe", "attn", "flash")
 
 
 class Timeline:
@@ -143,3 +143,74 @@ def to_chrome_trace(stamps: np.ndarray, rank: int = 0) -> str:
     ev = [{"name": KIND_NAMES.get(int(s["kind"]), str(int(s["kind"]))), "ph": "i", "s": "t", "pid": rank, "tid": int(s["a"]),
            "ts": (int(s["t"]) - t0) / 1e3, "args": {"tile": int(s["b"]), "rank": int(s["c"])}} for s in stamps]
     return json.dumps({"traceEvents": ev, "displayTimeUnit": "ns"})
+
+
+# ---- kernel phase stamps (kinds 100 + kernel id) ---------------------------------------------------------------------
+KERNEL_NAMES = {1: "gemm", 2: "mla_flash", 3: "mla_combine", 4: "rmsnorm", 5: "mla_qkv_post", 6: "embed_gather", 7: "gather_rows",
+                8: "argmax", 9: "router_logits", 10: "moe_gate", 11: "moe_permute", 12: "moe_combine", 13: "moe_combine_norm",
+                14: "moe_route_fused", 15: "topk"}
+
+
+def kernel_launches(stamps: np.ndarray) -> List[Dict]:
+    """Groups the phase stamps (kind >= 100) into launches, in launch order.
+
+    Every CTA stamps phase 0 on entry, and a kernel's CTAs all enter before the next kernel's do, so the entry stamps
+    sorted by time fall into consecutive runs of ``b`` (grid size) stamps of one kind: one run per launch.  The other
+    phases of a CTA are matched to its launch by counting: the n-th phase-p stamp of (kind, grid size, block) belongs to the
+    n-th launch with that kind and grid size.  Per launch: name, grid, and per phase the first and last time a CTA reached
+    it, in microseconds from the first entry stamp of the whole record."""
+    ks = stamps[stamps["kind"] >= 100]
+    if ks.shape[0] == 0:
+        return []
+    ks = ks[np.argsort(ks["t"], kind="stable")]
+    t0 = int(ks["t"][0])
+    entries = ks[ks["c"] == 0]
+    launches: List[Dict] = []
+    by_key: Dict[tuple, List[int]] = {}
+    i = 0
+    while i < entries.shape[0]:
+        kind, grid = int(entries["kind"][i]), int(entries["b"][i])
+        j = i
+        while j < entries.shape[0] and j - i < grid and int(entries["kind"][j]) == kind and int(entries["b"][j]) == grid:
+            j += 1
+        rec = {"kernel": KERNEL_NAMES.get(kind - 100, str(kind - 100)), "grid": grid, "n_entered": j - i,
+               "phases": {0: [(int(entries["t"][i]) - t0) / 1e3, (int(entries["t"][j - 1]) - t0) / 1e3]}}
+        by_key.setdefault((kind, grid), []).append(len(launches))
+        launches.append(rec)
+        i = j
+    seen: Dict[tuple, int] = {}
+    for s in ks[ks["c"] != 0]:
+        key = (int(s["kind"]), int(s["b"]))
+        cta = (key, int(s["a"]), int(s["c"]))
+        n = seen.get(cta, 0)
+        seen[cta] = n + 1
+        idx = by_key.get(key)
+        if idx is None or n >= len(idx):
+            continue
+        ph = launches[idx[n]]["phases"]
+        t = (int(s["t"]) - t0) / 1e3
+        cur = ph.get(int(s["c"]))
+        if cur is None:
+            ph[int(s["c"])] = [t, t]
+        else:
+            cur[0], cur[1] = min(cur[0], t), max(cur[1], t)
+    return launches
+
+
+def format_kernel_launches(launches: List[Dict]) -> str:
+    """One line per launch: when its first CTA entered, when its CTAs got past the wait for the previous kernel, when the
+    last CTA left, and (GEMM / attention) the kernel-specific phases as first..last over the CTAs."""
+    lines = [f"{'#':>4s} {'kernel':18s} {'grid':>5s} {'enter':>9s} {'past wait':>17s} {'exit (last)':>11s} {'busy us':>8s}  other phases (first..last)"]
+    prev_exit = 0.0
+    for n, r in enumerate(launches):
+        ph = r["phases"]
+        enter = ph[0][0]
+        wait = ph.get(1)
+        ex = ph.get(9, [float("nan"), float("nan")])[1]
+        start = wait[0] if wait else enter
+        extra = "  ".join(f"p{p}:{v[0]:.1f}..{v[1]:.1f}" for p, v in sorted(ph.items()) if p not in (0, 1, 9))
+        lines.append(f"{n:4d} {r['kernel']:18s} {r['grid']:5d} {enter:9.1f} {(f'{wait[0]:.1f}..{wait[1]:.1f}' if wait else '-'):>17s} {ex:11.1f} "
+                     f"{ex - max(start, prev_exit):8.1f}  {extra}")
+        if ex == ex:
+            prev_exit = max(prev_exit, ex)
+    return "\n".join(lines)

@@ -218,12 +218,10 @@ def test_kv_block_copy(nat):
     assert torch.equal(cache, exp)
 
 
-@pytest.mark.skipif(__import__("os").environ.get("JIB_PERMUTE_MULTI", "") != "1",
-                    reason="the multi-CTA expert sort has not run on a GPU yet: set JIB_PERMUTE_MULTI=1 to try it")
 @pytest.mark.parametrize("T,k,E", [(1024, 6, 64), (2048, 8, 66), (700, 6, 160)])
 def test_moe_permute_multi_cta(nat, T, k, E):
-    """With JIB_PERMUTE_MULTI=1 batches of 4096 pairs and more take the histogram / scan / scatter kernels: same stable
-    sort by expert as the single-CTA kernel."""
+    """Batches of 4096 pairs and more take the histogram / scan / scatter kernels: same stable sort by expert as the
+    single-CTA kernel."""
     ids = torch.randint(0, E, (T, k), device="cuda", dtype=torch.int32)
     assert nat.PERMUTE_MULTI and T * k >= nat.PERMUTE_MULTI_MIN
     seg, src, dest = nat.moe_permute(ids, 0, E)
@@ -237,35 +235,75 @@ def test_moe_permute_multi_cta(nat, T, k, E):
     assert torch.equal(seg.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]))
 
 
-@pytest.mark.skipif(__import__("os").environ.get("JIB_FUSED_ROUTE", "") != "1",
-                    reason="the one-launch router has not run on a GPU yet: set JIB_FUSED_ROUTE=1 to try it")
 @pytest.mark.parametrize("T,d,E,k,n_group,topk_group,n_shared,base,E_local",
                          [(1, 2048, 64, 6, 1, 1, 2, 0, 66), (8, 2048, 64, 6, 1, 1, 2, 0, 66), (64, 2048, 64, 6, 1, 1, 0, 0, 64),
                           (8, 5120, 160, 6, 8, 3, 0, 40, 20), (33, 5120, 160, 6, 8, 3, 0, 0, 160)])
 def test_fused_route_matches_the_separate_kernels(nat, T, d, E, k, n_group, topk_group, n_shared, base, E_local):
-    """Router logits + gating + expert sort in one launch (decode batches): bitwise the ids, weights and sort of the
-    three separate launches; a second call checks that the last-CTA counter was left at zero."""
-    g = rnd(T, d)
+    """[RMSNorm +] router logits + gating + expert sort in one launch (decode batches): bitwise the ids, weights, sort
+    (and normalised rows) of the separate launches; a second call checks that the last-CTA counter was left at zero."""
+    y = rnd(T, d)
     w_router = torch.randn(E, d, device=DEV, dtype=torch.float32) * 0.05
+    w_norm = torch.rand(d, device=DEV, dtype=torch.float32) + 0.5
     assert nat.FUSED_ROUTE
-    for _ in range(2):
-        nat.FUSED_ROUTE = False
-        ids0, wts0 = nat.moe_gate(g, w_router, None, k, n_group, topk_group, 1.0, False, False, n_shared)
-        seg0, src0, dest0 = nat.moe_permute(ids0, base, E_local)
+    try:
+        for pre in (None, (w_norm, 1e-6), None):
+            nat.FUSED_ROUTE = False
+            g = y if pre is None else nat.rmsnorm(y, pre[0], pre[1])[0]
+            ids0, wts0 = nat.moe_gate(g, w_router, None, k, n_group, topk_group, 1.0, False, False, n_shared)
+            seg0, src0, dest0 = nat.moe_permute(ids0, base, E_local)
+            nat.FUSED_ROUTE = True
+            res = nat.moe_gate(y, w_router, None, k, n_group, topk_group, 1.0, False, False, n_shared, False, (base, E_local), pre)
+            ids1, wts1 = res[0], res[1]
+            seg1, src1, dest1 = nat.moe_permute(ids1, base, E_local)
+            torch.cuda.synchronize()
+            assert not nat._route_stash                       # the sort came from the fused launch
+            if pre is not None:
+                assert torch.equal(res[2], g)                 # the rows the router normalised = the norm kernel's rows
+            assert torch.equal(ids0, ids1) and torch.equal(wts0, wts1)
+            assert torch.equal(seg0, seg1) and torch.equal(dest0, dest1)
+            n_local = int(seg0[-1])
+            assert torch.equal(src0[:n_local], src1[:n_local]) and bool((src1[n_local:] == -1).all())
+            assert int(nat.workspace(y.device).route_counter.item()) == 0
+    finally:
         nat.FUSED_ROUTE = True
-        ids1, wts1 = nat.moe_gate(g, w_router, None, k, n_group, topk_group, 1.0, False, False, n_shared, False, (base, E_local))
-        seg1, src1, dest1 = nat.moe_permute(ids1, base, E_local)
+
+
+def test_gate_matches_the_fp32_reference(nat):
+    """ids of the gate kernel against the PyTorch restatement (softmax top-k, group-limited variant)."""
+    for T, d, E, k, ng, tg in ((8, 2048, 64, 6, 1, 1), (33, 5120, 160, 6, 8, 3)):
+        g = rnd(T, d)
+        w_router = torch.randn(E, d, device=DEV, dtype=torch.float32) * 0.05
+        ids, wts = nat.moe_gate(g, w_router, None, k, ng, tg, 1.0, False, False, 0)
+        ids_r, wts_r = ref.moe_gate(g, w_router, None, k, ng, tg, 1.0, False, False, 0)
+        assert torch.equal(ids.sort(-1).values, ids_r.sort(-1).values)
+        close(wts.sort(-1).values, wts_r.sort(-1).values, tol=1e-4)
+
+
+@pytest.mark.parametrize("T,E,k,F,d", [(1, 66, 8, 1408, 2048), (8, 66, 8, 1408, 2048), (33, 66, 8, 1408, 2048), (64, 20, 6, 1536, 5120),
+                                       (5, 8, 2, 128, 256)])
+def test_grouped_gateup_reads_tokens_in_place(nat, T, E, k, F, d):
+    """Decode batches: the grouped gate|up GEMM given the unsorted token rows and the sort's source index equals, bit for
+    bit, the same GEMM over rows gathered into expert order (same split of K); both track the fp32 reference."""
+    x = rnd(T, d)
+    wg, wu = rnd(E, F, d, scale=0.03), rnd(E, F, d, scale=0.03, seed=9)
+    gen = torch.Generator().manual_seed(T)
+    ids = torch.stack([torch.randperm(E, generator=gen)[:k] for _ in range(T)]).int().to(DEV)
+    seg, src, dest = nat.moe_permute(ids, 0, E)
+    active = min(E, T * k)
+    for _ in range(2):
+        h0 = nat.gemm_grouped(nat.gather_rows(x, src), seg, wg, wu, T, active)
+        h1 = nat.gemm_grouped_raw(x.data_ptr(), T * k, d, seg, wg, wu, T, active, device=x.device, src_token=src, src_rows=T)
         torch.cuda.synchronize()
-        assert not nat._route_stash                       # the sort came from the fused launch
-        assert torch.equal(ids0, ids1) and torch.equal(wts0, wts1)
-        assert torch.equal(seg0, seg1) and torch.equal(dest0, dest1)
-        n_local = int(seg0[-1])
-        assert torch.equal(src0[:n_local], src1[:n_local]) and bool((src1[n_local:] == -1).all())
-        assert int(nat.workspace(g.device).route_counter.item()) == 0
+        assert torch.equal(h0, h1)
+    flat = ids.flatten().long()
+    order = torch.sort(flat, stable=True).indices
+    xs = x.float()[order // k]
+    e_of = flat[order]
+    want = torch.nn.functional.silu(torch.einsum("rd,rfd->rf", xs, wg.float()[e_of])) * torch.einsum("rd,rfd->rf", xs, wu.float()[e_of])
+    close(h1, want, tol=3e-2)
+    nat.check_status()
 
 
-@pytest.mark.skipif(__import__("os").environ.get("JIB_FUSED_COMBINE_NORM", "") != "1",
-                    reason="the combine + norm kernel has not run on a GPU yet: set JIB_FUSED_COMBINE_NORM=1 to try it")
 @pytest.mark.parametrize("T,k,d,with_shared", [(1, 8, 2048, False), (8, 8, 2048, False), (64, 6, 2048, True), (8, 6, 5120, True),
                                                (300, 6, 5120, False), (5, 6, 512, False)])
 def test_combine_fused_with_the_next_norm(nat, T, k, d, with_shared):
@@ -288,8 +326,6 @@ def test_combine_fused_with_the_next_norm(nat, T, k, d, with_shared):
     assert (norm0 != norm1).float().mean().item() < 0.01
 
 
-@pytest.mark.skipif(__import__("os").environ.get("JITTORINFER_DEVICE_SAMPLING", "") != "1",
-                    reason="the device sampler has not run on a GPU yet: set JITTORINFER_DEVICE_SAMPLING=1 to try it")
 @pytest.mark.parametrize("k", [8, 64, 128])
 def test_device_sampler_matches_the_reference(nat, k):
     """top-k / top-p / min-p / temperature + one draw per row: the ids of the PyTorch fp32 restatement, except for draws
@@ -313,10 +349,6 @@ def test_device_sampler_matches_the_reference(nat, k):
     assert torch.equal(got[greedy], ids[greedy, 0])
 
 
-@pytest.mark.gpu
-@pytest.mark.skipif(os.environ.get("JITTORINFER_DEVICE_DEQUANT", "") != "1",
-                    reason="the device expander of block-quantised checkpoints has been cross-compiled but not yet run on a GPU; "
-                           "set JITTORINFER_DEVICE_DEQUANT=1 to try it")
 def test_device_dequantize_matches_the_host_expander():
     import numpy as np
     from jittorinfer_b200.gguf import quants as Q
