@@ -147,7 +147,7 @@ def _build_kernels_variant(define: str, suffix: str, force: bool, verbose: bool)
             o = os.path.join(objdir, os.path.basename(s) + ".o")
             objs.append(o)
             cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", *NVCC_ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
-                   "-D" + define, "-I", os.path.join(CSRC, "kernels"), "-I", os.path.join(CSRC, "include"), "-c", s, "-o", o]
+                   *["-D" + d for d in define.split(",")], "-I", os.path.join(CSRC, "kernels"), "-I", os.path.join(CSRC, "include"), "-c", s, "-o", o]
             procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         for cmd, p in procs:
             o, _ = p.communicate()
@@ -168,6 +168,12 @@ def build_kernels_timeline(force: bool = False, verbose: bool = False) -> str:
     """The kernels with -DJIB_TIMELINE (device time stamps of the collective phases, csrc/kernels/timeline.cuh) as
     libjib200_kernels_tl.so; select it with JITTORINFER_KERNELS_SO=<path> and read the stamps with parallel/timeline.py."""
     return _build_kernels_variant("JIB_TIMELINE", "tl", force, verbose)
+
+
+def build_kernels_pdl_late(force: bool = False, verbose: bool = False, timeline: bool = False) -> str:
+    """The kernels with -DJIB_PDL_LATE (csrc/kernels/pdl.cuh: dependents are released once a kernel's loads are in flight instead
+    of first thing) as libjib200_kernels_late.so, for A/B measurements; ``timeline=True`` adds the time stamps (…_late_tl.so)."""
+    return _build_kernels_variant("JIB_PDL_LATE,JIB_TIMELINE" if timeline else "JIB_PDL_LATE", "late_tl" if timeline else "late", force, verbose)
 
 
 def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[str] = ()) -> str:

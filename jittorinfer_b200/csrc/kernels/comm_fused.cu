@@ -30,7 +30,7 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 __global__ void epoch_bump_kernel(unsigned * epoch) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     *epoch += 1;
 }
@@ -39,7 +39,7 @@ __global__ void epoch_bump_kernel(unsigned * epoch) {
 template <typename TIn>
 __global__ void __launch_bounds__(128) allreduce_oneshot_kernel(const TIn * __restrict__ x, const bf16 * __restrict__ residual,
                                                                 bf16 * __restrict__ out, int T, int d, JibArCtx ar, int site) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const unsigned epoch = *ar.epoch;
     const int parity = (site + (int) (epoch % 2u) * (ar.n_sites & 1)) & 1;
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(128) allreduce_oneshot_kernel(const TIn * __re
 template <typename TIn>
 __global__ void __launch_bounds__(128) allreduce_twoshot_kernel(const TIn * __restrict__ x, const bf16 * __restrict__ residual, int T, int d,
                                                                 JibArCtx ar, int site, int rs_rows) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     const unsigned epoch = *ar.epoch;
     const int parity = (site + (int) (epoch % 2u) * (ar.n_sites & 1)) & 1;
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(128) allreduce_twoshot_kernel(const TIn * __re
 // then also waits for every source (bounded), so that the buffer is complete when the kernel ends -- without it the
 // consumer (the GEMM's TMA warp) waits per token tile on the same flags.
 __global__ void __launch_bounds__(256) allgather_push_kernel(const bf16 * __restrict__ x_loc, int R, int d, JibArCtx ar, int site, int wait) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     const unsigned epoch = *ar.epoch;
     const int par = (site >> 1) & 1;
@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const bf16 * __rest
     if (wait && (int) threadIdx.x < ar.world) {
         const unsigned * f = ar.flags3[ar.rank] + (size_t) site * ar.world + threadIdx.x;
         bool got = false;
-        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+        for (unsigned i = 0, lim = jib_ar_limit(ar); i < lim; ++i) {
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }

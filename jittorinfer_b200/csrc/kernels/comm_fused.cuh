@@ -26,6 +26,7 @@ struct JibArCtx {
     void * xg[JIB_AR_MAX_WORLD];          // [2][max_rows2][d_max] bf16 gathered rows
     unsigned * flags3[JIB_AR_MAX_WORLD];  // [n_sites][world] "rows of source s have landed" flags
     int * ag_counter;                     // this rank's block counter of the push kernel (zero between launches)
+    unsigned spin_limit;                  // polls a wait on a peer's flag may take before it gives up; 0 = JIB_AR_SPIN_LIMIT
 };
 
 #ifdef __CUDACC__
@@ -39,6 +40,7 @@ __device__ __forceinline__ unsigned jib_ld_acquire_sys(const unsigned * p) {
     return v;
 }
 __device__ __forceinline__ float4 jib_ld_cg4(const float * p) { return __ldcg((const float4 *) p); }
+__device__ __forceinline__ unsigned jib_ar_limit(const JibArCtx & ar) { return ar.spin_limit != 0 ? ar.spin_limit : JIB_AR_SPIN_LIMIT; }
 
 // Called by `nthreads` threads (a multiple of 32, named barrier 1) after they stored their partials to the peers.
 // local_tid in [0, nthreads).  Returns false if a source never signalled within the poll budget.
@@ -55,7 +57,7 @@ __device__ __forceinline__ bool jib_ar_signal_and_wait(const JibArCtx & ar, int 
     if (local_tid < ar.world) {                   // wait for source `local_tid`
         const unsigned * f = ar.flags[ar.rank] + slot + (size_t) local_tid * ar.max_tiles;
         bool got = false;
-        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+        for (unsigned i = 0, lim = jib_ar_limit(ar); i < lim; ++i) {
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }
@@ -91,7 +93,7 @@ __device__ __forceinline__ bool jib_ar2_signal_owner(const JibArCtx & ar, int si
     if (ar.rank == owner && local_tid < ar.world) {
         const unsigned * f = ar.flags[ar.rank] + slot + (size_t) local_tid * ar.max_tiles;
         bool got = false;
-        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+        for (unsigned i = 0, lim = jib_ar_limit(ar); i < lim; ++i) {
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }
@@ -123,7 +125,7 @@ __device__ __forceinline__ bool jib_ar2_deliver_and_wait(const JibArCtx & ar, in
         s_ok3 = 1;
         const unsigned * f = ar.flags2[ar.rank] + slot;
         bool got = false;
-        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+        for (unsigned i = 0, lim = jib_ar_limit(ar); i < lim; ++i) {
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }

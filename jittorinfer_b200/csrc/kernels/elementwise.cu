@@ -46,7 +46,7 @@ __device__ __forceinline__ float block_sum(float v, float * red) {
 __global__ void embed_gather_kernel(const bf16 * __restrict__ table, const int * __restrict__ ids, bf16 * __restrict__ out, int d,
                                     int n_vocab) {
     JIB_KS(6, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(6, 1);
     const int t = blockIdx.x;
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x
                                                      const float * __restrict__ w, bf16 * __restrict__ out_norm,
                                                      bf16 * __restrict__ out_sum, int d, long long x_stride, float eps) {
     JIB_KS(4, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(4, 1);
     __shared__ float red[32];
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(NT) mla_qkv_post_kernel(const bf16 * __restric
                                                           bf16 * __restrict__ q_out, int H, int dn, int dr, int r, int max_pos,
                                                           long long n_slots, int * status) {
     JIB_KS(5, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(5, 1);
     __shared__ float red[32];
@@ -181,7 +181,7 @@ __device__ __forceinline__ uint32_t f2key(float f) {   // order-preserving float
 template <int NT>
 __global__ void __launch_bounds__(NT) argmax_kernel(const float * __restrict__ logits, int * __restrict__ out, int V) {
     JIB_KS(8, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(8, 1);
     __shared__ unsigned long long best_s[NT / 32];
@@ -219,7 +219,7 @@ template <int NT>
 __global__ void __launch_bounds__(NT) topk_kernel(const float * __restrict__ logits, float * __restrict__ vals, int * __restrict__ ids,
                                                   int V, int k) {
     JIB_KS(15, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(15, 1);
     __shared__ int hist[2048];
@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(NT) topk_kernel(const float * __restrict__ log
 
 __global__ void kv_block_copy_kernel(bf16 * cache, long long layer_stride, const int * __restrict__ src, const int * __restrict__ dst,
                                      int block_elems) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     const int i = blockIdx.x, l = blockIdx.y;
     const uint4 * s = (const uint4 *) (cache + (size_t) l * layer_stride + (size_t) src[i] * block_elems);
@@ -311,7 +311,7 @@ __global__ void kv_block_copy_kernel(bf16 * cache, long long layer_stride, const
 
 __global__ void gather_rows_kernel(const bf16 * __restrict__ x, const int * __restrict__ src_row, bf16 * __restrict__ out, int d, int n_src) {
     JIB_KS(7, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(7, 1);
     const int rrow = blockIdx.x;

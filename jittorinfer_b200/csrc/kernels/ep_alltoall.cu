@@ -53,7 +53,7 @@ __device__ bool ep_signal_and_wait(const JibEpCtx & c, int site, int phase, unsi
         if (do_signal) jib_st_release_sys(ep_flag(c, (int) threadIdx.x, site, phase, c.rank), epoch);
         const unsigned * f = ep_flag(c, c.rank, site, phase, (int) threadIdx.x);
         bool got = false;
-        for (unsigned i = 0; i < JIB_AR_SPIN_LIMIT; ++i) {
+        for (unsigned i = 0, lim = c.spin_limit != 0 ? c.spin_limit : JIB_AR_SPIN_LIMIT; i < lim; ++i) {
             if (jib_ld_acquire_sys(f) == epoch) { got = true; break; }
             __nanosleep(40);
         }
@@ -75,7 +75,7 @@ __device__ bool ep_signal_and_wait(const JibEpCtx & c, int site, int phase, unsi
 // experts in my receive buffer; pair_dst [n] = owner rank << 27 | row in the owner's buffer (-1: dropped, buffer full).
 __global__ void __launch_bounds__(1024) ep_plan_kernel(const int * __restrict__ ids, int n, JibEpCtx c, int site, int * __restrict__ seg,
                                                       int * __restrict__ pair_dst) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     __shared__ int cnt[EP_MAX_E];                 // my pairs per global expert
     __shared__ int base[EP_MAX_E];                // first row of my pairs for expert e in its owner's buffer
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int * __restrict__ 
 __global__ void __launch_bounds__(256) ep_push_kernel(const bf16 * __restrict__ x, const int * __restrict__ pair_dst, int n, int k,
                                                      JibEpCtx c, int site, const int * __restrict__ seg, int * done_counter,
                                                      unsigned long long * __restrict__ row_ptr) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     const unsigned epoch = *c.epoch;
     const int par = ep_parity(c, site, epoch);
@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const bf16 * __restrict__ 
 __global__ void __launch_bounds__(256) ep_combine_kernel(const float * __restrict__ wts, const int * __restrict__ pair_dst,
                                                         const bf16 * __restrict__ shared, const bf16 * __restrict__ residual,
                                                         bf16 * __restrict__ out, int T, int k, JibEpCtx c, int site) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     const unsigned epoch = *c.epoch;
     const int par = ep_parity(c, site, epoch);

@@ -14,6 +14,7 @@ struct JibEpCtx {
     unsigned * epoch;                          // this rank's step counter
     int * status;                              // this rank's status words (code, site, block, extra)
     int world, rank, n_sites, E_local, d, max_recv_rows, max_pairs;
+    unsigned spin_limit;                       // polls a wait on a peer's flag may take; 0 = JIB_AR_SPIN_LIMIT
 };
 
 #ifdef __CUDACC__

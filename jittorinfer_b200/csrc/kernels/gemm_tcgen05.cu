@@ -60,9 +60,12 @@ struct GemmArgs {
     const unsigned * ag_flags;
     const unsigned * ag_epoch;
     int ag_rows, ag_world;    // rows per source rank, number of ranks
+    unsigned ag_spin_limit;   // polls of the wait for a source's rows (0 = JIB_AR_SPIN_LIMIT)
     int ar_rs_rows;           // two-shot: > 0 delivers each reduced row only to rank row / ar_rs_rows (reduce-scatter)
     void * const * row_ptr;   // null, or per output row the address of its bf16 row (rows scattered to other buffers,
                               // possibly on other GPUs: the expert-parallel return path)
+    int w_evict_first;        // weight tiles are loaded with the L2 evict_first policy (each is read once: small batches)
+    int vec_store;            // bf16 result rows are written as 16-byte vectors through a shared-memory transpose
     const int * src_token;    // grouped, decode batches: x holds the T token rows unsorted, every expert multiplies all of
                               // them (one token tile) and sorted row i of the result is accumulator column src_token[i]
 };
@@ -168,7 +171,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int rows_valid = args.T;         // rows of this batch's matrix
     int row_base = 0;                // grouped: offset of the expert's segment in the sorted rows
     JIB_KS(1, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     if (args.seg != nullptr) {
         pdl_wait();                  // segment offsets are produced by the routing kernels just before
         row_base = args.seg[batch];
@@ -220,6 +223,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // Weights are launch-invariant: their tiles of the first ring pass are requested BEFORE the wait for the
             // previous kernel, so the HBM latency of the stream's head overlaps that kernel's tail.  The activation
             // tile of each stage follows after the wait and completes the same barrier phase.
+            const uint64_t wpol = l2_policy_evict_first();
+            const bool wfirst = args.w_evict_first != 0;
             int pre = 0;
             if (early && args.ag_flags == nullptr) {
                 pre = min(nkb, C::STAGES);
@@ -227,8 +232,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     uint8_t * st = tiles + i * C::STAGE_BYTES;
                     mbar_expect_tx(&full[i], C::STAGE_BYTES);
                     const int k = (kb0 + i) * BK;
-                    tma_load_3d(st, &tmA, &full[i], k, n0, a_z);
-                    if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[i], k, n0, a_z);
+                    if (wfirst) {
+                        tma_load_3d_hint(st, &tmA, &full[i], k, n0, a_z, wpol);
+                        if (DUAL) tma_load_3d_hint(st + C::A_BYTES, &tmA2, &full[i], k, n0, a_z, wpol);
+                    } else {
+                        tma_load_3d(st, &tmA, &full[i], k, n0, a_z);
+                        if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[i], k, n0, a_z);
+                    }
                 }
             }
             if (early) pdl_wait();
@@ -241,7 +251,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 const int hi = min((int) ((row_base + row0 + BN - 1) / args.ag_rows), args.ag_world - 1);
                 for (int src = lo; src <= hi; ++src) {
                     bool got = false;
-                    for (unsigned it = 0; it < JIB_AR_SPIN_LIMIT; ++it) {
+                    for (unsigned it = 0, lim = args.ag_spin_limit != 0 ? args.ag_spin_limit : JIB_AR_SPIN_LIMIT; it < lim; ++it) {
                         if (jib_ld_acquire_sys(args.ag_flags + src) == want) { got = true; break; }
                         __nanosleep(40);
                     }
@@ -257,12 +267,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (i >= pre) {
                     if (!mbar_wait(&empty[s], ph ^ 1)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 1, i); break; }
                     mbar_expect_tx(&full[s], C::STAGE_BYTES);
-                    tma_load_3d(st, &tmA, &full[s], k, n0, a_z);
-                    if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[s], k, n0, a_z);
+                    if (wfirst) {
+                        tma_load_3d_hint(st, &tmA, &full[s], k, n0, a_z, wpol);
+                        if (DUAL) tma_load_3d_hint(st + C::A_BYTES, &tmA2, &full[s], k, n0, a_z, wpol);
+                    } else {
+                        tma_load_3d(st, &tmA, &full[s], k, n0, a_z);
+                        if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[s], k, n0, a_z);
+                    }
                 }
                 tma_load_3d(st + (DUAL ? 2 : 1) * C::A_BYTES, &tmB, &full[s], k, b_row, b_z);
             }
             JIB_KS_ANY(1, 2);
+            PDL_TRIGGER_LATE();      // every load of this CTA is in flight: the next kernel may start its own
         } else if (early) {
             pdl_wait();
         }
@@ -503,7 +519,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         }
                     }
                 }
-                if (n < args.N) {
+                if (args.vec_store) {
+                    // The accumulators hold [feature lane][token column]; the result is [token][feature].  Transpose 16 token
+                    // columns through shared memory (fp32, two buffers in the idle pipeline area) so that a thread stores 8
+                    // adjacent features of one token row as one 16-byte vector (residual added in fp32 before rounding).
+                    const int ltid = (int) threadIdx.x - 64;
+                    float * sb = stage + ((c >> 4) & 1) * (16 * BM);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sb[j * BM + r] = DUAL ? silu(g[j]) * u[j] : g[j];
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 1
+                    for (int it = 0; it < 2; ++it) {
+                        const int tok = (ltid >> 4) + it * 8, fg = (ltid & 15) * 8;
+                        const int col = c + tok, nn = n0 + fg;
+                        if (col >= ncols || nn >= args.N) continue;
+                        const long long row = row_base + row0 + col;
+                        if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 5, (int) row); continue; }
+                        float4 a = *(const float4 *) (sb + tok * BM + fg), b = *(const float4 *) (sb + tok * BM + fg + 4);
+                        if (args.residual != nullptr) {
+                            const long long ri = rbase + row * args.ldr + nn;
+                            if (args.res_f32) {
+                                const float4 ra = *(const float4 *) ((const float *) args.residual + ri);
+                                const float4 rb = *(const float4 *) ((const float *) args.residual + ri + 4);
+                                a.x += ra.x; a.y += ra.y; a.z += ra.z; a.w += ra.w;
+                                b.x += rb.x; b.y += rb.y; b.z += rb.z; b.w += rb.w;
+                            } else {
+                                const uint4 raw = *(const uint4 *) ((const __nv_bfloat16 *) args.residual + ri);
+                                const float2 r0 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                                const float2 r1 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                                const float2 r2 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.z);
+                                const float2 r3 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.w);
+                                a.x += r0.x; a.y += r0.y; a.z += r1.x; a.w += r1.y;
+                                b.x += r2.x; b.y += r2.y; b.z += r3.x; b.w += r3.y;
+                            }
+                        }
+                        const uint2 lo = pack_bf16x4(a), hi = pack_bf16x4(b);
+                        __nv_bfloat16 * dst = args.row_ptr != nullptr
+                                                  ? (__nv_bfloat16 *) __ldg((const unsigned long long *) args.row_ptr + row)
+                                                  : (__nv_bfloat16 *) args.out + obase + row * args.ldo;
+                        if (dst != nullptr) *(uint4 *) (dst + nn) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                    }
+                } else if (n < args.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         if (c + j >= ncols) break;
@@ -633,6 +689,40 @@ bool jib_no_cluster() {
     return off;
 }
 
+// JIB_SPLIT_SMALL=1: split-K also for tiles of 8 k-blocks and fewer (A/B measurements).
+bool jib_split_small() {
+    static const bool on = [] {
+        const char * e = getenv("JIB_SPLIT_SMALL");
+        return e != nullptr && e[0] == '1';
+    }();
+    return on;
+}
+
+// JIB_EVICT_FIRST=0: weight loads use the default L2 policy (A/B measurements).
+bool jib_no_evict_first() {
+    static const bool off = [] {
+        const char * e = getenv("JIB_EVICT_FIRST");
+        return e != nullptr && e[0] == '0';
+    }();
+    return off;
+}
+
+// Automatic split-K count: fill the machine when there are too few output tiles.  base_ctas: CTAs without a split;
+// one wave holds sms CTAs (twice that for the narrow token tiles, which share an SM in pairs).
+int auto_splits(long long base_ctas, int num_kb, int bn, int sms) {
+    int splits = 1;
+    const int slots = sms * (bn <= 32 ? 2 : 1);
+    if (2 * base_ctas <= slots) {
+        splits = (int) (slots / base_ctas);
+        if (splits > num_kb / 4) splits = num_kb / 4;      // at least 4 k-blocks (256 K) per split
+        // a split costs ~3 us (partials parked, cluster barrier, remote reads); one CTA streams ~64 KB of weights per
+        // microsecond, so tiles of up to 8 k-blocks (128 KB single, 256 KB gate|up) are quicker unsplit
+        if (num_kb <= 8 && !jib_split_small()) splits = 1;
+        if (splits < 1) splits = 1;
+    }
+    return splits;
+}
+
 template <int BN, bool DUAL>
 int launch(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b, const GemmArgs & args, dim3 grid,
            cudaStream_t stream) {
@@ -670,16 +760,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     // split-K: fill the machine when there are too few output tiles
     int splits = d->splits;
     const long long base_ctas = (long long) n_tiles * t_tiles * (grouped ? (d->active_hint > 0 ? d->active_hint : batch) : batch);
-    if (splits <= 0) {
-        splits = 1;
-        const int sms = d->sm_count > 0 ? d->sm_count : 148;
-        const int slots = sms * (bn <= 32 ? 2 : 1);             // CTAs resident at once (one wave)
-        if (2 * base_ctas <= slots && d->scratch != nullptr) {
-            splits = (int) (slots / base_ctas);
-            if (splits > num_kb / 4) splits = num_kb / 4;      // at least 4 k-blocks (256 K) per split
-            if (splits < 1) splits = 1;
-        }
-    }
+    if (splits <= 0) splits = d->scratch != nullptr ? auto_splits(base_ctas, num_kb, bn, d->sm_count > 0 ? d->sm_count : 148) : 1;
     // Two ways to add the splits up: inside a thread-block cluster through distributed shared memory (at most 8 CTAs,
     // cheap reduction) or through a global scratch with a last-arriver reduction (any count).  Measured per decode GEMM
     // on B200: with few tiles (qkv_a 17-29, q_b 24, shared / dense down 16) the cluster wins by 0.5-2.7 us; with 40
@@ -727,8 +808,16 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     a.cluster_split = cluster_split ? 1 : 0;
     a.row_ptr = (void * const *) d->out_row_ptr;
     a.src_token = d->src_token;
+    a.w_evict_first = (t_tiles == 1 && !jib_no_evict_first()) ? 1 : 0;      // one token tile: every weight byte is used once
+    // 16-byte result stores: bf16 rows whose feature offsets keep 16-byte alignment (row pointers of the expert-parallel return
+    // path are row starts of bf16 matrices with d % 8 == 0, hence aligned as well)
+    a.vec_store = (!d->out_f32 && d->ar == nullptr && d->N % 8 == 0 && d->ldo % 8 == 0 && d->out_batch_stride % 8 == 0 &&
+                   ((uintptr_t) d->out & 15) == 0 &&
+                   (d->residual == nullptr || (((uintptr_t) d->residual & 15) == 0 && d->ldr % 8 == 0 && d->res_batch_stride % 8 == 0)))
+                      ? 1 : 0;
     a.ag_flags = (const unsigned *) d->ag_flags; a.ag_epoch = (const unsigned *) d->ag_epoch;
     a.ag_rows = d->ag_rows; a.ag_world = d->ag_world; a.ar_rs_rows = d->ar_rs_rows;
+    a.ag_spin_limit = d->ar != nullptr ? ((const JibArCtx *) d->ar)->spin_limit : 0;
     if (a.ag_flags != nullptr && (a.ag_epoch == nullptr || a.ag_rows <= 0 || a.ag_world <= 0 || grouped || batch != 1)) return JIB_E_ARG;
     if (a.ar_rs_rows < 0) return JIB_E_ARG;
     if (a.row_ptr != nullptr && (dual || d->out_f32 || d->residual != nullptr || d->ar != nullptr)) return JIB_E_ARG;
@@ -778,10 +867,11 @@ namespace {
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
 unsigned char * g_noalloc_base[NOALLOC_MAX_DEVICES] = {nullptr};
+int g_noalloc_sms[NOALLOC_MAX_DEVICES] = {0};
 std::mutex g_noalloc_mu;
 
-// Device address of the built-in scratch for the current device; looked up on first use.
-int noalloc_base(unsigned char ** out) {
+// Device address of the built-in scratch for the current device and that device's SM count; looked up on first use.
+int noalloc_base(unsigned char ** out, int * sms) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return JIB_E_ARG;
     std::lock_guard<std::mutex> g(g_noalloc_mu);
@@ -789,9 +879,13 @@ int noalloc_base(unsigned char ** out) {
         void * p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&p, jib_noalloc_scratch);
         if (e != cudaSuccess || p == nullptr) return JIB_E_DRIVER;
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return JIB_E_DRIVER;
+        g_noalloc_sms[dev] = n;
         g_noalloc_base[dev] = (unsigned char *) p;
     }
     *out = g_noalloc_base[dev];
+    if (sms != nullptr) *sms = g_noalloc_sms[dev];
     return 0;
 }
 
@@ -800,21 +894,13 @@ struct NoallocPlan {
     size_t need;
 };
 
-NoallocPlan noalloc_plan(int T, int N, int K, int splits) {
+NoallocPlan noalloc_plan(int T, int N, int K, int splits, int sms) {
     NoallocPlan p;
     p.bn = 16;
     while (p.bn < T && p.bn < 256) p.bn *= 2;
     p.n_tiles = (N + BM - 1) / BM;
     p.num_kb = (K + BK - 1) / BK;
-    if (splits <= 0) {                       // same rule as jib_gemm_bf16 for a 148-SM part
-        splits = 1;
-        const int slots = 148 * (p.bn <= 32 ? 2 : 1);
-        if (2 * p.n_tiles <= slots) {
-            splits = slots / p.n_tiles;
-            if (splits > p.num_kb / 4) splits = p.num_kb / 4;
-            if (splits < 1) splits = 1;
-        }
-    }
+    if (splits <= 0) splits = auto_splits(p.n_tiles, p.num_kb, p.bn, sms);      // the rule jib_gemm_bf16 applies
     if (splits > p.num_kb) splits = p.num_kb;
     p.kbps = (p.num_kb + splits - 1) / splits;
     p.splits = (p.num_kb + p.kbps - 1) / p.kbps;
@@ -841,7 +927,24 @@ int encode_plain(CUtensorMap * out, const void * ptr, long long rows, long long 
 
 extern "C" JIB_EXPORT size_t jib_gemm_bf16_noalloc_need(int T, int N, int K, int splits) {
     if (T <= 0 || N <= 0 || K <= 0) return 0;
-    return noalloc_plan(T, N, K, splits).need;
+    int sms = 148;                           // splits == 0 depends on the SM count of the current device
+    if (splits <= 0) {
+        unsigned char * base = nullptr;
+        if (noalloc_base(&base, &sms) != 0) sms = 148;
+    }
+    return noalloc_plan(T, N, K, splits, sms).need;
+}
+
+// Copies the four status words of the most recent jib_gemm_bf16_noalloc call on the current device into out (host memory,
+// ideally pinned), in stream order behind that call; allocates nothing.  out[0] != 0 after the stream has been
+// synchronised means the kernel recorded a fault (1 = a bounded wait ran out, 2 = an index out of range; out[1] = site).
+extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc_status(int * out, void * stream_) {
+    if (out == nullptr) return JIB_E_ARG;
+    unsigned char * base = nullptr;
+    const int rc = noalloc_base(&base, nullptr);
+    if (rc) return rc;
+    const int * status = (const int *) (base + JIB_NOALLOC_SCRATCH_BYTES) + JIB_NOALLOC_MAX_TILES;
+    return cudaMemcpyAsync(out, status, 4 * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t) stream_) == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 
 extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, void * out, int T, int N, int K, int splits,
@@ -849,11 +952,12 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     cudaStream_t stream = (cudaStream_t) stream_;
     if (T <= 0 || N <= 0 || K <= 0) return 0;
     if (T > 256 || x == nullptr || w == nullptr || out == nullptr) return JIB_E_ARG;
-    const NoallocPlan p = noalloc_plan(T, N, K, splits);
-    if (p.need > JIB_NOALLOC_SCRATCH_BYTES || p.n_tiles > JIB_NOALLOC_MAX_TILES) return JIB_E_NOALLOC_TOO_LARGE;
     unsigned char * base = nullptr;
-    int rc = noalloc_base(&base);            // first call on this device: symbol lookup (keep it outside stream capture)
+    int sms = 148;
+    int rc = noalloc_base(&base, &sms);      // first call on this device: symbol lookup (keep it outside stream capture)
     if (rc) return rc;
+    const NoallocPlan p = noalloc_plan(T, N, K, splits, sms);
+    if (p.need > JIB_NOALLOC_SCRATCH_BYTES || p.n_tiles > JIB_NOALLOC_MAX_TILES) return JIB_E_NOALLOC_TOO_LARGE;
     int * counters = (int *) (base + JIB_NOALLOC_SCRATCH_BYTES);
     int * status = counters + JIB_NOALLOC_MAX_TILES;
     // the array keeps whatever the previous call left: counters (and the status words) must start at zero
@@ -874,7 +978,9 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.cluster_split = 0;
     a.row_ptr = nullptr;
     a.src_token = nullptr;
-    a.ag_flags = nullptr; a.ag_epoch = nullptr; a.ag_rows = 0; a.ag_world = 0; a.ar_rs_rows = 0;
+    a.vec_store = 0;
+    a.w_evict_first = 0;
+    a.ag_flags = nullptr; a.ag_epoch = nullptr; a.ag_rows = 0; a.ag_world = 0; a.ar_rs_rows = 0; a.ag_spin_limit = 0;
     memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);
     switch (p.bn) {

@@ -19,8 +19,16 @@
 // Limits and errors.  The partial sums need
 //     ceil(N/128) * splits * max(16, pow2ceil(T)) * 128 * 4 bytes  <=  JIB_NOALLOC_SCRATCH_BYTES
 // and ceil(N/128) <= JIB_NOALLOC_MAX_TILES.  A call beyond either limit returns
-// JIB_E_NOALLOC_TOO_LARGE and launches nothing.  Other failures return the JIB_E_* codes of
-// jib_kernels.h.  Pointers must be 16-byte aligned and K a multiple of 8.
+// JIB_E_NOALLOC_TOO_LARGE and launches nothing.  Other failures the host can see (bad arguments,
+// alignment, a refused launch) return the JIB_E_* codes of jib_kernels.h.  Pointers must be 16-byte
+// aligned and K a multiple of 8.  With splits = 0 the count follows the SM count of the current
+// device (queried once per device), by the same rule as jib_gemm_bf16.
+//
+// Faults found on the device.  The kernel's waits are bounded and its scratch indices checked; when
+// a wait runs out or an index is out of range it records a code in four status words inside the
+// built-in array and finishes normally, so the return value of the launch cannot show it.  Each
+// call clears those words; read them with jib_gemm_bf16_noalloc_status() after the call (same
+// stream) and before the next call on that device.
 //
 // First call.  The first call on each device looks up the device address of the built-in array
 // (with that device current) and remembers it; make that first call outside any stream capture.
@@ -46,6 +54,10 @@ JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, void * out,
 
 // Bytes of partial-sum scratch a call with these sizes needs (for callers that want to check first).
 JIB_EXPORT size_t jib_gemm_bf16_noalloc_need(int T, int N, int K, int splits);
+
+// Copies the status words {code, site, block, extra} of the last call on the current device to out[4] (host memory) in
+// stream order; code 0 = no fault, 1 = a bounded wait ran out, 2 = an index was out of range.  Allocates nothing.
+JIB_EXPORT int jib_gemm_bf16_noalloc_status(int * out, void * stream);
 
 #ifdef __cplusplus
 }

@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(NT) mla_attn_split_kernel(const bf16 * __restr
                                                             const int * __restrict__ seq_lens, const int * __restrict__ q_start, int n_seqs,
                                                             int H, int block_size, float scale, int n_splits, float * __restrict__ part_o,
                                                             float * __restrict__ part_ml, bf16 * __restrict__ o_lat) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     constexpr int D = R + DR;              // 576
     constexpr int ROWB = D * 2 + 16;       // padded smem row (bytes): conflict-free 16-byte reads across rows
@@ -177,7 +177,7 @@ template <int R>
 __global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_ml, int n_splits, int H,
                                         bf16 * __restrict__ o_lat) {
     JIB_KS(3, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(3, 1);
     // n_splits <= 32: warp 0 turns the (m, l) pairs into normalised weights, then every thread sums its

@@ -139,7 +139,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int p = 0; p < n_pass; ++p) total_tiles += pass_k1[p] > pass_k0[p] ? (pass_k1[p] - pass_k0[p] + KV_TILE - 1) / KV_TILE : 0;
 
     JIB_KS(2, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     if (total_tiles == 0) {
         pdl_wait();
         // nothing visible for this (group, split): publish an empty partial / zero output and leave
@@ -223,6 +223,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
                 }
             }
+            PDL_TRIGGER_LATE();      // every load of this CTA is in flight
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================

@@ -142,7 +142,7 @@ __device__ __forceinline__ void router_rows(const bf16 * __restrict__ x, const f
 __global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
                                                                 float * __restrict__ logits, int T, int d, int E) {
     JIB_KS(9, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(9, 1);
     __shared__ float red[GATE_NT / 32][GATE_TG];
@@ -152,14 +152,18 @@ __global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __r
 }
 
 // Gating of one token by one warp: softmax/sigmoid over the logits, optional group-limited masking, k rounds of arg-max.
-// prob / sel: MAX_E floats each, gscore: 32 floats, all private to the warp.
-__device__ __forceinline__ void gate_token(const float * __restrict__ logits_row, const float * __restrict__ bias, int * __restrict__ ids,
+// prob / sel: MAX_E floats each, gscore: 32 floats, all private to the warp.  Not inlined: the fused router calls it twice
+// (a dry run, then the real one) and both calls must execute the same copy of the code.
+__device__ __noinline__ void gate_token(const float * __restrict__ logits_row, const float * __restrict__ bias, int * __restrict__ ids,
                                            float * __restrict__ wts, int t, int E, int k, int n_group, int topk_group, float scale,
                                            int norm, int sigmoid, int n_shared, int group_top2, float * prob, float * sel,
-                                           float * gscore, int * ids_copy = nullptr) {
+                                           float * gscore, int * ids_copy = nullptr, bool dry = false) {
+    // dry: runs the same instructions on whatever `prob` holds and stores nothing -- a caller that is still waiting for its
+    // inputs uses it to pull this code into the SM's instruction cache ahead of the real call
     const int lane = threadIdx.x & 31;
     const int ld = k + n_shared;
-    for (int e = lane; e < E; e += 32) prob[e] = __ldcg(logits_row + e);      // possibly written by other CTAs: from L2
+    if (!dry)
+        for (int e = lane; e < E; e += 32) prob[e] = __ldcg(logits_row + e);      // possibly written by other CTAs: from L2
     __syncwarp();
     // softmax / sigmoid over E (E <= 256 -> 8 per lane)
     float mx = -FLT_MAX;
@@ -227,13 +231,17 @@ __device__ __forceinline__ void gate_token(const float * __restrict__ logits_row
     if (lane < k) {
         float w = my_w;
         if (norm) w /= wsum;
-        ids[(size_t) t * ld + lane] = my_id;
-        wts[(size_t) t * ld + lane] = w * scale;
+        if (!dry) {
+            ids[(size_t) t * ld + lane] = my_id;
+            wts[(size_t) t * ld + lane] = w * scale;
+        }
         if (ids_copy != nullptr) ids_copy[t * ld + lane] = my_id;
     } else if (lane < ld) {
         // shared experts ride along as always-selected experts E, E+1, ... with weight 1
-        ids[(size_t) t * ld + lane] = E + (lane - k);
-        wts[(size_t) t * ld + lane] = 1.f;
+        if (!dry) {
+            ids[(size_t) t * ld + lane] = E + (lane - k);
+            wts[(size_t) t * ld + lane] = 1.f;
+        }
         if (ids_copy != nullptr) ids_copy[t * ld + lane] = E + (lane - k);
     }
 }
@@ -244,7 +252,7 @@ __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__
                                                       int topk_group, float scale, int norm, int sigmoid, int n_shared,
                                                       int group_top2) {
     JIB_KS(10, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(10, 1);
     __shared__ float prob[MAX_E];
@@ -261,8 +269,10 @@ __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__
 // Every warp walks the id list twice per expert it owns, so `ids` should sit in shared memory (SORT_SMEM_MAX ids fit the
 // callers' staging buffers); a global pointer works too, at an L2 round trip per 32 ids.
 constexpr int SORT_SMEM_MAX = 4096;
-__device__ __forceinline__ void sort_pairs(const int * __restrict__ ids, int n, int k, int expert_base, int E_local, int * __restrict__ seg,
-                                           int * __restrict__ src_token, int * __restrict__ dest, int * count, int * offs) {
+__device__ __noinline__ void sort_pairs(const int * __restrict__ ids, int n, int k, int expert_base, int E_local, int * __restrict__ seg,
+                                           int * __restrict__ src_token, int * __restrict__ dest, int * count, int * offs,
+                                           bool dry = false) {
+    // dry: same instructions, no global stores (instruction-cache warm-up, see gate_token)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int e = warp; e < E_local; e += nw) {
         int c = 0;
@@ -292,11 +302,13 @@ __device__ __forceinline__ void sort_pairs(const int * __restrict__ ids, int n, 
         if (lane == 0) offs[E_local] = run;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e <= E_local; e += blockDim.x) seg[e] = offs[e];
-    for (int i = offs[E_local] + threadIdx.x; i < n; i += blockDim.x) src_token[i] = -1;   // rows no local expert owns
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int le = ids[i] - expert_base;
-        if (le < 0 || le >= E_local) dest[i] = -1;
+    if (!dry) {
+        for (int e = threadIdx.x; e <= E_local; e += blockDim.x) seg[e] = offs[e];
+        for (int i = offs[E_local] + threadIdx.x; i < n; i += blockDim.x) src_token[i] = -1;   // rows no local expert owns
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const int le = ids[i] - expert_base;
+            if (le < 0 || le >= E_local) dest[i] = -1;
+        }
     }
     for (int e = warp; e < E_local; e += nw) {
         int base = offs[e];
@@ -304,7 +316,7 @@ __device__ __forceinline__ void sort_pairs(const int * __restrict__ ids, int n, 
             const int i = i0 + lane;
             const bool hit = i < n && ids[i] - expert_base == e;
             const unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
+            if (hit && !dry) {
                 const int row = base + __popc(m & ((1u << lane) - 1));
                 dest[i] = row;
                 if (row < n) src_token[row] = i / k;
@@ -317,7 +329,7 @@ __device__ __forceinline__ void sort_pairs(const int * __restrict__ ids, int n, 
 __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
                                                           int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest) {
     JIB_KS(11, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(11, 1);
     __shared__ int count[MAX_E + 1];
@@ -337,7 +349,7 @@ constexpr int PERM_CHUNK = 1024;
 
 __global__ void __launch_bounds__(PERM_CHUNK) permute_count_kernel(const int * __restrict__ ids, int n, int expert_base, int E_local,
                                                                    int * __restrict__ tmp) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     __shared__ int hist[MAX_E];
     for (int e = threadIdx.x; e < E_local; e += blockDim.x) hist[e] = 0;
@@ -354,7 +366,7 @@ __global__ void __launch_bounds__(PERM_CHUNK) permute_count_kernel(const int * _
 // One CTA: tmp[c][e] becomes the first sorted row of chunk c's pairs of expert e; seg[e] the expert's first row.
 __global__ void __launch_bounds__(MAX_E) permute_scan_kernel(int * __restrict__ tmp, int n_chunks, int E_local, int n, int * __restrict__ seg,
                                                             int * __restrict__ src_token) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     __shared__ int total[MAX_E + 1];
     const int e = threadIdx.x;
@@ -385,7 +397,7 @@ __global__ void __launch_bounds__(MAX_E) permute_scan_kernel(int * __restrict__ 
 __global__ void __launch_bounds__(PERM_CHUNK) permute_scatter_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
                                                                      const int * __restrict__ tmp, int * __restrict__ src_token,
                                                                      int * __restrict__ dest) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();
     extern __shared__ int warp_cnt[];              // [32 warps][E_local]: pairs of expert e in warp w, then their prefix over w
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -431,16 +443,35 @@ __global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * _
                                                                   int * __restrict__ counter, int T, int d, int E, int k, int n_group,
                                                                   int topk_group, float scale, int norm, int sigmoid, int n_shared,
                                                                   int group_top2, int expert_base, int E_local,
-                                                                  const float * __restrict__ norm_w, float eps, bf16 * __restrict__ g_out) {
+                                                                  const float * __restrict__ norm_w, float eps, bf16 * __restrict__ g_out,
+                                                                  int warm) {
     JIB_KS(14, 0);
-    pdl_launch_dependents();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(14, 1);
+    PDL_TRIGGER_TOP();
     __shared__ float red[GATE_NT / 32][GATE_TG];
     __shared__ float inv_s[GATE_TG];
     __shared__ int s_last;
+    __shared__ float prob_s[GATE_NT / 32][MAX_E];
+    __shared__ float sel_s[GATE_NT / 32][MAX_E];
+    __shared__ float gscore_s[GATE_NT / 32][32];
+    __shared__ int ids_s[ROUTE_MAX_T * 32];      // k + n_shared <= 32 columns
+    __shared__ int count[MAX_E + 1];
+    __shared__ int offs[MAX_E + 1];
     const int warp = threadIdx.x >> 5;
+    if (warm) {
+        // While the previous kernel is still running: walk the gating and sorting code once on scratch values, storing
+        // nothing, so that whichever CTA turns out to be last finds that code in its SM's instruction cache.
+        for (int e = threadIdx.x & 31; e < MAX_E; e += 32) prob_s[warp][e] = (float) ((e * 37 + warp) & 63);
+        __syncwarp();
+        gate_token(nullptr, bias == nullptr ? nullptr : (const float *) prob_s[warp], nullptr, nullptr, 0, E, k, n_group, topk_group, scale,
+                   norm, sigmoid, n_shared, group_top2, prob_s[warp], sel_s[warp], gscore_s[warp], ids_s, true);
+        __syncthreads();
+        sort_pairs(ids_s, k + n_shared, k + n_shared, expert_base, E_local, nullptr, nullptr, nullptr, count, offs, true);
+        __syncthreads();
+    }
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(14, 1);
     router_rows(g, w_router, norm_w, eps, g_out, logits, 0, T, T, d, E, blockIdx.x, red, inv_s);
+    JIB_KS(14, 2);
     // ---- last CTA to finish carries on ----
     __threadfence();
     __syncthreads();
@@ -449,20 +480,16 @@ __global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * _
     if (!s_last) return;
     if (threadIdx.x == 0) *counter = 0;      // ready for the next launch
     __threadfence();
+    JIB_KS(14, 3);
 
     // ---- gating: warp w takes tokens w, w + 8, ... ----
-    __shared__ float prob_s[GATE_NT / 32][MAX_E];
-    __shared__ float sel_s[GATE_NT / 32][MAX_E];
-    __shared__ float gscore_s[GATE_NT / 32][32];
-    __shared__ int ids_s[ROUTE_MAX_T * 32];      // k + n_shared <= 32 columns
     for (int t = warp; t < T; t += GATE_NT / 32) {
         gate_token(logits + (size_t) t * E, bias, ids, wts, t, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2,
                    prob_s[warp], sel_s[warp], gscore_s[warp], ids_s);
         __syncwarp();
     }
     __syncthreads();         // ids of all tokens are in shared memory
-    __shared__ int count[MAX_E + 1];
-    __shared__ int offs[MAX_E + 1];
+    JIB_KS(14, 4);
     sort_pairs(ids_s, T * (k + n_shared), k + n_shared, expert_base, E_local, seg, src_token, dest, count, offs);
     JIB_KS(14, 9);
 }
@@ -472,7 +499,7 @@ __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __re
                                    const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
                                    int d) {
     JIB_KS(12, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(12, 1);
     const int t = blockIdx.x;
@@ -547,7 +574,7 @@ __global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __res
                                                               bf16 * __restrict__ out, bf16 * __restrict__ out_norm, int k, int d,
                                                               float eps) {
     JIB_KS(13, 0);
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(13, 1);
     __shared__ float red[32];
@@ -630,6 +657,15 @@ __global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __res
 
 inline int launched() { return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH; }
 
+// JIB_ROUTE_WARM=0: the fused router does not pre-walk its gating / sorting code while it waits (A/B measurements).
+inline bool route_warm() {
+    static const bool on = [] {
+        const char * e = getenv("JIB_ROUTE_WARM");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
+}
+
 }  // namespace
 
 JIB_BC_DEFINE_SETTER(moe)
@@ -661,7 +697,7 @@ int jib_moe_route_fused(const void * g, const float * w_router, const float * bi
     if (norm_w != nullptr && g_out == nullptr) return JIB_E_ARG;
     JIB_LAUNCH((moe_route_fused_kernel), E, GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, bias, logits, ids, wts, seg,
                src_token, dest, counter, T, d, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, expert_base, E_local,
-               norm_w, eps, (bf16 *) g_out);
+               norm_w, eps, (bf16 *) g_out, route_warm() ? 1 : 0);
     return launched();
 }
 

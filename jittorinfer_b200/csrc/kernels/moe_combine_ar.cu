@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(NT) moe_combine_ar_kernel(const bf16 * __restr
                                                             const bf16 * __restrict__ residual, const float * __restrict__ norm_w,
                                                             bf16 * __restrict__ out, bf16 * __restrict__ out_norm, int k, int d,
                                                             float eps, JibArCtx ar, int site) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ float red[32];
     const int t = blockIdx.x;

@@ -18,6 +18,22 @@
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Where a kernel lets its dependents start.  Default: first thing (the next kernels become resident as early as the SMs have
+// room and park in pdl_wait()).  -DJIB_PDL_LATE: only once the kernel's own loads have been issued (PDL_TRIGGER_LATE() sites;
+// kernels without such a site release their dependents when their CTAs exit), so that parked CTAs do not share the SMs
+// with the running kernel for its whole duration.
+#ifdef JIB_PDL_LATE
+#define PDL_TRIGGER_TOP() \
+    do {                  \
+    } while (0)
+#define PDL_TRIGGER_LATE() pdl_launch_dependents()
+#else
+#define PDL_TRIGGER_TOP() pdl_launch_dependents()
+#define PDL_TRIGGER_LATE() \
+    do {                   \
+    } while (0)
+#endif
+
 namespace jib {
 
 inline bool pdl_enabled() {

@@ -24,7 +24,7 @@ constexpr int SAMPLE_MAX_K = 128;
 // a candidate is below top_p (softmax of the untempered logits of the top-k set), min-p while logit >= best + ln(min_p).
 __global__ void __launch_bounds__(32) sample_topk_kernel(const float * __restrict__ vals, const int * __restrict__ ids,
                                                          const float * __restrict__ params, int * __restrict__ out, int k) {
-    pdl_launch_dependents();
+    PDL_TRIGGER_TOP();
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     __shared__ float e[SAMPLE_MAX_K];
     const int row = blockIdx.x, lane = threadIdx.x;

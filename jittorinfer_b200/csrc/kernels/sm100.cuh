@@ -73,6 +73,19 @@ __device__ __forceinline__ void tma_load_3d(void * dst, const CUtensorMap * m, u
         ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
+// The same with an L2 eviction policy for the loaded lines.  evict_first: data read once per forward pass (the weights of a
+// decode step, tens of GB) leaves the L2 before anything else does, so that activations, small tables and kernel code stay.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_load_3d_hint(void * dst, const CUtensorMap * m, uint64_t * bar, int x, int y, int z, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void * dst, const CUtensorMap * m, uint64_t * bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

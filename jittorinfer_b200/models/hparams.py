@@ -235,6 +235,17 @@ def preset(name: str) -> DeepSeek2HParams:
             n_group=4, topk_group=2, expert_weights_scale=4.0, bos_id=0, eos_id=1)
     if name in ("lite", "deepseek-v2-lite", "v2-lite"):
         return DeepSeek2HParams()
+    if name in ("lite-2l",):
+        # DeepSeek-V2-Lite's layer shapes (hidden 2048, 16 heads, latent 512 + 64, 64 experts top-6 + 2 shared) with three
+        # layers (one dense, two MoE) and a small vocabulary: what the GPU tests run the benchmarked kernels on
+        return DeepSeek2HParams(n_layer=3, n_vocab=4096)
+    if name in ("v2-2l",):
+        # DeepSeek-V2's shapes where they select kernels (hidden 5120, q-LoRA 1536, latent 512 + 64, 160 experts in 8 groups
+        # of which 3 are eligible, top-6, weight scale 16), cut down where only size follows (32 heads, expert width 512,
+        # two layers, small vocabulary) so that a test can hold it next to an fp32 oracle
+        return DeepSeek2HParams(
+            n_vocab=4096, n_embd=5120, n_layer=2, n_head=32, n_ff=4096, n_ff_exp=512, n_expert=160, n_expert_used=6,
+            n_expert_shared=2, expert_weights_scale=16.0, n_group=8, topk_group=3, q_lora_rank=1536)
     if name in ("v2", "deepseek-v2"):
         return DeepSeek2HParams(
             n_embd=5120, n_layer=60, n_head=128, n_ff=12288, n_ff_exp=1536, n_expert=160, n_expert_used=6,

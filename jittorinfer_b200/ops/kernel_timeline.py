@@ -28,6 +28,7 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--steps", type=int, default=3, help="replays recorded; the last one is printed")
     ap.add_argument("--out", default=None, help="also write the table to this file")
+    ap.add_argument("--raw", default=None, help="also save the last step's stamps (numpy structured array, .npy)")
     args = ap.parse_args(argv)
 
     from ..models.hparams import preset
@@ -60,6 +61,9 @@ def main(argv=None) -> int:
     head = f"# {args.model}, {args.layers} layers, batch {C}, context {args.context}: {len(launches)} launches in the last step"
     print(head)
     print(text)
+    if args.raw:
+        import numpy as np
+        np.save(args.raw, stamps)
     if args.out:
         with open(args.out, "w") as f:
             f.write(head + "\n" + text + "\n")

@@ -15,13 +15,16 @@ import torch
 _lib = None
 _ws: Dict[int, "Workspace"] = {}
 launch_count = 0            # kernels launched through this module (bench.py reports it)
+launches_by_name: Dict[str, int] = {}      # the same per launcher ("gemm", "mla_flash", ...): tests assert which path ran
 
 # Switches for A/B measurements (each defaults to the faster path; "0" selects the separate launches).
 # Expert sort over many CTAs (histogram / scan / scatter) for batches of PERMUTE_MULTI_MIN (token, expert) pairs and more.
 PERMUTE_MULTI = os.environ.get("JIB_PERMUTE_MULTI", "1") == "1"
 PERMUTE_MULTI_MIN = 4096
-# [RMSNorm +] router logits + gating + expert sort in one launch for decode batches (<= FUSED_ROUTE_MAX_T tokens).
-FUSED_ROUTE = os.environ.get("JIB_FUSED_ROUTE", "1") == "1"
+# [RMSNorm +] router logits + gating + expert sort in one launch for decode batches (<= FUSED_ROUTE_MAX_T tokens).  Off by
+# default: measured on B200 the single CTA that gates and sorts after the last logit arrives costs as much as the three
+# launches it replaces (profiles/decode_switches_ab_lite.md).
+FUSED_ROUTE = os.environ.get("JIB_FUSED_ROUTE", "0") == "1"
 # Grouped-GEMM split-K hint from the expected number of experts hit instead of all local experts.
 ACTIVE_HINT_EXPECTED = os.environ.get("JIB_ACTIVE_HINT", "0") == "1"
 # Expert combine fused with the RMSNorm of the next block (one launch fewer per MoE layer).
@@ -29,6 +32,8 @@ FUSED_COMBINE_NORM = os.environ.get("JIB_FUSED_COMBINE_NORM", "1") == "1"
 # Decode batches: the grouped gate|up GEMM reads the token rows in place (no gather into expert order).
 GROUPED_SRC = os.environ.get("JIB_GROUPED_SRC", "1") == "1"
 GROUPED_SRC_MAX_T = 64
+# The router launch of a decode batch also applies the RMSNorm of its input ("0": a separate norm launch before it).
+ROUTE_NORM = os.environ.get("JIB_ROUTE_NORM", "1") == "1"
 FUSED_ROUTE_MAX_T = 64
 _route_stash: Dict[tuple, tuple] = {}       # (ids ptr, expert_base, E_local) -> (seg, src, dest) produced by the fused launch
 
@@ -152,6 +157,7 @@ def _stream() -> int:
 def _ck(rc: int, what: str):
     global launch_count
     launch_count += 1
+    launches_by_name[what] = launches_by_name.get(what, 0) + 1
     if rc != 0:
         raise RuntimeError(f"{what}: {ERRORS.get(rc, rc)}")
 
@@ -345,8 +351,12 @@ def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_
     T, d = g.shape
     fused = FUSED_ROUTE and route is not None and T <= FUSED_ROUTE_MAX_T
     g_in = g
-    if pre_norm is not None and not fused:
+    g_pre = None
+    if pre_norm is not None and not (fused and ROUTE_NORM):
         g, _ = rmsnorm(g, pre_norm[0], pre_norm[1])
+        g_in, g_pre, pre_norm_k = g, g, None
+    else:
+        pre_norm_k = pre_norm
     E = w_router.shape[0]
     ids = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
     wts = torch.empty(T, k + n_shared, dtype=torch.float32, device=g.device)
@@ -358,15 +368,15 @@ def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_
         src = torch.empty(n, dtype=torch.int32, device=g.device)
         dest = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
         assert g_in.dtype == torch.bfloat16 and g_in.is_contiguous()
-        g_out = torch.empty_like(g_in) if pre_norm is not None else None
+        g_out = torch.empty_like(g_in) if pre_norm_k is not None else None
         _ck(load().jib_moe_route_fused(g_in.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(),
                                        seg.data_ptr(), src.data_ptr(), dest.data_ptr(), workspace(g.device).route_counter.data_ptr(),
                                        T, d, E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared,
-                                       int(group_top2), expert_base, E_local, pre_norm[0].data_ptr() if pre_norm is not None else None,
-                                       float(pre_norm[1]) if pre_norm is not None else 0.0, _p(g_out), _stream()), "moe_route_fused")
+                                       int(group_top2), expert_base, E_local, pre_norm_k[0].data_ptr() if pre_norm_k is not None else None,
+                                       float(pre_norm_k[1]) if pre_norm_k is not None else 0.0, _p(g_out), _stream()), "moe_route_fused")
         _route_stash.clear()                       # at most one pending result: the sort that follows this gate
         _route_stash[(ids.data_ptr(), expert_base, E_local)] = (seg, src, dest, ids)
-        return (ids, wts, g_out) if pre_norm is not None else (ids, wts)
+        return (ids, wts, g_out if g_out is not None else g_pre) if pre_norm is not None else (ids, wts)
     _ck(load().jib_moe_gate(g.data_ptr(), w_router.data_ptr(), _p(bias), logits.data_ptr(), ids.data_ptr(), wts.data_ptr(), T, d,
                             E, k, n_group, topk_group, float(scale), int(norm), int(sigmoid), n_shared, int(group_top2), _stream()), "moe_gate")
     return (ids, wts, g) if pre_norm is not None else (ids, wts)

@@ -109,7 +109,8 @@ class ArCtx(C.Structure):
     _fields_ = [("recv", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("status", C.c_void_p),
                 ("world", C.c_int), ("rank", C.c_int), ("n_sites", C.c_int), ("max_rows", C.c_int), ("d_max", C.c_int),
                 ("max_tiles", C.c_int), ("recv2", C.c_void_p * 8), ("out2", C.c_void_p * 8), ("flags2", C.c_void_p * 8),
-                ("max_rows2", C.c_int), ("xg", C.c_void_p * 8), ("flags3", C.c_void_p * 8), ("ag_counter", C.c_void_p)]
+                ("max_rows2", C.c_int), ("xg", C.c_void_p * 8), ("flags3", C.c_void_p * 8), ("ag_counter", C.c_void_p),
+                ("spin_limit", C.c_uint)]
 
 
 class FusedCommunicator(Communicator):

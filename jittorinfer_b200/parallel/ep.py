@@ -112,7 +112,7 @@ class EpCtx(C.Structure):
     _fields_ = [("xrecv", C.c_void_p * 8), ("meta", C.c_void_p * 8), ("counts", C.c_void_p * 8), ("yret", C.c_void_p * 8),
                 ("flags", C.c_void_p * 8), ("epoch", C.c_void_p), ("status", C.c_void_p),
                 ("world", C.c_int), ("rank", C.c_int), ("n_sites", C.c_int), ("E_local", C.c_int), ("d", C.c_int),
-                ("max_recv_rows", C.c_int), ("max_pairs", C.c_int)]
+                ("max_recv_rows", C.c_int), ("max_pairs", C.c_int), ("spin_limit", C.c_uint)]
 
 
 class FusedEpDispatcher(EpDispatcher):

@@ -167,17 +167,22 @@ def kernel_launches(stamps: np.ndarray) -> List[Dict]:
     entries = ks[ks["c"] == 0]
     launches: List[Dict] = []
     by_key: Dict[tuple, List[int]] = {}
-    i = 0
-    while i < entries.shape[0]:
-        kind, grid = int(entries["kind"][i]), int(entries["b"][i])
-        j = i
-        while j < entries.shape[0] and j - i < grid and int(entries["kind"][j]) == kind and int(entries["b"][j]) == grid:
-            j += 1
-        rec = {"kernel": KERNEL_NAMES.get(kind - 100, str(kind - 100)), "grid": grid, "n_entered": j - i,
-               "phases": {0: [(int(entries["t"][i]) - t0) / 1e3, (int(entries["t"][j - 1]) - t0) / 1e3]}}
+    # launches of one (kernel, grid size) enter in launch order even when kernels of different kinds are resident together
+    # (programmatic dependent launch makes a chain of kernels resident early): chunk each kind's entry stamps by grid size
+    per_key: Dict[tuple, List[int]] = {}
+    for i in range(entries.shape[0]):
+        per_key.setdefault((int(entries["kind"][i]), int(entries["b"][i])), []).append(int(entries["t"][i]))
+    protos = []
+    for (kind, grid), ts in per_key.items():
+        for j in range(0, len(ts), max(1, grid)):
+            chunk = ts[j:j + max(1, grid)]
+            protos.append((chunk[0], kind, grid, len(chunk), chunk[-1]))
+    protos.sort()
+    for first, kind, grid, n_in, last in protos:
+        rec = {"kernel": KERNEL_NAMES.get(kind - 100, str(kind - 100)), "grid": grid, "n_entered": n_in,
+               "phases": {0: [(first - t0) / 1e3, (last - t0) / 1e3]}}
         by_key.setdefault((kind, grid), []).append(len(launches))
         launches.append(rec)
-        i = j
     seen: Dict[tuple, int] = {}
     for s in ks[ks["c"] != 0]:
         key = (int(s["kind"]), int(s["b"]))

@@ -79,6 +79,7 @@ class _InFlight:
     event: Optional[object]            # CUDA event after that copy (None on the CPU)
     n_out: int
     out_slots: np.ndarray              # scheduler slot of each output row
+    status: Optional[torch.Tensor] = None   # pinned copy of the device status words taken behind this step
 
 
 class _StepIO:
@@ -212,6 +213,15 @@ class LLMEngine:
             and not getattr(model, "split", False)
         self._inflight: Optional[_InFlight] = None
         self._stage = 0
+        # Kernels that give up on a bounded wait (an mbarrier, a peer's flag) or catch an index out of range record it in
+        # four status words on the device and carry on.  The engine copies them to pinned memory behind every step's ids
+        # (same stream, no extra synchronisation) and fails the step when a code is set: nothing computed from such a step
+        # is sampled or sent to a client; the caller resets the engine (the server answers 503 and keeps serving).
+        self._status_dev = None
+        self._status_hosts = None
+        if self.device.type == "cuda" and not ops.force_torch() and not getattr(model, "split", False):
+            self._status_dev = ops.nat().workspace(self.device).status
+            self._status_hosts = [torch.zeros(4, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._out_hosts = [self._out_host, torch.zeros_like(self._out_host).pin_memory() if self.device.type == "cuda"
                            else torch.zeros_like(self._out_host)] if self._run_ahead else [self._out_host]
         self._flip = 0
@@ -497,10 +507,25 @@ class LLMEngine:
         """No live request needs the host sampler chain (ids are chosen on the device: arg-max or the device sampler)."""
         return all(st.sampler is None and not st.params.logprobs for st in self.requests.values() if st.finish_reason is None)
 
+    def _check_device_status(self, host: Optional[torch.Tensor]) -> None:
+        """``host``: the pinned copy of the status words taken behind a step, valid once that step's stream work is done."""
+        if host is None or int(host[0]) == 0:
+            return
+        st = host.tolist()
+        ws = ops.nat().workspace(self.device)
+        ws.status.zero_()
+        ws.counters.zero_()
+        ws.route_counter.zero_()
+        host.zero_()
+        self.stats["device_faults"] = self.stats.get("device_faults", 0) + 1
+        names = {1: "wait timeout", 2: "index out of bounds", 3: "misaligned"}
+        raise RuntimeError(f"kernel status: {names.get(st[0], st[0])} at site {st[1]} block {st[2]} extra {st[3]}: step discarded")
+
     def _collect(self, infl: _InFlight) -> np.ndarray:
         if infl.event is not None:
             infl.event.synchronize()
-        self.stats["d2h_bytes"] += infl.n_out * 4
+        self._check_device_status(infl.status)
+        self.stats["d2h_bytes"] += infl.n_out * 4 + (16 if infl.status is not None else 0)
         return infl.host[:infl.n_out].numpy().astype(np.int32, copy=True)
 
     def _launch_greedy(self, n_tokens: int, n_seqs: int, n_out: int, max_q: int, feedback: Optional[_InFlight]) -> _InFlight:
@@ -547,6 +572,10 @@ class LLMEngine:
         host = self._out_hosts[self._flip]
         self._flip ^= 1
         host[:n_out].copy_(out.reshape(-1)[:n_out], non_blocking=True)
+        status = None
+        if self._status_hosts is not None:
+            status = self._status_hosts[self._flip]
+            status.copy_(self._status_dev, non_blocking=True)
         event = None
         if self.device.type == "cuda":
             event = torch.cuda.Event()
@@ -555,7 +584,7 @@ class LLMEngine:
         self.stats["tokens_in"] += n_tokens
         self.stats["tokens_out"] += n_out
         self.stats["h2d_bytes"] += io.h2d_bytes
-        return _InFlight(out, host, event, n_out, io.h["out_slots"][:n_out].copy())
+        return _InFlight(out, host, event, n_out, io.h["out_slots"][:n_out].copy(), status)
 
     def _trace_ahead(self, pt, ev, launched, n_tokens=0, n_seqs=0, n_out=0, max_q=0) -> None:
         """Step trace of the run-ahead path: "step" for a call that launched one (its events belong to the step before),
@@ -715,11 +744,14 @@ class LLMEngine:
             n_el = flat.numel()
             host = self._out_host[:n_el]
             host.copy_(flat, non_blocking=True)
+            if self._status_hosts is not None:
+                self._status_hosts[0].copy_(self._status_dev, non_blocking=True)
             if self.device.type == "cuda":
                 torch.cuda.current_stream(out.device).synchronize()
+            self._check_device_status(self._status_hosts[0] if self._status_hosts is not None else None)
             if pt:
                 pt.mark("wait")
-            self.stats["d2h_bytes"] += n_el * 4
+            self.stats["d2h_bytes"] += n_el * 4 + (16 if self._status_hosts is not None else 0)
             res = host.numpy().reshape(out.shape[0], -1)
             sampled = np.empty(n_out, dtype=np.int32)
             if mode in ("greedy", "sample"):

@@ -244,7 +244,7 @@ def test_fused_route_matches_the_separate_kernels(nat, T, d, E, k, n_group, topk
     y = rnd(T, d)
     w_router = torch.randn(E, d, device=DEV, dtype=torch.float32) * 0.05
     w_norm = torch.rand(d, device=DEV, dtype=torch.float32) + 0.5
-    assert nat.FUSED_ROUTE
+    saved = nat.FUSED_ROUTE
     try:
         for pre in (None, (w_norm, 1e-6), None):
             nat.FUSED_ROUTE = False
@@ -265,7 +265,7 @@ def test_fused_route_matches_the_separate_kernels(nat, T, d, E, k, n_group, topk
             assert torch.equal(src0[:n_local], src1[:n_local]) and bool((src1[n_local:] == -1).all())
             assert int(nat.workspace(y.device).route_counter.item()) == 0
     finally:
-        nat.FUSED_ROUTE = True
+        nat.FUSED_ROUTE = saved
 
 
 def test_gate_matches_the_fp32_reference(nat):

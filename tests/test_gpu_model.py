@@ -77,3 +77,78 @@ def test_engine_cuda_graphs_equal_eager_and_track_oracle():
     o = OracleModel(hp, {k: v.bfloat16().float() for k, v in w.items()})
     agree = sum(a == b for p, out in zip(prompts, outs[True]) for a, b in zip(out, o.generate(p, 24)))
     assert agree >= 36      # bf16 vs fp32: greedy paths may split late, never early
+
+
+def _row_rel_err(a, b):
+    """Per row: largest logit error relative to the row's largest reference logit."""
+    return ((a - b).abs().amax(dim=-1) / b.abs().amax(dim=-1).clamp_min(1e-6))
+
+
+@pytest.mark.parametrize("name", ["lite-2l", "v2-2l"])
+def test_real_shapes_logits_match_oracle_and_take_the_tensor_core_paths(name):
+    """DeepSeek-V2-Lite / DeepSeek-V2 layer shapes (the benchmarked kernels: tcgen05 flash-MLA over the 576-wide latent rows,
+    K = 2048 / 5120 GEMMs, 64 / 160-expert gating, grouped expert GEMMs) against the fp32 oracle, on logits: a 70-token prompt
+    chunk, a chunked continuation, then 8 sequences decoding under CUDA graphs.  Rows whose routing flipped on a near-tie
+    (bf16 activations against fp32) may exceed the tolerance; they are counted and bounded separately."""
+    hp = preset(name)
+    w = random_weights(hp, seed=0, std=0.02)
+    o = OracleModel(hp, {k: v.bfloat16().float() for k, v in w.items()})
+    m = DeepSeek2Model(hp, w.items(), dtype=torch.bfloat16, device="cuda")
+    nat = ops.nat()
+    n0 = dict(nat.launches_by_name)
+    cache = torch.zeros(hp.n_layer, 8 * 64, hp.kv_row, dtype=torch.bfloat16, device="cuda")
+    toks = torch.randint(0, hp.n_vocab, (70,), generator=torch.Generator().manual_seed(2)).tolist()
+    l_ref = o.forward(torch.tensor(toks))
+    l_nat = m.forward(_batch(toks, 0, "cuda"), cache).float().cpu()
+    nxt = torch.randint(0, hp.n_vocab, (9,), generator=torch.Generator().manual_seed(3)).tolist()
+    l_ref2 = o.forward(torch.tensor(nxt))
+    l_nat2 = m.forward(_batch(nxt, 70, "cuda"), cache).float().cpu()
+    nat.check_status()
+    err = torch.cat([_row_rel_err(l_nat, l_ref), _row_rel_err(l_nat2, l_ref2)])
+    tight = (err <= 2e-2).float().mean().item()
+    flipped = int((err > 2e-2).sum())
+    print(f"{name}: rows within 2e-2: {tight:.3f}; median row error {err.median().item():.4f}; rows beyond (routing flips): {flipped}; "
+          f"worst {err.max().item():.3f}")
+    assert tight >= 0.95, f"{name}: only {tight:.3f} of rows within 2e-2 (worst {err.max().item():.3f})"
+    assert err.max().item() < 0.5                              # a flipped expert moves a row, it does not destroy it
+    # arg-max agreement where the reference's margin is not a near-tie
+    top2 = l_ref.topk(2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0.05 * l_ref.abs().amax(dim=-1)
+    assert bool((l_nat.argmax(-1)[clear] == l_ref.argmax(-1)[clear]).all())
+    ran = {k: nat.launches_by_name.get(k, 0) - n0.get(k, 0) for k in ("mla_flash", "mla_attention", "gemm_grouped", "moe_gate")}
+    assert ran["mla_flash"] >= 2 * hp.n_layer and ran["mla_attention"] == 0, ran     # tcgen05 attention, not the SIMT fallback
+    assert ran["gemm_grouped"] >= 4 and ran["moe_gate"] >= 2, ran
+    # 8 sequences decoding under CUDA graphs: tokens against the oracle's greedy continuation
+    eng = LLMEngine(m, EngineConfig(n_ctx=8 * 256, n_batch=256, n_parallel=8, graph_buckets=(1, 2, 4, 8)))
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (70, 33, 8, 100, 64, 65, 17, 5)]
+    n1 = nat.launches_by_name.get("mla_flash", 0)
+    outs = eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=6)
+    nat.check_status()
+    assert eng.stats["graph_steps"] >= 5 and nat.launches_by_name.get("mla_flash", 0) > n1
+    ref = [o.generate(p, 6) for p in prompts[:3]]
+    first = sum(int(a[0] == b[0]) for a, b in zip(outs, ref))
+    agree = sum(int(x == y) for a, b in zip(outs, ref) for x, y in zip(a, b))
+    print(f"{name}: {agree}/18 greedy tokens equal the oracle's over 3 sequences (first tokens: {first}/3)")
+    assert first == 3 and agree >= 12
+
+
+def test_layer_split_over_two_gpus_equals_one_gpu():
+    """Layer-split serving (consecutive layer ranges on consecutive GPUs of one process, activations hopping between them): the
+    same tokens as the model on one GPU, eager steps on both devices (every kernel sets its per-device launch attributes)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    hp = preset("lite-2l")
+    w = random_weights(hp, seed=0, std=0.02)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, hp.n_vocab, (n,), generator=g).tolist() for n in (40, 70, 9)]
+    outs = []
+    for devices in (None, [torch.device("cuda", 0), torch.device("cuda", 1), torch.device("cuda", 1)]):
+        m = DeepSeek2Model(hp, w.items(), dtype=torch.bfloat16, device="cuda:0", layer_devices=devices)
+        eng = LLMEngine(m, EngineConfig(n_ctx=2048, n_batch=64, n_parallel=4, graph_buckets=(1, 2, 4)))
+        outs.append(eng.generate(prompts, SamplingParams(ignore_eos=True), max_new_tokens=10))
+        for d in range(2):
+            torch.cuda.synchronize(d)
+        ops.nat().check_status()
+        del eng, m
+    assert outs[0] == outs[1]

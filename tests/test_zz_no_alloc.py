@@ -27,6 +27,8 @@ def _lib():
     L.jib_gemm_bf16_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     L.jib_gemm_bf16_noalloc_need.restype = C.c_size_t
     L.jib_gemm_bf16_noalloc_need.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int]
+    L.jib_gemm_bf16_noalloc_status.restype = C.c_int
+    L.jib_gemm_bf16_noalloc_status.argtypes = [C.c_void_p, C.c_void_p]
     return L, native
 
 
@@ -35,7 +37,8 @@ def _rand(shape, scale, seed):
     return (torch.randn(*shape, generator=g) * scale).bfloat16().cuda()
 
 
-@pytest.mark.parametrize("T,N,K,splits", [(1, 2048, 2048, 8), (8, 3648, 2048, 4), (40, 384, 1408, 2), (8, 512, 2048, 0), (5, 640, 512, 1)])
+@pytest.mark.parametrize("T,N,K,splits", [(1, 2048, 2048, 8), (8, 3648, 2048, 4), (40, 384, 1408, 2), (8, 512, 2048, 0), (5, 640, 512, 1),
+                                          (64, 1024, 2048, 4), (200, 512, 1400, 3), (200, 640, 2048, 0)])
 def test_noalloc_matches_regular_entry_point_twice(T, N, K, splits):
     L, native = _lib()
     stream = torch.cuda.current_stream().cuda_stream
@@ -50,6 +53,11 @@ def test_noalloc_matches_regular_entry_point_twice(T, N, K, splits):
         mag = exact.abs().max().item() + 1e-6
         assert (out.float() - ref.float()).abs().max().item() <= 2e-2 * mag
         assert (out.float() - exact).abs().max().item() <= 2e-2 * mag
+        # faults the kernel itself found (a wait that ran out, an index out of range) are only visible here
+        status = torch.zeros(4, dtype=torch.int32).pin_memory()
+        assert L.jib_gemm_bf16_noalloc_status(status.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0, 0, 0]
     native.check_status()
 
 
