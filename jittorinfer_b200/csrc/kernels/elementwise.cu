@@ -60,15 +60,11 @@ __global__ void embed_gather_kernel(const bf16 * __restrict__ table, const int *
 }
 
 // out_sum = x + residual (bf16-rounded), out_norm = rmsnorm(out_sum) * w.  One block per row.
+// dry: the same instructions without the stores (see pdl.cuh: warm_enabled).
 template <int NT, int MAXV>
-__global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x, const bf16 * __restrict__ residual,
-                                                     const float * __restrict__ w, bf16 * __restrict__ out_norm,
-                                                     bf16 * __restrict__ out_sum, int d, long long x_stride, float eps) {
-    JIB_KS(4, 0);
-    PDL_TRIGGER_TOP();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(4, 1);
-    __shared__ float red[32];
+__device__ __noinline__ void rmsnorm_row(const bf16 * __restrict__ x, const bf16 * __restrict__ residual, const float * __restrict__ w,
+                                         bf16 * __restrict__ out_norm, bf16 * __restrict__ out_sum, int d, long long x_stride, float eps,
+                                         float * red, bool dry) {
     const int t = blockIdx.x;
     const bf16x8 * xr = (const bf16x8 *) (x + (size_t) t * x_stride);
     const bf16x8 * rr = residual ? (const bf16x8 *) (residual + (size_t) t * d) : nullptr;
@@ -88,7 +84,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x
                     a.v[j] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
                 }
             }
-            if (out_sum) ((bf16x8 *) (out_sum + (size_t) t * d))[i] = a;
+            if (out_sum && !dry) ((bf16x8 *) (out_sum + (size_t) t * d))[i] = a;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 float2 f = __bfloat1622float2(a.v[j]);
@@ -110,31 +106,40 @@ __global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x
             o.v[1] = __floats2bfloat162_rn(vals[it][2] * inv * w0.z, vals[it][3] * inv * w0.w);
             o.v[2] = __floats2bfloat162_rn(vals[it][4] * inv * w1.x, vals[it][5] * inv * w1.y);
             o.v[3] = __floats2bfloat162_rn(vals[it][6] * inv * w1.z, vals[it][7] * inv * w1.w);
-            ((bf16x8 *) (out_norm + (size_t) t * d))[i] = o;
+            if (!dry) ((bf16x8 *) (out_norm + (size_t) t * d))[i] = o;
         }
     }
+}
+
+template <int NT, int MAXV>
+__global__ void __launch_bounds__(NT) rmsnorm_kernel(const bf16 * __restrict__ x, const bf16 * __restrict__ residual,
+                                                     const float * __restrict__ w, bf16 * __restrict__ out_norm,
+                                                     bf16 * __restrict__ out_sum, int d, long long x_stride, float eps, int warm) {
+    JIB_KS(4, 0);
+    PDL_TRIGGER_TOP();
+    __shared__ float red[32];
+    if (warm) rmsnorm_row<NT, MAXV>(x, residual, w, out_norm, out_sum, d, x_stride, eps, red, true);
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(4, 1);
+    rmsnorm_row<NT, MAXV>(x, residual, w, out_norm, out_sum, d, x_stride, eps, red, false);
     JIB_KS(4, 9);
 }
 
 // One block per token: c = rmsnorm(ckv[:r]) * w -> cache[slot][:r]; k_pe = rope(ckv[r:]) -> cache[slot][r:];
 // q_pe = rope(q[h][dn:]) -> q_out[t][h][r:].  rope_table [max_pos][dr/2][2] holds (cos, sin) * magnitude.
+// dry: the same instructions without stores or status reports.
 template <int NT>
-__global__ void __launch_bounds__(NT) mla_qkv_post_kernel(const bf16 * __restrict__ q, long long q_stride, const bf16 * __restrict__ ckv,
-                                                          long long ckv_stride, const float * __restrict__ kv_norm_w, float eps,
-                                                          const float * __restrict__ rope_table, const int * __restrict__ positions,
-                                                          const int * __restrict__ slot_mapping, bf16 * __restrict__ cache,
-                                                          bf16 * __restrict__ q_out, int H, int dn, int dr, int r, int max_pos,
-                                                          long long n_slots, int * status) {
-    JIB_KS(5, 0);
-    PDL_TRIGGER_TOP();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(5, 1);
-    __shared__ float red[32];
+__device__ __noinline__ void mla_qkv_post_row(const bf16 * __restrict__ q, long long q_stride, const bf16 * __restrict__ ckv,
+                                              long long ckv_stride, const float * __restrict__ kv_norm_w, float eps,
+                                              const float * __restrict__ rope_table, const int * __restrict__ positions,
+                                              const int * __restrict__ slot_mapping, bf16 * __restrict__ cache, bf16 * __restrict__ q_out,
+                                              long long qo_row, long long qo_head, int H, int dn, int dr, int r, int max_pos,
+                                              long long n_slots, int * status, float * red, bool dry) {
     const int t = blockIdx.x;
     const int slot = slot_mapping[t];
     int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {
-        if (slot >= 0) jib_report(status, JIB_ERR_BOUNDS, 10, pos);
+        if (slot >= 0 && !dry) jib_report(status, JIB_ERR_BOUNDS, 10, pos);
         pos = pos < 0 ? 0 : max_pos - 1;
     }
     const float * cs = rope_table + (size_t) pos * dr;       // dr/2 pairs * 2
@@ -148,27 +153,51 @@ __global__ void __launch_bounds__(NT) mla_qkv_post_kernel(const bf16 * __restric
     ss = block_sum<NT>(ss, red);
     const float inv = rsqrtf(ss / (float) r + eps);
     const bool write_kv = slot >= 0 && slot < n_slots;
-    if (slot >= n_slots) jib_report(status, JIB_ERR_BOUNDS, 11, slot);
+    if (slot >= n_slots && !dry) jib_report(status, JIB_ERR_BOUNDS, 11, slot);
     if (write_kv) {
         bf16 * dst = cache + (size_t) slot * (r + dr);
-        for (int i = threadIdx.x; i < r; i += NT) dst[i] = __float2bfloat16(__bfloat162float(crow[i]) * inv * kv_norm_w[i]);
+        for (int i = threadIdx.x; i < r; i += NT) {
+            const bf16 v = __float2bfloat16(__bfloat162float(crow[i]) * inv * kv_norm_w[i]);
+            if (!dry) dst[i] = v;
+        }
         for (int i = threadIdx.x; i < dr / 2; i += NT) {
             const float x0 = __bfloat162float(crow[r + 2 * i]), x1 = __bfloat162float(crow[r + 2 * i + 1]);
             const float c = cs[2 * i], s = cs[2 * i + 1];
-            *(__nv_bfloat162 *) (dst + r + 2 * i) = __floats2bfloat162_rn(x0 * c - x1 * s, x0 * s + x1 * c);
+            const __nv_bfloat162 v = __floats2bfloat162_rn(x0 * c - x1 * s, x0 * s + x1 * c);
+            if (!dry) *(__nv_bfloat162 *) (dst + r + 2 * i) = v;
         }
     }
     // q rope: H * dr/2 pairs
     const int half = dr / 2;
     const bf16 * qrow = q + (size_t) t * q_stride;
-    bf16 * qo = q_out + (size_t) t * H * (r + dr);
+    bf16 * qo = q_out + (size_t) t * qo_row;      // q_out points at the first RoPE element of token 0, head 0
     for (int i = threadIdx.x; i < H * half; i += NT) {
         const int h = i / half, p = i - h * half;
         const __nv_bfloat162 xx = *(const __nv_bfloat162 *) (qrow + (size_t) h * (dn + dr) + dn + 2 * p);
         const float2 f = __bfloat1622float2(xx);
         const float c = cs[2 * p], s = cs[2 * p + 1];
-        *(__nv_bfloat162 *) (qo + (size_t) h * (r + dr) + r + 2 * p) = __floats2bfloat162_rn(f.x * c - f.y * s, f.x * s + f.y * c);
+        const __nv_bfloat162 v = __floats2bfloat162_rn(f.x * c - f.y * s, f.x * s + f.y * c);
+        if (!dry) *(__nv_bfloat162 *) (qo + (size_t) h * qo_head + 2 * p) = v;
     }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(NT) mla_qkv_post_kernel(const bf16 * __restrict__ q, long long q_stride, const bf16 * __restrict__ ckv,
+                                                          long long ckv_stride, const float * __restrict__ kv_norm_w, float eps,
+                                                          const float * __restrict__ rope_table, const int * __restrict__ positions,
+                                                          const int * __restrict__ slot_mapping, bf16 * __restrict__ cache,
+                                                          bf16 * __restrict__ q_out, long long qo_row, long long qo_head, int H, int dn,
+                                                          int dr, int r, int max_pos, long long n_slots, int * status, int warm) {
+    JIB_KS(5, 0);
+    PDL_TRIGGER_TOP();
+    __shared__ float red[32];
+    // positions / slot_mapping are step inputs, uploaded before the first kernel of the step: valid during the dry pass
+    if (warm) mla_qkv_post_row<NT>(q, q_stride, ckv, ckv_stride, kv_norm_w, eps, rope_table, positions, slot_mapping, cache, q_out, qo_row,
+                                   qo_head, H, dn, dr, r, max_pos, n_slots, status, red, true);
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(5, 1);
+    mla_qkv_post_row<NT>(q, q_stride, ckv, ckv_stride, kv_norm_w, eps, rope_table, positions, slot_mapping, cache, q_out, qo_row, qo_head, H,
+                         dn, dr, r, max_pos, n_slots, status, red, false);
     JIB_KS(5, 9);
 }
 
@@ -356,26 +385,28 @@ int jib_rmsnorm(const void * x, const void * residual, const float * w, void * o
     cudaStream_t s = (cudaStream_t) stream;
     const int nv = d / 8;
     if (nv <= 128)
-        JIB_LAUNCH((rmsnorm_kernel<128, 1>), T, 128, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<128, 1>), T, 128, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
     else if (nv <= 256)
-        JIB_LAUNCH((rmsnorm_kernel<256, 1>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<256, 1>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
     else if (nv <= 1024)
-        JIB_LAUNCH((rmsnorm_kernel<256, 4>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<256, 4>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
     else if (nv <= 2048)
-        JIB_LAUNCH((rmsnorm_kernel<512, 4>), T, 512, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps);
+        JIB_LAUNCH((rmsnorm_kernel<512, 4>), T, 512, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
     else
         return JIB_E_ARG;
     return launched();
 }
 
 int jib_mla_qkv_post(const void * q, long long q_stride, const void * ckv, long long ckv_stride, const float * kv_norm_w, float eps,
-                     const float * rope_table, const int * positions, const int * slot_mapping, void * cache, void * q_out, int T,
-                     int H, int dn, int dr, int r, int max_pos, long long n_slots, int * status, void * stream) {
+                     const float * rope_table, const int * positions, const int * slot_mapping, void * cache, void * q_out,
+                     long long qo_row, long long qo_head, int T, int H, int dn, int dr, int r, int max_pos, long long n_slots, int * status,
+                     void * stream) {
     if (T <= 0) return 0;
-    if ((dr & 1) || (dn & 1) || (r & 1) || (q_stride & 1)) return JIB_E_ARG;
+    if ((dr & 1) || (dn & 1) || (r & 1) || (q_stride & 1) || (qo_row & 1) || (qo_head & 1) || ((uintptr_t) q_out & 3)) return JIB_E_ARG;
     JIB_LAUNCH((mla_qkv_post_kernel<256>), T, 256, 0, (cudaStream_t) stream, (const bf16 *) q, q_stride, (const bf16 *) ckv, ckv_stride, kv_norm_w,
                                                                     eps, rope_table, positions, slot_mapping, (bf16 *) cache,
-                                                                    (bf16 *) q_out, H, dn, dr, r, max_pos, n_slots, status);
+                                                                    (bf16 *) q_out, qo_row, qo_head, H, dn, dr, r, max_pos, n_slots, status,
+                                                                    jib::warm_enabled());
     return launched();
 }
 

@@ -64,6 +64,7 @@ struct GemmArgs {
     int ar_rs_rows;           // two-shot: > 0 delivers each reduced row only to rank row / ar_rs_rows (reduce-scatter)
     void * const * row_ptr;   // null, or per output row the address of its bf16 row (rows scattered to other buffers,
                               // possibly on other GPUs: the expert-parallel return path)
+    int pdl_flags;            // grouped pairs: bit 0 = release dependents after the own wait, bit 1 = segment table valid at start
     int w_evict_first;        // weight tiles are loaded with the L2 evict_first policy (each is read once: small batches)
     int vec_store;            // bf16 result rows are written as 16-byte vectors through a shared-memory transpose
     const int * src_token;    // grouped, decode batches: x holds the T token rows unsorted, every expert multiplies all of
@@ -171,13 +172,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int rows_valid = args.T;         // rows of this batch's matrix
     int row_base = 0;                // grouped: offset of the expert's segment in the sorted rows
     JIB_KS(1, 0);
-    PDL_TRIGGER_TOP();
+    // Grouped launches need the segment table.  Normally the routing kernel just before produced it, so they wait first.
+    // A pair of grouped launches (gate|up, then down) shares one table: the first of the pair (pdl_flags bit 0) releases its
+    // dependents only AFTER its own wait, which tells the second (bit 1) that the table is complete when it starts -- it
+    // reads the table and requests its weight tiles before waiting for the first launch's results.
+    const bool seg_early = args.seg != nullptr && (args.pdl_flags & 2) != 0;
+    if (args.seg != nullptr && (args.pdl_flags & 1) != 0) {
+        pdl_wait();
+        pdl_launch_dependents();
+    } else {
+        PDL_TRIGGER_TOP();
+        if (args.seg != nullptr && !seg_early) pdl_wait();
+    }
     if (args.seg != nullptr) {
-        pdl_wait();                  // segment offsets are produced by the routing kernels just before
         row_base = args.seg[batch];
         rows_valid = args.seg[batch + 1] - row_base;
     }
-    if (row0 >= rows_valid) return;  // whole CTA: nothing to do (empty expert / tail tile)
+    if (row0 >= rows_valid) {        // whole CTA: nothing to do (empty expert / tail tile)
+        if (seg_early) pdl_wait();
+        return;
+    }
 
     const int num_kb = (args.K + BK - 1) / BK;
     const int kb0 = split * args.kb_per_split;
@@ -212,7 +226,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint32_t tmem = *tmem_slot;
     // Everything above touched only shared/tensor memory and launch-invariant data; activations, the residual,
     // scratch and the output belong to the stream order from here on.
-    const bool early = args.seg == nullptr;     // grouped launches waited above (they need the segment table)
+    const bool early = args.seg == nullptr || seg_early;     // other grouped launches waited above
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -808,6 +822,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     a.cluster_split = cluster_split ? 1 : 0;
     a.row_ptr = (void * const *) d->out_row_ptr;
     a.src_token = d->src_token;
+    a.pdl_flags = grouped ? d->pdl_flags : 0;
     a.w_evict_first = (t_tiles == 1 && !jib_no_evict_first()) ? 1 : 0;      // one token tile: every weight byte is used once
     // 16-byte result stores: bf16 rows whose feature offsets keep 16-byte alignment (row pointers of the expert-parallel return
     // path are row starts of bf16 matrices with d % 8 == 0, hence aligned as well)
@@ -980,6 +995,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.src_token = nullptr;
     a.vec_store = 0;
     a.w_evict_first = 0;
+    a.pdl_flags = 0;
     a.ag_flags = nullptr; a.ag_epoch = nullptr; a.ag_rows = 0; a.ag_world = 0; a.ar_rs_rows = 0; a.ag_spin_limit = 0;
     memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);

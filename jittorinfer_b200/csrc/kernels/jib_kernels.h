@@ -56,6 +56,9 @@ typedef struct jib_gemm_desc {
     int src_rows;              //   non-empty expert multiplies all of them (src_rows <= the token tile) and result row i (in the
                                //   expert-sorted order that seg describes) is the accumulator column src_token[i]: the gather of
                                //   token rows into sorted order is never materialised
+    int pdl_flags;             // grouped, two launches back to back over one segment table: 1 on the first (it lets its dependents
+                               //   start only once the table is known to be complete), 2 on the second (it may read the table and
+                               //   request weights before the first launch has finished); 0 otherwise
 } jib_gemm_desc;
 
 JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream);
@@ -72,10 +75,12 @@ JIB_EXPORT int jib_dequantize_bf16(unsigned ggml_type, const void * src, unsigne
 JIB_EXPORT int jib_embed_gather(const void * table, const int * ids, void * out, int T, int d, int n_vocab, void * stream);
 JIB_EXPORT int jib_rmsnorm(const void * x, const void * residual, const float * w, void * out_norm, void * out_sum, int T, int d,
                            long long x_stride, float eps, void * stream);
+// q_out: where the rotated RoPE part of token 0, head 0 goes; token t, head h at q_out + t * qo_row + h * qo_head (elements):
+// into the absorbed-query buffer [T][H][r + dr] at offset r, or in place into q at offset dn.
 JIB_EXPORT int jib_mla_qkv_post(const void * q, long long q_stride, const void * ckv, long long ckv_stride, const float * kv_norm_w,
                                 float eps, const float * rope_table, const int * positions, const int * slot_mapping, void * cache,
-                                void * q_out, int T, int H, int dn, int dr, int r, int max_pos, long long n_slots, int * status,
-                                void * stream);
+                                void * q_out, long long qo_row, long long qo_head, int T, int H, int dn, int dr, int r, int max_pos,
+                                long long n_slots, int * status, void * stream);
 JIB_EXPORT int jib_argmax(const float * logits, int * out, int n, int V, void * stream);
 JIB_EXPORT int jib_topk(const float * logits, float * vals, int * ids, int n, int V, int k, void * stream);
 JIB_EXPORT int jib_kv_block_copy(void * cache, long long layer_stride_elems, int n_layers, const int * src, const int * dst, int n,
@@ -118,6 +123,15 @@ JIB_EXPORT int jib_mla_combine(const float * part_o, const float * part_ml, int 
 JIB_EXPORT int jib_mla_flash(const void * q, const void * cache, long long n_slots, const int * block_tables, int max_blocks,
                              const int * seq_lens, const int * q_start, int n_seqs, int T, int H, float scale, int n_splits, int qt,
                              float * part_o, float * part_ml, void * o_lat, int * status, void * stream);
+
+// ---- prefill attention in the per-head form (mha_prefill_tcgen05.cu): head dims 128 + 64 (keys), 128 (values) ---------------
+// jib_kv_gather: lat [total_cap][row_elems] <- the cached latent rows of every sequence, in sequence order; kv_start [n_seqs].
+JIB_EXPORT int jib_kv_gather(const void * cache, long long n_slots, const int * block_tables, int max_blocks, const int * seq_lens,
+                             int n_seqs, int block_size, int row_elems, void * lat, int * kv_start, int total_cap, void * stream);
+// q [T][H][192] (RoPE applied), kv [total][H][256] = k_nope | v, kpe [total][64] (row stride kpe_stride), out [T][H * 128].
+JIB_EXPORT int jib_mha_prefill(const void * q, long long q_stride, const void * kv, const void * kpe, long long kpe_stride, long long total,
+                               const int * q_start, const int * seq_lens, const int * kv_start, int n_seqs, int T, int H, float scale,
+                               int n_q_tiles, void * out, long long ldo, int * status, void * stream);
 
 // ---- expert-parallel all-to-all over peer memory (ep_alltoall.cu); ctx is a JibEpCtx (ep_alltoall.h) ---------
 JIB_EXPORT int jib_ep_plan(const int * ids, int T, int k, const struct JibEpCtx * ctx, int site, int * seg, int * pair_dst, void * stream);

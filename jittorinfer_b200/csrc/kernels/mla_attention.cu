@@ -174,15 +174,10 @@ __global__ void __launch_bounds__(NT) mla_attn_split_kernel(const bf16 * __restr
 
 // grid (T, H); 128 threads. Merges split partials.
 template <int R>
-__global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_ml, int n_splits, int H,
-                                        bf16 * __restrict__ o_lat) {
-    JIB_KS(3, 0);
-    PDL_TRIGGER_TOP();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(3, 1);
+__device__ __noinline__ void mla_combine_head(const float * __restrict__ part_o, const float * __restrict__ part_ml, int n_splits, int H,
+                                              bf16 * __restrict__ o_lat, float * wsm, bool dry) {
     // n_splits <= 32: warp 0 turns the (m, l) pairs into normalised weights, then every thread sums its
-    // dims over the splits with independent loads.
-    __shared__ float wsm[32];
+    // dims over the splits with independent loads.  dry: same instructions, no stores (see pdl.cuh: warm_enabled).
     const int t = blockIdx.x, h = blockIdx.y;
     if (threadIdx.x < 32) {
         const int s = threadIdx.x;
@@ -214,9 +209,25 @@ __global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const
             }
         }
         __nv_bfloat162 * po = (__nv_bfloat162 *) (o_lat + ((size_t) t * H + h) * R + i);
-        po[0] = __floats2bfloat162_rn(acc.x, acc.y);
-        po[1] = __floats2bfloat162_rn(acc.z, acc.w);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        if (!dry) {
+            po[0] = lo;
+            po[1] = hi;
+        }
     }
+    __syncthreads();
+}
+
+template <int R>
+__global__ void mla_attn_combine_kernel(const float * __restrict__ part_o, const float * __restrict__ part_ml, int n_splits, int H,
+                                        bf16 * __restrict__ o_lat, int warm) {
+    JIB_KS(3, 0);
+    PDL_TRIGGER_TOP();
+    __shared__ float wsm[32];
+    if (warm) mla_combine_head<R>(part_o, part_ml, n_splits, H, o_lat, wsm, true);
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(3, 1);
+    mla_combine_head<R>(part_o, part_ml, n_splits, H, o_lat, wsm, false);
     JIB_KS(3, 9);
 }
 
@@ -247,7 +258,7 @@ extern "C" int jib_mla_attention(const void * q, const void * cache, const int *
                                                               part_ml, (bf16 *) o_lat);                                          \
         if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;                                                              \
         if (n_splits > 1) {                                                                                                      \
-            JIB_LAUNCH((mla_attn_combine_kernel<R_>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat);                \
+            JIB_LAUNCH((mla_attn_combine_kernel<R_>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_enabled());                \
             if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;                                                          \
         }                                                                                                                        \
         return 0;                                                                                                                \
@@ -264,8 +275,8 @@ extern "C" int jib_mla_combine(const float * part_o, const float * part_ml, int 
     if (T <= 0) return 0;
     if (n_splits < 1 || n_splits > 32) return JIB_E_ARG;
     cudaStream_t s = (cudaStream_t) stream;
-    if (r == 512) JIB_LAUNCH((mla_attn_combine_kernel<512>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat);
-    else if (r == 64) JIB_LAUNCH((mla_attn_combine_kernel<64>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat);
+    if (r == 512) JIB_LAUNCH((mla_attn_combine_kernel<512>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_enabled());
+    else if (r == 64) JIB_LAUNCH((mla_attn_combine_kernel<64>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_enabled());
     else return JIB_E_ARG;
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }

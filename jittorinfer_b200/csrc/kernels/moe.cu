@@ -42,9 +42,9 @@ struct alignas(16) bf16x8 {
     __nv_bfloat162 v[4];
 };
 
-__device__ __forceinline__ void router_rows(const bf16 * __restrict__ x, const float * __restrict__ w_router, const float * __restrict__ norm_w,
+__device__ __noinline__ void router_rows(const bf16 * __restrict__ x, const float * __restrict__ w_router, const float * __restrict__ norm_w,
                                             float eps, bf16 * __restrict__ g_out, float * __restrict__ logits, int t_begin, int t_end,
-                                            int T, int d, int E, int e, float (*red)[GATE_TG], float * inv_s) {
+                                            int T, int d, int E, int e, float (*red)[GATE_TG], float * inv_s, bool dry = false) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nv = d / 8;
     float4 w[GATE_MAXC][2];
@@ -112,7 +112,7 @@ __device__ __forceinline__ void router_rows(const bf16 * __restrict__ x, const f
                         a.v[1] = __floats2bfloat162_rn(f1.x * inv * nw[c][0].z, f1.y * inv * nw[c][0].w);
                         a.v[2] = __floats2bfloat162_rn(f2.x * inv * nw[c][1].x, f2.y * inv * nw[c][1].y);
                         a.v[3] = __floats2bfloat162_rn(f3.x * inv * nw[c][1].z, f3.y * inv * nw[c][1].w);
-                        if (g_out != nullptr && t0 + j < t_end && (t0 + j) % (int) gridDim.x == (int) blockIdx.x)
+                        if (g_out != nullptr && !dry && t0 + j < t_end && (t0 + j) % (int) gridDim.x == (int) blockIdx.x)
                             ((bf16x8 *) (g_out + (size_t) (t0 + j) * d))[i] = a;
                     }
                     const float2 f0 = __bfloat1622float2(a.v[0]), f1 = __bfloat1622float2(a.v[1]);
@@ -132,7 +132,7 @@ __device__ __forceinline__ void router_rows(const bf16 * __restrict__ x, const f
             float s = 0.f;
 #pragma unroll
             for (int q = 0; q < GATE_NT / 32; ++q) s += red[q][threadIdx.x];
-            logits[(size_t) (t0 + threadIdx.x) * E + e] = s;
+            if (!dry) logits[(size_t) (t0 + threadIdx.x) * E + e] = s;
         }
         __syncthreads();
     }
@@ -140,12 +140,15 @@ __device__ __forceinline__ void router_rows(const bf16 * __restrict__ x, const f
 
 // grid (E, ceil(T/64))
 __global__ void __launch_bounds__(GATE_NT) router_logits_kernel(const bf16 * __restrict__ g, const float * __restrict__ w_router,
-                                                                float * __restrict__ logits, int T, int d, int E) {
+                                                                float * __restrict__ logits, int T, int d, int E, int warm) {
     JIB_KS(9, 0);
     PDL_TRIGGER_TOP();
+    __shared__ float red[GATE_NT / 32][GATE_TG];
+    if (warm)          // one token group, no stores: the code and this expert's router row are on the SM before the inputs are
+        router_rows(g, w_router, nullptr, 0.f, nullptr, logits, blockIdx.y * 64, min(T, (int) blockIdx.y * 64 + GATE_TG), T, d, E,
+                    blockIdx.x, red, nullptr, true);
     pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
     JIB_KS(9, 1);
-    __shared__ float red[GATE_NT / 32][GATE_TG];
     router_rows(g, w_router, nullptr, 0.f, nullptr, logits, blockIdx.y * 64, min(T, (int) (blockIdx.y + 1) * 64), T, d, E, blockIdx.x, red,
                 nullptr);
     JIB_KS(9, 9);
@@ -250,15 +253,22 @@ __device__ __noinline__ void gate_token(const float * __restrict__ logits_row, c
 __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__ logits, const float * __restrict__ bias,
                                                       int * __restrict__ ids, float * __restrict__ wts, int E, int k, int n_group,
                                                       int topk_group, float scale, int norm, int sigmoid, int n_shared,
-                                                      int group_top2) {
+                                                      int group_top2, int warm) {
     JIB_KS(10, 0);
     PDL_TRIGGER_TOP();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(10, 1);
     __shared__ float prob[MAX_E];
     __shared__ float sel[MAX_E];
     __shared__ float gscore[32];
     const int t = blockIdx.x;
+    if (warm) {
+        for (int e = threadIdx.x & 31; e < MAX_E; e += 32) prob[e] = (float) ((e * 37 + t) & 63);
+        __syncwarp();
+        gate_token(nullptr, bias == nullptr ? nullptr : (const float *) prob, nullptr, nullptr, 0, E, k, n_group, topk_group, scale, norm,
+                   sigmoid, n_shared, group_top2, prob, sel, gscore, nullptr, true);
+        __syncwarp();
+    }
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(10, 1);
     gate_token(logits + (size_t) t * E, bias, ids, wts, t, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2, prob,
                sel, gscore);
     JIB_KS(10, 9);
@@ -327,14 +337,21 @@ __device__ __noinline__ void sort_pairs(const int * __restrict__ ids, int n, int
 }
 
 __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
-                                                          int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest) {
+                                                          int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest,
+                                                          int warm) {
     JIB_KS(11, 0);
     PDL_TRIGGER_TOP();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(11, 1);
     __shared__ int count[MAX_E + 1];
     __shared__ int offs[MAX_E + 1];
     __shared__ int ids_s[SORT_SMEM_MAX];
+    if (warm) {
+        for (int i = threadIdx.x; i < 32; i += blockDim.x) ids_s[i] = expert_base + (i % max(E_local, 1));
+        __syncthreads();
+        sort_pairs(ids_s, min(n, 32), k, expert_base, E_local, nullptr, nullptr, nullptr, count, offs, true);
+        __syncthreads();
+    }
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(11, 1);
     if (n <= SORT_SMEM_MAX) {
         for (int i = threadIdx.x; i < n; i += blockDim.x) ids_s[i] = ids[i];
         __syncthreads();
@@ -495,20 +512,17 @@ __global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * _
 }
 
 // out[t] = residual[t] + shared[t] + sum_j wts[t][j] * y[dest[t][j]]   (fp32 accumulate, bf16 out)
-__global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
-                                   const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
-                                   int d) {
-    JIB_KS(12, 0);
-    PDL_TRIGGER_TOP();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(12, 1);
+// dry: the same instructions with row 0 in place of the sorted-row indices (which are not valid yet) and no stores.
+__device__ __noinline__ void moe_combine_row(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
+                                             const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out,
+                                             int k, int d, bool dry) {
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < d / 8; i += blockDim.x) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         for (int j = 0; j < k; ++j) {
-            const int row = dest[(size_t) t * k + j];
+            const int row = dry ? 0 : dest[(size_t) t * k + j];
             JIB_BC(row < (int) gridDim.x * k, 14, row);
             if (row < 0) continue;
             const float w = wts[(size_t) t * k + j];
@@ -545,8 +559,19 @@ __global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __re
         __nv_bfloat162 * po = (__nv_bfloat162 *) &o;
 #pragma unroll
         for (int q = 0; q < 4; ++q) po[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-        ((uint4 *) (out + (size_t) t * d))[i] = o;
+        if (!dry) ((uint4 *) (out + (size_t) t * d))[i] = o;
     }
+}
+
+__global__ void moe_combine_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
+                                   const bf16 * __restrict__ shared, const bf16 * __restrict__ residual, bf16 * __restrict__ out, int k,
+                                   int d, int warm) {
+    JIB_KS(12, 0);
+    PDL_TRIGGER_TOP();
+    if (warm) moe_combine_row(y, dest, wts, shared, residual, out, k, d, true);
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(12, 1);
+    moe_combine_row(y, dest, wts, shared, residual, out, k, d, false);
     JIB_KS(12, 9);
 }
 
@@ -568,16 +593,10 @@ __device__ __forceinline__ float block_sum_nt(float v, float * red) {
 }
 
 template <int NT, int MAXV>
-__global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest,
-                                                              const float * __restrict__ wts, const bf16 * __restrict__ shared,
-                                                              const bf16 * __restrict__ residual, const float * __restrict__ norm_w,
-                                                              bf16 * __restrict__ out, bf16 * __restrict__ out_norm, int k, int d,
-                                                              float eps) {
-    JIB_KS(13, 0);
-    PDL_TRIGGER_TOP();
-    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
-    JIB_KS(13, 1);
-    __shared__ float red[32];
+__device__ __noinline__ void moe_combine_norm_row(const bf16 * __restrict__ y, const int * __restrict__ dest, const float * __restrict__ wts,
+                                                  const bf16 * __restrict__ shared, const bf16 * __restrict__ residual,
+                                                  const float * __restrict__ norm_w, bf16 * __restrict__ out, bf16 * __restrict__ out_norm,
+                                                  int k, int d, float eps, float * red, bool dry) {
     const int t = blockIdx.x;
     const int nv = d / 8;
     float vals[MAXV][8];
@@ -590,7 +609,7 @@ __global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __res
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
             for (int j = 0; j < k; ++j) {
-                const int row = dest[(size_t) t * k + j];
+                const int row = dry ? 0 : dest[(size_t) t * k + j];
                 if (row < 0) continue;
                 const float w = wts[(size_t) t * k + j];
                 const uint4 raw = ((const uint4 *) (y + (size_t) row * d))[i];
@@ -626,7 +645,7 @@ __global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __res
             __nv_bfloat162 * po = (__nv_bfloat162 *) &o;
 #pragma unroll
             for (int q = 0; q < 4; ++q) po[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-            ((uint4 *) (out + (size_t) t * d))[i] = o;
+            if (!dry) ((uint4 *) (out + (size_t) t * d))[i] = o;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {                 // the norm sees what the next kernel would have read back
                 const float2 f = __bfloat1622float2(po[q]);
@@ -649,9 +668,24 @@ __global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __res
             po[1] = __floats2bfloat162_rn(vals[it][2] * inv * w0.z, vals[it][3] * inv * w0.w);
             po[2] = __floats2bfloat162_rn(vals[it][4] * inv * w1.x, vals[it][5] * inv * w1.y);
             po[3] = __floats2bfloat162_rn(vals[it][6] * inv * w1.z, vals[it][7] * inv * w1.w);
-            ((uint4 *) (out_norm + (size_t) t * d))[i] = o;
+            if (!dry) ((uint4 *) (out_norm + (size_t) t * d))[i] = o;
         }
     }
+}
+
+template <int NT, int MAXV>
+__global__ void __launch_bounds__(NT) moe_combine_norm_kernel(const bf16 * __restrict__ y, const int * __restrict__ dest,
+                                                              const float * __restrict__ wts, const bf16 * __restrict__ shared,
+                                                              const bf16 * __restrict__ residual, const float * __restrict__ norm_w,
+                                                              bf16 * __restrict__ out, bf16 * __restrict__ out_norm, int k, int d,
+                                                              float eps, int warm) {
+    JIB_KS(13, 0);
+    PDL_TRIGGER_TOP();
+    __shared__ float red[32];
+    if (warm) moe_combine_norm_row<NT, MAXV>(y, dest, wts, shared, residual, norm_w, out, out_norm, k, d, eps, red, true);
+    pdl_wait();      // inputs come from earlier kernels; nothing is written before this point
+    JIB_KS(13, 1);
+    moe_combine_norm_row<NT, MAXV>(y, dest, wts, shared, residual, norm_w, out, out_norm, k, d, eps, red, false);
     JIB_KS(13, 9);
 }
 
@@ -678,9 +712,11 @@ int jib_moe_gate(const void * g, const float * w_router, const float * bias, flo
                  void * stream) {
     if (T <= 0) return 0;
     if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 8 || d > GATE_MAXC * GATE_NT * 8 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
-    JIB_LAUNCH((router_logits_kernel), dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, logits, T, d, E);
+    JIB_LAUNCH((router_logits_kernel), dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, logits, T, d, E,
+               jib::warm_enabled());
     if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;
-    JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2);
+    JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2,
+               jib::warm_enabled());
     return launched();
 }
 
@@ -704,7 +740,8 @@ int jib_moe_route_fused(const void * g, const float * w_router, const float * bi
 int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest, void * stream) {
     if (T <= 0) return 0;
     if (E_local > MAX_E) return JIB_E_ARG;
-    JIB_LAUNCH((moe_permute_kernel), 1, 1024, 0, (cudaStream_t) stream, ids, T * k, k, expert_base, E_local, seg, src_token, dest);
+    JIB_LAUNCH((moe_permute_kernel), 1, 1024, 0, (cudaStream_t) stream, ids, T * k, k, expert_base, E_local, seg, src_token, dest,
+               jib::warm_enabled());
     return launched();
 }
 
@@ -729,7 +766,7 @@ int jib_moe_combine(const void * y, const int * dest, const float * wts, const v
     if (T <= 0) return 0;
     if (d % 8) return JIB_E_ARG;
     JIB_LAUNCH((moe_combine_kernel), T, 256, 0, (cudaStream_t) stream, (const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual,
-                                                              (bf16 *) out, k, d);
+                                                              (bf16 *) out, k, d, jib::warm_enabled());
     return launched();
 }
 
@@ -742,7 +779,7 @@ int jib_moe_combine_norm(const void * y, const int * dest, const float * wts, co
     cudaStream_t s = (cudaStream_t) stream;
 #define JIB_CN(NT, MAXV)                                                                                                         \
     JIB_LAUNCH((moe_combine_norm_kernel<NT, MAXV>), T, NT, 0, s, (const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual, \
-               norm_w, (bf16 *) out, (bf16 *) out_norm, k, d, eps)
+               norm_w, (bf16 *) out, (bf16 *) out_norm, k, d, eps, jib::warm_enabled())
     if (nv <= 128) JIB_CN(128, 1);            // the same (threads, values per thread) choice as jib_rmsnorm
     else if (nv <= 256) JIB_CN(256, 1);
     else if (nv <= 1024) JIB_CN(256, 4);

@@ -57,6 +57,18 @@ inline bool ensure_dyn_smem(K kern, int bytes, std::atomic<unsigned char> (&done
     return true;
 }
 
+// Small latency-bound kernels run their body twice: once "dry" (same instructions, no stores, indices that come from memory
+// replaced by safe ones) while they still wait for the previous kernel, then for real.  A kernel's first pass over cold code
+// costs an instruction-cache miss every few instructions; the dry pass takes those misses in the shadow of the previous
+// kernel.  JIB_WARM=0 turns the dry passes off (A/B measurements).
+inline int warm_enabled() {
+    static const int on = [] {
+        const char * e = getenv("JIB_WARM");
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
+    }();
+    return on;
+}
+
 // cluster_z > 1: consecutive blockIdx.z values form a thread-block cluster of that size.
 template <typename... P, typename... A>
 inline cudaError_t launch_pdl_cluster(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_z,

@@ -32,6 +32,8 @@ FUSED_COMBINE_NORM = os.environ.get("JIB_FUSED_COMBINE_NORM", "1") == "1"
 # Decode batches: the grouped gate|up GEMM reads the token rows in place (no gather into expert order).
 GROUPED_SRC = os.environ.get("JIB_GROUPED_SRC", "1") == "1"
 GROUPED_SRC_MAX_T = 64
+# The down-projection launch reads the segment table and requests its weights before the gate|up launch has finished.
+GROUPED_PAIR = os.environ.get("JIB_GROUPED_PAIR", "1") == "1"
 # The router launch of a decode batch also applies the RMSNorm of its input ("0": a separate norm launch before it).
 ROUTE_NORM = os.environ.get("JIB_ROUTE_NORM", "1") == "1"
 FUSED_ROUTE_MAX_T = 64
@@ -50,7 +52,7 @@ class GemmDesc(C.Structure):
                                        "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p), ("out_row_ptr", C.c_void_p), ("ag_flags", C.c_void_p),
                                                                              ("ag_epoch", C.c_void_p), ("ag_rows", C.c_int),
                                                                              ("ag_world", C.c_int), ("ar_rs_rows", C.c_int),
-                                                                             ("src_token", C.c_void_p), ("src_rows", C.c_int)]
+                                                                             ("src_token", C.c_void_p), ("src_rows", C.c_int), ("pdl_flags", C.c_int)]
 
 
 def load():
@@ -72,7 +74,9 @@ def load():
     sig("jib_gemm_bf16", C.POINTER(GemmDesc), vp)
     sig("jib_embed_gather", vp, ip, vp, i, i, i, vp)
     sig("jib_rmsnorm", vp, vp, fp, vp, vp, i, i, ll, f, vp)
-    sig("jib_mla_qkv_post", vp, ll, vp, ll, fp, f, fp, ip, ip, vp, vp, i, i, i, i, i, i, ll, ip, vp)
+    sig("jib_mla_qkv_post", vp, ll, vp, ll, fp, f, fp, ip, ip, vp, vp, ll, ll, i, i, i, i, i, i, ll, ip, vp)
+    sig("jib_kv_gather", vp, ll, ip, i, ip, i, i, i, vp, ip, i, vp)
+    sig("jib_mha_prefill", vp, ll, vp, vp, ll, ll, ip, ip, ip, i, i, i, f, i, vp, ll, ip, vp)
     sig("jib_argmax", fp, ip, i, i, vp)
     sig("jib_topk", fp, fp, ip, i, i, i, vp)
     sig("jib_sample_topk", fp, ip, fp, ip, i, i, vp)
@@ -215,7 +219,8 @@ def gemm_batched(x_ptr: int, x_row_stride: int, x_batch_stride: int, w: torch.Te
 
 def gemm_grouped_raw(x_ptr: int, x_rows_total: int, K: int, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor],
                      max_rows: int, active_hint: int, splits: int = 0, bn: int = 0, device=None,
-                     out_row_ptr: Optional[int] = None, src_token: Optional[torch.Tensor] = None, src_rows: int = 0) -> Optional[torch.Tensor]:
+                     out_row_ptr: Optional[int] = None, src_token: Optional[torch.Tensor] = None, src_rows: int = 0,
+                     pdl_flags: int = 0) -> Optional[torch.Tensor]:
     """Grouped GEMM over a raw row buffer (e.g. a peer-mapped receive buffer).  With ``out_row_ptr`` (device array of
     row addresses) every result row is stored through its pointer and nothing is returned.  With ``src_token`` the
     buffer holds the ``src_rows`` token rows unsorted and sorted result row i is computed from token ``src_token[i]``
@@ -237,15 +242,17 @@ def gemm_grouped_raw(x_ptr: int, x_rows_total: int, K: int, seg: torch.Tensor, w
     d.out_row_ptr = out_row_ptr
     if src_token is not None:
         d.src_token, d.src_rows = src_token.data_ptr(), src_rows
+    d.pdl_flags = pdl_flags
     _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_grouped")
     return out
 
 
 def gemm_grouped(xp: torch.Tensor, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor], max_rows: int,
-                 active_hint: int, splits: int = 0) -> torch.Tensor:
+                 active_hint: int, splits: int = 0, pdl_flags: int = 0) -> torch.Tensor:
     """Rows of xp are sorted by expert; expert e owns rows seg[e]:seg[e+1] and weight w[e] ([E,N,K])."""
     assert xp.stride(0) == xp.shape[1] and xp.stride(1) == 1
-    return gemm_grouped_raw(xp.data_ptr(), xp.shape[0], xp.shape[1], seg, w, w2, max_rows, active_hint, splits, device=xp.device)
+    return gemm_grouped_raw(xp.data_ptr(), xp.shape[0], xp.shape[1], seg, w, w2, max_rows, active_hint, splits, device=xp.device,
+                            pdl_flags=pdl_flags)
 
 
 def linear(x, w, residual=None, out_dtype=None):
@@ -275,11 +282,16 @@ def rmsnorm(x, w, eps, residual=None):
 
 
 def mla_qkv_post(q, ckv, kv_norm_w, eps, rope_table, positions, slot_mapping, cache, q_out, n_head, dn, dr, r):
+    """``q_out`` None: the rotated RoPE part of q is written back into q (the per-head prefill form reads q as it is)."""
     T = q.shape[0]
     ws = workspace(q.device)
+    if q_out is None:
+        qo_ptr, qo_row, qo_head = q.data_ptr() + dn * 2, q.stride(0), dn + dr
+    else:
+        qo_ptr, qo_row, qo_head = q_out.data_ptr() + r * 2, n_head * (r + dr), r + dr
     _ck(load().jib_mla_qkv_post(q.data_ptr(), q.stride(0), ckv.data_ptr(), ckv.stride(0), kv_norm_w.data_ptr(), float(eps),
                                 rope_table.data_ptr(), positions.data_ptr(), slot_mapping.data_ptr(), cache.data_ptr(),
-                                q_out.data_ptr(), T, n_head, dn, dr, r, rope_table.shape[0], cache.shape[0],
+                                qo_ptr, qo_row, qo_head, T, n_head, dn, dr, r, rope_table.shape[0], cache.shape[0],
                                 ws.status.data_ptr(), _stream()), "mla_qkv_post")
     return q.view(T, n_head, dn + dr)[..., :dn] if q.is_contiguous() else q.as_strided((T, n_head, dn), (q.stride(0), dn + dr, 1))
 
@@ -339,6 +351,38 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
                                  seq_lens.data_ptr(), q_start.data_ptr(), n_seqs, T, H, r, D - r, block_size, float(scale),
                                  n_splits, _p(part_o), _p(part_ml), o.data_ptr(), _stream()), "mla_attention")
     return o
+
+
+MHA_PREFILL = os.environ.get("JIB_MHA_PREFILL", "1") == "1"      # "0": prompt chunks use the absorbed form as well (A/B)
+MHA_PREFILL_MIN_TOKENS = 64
+
+
+def mha_prefill_ok(T: int, dn: int, dr: int, dv: int, r: int, block_size: int, meta) -> bool:
+    """Whether a chunk of T query tokens takes the per-head prefill attention (needs the host-side totals in ``meta``)."""
+    return bool(MHA_PREFILL and meta is not None and T >= MHA_PREFILL_MIN_TOKENS and dn == 128 and dr == 64 and dv == 128 and r == 512
+                and meta.get("total_kv", 0) > 0)
+
+
+def mha_prefill(q, cache, w_kv_b, block_tables, seq_lens, q_start, scale, n_head, block_size, meta):
+    """Causal multi-head attention of a prompt chunk in the per-head form.  q [T, H*192] (RoPE already applied in place; may
+    be a strided view), cache [n_slots, 576] one layer's latent rows, w_kv_b [H*256, 512].  ``meta``: host-side totals of the
+    batch, {"total_kv": sum of seq_lens, "n_q_tiles": upper bound of sum ceil(q_len / 128)}.  Returns [T, H*128] bf16."""
+    T = q.shape[0]
+    n_seqs = seq_lens.shape[0]
+    total = int(meta["total_kv"])
+    row = cache.shape[1]
+    dev = q.device
+    lat = torch.empty(total, row, dtype=torch.bfloat16, device=dev)
+    kv_start = torch.empty(n_seqs, dtype=torch.int32, device=dev)
+    _ck(load().jib_kv_gather(cache.data_ptr(), cache.shape[0], block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(),
+                             n_seqs, block_size, row, lat.data_ptr(), kv_start.data_ptr(), total, _stream()), "kv_gather")
+    kv = gemm(lat[:, :512], w_kv_b)                     # [total, H*256]: k_nope | v per head
+    out = torch.empty(T, n_head * 128, dtype=torch.bfloat16, device=dev)
+    ws = workspace(dev)
+    _ck(load().jib_mha_prefill(q.data_ptr(), q.stride(0), kv.data_ptr(), lat.data_ptr() + 512 * 2, row, total, q_start.data_ptr(),
+                               seq_lens.data_ptr(), kv_start.data_ptr(), n_seqs, T, n_head, float(scale), int(meta["n_q_tiles"]),
+                               out.data_ptr(), out.stride(0), ws.status.data_ptr(), _stream()), "mha_prefill")
+    return out
 
 
 # ---- MoE -----------------------------------------------------------------------------------------
@@ -440,16 +484,19 @@ def moe_routed(x, ids, wts, wg, wu, wd, expert_base=0, n_expert=None):
     T, k = ids.shape
     E_local = wg.shape[0]
     seg, src, dest = moe_permute(ids, expert_base, E_local)
+    # the two grouped launches run back to back over one segment table: the second may start on its weights early
+    pair = (1, 2) if GROUPED_PAIR else (0, 0)
     active = min(E_local, T * k)
     if ACTIVE_HINT_EXPECTED and n_expert:        # split-K sized for the experts a batch is expected to hit, not for all
         active = min(active, expected_active_experts(T, k, E_local, n_expert))
     if GROUPED_SRC and T <= GROUPED_SRC_MAX_T and x.is_contiguous():
         # decode batches: every expert that has rows multiplies the whole (tiny) token tile and picks its tokens' columns in the
         # epilogue, so the token rows are never gathered into expert order
-        h = gemm_grouped_raw(x.data_ptr(), T * k, x.shape[1], seg, wg, wu, T, active, device=x.device, src_token=src, src_rows=T)
+        h = gemm_grouped_raw(x.data_ptr(), T * k, x.shape[1], seg, wg, wu, T, active, device=x.device, src_token=src, src_rows=T,
+                             pdl_flags=pair[0])
     else:
-        h = gemm_grouped(gather_rows(x, src), seg, wg, wu, T, active)
-    y = gemm_grouped(h, seg, wd, None, T, active)
+        h = gemm_grouped(gather_rows(x, src), seg, wg, wu, T, active, pdl_flags=pair[0])
+    y = gemm_grouped(h, seg, wd, None, T, active, pdl_flags=pair[1])
     return y, dest
 
 

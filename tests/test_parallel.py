@@ -200,8 +200,8 @@ def test_v2_shapes_two_gpus_logits_match_single_gpu(comm_impl):
     cache = torch.zeros(hp.n_layer, 8 * 64, hp.kv_row, dtype=torch.bfloat16, device=dev)
     one = m.forward(_logits_batch(40, dev), cache).float().cpu()
     err = (res[0][6] - one).abs().amax(dim=-1) / one.abs().amax(dim=-1).clamp_min(1e-6)
-    tight = (err <= 2e-2).float().mean().item()
-    print(f"v2-2l tp2+ep2 ({comm_impl}) vs 1 GPU: rows within 2e-2: {tight:.3f}, median {err.median().item():.4f}, worst {err.max().item():.3f}")
+    tight = (err <= 3e-2).float().mean().item()
+    print(f"v2-2l tp2+ep2 ({comm_impl}) vs 1 GPU: rows within 3e-2: {tight:.3f}, median {err.median().item():.4f}, worst {err.max().item():.3f}")
     assert tight >= 0.9 and err.max().item() < 0.5
 
 

@@ -8,6 +8,8 @@ import sys
 import time
 import urllib.request
 
+import pytest
+
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -124,6 +126,67 @@ def test_mpi_server_launcher_two_cpu_ranks(tmp_path):
         prompt = torch.randint(1, hp.n_vocab, (15,), generator=torch.Generator().manual_seed(9)).tolist()
         out = _post(url + "/v1/completions", {"prompt": prompt, "max_tokens": 5, "temperature": 0, "ignore_eos": True, "return_tokens": True})
         assert out["choices"][0]["tokens"] == OracleModel(hp, random_weights(hp, seed=0)).generate(prompt, 5)
+        try:
+            urllib.request.urlopen(url + "/exit", timeout=10).read()
+        except Exception:
+            pass
+        assert p.wait(timeout=120) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()               # our own child, by handle
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dp", [False, True])
+def test_mpi_server_two_gpus_serves_over_http(tmp_path, dp):
+    """The multi-process server on two GPUs with the in-kernel collectives and CUDA graphs: tensor + expert parallel ranks with
+    identical schedulers, or (dp) data-parallel attention with the routed experts reached through the all-to-all dispatcher.
+    Several requests at once over HTTP; tokens against the fp32 oracle (bf16 weights); ``GET /exit`` stops every rank."""
+    import subprocess
+    import threading
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from jittorinfer_b200.models.hparams import preset
+    from jittorinfer_b200.models.oracle import OracleModel
+    from jittorinfer_b200.models.weights import random_weights
+    hport, mport = _free_port(), _free_port()
+    cfg = tmp_path / "c.yaml"
+    cfg.write_text(f"random_init: tiny-v2\nn_ctx: 2048\nn_parallel: 4\nn_batch: 64\nport: {hport}\nenable_ge: true\ntp_size: 2\nep_size: 2\n"
+                   + ("attention_dp: true\n" if dp else ""))
+    env = dict(os.environ, JITTORINFER_COMM="fused", NCCL_NVLS_ENABLE="0", JITTORINFER_HEARTBEAT_TIMEOUT="30")
+    p = subprocess.Popen([sys.executable, "-m", "jittorinfer_b200.server.mpi_server", "--nproc", "2", "--master-port", str(mport),
+                          "-c", str(cfg)], cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        url = f"http://127.0.0.1:{hport}"
+        deadline = time.time() + 240
+        up = False
+        while time.time() < deadline:
+            try:
+                if urllib.request.urlopen(url + "/health", timeout=2).status == 200:
+                    up = True
+                    break
+            except Exception:
+                assert p.poll() is None, p.stdout.read()[-3000:]
+                time.sleep(0.5)
+        assert up, "server did not come up"
+        hp = preset("tiny-v2")
+        g = torch.Generator().manual_seed(9)
+        prompts = [torch.randint(1, hp.n_vocab, (n,), generator=g).tolist() for n in (15, 40, 7, 22)]
+        outs = [None] * len(prompts)
+
+        def ask(i):
+            outs[i] = _post(url + "/v1/completions", {"prompt": prompts[i], "max_tokens": 6, "temperature": 0, "ignore_eos": True,
+                                                      "return_tokens": True})["choices"][0]["tokens"]
+        ths = [threading.Thread(target=ask, args=(i,)) for i in range(len(prompts))]
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join(timeout=120)
+        o = OracleModel(hp, {k: v.bfloat16().float() for k, v in random_weights(hp, seed=0).items()})
+        for pr, got in zip(prompts, outs):
+            want = o.generate(pr, 6)
+            assert got is not None and len(got) == 6 and got[0] == want[0], (got, want)
+            assert sum(int(a == b) for a, b in zip(got, want)) >= 3, (got, want)
         try:
             urllib.request.urlopen(url + "/exit", timeout=10).read()
         except Exception:
