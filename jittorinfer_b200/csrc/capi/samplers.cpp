@@ -258,7 +258,8 @@ void xtc_reset(llama_sampler * s) {
 llama_sampler * xtc_clone(const llama_sampler * s) {
     auto * c = (XtcCtx *) s->ctx;
     llama_sampler * r = llama_sampler_init_xtc(c->p, c->t, c->min_keep, c->seed);
-    ((XtcCtx *) r->ctx)->rng = c->rng;
+    ((XtcCtx *) r->ctx)->rng = c->rng;                 // the clone continues the same random stream ...
+    ((XtcCtx *) r->ctx)->seed_cur = c->seed_cur;       // ... and reports the seed that stream started from
     return r;
 }
 const llama_sampler_i xtc_i = {xtc_name, nullptr, xtc_apply, xtc_reset, xtc_clone, free_ctx<XtcCtx>};

@@ -64,6 +64,8 @@ struct GemmArgs {
     int ar_rs_rows;           // two-shot: > 0 delivers each reduced row only to rank row / ar_rs_rows (reduce-scatter)
     void * const * row_ptr;   // null, or per output row the address of its bf16 row (rows scattered to other buffers,
                               // possibly on other GPUs: the expert-parallel return path)
+    const int * expert_list;  // grouped: null, or the experts the grid's z slots stand for (device; -1 = unused slot)
+    int list_tiles;           // the list holds (token tile << 16 | expert) entries and gridDim.y is 1
     int pdl_flags;            // grouped pairs: bit 0 = release dependents after the own wait, bit 1 = segment table valid at start
     int w_evict_first;        // weight tiles are loaded with the L2 evict_first policy (each is read once: small batches)
     int vec_store;            // bf16 result rows are written as 16-byte vectors through a shared-memory transpose
@@ -166,9 +168,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
     const int n0 = blockIdx.x * BM;
     const int splits = args.splits;
-    const int batch = blockIdx.z / splits;
-    const int split = blockIdx.z - batch * splits;
-    int row0 = blockIdx.y * BN;      // first token row of this tile, relative to the segment / matrix
+    const int slot = blockIdx.z / splits;          // batch index, or (grouped with an expert list) position in that list
+    const int split = blockIdx.z - slot * splits;
+    int batch = slot;
+    int row0 = blockIdx.y * BN;      // first token row of this tile, relative to the segment / matrix (list_tiles: from the list)
     int rows_valid = args.T;         // rows of this batch's matrix
     int row_base = 0;                // grouped: offset of the expert's segment in the sorted rows
     JIB_KS(1, 0);
@@ -185,8 +188,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (args.seg != nullptr && !seg_early) pdl_wait();
     }
     if (args.seg != nullptr) {
-        row_base = args.seg[batch];
-        rows_valid = args.seg[batch + 1] - row_base;
+        // decode batches hit few of the experts: the grid then covers a list of the experts that have rows (written by the
+        // sort next to the segment table, -1 past its end) instead of all of them
+        if (args.expert_list != nullptr) {
+            batch = args.expert_list[slot];
+            if (args.list_tiles && batch >= 0) {       // entry = token tile << 16 | expert: the grid walks (expert, tile) pairs
+                row0 = (batch >> 16) * BN;
+                batch &= 0xffff;
+            }
+        }
+        if (batch < 0) {
+            rows_valid = 0;
+        } else {
+            row_base = args.seg[batch];
+            rows_valid = args.seg[batch + 1] - row_base;
+        }
     }
     if (row0 >= rows_valid) {        // whole CTA: nothing to do (empty expert / tail tile)
         if (seg_early) pdl_wait();
@@ -335,7 +351,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tc_fence_after();
         JIB_KS_T(1, 4, 64);
         const uint32_t tbase = tmem + ((uint32_t) (q * 32) << 16);
-        const int tile_id = (batch * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        const int tile_id = (slot * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
         if (args.ar_on != 0 && (threadIdx.x & 127) == 0) JIB_TS(30, args.ar_site, tile_id, split);
         constexpr int ACC = DUAL ? 2 : 1;
         float * part = nullptr;
@@ -550,6 +566,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         const long long row = row_base + row0 + col;
                         if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 5, (int) row); continue; }
                         float4 a = *(const float4 *) (sb + tok * BM + fg), b = *(const float4 *) (sb + tok * BM + fg + 4);
+                        if (args.ar_on) {
+                            // fused all-reduce: the fp32 partial goes to slot [rank] of every peer (one-shot) or of the
+                            // tile's owner (two-shot) as 16-byte stores; the residual is added after the reduction
+                            if (args.ar_on == 2) {
+                                float * dst = args.ar.recv2[ar_owner] + ar_par + ((size_t) args.ar.rank * args.ar.max_rows2 + row) * args.ar.d_max + nn;
+                                *(float4 *) dst = a;
+                                *(float4 *) (dst + 4) = b;
+                            } else {
+                                const size_t off = ar_par + ((size_t) args.ar.rank * args.ar.max_rows + row) * args.ar.d_max + nn;
+                                for (int p = 0; p < args.ar.world; ++p) {
+                                    *(float4 *) (args.ar.recv[p] + off) = a;
+                                    *(float4 *) (args.ar.recv[p] + off + 4) = b;
+                                }
+                            }
+                            continue;
+                        }
                         if (args.residual != nullptr) {
                             const long long ri = rbase + row * args.ldr + nn;
                             if (args.res_f32) {
@@ -787,7 +819,11 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     int kbps = (num_kb + splits - 1) / splits;
     splits = (num_kb + kbps - 1) / kbps;                        // no empty split
     const bool cluster_split = cluster_ok && splits > 1 && splits <= 8;
-    const long long tiles_total = (long long) n_tiles * t_tiles * batch;
+    const bool list_tiles = grouped && d->expert_list != nullptr && d->list_tiles != 0 && d->n_slots > 0;
+    if (list_tiles && (batch > 0xffff || d->bn == 0)) return JIB_E_ARG;      // the list was built for one token-tile width
+    const int n_slots = list_tiles ? d->n_slots
+                                   : (grouped && d->expert_list != nullptr && d->n_slots > 0 && d->n_slots < batch) ? d->n_slots : batch;
+    const long long tiles_total = (long long) n_tiles * (list_tiles ? 1 : t_tiles) * n_slots;
     if (splits > 1 && !cluster_split) {
         const size_t need = (size_t) tiles_total * splits * (dual ? 2 : 1) * bn * BM * sizeof(float);
         if (d->scratch == nullptr || need > d->scratch_bytes || tiles_total > d->n_counters) {
@@ -823,13 +859,15 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
     a.row_ptr = (void * const *) d->out_row_ptr;
     a.src_token = d->src_token;
     a.pdl_flags = grouped ? d->pdl_flags : 0;
+    a.expert_list = grouped ? d->expert_list : nullptr;
+    a.list_tiles = (grouped && d->expert_list != nullptr && d->list_tiles) ? 1 : 0;
     a.w_evict_first = (t_tiles == 1 && !jib_no_evict_first()) ? 1 : 0;      // one token tile: every weight byte is used once
     // 16-byte result stores: bf16 rows whose feature offsets keep 16-byte alignment (row pointers of the expert-parallel return
     // path are row starts of bf16 matrices with d % 8 == 0, hence aligned as well)
-    a.vec_store = (!d->out_f32 && d->ar == nullptr && d->N % 8 == 0 && d->ldo % 8 == 0 && d->out_batch_stride % 8 == 0 &&
-                   ((uintptr_t) d->out & 15) == 0 &&
+    a.vec_store = (!d->out_f32 && d->N % 8 == 0 && d->ldo % 8 == 0 && d->out_batch_stride % 8 == 0 && ((uintptr_t) d->out & 15) == 0 &&
                    (d->residual == nullptr || (((uintptr_t) d->residual & 15) == 0 && d->ldr % 8 == 0 && d->res_batch_stride % 8 == 0)))
                       ? 1 : 0;
+    if (d->ar != nullptr && (((const JibArCtx *) d->ar)->d_max % 8 != 0 || d->out_f32)) a.vec_store = 0;
     a.ag_flags = (const unsigned *) d->ag_flags; a.ag_epoch = (const unsigned *) d->ag_epoch;
     a.ag_rows = d->ag_rows; a.ag_world = d->ag_world; a.ar_rs_rows = d->ar_rs_rows;
     a.ag_spin_limit = d->ar != nullptr ? ((const JibArCtx *) d->ar)->spin_limit : 0;
@@ -848,7 +886,7 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
         if (two_shot && (d->T > ar->max_rows2 || ar->recv2[0] == nullptr || (ar->n_sites & 1) || d->out_f32)) return JIB_E_ARG;
         a.ar = *ar; a.ar_on = two_shot ? 2 : 1; a.ar_site = d->ar_site;
     }
-    dim3 grid(n_tiles, t_tiles, batch * splits);
+    dim3 grid(n_tiles, list_tiles ? 1 : t_tiles, n_slots * splits);
 #define JIB_GEMM_CASE(BN_)                                                                          \
     case BN_:                                                                                     \
         return dual ? launch<BN_, true>(ma, ma2, mb, a, grid, stream) : launch<BN_, false>(ma, ma2, mb, a, grid, stream);
@@ -996,6 +1034,8 @@ extern "C" JIB_EXPORT int jib_gemm_bf16_noalloc(const void * x, const void * w, 
     a.vec_store = 0;
     a.w_evict_first = 0;
     a.pdl_flags = 0;
+    a.expert_list = nullptr;
+    a.list_tiles = 0;
     a.ag_flags = nullptr; a.ag_epoch = nullptr; a.ag_rows = 0; a.ag_world = 0; a.ar_rs_rows = 0; a.ag_spin_limit = 0;
     memset(&a.ar, 0, sizeof(a.ar));
     dim3 grid(p.n_tiles, 1, p.splits);

@@ -56,6 +56,10 @@ typedef struct jib_gemm_desc {
     int src_rows;              //   non-empty expert multiplies all of them (src_rows <= the token tile) and result row i (in the
                                //   expert-sorted order that seg describes) is the accumulator column src_token[i]: the gather of
                                //   token rows into sorted order is never materialised
+    const int * expert_list;   // grouped: NULL, or device int[n_slots]: the launch covers only these experts (entries < 0 are unused
+    int n_slots;               //   slots); n_slots <= batch.  For batches that hit few experts: most of the grid would exit at once
+    int list_tiles;            // 1: expert_list entries are (token tile << 16 | expert) pairs (jib_moe_tile_list, built for this bn):
+                               //   the launch covers exactly the token tiles that exist instead of T / bn tiles for every expert
     int pdl_flags;             // grouped, two launches back to back over one segment table: 1 on the first (it lets its dependents
                                //   start only once the table is known to be complete), 2 on the second (it may read the table and
                                //   request weights before the first launch has finished); 0 otherwise
@@ -100,8 +104,14 @@ JIB_EXPORT int jib_moe_route_fused(const void * g, const float * w_router, const
                                    int topk_group, float scale, int norm, int sigmoid, int n_shared, int group_top2, int expert_base,
                                    int E_local, const float * norm_w, float eps, void * g_out, void * stream);
 // Stable counting sort of the (token, k) pairs by local expert. dest[t*k+j] = sorted row or -1 (not local).
+// seg has room for 2 * E_local + 1 ints: the E_local + 1 segment offsets, then the list of the experts that have rows (in
+// order, -1 after the last): what jib_gemm_desc.expert_list takes.  (jib_moe_route_fused writes the same; the multi-CTA
+// sort for large batches writes the offsets only.)
 JIB_EXPORT int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
                                void * stream);
+// (expert, token tile) work list of a grouped launch with token-tile width bn: out[i] = tile << 16 | expert for every tile of
+// every expert that has rows, in expert order, -1 up to cap.  cap >= rows / bn + E_local always suffices.
+JIB_EXPORT int jib_moe_tile_list(const int * seg, int E_local, int bn, int * out, int cap, void * stream);
 JIB_EXPORT int jib_moe_permute_multi(const int * ids, int T, int k, int expert_base, int E_local, int * seg, int * src_token, int * dest,
                                      int * tmp, void * stream);
 JIB_EXPORT int jib_moe_combine(const void * y, const int * dest, const float * wts, const void * shared, const void * residual,
@@ -123,15 +133,6 @@ JIB_EXPORT int jib_mla_combine(const float * part_o, const float * part_ml, int 
 JIB_EXPORT int jib_mla_flash(const void * q, const void * cache, long long n_slots, const int * block_tables, int max_blocks,
                              const int * seq_lens, const int * q_start, int n_seqs, int T, int H, float scale, int n_splits, int qt,
                              float * part_o, float * part_ml, void * o_lat, int * status, void * stream);
-
-// ---- prefill attention in the per-head form (mha_prefill_tcgen05.cu): head dims 128 + 64 (keys), 128 (values) ---------------
-// jib_kv_gather: lat [total_cap][row_elems] <- the cached latent rows of every sequence, in sequence order; kv_start [n_seqs].
-JIB_EXPORT int jib_kv_gather(const void * cache, long long n_slots, const int * block_tables, int max_blocks, const int * seq_lens,
-                             int n_seqs, int block_size, int row_elems, void * lat, int * kv_start, int total_cap, void * stream);
-// q [T][H][192] (RoPE applied), kv [total][H][256] = k_nope | v, kpe [total][64] (row stride kpe_stride), out [T][H * 128].
-JIB_EXPORT int jib_mha_prefill(const void * q, long long q_stride, const void * kv, const void * kpe, long long kpe_stride, long long total,
-                               const int * q_start, const int * seq_lens, const int * kv_start, int n_seqs, int T, int H, float scale,
-                               int n_q_tiles, void * out, long long ldo, int * status, void * stream);
 
 // ---- expert-parallel all-to-all over peer memory (ep_alltoall.cu); ctx is a JibEpCtx (ep_alltoall.h) ---------
 JIB_EXPORT int jib_ep_plan(const int * ids, int T, int k, const struct JibEpCtx * ctx, int site, int * seg, int * pair_dst, void * stream);

@@ -281,7 +281,7 @@ __global__ void __launch_bounds__(32) moe_gate_kernel(const float * __restrict__
 constexpr int SORT_SMEM_MAX = 4096;
 __device__ __noinline__ void sort_pairs(const int * __restrict__ ids, int n, int k, int expert_base, int E_local, int * __restrict__ seg,
                                            int * __restrict__ src_token, int * __restrict__ dest, int * count, int * offs,
-                                           bool dry = false) {
+                                           bool dry = false, int * __restrict__ active = nullptr) {
     // dry: same instructions, no global stores (instruction-cache warm-up, see gate_token)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int e = warp; e < E_local; e += nw) {
@@ -310,6 +310,18 @@ __device__ __noinline__ void sort_pairs(const int * __restrict__ ids, int n, int
             run += __shfl_sync(0xffffffffu, inc, 31);
         }
         if (lane == 0) offs[E_local] = run;
+        if (active != nullptr && !dry) {
+            // the experts that have rows, in order, then -1: grouped launches of small batches cover this list only
+            int n_act = 0;
+            for (int e0 = 0; e0 < E_local; e0 += 32) {
+                const int e = e0 + lane;
+                const bool has = e < E_local && count[e] > 0;
+                const unsigned m = __ballot_sync(0xffffffffu, has);
+                if (has) active[n_act + __popc(m & ((1u << lane) - 1))] = e;
+                n_act += __popc(m);
+            }
+            for (int i = n_act + lane; i < E_local; i += 32) active[i] = -1;
+        }
     }
     __syncthreads();
     if (!dry) {
@@ -338,7 +350,7 @@ __device__ __noinline__ void sort_pairs(const int * __restrict__ ids, int n, int
 
 __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restrict__ ids, int n, int k, int expert_base, int E_local,
                                                           int * __restrict__ seg, int * __restrict__ src_token, int * __restrict__ dest,
-                                                          int warm) {
+                                                          int warm, int * __restrict__ active) {
     JIB_KS(11, 0);
     PDL_TRIGGER_TOP();
     __shared__ int count[MAX_E + 1];
@@ -356,7 +368,7 @@ __global__ void __launch_bounds__(1024) moe_permute_kernel(const int * __restric
         for (int i = threadIdx.x; i < n; i += blockDim.x) ids_s[i] = ids[i];
         __syncthreads();
     }
-    sort_pairs(n <= SORT_SMEM_MAX ? ids_s : ids, n, k, expert_base, E_local, seg, src_token, dest, count, offs);
+    sort_pairs(n <= SORT_SMEM_MAX ? ids_s : ids, n, k, expert_base, E_local, seg, src_token, dest, count, offs, false, active);
     JIB_KS(11, 9);
 }
 
@@ -507,8 +519,37 @@ __global__ void __launch_bounds__(GATE_NT) moe_route_fused_kernel(const bf16 * _
     }
     __syncthreads();         // ids of all tokens are in shared memory
     JIB_KS(14, 4);
-    sort_pairs(ids_s, T * (k + n_shared), k + n_shared, expert_base, E_local, seg, src_token, dest, count, offs);
+    sort_pairs(ids_s, T * (k + n_shared), k + n_shared, expert_base, E_local, seg, src_token, dest, count, offs, false, seg + E_local + 1);
     JIB_KS(14, 9);
+}
+
+// (expert, token tile) pairs of a grouped launch, one CTA: see jib_moe_tile_list.
+__global__ void __launch_bounds__(256) tile_list_kernel(const int * __restrict__ seg, int E_local, int bn, int * __restrict__ out, int cap) {
+    PDL_TRIGGER_TOP();
+    pdl_wait();
+    __shared__ int first[MAX_E + 1];
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int run = 0;
+        for (int e0 = 0; e0 < E_local; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < E_local ? (seg[e + 1] - seg[e] + bn - 1) / bn : 0;
+            int inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += v;
+            }
+            if (e < E_local) first[e] = run + inc - c;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) first[E_local] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E_local; e += blockDim.x)
+        for (int i = first[e], t = 0; i < first[e + 1]; ++i, ++t)
+            if (i < cap) out[i] = (t << 16) | e;
+    for (int i = first[E_local] + threadIdx.x; i < cap; i += blockDim.x) out[i] = -1;
 }
 
 // out[t] = residual[t] + shared[t] + sum_j wts[t][j] * y[dest[t][j]]   (fp32 accumulate, bf16 out)
@@ -741,7 +782,13 @@ int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local,
     if (T <= 0) return 0;
     if (E_local > MAX_E) return JIB_E_ARG;
     JIB_LAUNCH((moe_permute_kernel), 1, 1024, 0, (cudaStream_t) stream, ids, T * k, k, expert_base, E_local, seg, src_token, dest,
-               jib::warm_enabled());
+               jib::warm_enabled(), seg + E_local + 1);
+    return launched();
+}
+
+int jib_moe_tile_list(const int * seg, int E_local, int bn, int * out, int cap, void * stream) {
+    if (E_local <= 0 || E_local > MAX_E || bn <= 0 || cap <= 0) return JIB_E_ARG;
+    JIB_LAUNCH((tile_list_kernel), 1, 256, 0, (cudaStream_t) stream, seg, E_local, bn, out, cap);
     return launched();
 }
 

@@ -44,21 +44,54 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t * bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One wait attempt: the thread may be suspended until the phase completes, but for no longer than the hint (the time a
+// try_wait without a hint may stay suspended is implementation-defined, which would make a poll count meaningless).
 __device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, uint32_t parity) {
+    uint32_t ok;
+    const uint32_t suspend_hint_ns = 20000;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_hint_ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false if the phase did not complete within the time budget.  One try_wait may itself block for an
+// implementation-defined while, so a poll count alone bounds nothing in wall time: the budget is JIB_WAIT_NS on
+// %globaltimer (checked every 16 unsuccessful polls; these barriers pace a CTA's own pipeline, where a healthy wait takes
+// microseconds), with the poll count as a second limit.
+#ifndef JIB_WAIT_NS
+#define JIB_WAIT_NS 2000000000ull
+#endif
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Non-blocking test of a phase (try_wait may suspend the thread for an implementation-defined time; this one never does).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t * bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
         "selp.b32 %0, 1, 0, P;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait. Returns false if the phase did not complete within the poll budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity) {
-    for (uint32_t i = 0; i < JIB_SPIN_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;          // the common case: one (possibly suspending) wait is enough
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 0; i < JIB_SPIN_LIMIT; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((i & 15) == 15) {
+            if (globaltimer_ns() - t0 > JIB_WAIT_NS) return false;
+            __nanosleep(64);
+        }
+    }
     return false;
 }
 

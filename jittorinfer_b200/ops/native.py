@@ -34,6 +34,11 @@ GROUPED_SRC = os.environ.get("JIB_GROUPED_SRC", "1") == "1"
 GROUPED_SRC_MAX_T = 64
 # The down-projection launch reads the segment table and requests its weights before the gate|up launch has finished.
 GROUPED_PAIR = os.environ.get("JIB_GROUPED_PAIR", "1") == "1"
+# Grouped launches of batches with fewer (token, expert) pairs than experts cover only the experts that have rows.
+EXPERT_LIST = os.environ.get("JIB_EXPERT_LIST", "1") == "1"
+# Grouped launches of prompt chunks walk a list of the (expert, token tile) pairs that exist.
+TILE_LIST = os.environ.get("JIB_TILE_LIST", "1") == "1"
+TILE_LIST_MIN_PAIRS = 1024
 # The router launch of a decode batch also applies the RMSNorm of its input ("0": a separate norm launch before it).
 ROUTE_NORM = os.environ.get("JIB_ROUTE_NORM", "1") == "1"
 FUSED_ROUTE_MAX_T = 64
@@ -52,7 +57,8 @@ class GemmDesc(C.Structure):
                                        "splits", "bn", "sm_count", "ar_site")] + [("ar", C.c_void_p), ("out_row_ptr", C.c_void_p), ("ag_flags", C.c_void_p),
                                                                              ("ag_epoch", C.c_void_p), ("ag_rows", C.c_int),
                                                                              ("ag_world", C.c_int), ("ar_rs_rows", C.c_int),
-                                                                             ("src_token", C.c_void_p), ("src_rows", C.c_int), ("pdl_flags", C.c_int)]
+                                                                             ("src_token", C.c_void_p), ("src_rows", C.c_int), ("expert_list", C.c_void_p),
+                                                                             ("n_slots", C.c_int), ("list_tiles", C.c_int), ("pdl_flags", C.c_int)]
 
 
 def load():
@@ -75,8 +81,6 @@ def load():
     sig("jib_embed_gather", vp, ip, vp, i, i, i, vp)
     sig("jib_rmsnorm", vp, vp, fp, vp, vp, i, i, ll, f, vp)
     sig("jib_mla_qkv_post", vp, ll, vp, ll, fp, f, fp, ip, ip, vp, vp, ll, ll, i, i, i, i, i, i, ll, ip, vp)
-    sig("jib_kv_gather", vp, ll, ip, i, ip, i, i, i, vp, ip, i, vp)
-    sig("jib_mha_prefill", vp, ll, vp, vp, ll, ll, ip, ip, ip, i, i, i, f, i, vp, ll, ip, vp)
     sig("jib_argmax", fp, ip, i, i, vp)
     sig("jib_topk", fp, fp, ip, i, i, i, vp)
     sig("jib_sample_topk", fp, ip, fp, ip, i, i, vp)
@@ -86,6 +90,7 @@ def load():
     sig("jib_moe_permute", ip, i, i, i, i, ip, ip, ip, vp)
     sig("jib_moe_route_fused", vp, fp, fp, fp, ip, fp, ip, ip, ip, ip, i, i, i, i, i, i, f, i, i, i, i, i, i, fp, f, vp, vp)
     sig("jib_moe_permute_multi", ip, i, i, i, i, ip, ip, ip, ip, vp)
+    sig("jib_moe_tile_list", ip, i, i, ip, i, vp)
     sig("jib_moe_combine", vp, ip, fp, vp, vp, vp, i, i, i, vp)
     sig("jib_moe_combine_norm", vp, ip, fp, vp, vp, fp, vp, vp, i, i, i, f, vp)
     sig("jib_mla_attention", vp, vp, ip, i, ip, ip, i, i, i, i, i, i, f, i, fp, fp, vp, vp)
@@ -217,10 +222,16 @@ def gemm_batched(x_ptr: int, x_row_stride: int, x_batch_stride: int, w: torch.Te
     _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_batched")
 
 
+def _seg_has_list(seg: torch.Tensor, E: int) -> bool:
+    """Whether the allocation behind a segment table has room for (and, coming from ``moe_permute`` / the fused router, holds)
+    the list of experts that have rows: E more ints behind the E + 1 offsets."""
+    return seg.untyped_storage().nbytes() // 4 - seg.storage_offset() >= 2 * E + 1
+
+
 def gemm_grouped_raw(x_ptr: int, x_rows_total: int, K: int, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor],
                      max_rows: int, active_hint: int, splits: int = 0, bn: int = 0, device=None,
                      out_row_ptr: Optional[int] = None, src_token: Optional[torch.Tensor] = None, src_rows: int = 0,
-                     pdl_flags: int = 0) -> Optional[torch.Tensor]:
+                     pdl_flags: int = 0, n_slots: int = 0, tile_list: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """Grouped GEMM over a raw row buffer (e.g. a peer-mapped receive buffer).  With ``out_row_ptr`` (device array of
     row addresses) every result row is stored through its pointer and nothing is returned.  With ``src_token`` the
     buffer holds the ``src_rows`` token rows unsorted and sorted result row i is computed from token ``src_token[i]``
@@ -243,16 +254,23 @@ def gemm_grouped_raw(x_ptr: int, x_rows_total: int, K: int, seg: torch.Tensor, w
     if src_token is not None:
         d.src_token, d.src_rows = src_token.data_ptr(), src_rows
     d.pdl_flags = pdl_flags
+    if tile_list is not None:    # (expert, token tile) pairs built for this bn (moe_tile_list): large batches
+        assert bn > 0
+        d.expert_list, d.n_slots, d.list_tiles = tile_list.data_ptr(), tile_list.numel(), 1
+    elif n_slots > 0:            # seg carries the list of experts that have rows behind its E + 1 offsets (moe_permute)
+        assert _seg_has_list(seg, E)
+        d.expert_list, d.n_slots = seg.data_ptr() + (E + 1) * 4, n_slots
     _ck(load().jib_gemm_bf16(C.byref(d), _stream()), "gemm_grouped")
     return out
 
 
 def gemm_grouped(xp: torch.Tensor, seg: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor], max_rows: int,
-                 active_hint: int, splits: int = 0, pdl_flags: int = 0) -> torch.Tensor:
+                 active_hint: int, splits: int = 0, pdl_flags: int = 0, n_slots: int = 0, bn: int = 0,
+                 tile_list: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows of xp are sorted by expert; expert e owns rows seg[e]:seg[e+1] and weight w[e] ([E,N,K])."""
     assert xp.stride(0) == xp.shape[1] and xp.stride(1) == 1
-    return gemm_grouped_raw(xp.data_ptr(), xp.shape[0], xp.shape[1], seg, w, w2, max_rows, active_hint, splits, device=xp.device,
-                            pdl_flags=pdl_flags)
+    return gemm_grouped_raw(xp.data_ptr(), xp.shape[0], xp.shape[1], seg, w, w2, max_rows, active_hint, splits, bn, device=xp.device,
+                            pdl_flags=pdl_flags, n_slots=n_slots, tile_list=tile_list)
 
 
 def linear(x, w, residual=None, out_dtype=None):
@@ -353,38 +371,6 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
     return o
 
 
-MHA_PREFILL = os.environ.get("JIB_MHA_PREFILL", "1") == "1"      # "0": prompt chunks use the absorbed form as well (A/B)
-MHA_PREFILL_MIN_TOKENS = 64
-
-
-def mha_prefill_ok(T: int, dn: int, dr: int, dv: int, r: int, block_size: int, meta) -> bool:
-    """Whether a chunk of T query tokens takes the per-head prefill attention (needs the host-side totals in ``meta``)."""
-    return bool(MHA_PREFILL and meta is not None and T >= MHA_PREFILL_MIN_TOKENS and dn == 128 and dr == 64 and dv == 128 and r == 512
-                and meta.get("total_kv", 0) > 0)
-
-
-def mha_prefill(q, cache, w_kv_b, block_tables, seq_lens, q_start, scale, n_head, block_size, meta):
-    """Causal multi-head attention of a prompt chunk in the per-head form.  q [T, H*192] (RoPE already applied in place; may
-    be a strided view), cache [n_slots, 576] one layer's latent rows, w_kv_b [H*256, 512].  ``meta``: host-side totals of the
-    batch, {"total_kv": sum of seq_lens, "n_q_tiles": upper bound of sum ceil(q_len / 128)}.  Returns [T, H*128] bf16."""
-    T = q.shape[0]
-    n_seqs = seq_lens.shape[0]
-    total = int(meta["total_kv"])
-    row = cache.shape[1]
-    dev = q.device
-    lat = torch.empty(total, row, dtype=torch.bfloat16, device=dev)
-    kv_start = torch.empty(n_seqs, dtype=torch.int32, device=dev)
-    _ck(load().jib_kv_gather(cache.data_ptr(), cache.shape[0], block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(),
-                             n_seqs, block_size, row, lat.data_ptr(), kv_start.data_ptr(), total, _stream()), "kv_gather")
-    kv = gemm(lat[:, :512], w_kv_b)                     # [total, H*256]: k_nope | v per head
-    out = torch.empty(T, n_head * 128, dtype=torch.bfloat16, device=dev)
-    ws = workspace(dev)
-    _ck(load().jib_mha_prefill(q.data_ptr(), q.stride(0), kv.data_ptr(), lat.data_ptr() + 512 * 2, row, total, q_start.data_ptr(),
-                               seq_lens.data_ptr(), kv_start.data_ptr(), n_seqs, T, n_head, float(scale), int(meta["n_q_tiles"]),
-                               out.data_ptr(), out.stride(0), ws.status.data_ptr(), _stream()), "mha_prefill")
-    return out
-
-
 # ---- MoE -----------------------------------------------------------------------------------------
 def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_shared=0, group_top2=False, route=None,
              pre_norm=None):
@@ -408,7 +394,7 @@ def moe_gate(g, w_router, bias, k, n_group, topk_group, scale, norm, sigmoid, n_
     if fused:
         expert_base, E_local = route
         n = T * (k + n_shared)
-        seg = torch.empty(E_local + 1, dtype=torch.int32, device=g.device)
+        seg = torch.empty(2 * E_local + 1, dtype=torch.int32, device=g.device)[:E_local + 1]     # + room for the list of experts hit
         src = torch.empty(n, dtype=torch.int32, device=g.device)
         dest = torch.empty(T, k + n_shared, dtype=torch.int32, device=g.device)
         assert g_in.dtype == torch.bfloat16 and g_in.is_contiguous()
@@ -432,7 +418,7 @@ def moe_permute(ids, expert_base, E_local):
     hit = _route_stash.pop((ids.data_ptr(), expert_base, E_local), None)
     if hit is not None and hit[3] is ids:          # the fused router launch already sorted exactly these ids
         return hit[0], hit[1], hit[2]
-    seg = torch.empty(E_local + 1, dtype=torch.int32, device=dev)
+    seg = torch.empty(2 * E_local + 1, dtype=torch.int32, device=dev)[:E_local + 1]       # + room for the list of experts hit
     src = torch.empty(T * k, dtype=torch.int32, device=dev)
     dest = torch.empty(T, k, dtype=torch.int32, device=dev)
     if PERMUTE_MULTI and T * k >= PERMUTE_MULTI_MIN:
@@ -444,6 +430,15 @@ def moe_permute(ids, expert_base, E_local):
     _ck(load().jib_moe_permute(ids.data_ptr(), T, k, expert_base, E_local, seg.data_ptr(), src.data_ptr(), dest.data_ptr(),
                                _stream()), "moe_permute")
     return seg, src, dest
+
+
+def moe_tile_list(seg, E_local: int, bn: int, n_pairs: int) -> torch.Tensor:
+    """(token tile << 16 | expert) for every ``bn``-row tile of every expert that has rows, -1 padded to the bound
+    n_pairs / bn + E_local (every expert can end in one partial tile)."""
+    cap = n_pairs // bn + E_local
+    out = torch.empty(cap, dtype=torch.int32, device=seg.device)
+    _ck(load().jib_moe_tile_list(seg.data_ptr(), E_local, bn, out.data_ptr(), cap, _stream()), "moe_tile_list")
+    return out
 
 
 def gather_rows(x, src_row):
@@ -486,17 +481,25 @@ def moe_routed(x, ids, wts, wg, wu, wd, expert_base=0, n_expert=None):
     seg, src, dest = moe_permute(ids, expert_base, E_local)
     # the two grouped launches run back to back over one segment table: the second may start on its weights early
     pair = (1, 2) if GROUPED_PAIR else (0, 0)
+    # few pairs, many experts: the grouped launches cover the list of experts that have rows instead of all of them
+    slots = T * k if (EXPERT_LIST and T * k < E_local and _seg_has_list(seg, E_local)) else 0
     active = min(E_local, T * k)
     if ACTIVE_HINT_EXPECTED and n_expert:        # split-K sized for the experts a batch is expected to hit, not for all
         active = min(active, expected_active_experts(T, k, E_local, n_expert))
+    if TILE_LIST and T * k >= TILE_LIST_MIN_PAIRS:
+        # prompt chunks: an expert holds ~T*k/E rows, far fewer than the T the grid would have to be sized for; both grouped
+        # launches walk a device-built list of the (expert, 128-token tile) pairs that exist
+        tl = moe_tile_list(seg, E_local, 128, T * k)
+        h = gemm_grouped(gather_rows(x, src), seg, wg, wu, T, active, pdl_flags=pair[0], bn=128, tile_list=tl)
+        return gemm_grouped(h, seg, wd, None, T, active, pdl_flags=pair[1], bn=128, tile_list=tl), dest
     if GROUPED_SRC and T <= GROUPED_SRC_MAX_T and x.is_contiguous():
         # decode batches: every expert that has rows multiplies the whole (tiny) token tile and picks its tokens' columns in the
         # epilogue, so the token rows are never gathered into expert order
         h = gemm_grouped_raw(x.data_ptr(), T * k, x.shape[1], seg, wg, wu, T, active, device=x.device, src_token=src, src_rows=T,
-                             pdl_flags=pair[0])
+                             pdl_flags=pair[0], n_slots=slots)
     else:
-        h = gemm_grouped(gather_rows(x, src), seg, wg, wu, T, active, pdl_flags=pair[0])
-    y = gemm_grouped(h, seg, wd, None, T, active, pdl_flags=pair[1])
+        h = gemm_grouped(gather_rows(x, src), seg, wg, wu, T, active, pdl_flags=pair[0], n_slots=slots)
+    y = gemm_grouped(h, seg, wd, None, T, active, pdl_flags=pair[1], n_slots=slots)
     return y, dest
 
 

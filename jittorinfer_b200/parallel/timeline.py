@@ -159,6 +159,7 @@ def kernel_launches(stamps: np.ndarray) -> List[Dict]:
     phases of a CTA are matched to its launch by counting: the n-th phase-p stamp of (kind, grid size, block) belongs to the
     n-th launch with that kind and grid size.  Per launch: name, grid, and per phase the first and last time a CTA reached
     it, in microseconds from the first entry stamp of the whole record."""
+    # (launches of one kind and grid size are told apart by the order of their entry stamps per CTA)
     ks = stamps[stamps["kind"] >= 100]
     if ks.shape[0] == 0:
         return []
@@ -183,14 +184,20 @@ def kernel_launches(stamps: np.ndarray) -> List[Dict]:
                "phases": {0: [(first - t0) / 1e3, (last - t0) / 1e3]}}
         by_key.setdefault((kind, grid), []).append(len(launches))
         launches.append(rec)
-    seen: Dict[tuple, int] = {}
+    # a later stamp of a CTA belongs to the launch whose entry stamp of that CTA is the last one before it (CTAs that leave
+    # early stamp no further phases, so counting stamps per CTA would drift)
+    entry_t: Dict[tuple, List[int]] = {}
+    for i in range(entries.shape[0]):
+        entry_t.setdefault((int(entries["kind"][i]), int(entries["b"][i]), int(entries["a"][i])), []).append(int(entries["t"][i]))
+    import bisect
     for s in ks[ks["c"] != 0]:
         key = (int(s["kind"]), int(s["b"]))
-        cta = (key, int(s["a"]), int(s["c"]))
-        n = seen.get(cta, 0)
-        seen[cta] = n + 1
+        times = entry_t.get((key[0], key[1], int(s["a"])))
         idx = by_key.get(key)
-        if idx is None or n >= len(idx):
+        if times is None or idx is None:
+            continue
+        n = bisect.bisect_right(times, int(s["t"])) - 1
+        if n < 0 or n >= len(idx):
             continue
         ph = launches[idx[n]]["phases"]
         t = (int(s["t"]) - t0) / 1e3

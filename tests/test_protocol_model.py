@@ -232,3 +232,59 @@ def test_the_model_catches_a_protocol_without_double_buffering():
         except AssertionError:
             tripped += 1
     assert tripped > 0
+
+
+# ---- CTA residency: the two-shot epilogue when a launch has more tiles than the GPU holds CTAs ----------------------------
+# A resident CTA of tile t sends its partial to the tile's owner; on the owner it then waits for every rank's partial of
+# tile t, and everywhere it waits for the owner's delivery before it leaves and frees its slot.  With more tiles than
+# slots, progress therefore needs the CTA of tile t to become resident on EVERY rank: guaranteed when all ranks dispatch
+# their tiles in the same order (the hardware dispatches blockIdx in order, and every rank launches the same grid), not
+# guaranteed for an arbitrary order.  The model: every rank has `slots` CTA slots and a dispatch order; a slot takes the
+# next tile when its CTA has finished.
+def _two_shot_resident(world, n_tiles, slots, orders, seed):
+    rng = random.Random(seed)
+    sent = set()            # (tile, src): partial stored at the owner
+    delivered = set()       # tile: owner has reduced and delivered
+    nxt = [0] * world       # next position in the rank's dispatch order
+    res = [[] for _ in range(world)]      # resident CTAs: [tile, stage]  stage 0 = to send, 1 = sent (owner: to reduce), 2 = wait delivery
+    done = [0] * world
+    for _ in range(100000):
+        moves = []
+        for r in range(world):
+            if len(res[r]) < slots and nxt[r] < n_tiles:
+                moves.append(("dispatch", r, None))
+            for cta in res[r]:
+                t, st = cta
+                owner = t % world
+                if st == 0:
+                    moves.append(("send", r, cta))
+                elif st == 1 and r == owner and all((t, s) in sent for s in range(world)):
+                    moves.append(("reduce", r, cta))
+                elif (st == 2 or (st == 1 and r != owner)) and t in delivered:
+                    moves.append(("leave", r, cta))
+        if not moves:
+            return all(d == n_tiles for d in done)
+        kind, r, cta = rng.choice(moves)
+        if kind == "dispatch":
+            res[r].append([orders[r][nxt[r]], 0])
+            nxt[r] += 1
+        elif kind == "send":
+            sent.add((cta[0], r))
+            cta[1] = 1
+        elif kind == "reduce":
+            delivered.add(cta[0])
+            cta[1] = 2
+        else:
+            res[r].remove(cta)
+            done[r] += 1
+    raise AssertionError("model did not terminate")
+
+
+def test_two_shot_with_more_tiles_than_resident_ctas_needs_one_dispatch_order():
+    world, n_tiles, slots = 4, 40, 3
+    same = [list(range(n_tiles))] * world
+    assert all(_two_shot_resident(world, n_tiles, slots, same, seed) for seed in range(200))
+    # the assumption is load-bearing: one rank walking its tiles backwards fills its slots with tiles whose CTAs are not
+    # resident elsewhere, and every rank ends up waiting (in the kernels such a wait is bounded and reports a timeout)
+    mixed = [list(range(n_tiles))] * (world - 1) + [list(reversed(range(n_tiles)))]
+    assert not any(_two_shot_resident(world, n_tiles, slots, mixed, seed) for seed in range(50))
