@@ -179,14 +179,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // A pair of grouped launches (gate|up, then down) shares one table: the first of the pair (pdl_flags bit 0) releases its
     // dependents only AFTER its own wait, which tells the second (bit 1) that the table is complete when it starts -- it
     // reads the table and requests its weight tiles before waiting for the first launch's results.
+    // The dependents are released further down, once this CTA holds its tensor-memory columns: tcgen05.alloc blocks until
+    // columns are free, so a CTA of the NEXT grid that became resident early, took columns and then sat in its own
+    // dependency wait could starve a CTA of THIS grid that had yet to start on that SM -- for good.  Released after the
+    // allocation (a CTA that leaves early releases by leaving), the next grid starts only when every CTA of this one has
+    // its columns.
     const bool seg_early = args.seg != nullptr && (args.pdl_flags & 2) != 0;
-    if (args.seg != nullptr && (args.pdl_flags & 1) != 0) {
-        pdl_wait();
-        pdl_launch_dependents();
-    } else {
-        PDL_TRIGGER_TOP();
-        if (args.seg != nullptr && !seg_early) pdl_wait();
-    }
+    if (args.seg != nullptr && !seg_early) pdl_wait();
     if (args.seg != nullptr) {
         // decode batches hit few of the experts: the grid then covers a list of the experts that have rows (written by the
         // sort next to the segment table, -1 past its end) instead of all of them
@@ -239,6 +238,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (args.seg != nullptr && (args.pdl_flags & 1) != 0) pdl_launch_dependents();      // first of a pair: always here
+    else PDL_TRIGGER_TOP();
     const uint32_t tmem = *tmem_slot;
     // Everything above touched only shared/tensor memory and launch-invariant data; activations, the residual,
     // scratch and the output belong to the stream order from here on.

@@ -134,6 +134,15 @@ JIB_EXPORT int jib_mla_flash(const void * q, const void * cache, long long n_slo
                              const int * seq_lens, const int * q_start, int n_seqs, int T, int H, float scale, int n_splits, int qt,
                              float * part_o, float * part_ml, void * o_lat, int * status, void * stream);
 
+// ---- prefill attention in the per-head form (mha_prefill_tcgen05.cu): head dims 128 + 64 (keys), 128 (values) ---------------
+// jib_kv_gather: lat [total_cap][row_elems] <- the cached latent rows of every sequence, in sequence order; kv_start [n_seqs].
+JIB_EXPORT int jib_kv_gather(const void * cache, long long n_slots, const int * block_tables, int max_blocks, const int * seq_lens,
+                             int n_seqs, int block_size, int row_elems, void * lat, int * kv_start, int total_cap, void * stream);
+// q [T][H][192] (RoPE applied), kv [total][H][256] = k_nope | v, kpe [total][64] (row stride kpe_stride), out [T][H * 128].
+JIB_EXPORT int jib_mha_prefill(const void * q, long long q_stride, const void * kv, const void * kpe, long long kpe_stride, long long total,
+                               const int * q_start, const int * seq_lens, const int * kv_start, int n_seqs, int T, int H, float scale,
+                               int n_q_tiles, void * out, long long ldo, int * status, void * stream);
+
 // ---- expert-parallel all-to-all over peer memory (ep_alltoall.cu); ctx is a JibEpCtx (ep_alltoall.h) ---------
 JIB_EXPORT int jib_ep_plan(const int * ids, int T, int k, const struct JibEpCtx * ctx, int site, int * seg, int * pair_dst, void * stream);
 JIB_EXPORT int jib_ep_push(const void * x, const int * pair_dst, int T, int k, const struct JibEpCtx * ctx, int site, const int * seg,

@@ -61,7 +61,6 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y;
-    PDL_TRIGGER_TOP();
 
     uint8_t * base = (uint8_t *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
     uint8_t * q_s = base;
@@ -94,6 +93,10 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         prefetch_tmap(&tmKV);
         prefetch_tmap(&tmPE);
     }
+    // This kernel takes ALL tensor-memory columns of its SM, and tcgen05.alloc blocks until they are free.  So it asks for them
+    // only after the grid before it has completed (a CTA of that grid that still had to start on this SM could never get
+    // its own columns), and it lets the grid after it start only once every CTA of this one holds its columns.
+    pdl_wait();                                       // q, the expanded K / V and the sequence tables
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
@@ -101,9 +104,9 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_launch_dependents();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_S = tmem, tm_O = tmem + 2 * KT;
-    pdl_wait();                                       // q, the expanded K / V and the sequence tables
 
     // ---- which (sequence, query tile) is this CTA?  blockIdx.x walks the tiles of all sequences, last tile of a
     // sequence first (it sees the most KV tiles) ----
@@ -203,7 +206,9 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         bool ok = true;
         for (int kt = 0; kt < n_tiles && ok; ++kt) {
             const int s = kt & 1;
-            if (!mbar_wait(&s_full[s], (kt >> 1) & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 36, kt); ok = false; break; }
+            if (!mbar_wait(&s_full[s], (kt >> 1) & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 36, kt); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);         // the tensor-memory loads below are warp-wide: leave as a whole warp
+            if (!ok) break;
             tc_fence_after();
             const uint32_t ts = tm_S + lane_addr + s * KT;
             const bool need_mask = (kt + 1) * KT > lim_first;          // the tile reaches the diagonal (or the sequence end)
@@ -229,6 +234,7 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (any_grow) {
                 // O holds sums relative to the old base: wait for the products in flight, then rescale this row
                 if (!mbar_wait(o_done, (kt - 1) & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 37, kt); ok = false; }
+                ok = __all_sync(0xffffffffu, ok);
                 tc_fence_after();
                 const float cf = (grow && m_ref != -INFINITY) ? exp2f(m_ref - m_new) : 1.f;
                 if (ok) {
@@ -250,6 +256,7 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             m_ref = m_new;
             // the previous P.V must have read P before it is overwritten
             if (kt > 0 && !mbar_wait(p_empty, (kt - 1) & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 38, kt); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
             // pass 2: p = 2^(x - base), row sum, P (bf16) into the swizzled K-major tile
 #pragma unroll 1
             for (int c = 0; c < KT; c += 16) {
@@ -284,10 +291,15 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         // ---- epilogue: O / l -> bf16 rows ----
         if (ok && !mbar_wait(o_done, (n_tiles - 1) & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 39, 0); ok = false; }
+        ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        if (ok && r < rows) {
+        if (ok) {
+            // tcgen05.ld is a warp-wide instruction (.sync.aligned): all 32 lanes execute it, also in a tile whose valid
+            // rows end inside this warp; only the stores are predicated per row.  (Executed under a per-lane condition it
+            // never completes.)
+            const bool valid = r < rows;
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-            bf16 * dst = a.out + (size_t) (row0 + r) * a.ldo + (size_t) h * DV;
+            bf16 * dst = a.out + (size_t) (row0 + (valid ? r : 0)) * a.ldo + (size_t) h * DV;
 #pragma unroll 1
             for (int c = 0; c < DV; c += 16) {
                 uint32_t v[16];
@@ -299,11 +311,11 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
                     o[j >> 1] = *(const uint32_t *) &pk;
                 }
-                *(uint4 *) (dst + c) = make_uint4(o[0], o[1], o[2], o[3]);
-                *(uint4 *) (dst + c + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                if (valid) {
+                    *(uint4 *) (dst + c) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *(uint4 *) (dst + c + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
             }
-        } else if (ok) {
-            // rows of the tile that belong to no query still have to drain their TMEM reads: nothing to do
         }
     }
 

@@ -139,7 +139,6 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int p = 0; p < n_pass; ++p) total_tiles += pass_k1[p] > pass_k0[p] ? (pass_k1[p] - pass_k0[p] + KV_TILE - 1) / KV_TILE : 0;
 
     JIB_KS(2, 0);
-    PDL_TRIGGER_TOP();
     if (total_tiles == 0) {
         pdl_wait();
         // nothing visible for this (group, split): publish an empty partial / zero output and leave
@@ -177,6 +176,7 @@ mla_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    PDL_TRIGGER_TOP();      // only now: the next grid may start once every CTA of this one holds its tensor-memory columns
     const uint32_t tmem = *tmem_slot;
     pdl_wait();                                 // q, the latent cache rows written this step, and all outputs
     JIB_KS(2, 1);

@@ -81,6 +81,8 @@ def load():
     sig("jib_embed_gather", vp, ip, vp, i, i, i, vp)
     sig("jib_rmsnorm", vp, vp, fp, vp, vp, i, i, ll, f, vp)
     sig("jib_mla_qkv_post", vp, ll, vp, ll, fp, f, fp, ip, ip, vp, vp, ll, ll, i, i, i, i, i, i, ll, ip, vp)
+    sig("jib_kv_gather", vp, ll, ip, i, ip, i, i, i, vp, ip, i, vp)
+    sig("jib_mha_prefill", vp, ll, vp, vp, ll, ll, ip, ip, ip, i, i, i, f, i, vp, ll, ip, vp)
     sig("jib_argmax", fp, ip, i, i, vp)
     sig("jib_topk", fp, fp, ip, i, i, i, vp)
     sig("jib_sample_topk", fp, ip, fp, ip, i, i, vp)
@@ -369,6 +371,49 @@ def mla_attention(q, cache, block_tables, seq_lens, q_start, scale, r, block_siz
                                  seq_lens.data_ptr(), q_start.data_ptr(), n_seqs, T, H, r, D - r, block_size, float(scale),
                                  n_splits, _p(part_o), _p(part_ml), o.data_ptr(), _stream()), "mla_attention")
     return o
+
+
+MHA_PREFILL = os.environ.get("JIB_MHA_PREFILL", "1") == "1"      # "0": prompt chunks use the absorbed form as well (A/B)
+MHA_PREFILL_MIN_TOKENS = 64
+
+
+def mha_prefill_ok(T: int, dn: int, dr: int, dv: int, r: int, block_size: int, meta) -> bool:
+    """Whether a chunk of T query tokens takes the per-head prefill attention (needs the host-side totals in ``meta``)."""
+    return bool(MHA_PREFILL and meta is not None and T >= MHA_PREFILL_MIN_TOKENS and dn == 128 and dr == 64 and dv == 128 and r == 512
+                and meta.get("total_kv", 0) > 0)
+
+
+def kv_gather(cache, block_tables, seq_lens, total: int, block_size: int):
+    """The cached latent rows of every sequence of the batch, in sequence order: ([total, row] bf16, first row of each
+    sequence [n_seqs] int32)."""
+    n_seqs = seq_lens.shape[0]
+    row = cache.shape[1]
+    lat = torch.empty(total, row, dtype=torch.bfloat16, device=cache.device)
+    kv_start = torch.empty(n_seqs, dtype=torch.int32, device=cache.device)
+    _ck(load().jib_kv_gather(cache.data_ptr(), cache.shape[0], block_tables.data_ptr(), block_tables.stride(0), seq_lens.data_ptr(),
+                             n_seqs, block_size, row, lat.data_ptr(), kv_start.data_ptr(), total, _stream()), "kv_gather")
+    return lat, kv_start
+
+
+def mha_prefill_core(q, kv, lat, kv_start, seq_lens, q_start, scale, n_head, n_q_tiles: int):
+    """The attention kernel itself: q [T, H*192], kv [total, H*256] = k_nope | v per head, lat [total, 576] (its last 64
+    columns are the RoPE part of the keys, shared by the heads).  Returns [T, H*128] bf16."""
+    T, total = q.shape[0], lat.shape[0]
+    out = torch.empty(T, n_head * 128, dtype=torch.bfloat16, device=q.device)
+    ws = workspace(q.device)
+    _ck(load().jib_mha_prefill(q.data_ptr(), q.stride(0), kv.data_ptr(), lat.data_ptr() + 512 * 2, lat.shape[1], total,
+                               q_start.data_ptr(), seq_lens.data_ptr(), kv_start.data_ptr(), seq_lens.shape[0], T, n_head, float(scale),
+                               int(n_q_tiles), out.data_ptr(), out.stride(0), ws.status.data_ptr(), _stream()), "mha_prefill")
+    return out
+
+
+def mha_prefill(q, cache, w_kv_b, block_tables, seq_lens, q_start, scale, n_head, block_size, meta):
+    """Causal multi-head attention of a prompt chunk in the per-head form.  q [T, H*192] (RoPE already applied in place; may
+    be a strided view), cache [n_slots, 576] one layer's latent rows, w_kv_b [H*256, 512].  ``meta``: host-side totals of the
+    batch, {"total_kv": sum of seq_lens, "n_q_tiles": upper bound of sum ceil(q_len / 128)}.  Returns [T, H*128] bf16."""
+    lat, kv_start = kv_gather(cache, block_tables, seq_lens, int(meta["total_kv"]), block_size)
+    kv = gemm(lat[:, :512], w_kv_b)                     # [total, H*256]: k_nope | v per head
+    return mha_prefill_core(q, kv, lat, kv_start, seq_lens, q_start, scale, n_head, int(meta["n_q_tiles"]))
 
 
 # ---- MoE -----------------------------------------------------------------------------------------

@@ -50,7 +50,8 @@ def _sig(args, kwargs) -> str:
 
 
 KERNEL_LEVEL = ("gemm", "gemm_batched", "gemm_grouped_raw", "moe_permute", "gather_rows", "moe_combine", "rmsnorm", "embed_gather",
-                "mla_qkv_post", "mla_attention", "moe_gate", "argmax", "topk_logits", "kv_block_copy")
+                "mla_qkv_post", "mla_attention", "moe_gate", "argmax", "topk_logits", "kv_block_copy", "mha_prefill", "kv_gather",
+                "mha_prefill_core")
 
 
 class OpProfile:

@@ -107,7 +107,8 @@ def main():
                     run(fused)
                     torch.cuda.synchronize()
                     dist.barrier()
-                    with torch.cuda.graph(gr, stream=st):
+                    torch.cuda.synchronize()            # the barrier's own work is over: nothing of the library is in flight
+                    with torch.cuda.graph(gr, stream=st, capture_error_mode="thread_local"):
                         run(fused)
                 torch.cuda.synchronize()
                 dist.barrier()

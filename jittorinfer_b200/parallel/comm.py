@@ -153,6 +153,8 @@ class FusedCommunicator(Communicator):
         self.ctx.max_rows, self.ctx.d_max, self.ctx.max_tiles = max_rows, d_max, self.MAX_TILES
         self.max_rows_large = max_rows_large
         self.ctx.max_rows2 = max_rows_large
+        # polls a wait on a peer's flag may take before the kernel reports the peer silent (0 = the built-in 2^20, about a second)
+        self.ctx.spin_limit = int(os.environ.get("JITTORINFER_PEER_WAIT_POLLS", "0"))
         if max_rows_large > 0:
             recv2 = self._exchange(2 * world * max_rows_large * d_max * 4)
             out2 = self._exchange(2 * max_rows_large * d_max * 2)
@@ -254,7 +256,7 @@ class FusedCommunicator(Communicator):
     n_two_shot = 0
 
     # ---- MoE block tail in one launch: expert combine + all-reduce + residual (+ the next block's norm) -----------
-    # Cross-compiled, not yet run on a GPU: off unless JIB_FUSED_COMBINE_AR=1.
+    # Off unless JIB_FUSED_COMBINE_AR=1.
     fused_combine = os.environ.get("JIB_FUSED_COMBINE_AR", "0") == "1"
 
     def moe_ffn_all_reduce(self, x, residual, ids, wts, wg, wu, wd, wgs, wus, wds, expert_base, n_expert=None, norm=None):

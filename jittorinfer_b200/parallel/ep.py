@@ -155,6 +155,7 @@ class FusedEpDispatcher(EpDispatcher):
         self.ctx.epoch, self.ctx.status = self.epoch.data_ptr(), ws.status.data_ptr()
         self.ctx.world, self.ctx.rank, self.ctx.n_sites, self.ctx.E_local = world, rank, self.n_sites, self.e_local
         self.ctx.d, self.ctx.max_recv_rows, self.ctx.max_pairs = d, R, P
+        self.ctx.spin_limit = int(os.environ.get("JITTORINFER_PEER_WAIT_POLLS", "0"))      # 0 = the built-in limit
         self.seg = torch.zeros(self.e_local + 1, dtype=torch.int32, device=device)
         self.pair_dst = torch.full((max(P, 1),), -1, dtype=torch.int32, device=device)
         self.done = torch.zeros(1, dtype=torch.int32, device=device)

@@ -92,7 +92,8 @@ def main():
         step(fused)
         torch.cuda.synchronize()
         dist.barrier()
-        with torch.cuda.graph(graph, stream=s):
+        torch.cuda.synchronize()                        # the barrier's own work is over: nothing of the library is in flight
+        with torch.cuda.graph(graph, stream=s, capture_error_mode="thread_local"):
             step(fused)
     torch.cuda.synchronize()
     dist.barrier()

@@ -236,6 +236,10 @@ class LLMEngine:
         il = graphdump.requested_layer()  # LLAMA_PRINT_LAYER=<il>: the first step writes that layer's op graph as dot text
         if il is not None:
             graphdump.dump_on_first_step(self, il)
+        # Loading the weights takes seconds and not the same time on every rank; the in-kernel collectives give a peer about
+        # a second before they report a silent peer.  Start the first step together.
+        if getattr(model, "comm", None) is not None or getattr(self, "dp", False):
+            self._host_barrier()
 
     # ------------------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -271,11 +275,18 @@ class LLMEngine:
     # ------------------------------------------------------------------------------------------
     def _batch_views(self, n_tokens: int, n_seqs: int, n_out: int, max_q_len: int) -> ForwardBatch:
         d = self.io.d
+        meta = None
+        if max_q_len > 1:
+            # host-side totals of a prompt step (the scheduler wrote these arrays; no device read): sizes of the gathered
+            # K / V buffers and of the attention grid of the per-head prefill form
+            h = self.io.h
+            qs = h["q_start"][:n_seqs + 1]
+            meta = {"total_kv": int(h["seq_lens"][:n_seqs].sum()), "n_q_tiles": int(((np.diff(qs) + 127) // 128).sum())}
         return ForwardBatch(tokens=d["tokens"][:n_tokens], positions=d["positions"][:n_tokens],
                             slot_mapping=d["slot_mapping"][:n_tokens],
                             block_tables=d["block_tables"].view(self.io.cap_seqs, self.max_blocks)[:n_seqs],
                             seq_lens=d["seq_lens"][:n_seqs], q_start=d["q_start"][:n_seqs + 1],
-                            out_rows=d["out_rows"][:n_out], max_q_len=max_q_len)
+                            out_rows=d["out_rows"][:n_out], max_q_len=max_q_len, attn_meta=meta)
 
     def _sample_device(self, logits: torch.Tensor, mode: str) -> torch.Tensor:
         """Returns an int32 tensor: [n] token ids (greedy) or [n, 2k] (k float bit patterns + k ids)."""

@@ -33,8 +33,8 @@ def build_model(hp: Optional[DeepSeek2HParams] = None, gguf_path: Optional[str] 
         reader = GGUFReader(gguf_path)
         if dtype == torch.bfloat16 and torch.device(device).type == "cuda":
             reader.quant_out_dtype = torch.bfloat16      # block-quantised tensors are expanded straight to the stored dtype
-            if os.environ.get("JITTORINFER_DEVICE_DEQUANT", "") == "1" and layer_devices is None:
-                reader.quant_device = torch.device(device)   # ... on the device (awaiting its first GPU run: off by default)
+            if os.environ.get("JITTORINFER_DEVICE_DEQUANT", "1") != "0" and layer_devices is None:
+                reader.quant_device = torch.device(device)   # ... on the device: the quantised bytes cross PCIe, not the bf16
         if kv_overrides:                 # metadata overrides (llama_model_params.kv_overrides)
             reader.kv.update(kv_overrides)
         hp = DeepSeek2HParams.from_gguf_kv(reader.kv, reader.tensors)

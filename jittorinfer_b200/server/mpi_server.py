@@ -28,11 +28,23 @@ def _rank_main(argv):
     else:
         dist.init_process_group("gloo")
     control = dist.new_group(backend="gloo")          # host-side task broadcasts
+    # The process leaves through os._exit: a rank whose peers are gone must not wait in the process group's destructor.
+    # The exit code and the traceback are therefore passed on by hand.
+    rc = 1
     try:
-        return main(argv, world=world, rank=rank, control_group=control)
+        rc = int(main(argv, world=world, rank=rank, control_group=control) or 0)
+    except SystemExit as e:
+        rc = e.code if isinstance(e.code, int) else (0 if e.code is None else 1)
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        rc = 1
     finally:
+        sys.stdout.flush()
+        sys.stderr.flush()
         if dist.is_initialized():
-            os._exit(0)
+            os._exit(rc)
+    return rc
 
 
 def cli(argv=None) -> int:

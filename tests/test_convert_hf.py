@@ -306,9 +306,6 @@ def test_v3_structure_matches_the_library_model(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.skipif(os.environ.get("JITTORINFER_TEST_HF_GPU", "") != "1",
-                    reason="the GPU engine against the library model has not yet been run on a GPU; "
-                           "set JITTORINFER_TEST_HF_GPU=1 to try it")
 def test_gpu_engine_on_a_converted_checkpoint_follows_the_library_model(tmp_path):
     """bf16 kernels against the library's fp32 model: the first tokens of a greedy continuation agree and the logits of the
     prompt's last position agree to bf16 resolution (read through the engine's top-k log-probabilities)."""

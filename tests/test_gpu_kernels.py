@@ -370,3 +370,52 @@ def test_device_dequantize_matches_the_host_expander():
         diff = (got.float() - want.float()).abs()
         assert float((diff / want.float().abs().clamp_min(1e-3)).max()) < 1e-2, Q.NAMES[t]      # fused multiply-add may move one bf16 ulp
         assert float((got != want).float().mean()) < 1e-3, Q.NAMES[t]
+
+
+@pytest.mark.parametrize("lens", [[(130, 130)], [(300, 300), (64, 64)], [(128, 400), (200, 200), (70, 1000)]])
+def test_prefill_attention_per_head_form(nat, lens):
+    """Prompt-chunk attention over K / V expanded from the cached latent rows (tcgen05, queries on the M axis) against an
+    fp32 restatement: several sequences per batch, chunks that continue a cached prefix (query rows are the LAST rows of a
+    sequence), partial tiles, block tables in scrambled order."""
+    H, dn, dr, dv, r, bs = 16, 128, 64, 128, 512, 64
+    g = torch.Generator().manual_seed(len(lens))
+    n_seqs = len(lens)
+    S_all = [s for _, s in lens]
+    n_blocks = sum((s + bs - 1) // bs for s in S_all) + 3
+    cache = (torch.randn(n_blocks * bs, r + dr, generator=g) * 0.5).bfloat16().to(DEV)
+    perm = torch.randperm(n_blocks - 1, generator=g) + 1
+    max_blocks = max((s + bs - 1) // bs for s in S_all)
+    bt = torch.zeros(n_seqs, max_blocks, dtype=torch.int32)
+    used = 0
+    for b, s in enumerate(S_all):
+        nb = (s + bs - 1) // bs
+        bt[b, :nb] = perm[used:used + nb].int()
+        used += nb
+    T = sum(q for q, _ in lens)
+    q = (torch.randn(T, H * (dn + dr), generator=g) * 0.5).bfloat16().to(DEV)
+    w_kv_b = (torch.randn(H * (dn + dv), r, generator=g) * 0.05).bfloat16().to(DEV)
+    q_start = torch.tensor([0] + list(torch.tensor([ql for ql, _ in lens]).cumsum(0)), dtype=torch.int32, device=DEV)
+    seq_lens = torch.tensor(S_all, dtype=torch.int32, device=DEV)
+    scale = 0.07
+    meta = {"total_kv": sum(S_all), "n_q_tiles": sum((ql + 127) // 128 for ql, _ in lens)}
+    out = nat.mha_prefill(q, cache, w_kv_b, bt.to(DEV), seq_lens, q_start, scale, H, bs, meta)
+    torch.cuda.synchronize()
+    nat.check_status()
+    # reference
+    row0 = 0
+    for b, (ql, S) in enumerate(lens):
+        slots = torch.cat([bt[b, i].long() * bs + torch.arange(bs) for i in range((S + bs - 1) // bs)])[:S].to(DEV)
+        lat = cache[slots].float()
+        kv = (lat[:, :r] @ w_kv_b.float().T).bfloat16().float().view(S, H, dn + dv)      # the kernel reads the bf16 expansion
+        k = torch.cat([kv[..., :dn], lat[:, None, r:].expand(S, H, dr)], dim=-1)
+        v = kv[..., dn:]
+        qq = q[row0:row0 + ql].float().view(ql, H, dn + dr)
+        s = torch.einsum("thd,shd->hts", qq, k) * scale
+        pos = torch.arange(S - ql, S, device=DEV)
+        mask = torch.arange(S, device=DEV)[None, :] > pos[:, None]
+        s = s.masked_fill(mask[None], float("-inf"))
+        want = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), v).reshape(ql, H * dv)
+        got = out[row0:row0 + ql].float()
+        err = (got - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item() + 1e-3, (b, err, want.abs().max().item())
+        row0 += ql

@@ -148,11 +148,14 @@ def test_mpi_server_two_gpus_serves_over_http(tmp_path, dp):
         pytest.skip("needs 2 GPUs")
     from jittorinfer_b200.models.hparams import preset
     from jittorinfer_b200.models.oracle import OracleModel
-    from jittorinfer_b200.models.weights import random_weights
+    from jittorinfer_b200.models.weights import random_weights, write_random_gguf
     hport, mport = _free_port(), _free_port()
     cfg = tmp_path / "c.yaml"
-    cfg.write_text(f"random_init: tiny-v2\nn_ctx: 2048\nn_parallel: 4\nn_batch: 64\nport: {hport}\nenable_ge: true\ntp_size: 2\nep_size: 2\n"
-                   + ("attention_dp: true\n" if dp else ""))
+    hp = preset("tiny-v2")
+    gguf = tmp_path / "m.gguf"                      # a file, so that every rank and the oracle hold the same numbers
+    write_random_gguf(str(gguf), hp, seed=0, std=0.05)
+    cfg.write_text(f"model: {gguf}\nn_ctx: 2048\nn_parallel: 4\nn_batch: 64\nport: {hport}\nenable_ge: true\n"
+                   + ("tp_size: 1\nep_size: 2\nattention_dp: true\nep_max_tokens: 64\n" if dp else "tp_size: 2\nep_size: 2\n"))
     env = dict(os.environ, JITTORINFER_COMM="fused", NCCL_NVLS_ENABLE="0", JITTORINFER_HEARTBEAT_TIMEOUT="30")
     p = subprocess.Popen([sys.executable, "-m", "jittorinfer_b200.server.mpi_server", "--nproc", "2", "--master-port", str(mport),
                           "-c", str(cfg)], cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -169,7 +172,6 @@ def test_mpi_server_two_gpus_serves_over_http(tmp_path, dp):
                 assert p.poll() is None, p.stdout.read()[-3000:]
                 time.sleep(0.5)
         assert up, "server did not come up"
-        hp = preset("tiny-v2")
         g = torch.Generator().manual_seed(9)
         prompts = [torch.randint(1, hp.n_vocab, (n,), generator=g).tolist() for n in (15, 40, 7, 22)]
         outs = [None] * len(prompts)
@@ -182,7 +184,7 @@ def test_mpi_server_two_gpus_serves_over_http(tmp_path, dp):
             t.start()
         for t in ths:
             t.join(timeout=120)
-        o = OracleModel(hp, {k: v.bfloat16().float() for k, v in random_weights(hp, seed=0).items()})
+        o = OracleModel(hp, {k: v.bfloat16().float() for k, v in random_weights(hp, seed=0, std=0.05).items()})
         for pr, got in zip(prompts, outs):
             want = o.generate(pr, 6)
             assert got is not None and len(got) == 6 and got[0] == want[0], (got, want)
