@@ -176,6 +176,12 @@ def build_kernels_pdl_late(force: bool = False, verbose: bool = False, timeline:
     return _build_kernels_variant("JIB_PDL_LATE,JIB_TIMELINE" if timeline else "JIB_PDL_LATE", "late_tl" if timeline else "late", force, verbose)
 
 
+def build_kernels_poll(force: bool = False, verbose: bool = False) -> str:
+    """The kernels with -DJIB_SUSPEND_NS=0 (csrc/kernels/sm100.cuh: mbarrier waits poll with test_wait and never suspend the
+    thread) as libjib200_kernels_poll.so, to compare the wake-up latency of a suspended wait against polling."""
+    return _build_kernels_variant("JIB_SUSPEND_NS=0", "poll", force, verbose)
+
+
 def build_kernels(force: bool = False, verbose: bool = False, extra_flags: List[str] = ()) -> str:
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
     hdrs = glob.glob(os.path.join(CSRC, "kernels", "*.cuh")) + glob.glob(os.path.join(CSRC, "kernels", "*.h")) + \

@@ -662,6 +662,240 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 // ---------------------------------------------------------------------------------------------
+// Persistent form for launches with several waves of tiles (prompt chunks): one CTA per SM walks the tile list, the TMA
+// ring keeps streaming across tile boundaries, and the accumulators are double-buffered in tensor memory, so the
+// epilogue of tile i (tcgen05.ld, SiLU, transpose, 16-byte stores) runs under the MMAs of tile i + 1 instead of leaving
+// the tensor core idle for a quarter (gate|up) to a half (down projection) of every tile.  Plain launches only: no
+// split-K, no fused collective, bf16 results through the vectorised epilogue; dense, batched or grouped (segment table,
+// expert list or (expert, tile) list).  Tile order: the n_x feature tiles of one token tile are adjacent, so the CTAs
+// running at one time share that token tile in L2.
+// ---------------------------------------------------------------------------------------------
+template <int BN, bool DUAL>
+struct PCfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
+    static constexpr int STAGING_BYTES = 2 * 16 * BM * 4;          // two [16 tokens][128 features] fp32 transposes
+    static constexpr int STAGES_RAW = (210 * 1024 - STAGING_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
+    static constexpr int TMEM_COLS = 2 * ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static_assert(2 * ACC_COLS <= 512, "two accumulator sets must fit tensor memory");
+    static_assert(ACC_COLS >= 128, "the persistent form is for wide token tiles");
+};
+
+struct PTile {
+    int n0, batch, row0, rows_valid, row_base;
+};
+
+// Work item -> tile; false: nothing to do (an expert without rows, an unused list slot, a token tile past the segment).
+template <int BN>
+__device__ __forceinline__ bool ptile_decode(const GemmArgs & args, int item, int n_x, int n_y, PTile & t) {
+    const int x = item % n_x, rest = item / n_x;
+    const int y = rest % n_y, slot = rest / n_y;
+    t.n0 = x * BM;
+    t.batch = slot;
+    t.row0 = y * BN;
+    t.rows_valid = args.T;
+    t.row_base = 0;
+    if (args.seg != nullptr) {
+        if (args.expert_list != nullptr) {
+            t.batch = args.expert_list[slot];
+            if (args.list_tiles && t.batch >= 0) {
+                t.row0 = (t.batch >> 16) * BN;
+                t.batch &= 0xffff;
+            }
+        }
+        if (t.batch < 0) return false;
+        t.row_base = args.seg[t.batch];
+        t.rows_valid = args.seg[t.batch + 1] - t.row_base;
+    }
+    return t.row0 < t.rows_valid;
+}
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+                       const __grid_constant__ CUtensorMap tmB, const GemmArgs args, const int n_x, const int n_y, const int n_items) {
+    using C = PCfg<BN, DUAL>;
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t * tiles = (uint8_t *) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    float * staging = (float *) (tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t * bars = (uint64_t *) ((uint8_t *) staging + C::STAGING_BYTES);
+    uint64_t * full = bars;
+    uint64_t * empty = bars + C::STAGES;
+    uint64_t * acc_ready = bars + 2 * C::STAGES;          // [2]
+    uint64_t * acc_empty = acc_ready + 2;                 // [2]
+    uint32_t * tmem_slot = (uint32_t *) (acc_empty + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_ready[b], 1); mbar_init(&acc_empty[b], 4); }
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        if (DUAL) prefetch_tmap(&tmA2);
+    }
+    // This kernel may take every tensor-memory column of its SM (tcgen05.alloc blocks until they are free): it asks only
+    // after the grid before it has completed and releases the grid after it only once it holds its columns.
+    pdl_wait();
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    pdl_launch_dependents();
+    const uint32_t tmem = *tmem_slot;
+    const int num_kb = (args.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                PTile t;
+                if (!ptile_decode<BN>(args, item, n_x, n_y, t)) continue;
+                const int b_z = args.seg != nullptr ? 0 : t.batch;
+                const int b_row = t.row_base + t.row0;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 11, item); ok = false; break; }
+                    uint8_t * st = tiles + s * C::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    tma_load_3d(st, &tmA, &full[s], kb * BK, t.n0, t.batch);
+                    if (DUAL) tma_load_3d(st + C::A_BYTES, &tmA2, &full[s], kb * BK, t.n0, t.batch);
+                    tma_load_3d(st + (DUAL ? 2 : 1) * C::A_BYTES, &tmB, &full[s], kb * BK, b_row, b_z);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16(BM, BN);
+            uint32_t it = 0;
+            int j = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                PTile t;
+                if (!ptile_decode<BN>(args, item, n_x, n_y, t)) continue;
+                const int buf = j & 1;
+                // the epilogue of the tile that used this accumulator set two tiles ago has read it
+                if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 12, item); ok = false; break; }
+                tc_fence_after();
+                const uint32_t acc = tmem + buf * C::ACC_COLS;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!mbar_wait(&full[s], ph)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 13, item); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + s * C::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + (DUAL ? 2 : 1) * C::A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t bd = desc_k_sw128(b_addr + kk * UMMA_K * 2);
+                        mma_bf16(acc, desc_k_sw128(a_addr + kk * UMMA_K * 2), bd, idesc, (kb | kk) != 0);
+                        if (DUAL) mma_bf16(acc + BN, desc_k_sw128(a_addr + C::A_BYTES + kk * UMMA_K * 2), bd, idesc, (kb | kk) != 0);
+                    }
+                    mma_commit(&empty[s]);
+                }
+                mma_commit(&acc_ready[buf]);       // also after a failed wait: the epilogue must not wait for good
+                ++j;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================= epilogue (warps 2..5) =================
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const int ltid = (int) threadIdx.x - 64;
+        int j = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            PTile t;
+            if (!ptile_decode<BN>(args, item, n_x, n_y, t)) continue;
+            const int buf = j & 1;
+            if (!mbar_wait(&acc_ready[buf], (j >> 1) & 1)) { jib_report(args.status, JIB_ERR_WAIT_TIMEOUT, 14, item); ok = false; }
+            {
+                // the four warps leave together or not at all: they meet at named barrier 1 inside the tile
+                uint32_t all;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                             : "=r"(all) : "r"((uint32_t) ok) : "memory");
+                ok = all != 0;
+            }
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tbase = tmem + buf * C::ACC_COLS + ((uint32_t) (q * 32) << 16);
+            const int ncols = min(BN, t.rows_valid - t.row0);
+            const long long obase = (long long) t.batch * args.out_batch_stride;
+            const long long rbase = (long long) t.batch * args.res_batch_stride;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (c >= ncols) break;
+                uint32_t gv[16], uv[16];
+                tmem_ld16(tbase + c, gv);
+                if (DUAL) tmem_ld16(tbase + BN + c, uv);
+                tmem_ld_wait();
+                float * sb = staging + ((c >> 4) & 1) * (16 * BM);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const float g = __uint_as_float(gv[k]);
+                    sb[k * BM + r] = DUAL ? silu(g) * __uint_as_float(uv[k]) : g;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    const int tok = (ltid >> 4) + h * 8, fg = (ltid & 15) * 8;
+                    const int col = c + tok, nn = t.n0 + fg;
+                    if (col >= ncols || nn >= args.N) continue;
+                    const long long row = t.row_base + t.row0 + col;
+                    if (row >= args.rows_total) { jib_report(args.status, JIB_ERR_BOUNDS, 15, (int) row); continue; }
+                    float4 a = *(const float4 *) (sb + tok * BM + fg), b = *(const float4 *) (sb + tok * BM + fg + 4);
+                    if (args.residual != nullptr) {
+                        const long long ri = rbase + row * args.ldr + nn;
+                        if (args.res_f32) {
+                            const float4 ra = *(const float4 *) ((const float *) args.residual + ri);
+                            const float4 rb = *(const float4 *) ((const float *) args.residual + ri + 4);
+                            a.x += ra.x; a.y += ra.y; a.z += ra.z; a.w += ra.w;
+                            b.x += rb.x; b.y += rb.y; b.z += rb.z; b.w += rb.w;
+                        } else {
+                            const uint4 raw = *(const uint4 *) ((const __nv_bfloat16 *) args.residual + ri);
+                            const float2 r0 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.x);
+                            const float2 r1 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.y);
+                            const float2 r2 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.z);
+                            const float2 r3 = __bfloat1622float2(*(const __nv_bfloat162 *) &raw.w);
+                            a.x += r0.x; a.y += r0.y; a.z += r1.x; a.w += r1.y;
+                            b.x += r2.x; b.y += r2.y; b.z += r3.x; b.w += r3.y;
+                        }
+                    }
+                    const uint2 lo = pack_bf16x4(a), hi = pack_bf16x4(b);
+                    __nv_bfloat16 * dst = args.row_ptr != nullptr
+                                              ? (__nv_bfloat16 *) __ldg((const unsigned long long *) args.row_ptr + row)
+                                              : (__nv_bfloat16 *) args.out + obase + row * args.ldo;
+                    if (dst != nullptr) *(uint4 *) (dst + nn) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                }
+            }
+            // this warp's tensor-memory reads of the set are complete: hand it back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            asm volatile("bar.sync 1, 128;" ::: "memory");       // the staging buffers start over with the next tile
+            ++j;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -782,6 +1016,28 @@ int launch(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b,
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }
 
+template <int BN, bool DUAL>
+int launch_persistent(const CUtensorMap & a, const CUtensorMap & a2, const CUtensorMap & b, const GemmArgs & args, int n_x, int n_y,
+                      long long n_items, int sms, cudaStream_t stream) {
+    using C = PCfg<BN, DUAL>;
+    static std::atomic<unsigned char> attr_done[jib::MAX_DEVICES];
+    if (!jib::ensure_dyn_smem(gemm_persistent_kernel<BN, DUAL>, C::SMEM_BYTES, attr_done)) return JIB_E_LAUNCH;
+    const int grid = (int) (n_items < sms ? n_items : sms);
+    const cudaError_t e = jib::launch_pdl(gemm_persistent_kernel<BN, DUAL>, dim3(grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, a, a2, b, args,
+                                          n_x, n_y, (int) n_items);
+    if (e != cudaSuccess) { (void) cudaGetLastError(); return JIB_E_LAUNCH; }
+    return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
+}
+
+// JIB_GEMM_PERSIST=0: launches with several waves of tiles use the one-tile-per-CTA kernel as well (A/B measurements).
+bool jib_no_persist() {
+    static const bool off = [] {
+        const char * e = getenv("JIB_GEMM_PERSIST");
+        return e != nullptr && e[0] == '0';
+    }();
+    return off;
+}
+
 }  // namespace
 
 JIB_TL_DEFINE_SETTER(gemm)
@@ -886,6 +1142,17 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
         if (d->N % 4 || ar->d_max % 4 || d->ldo % 4 || (d->residual != nullptr && d->ldr % 4)) return JIB_E_ALIGN;
         if (two_shot && (d->T > ar->max_rows2 || ar->recv2[0] == nullptr || (ar->n_sites & 1) || d->out_f32)) return JIB_E_ARG;
         a.ar = *ar; a.ar_on = two_shot ? 2 : 1; a.ar_site = d->ar_site;
+    }
+    // Several waves of wide tiles and nothing but a plain product: the persistent kernel (epilogue under the next tile's MMAs)
+    const int sms = d->sm_count > 0 ? d->sm_count : 148;
+    if (splits == 1 && a.ar_on == 0 && !src_mode && a.ag_flags == nullptr && a.vec_store && bn >= 128 && !(dual && bn > 128) &&
+        tiles_total >= 2LL * sms && tiles_total < (1LL << 30) && !jib_no_persist()) {
+        const int n_y = list_tiles ? 1 : t_tiles;
+        if (bn == 128) {
+            return dual ? launch_persistent<128, true>(ma, ma2, mb, a, n_tiles, n_y, tiles_total, sms, stream)
+                        : launch_persistent<128, false>(ma, ma2, mb, a, n_tiles, n_y, tiles_total, sms, stream);
+        }
+        return launch_persistent<256, false>(ma, ma2, mb, a, n_tiles, n_y, tiles_total, sms, stream);
     }
     dim3 grid(n_tiles, list_tiles ? 1 : t_tiles, n_slots * splits);
 #define JIB_GEMM_CASE(BN_)                                                                          \

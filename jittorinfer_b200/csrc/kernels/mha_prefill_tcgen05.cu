@@ -213,20 +213,23 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const uint32_t ts = tm_S + lane_addr + s * KT;
             const bool need_mask = (kt + 1) * KT > lim_first;          // the tile reaches the diagonal (or the sequence end)
             const int vis = lim - kt * KT;            // columns [0, vis) of this tile are visible to this row
-            // pass 1: row maximum of the tile
-            float mt = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < KT; c += 16) {
-                uint32_t v[16];
-                tmem_ld16(ts + c, v);
-                tmem_ld_wait();
+            // The row's 128 scores come out of tensor memory once, all loads in flight before one wait; the S buffer is
+            // handed back to the tensor core right away (Q.K^T of the tile after the next may start).
+            float x[KT];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float x = __uint_as_float(v[j]);
-                    if (!need_mask || c + j < vis) mt = fmaxf(mt, x);
-                }
+            for (int c = 0; c < KT; c += 16) tmem_ld16(ts + c, reinterpret_cast<uint32_t (&)[16]>(x[c]));
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[s]);
+            float mt = -INFINITY;
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < KT; ++c) { x[c] = c < vis ? x[c] * a.scale_log2e : -INFINITY; mt = fmaxf(mt, x[c]); }
+            } else {
+#pragma unroll
+                for (int c = 0; c < KT; ++c) { x[c] *= a.scale_log2e; mt = fmaxf(mt, x[c]); }
             }
-            mt *= a.scale_log2e;
             // the exponent base follows the maximum only when it has fallen behind by more than RESCALE_LAG
             const bool grow = mt > m_ref + RESCALE_LAG || m_ref == -INFINITY;
             const float m_new = grow ? mt : m_ref;
@@ -254,40 +257,30 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 l_sum *= exp2f(m_ref - m_new);        // kt == 0 cannot get here; kept for completeness
             }
             m_ref = m_new;
+            // p = 2^(x - base) in registers (the previous P.V may still be reading the P tile), row sum
+            const float base_l2 = m_ref == -INFINITY ? 0.f : m_ref;   // every x is -inf then: p = 0
+            uint32_t packed[KT / 2];
+#pragma unroll
+            for (int c = 0; c < KT; c += 2) {
+                const float p0 = exp2f(x[c] - base_l2), p1 = exp2f(x[c + 1] - base_l2);
+                l_sum += p0 + p1;
+                const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                packed[c >> 1] = *(const uint32_t *) &pk;
+            }
             // the previous P.V must have read P before it is overwritten
             if (kt > 0 && !mbar_wait(p_empty, (kt - 1) & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 38, kt); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
-            // pass 2: p = 2^(x - base), row sum, P (bf16) into the swizzled K-major tile
-#pragma unroll 1
-            for (int c = 0; c < KT; c += 16) {
-                uint32_t v[16];
-                tmem_ld16(ts + c, v);
-                tmem_ld_wait();
-                uint32_t packed[8];
+            // P (bf16) into the swizzled K-major tile: 8 kv columns = one 16-byte unit of row r in chunk c / 64
 #pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    float p0 = 0.f, p1 = 0.f;
-                    if (m_ref != -INFINITY) {
-                        if (!need_mask || c + j < vis) p0 = exp2f(__uint_as_float(v[j]) * a.scale_log2e - m_ref);
-                        if (!need_mask || c + j + 1 < vis) p1 = exp2f(__uint_as_float(v[j + 1]) * a.scale_log2e - m_ref);
-                    }
-                    l_sum += p0 + p1;
-                    const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                    packed[j >> 1] = *(const uint32_t *) &pk;
-                }
-                // 16 kv columns = two 16-byte units of row r in chunk c / 64
+            for (int c = 0; c < KT; c += 8) {
                 uint8_t * prow = p_s + (c >> 6) * CHUNK + r * 128;
                 const int u0 = (c & 63) >> 3;         // 16-byte unit index inside the 128-byte row
-                *(uint4 *) (prow + (((u0) ^ (r & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                *(uint4 *) (prow + (((u0 + 1) ^ (r & 7)) << 4)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                *(uint4 *) (prow + ((u0 ^ (r & 7)) << 4)) = make_uint4(packed[c / 2], packed[c / 2 + 1], packed[c / 2 + 2], packed[c / 2 + 3]);
             }
             fence_proxy_async();                      // P stores -> visible to the tensor core's async-proxy reads
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&s_empty[s]);             // this warp has read its S rows
-                mbar_arrive(p_full);
-            }
+            if (lane == 0) mbar_arrive(p_full);
         }
         // ---- epilogue: O / l -> bf16 rows ----
         if (ok && !mbar_wait(o_done, (n_tiles - 1) & 1)) { jib_report(a.status, JIB_ERR_WAIT_TIMEOUT, 39, 0); ok = false; }

@@ -46,9 +46,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t * bar) {
 }
 // One wait attempt: the thread may be suspended until the phase completes, but for no longer than the hint (the time a
 // try_wait without a hint may stay suspended is implementation-defined, which would make a poll count meaningless).
+#ifndef JIB_SUSPEND_NS
+#define JIB_SUSPEND_NS 20000        // 0: never suspend, poll with test_wait only (a build variant, to compare wake-up latency)
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, uint32_t parity) {
     uint32_t ok;
-    const uint32_t suspend_hint_ns = 20000;
+    const uint32_t suspend_hint_ns = JIB_SUSPEND_NS;
     asm volatile(
         "{\n\t.reg .pred P;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
@@ -83,13 +86,19 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t * bar, uint32_t parity) 
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity) {
+#if JIB_SUSPEND_NS > 0
     if (mbar_try_wait(bar, parity)) return true;          // the common case: one (possibly suspending) wait is enough
+#endif
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 0; i < JIB_SPIN_LIMIT; ++i) {
         if (mbar_test_wait(bar, parity)) return true;
         if ((i & 15) == 15) {
             if (globaltimer_ns() - t0 > JIB_WAIT_NS) return false;
+#if JIB_SUSPEND_NS > 0
             __nanosleep(64);
+#else
+            if (i > 4096) __nanosleep(64);                // a long wait: stop taking issue slots from the warps that work
+#endif
         }
     }
     return false;

@@ -5,6 +5,7 @@
     python -m jittorinfer_b200.ops.microbench moe --T 8 --E 64 --k 6 --F 1408 --d 2048
     python -m jittorinfer_b200.ops.microbench attn --B 8 --S 1280
     python -m jittorinfer_b200.ops.microbench prefill_gemm --T 4096 --N 4096 --K 4096
+    python -m jittorinfer_b200.ops.microbench prefill_attn --T 2048 --H 16
 
 Each case is timed with CUDA events on the launching stream after warm-up (synchronise on both
 sides); operands are larger than the 126 MB L2 or rotated over several buffers so that every
@@ -57,7 +58,7 @@ def report(name, ms, nbytes, flops, extra=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gateup", "moe", "attn", "prefill_gemm", "route", "combine_norm", "permute", "sample"])
+    ap.add_argument("case", choices=["gemm", "gateup", "moe", "attn", "prefill_attn", "prefill_gemm", "route", "combine_norm", "permute", "sample"])
     ap.add_argument("--T", type=int, default=8)
     ap.add_argument("--N", type=int, default=32768)
     ap.add_argument("--K", type=int, default=2048)
@@ -153,6 +154,26 @@ def main(argv=None):
         ms = timeit(fn, a.iters, a.warmup)
         report(f"mla decode B={B} S={S} H={H} impl={nat.ATTN_IMPL}" + (" [torch]" if a.torch else ""), ms, B * S * 576 * 2,
                2.0 * B * H * S * (576 + 512))
+    elif a.case == "prefill_attn":
+        # one prompt chunk of --T tokens of one sequence (nothing cached before it), --H heads of 128 + 64 / 128 dims: the
+        # per-head kernel alone (K / V already expanded), and the whole op (gather + expansion GEMM + kernel)
+        T, H, bs = a.T, a.H, 64
+        nb = (T + bs - 1) // bs
+        cache = rnd((nb + 1) * bs, 576, scale=0.5)
+        bt = torch.arange(1, nb + 1, dtype=torch.int32, device=dev).view(1, nb)
+        sl = torch.tensor([T], dtype=torch.int32, device=dev)
+        qs = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        q = rnd(T, H * 192, scale=0.5)
+        w_kv_b = rnd(H * 256, 512, scale=0.05)
+        meta = {"total_kv": T, "n_q_tiles": (T + 127) // 128}
+        lat, kv_start = nat.kv_gather(cache, bt, sl, T, bs)
+        kv = nat.gemm(lat[:, :512], w_kv_b)
+        flops = 2.0 * H * (192 + 128) * T * (T + 1) / 2
+        ms = timeit(lambda: nat.mha_prefill_core(q, kv, lat, kv_start, sl, qs, 0.1147, H, meta["n_q_tiles"]), a.iters, a.warmup)
+        report(f"prefill attention kernel T={T} H={H} (causal FLOPs)", ms, (T * H * (192 + 128) + kv.numel() + T * 64) * 2, flops)
+        ms = timeit(lambda: nat.mha_prefill(q, cache, w_kv_b, bt, sl, qs, 0.1147, H, bs, meta), a.iters, a.warmup)
+        report(f"prefill attention op (gather + K/V expansion + kernel) T={T} H={H}", ms, 0, flops + 2.0 * T * 512 * H * 256)
+        nat.check_status()
     elif a.case == "route":
         # router chain of one MoE layer: logits + gating + expert sort as three launches vs the one-launch kernel
         E, k, d, T = a.E, a.k, a.d, a.T

@@ -123,8 +123,9 @@ def test_real_shapes_logits_match_oracle_and_take_the_tensor_core_paths(name):
     clear = (top2[:, 0] - top2[:, 1]) > 0.05 * l_ref.abs().amax(dim=-1)
     clear &= err[:l_ref.shape[0]] <= tol                                        # a row whose routing flipped may also change its arg-max
     assert bool((l_nat.argmax(-1)[clear] == l_ref.argmax(-1)[clear]).all())
-    ran = {k: nat.launches_by_name.get(k, 0) - n0.get(k, 0) for k in ("mla_flash", "mla_attention", "gemm_grouped", "moe_gate")}
-    assert ran["mla_flash"] >= 2 * hp.n_layer and ran["mla_attention"] == 0, ran     # tcgen05 attention, not the SIMT fallback
+    ran = {k: nat.launches_by_name.get(k, 0) - n0.get(k, 0) for k in ("mla_flash", "mha_prefill", "mla_attention", "gemm_grouped", "moe_gate")}
+    # tcgen05 attention, not the SIMT fallback: the 70-token chunk in the per-head form, the 9-token one in the absorbed form
+    assert ran["mha_prefill"] == hp.n_layer and ran["mla_flash"] == hp.n_layer and ran["mla_attention"] == 0, ran
     assert ran["gemm_grouped"] >= 4 and ran["moe_gate"] >= 2, ran
     # 8 sequences decoding under CUDA graphs: tokens against the oracle's greedy continuation
     eng = LLMEngine(m, EngineConfig(n_ctx=8 * 256, n_batch=256, n_parallel=8, graph_buckets=(1, 2, 4, 8)))
