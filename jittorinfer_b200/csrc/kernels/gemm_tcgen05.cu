@@ -1058,6 +1058,14 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
         if (dual && bn > 128) bn = 128;     // keeps three pipeline stages in shared memory
     }
     const int n_tiles = (d->N + BM - 1) / BM;
+    const int sms = d->sm_count > 0 ? d->sm_count : 148;
+    if (d->bn == 0 && bn == 256 && !grouped && d->ar == nullptr && !d->out_f32 && !jib_no_persist()) {
+        // Between one and two waves of 256-token tiles the second wave runs half empty and every CTA pays its prologue and
+        // epilogue in the open; the same product as 128-token tiles fills the persistent kernel's two to four rounds evenly
+        // with the epilogues hidden (2048 x 2048 x 2048: 25 us -> the persistent form).
+        const long long t256 = (long long) n_tiles * ((rows_bound + 255) / 256) * batch;
+        if (t256 < 2LL * sms && 4 * t256 >= 3LL * sms) bn = 128;
+    }
     const int t_tiles = (rows_bound + bn - 1) / bn;
     const int num_kb = (d->K + BK - 1) / BK;
     // split-K: fill the machine when there are too few output tiles
@@ -1144,9 +1152,8 @@ extern "C" JIB_EXPORT int jib_gemm_bf16(const jib_gemm_desc * d, void * stream_)
         a.ar = *ar; a.ar_on = two_shot ? 2 : 1; a.ar_site = d->ar_site;
     }
     // Several waves of wide tiles and nothing but a plain product: the persistent kernel (epilogue under the next tile's MMAs)
-    const int sms = d->sm_count > 0 ? d->sm_count : 148;
     if (splits == 1 && a.ar_on == 0 && !src_mode && a.ag_flags == nullptr && a.vec_store && bn >= 128 && !(dual && bn > 128) &&
-        tiles_total >= 2LL * sms && tiles_total < (1LL << 30) && !jib_no_persist()) {
+        2 * tiles_total >= 3LL * sms && tiles_total < (1LL << 30) && !jib_no_persist()) {
         const int n_y = list_tiles ? 1 : t_tiles;
         if (bn == 128) {
             return dual ? launch_persistent<128, true>(ma, ma2, mb, a, n_tiles, n_y, tiles_total, sms, stream)

@@ -69,6 +69,44 @@ def test_gemm_gateup_silu(nat, T, splits):
     nat.check_status()
 
 
+def test_gemm_several_waves_takes_the_persistent_kernel(nat, monkeypatch):
+    """Launches of several waves of wide tiles run as one CTA per SM walking the tile list with two accumulator sets in
+    tensor memory: dense with a residual and a ragged last token tile, gate|up, and the grouped pair of a prompt chunk
+    (tile list).  Each against fp32 and against the one-tile-per-CTA kernel (bitwise: same tiles, same order of sums)."""
+    import os
+    x, w, res = rnd(2000, 1088), rnd(5120, 1088, scale=0.05), rnd(2000, 5120, seed=7)
+    y = nat.gemm(x, w, residual=res)
+    close(y, x.float() @ w.float().T + res.float(), tol=1e-2)
+    x2, wg, wu = rnd(1500, 512), rnd(4096, 512, scale=0.05), rnd(4096, 512, scale=0.05, seed=3)
+    y2 = nat.gemm(x2, wg, wu)
+    close(y2, torch.nn.functional.silu(x2.float() @ wg.float().T) * (x2.float() @ wu.float().T))
+    w4 = rnd(2048, 1088, scale=0.05, seed=11)          # between one and two waves of 256-token tiles: 128-token tiles instead
+    y4 = nat.gemm(x, w4)
+    close(y4, x.float() @ w4.float().T, tol=1e-2)
+    T, E, k, d, F = 2048, 64, 6, 1024, 768
+    xm = rnd(T, d)
+    eg, eu, ed = rnd(E, F, d, scale=0.05), rnd(E, F, d, scale=0.05, seed=5), rnd(E, d, F, scale=0.05)
+    g = torch.Generator().manual_seed(T)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).int().to(DEV)
+    wts = torch.rand(T, k, generator=g).to(DEV)
+    y3 = nat.moe_experts(xm, ids, wts, eg, eu, ed, 0)
+    close(y3, ref.moe_experts(xm, ids, wts, eg, eu, ed, 0), tol=3e-2)
+    nat.check_status()
+    # the same three through the other kernel (the switch is read once per process by the library: a child process)
+    import subprocess, sys
+    code = ("import torch, sys; sys.path.insert(0, %r); from tests.test_gpu_kernels import rnd, DEV; from jittorinfer_b200.ops import native as nat; nat.load();"
+            "x, w, res = rnd(2000, 1088), rnd(5120, 1088, scale=0.05), rnd(2000, 5120, seed=7);"
+            "x2, wg, wu = rnd(1500, 512), rnd(4096, 512, scale=0.05), rnd(4096, 512, scale=0.05, seed=3);"
+            "w4 = rnd(2048, 1088, scale=0.05, seed=11);"
+            "torch.save([nat.gemm(x, w, residual=res).cpu(), nat.gemm(x2, wg, wu).cpu(), nat.gemm(x, w4).cpu()], sys.argv[1]); nat.check_status()") % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    import tempfile
+    with tempfile.TemporaryDirectory() as td:
+        out = os.path.join(td, "o.pt")
+        subprocess.run([sys.executable, "-c", code, out], check=True, env=dict(os.environ, JIB_GEMM_PERSIST="0"), timeout=300)
+        a, b, c4 = torch.load(out)
+    assert torch.equal(a, y.cpu()) and torch.equal(b, y2.cpu()) and torch.equal(c4, y4.cpu())
+
+
 def test_gemm_strided_rows(nat):
     big = rnd(9, 1000)
     x = big[:, 104:104 + 512]            # row stride 1000, 16-byte aligned start
