@@ -111,6 +111,9 @@ def main():
     ap.add_argument("--no-same-model", action="store_true", help="skip the fixed-model strong-scaling sub-record")
     ap.add_argument("--no-http", action="store_true", help="skip the through-the-server sub-record (1 GPU only)")
     ap.add_argument("--same-model-layers", type=int, default=12)
+    ap.add_argument("--experts", default=os.environ.get("JITTORINFER_BENCH_EXPERTS", "ep"), choices=["ep", "tp"],
+                    help="N > 1: routed experts sharded by expert (ep: every rank holds E / N whole experts, the reference's layout) or "
+                         "by FFN column (tp: every rank holds 1 / N of every expert, no load imbalance between ranks at small batches)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: dry run of this script's whole flow on the reference ops with --model tiny (a check of the "
                          "script, not a measurement)")
@@ -254,7 +257,8 @@ def main():
                                   f"prefill included, {n_steps} engine steps, wall clock"}
         return out
 
-    eng = build_engine(hp, device=dev, world=world, rank=rank, n_parallel=C, n_ctx_slot=total_len + 64,
+    ep_shard = args.experts == "ep"
+    eng = build_engine(hp, device=dev, world=world, rank=rank, expert_parallel=ep_shard, n_parallel=C, n_ctx_slot=total_len + 64,
                        n_batch=2048, seed=0, graph_buckets=buckets(C), run_ahead=args.run_ahead)
     weight_gib = eng.model.weight_bytes() / 2**30
     note(f"model built: {weight_gib:.1f} GiB of weights on this rank")
@@ -321,14 +325,14 @@ def main():
         if cuda:
             torch.cuda.empty_cache()
         hp2 = preset("v2").replace(n_layer=args.same_model_layers)
-        eng2 = build_engine(hp2, device=dev, world=world, rank=rank, n_parallel=C, n_ctx_slot=total_len + 64, n_batch=2048,
+        eng2 = build_engine(hp2, device=dev, world=world, rank=rank, expert_parallel=ep_shard, n_parallel=C, n_ctx_slot=total_len + 64, n_batch=2048,
                             seed=0, graph_buckets=buckets(C), comm=comm)
         note(f"same_model built: {eng2.model.weight_bytes() / 2**30:.1f} GiB on this rank")
         eng2.warmup()
         rec = {}
         for c in ([C] if args.no_sweep else sorted({1, C})):
             rec[str(c)] = record(eng2, hp2, c, False)
-        same_model = {"model": f"DeepSeek-V2 architecture, {hp2.n_layer} layers, random init", "parallelism": f"tp{world}+ep{world}" if world > 1 else "single GPU",
+        same_model = {"model": f"DeepSeek-V2 architecture, {hp2.n_layer} layers, random init", "parallelism": (f"tp{world}+ep{world}" if ep_shard else f"tp{world}") if world > 1 else "single GPU",
                       "scaling": "strong", "global_batch": C, "value": rec[str(C)]["value"], "unit": "tokens/s", "by_concurrency": rec}
         synchronize()
         if args.ops == "native" and cuda:
@@ -338,7 +342,8 @@ def main():
     if rank == 0:
         full = (model_name == "lite" and world == 1 and hp.n_layer == 27) or (model_name == "v2" and world == 8 and hp.n_layer == 60)
         base = BASELINE.get((model_name, C)) if full else None
-        par = "single GPU" if world == 1 else f"tp{world}+ep{world} (attention heads and routed experts sharded, fused GEMM+all-reduce)"
+        par = "single GPU" if world == 1 else (f"tp{world}+ep{world} (attention heads and routed experts sharded, fused GEMM+all-reduce)" if ep_shard
+                                               else f"tp{world} (attention heads and every expert's FFN columns sharded, fused GEMM+all-reduce)")
         for c, r in by_conc.items():
             b = BASELINE.get((model_name, int(c))) if full else None
             r["vs_baseline"] = round(r["value"] / b, 3) if b else None
