@@ -237,12 +237,14 @@ class DeepSeek2Model:
         self._uploaders.clear()               # release the pinned staging buffers
         if self.w_out is None:
             self.w_out = self.tok_embd if self.out_device == self.device else self.tok_embd.to(self.out_device)
-        if not self.spec.sharded:
-            # single-GPU: the shared experts have the routed experts' shape, so they become experts E, E+1, ... of the
-            # grouped GEMMs (two fewer launches per layer, better fill); the router appends them to every token
-            F = hp.n_ff_exp
+        if not self.spec.sharded or not (self.spec.expert_parallel or self.spec.dp_attention):
+            # single GPU, or every expert's FFN columns sharded over the ranks: the (local part of the) shared experts has
+            # the (local) routed experts' shape, so it becomes experts E, E+1, ... of the grouped GEMMs (two fewer launches
+            # per layer, better fill); the router appends them to every token.  Any split of the shared FFN's hidden units
+            # into groups of the local expert width is a valid set of experts: the block is a sum over hidden units.
             for L in self.layers:
                 L.n_shared_merged = 0
+                F = L.w_gate_exps.shape[1] if L.is_moe and L.w_gate_exps is not None else hp.n_ff_exp
                 if L.is_moe and L.w_gate_sh is not None and L.w_gate_sh.shape[0] % F == 0:
                     ns, d = L.w_gate_sh.shape[0] // F, hp.n_embd
                     L.w_gate_exps = torch.cat([L.w_gate_exps, L.w_gate_sh.view(ns, F, d)], dim=0)
@@ -376,8 +378,8 @@ class DeepSeek2Model:
             else:
                 g = comm.all_gather_rows(g_loc)
                 ids, wts = ops.moe_gate(g, L.w_router, L.router_bias, hp.n_expert_used, hp.n_group, hp.topk_group,
-                                        hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid", 0,
-                                        hp.group_score_top2)
+                                        hp.expert_weights_scale, hp.expert_weights_norm, hp.expert_gating_func == "sigmoid",
+                                        L.n_shared_merged or 0, hp.group_score_top2)
                 base = self.expert_base if self.spec.expert_parallel else 0
                 part = ops.moe_ffn(g, None, ids, wts, L.w_gate_exps, L.w_up_exps, L.w_down_exps, L.w_gate_sh, L.w_up_sh,
                                    L.w_down_sh, base)

@@ -131,9 +131,9 @@ def test_q_absorb_v_up(nat, T):
     nat.check_status()
 
 
-@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (8, 64, 6), (50, 64, 6), (300, 16, 4)])
-def test_moe_routed(nat, T, E, k):
-    d, F = 512, 384
+@pytest.mark.parametrize("T,E,k,d,F", [(1, 8, 2, 512, 384), (8, 64, 6, 512, 384), (50, 64, 6, 512, 384), (300, 16, 4, 512, 384),
+                                       (8, 160, 6, 5120, 192), (1, 160, 6, 5120, 192)])     # last two: a rank's share of every
+def test_moe_routed(nat, T, E, k, d, F):                                                     # DeepSeek-V2 expert at TP 8
     x = rnd(T, d)
     wg, wu, wd = rnd(E, F, d, scale=0.05), rnd(E, F, d, scale=0.05, seed=5), rnd(E, d, F, scale=0.05)
     g = torch.Generator().manual_seed(T)
