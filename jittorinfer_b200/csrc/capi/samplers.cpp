@@ -315,7 +315,8 @@ struct DryCtx {
     int32_t n_ctx_train;
     float multiplier, base;
     int32_t allowed_length, last_n;
-    std::vector<uint8_t> is_breaker;    // per token id
+    std::vector<uint8_t> is_breaker;    // per token id: the token's text contains a breaker string
+    std::vector<std::vector<llama_token>> multi;   // breaker strings that no single token contains, as token sequences
     std::vector<llama_token> hist;      // most recent last, capped at the effective window
     int32_t window() const { return last_n < 0 ? n_ctx_train : last_n; }
 };
@@ -338,6 +339,14 @@ void dry_apply(llama_sampler * s, arr_t * a) {
     // a match cannot reach back across a breaker: cap = number of trailing non-breaker tokens
     size_t cap = 0;
     while (cap < n && !breaker(h[n - 1 - cap])) ++cap;
+    // ... nor across a breaker that is spelled with several tokens: the most recent place where such a sequence ends
+    for (const std::vector<llama_token> & seq : c->multi) {
+        const size_t L = seq.size();
+        for (size_t back = 0; back < cap && back + L <= n; ++back) {       // the sequence ends `back` tokens before the end
+            const llama_token * at = h + (n - back - L);
+            if (std::equal(seq.begin(), seq.end(), at)) { cap = back; break; }
+        }
+    }
     if (cap == 0) return;
     // Z-function of the reversed history: z[i] = length of the match between the text ending at the end and the
     // text ending at position n-1-i
@@ -626,12 +635,21 @@ llama_sampler * llama_sampler_init_dry(const llama_vocab * vocab, int32_t n_ctx_
         for (size_t i = 0; i < num_breakers; ++i)
             if (seq_breakers[i] != nullptr && seq_breakers[i][0] != 0) brk.emplace_back(seq_breakers[i]);
         char buf[256];
+        std::vector<uint8_t> found(brk.size(), 0);
         for (int32_t t = 0; t < V && !brk.empty(); ++t) {
             const int32_t len = llama_token_to_piece(vocab, t, buf, (int32_t) sizeof(buf), 0, true);
             if (len <= 0) continue;
             const std::string piece(buf, (size_t) len);
-            for (const std::string & b : brk)
-                if (piece.find(b) != std::string::npos) { c->is_breaker[(size_t) t] = 1; break; }
+            for (size_t i = 0; i < brk.size(); ++i)
+                if (piece.find(brk[i]) != std::string::npos) { c->is_breaker[(size_t) t] = 1; found[i] = 1; }
+        }
+        // a breaker that only ever appears spread over several tokens is matched as the token sequence it tokenises to
+        // (the reference keeps head token -> tail sequences for the same purpose, src/llama-sampling.cpp:895)
+        for (size_t i = 0; i < brk.size(); ++i) {
+            if (found[i]) continue;
+            llama_token ids[64];
+            const int32_t n = llama_tokenize(vocab, brk[i].c_str(), (int32_t) brk[i].size(), ids, 64, false, false);
+            if (n >= 2) c->multi.emplace_back(ids, ids + n);
         }
     }
     return llama_sampler_init(&dry_i, c);

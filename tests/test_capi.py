@@ -145,6 +145,36 @@ def test_sampler_penalties_bias_dry(L):
     L.llama_sampler_free(s)
 
 
+def test_dry_breaker_spelled_with_several_tokens(L, gguf_path):
+    """A sequence breaker that no single token contains ("ab" in the byte-level toy vocabulary) stops a repetition match like
+    a one-token breaker does: the match may not reach back across the place where the token sequence "a" "b" ends."""
+    mp = L.llama_model_default_params()
+    mp.vocab_only = True
+    model = L.llama_model_load_from_file(gguf_path.encode(), mp)
+    vocab = L.llama_model_get_vocab(model)
+    buf = (capi.llama_token * 16)()
+
+    def ids(text):
+        n = L.llama_tokenize(vocab, text.encode(), len(text), buf, 16, False, False)
+        return list(buf[:n])
+    (a, b), (q,), (x,), (y,), (z,) = ids("ab"), ids("q"), ids("x"), ids("y"), ids("z")
+    hist = [q, a, b, x, y, z, q, a, b, x, y]           # "q a b x y" repeats; z followed its first occurrence
+    n_vocab = L.llama_vocab_n_tokens(vocab)
+
+    def penalty_on_z(breakers):
+        arr = (C.c_char_p * len(breakers))(*[s.encode() for s in breakers]) if breakers else None
+        smp = L.llama_sampler_init_dry(vocab, 64, 0.8, 1.75, 2, -1, arr, len(breakers))
+        for t in hist:
+            L.llama_sampler_accept(smp, t)
+        _, out = apply(L, smp, [0.0] * n_vocab)
+        L.llama_sampler_free(smp)
+        return -{o[0]: o[1] for o in out}[z]
+    assert abs(penalty_on_z([]) - 0.8 * 1.75 ** 3) < 1e-4              # repeat of length 5, allowed 2
+    assert abs(penalty_on_z(["ab"]) - 0.8) < 1e-5                      # only "x y" after the breaker counts: length 2
+    assert abs(penalty_on_z(["y"]) - 0.0) < 1e-6                       # a one-token breaker right at the end: no match at all
+    L.llama_model_free(model)
+
+
 def test_sampler_chain_dist_clone_and_perf(L):
     p = capi.SamplerChainParams(False)
     chain = L.llama_sampler_chain_init(p)
