@@ -20,6 +20,9 @@ What has to be stood in for, and how (nothing of the checkout is modified; a COP
   ``GGML_OP_RMS_NORM_FUSED``, and ``MUL`` of an f32 activation with an f16 norm weight (src/llama-graph-utils.cpp:93-95 casts
   every norm weight to half precision for the device).  Each gets a plain loop in the copied ``ggml-cpu.c``.
 
+The other direction is checked too: ``ref_rewrite`` passes the file through the reference's GGUF reader and writer, and the
+result is byte-identical to what this package wrote (same key order, tensor order, alignment and padding).
+
 Known difference that the comparison has to avoid: the reference ranks ALL experts and ignores ``n_group`` / ``topk_group``
 (src/llama-graph-ffn.cpp:173-176), so a configuration with group-limited routing is compared with ``n_group = 1``.
 The f16 cache and f16 norm weights of the reference bound the agreement at a few 1e-3 of the largest logit.
@@ -155,6 +158,43 @@ int main(int argc, char ** argv) {
 '''
 
 
+REWRITE_CPP = r'''// usage: ref_rewrite in.gguf out.gguf -- read a file with the reference's GGUF reader, write it back with its writer
+#include <cstdio>
+#include "ggml.h"
+#include "gguf.h"
+int main(int argc, char ** argv) {
+    if (argc < 3) return 2;
+    struct ggml_context * data = nullptr;
+    struct gguf_init_params p = { /*no_alloc=*/false, /*ctx=*/&data };
+    struct gguf_context * g = gguf_init_from_file(argv[1], p);
+    if (!g) { fprintf(stderr, "read failed\n"); return 1; }
+    // a fresh writer context: the keys copied over, the tensors added in file order from the loaded data (the tensor records of
+    // a context that was READ carry an uninitialised buffer field, which the writer would follow)
+    struct gguf_context * w = gguf_init_empty();
+    gguf_set_kv(w, g);
+    for (int64_t i = 0; i < gguf_get_n_tensors(g); ++i) {
+        struct ggml_tensor * t = ggml_get_tensor(data, gguf_get_tensor_name(g, i));
+        if (!t) { fprintf(stderr, "tensor %lld missing\n", (long long) i); return 1; }
+        gguf_add_tensor(w, t);
+    }
+    if (!gguf_write_to_file(w, argv[2], false)) { fprintf(stderr, "write failed\n"); return 1; }
+    gguf_free(w);
+    gguf_free(g);
+    ggml_free(data);
+    return 0;
+}
+'''
+
+
+def build_rewriter(workdir: str) -> str:
+    """``ref_rewrite``: the reference's GGUF reader + writer as a filter (after ``build``, which made the objects)."""
+    open(os.path.join(workdir, "ref_rewrite.cpp"), "w").write(REWRITE_CPP)
+    objs = [os.path.relpath(o, workdir) for o in sorted(glob.glob(os.path.join(workdir, "obj", "ggml_*.o")))]
+    subprocess.run(["g++", "-std=c++17", "-O1", "-w", "-Iggml/include", "-Iggml/src", "ref_rewrite.cpp", *objs, "-o", "ref_rewrite",
+                    "-lpthread", "-ldl", "-lm", "-fopenmp"], cwd=workdir, check=True)
+    return os.path.join(workdir, "ref_rewrite")
+
+
 def _patch_cpu_dispatch(path: str) -> None:
     """Adds the three plain kernels to the COPIED ggml-cpu.c and routes their ops to them."""
     s = open(path).read()
@@ -273,6 +313,11 @@ def main(argv=None) -> int:
         print(json.dumps({"case": name, "layers": hp.n_layer, "positions": len(toks), "max_abs_diff": round(err, 5), "largest_logit": round(mag, 4),
                           "argmax_agreement": agree}))
         rc |= int(err > 1e-2 * max(mag, 1.0) or agree < 1.0)
+        # the other direction: the reference's GGUF writer re-emits the file; this package's reader must see the same tensors
+        back = os.path.join(args.workdir, f"case_{name}_rewritten.gguf")
+        subprocess.run([build_rewriter(args.workdir), path, back], check=True, stderr=subprocess.DEVNULL)
+        import filecmp
+        print(json.dumps({"case": name, "rewritten_by_the_reference_writer": "byte-identical" if filecmp.cmp(path, back, shallow=False) else "differs"}))
         saved[f"{name}_tokens"] = np.asarray(toks, dtype=np.int32)
         saved[f"{name}_logits"] = ref
     if args.save:

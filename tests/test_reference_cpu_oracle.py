@@ -61,3 +61,9 @@ def test_stubbed_build_of_the_reference_reproduces_the_stored_logits(tmp_path):
     write_random_gguf(path, hp, seed=0, std=0.05)
     live = R.reference_logits(exe, path, gold["v2_tokens"].tolist(), str(tmp_path))
     assert np.abs(live - gold["v2_logits"]).max() <= 1e-4
+    # and back: the reference's GGUF writer re-emits the file byte for byte
+    import filecmp
+    import subprocess
+    back = str(tmp_path / "back.gguf")
+    subprocess.run([R.build_rewriter(str(tmp_path)), path, back], check=True)
+    assert filecmp.cmp(path, back, shallow=False)
