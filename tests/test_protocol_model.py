@@ -288,3 +288,101 @@ def test_two_shot_with_more_tiles_than_resident_ctas_needs_one_dispatch_order():
     # resident elsewhere, and every rank ends up waiting (in the kernels such a wait is bounded and reports a timeout)
     mixed = [list(range(n_tiles))] * (world - 1) + [list(reversed(range(n_tiles)))]
     assert not any(_two_shot_resident(world, n_tiles, slots, mixed, seed) for seed in range(50))
+
+
+# ---- the persistent GEMM's roles inside one CTA (gemm_persistent_kernel): TMA producer, MMA issuer, four epilogue warps ------------
+# mbarriers are modelled as phase counters; a wait on parity P passes when the phase of parity P has completed, i.e. when the
+# barrier's current phase has the other parity -- exactly what mbarrier.test_wait.parity answers.  Ring slots and accumulator
+# sets carry tags, so a slot overwritten before the MMA read it, or an accumulator set reused before all four epilogue warps
+# read it, shows as a wrong tag.
+def _phase_wait(key, parity):
+    return lambda mem: (mem.get(key, 0) & 1) != parity
+
+
+def _persistent_roles(stages, num_kb, n_items, n_epi=4):
+    def producer():
+        it = 0
+        for j in range(n_items):
+            for kb in range(num_kb):
+                s, ph = it % stages, (it // stages) & 1
+                yield ("wait", _phase_wait(("empty", s), ph ^ 1))
+                yield ("store", ("ring", s), (j, kb))
+                yield ("add", ("full", s))                     # the TMA transaction completes the slot's phase
+                it += 1
+
+    def mma():
+        it = 0
+        for j in range(n_items):
+            b = j & 1
+            yield ("wait", _phase_wait(("acc_empty", b), ((j >> 1) & 1) ^ 1))
+            for kb in range(num_kb):
+                s, ph = it % stages, (it // stages) & 1
+                yield ("wait", _phase_wait(("full", s), ph))
+                yield ("check", ("ring", s), (j, kb))
+                yield ("store", ("acc", b), (j, kb))
+                yield ("add", ("empty", s))                    # tcgen05.commit: the slot may be refilled
+                it += 1
+            yield ("add", ("acc_ready", b))
+
+    def epilogue(w):
+        for j in range(n_items):
+            b = j & 1
+            yield ("wait", _phase_wait(("acc_ready", b), (j >> 1) & 1))
+            yield ("check", ("acc", b), (j, num_kb - 1))
+            yield ("arrive", ("acc_empty", b), n_epi)          # the phase completes with the fourth warp's arrival
+    return [producer(), mma()] + [epilogue(w) for w in range(n_epi)]
+
+
+class _PhaseSim(Sim):
+    """Sim plus two barrier operations: "add" completes a phase, "arrive" completes one after `count` arrivals."""
+
+    def run(self, max_steps=2_000_000):
+        n = len(self.programs)
+        while not all(self.done):
+            ready = [r for r in range(n) if self._runnable(r)]
+            if not ready and all(self.done):
+                break
+            assert ready, "deadlock: every role waits"
+            r = self.bias if self.bias is not None and self.bias in ready and self.rng.random() < 0.9 else self.rng.choice(ready)
+            op = self.pending[r]
+            self.pending[r] = None
+            if op[0] == "store":
+                self.mem[op[1]] = op[2]
+            elif op[0] == "check":
+                assert self.mem.get(op[1]) == op[2], f"role {r} read {self.mem.get(op[1])} at {op[1]}, expected {op[2]}"
+            elif op[0] == "add":
+                self.mem[op[1]] = self.mem.get(op[1], 0) + 1
+            elif op[0] == "arrive":
+                k = ("pending",) + op[1]
+                self.mem[k] = self.mem.get(k, 0) + 1
+                if self.mem[k] == op[2]:
+                    self.mem[k] = 0
+                    self.mem[op[1]] = self.mem.get(op[1], 0) + 1
+            self.steps += 1
+            assert self.steps < max_steps
+
+
+@pytest.mark.parametrize("stages,num_kb", [(3, 1), (4, 2), (4, 5), (6, 22), (4, 32)])
+def test_persistent_gemm_pipeline_never_reads_a_slot_or_an_accumulator_out_of_turn(stages, num_kb):
+    for seed in range(60):
+        for bias in (None, 0, 1, 2):                           # also: the producer, the MMA issuer or one epilogue warp races ahead
+            _PhaseSim(_persistent_roles(stages, num_kb, n_items=7), seed, bias).run()
+
+
+def test_the_pipeline_model_catches_a_single_accumulator_set():
+    """Without the second accumulator set (b = 0 for every tile, the wait parities unchanged) the MMA issuer overwrites what
+    the epilogue has yet to read, or the roles block each other: the model has to notice."""
+    def broken(stages, num_kb, n_items):
+        roles = _persistent_roles(stages, num_kb, n_items)
+
+        def one_set(gen):
+            for op in gen:
+                if len(op) > 1 and isinstance(op[1], tuple) and op[1][0] in ("acc", "acc_ready", "acc_empty"):
+                    op = (op[0], (op[1][0], 0)) + tuple(op[2:])
+                elif op[0] == "wait":
+                    pass
+                yield op
+        return [one_set(g) for g in roles]
+    with pytest.raises(AssertionError):
+        for seed in range(40):
+            _PhaseSim(broken(4, 2, 7), seed, 1).run()
