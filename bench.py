@@ -149,8 +149,8 @@ def main():
         new_event = lambda: torch.cuda.Event(enable_timing=True)      # noqa: E731
         synchronize = torch.cuda.synchronize
     else:
-        if world > 1 or (args.model or "lite") != "tiny":
-            raise SystemExit("--device cpu is a single-process dry run with --model tiny")
+        if (args.model or "lite") != "tiny":
+            raise SystemExit("--device cpu is a dry run of the script with --model tiny (one process, or gloo ranks under torchrun)")
         dev = torch.device("cpu")
 
         class _HostEvent:
@@ -162,7 +162,10 @@ def main():
         new_event = _HostEvent
         synchronize = lambda: None                                     # noqa: E731
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        if cuda:
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            dist.init_process_group("gloo")
     if args.ops == "torch":
         ops.set_force_torch(True)
 
@@ -173,10 +176,14 @@ def main():
     elif model_name == "v2" and world < 8:
         hp = hp.replace(n_layer=max(2, 60 * world // 8))
     C = args.concurrency
-    total_len = args.prompt_len + args.gen_len
     K, W = args.steps, args.warmup
-    if W + K >= args.gen_len:
-        raise SystemExit("steps + warmup must be smaller than --gen-len")
+    if K < 1:
+        raise SystemExit("--steps must be at least 1")
+    if W + K + 4 >= args.gen_len:
+        # the requested number of timed steps does not fit the configured generation length: generate longer rather than
+        # refuse (one region; the JSON line's config carries the length actually used)
+        args.gen_len = W + K + 8
+    total_len = args.prompt_len + args.gen_len
     R = max(1, min(args.regions, (args.gen_len - W - 4) // K))
     bandwidth = default_bandwidth()
 
@@ -385,7 +392,7 @@ def main():
     sys.stdout.flush()
     if world > 1:
         dist.barrier()
-        torch.cuda.synchronize()
+        synchronize()
         # leave without interpreter teardown: destroying captured graphs that hold communicator state after the
         # process group is gone can block at exit
         os._exit(0)

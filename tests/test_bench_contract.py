@@ -42,3 +42,26 @@ def test_reference_arm_reports_unavailable():
     assert r.returncode == 0
     out = json.loads(r.stdout.strip().splitlines()[-1])
     assert out["impl"] == "reference" and "unavailable" in out
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("experts", ["tp", "ep"])
+def test_bench_dry_run_on_two_ranks(experts):
+    """The multi-rank flow of the script (barriers, maximum over ranks, the same-model record that reuses the communicator, both
+    expert layouts) as two gloo ranks on the CPU: rank 0 prints the one JSON line."""
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(ROOT, "bench.py"), "--gpus", "2", "--device", "cpu", "--model", "tiny", "--steps", "3",
+           "--warmup", "3", "--prompt-len", "8", "--gen-len", "12", "--concurrency", "2", "--experts", experts, "--no-same-model"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=800, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    out = json.loads(lines[0])
+    assert REQUIRED <= set(out) and out["n_gpus"] == 2 and out["value"] > 0
+    assert out["config"]["parallelism"].startswith("tp2+ep2" if experts == "ep" else "tp2 ")
+    assert set(out["by_concurrency"]) == {"1", "2"} and out["e2e"]["value"] > 0
