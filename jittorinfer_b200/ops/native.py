@@ -379,8 +379,13 @@ MHA_PREFILL_MIN_TOKENS = 64
 
 def mha_prefill_ok(T: int, dn: int, dr: int, dv: int, r: int, block_size: int, meta) -> bool:
     """Whether a chunk of T query tokens takes the per-head prefill attention (needs the host-side totals in ``meta``)."""
-    return bool(MHA_PREFILL and meta is not None and T >= MHA_PREFILL_MIN_TOKENS and dn == 128 and dr == 64 and dv == 128 and r == 512
-                and meta.get("total_kv", 0) > 0)
+    if not (MHA_PREFILL and meta is not None and T >= MHA_PREFILL_MIN_TOKENS and dn == 128 and dr == 64 and dv == 128 and r == 512):
+        return False
+    total, dec = meta.get("total_kv", 0), meta.get("kv_decode", 0)
+    # Expanding K / V costs ~4 MFLOP per cached row and pays for itself over the many query rows of a prompt; a sequence that
+    # only decodes brings one query row and its whole context.  A mixed step whose gathered rows are mostly such contexts
+    # stays with the absorbed form, which reads the latent rows as they are.
+    return total > 0 and dec <= total - dec
 
 
 def kv_gather(cache, block_tables, seq_lens, total: int, block_size: int):

@@ -281,7 +281,10 @@ class LLMEngine:
             # K / V buffers and of the attention grid of the per-head prefill form
             h = self.io.h
             qs = h["q_start"][:n_seqs + 1]
-            meta = {"total_kv": int(h["seq_lens"][:n_seqs].sum()), "n_q_tiles": int(((np.diff(qs) + 127) // 128).sum())}
+            q_len, s_len = np.diff(qs), h["seq_lens"][:n_seqs]
+            # kv_decode: cached rows of the sequences that only decode in this step (the per-head form would expand them all)
+            meta = {"total_kv": int(s_len.sum()), "n_q_tiles": int(((q_len + 127) // 128).sum()),
+                    "kv_decode": int(s_len[q_len <= 1].sum())}
         return ForwardBatch(tokens=d["tokens"][:n_tokens], positions=d["positions"][:n_tokens],
                             slot_mapping=d["slot_mapping"][:n_tokens],
                             block_tables=d["block_tables"].view(self.io.cap_seqs, self.max_blocks)[:n_seqs],
