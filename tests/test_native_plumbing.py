@@ -80,3 +80,17 @@ def test_model_calls_fit_the_native_signatures(monkeypatch, name, fused_norm):
     used = set(calls)
     assert {"rmsnorm", "linear", "mla_qkv_post", "q_absorb", "mla_attention", "v_up", "moe_gate", "moe_ffn", "argmax", "topk_logits",
             "sample_topk", "embed_gather"} <= used, sorted(used)
+
+
+def test_prompt_attention_form_is_chosen_by_what_would_be_expanded():
+    """The per-head prompt attention expands the cached rows of every sequence of the step: it is taken for prompt chunks, not
+    for small batches, other head sizes, or mixed steps whose rows are mostly the contexts of sequences that only decode."""
+    ok = native.mha_prefill_ok
+    dims = (128, 64, 128, 512, 64)
+    assert ok(2048, *dims, {"total_kv": 2048, "n_q_tiles": 16})
+    assert ok(2048, *dims, {"total_kv": 2048 + 30000, "n_q_tiles": 16, "kv_decode": 0})          # a chunk deep into a long prompt
+    assert ok(2048, *dims, {"total_kv": 2048 + 1500, "n_q_tiles": 17, "kv_decode": 1500})        # one decoding neighbour
+    assert not ok(2048, *dims, {"total_kv": 2048 + 64 * 4000, "n_q_tiles": 80, "kv_decode": 64 * 4000})
+    assert not ok(32, *dims, {"total_kv": 32, "n_q_tiles": 1})                                    # below the size that pays
+    assert not ok(2048, 32, 16, 32, 64, 64, {"total_kv": 2048, "n_q_tiles": 16})                  # not the DeepSeek head sizes
+    assert not ok(2048, *dims, None)
