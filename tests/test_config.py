@@ -11,11 +11,13 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_shipped_configs_load():
     files = sorted(glob.glob(os.path.join(ROOT, "configs", "*.yaml")))
-    assert len(files) == 5          # the four reference configs + EP with data-parallel attention
+    assert len(files) == 6          # the four reference configs + EP with data-parallel attention + column-sharded experts
     for f in files:
         c = load_yaml(f)
         assert c.model.endswith(".gguf") and c.n_parallel >= 8
     assert load_yaml(os.path.join(ROOT, "configs", "config_deepseek_v2_ep.yaml")).world_size == 8
+    tp = load_yaml(os.path.join(ROOT, "configs", "config_deepseek_v2_tp.yaml"))
+    assert tp.world_size == 8 and tp.ep_size == 1 and tp.run_ahead
 
 
 def test_reference_style_file_and_defaults(tmp_path):
