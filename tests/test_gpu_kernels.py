@@ -92,6 +92,17 @@ def test_gemm_several_waves_takes_the_persistent_kernel(nat, monkeypatch):
     y3 = nat.moe_experts(xm, ids, wts, eg, eu, ed, 0)
     close(y3, ref.moe_experts(xm, ids, wts, eg, eu, ed, 0), tol=3e-2)
     nat.check_status()
+    # a rank's share of every DeepSeek-V2 expert at TP 8 (192 of 1536 FFN columns: a ragged second feature tile for gate|up,
+    # three k-blocks for down) at prompt-chunk size
+    T, E, k, d, F = 1024, 160, 6, 5120, 192
+    xm = rnd(T, d, scale=0.3)
+    eg, eu, ed = rnd(E, F, d, scale=0.02), rnd(E, F, d, scale=0.02, seed=5), rnd(E, d, F, scale=0.05)
+    g = torch.Generator().manual_seed(T)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).int().to(DEV)
+    wts = torch.rand(T, k, generator=g).to(DEV)
+    y5 = nat.moe_experts(xm, ids, wts, eg, eu, ed, 0)
+    close(y5, ref.moe_experts(xm, ids, wts, eg, eu, ed, 0), tol=3e-2)
+    nat.check_status()
     # the same three through the other kernel (the switch is read once per process by the library: a child process)
     import subprocess, sys
     code = ("import torch, sys; sys.path.insert(0, %r); from tests.test_gpu_kernels import rnd, DEV; from jittorinfer_b200.ops import native as nat; nat.load();"
