@@ -99,16 +99,18 @@ def test_dp_server_two_cpu_ranks():
                 p.terminate()
 
 
-def test_mpi_server_launcher_two_cpu_ranks(tmp_path):
+@pytest.mark.parametrize("ep_size", [2, 1])
+def test_mpi_server_launcher_two_cpu_ranks(tmp_path, ep_size):
     """The real entry point: ``python -m jittorinfer_b200.server.mpi_server --nproc 2`` spawns the ranks, rank 0 serves
-    HTTP, the ranks run tensor-parallel with identical schedulers, heartbeats are on, ``GET /exit`` stops every rank."""
+    HTTP, the ranks run tensor-parallel with identical schedulers, heartbeats are on, ``GET /exit`` stops every rank.
+    ``ep_size`` 2: whole experts per rank; 1: every expert's FFN columns sharded over the ranks."""
     import subprocess
     from jittorinfer_b200.models.hparams import preset
     from jittorinfer_b200.models.oracle import OracleModel
     from jittorinfer_b200.models.weights import random_weights
     hport, mport = _free_port(), _free_port()
     cfg = tmp_path / "c.yaml"
-    cfg.write_text(f"random_init: tiny-v2\nn_ctx: 1024\nn_parallel: 2\nn_batch: 64\nport: {hport}\nenable_ge: false\ntp_size: 2\nep_size: 2\n")
+    cfg.write_text(f"random_init: tiny-v2\nn_ctx: 1024\nn_parallel: 2\nn_batch: 64\nport: {hport}\nenable_ge: false\ntp_size: 2\nep_size: {ep_size}\n")
     env = dict(os.environ, JITTORINFER_COMM="nccl", JITTORINFER_HEARTBEAT_TIMEOUT="20")
     p = subprocess.Popen([sys.executable, "-m", "jittorinfer_b200.server.mpi_server", "--nproc", "2", "--master-port", str(mport),
                           "-c", str(cfg)], cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
