@@ -385,13 +385,13 @@ int jib_rmsnorm(const void * x, const void * residual, const float * w, void * o
     cudaStream_t s = (cudaStream_t) stream;
     const int nv = d / 8;
     if (nv <= 128)
-        JIB_LAUNCH((rmsnorm_kernel<128, 1>), T, 128, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
+        JIB_LAUNCH((rmsnorm_kernel<128, 1>), T, 128, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_for(T));
     else if (nv <= 256)
-        JIB_LAUNCH((rmsnorm_kernel<256, 1>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
+        JIB_LAUNCH((rmsnorm_kernel<256, 1>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_for(T));
     else if (nv <= 1024)
-        JIB_LAUNCH((rmsnorm_kernel<256, 4>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
+        JIB_LAUNCH((rmsnorm_kernel<256, 4>), T, 256, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_for(T));
     else if (nv <= 2048)
-        JIB_LAUNCH((rmsnorm_kernel<512, 4>), T, 512, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_enabled());
+        JIB_LAUNCH((rmsnorm_kernel<512, 4>), T, 512, 0, s, (const bf16 *) x, (const bf16 *) residual, w, (bf16 *) out_norm, (bf16 *) out_sum, d, x_stride, eps, jib::warm_for(T));
     else
         return JIB_E_ARG;
     return launched();
@@ -406,7 +406,7 @@ int jib_mla_qkv_post(const void * q, long long q_stride, const void * ckv, long 
     JIB_LAUNCH((mla_qkv_post_kernel<256>), T, 256, 0, (cudaStream_t) stream, (const bf16 *) q, q_stride, (const bf16 *) ckv, ckv_stride, kv_norm_w,
                                                                     eps, rope_table, positions, slot_mapping, (bf16 *) cache,
                                                                     (bf16 *) q_out, qo_row, qo_head, H, dn, dr, r, max_pos, n_slots, status,
-                                                                    jib::warm_enabled());
+                                                                    jib::warm_for(T));
     return launched();
 }
 

@@ -258,7 +258,7 @@ extern "C" int jib_mla_attention(const void * q, const void * cache, const int *
                                                               part_ml, (bf16 *) o_lat);                                          \
         if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;                                                              \
         if (n_splits > 1) {                                                                                                      \
-            JIB_LAUNCH((mla_attn_combine_kernel<R_>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_enabled());                \
+            JIB_LAUNCH((mla_attn_combine_kernel<R_>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_for(T));                \
             if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;                                                          \
         }                                                                                                                        \
         return 0;                                                                                                                \
@@ -275,8 +275,8 @@ extern "C" int jib_mla_combine(const float * part_o, const float * part_ml, int 
     if (T <= 0) return 0;
     if (n_splits < 1 || n_splits > 32) return JIB_E_ARG;
     cudaStream_t s = (cudaStream_t) stream;
-    if (r == 512) JIB_LAUNCH((mla_attn_combine_kernel<512>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_enabled());
-    else if (r == 64) JIB_LAUNCH((mla_attn_combine_kernel<64>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_enabled());
+    if (r == 512) JIB_LAUNCH((mla_attn_combine_kernel<512>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_for(T));
+    else if (r == 64) JIB_LAUNCH((mla_attn_combine_kernel<64>), dim3(T, H), 128, 0, s, part_o, part_ml, n_splits, H, (bf16 *) o_lat, jib::warm_for(T));
     else return JIB_E_ARG;
     return cudaGetLastError() == cudaSuccess ? 0 : JIB_E_LAUNCH;
 }

@@ -754,10 +754,10 @@ int jib_moe_gate(const void * g, const float * w_router, const float * bias, flo
     if (T <= 0) return 0;
     if (E > MAX_E || k + n_shared > 32 || n_shared < 0 || k > E || d % 8 || d > GATE_MAXC * GATE_NT * 8 || n_group > 32 || (n_group > 1 && E % n_group)) return JIB_E_ARG;
     JIB_LAUNCH((router_logits_kernel), dim3(E, (T + 63) / 64), GATE_NT, 0, (cudaStream_t) stream, (const bf16 *) g, w_router, logits, T, d, E,
-               jib::warm_enabled());
+               jib::warm_for(T));
     if (cudaGetLastError() != cudaSuccess) return JIB_E_LAUNCH;
     JIB_LAUNCH((moe_gate_kernel), T, 32, 0, (cudaStream_t) stream, logits, bias, ids, wts, E, k, n_group, topk_group, scale, norm, sigmoid, n_shared, group_top2,
-               jib::warm_enabled());
+               jib::warm_for(T));
     return launched();
 }
 
@@ -782,7 +782,7 @@ int jib_moe_permute(const int * ids, int T, int k, int expert_base, int E_local,
     if (T <= 0) return 0;
     if (E_local > MAX_E) return JIB_E_ARG;
     JIB_LAUNCH((moe_permute_kernel), 1, 1024, 0, (cudaStream_t) stream, ids, T * k, k, expert_base, E_local, seg, src_token, dest,
-               jib::warm_enabled(), seg + E_local + 1);
+               jib::warm_for(T), seg + E_local + 1);
     return launched();
 }
 
@@ -813,7 +813,7 @@ int jib_moe_combine(const void * y, const int * dest, const float * wts, const v
     if (T <= 0) return 0;
     if (d % 8) return JIB_E_ARG;
     JIB_LAUNCH((moe_combine_kernel), T, 256, 0, (cudaStream_t) stream, (const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual,
-                                                              (bf16 *) out, k, d, jib::warm_enabled());
+                                                              (bf16 *) out, k, d, jib::warm_for(T));
     return launched();
 }
 
@@ -826,7 +826,7 @@ int jib_moe_combine_norm(const void * y, const int * dest, const float * wts, co
     cudaStream_t s = (cudaStream_t) stream;
 #define JIB_CN(NT, MAXV)                                                                                                         \
     JIB_LAUNCH((moe_combine_norm_kernel<NT, MAXV>), T, NT, 0, s, (const bf16 *) y, dest, wts, (const bf16 *) shared, (const bf16 *) residual, \
-               norm_w, (bf16 *) out, (bf16 *) out_norm, k, d, eps, jib::warm_enabled())
+               norm_w, (bf16 *) out, (bf16 *) out_norm, k, d, eps, jib::warm_for(T))
     if (nv <= 128) JIB_CN(128, 1);            // the same (threads, values per thread) choice as jib_rmsnorm
     else if (nv <= 256) JIB_CN(256, 1);
     else if (nv <= 1024) JIB_CN(256, 4);

@@ -69,6 +69,11 @@ inline int warm_enabled() {
     return on;
 }
 
+// ... for launches of up to `WARM_MAX_ROWS` rows only: in a grid of thousands of CTAs every CTA would pay for the dry pass while
+// only the first one on each SM finds cold code.
+constexpr int WARM_MAX_ROWS = 256;
+inline int warm_for(long long rows) { return (warm_enabled() && rows <= WARM_MAX_ROWS) ? 1 : 0; }
+
 // cluster_z > 1: consecutive blockIdx.z values form a thread-block cluster of that size.
 template <typename... P, typename... A>
 inline cudaError_t launch_pdl_cluster(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_z,
