@@ -166,9 +166,11 @@ mha_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 for (int kk = 0; kk < KT / 16; ++kk)
                     mma_bf16(tm_O, desc_k_sw128(p_addr + (kk >> 2) * CHUNK + (kk & 3) * 32), desc_mn_sw128(v_addr + kk * 2048, CHUNK, 1024),
                              idesc_pv, (t | kk) != 0);
+                // o_done first: a softmax warp that has seen p_empty of this product must find o_done of the same product
+                // complete as well, or its parity wait at the end (or before a rescale) could be answered by the phase before
+                mma_commit(o_done);
                 mma_commit(v_empty);
                 mma_commit(p_empty);
-                mma_commit(o_done);
             };
             for (int kt = 0; kt < n_tiles && ok; ++kt) {
                 const int s = kt & 1;

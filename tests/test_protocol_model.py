@@ -386,3 +386,68 @@ def test_the_pipeline_model_catches_a_single_accumulator_set():
     with pytest.raises(AssertionError):
         for seed in range(40):
             _PhaseSim(broken(4, 2, 7), seed, 1).run()
+
+
+# ---- the prompt-attention kernel's roles (mha_prefill_kernel): TMA producer, MMA issuer, four softmax warps ---------------------------
+# K tiles are double-buffered, the V and P tiles single, S double-buffered in tensor memory; Q.K^T of tile t + 1 is issued before
+# P.V of tile t.  Tags: ("K", t) in a K slot, ("V", t), ("S", t) in an S buffer, ("P", t).
+def _mha_roles(n_tiles, n_smx=4, rescale_at=()):
+    def producer():
+        for t in range(n_tiles):
+            s = t & 1
+            yield ("wait", _phase_wait(("k_empty", s), ((t >> 1) & 1) ^ 1))
+            yield ("store", ("K", s), t)
+            yield ("add", ("k_full", s))
+            yield ("wait", _phase_wait(("v_empty",), (t & 1) ^ 1))
+            yield ("store", ("V",), t)
+            yield ("add", ("v_full",))
+
+    def mma():
+        def pv(t):
+            yield ("wait", _phase_wait(("p_full",), t & 1))
+            yield ("wait", _phase_wait(("v_full",), t & 1))
+            yield ("check", ("P",), t)
+            yield ("check", ("V",), t)
+            yield ("store", ("O",), t)
+            yield ("add", ("o_done",))          # committed first: see the kernel
+            yield ("add", ("v_empty",))
+            yield ("add", ("p_empty",))
+        for t in range(n_tiles):
+            s, ph = t & 1, (t >> 1) & 1
+            yield ("wait", _phase_wait(("k_full", s), ph))
+            yield ("wait", _phase_wait(("s_empty", s), ph ^ 1))
+            yield ("check", ("K", s), t)
+            yield ("store", ("S", s), t)
+            yield ("add", ("k_empty", s))
+            yield ("add", ("s_full", s))
+            if t >= 1:
+                yield from pv(t - 1)
+        yield from pv(n_tiles - 1)
+
+    def softmax(w):
+        for t in range(n_tiles):
+            s = t & 1
+            yield ("wait", _phase_wait(("s_full", s), (t >> 1) & 1))
+            yield ("check", ("S", s), t)
+            yield ("arrive", ("s_empty", s), n_smx)           # scores are in registers: the S buffer goes back at once
+            if t in rescale_at and t > 0:                       # the exponent base moved: O is rescaled after the products in flight
+                yield ("wait", _phase_wait(("o_done",), (t - 1) & 1))
+                yield ("check", ("O",), t - 1)
+            if t > 0:
+                yield ("wait", _phase_wait(("p_empty",), (t - 1) & 1))
+            if w == 0:
+                yield ("store", ("P",), t)
+            yield ("arrive", ("p_full",), n_smx)
+        yield ("wait", _phase_wait(("o_done",), (n_tiles - 1) & 1))
+        yield ("check", ("O",), n_tiles - 1)
+    return [producer(), mma()] + [softmax(w) for w in range(n_smx)]
+
+
+@pytest.mark.parametrize("n_tiles", [1, 2, 3, 8, 17])
+def test_prompt_attention_pipeline_never_reads_a_tile_out_of_turn(n_tiles):
+    """(This model found that the three barriers a P.V product completes must be completed with o_done first: with o_done last a
+    softmax warp could see p_empty of product t, finish tile t + 1 and ask for o_done while that barrier was still a whole
+    phase behind -- and a parity wait cannot tell "the phase before" from "this phase".)"""
+    for seed in range(40):
+        for bias in (None, 0, 1, 2):
+            _PhaseSim(_mha_roles(n_tiles, rescale_at=(1, 2, 5, 16)), seed, bias).run()
