@@ -451,3 +451,64 @@ def test_prompt_attention_pipeline_never_reads_a_tile_out_of_turn(n_tiles):
     for seed in range(40):
         for bias in (None, 0, 1, 2):
             _PhaseSim(_mha_roles(n_tiles, rescale_at=(1, 2, 5, 16)), seed, bias).run()
+
+
+# ---- the decode attention kernel's roles (mla_flash_kernel): TMA producer, MMA issuer, four softmax warps -------------------------------
+# A ring of latent "pair" slots (4 pairs per KV tile, NPAIR slots) that BOTH products of a tile read, two slots for the rope
+# chunk, one S buffer, one P buffer, O accumulated in place.
+def _flash_roles(n_tiles, npair, n_smx=4):
+    def producer():
+        for it in range(n_tiles):
+            s = it & 1
+            yield ("wait", _phase_wait(("rope_free", s), ((it >> 1) & 1) ^ 1))
+            yield ("store", ("rope", s), it)
+            yield ("add", ("rope_full", s))
+            for m in range(4):
+                u = it * 4 + m
+                s = u % npair
+                yield ("wait", _phase_wait(("lat_free", s), ((u // npair) & 1) ^ 1))
+                yield ("store", ("lat", s), (it, m))
+                yield ("add", ("lat_full", s))
+
+    def mma():
+        for it in range(n_tiles):
+            for m in range(4):
+                u = it * 4 + m
+                s = u % npair
+                yield ("wait", _phase_wait(("lat_full", s), (u // npair) & 1))
+                yield ("check", ("lat", s), (it, m))
+            s = it & 1
+            yield ("wait", _phase_wait(("rope_full", s), (it >> 1) & 1))
+            yield ("check", ("rope", s), it)
+            yield ("add", ("rope_free", s))
+            yield ("store", ("S",), it)
+            yield ("add", ("s_ready",))
+            yield ("wait", _phase_wait(("p_ready",), it & 1))
+            yield ("check", ("P",), it)
+            for m in range(4):
+                s = (it * 4 + m) % npair
+                yield ("check", ("lat", s), (it, m))          # the second product reads the same copy of the tile
+                yield ("add", ("lat_free", s))
+            yield ("store", ("O",), it)
+            yield ("add", ("o_ready",))
+
+    def softmax(w):
+        for it in range(n_tiles):
+            yield ("wait", _phase_wait(("s_ready",), it & 1))
+            yield ("check", ("S",), it)
+            if it > 0:
+                yield ("wait", _phase_wait(("o_ready",), (it - 1) & 1))
+                yield ("check", ("O",), it - 1)                 # running-max correction of what the products so far left
+            if w == 0:
+                yield ("store", ("P",), it)
+            yield ("arrive", ("p_ready",), n_smx)
+        yield ("wait", _phase_wait(("o_ready",), (n_tiles - 1) & 1))
+        yield ("check", ("O",), n_tiles - 1)
+    return [producer(), mma()] + [softmax(w) for w in range(n_smx)]
+
+
+@pytest.mark.parametrize("n_tiles,npair", [(1, 5), (2, 4), (3, 5), (9, 4), (10, 5)])
+def test_decode_attention_pipeline_never_reads_a_tile_out_of_turn(n_tiles, npair):
+    for seed in range(40):
+        for bias in (None, 0, 1, 2):
+            _PhaseSim(_flash_roles(n_tiles, npair), seed, bias).run()
