@@ -316,7 +316,8 @@ struct DryCtx {
     float multiplier, base;
     int32_t allowed_length, last_n;
     std::vector<uint8_t> is_breaker;    // per token id: the token's text contains a breaker string
-    std::vector<std::vector<llama_token>> multi;   // breaker strings that no single token contains, as token sequences
+    std::vector<std::vector<llama_token>> multi;   // breakers spelled with several tokens, as token sequences
+    std::unordered_map<llama_token, std::vector<int32_t>> by_last;     // last token of a sequence -> indices into multi
     std::vector<llama_token> hist;      // most recent last, capped at the effective window
     int32_t window() const { return last_n < 0 ? n_ctx_train : last_n; }
 };
@@ -340,11 +341,17 @@ void dry_apply(llama_sampler * s, arr_t * a) {
     size_t cap = 0;
     while (cap < n && !breaker(h[n - 1 - cap])) ++cap;
     // ... nor across a breaker that is spelled with several tokens: the most recent place where such a sequence ends
-    for (const std::vector<llama_token> & seq : c->multi) {
-        const size_t L = seq.size();
-        for (size_t back = 0; back < cap && back + L <= n; ++back) {       // the sequence ends `back` tokens before the end
-            const llama_token * at = h + (n - back - L);
-            if (std::equal(seq.begin(), seq.end(), at)) { cap = back; break; }
+    if (!c->multi.empty()) {
+        for (size_t back = 0; back < cap; ++back) {                        // a sequence that ends `back` tokens before the end
+            auto it = c->by_last.find(h[n - 1 - back]);
+            if (it == c->by_last.end()) continue;
+            bool hit = false;
+            for (int32_t idx : it->second) {
+                const std::vector<llama_token> & seq = c->multi[(size_t) idx];
+                const size_t L = seq.size();
+                if (back + L <= n && std::equal(seq.begin(), seq.end(), h + (n - back - L))) { hit = true; break; }
+            }
+            if (hit) { cap = back; break; }
         }
     }
     if (cap == 0) return;
@@ -636,21 +643,38 @@ llama_sampler * llama_sampler_init_dry(const llama_vocab * vocab, int32_t n_ctx_
             if (seq_breakers[i] != nullptr && seq_breakers[i][0] != 0) brk.emplace_back(seq_breakers[i]);
         char buf[256];
         std::vector<uint8_t> found(brk.size(), 0);
+        llama_token ids[64];
         for (int32_t t = 0; t < V && !brk.empty(); ++t) {
             const int32_t len = llama_token_to_piece(vocab, t, buf, (int32_t) sizeof(buf), 0, true);
             if (len <= 0) continue;
             const std::string piece(buf, (size_t) len);
-            for (size_t i = 0; i < brk.size(); ++i)
-                if (piece.find(brk[i]) != std::string::npos) { c->is_breaker[(size_t) t] = 1; found[i] = 1; }
+            for (size_t i = 0; i < brk.size(); ++i) {
+                const std::string & b = brk[i];
+                if (piece.find(b) != std::string::npos) { c->is_breaker[(size_t) t] = 1; found[i] = 1; continue; }
+                // the breaker may begin inside this token: the token's last characters are the breaker's first ones, the rest
+                // follows as the tokens the remainder tokenises to (the reference's head-token table, src/llama-sampling.cpp:895)
+                for (size_t ov = std::min(piece.size(), b.size() - 1); ov >= 1; --ov) {
+                    if (piece.compare(piece.size() - ov, ov, b, 0, ov) != 0) continue;
+                    const std::string rest = b.substr(ov);
+                    const int32_t n = llama_tokenize(vocab, rest.c_str(), (int32_t) rest.size(), ids, 63, false, false);
+                    if (n >= 1 && c->multi.size() < 4096) {
+                        std::vector<llama_token> seq;
+                        seq.push_back(t);
+                        seq.insert(seq.end(), ids, ids + n);
+                        c->multi.push_back(std::move(seq));
+                    }
+                    break;                                 // the longest overlap only
+                }
+            }
         }
         // a breaker that only ever appears spread over several tokens is matched as the token sequence it tokenises to
         // (the reference keeps head token -> tail sequences for the same purpose, src/llama-sampling.cpp:895)
         for (size_t i = 0; i < brk.size(); ++i) {
             if (found[i]) continue;
-            llama_token ids[64];
             const int32_t n = llama_tokenize(vocab, brk[i].c_str(), (int32_t) brk[i].size(), ids, 64, false, false);
             if (n >= 2) c->multi.emplace_back(ids, ids + n);
         }
+        for (size_t i = 0; i < c->multi.size(); ++i) c->by_last[c->multi[i].back()].push_back((int32_t) i);
     }
     return llama_sampler_init(&dry_i, c);
 }

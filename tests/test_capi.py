@@ -172,6 +172,12 @@ def test_dry_breaker_spelled_with_several_tokens(L, gguf_path):
     assert abs(penalty_on_z([]) - 0.8 * 1.75 ** 3) < 1e-4              # repeat of length 5, allowed 2
     assert abs(penalty_on_z(["ab"]) - 0.8) < 1e-5                      # only "x y" after the breaker counts: length 2
     assert abs(penalty_on_z(["y"]) - 0.0) < 1e-6                       # a one-token breaker right at the end: no match at all
+    # a breaker that begins inside a token: "ex" over the merged token "he" followed by "x"
+    (he,) = ids("he")
+    assert len(ids("he")) == 1 and len(ids("ex")) == 2
+    hist[:] = [q, he, x, a, y, z, q, he, x, a, y]                      # "q he x a y" repeats; "ex" sits across "he" | "x"
+    assert abs(penalty_on_z([]) - 0.8 * 1.75 ** 3) < 1e-4
+    assert abs(penalty_on_z(["ex"]) - 0.8) < 1e-5                      # only "a y" after the breaker counts
     L.llama_model_free(model)
 
 
