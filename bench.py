@@ -334,20 +334,25 @@ def main():
         del eng
         if cuda:
             torch.cuda.empty_cache()
-        hp2 = preset("v2").replace(n_layer=args.same_model_layers)
-        eng2 = build_engine(hp2, device=dev, world=world, rank=rank, expert_parallel=ep_shard, n_parallel=C, n_ctx_slot=total_len + 64, n_batch=2048,
-                            seed=0, graph_buckets=buckets(C), comm=comm)
-        note(f"same_model built: {eng2.model.weight_bytes() / 2**30:.1f} GiB on this rank")
-        eng2.warmup()
-        rec = {}
-        for c in ([C] if args.no_sweep else sorted({1, C})):
-            rec[str(c)] = record(eng2, hp2, c, False)
-        same_model = {"model": f"DeepSeek-V2 architecture, {hp2.n_layer} layers, random init", "parallelism": (f"tp{world}+ep{world}" if ep_shard else f"tp{world}") if world > 1 else "single GPU",
-                      "scaling": "strong", "global_batch": C, "value": rec[str(C)]["value"], "unit": "tokens/s", "by_concurrency": rec}
-        synchronize()
-        if args.ops == "native" and cuda:
-            ops.nat().check_status()
-        note(f"same_model: {same_model['value']} tok/s at concurrency {C}")
+        try:       # a sub-record: whatever goes wrong here (memory for the second model, ...) must not take the headline with it
+            hp2 = preset("v2").replace(n_layer=args.same_model_layers)
+            eng2 = build_engine(hp2, device=dev, world=world, rank=rank, expert_parallel=ep_shard, n_parallel=C, n_ctx_slot=total_len + 64,
+                                n_batch=2048, seed=0, graph_buckets=buckets(C), comm=comm)
+            note(f"same_model built: {eng2.model.weight_bytes() / 2**30:.1f} GiB on this rank")
+            eng2.warmup()
+            rec = {}
+            for c in ([C] if args.no_sweep else sorted({1, C})):
+                rec[str(c)] = record(eng2, hp2, c, False)
+            same_model = {"model": f"DeepSeek-V2 architecture, {hp2.n_layer} layers, random init",
+                          "parallelism": (f"tp{world}+ep{world}" if ep_shard else f"tp{world}") if world > 1 else "single GPU",
+                          "scaling": "strong", "global_batch": C, "value": rec[str(C)]["value"], "unit": "tokens/s", "by_concurrency": rec}
+            synchronize()
+            if args.ops == "native" and cuda:
+                ops.nat().check_status()
+            note(f"same_model: {same_model['value']} tok/s at concurrency {C}")
+        except Exception as e:
+            same_model = {"error": f"{type(e).__name__}: {e}"}
+            note(f"same_model failed: {same_model['error']}")
 
     if rank == 0:
         full = (model_name == "lite" and world == 1 and hp.n_layer == 27) or (model_name == "v2" and world == 8 and hp.n_layer == 60)
