@@ -109,10 +109,17 @@ def prefill_launches(hp: DeepSeek2HParams, T: int, world: int = 1) -> List[Tuple
     else:
         gemm("GEMM q + kv_a", H * (dn + dr) + r + dr, d)
     elem("mla_qkv_post (kv norm, RoPE, cache write)", T * (H * (dn + dr) + r + dr) * 2 * 2)
-    gemm("GEMM q_absorb (batched per head)", H * r, dn, note="per head 128 -> 512", weights=H * dn * r)
-    out.append(("flash MLA (absorbed, causal)", 2.0 * H * (T * T / 2) * ((r + dr) + r), float(T * (r + dr) * 2 + T * H * (2 * r + dr) * 2),
-                "scores over 576 dims, values over 512"))
-    gemm("GEMM v_up (batched per head)", H * dv, r, note="per head 512 -> 128", weights=H * r * dv)
+    if (dn, dr, dv, r) == (128, 64, 128, 512) and T >= 64:
+        # prompt chunks at the DeepSeek head sizes run the per-head form: K / V expanded from the latent rows by one GEMM
+        elem("kv gather (latent rows of the chunk's sequences)", T * (r + dr) * 2 * 2)
+        gemm("GEMM K/V expansion (k_nope | v per head)", H * (dn + dv), r)
+        out.append(("prompt attention (per head, causal)", 2.0 * H * (T * (T + 1) / 2) * ((dn + dr) + dv),
+                    float(T * H * (dn + dr) * 2 + T * H * (dn + dv) * 2 + T * dr * 2 + T * H * dv * 2), "scores over 192 dims, values over 128"))
+    else:
+        gemm("GEMM q_absorb (batched per head)", H * r, dn, note="per head 128 -> 512", weights=H * dn * r)
+        out.append(("flash MLA (absorbed, causal)", 2.0 * H * (T * T / 2) * ((r + dr) + r), float(T * (r + dr) * 2 + T * H * (2 * r + dr) * 2),
+                    "scores over 576 dims, values over 512"))
+        gemm("GEMM v_up (batched per head)", H * dv, r, note="per head 512 -> 128", weights=H * r * dv)
     gemm("GEMM o_proj (+ residual" + (", + all-reduce" if world > 1 else "") + ")", d, H * dv)
     elem("rmsnorm (ffn_norm)", T * d * 2 * 2)
     out.append(("router logits (fp32)", 2.0 * T * E * d, float(E * d * 4 + T * d * 2), ""))

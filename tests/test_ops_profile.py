@@ -78,7 +78,12 @@ def test_expected_prefill_bounds():
     hp = preset("lite")
     rows = {k: (f, b) for k, f, b, _ in prefill_launches(hp, 2048, 1)}
     assert rows["GEMM o_proj (+ residual)"][0] == 2.0 * 2048 * 2048 * 2048
-    assert abs(rows["flash MLA (absorbed, causal)"][0] - 2.0 * 16 * (2048 * 2048 / 2) * (576 + 512)) < 1
+    # DeepSeek head sizes: a prompt chunk runs the per-head form (K / V expanded by one GEMM); small batches and other head
+    # sizes keep the absorbed form
+    assert abs(rows["prompt attention (per head, causal)"][0] - 2.0 * 16 * (2048 * 2049 / 2) * (192 + 128)) < 1
+    assert rows["GEMM K/V expansion (k_nope | v per head)"][0] == 2.0 * 2048 * (16 * 256) * 512
+    tiny = {k: f for k, f, _, _ in prefill_launches(preset("tiny"), 128, 1)}
+    assert "flash MLA (absorbed, causal)" in tiny and "GEMM q_absorb (batched per head)" in tiny
     assert abs(rows["grouped GEMM gate|up"][0] - 2.0 * 2048 * 8 * 2 * 1408 * 2048) < 1
     text = report_prefill(hp, 2048, 1, 6.5e12, 1360.0, measured_ms=55)
     assert "27 layers" in text and "of the bound" in text
